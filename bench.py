@@ -1,0 +1,455 @@
+#!/usr/bin/env python
+"""Benchmark of the B200 provider's hot path.
+
+Headline workload (the only one that shards): the Q8_0 sweep point R x 8192 bf16 -> Q8_0 blocks +
+decoded bf16 + sum of squares, row-sharded over the ranks, per-rank sums combined by one NCCL
+all-reduce.  A step is one pass over the whole tensor.  `value` is Gelem/s with the input resident
+in HBM; `e2e` is the same pass from pinned HOST buffers through the C ABI (host->device and
+device->host copies inside the timed region); `ops` lists the other operators' largest shapes.
+
+    python bench.py [--gpus N] [--steps K] [--warmup W]            # this library
+    python bench.py --impl reference [...]                          # the CPU provider restated, host cores
+    torchrun --nproc-per-node N bench.py --gpus N ...               # one rank per GPU
+"""
+from __future__ import annotations
+
+import argparse
+import json
+import os
+import statistics
+import subprocess
+import sys
+import time
+
+ROOT = os.path.dirname(os.path.abspath(__file__))
+sys.path.insert(0, ROOT)
+
+import numpy as np  # noqa: E402
+
+SWEEP_COLS = 8192
+DEFAULT_ROWS = 262144                       # 4 GiB of bf16: the largest sweep point
+BYTES_PER_ELEMENT = 2 + 34 / 32 + 2         # read bf16, write Q8_0 block share, write decoded bf16
+# dram__bytes_read.sum + dram__bytes_write.sum per element of the roundtrip kernel, from the ncu
+# capture summarised in profiles/ (None until a capture exists).
+NCU_TRAFFIC_BYTES_PER_ELEMENT = None
+FALLBACK_HBM_GBS = 6650.0
+METRIC = "Q8_0 quantise+dequantise+sum-of-squares sweep throughput"
+UNIT = "Gelem/s"
+
+
+def hbm_peak():
+    path = os.path.join(ROOT, "MEASURED_PEAKS.json")
+    try:
+        with open(path) as f:
+            return float(json.load(f)["hbm_gbs"]), "measured"
+    except Exception:
+        return FALLBACK_HBM_GBS, "fallback"
+
+
+class ClockSampler:
+    """nvidia-smi clocks and throttle reasons, sampled every 200 ms while the timed region runs."""
+
+    QUERY = ("index,clocks.sm,clocks.max.sm,power.draw,clocks_event_reasons.active,"
+             "clocks_event_reasons.hw_slowdown,clocks_event_reasons.hw_thermal_slowdown,"
+             "clocks_event_reasons.sw_thermal_slowdown,clocks_event_reasons.sw_power_cap")
+
+    def __init__(self, device_index: int):
+        self.device_index = device_index
+        self.process = None
+
+    def start(self):
+        try:
+            self.process = subprocess.Popen(
+                ["nvidia-smi", f"--query-gpu={self.QUERY}", "--format=csv,noheader,nounits", "-lms", "200",
+                 "-i", str(self.device_index)], stdout=subprocess.PIPE, stderr=subprocess.DEVNULL, text=True)
+        except OSError:
+            self.process = None
+
+    def stop(self):
+        if self.process is None:
+            return {"sm_mhz": None, "sm_max_mhz": None, "reasons": ["nvidia-smi unavailable"]}
+        self.process.terminate()
+        try:
+            out, _ = self.process.communicate(timeout=5)
+        except subprocess.TimeoutExpired:
+            self.process.kill()
+            out, _ = self.process.communicate()
+        clocks, max_clock, reasons = [], None, set()
+        names = ["hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap"]
+        for line in out.strip().splitlines():
+            parts = [p.strip() for p in line.split(",")]
+            if len(parts) < 9:
+                continue
+            try:
+                clocks.append(float(parts[1]))
+                max_clock = float(parts[2])
+            except ValueError:
+                continue
+            for name, flag in zip(names, parts[5:9]):
+                if flag.lower().startswith("active"):
+                    reasons.add(name)
+        return {"sm_mhz": statistics.median(clocks) if clocks else None, "sm_max_mhz": max_clock,
+                "reasons": sorted(reasons), "samples": len(clocks)}
+
+
+# ---------------------------------------------------------------------------------------------------------
+# reference arm: the CPU restatement of the provider's Q8_0 path on the host cores
+# ---------------------------------------------------------------------------------------------------------
+def cpu_sample_rows(oracle, target_seconds: float, max_rows: int) -> int:
+    """Rows of the sweep tensor the CPU gets through in about `target_seconds` (power of two)."""
+    from hyle_b200 import workloads as wl
+
+    probe_rows = 256
+    w = wl.q8_sweep_inputs(probe_rows)
+    oracle.q8_0_roundtrip(w)
+    t0 = time.perf_counter()
+    oracle.q8_0_roundtrip(w)
+    per_row = (time.perf_counter() - t0) / probe_rows
+    rows = probe_rows
+    while rows * 2 * per_row <= target_seconds and rows * 2 <= max_rows:
+        rows *= 2
+    return rows
+
+
+def time_cpu(oracle, rows: int, steps: int, warmup: int):
+    from hyle_b200 import workloads as wl
+
+    w = np.tile(wl.q8_sweep_inputs(min(rows, 1024)), (max(1, rows // 1024), 1))[:rows]
+    blocks = np.empty(w.size // 32 * 34, np.uint8)
+    decoded = np.empty(w.size, np.uint16)
+    for _ in range(warmup):
+        oracle.q8_0_roundtrip(w, blocks, decoded)
+    t0 = time.perf_counter()
+    for _ in range(steps):
+        oracle.q8_0_roundtrip(w, blocks, decoded)
+    seconds = (time.perf_counter() - t0) / steps
+    return w.size / seconds / 1e9, seconds
+
+
+def run_reference(args):
+    rank = int(os.environ.get("RANK", "0"))
+    if rank != 0:
+        return  # the CPU arm is one process on the host cores
+    from oracle.binding import Oracle
+
+    oracle = Oracle()
+    cores = os.cpu_count() or 1
+    oracle.set_threads(cores)
+    total_steps = max(1, args.steps + args.warmup)
+    rows = cpu_sample_rows(oracle, target_seconds=max(0.5, 120.0 / total_steps), max_rows=args.rows)
+    value, seconds = time_cpu(oracle, rows, args.steps, args.warmup)
+    sample = f"{rows} of {args.rows} rows x {SWEEP_COLS} per step ({rows * SWEEP_COLS * 2 / 2**20:.0f} MiB of bf16)"
+    line = {
+        "impl": "reference", "metric": METRIC, "value": value, "unit": UNIT, "n_gpus": args.gpus,
+        "steps": args.steps, "warmup": args.warmup, "ms_per_step": seconds * 1e3, "higher_is_better": True,
+        "scaling": "strong", "vs_baseline": None, "dtype": "bf16->q8_0(int8+f16)", "data": "synthetic",
+        "config": {"workload": f"Q8_0 sweep R={args.rows} x {SWEEP_COLS} bf16 (CPU sample: {sample})",
+                   "l2": "working set larger than the host caches"},
+        "cpu_baseline": {"value": value, "unit": UNIT, "cores": cores, "kind": "port", "sample": sample},
+        "e2e": {"value": value, "unit": UNIT, "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
+        "gpu_launches": 0,
+    }
+    print(json.dumps(line), flush=True)
+
+
+# ---------------------------------------------------------------------------------------------------------
+# this library
+# ---------------------------------------------------------------------------------------------------------
+def event_pairs_ms(pairs):
+    return [a.elapsed_time(b) for a, b in pairs]
+
+
+def time_op(torch, launch, sets: int, iterations: int = 40, warmup: int = 5):
+    """Average device time of `launch(i)` over rotating buffer sets (footprint >> L2), CUDA events."""
+    for i in range(warmup):
+        launch(i % sets)
+    torch.cuda.synchronize()
+    start, stop = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    start.record()
+    for i in range(iterations):
+        launch(i % sets)
+    stop.record()
+    torch.cuda.synchronize()
+    return start.elapsed_time(stop) / iterations
+
+
+def other_ops(torch, peak_gbs):
+    """Largest single-GPU shape of workloads 1-4: GB/s against algorithmic bytes, rotating inputs."""
+    from hyle_b200 import abi, ops
+
+    results = []
+    dev = "cuda"
+
+    def report(name, shape, elements, algorithmic_bytes, ms, sets):
+        gbs = algorithmic_bytes / (ms * 1e-3) / 1e9
+        results.append({"op": name, "shape": shape, "us": ms * 1e3, "GB/s": gbs, "Gelem/s": elements / (ms * 1e-3) / 1e9,
+                        "roofline_frac": gbs / peak_gbs, "algorithmic_bytes": algorithmic_bytes,
+                        "buffer_sets": sets})
+
+    # 1: f32 broadcast add + row sum + row max, 4096 x 4096
+    sets = 8
+    a = [torch.randn(4096, 4096, device=dev) for _ in range(sets)]
+    bias = torch.rand(4096, device=dev) * 2 - 1
+    c = [torch.empty_like(a[0]) for _ in range(sets)]
+    rs, rm = torch.empty(4096, device=dev), torch.empty(4096, device=dev)
+    lib, stream = abi.load(), torch.cuda.current_stream().cuda_stream
+    ms = time_op(torch, lambda i: lib.hyle_b200_add_bias_row_sum_max_f32(
+        stream, a[i].data_ptr(), bias.data_ptr(), c[i].data_ptr(), rs.data_ptr(), rm.data_ptr(), 4096, 4096), sets)
+    report("add_bias_row_sum_max_f32", "4096x4096", 4096 * 4096, 2 * 4096 * 4096 * 4 + 3 * 4096 * 4, ms, sets)
+    del a, c
+
+    # 2: bf16 residual add + RMSNorm, T = 4096, hidden 2048
+    sets = 16
+    x = [torch.randn(4096, 2048, device=dev).bfloat16() for _ in range(sets)]
+    r = [torch.randn(4096, 2048, device=dev).bfloat16() for _ in range(sets)]
+    w = (torch.rand(2048, device=dev) + 0.5).bfloat16()
+    y = [torch.empty_like(x[0]) for _ in range(sets)]
+    h = [torch.empty_like(x[0]) for _ in range(sets)]
+    ms = time_op(torch, lambda i: lib.hyle_b200_add_rms_norm_bf16(
+        stream, x[i].data_ptr(), r[i].data_ptr(), w.data_ptr(), abi.BF16, y[i].data_ptr(), h[i].data_ptr(),
+        4096, 2048, 1e-6), sets)
+    report("add_rms_norm_bf16", "4096x2048", 4096 * 2048, 4 * 4096 * 2048 * 2 + 2048 * 2, ms, sets)
+    del x, r, y, h
+
+    # 3: bf16 SwiGLU, T = 4096, 6144 columns
+    sets = 8
+    g = [(1.5 * torch.randn(4096, 6144, device=dev)).bfloat16() for _ in range(sets)]
+    u = [(1.5 * torch.randn(4096, 6144, device=dev)).bfloat16() for _ in range(sets)]
+    o = [torch.empty_like(g[0]) for _ in range(sets)]
+    ms = time_op(torch, lambda i: lib.hyle_b200_swiglu_bf16(
+        stream, g[i].data_ptr(), u[i].data_ptr(), o[i].data_ptr(), 4096, 6144, 6144, 6144), sets)
+    report("swiglu_bf16", "4096x6144", 4096 * 6144, 3 * 4096 * 6144 * 2, ms, sets)
+    del g, u, o
+
+    # 4: f32 logits -> lse, softmax bf16, argmax, B = 256, vocabulary 151936
+    sets = 4
+    rows, cols = 256, 151936
+    logits = [4.0 * torch.randn(rows, cols, device=dev) for _ in range(sets)]
+    probs = [torch.empty(rows, cols, dtype=torch.bfloat16, device=dev) for _ in range(sets)]
+    lse = torch.empty(rows, device=dev)
+    idx = torch.empty(rows, dtype=torch.int32, device=dev)
+    val = torch.empty(rows, device=dev)
+    ms = time_op(torch, lambda i: lib.hyle_b200_logits_reduce_f32(
+        stream, logits[i].data_ptr(), rows, cols, lse.data_ptr(), probs[i].data_ptr(), idx.data_ptr(),
+        val.data_ptr()), sets, iterations=20)
+    report("logits_reduce_f32", "256x151936", rows * cols, rows * cols * 6 + rows * 12, ms, sets)
+    del logits, probs
+    torch.cuda.empty_cache()
+    return results
+
+
+def run_e2e(torch, ops, abi, shard_rows: int, steps: int, warmup: int):
+    """One pass from pinned host buffers: chunks flow host -> device -> kernel -> host on rotating
+    streams so both copy directions and the kernels overlap."""
+    chunk_rows = min(shard_rows, 4096)                     # 64 MiB of bf16 per chunk
+    chunks = (shard_rows + chunk_rows - 1) // chunk_rows
+    lanes = min(3, chunks)
+    host_in = torch.empty((shard_rows, SWEEP_COLS), dtype=torch.bfloat16, pin_memory=True)
+    host_in.copy_(torch.randn(1024, SWEEP_COLS).mul_(0.02).bfloat16().repeat((shard_rows + 1023) // 1024, 1)[:shard_rows])
+    host_blocks = torch.empty(shard_rows * SWEEP_COLS // 32 * 34, dtype=torch.uint8, pin_memory=True)
+    host_decoded = torch.empty((shard_rows, SWEEP_COLS), dtype=torch.bfloat16, pin_memory=True)
+    host_sums = torch.empty(chunks, dtype=torch.float64, pin_memory=True)
+    streams = [torch.cuda.Stream() for _ in range(lanes)]
+    dev_in = [torch.empty((chunk_rows, SWEEP_COLS), dtype=torch.bfloat16, device="cuda") for _ in range(lanes)]
+    dev_blocks = [torch.empty(chunk_rows * SWEEP_COLS // 32 * 34, dtype=torch.uint8, device="cuda") for _ in range(lanes)]
+    dev_decoded = [torch.empty((chunk_rows, SWEEP_COLS), dtype=torch.bfloat16, device="cuda") for _ in range(lanes)]
+    dev_sums = torch.zeros(chunks, dtype=torch.float64, device="cuda")
+    workspaces = [ops.make_workspace("cuda") for _ in range(lanes)]
+    lib = abi.load()
+    block_bytes_per_row = SWEEP_COLS // 32 * 34
+
+    def one_pass():
+        for c in range(chunks):
+            lane = c % lanes
+            first = c * chunk_rows
+            rows = min(chunk_rows, shard_rows - first)
+            with torch.cuda.stream(streams[lane]):
+                dev_in[lane][:rows].copy_(host_in[first:first + rows], non_blocking=True)
+                abi.check("roundtrip", lib.hyle_b200_q8_0_roundtrip_bf16(
+                    streams[lane].cuda_stream, dev_in[lane].data_ptr(), rows * SWEEP_COLS, dev_blocks[lane].data_ptr(),
+                    dev_decoded[lane].data_ptr(), dev_sums[c:].data_ptr(), None, workspaces[lane].data_ptr(),
+                    workspaces[lane].numel()))
+                host_blocks[first * block_bytes_per_row:(first + rows) * block_bytes_per_row].copy_(
+                    dev_blocks[lane][:rows * block_bytes_per_row], non_blocking=True)
+                host_decoded[first:first + rows].copy_(dev_decoded[lane][:rows], non_blocking=True)
+        for s in streams:
+            s.synchronize()
+        host_sums.copy_(dev_sums)
+        return float(host_sums.sum())
+
+    for _ in range(warmup):
+        one_pass()
+    torch.cuda.synchronize()
+    t0 = time.perf_counter()
+    for _ in range(steps):
+        total = one_pass()
+    torch.cuda.synchronize()
+    seconds = (time.perf_counter() - t0) / steps
+    h2d = shard_rows * SWEEP_COLS * 2
+    d2h = shard_rows * block_bytes_per_row + shard_rows * SWEEP_COLS * 2 + chunks * 8
+    return seconds, h2d, d2h, total
+
+
+def run_gpu(args):
+    import torch
+    import torch.distributed as dist
+
+    from hyle_b200 import abi, ops
+    from hyle_b200 import workloads as wl
+
+    world = int(os.environ.get("WORLD_SIZE", "1"))
+    rank = int(os.environ.get("RANK", "0"))
+    local_rank = int(os.environ.get("LOCAL_RANK", "0"))
+    if world != args.gpus:
+        if world == 1 and args.gpus > 1:
+            raise SystemExit("for --gpus N > 1 launch with: python -m torch.distributed.run --nproc-per-node N bench.py --gpus N ...")
+        raise SystemExit(f"--gpus {args.gpus} but WORLD_SIZE={world}")
+    torch.cuda.set_device(local_rank)
+    if world > 1:
+        dist.init_process_group("nccl", device_id=torch.device("cuda", local_rank))
+    abi.load()  # fails loudly when libhyle_b200.so is missing
+
+    peak_gbs, peak_kind = hbm_peak()
+    shard = wl.shard_rows(args.rows, world, rank)
+    w = wl.q8_sweep_device_shard(shard)
+    count = w.numel()
+    blocks = torch.empty(ops.q8_0_bytes(count), dtype=torch.uint8, device="cuda")
+    decoded = torch.empty_like(w)
+    partial = torch.zeros(1, dtype=torch.float64, device="cuda")
+    status = torch.zeros(1, dtype=torch.int32, device="cuda")
+    workspace = ops.make_workspace("cuda")
+    lib = abi.load()
+    stream = torch.cuda.current_stream().cuda_stream
+
+    def step():
+        abi.check("roundtrip", lib.hyle_b200_q8_0_roundtrip_bf16(
+            stream, w.data_ptr(), count, blocks.data_ptr(), decoded.data_ptr(), partial.data_ptr(),
+            status.data_ptr(), workspace.data_ptr(), workspace.numel()))
+
+    def combine():
+        if world > 1:
+            dist.all_reduce(partial)  # the one exchange of the path: 8 bytes per rank over NVLink
+
+    for _ in range(args.warmup):
+        step()
+        combine()
+    torch.cuda.synchronize()
+
+    sampler = ClockSampler(local_rank)
+    if rank == 0:
+        sampler.start()
+    if world > 1:
+        dist.barrier()
+    torch.cuda.synchronize()
+    kernel_events = [(torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)) for _ in range(args.steps)]
+    start, stop = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    start.record()
+    for k in range(args.steps):
+        kernel_events[k][0].record()
+        step()
+        kernel_events[k][1].record()
+        combine()
+    stop.record()
+    torch.cuda.synchronize()
+    if world > 1:
+        dist.barrier()
+    elapsed_ms = torch.tensor([start.elapsed_time(stop)], dtype=torch.float64, device="cuda")
+    kernel_ms = torch.tensor([statistics.mean(event_pairs_ms(kernel_events))], dtype=torch.float64, device="cuda")
+    if world > 1:
+        dist.all_reduce(elapsed_ms, op=dist.ReduceOp.MAX)
+        dist.all_reduce(kernel_ms, op=dist.ReduceOp.MAX)
+    clocks = sampler.stop() if rank == 0 else None
+    sum_squares = float(partial.item())
+    if int(status.item()) != 0:
+        raise SystemExit("the Q8_0 kernel flagged invalid input on synthetic data")
+
+    # end-to-end from host buffers (every rank moves its own shard).  The pinned staging is
+    # 6.06 bytes per element; if that is more than a quarter of the free host memory per rank,
+    # time a leading part of the shard instead and say so.
+    e2e_steps = max(1, min(args.steps, 3))
+    e2e_rows = shard.rows
+    try:
+        import psutil
+        budget = psutil.virtual_memory().available // (4 * world)
+        while e2e_rows > 1024 and e2e_rows * SWEEP_COLS * 6.0625 > budget:
+            e2e_rows //= 2
+    except ImportError:
+        pass
+    e2e_seconds, h2d, d2h, _ = run_e2e(torch, ops, abi, e2e_rows, e2e_steps, 1)
+    e2e_seconds *= shard.rows / e2e_rows
+    h2d, d2h = h2d * shard.rows // e2e_rows, d2h * shard.rows // e2e_rows
+    e2e_t = torch.tensor([e2e_seconds], dtype=torch.float64, device="cuda")
+    if world > 1:
+        dist.all_reduce(e2e_t, op=dist.ReduceOp.MAX)
+
+    if rank != 0:
+        if world > 1:
+            dist.destroy_process_group()
+        return
+
+    total_elements = args.rows * SWEEP_COLS
+    ms_per_step = float(elapsed_ms.item()) / args.steps
+    value = total_elements / (ms_per_step * 1e-3) / 1e9
+    kernel_s = float(kernel_ms.item()) * 1e-3
+    algorithmic = BYTES_PER_ELEMENT * count
+    achieved = algorithmic / kernel_s / 1e9
+    roofline = {"bound": "hbm", "kernel": "q8_0_kernel<bf16, encode, decode, sum_squares>",
+                "achieved": achieved, "peak": peak_gbs, "unit": "GB/s", "frac": achieved / peak_gbs,
+                "peak_kind": peak_kind, "algorithmic_bytes_per_launch": algorithmic,
+                "launch_us": kernel_s * 1e6,
+                "traffic": None if NCU_TRAFFIC_BYTES_PER_ELEMENT is None else NCU_TRAFFIC_BYTES_PER_ELEMENT * count}
+
+    line = {
+        "metric": METRIC, "value": value, "unit": UNIT, "n_gpus": world, "steps": args.steps,
+        "warmup": args.warmup, "ms_per_step": ms_per_step, "higher_is_better": True, "scaling": "strong",
+        "vs_baseline": None, "dtype": "bf16->q8_0(int8+f16)", "data": "synthetic",
+        "config": {"workload": f"Q8_0 sweep R={args.rows} x {SWEEP_COLS} bf16 -> Q8_0 + decoded bf16 + sum of squares",
+                   "rows_per_gpu": shard.rows, "parallelism": f"row-sharded x{world}, one all-reduce of 8 bytes",
+                   "l2": "inputs larger than L2 (no flush needed)" if count * 2 > 4 * 126e6 else "input fits L2: cold-cache not guaranteed"},
+        "roofline": roofline,
+        "e2e": {"value": total_elements / float(e2e_t.item()) / 1e9, "unit": UNIT,
+                "h2d_bytes_per_step": h2d * world, "d2h_bytes_per_step": d2h * world, "steps": e2e_steps,
+                "rows_timed_per_gpu": e2e_rows, "rows_per_gpu": shard.rows},
+        "gpu_launches": args.steps,
+        "clocks": clocks,
+        "sum_squares": sum_squares,
+    }
+
+    if world == 1:
+        if not args.skip_ops:
+            line["ops"] = other_ops(torch, peak_gbs)
+        if not args.skip_cpu:
+            from oracle.binding import Oracle
+
+            oracle = Oracle()
+            cores = os.cpu_count() or 1
+            oracle.set_threads(cores)
+            rows = cpu_sample_rows(oracle, target_seconds=4.0, max_rows=args.rows)
+            cpu_value, _ = time_cpu(oracle, rows, steps=3, warmup=1)
+            line["cpu_baseline"] = {"value": cpu_value, "unit": UNIT, "cores": cores, "kind": "port",
+                                    "sample": f"{rows} of {args.rows} rows x {SWEEP_COLS} per step, 3 timed steps"}
+    print(json.dumps(line), flush=True)
+    if world > 1:
+        dist.destroy_process_group()
+
+
+def main():
+    parser = argparse.ArgumentParser()
+    parser.add_argument("--gpus", type=int, default=1)
+    parser.add_argument("--steps", type=int, default=20)
+    parser.add_argument("--warmup", type=int, default=5)
+    parser.add_argument("--impl", default="b200", choices=["b200", "reference"])
+    parser.add_argument("--rows", type=int, default=DEFAULT_ROWS, help="total rows of the sweep point")
+    parser.add_argument("--skip-ops", action="store_true", help="do not time workloads 1-4")
+    parser.add_argument("--skip-cpu", action="store_true", help="do not time the CPU baseline")
+    args = parser.parse_args()
+    if args.warmup < 3:
+        args.warmup = 3
+    if args.impl == "reference":
+        run_reference(args)
+    else:
+        run_gpu(args)
+
+
+if __name__ == "__main__":
+    main()

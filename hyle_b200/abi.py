@@ -1,0 +1,91 @@
+"""ctypes binding of the C ABI declared in ``include/hyle_b200.h``.
+
+This module is plumbing: it loads ``libhyle_b200.so`` and declares argument types.  It never
+falls back to another implementation; a missing library is an ImportError-like failure at the
+first call (``load()``), so GPU code paths cannot silently run on something else.
+"""
+from __future__ import annotations
+
+import ctypes
+import os
+
+from .build import LIBRARY_PATH
+
+# enum hyle_b200_dtype
+F32, BF16, F16 = 0, 1, 2
+# enum hyle_b200_binary_kind
+BINARY_ADD, BINARY_MULTIPLY = 0, 1
+# enum hyle_b200_reduce_kind
+REDUCE_SUM, REDUCE_MEAN, REDUCE_MINIMUM, REDUCE_MAXIMUM = 0, 1, 2, 3
+# enum hyle_b200_softmax_kind
+SOFTMAX, LOG_SOFTMAX = 0, 1
+# enum hyle_b200_result
+OK, INVALID_VALUE, NOT_SUPPORTED = 0, 1, 801
+# enum hyle_b200_status_bits
+STATUS_INVALID_Q8_INPUT = 1
+
+ABI_VERSION = 1
+
+_p = ctypes.c_void_p
+_u64 = ctypes.c_uint64
+_i = ctypes.c_int
+_f = ctypes.c_float
+
+# name -> (restype, argtypes); the complete export list of include/hyle_b200.h
+SIGNATURES = {
+    "hyle_b200_abi_version": (_i, []),
+    "hyle_b200_result_string": (ctypes.c_char_p, [_i]),
+    "hyle_b200_binary": (_i, [_p, _i, _i, _p, _p, _p, _u64, _u64]),
+    "hyle_b200_reduce_rows_f32": (_i, [_p, _i, _p, _p, _u64, _u64]),
+    "hyle_b200_add_bias_row_sum_max_f32": (_i, [_p, _p, _p, _p, _p, _p, _u64, _u64]),
+    "hyle_b200_rms_norm_bf16": (_i, [_p, _p, _p, _i, _p, _u64, _u64, _f]),
+    "hyle_b200_add_rms_norm_bf16": (_i, [_p, _p, _p, _p, _i, _p, _p, _u64, _u64, _f]),
+    "hyle_b200_swiglu_bf16": (_i, [_p, _p, _p, _p, _u64, _u64, _u64, _u64]),
+    "hyle_b200_logits_reduce_f32": (_i, [_p, _p, _u64, _u64, _p, _p, _p, _p]),
+    "hyle_b200_softmax_f32": (_i, [_p, _i, _p, _p, _u64, _u64]),
+    "hyle_b200_cast_f32_to_bf16": (_i, [_p, _p, _p, _u64]),
+    "hyle_b200_q8_0_encode": (_i, [_p, _i, _p, _u64, _p, _p]),
+    "hyle_b200_q8_0_decode_bf16": (_i, [_p, _p, _u64, _p]),
+    "hyle_b200_sum_squares_workspace_bytes": (_u64, []),
+    "hyle_b200_sum_squares_bf16": (_i, [_p, _p, _u64, _p, _p, _u64]),
+    "hyle_b200_q8_0_roundtrip_bf16": (_i, [_p, _p, _u64, _p, _p, _p, _p, _p, _u64]),
+}
+
+_library = None
+
+
+class LibraryMissing(RuntimeError):
+    """libhyle_b200.so is not built; there is no other implementation to fall back to."""
+
+
+def load() -> ctypes.CDLL:
+    """Load the kernel library once and declare every entry point's signature."""
+    global _library
+    if _library is not None:
+        return _library
+    if not os.path.exists(LIBRARY_PATH):
+        raise LibraryMissing(
+            f"{LIBRARY_PATH} not found: build it with `python -m hyle_b200.build` "
+            "(there is no CPU or framework fallback for these operators)")
+    library = ctypes.CDLL(LIBRARY_PATH)
+    for name, (restype, argtypes) in SIGNATURES.items():
+        function = getattr(library, name)  # AttributeError if the export is missing
+        function.restype = restype
+        function.argtypes = argtypes
+    version = library.hyle_b200_abi_version()
+    if version != ABI_VERSION:
+        raise RuntimeError(f"libhyle_b200.so has ABI version {version}, binding expects {ABI_VERSION}")
+    _library = library
+    return library
+
+
+class KernelError(RuntimeError):
+    def __init__(self, function: str, code: int):
+        self.code = code
+        text = load().hyle_b200_result_string(code).decode()
+        super().__init__(f"{function} failed: {code} ({text})")
+
+
+def check(function: str, code: int) -> None:
+    if code != OK:
+        raise KernelError(function, code)

@@ -1,0 +1,31 @@
+// ABI version, result strings and the per-device SM count cache.
+#include "common.cuh"
+
+namespace hb {
+
+int sm_count() {
+  constexpr int kMaxDevices = 64;
+  static int cached[kMaxDevices] = {};
+  int device = 0;
+  if (cudaGetDevice(&device) != cudaSuccess || device < 0 || device >= kMaxDevices) return 148;
+  int count = cached[device];
+  if (count == 0) {
+    if (cudaDeviceGetAttribute(&count, cudaDevAttrMultiProcessorCount, device) != cudaSuccess || count <= 0)
+      count = 148;
+    cached[device] = count;  // benign race: every writer stores the same value
+  }
+  return count;
+}
+
+}  // namespace hb
+
+extern "C" int hyle_b200_abi_version(void) { return HYLE_B200_ABI_VERSION; }
+
+extern "C" const char *hyle_b200_result_string(int result) {
+  switch (result) {
+    case HYLE_B200_OK: return "ok";
+    case HYLE_B200_INVALID_VALUE: return "invalid argument";
+    case HYLE_B200_NOT_SUPPORTED: return "shape or alignment not supported by this library";
+    default: return cudaGetErrorString(static_cast<cudaError_t>(result));
+  }
+}

@@ -1,0 +1,400 @@
+// Streaming elementwise operators: Binary{kAdd|kMultiply} with trailing-axis broadcast,
+// GatedActivation{kSilu} (SwiGLU) and Cast{f32->bf16}.  All are HBM-bound: every thread keeps
+// several independent 16-byte loads in flight, computes in f32 and writes 16-byte vectors.
+#include "common.cuh"
+
+namespace hb {
+namespace {
+
+constexpr int kThreads = 256;
+constexpr int kUnroll = 4;       // independent 16-byte vectors in flight per thread and operand
+constexpr int kCtasPerSm = 8;    // 8 x 256 threads fill an SM
+
+// ---- element math --------------------------------------------------------------------------------
+template <int kKind>
+__device__ __forceinline__ float binary_op(float a, float b) {
+  if constexpr (kKind == HYLE_B200_BINARY_ADD) return __fadd_rn(a, b);
+  return __fmul_rn(a, b);
+}
+
+template <int kKind>
+__device__ __forceinline__ float4 binary_vec(float4 a, float4 b) {
+  return make_float4(binary_op<kKind>(a.x, b.x), binary_op<kKind>(a.y, b.y),
+                     binary_op<kKind>(a.z, b.z), binary_op<kKind>(a.w, b.w));
+}
+
+template <int kDtype>
+__device__ __forceinline__ float narrow_lo(uint32_t w) {
+  if constexpr (kDtype == HYLE_B200_BF16) return bf16_lo(w);
+  return f16_to_f32(static_cast<unsigned short>(w & 0xffffu));
+}
+template <int kDtype>
+__device__ __forceinline__ float narrow_hi(uint32_t w) {
+  if constexpr (kDtype == HYLE_B200_BF16) return bf16_hi(w);
+  return f16_to_f32(static_cast<unsigned short>(w >> 16));
+}
+template <int kDtype>
+__device__ __forceinline__ uint32_t narrow_pack(float lo, float hi) {
+  if constexpr (kDtype == HYLE_B200_BF16) return pack_bf16x2(lo, hi);
+  return static_cast<uint32_t>(f32_to_f16(lo)) | (static_cast<uint32_t>(f32_to_f16(hi)) << 16);
+}
+template <int kDtype>
+__device__ __forceinline__ float narrow_scalar(unsigned short s) {
+  if constexpr (kDtype == HYLE_B200_BF16) return bf16_to_f32(s);
+  return f16_to_f32(s);
+}
+template <int kDtype>
+__device__ __forceinline__ unsigned short narrow_store(float v) {
+  if constexpr (kDtype == HYLE_B200_BF16) return f32_to_bf16(v);
+  return f32_to_f16(v);
+}
+
+// f32 operation on packed 16-bit pairs, one rounding back to storage (docs/user/compute.md:358-359).
+template <int kKind, int kDtype>
+__device__ __forceinline__ uint32_t binary_pair(uint32_t a, uint32_t b) {
+  return narrow_pack<kDtype>(binary_op<kKind>(narrow_lo<kDtype>(a), narrow_lo<kDtype>(b)),
+                             binary_op<kKind>(narrow_hi<kDtype>(a), narrow_hi<kDtype>(b)));
+}
+template <int kKind, int kDtype>
+__device__ __forceinline__ uint4 binary_vec(uint4 a, uint4 b) {
+  return make_uint4(binary_pair<kKind, kDtype>(a.x, b.x), binary_pair<kKind, kDtype>(a.y, b.y),
+                    binary_pair<kKind, kDtype>(a.z, b.z), binary_pair<kKind, kDtype>(a.w, b.w));
+}
+
+template <int kKind, int kDtype, class Vec>
+__device__ __forceinline__ Vec apply_vec(Vec a, Vec b) {
+  if constexpr (kDtype == HYLE_B200_F32) {
+    return binary_vec<kKind>(a, b);
+  } else {
+    return binary_vec<kKind, kDtype>(a, b);
+  }
+}
+
+template <int kDtype> struct Storage { using Vec = uint4; using Scalar = unsigned short; };
+template <> struct Storage<HYLE_B200_F32> { using Vec = float4; using Scalar = float; };
+
+// ---- Binary, same shape: flat stream over 16-byte vectors ------------------------------------------
+template <int kKind, int kDtype>
+__global__ void __launch_bounds__(kThreads)
+binary_flat_kernel(const typename Storage<kDtype>::Vec *lhs,
+                   const typename Storage<kDtype>::Vec *__restrict__ rhs,
+                   typename Storage<kDtype>::Vec *out, uint64_t vectors) {
+  using Vec = typename Storage<kDtype>::Vec;
+  const uint64_t stride = static_cast<uint64_t>(gridDim.x) * kThreads;
+  uint64_t i = static_cast<uint64_t>(blockIdx.x) * kThreads + threadIdx.x;
+  for (; i + (kUnroll - 1) * stride < vectors; i += kUnroll * stride) {
+    Vec a[kUnroll], b[kUnroll];
+#pragma unroll
+    for (int k = 0; k < kUnroll; ++k) {
+      a[k] = ld_stream(lhs + i + k * stride);
+      b[k] = ld_stream(rhs + i + k * stride);
+    }
+#pragma unroll
+    for (int k = 0; k < kUnroll; ++k)
+      st_stream(out + i + k * stride, apply_vec<kKind, kDtype>(a[k], b[k]));
+  }
+  for (; i < vectors; i += stride)
+    st_stream(out + i, apply_vec<kKind, kDtype>(ld_stream(lhs + i), ld_stream(rhs + i)));
+}
+
+// ---- Binary, right operand is one row repeated (bias over rows) -----------------------------------
+// The grid is (column tiles, row groups).  A thread owns one 16-byte column slot: the bias vector is
+// read once into registers and reused for every row the CTA walks, so the only HBM streams are lhs
+// and out, and no per-element index arithmetic remains.
+template <int kKind, int kDtype>
+__global__ void __launch_bounds__(kThreads)
+binary_rowvec_kernel(const typename Storage<kDtype>::Vec *lhs,
+                     const typename Storage<kDtype>::Vec *__restrict__ rhs,
+                     typename Storage<kDtype>::Vec *out, uint64_t rows,
+                     uint32_t row_vectors) {
+  using Vec = typename Storage<kDtype>::Vec;
+  const uint32_t column = blockIdx.x * kThreads + threadIdx.x;
+  if (column >= row_vectors) return;
+  const Vec bias = __ldg(rhs + column);
+  const uint64_t step = gridDim.y;
+  uint64_t row = blockIdx.y;
+  for (; row + (kUnroll - 1) * step < rows; row += kUnroll * step) {
+    Vec a[kUnroll];
+#pragma unroll
+    for (int k = 0; k < kUnroll; ++k) a[k] = ld_stream(lhs + (row + k * step) * row_vectors + column);
+#pragma unroll
+    for (int k = 0; k < kUnroll; ++k)
+      st_stream(out + (row + k * step) * row_vectors + column, apply_vec<kKind, kDtype>(a[k], bias));
+  }
+  for (; row < rows; row += step)
+    st_stream(out + row * row_vectors + column,
+              apply_vec<kKind, kDtype>(ld_stream(lhs + row * row_vectors + column), bias));
+}
+
+// ---- Binary, any period / any alignment: one element per thread-iteration --------------------------
+template <int kKind, int kDtype>
+__global__ void __launch_bounds__(kThreads)
+binary_scalar_kernel(const typename Storage<kDtype>::Scalar *lhs,
+                     const typename Storage<kDtype>::Scalar *__restrict__ rhs,
+                     typename Storage<kDtype>::Scalar *out, uint64_t count,
+                     uint64_t period) {
+  const uint64_t stride = static_cast<uint64_t>(gridDim.x) * kThreads;
+  for (uint64_t i = static_cast<uint64_t>(blockIdx.x) * kThreads + threadIdx.x; i < count;
+       i += stride) {
+    const uint64_t j = period == count ? i : (count <= 0xffffffffull
+                                                  ? static_cast<uint32_t>(i) % static_cast<uint32_t>(period)
+                                                  : i % period);
+    if constexpr (kDtype == HYLE_B200_F32) {
+      out[i] = binary_op<kKind>(lhs[i], rhs[j]);
+    } else {
+      out[i] = narrow_store<kDtype>(
+          binary_op<kKind>(narrow_scalar<kDtype>(lhs[i]), narrow_scalar<kDtype>(rhs[j])));
+    }
+  }
+}
+
+template <int kKind, int kDtype>
+int launch_binary(cudaStream_t stream, const void *lhs, const void *rhs, void *out, uint64_t count,
+                  uint64_t period) {
+  using Vec = typename Storage<kDtype>::Vec;
+  using Scalar = typename Storage<kDtype>::Scalar;
+  constexpr uint64_t kLanes = sizeof(Vec) / sizeof(Scalar);
+  const bool vector_ok = aligned_to(lhs, 16) && aligned_to(rhs, 16) && aligned_to(out, 16) &&
+                         count % kLanes == 0 && period % kLanes == 0;
+  const uint64_t resident = static_cast<uint64_t>(sm_count()) * kCtasPerSm;
+  if (vector_ok && period == count) {
+    const uint64_t vectors = count / kLanes;
+    const unsigned grid = clamp_grid((vectors + kThreads * kUnroll - 1) / (kThreads * kUnroll), resident);
+    binary_flat_kernel<kKind, kDtype><<<grid, kThreads, 0, stream>>>(
+        static_cast<const Vec *>(lhs), static_cast<const Vec *>(rhs), static_cast<Vec *>(out), vectors);
+    return launch_result();
+  }
+  const uint64_t row_vectors = period / kLanes;
+  if (vector_ok && row_vectors >= 64 && row_vectors <= 0x7fffffffull) {
+    const uint64_t rows = count / period;
+    const unsigned tiles = static_cast<unsigned>((row_vectors + kThreads - 1) / kThreads);
+    // Enough row groups to fill the machine, never more than rows/unroll so the main loop runs.
+    uint64_t groups = (resident + tiles - 1) / tiles;
+    const uint64_t useful = (rows + kUnroll - 1) / kUnroll;
+    if (groups > useful) groups = useful;
+    if (groups > 65535) groups = 65535;
+    if (groups < 1) groups = 1;
+    binary_rowvec_kernel<kKind, kDtype><<<dim3(tiles, static_cast<unsigned>(groups)), kThreads, 0, stream>>>(
+        static_cast<const Vec *>(lhs), static_cast<const Vec *>(rhs), static_cast<Vec *>(out), rows,
+        static_cast<uint32_t>(row_vectors));
+    return launch_result();
+  }
+  const unsigned grid = clamp_grid((count + kThreads - 1) / kThreads, resident);
+  binary_scalar_kernel<kKind, kDtype><<<grid, kThreads, 0, stream>>>(
+      static_cast<const Scalar *>(lhs), static_cast<const Scalar *>(rhs), static_cast<Scalar *>(out),
+      count, period);
+  return launch_result();
+}
+
+// ---- SwiGLU --------------------------------------------------------------------------------------
+// exp(-|x|) for finite or infinite x: the product with log2(e) is carried in two parts so the
+// argument error does not grow with |x|; ex2.approx supplies 2^t.
+__device__ __forceinline__ float exp_neg_abs(float x) {
+  const float a = fmaxf(-fabsf(x), -128.0f);  // exp(-128) is already 0 in f32; also tames inf/NaN
+  constexpr float kLog2eHi = 1.4426950216293335f;
+  constexpr float kLog2eLo = 1.925963033500175e-8f;
+  const float t = __fmul_rn(a, kLog2eHi);
+  float lo = fmaf(a, kLog2eHi, -t);
+  lo = fmaf(a, kLog2eLo, lo);
+  float p;
+  asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(p) : "f"(t));
+  return fmaf(p, lo * 0.6931471805599453f, p);
+}
+
+// silu(x) = x * sigmoid(x) with the overflow-free sigmoid of src/simd/math/activations.cc:21-25:
+// e = exp(-|x|); sigmoid = x < 0 ? e/(1+e) : 1/(1+e); silu(-inf) = 0 (:44-47).
+__device__ __forceinline__ float silu(float x) {
+  const float e = exp_neg_abs(x);
+  const float numerator = x < 0.0f ? e : 1.0f;
+  const float denominator = 1.0f + e;  // in [1, 2]
+  float r;
+  asm("rcp.approx.ftz.f32 %0, %1;" : "=f"(r) : "f"(denominator));
+  float q = numerator * r;
+  q = fmaf(fmaf(-denominator, q, numerator), r, q);  // one Newton step: ~correctly rounded quotient
+  const float y = x * q;
+  return x == -INFINITY ? 0.0f : y;
+}
+
+__device__ __forceinline__ uint32_t swiglu_pair(uint32_t g, uint32_t u) {
+  return pack_bf16x2(__fmul_rn(silu(bf16_lo(g)), bf16_lo(u)), __fmul_rn(silu(bf16_hi(g)), bf16_hi(u)));
+}
+__device__ __forceinline__ uint4 swiglu_vec(uint4 g, uint4 u) {
+  return make_uint4(swiglu_pair(g.x, u.x), swiglu_pair(g.y, u.y), swiglu_pair(g.z, u.z),
+                    swiglu_pair(g.w, u.w));
+}
+
+// Dense separate gate/up: one flat stream.
+__global__ void __launch_bounds__(kThreads)
+swiglu_flat_kernel(const uint4 *__restrict__ gate, const uint4 *__restrict__ up,
+                   uint4 *__restrict__ out, uint64_t vectors) {
+  const uint64_t stride = static_cast<uint64_t>(gridDim.x) * kThreads;
+  uint64_t i = static_cast<uint64_t>(blockIdx.x) * kThreads + threadIdx.x;
+  for (; i + (kUnroll - 1) * stride < vectors; i += kUnroll * stride) {
+    uint4 g[kUnroll], u[kUnroll];
+#pragma unroll
+    for (int k = 0; k < kUnroll; ++k) {
+      g[k] = ld_stream(gate + i + k * stride);
+      u[k] = ld_stream(up + i + k * stride);
+    }
+#pragma unroll
+    for (int k = 0; k < kUnroll; ++k) st_stream(out + i + k * stride, swiglu_vec(g[k], u[k]));
+  }
+  for (; i < vectors; i += stride) st_stream(out + i, swiglu_vec(ld_stream(gate + i), ld_stream(up + i)));
+}
+
+// Row-strided operands (the packed-halves layout): grid = (column tiles, row groups).
+__global__ void __launch_bounds__(kThreads)
+swiglu_rows_kernel(const uint4 *__restrict__ gate, const uint4 *__restrict__ up,
+                   uint4 *__restrict__ out, uint64_t rows, uint32_t row_vectors,
+                   uint64_t gate_stride_vectors, uint64_t up_stride_vectors) {
+  const uint32_t column = blockIdx.x * kThreads + threadIdx.x;
+  if (column >= row_vectors) return;
+  const uint64_t step = gridDim.y;
+  uint64_t row = blockIdx.y;
+  for (; row + (kUnroll - 1) * step < rows; row += kUnroll * step) {
+    uint4 g[kUnroll], u[kUnroll];
+#pragma unroll
+    for (int k = 0; k < kUnroll; ++k) {
+      g[k] = ld_stream(gate + (row + k * step) * gate_stride_vectors + column);
+      u[k] = ld_stream(up + (row + k * step) * up_stride_vectors + column);
+    }
+#pragma unroll
+    for (int k = 0; k < kUnroll; ++k)
+      st_stream(out + (row + k * step) * row_vectors + column, swiglu_vec(g[k], u[k]));
+  }
+  for (; row < rows; row += step)
+    st_stream(out + row * row_vectors + column,
+              swiglu_vec(ld_stream(gate + row * gate_stride_vectors + column),
+                         ld_stream(up + row * up_stride_vectors + column)));
+}
+
+// Any width / alignment.
+__global__ void __launch_bounds__(kThreads)
+swiglu_scalar_kernel(const unsigned short *__restrict__ gate, const unsigned short *__restrict__ up,
+                     unsigned short *__restrict__ out, uint64_t rows, uint64_t cols,
+                     uint64_t gate_stride, uint64_t up_stride) {
+  const uint64_t stride = static_cast<uint64_t>(gridDim.x) * kThreads;
+  const uint64_t count = rows * cols;
+  for (uint64_t i = static_cast<uint64_t>(blockIdx.x) * kThreads + threadIdx.x; i < count;
+       i += stride) {
+    const uint64_t row = i / cols, column = i - row * cols;
+    const float g = bf16_to_f32(gate[row * gate_stride + column]);
+    const float u = bf16_to_f32(up[row * up_stride + column]);
+    out[i] = f32_to_bf16(__fmul_rn(silu(g), u));
+  }
+}
+
+// ---- Cast f32 -> bf16 -----------------------------------------------------------------------------
+__global__ void __launch_bounds__(kThreads)
+cast_f32_bf16_kernel(const float4 *__restrict__ in, uint4 *__restrict__ out, uint64_t vectors) {
+  const uint64_t stride = static_cast<uint64_t>(gridDim.x) * kThreads;
+  uint64_t i = static_cast<uint64_t>(blockIdx.x) * kThreads + threadIdx.x;
+  for (; i + (kUnroll - 1) * stride < vectors; i += kUnroll * stride) {
+    float4 a[kUnroll], b[kUnroll];
+#pragma unroll
+    for (int k = 0; k < kUnroll; ++k) {
+      a[k] = ld_stream(in + 2 * (i + k * stride));
+      b[k] = ld_stream(in + 2 * (i + k * stride) + 1);
+    }
+#pragma unroll
+    for (int k = 0; k < kUnroll; ++k)
+      st_stream(out + i + k * stride,
+                make_uint4(pack_bf16x2(a[k].x, a[k].y), pack_bf16x2(a[k].z, a[k].w),
+                           pack_bf16x2(b[k].x, b[k].y), pack_bf16x2(b[k].z, b[k].w)));
+  }
+  for (; i < vectors; i += stride) {
+    const float4 a = ld_stream(in + 2 * i), b = ld_stream(in + 2 * i + 1);
+    st_stream(out + i, make_uint4(pack_bf16x2(a.x, a.y), pack_bf16x2(a.z, a.w),
+                                  pack_bf16x2(b.x, b.y), pack_bf16x2(b.z, b.w)));
+  }
+}
+
+__global__ void __launch_bounds__(kThreads)
+cast_f32_bf16_scalar_kernel(const float *__restrict__ in, unsigned short *__restrict__ out,
+                            uint64_t count) {
+  const uint64_t stride = static_cast<uint64_t>(gridDim.x) * kThreads;
+  for (uint64_t i = static_cast<uint64_t>(blockIdx.x) * kThreads + threadIdx.x; i < count; i += stride)
+    out[i] = f32_to_bf16(in[i]);
+}
+
+}  // namespace
+}  // namespace hb
+
+using namespace hb;
+
+extern "C" int hyle_b200_binary(hyle_b200_stream_t stream, int kind, int dtype, const void *lhs,
+                                const void *rhs, void *out, uint64_t count, uint64_t rhs_period) {
+  if (count == 0) return HYLE_B200_OK;
+  if (lhs == nullptr || rhs == nullptr || out == nullptr || rhs_period == 0 ||
+      count % rhs_period != 0)
+    return HYLE_B200_INVALID_VALUE;
+  auto s = reinterpret_cast<cudaStream_t>(stream);
+#define HB_BINARY_CASE(K, D) \
+  if (kind == K && dtype == D) return launch_binary<K, D>(s, lhs, rhs, out, count, rhs_period)
+  HB_BINARY_CASE(HYLE_B200_BINARY_ADD, HYLE_B200_F32);
+  HB_BINARY_CASE(HYLE_B200_BINARY_MULTIPLY, HYLE_B200_F32);
+  HB_BINARY_CASE(HYLE_B200_BINARY_ADD, HYLE_B200_BF16);
+  HB_BINARY_CASE(HYLE_B200_BINARY_MULTIPLY, HYLE_B200_BF16);
+  HB_BINARY_CASE(HYLE_B200_BINARY_ADD, HYLE_B200_F16);
+  HB_BINARY_CASE(HYLE_B200_BINARY_MULTIPLY, HYLE_B200_F16);
+#undef HB_BINARY_CASE
+  return HYLE_B200_INVALID_VALUE;
+}
+
+extern "C" int hyle_b200_swiglu_bf16(hyle_b200_stream_t stream, const void *gate, const void *up,
+                                     void *out, uint64_t rows, uint64_t cols,
+                                     uint64_t gate_row_stride, uint64_t up_row_stride) {
+  if (rows == 0 || cols == 0) return HYLE_B200_OK;
+  if (gate == nullptr || up == nullptr || out == nullptr || gate_row_stride < cols ||
+      up_row_stride < cols)
+    return HYLE_B200_INVALID_VALUE;
+  auto s = reinterpret_cast<cudaStream_t>(stream);
+  const uint64_t resident = static_cast<uint64_t>(sm_count()) * kCtasPerSm;
+  const bool vector_ok = aligned_to(gate, 16) && aligned_to(up, 16) && aligned_to(out, 16) &&
+                         cols % 8 == 0 && gate_row_stride % 8 == 0 && up_row_stride % 8 == 0;
+  if (vector_ok && gate_row_stride == cols && up_row_stride == cols) {
+    const uint64_t vectors = rows * cols / 8;
+    const unsigned grid = clamp_grid((vectors + kThreads * kUnroll - 1) / (kThreads * kUnroll), resident);
+    swiglu_flat_kernel<<<grid, kThreads, 0, s>>>(static_cast<const uint4 *>(gate),
+                                                 static_cast<const uint4 *>(up),
+                                                 static_cast<uint4 *>(out), vectors);
+    return launch_result();
+  }
+  if (vector_ok && cols / 8 <= 0x7fffffffull) {
+    const uint64_t row_vectors = cols / 8;
+    const unsigned tiles = static_cast<unsigned>((row_vectors + kThreads - 1) / kThreads);
+    uint64_t groups = (resident + tiles - 1) / tiles;
+    const uint64_t useful = (rows + kUnroll - 1) / kUnroll;
+    if (groups > useful) groups = useful;
+    if (groups > 65535) groups = 65535;
+    if (groups < 1) groups = 1;
+    swiglu_rows_kernel<<<dim3(tiles, static_cast<unsigned>(groups)), kThreads, 0, s>>>(
+        static_cast<const uint4 *>(gate), static_cast<const uint4 *>(up), static_cast<uint4 *>(out),
+        rows, static_cast<uint32_t>(row_vectors), gate_row_stride / 8, up_row_stride / 8);
+    return launch_result();
+  }
+  const unsigned grid = clamp_grid((rows * cols + kThreads - 1) / kThreads, resident);
+  swiglu_scalar_kernel<<<grid, kThreads, 0, s>>>(static_cast<const unsigned short *>(gate),
+                                                 static_cast<const unsigned short *>(up),
+                                                 static_cast<unsigned short *>(out), rows, cols,
+                                                 gate_row_stride, up_row_stride);
+  return launch_result();
+}
+
+extern "C" int hyle_b200_cast_f32_to_bf16(hyle_b200_stream_t stream, const float *in,
+                                          void *out_bf16, uint64_t count) {
+  if (count == 0) return HYLE_B200_OK;
+  if (in == nullptr || out_bf16 == nullptr) return HYLE_B200_INVALID_VALUE;
+  auto s = reinterpret_cast<cudaStream_t>(stream);
+  const uint64_t resident = static_cast<uint64_t>(sm_count()) * kCtasPerSm;
+  if (aligned_to(in, 16) && aligned_to(out_bf16, 16) && count % 8 == 0) {
+    const uint64_t vectors = count / 8;
+    const unsigned grid = clamp_grid((vectors + kThreads * kUnroll - 1) / (kThreads * kUnroll), resident);
+    cast_f32_bf16_kernel<<<grid, kThreads, 0, s>>>(reinterpret_cast<const float4 *>(in),
+                                                   static_cast<uint4 *>(out_bf16), vectors);
+    return launch_result();
+  }
+  const unsigned grid = clamp_grid((count + kThreads - 1) / kThreads, resident);
+  cast_f32_bf16_scalar_kernel<<<grid, kThreads, 0, s>>>(in, static_cast<unsigned short *>(out_bf16), count);
+  return launch_result();
+}

@@ -1,0 +1,466 @@
+// Row softmax family over f32 rows: log-sum-exp, softmax (bf16 or f32 out), log-softmax and
+// argmax, in ONE pass over HBM.
+//
+// A vocabulary row (151 936 f32 = 608 KB) does not fit one SM, so a thread-block cluster shares it:
+// CTA k of the cluster keeps slice k of the row in its own shared memory, and only three scalars
+// per CTA cross the cluster (distributed shared memory reads of the peers' slots):
+//   phase A  global -> registers -> shared; NaN-propagating running maximum (one instruction/element)
+//   exchange (max)                                                           cluster barrier 1
+//   phase B  e = expf(x - max) written back to shared; f32 thread sums, f64 from the warp up;
+//            lowest index whose value equals the maximum
+//   exchange (sum, index)                                                    cluster barrier 2
+//   phase C  shared -> bf16/f32 probabilities (or x - shift) -> 16-byte global stores
+// HBM traffic is the algorithmic minimum (4 B read + 2 B written per element for bf16 output); the
+// second and third touches of every element hit shared memory.
+//
+// Semantics follow src/simd/math/activations.cc:301-334 (softmax: f32 exp, f64 sum, multiply by
+// float(1/sum); log-softmax shift = max + float(log(sum)); rows with NaN/+inf or only -inf are all
+// NaN) and src/simd/sort/top_k.cc:17-27 (argmax: larger value first, NaN last, lower index on ties).
+#include "common.cuh"
+
+#include <cooperative_groups.h>
+#include <math_constants.h>
+
+namespace cg = cooperative_groups;
+
+namespace hb {
+namespace {
+
+constexpr int kThreads = 512;
+constexpr int kWarps = kThreads / 32;
+constexpr int kLoadBatch = 4;  // 16-byte loads in flight per thread in phase A
+constexpr uint32_t kNoIndex = 0xffffffffu;
+constexpr int kMaxCluster = 8;
+constexpr size_t kTwoCtaSliceBytes = 76 * 1024;   // two CTAs of this size share an SM
+constexpr size_t kMaxSliceBytes = 200 * 1024;     // one CTA per SM
+
+enum Mode { kProbsBf16 = 0, kProbsF32 = 1, kLogF32 = 2, kArgmaxOnly = 3 };
+
+struct LogitsParams {
+  const float *in;
+  uint64_t rows;
+  uint32_t cols;
+  uint32_t slice;  // elements per CTA, a multiple of 8
+  float *lse;
+  void *out;       // probabilities / log-probabilities, or nullptr
+  int32_t *index;
+  float *value;
+};
+
+struct Best {
+  float value;
+  uint32_t index;
+};
+
+// TopK order restricted to non-NaN candidates; "no candidate" is (-inf, kNoIndex) and loses ties.
+__device__ __forceinline__ Best better_of(Best a, Best b) {
+  const bool take_b = b.value > a.value || (b.value == a.value && b.index < a.index);
+  return take_b ? b : a;
+}
+
+__device__ __forceinline__ void consider(float x, uint32_t index, Best &best) {
+  if (x > best.value) {  // strict: the first of equal values stays; NaN never enters
+    best.value = x;
+    best.index = index;
+  }
+}
+
+__device__ __forceinline__ Best warp_best(Best best) {
+#pragma unroll
+  for (int o = 16; o > 0; o >>= 1) {
+    Best other;
+    other.value = __shfl_xor_sync(kFullMask, best.value, o);
+    other.index = __shfl_xor_sync(kFullMask, best.index, o);
+    best = better_of(best, other);
+  }
+  return best;
+}
+
+// Full TopK{1} order for one row, by one CTA, from global memory: larger value first, NaN last,
+// lower index on ties.  Used for rows the fast paths cannot decide (NaN present, or nothing above
+// -inf).  All threads of the CTA must call it.
+__device__ void rescan_argmax(const float *whole, uint32_t cols, int32_t *index_out, float *value_out) {
+  __shared__ Best s_best[kWarps];
+  __shared__ uint32_t s_first[kWarps];
+  const int t = threadIdx.x, lane = t & 31, warp = t >> 5;
+  Best best{-CUDART_INF_F, kNoIndex};
+  uint32_t first_floor = kNoIndex;  // first -inf
+  for (uint32_t i = t; i < cols; i += kThreads) {
+    const float x = whole[i];
+    consider(x, i, best);
+    if (x == -CUDART_INF_F && first_floor == kNoIndex) first_floor = i;
+  }
+  best = warp_best(best);
+  first_floor = __reduce_min_sync(kFullMask, first_floor);
+  if (lane == 0) {
+    s_best[warp] = best;
+    s_first[warp] = first_floor;
+  }
+  __syncthreads();
+  if (t == 0) {
+    for (int w = 1; w < kWarps; ++w) {
+      best = better_of(best, s_best[w]);
+      first_floor = min(first_floor, s_first[w]);
+    }
+    // nothing above -inf: the first -inf, else the row is all NaN and element 0 stays
+    const uint32_t chosen = best.index != kNoIndex ? best.index : (first_floor != kNoIndex ? first_floor : 0u);
+    if (index_out != nullptr) *index_out = static_cast<int32_t>(chosen);
+    if (value_out != nullptr) *value_out = whole[chosen];
+  }
+  __syncthreads();
+}
+
+// ---- argmax alone: a pure read stream, one cluster barrier per row ------------------------------
+template <bool kVec>
+__global__ void __launch_bounds__(kThreads)
+argmax_kernel(const LogitsParams p) {
+  __shared__ Best s_warp_best[kWarps];
+  __shared__ Best s_cta_best[2];  // by row parity; read by the peers after the barrier
+  __shared__ Best s_row_best;
+  cg::cluster_group cluster = cg::this_cluster();
+  const unsigned rank = cluster.block_rank();
+  const unsigned cluster_size = cluster.num_blocks();
+  const int t = threadIdx.x, lane = t & 31, warp = t >> 5;
+  const uint64_t cluster_id = blockIdx.x / cluster_size;
+  const uint64_t cluster_count = gridDim.x / cluster_size;
+  const uint32_t begin = min(rank * p.slice, p.cols);
+  const uint32_t end = min(begin + p.slice, p.cols);
+  const uint32_t n = end - begin;
+  int parity = 0;
+  for (uint64_t row = cluster_id; row < p.rows; row += cluster_count, parity ^= 1) {
+    const float *src = p.in + row * p.cols + begin;
+    Best best{-CUDART_INF_F, kNoIndex};
+    if constexpr (kVec) {
+      const uint32_t vectors = n / 4;
+      for (uint32_t v0 = t; v0 < vectors; v0 += kThreads * kLoadBatch) {
+        float4 x[kLoadBatch];
+#pragma unroll
+        for (int k = 0; k < kLoadBatch; ++k)
+          if (v0 + k * kThreads < vectors) x[k] = ld_stream(reinterpret_cast<const float4 *>(src) + v0 + k * kThreads);
+#pragma unroll
+        for (int k = 0; k < kLoadBatch; ++k) {
+          const uint32_t v = v0 + k * kThreads;
+          if (v < vectors) {
+            const uint32_t i = begin + v * 4;
+            consider(x[k].x, i, best);
+            consider(x[k].y, i + 1, best);
+            consider(x[k].z, i + 2, best);
+            consider(x[k].w, i + 3, best);
+          }
+        }
+      }
+    } else {
+      for (uint32_t i = t; i < n; i += kThreads) consider(ld_stream(src + i), begin + i, best);
+    }
+    best = warp_best(best);
+    if (lane == 0) s_warp_best[warp] = best;
+    __syncthreads();
+    if (t == 0) {
+      Best b = s_warp_best[0];
+#pragma unroll
+      for (int w = 1; w < kWarps; ++w) b = better_of(b, s_warp_best[w]);
+      s_cta_best[parity] = b;
+    }
+    cluster.sync();
+    if (rank == 0) {  // only the CTA that writes the result gathers the peers' slots
+      if (warp == 0) {
+        Best b{-CUDART_INF_F, kNoIndex};
+        if (lane < cluster_size) b = *cluster.map_shared_rank(&s_cta_best[parity], lane);
+        b = warp_best(b);
+        if (lane == 0) s_row_best = b;
+      }
+      __syncthreads();
+      const Best row_best = s_row_best;
+      if (row_best.index != kNoIndex) {
+        if (t == 0) {
+          if (p.index != nullptr) p.index[row] = static_cast<int32_t>(row_best.index);
+          if (p.value != nullptr) p.value[row] = row_best.value;
+        }
+      } else {
+        rescan_argmax(p.in + row * p.cols, p.cols, p.index != nullptr ? p.index + row : nullptr,
+                      p.value != nullptr ? p.value + row : nullptr);
+      }
+    }
+  }
+  cluster.sync();  // no CTA leaves while a peer may still read its shared memory
+}
+
+// ---- fused lse / softmax / argmax ---------------------------------------------------------------
+struct SumSlot {
+  double sum;
+  uint32_t index;  // lowest index in this CTA's slice holding the row maximum, or kNoIndex
+  uint32_t pad;
+};
+
+template <int kMode, bool kVec>
+__global__ void __launch_bounds__(kThreads)
+logits_kernel(const LogitsParams p) {
+  extern __shared__ __align__(16) float slice_data[];
+  __shared__ float s_warp_max[kWarps];
+  __shared__ double s_warp_sum[kWarps];
+  __shared__ uint32_t s_warp_index[kWarps];
+  __shared__ float s_cta_max;      // read by the peers after barrier 1
+  __shared__ SumSlot s_cta_sum;    // read by the peers after barrier 2
+  __shared__ float s_row_max;      // cluster-wide results, broadcast inside the CTA
+  __shared__ SumSlot s_row_sum;
+
+  cg::cluster_group cluster = cg::this_cluster();
+  const unsigned rank = cluster.block_rank();
+  const unsigned cluster_size = cluster.num_blocks();
+  const int t = threadIdx.x, lane = t & 31, warp = t >> 5;
+  const uint64_t cluster_id = blockIdx.x / cluster_size;
+  const uint64_t cluster_count = gridDim.x / cluster_size;
+  const bool want_index = p.index != nullptr || p.value != nullptr;
+
+  const uint32_t begin = min(rank * p.slice, p.cols);
+  const uint32_t end = min(begin + p.slice, p.cols);
+  const uint32_t n = end - begin;
+
+  for (uint64_t row = cluster_id; row < p.rows; row += cluster_count) {
+    const float *src = p.in + row * p.cols + begin;
+
+    // ---- phase A: global -> shared, NaN-propagating maximum ------------------------------------
+    float maximum = -CUDART_INF_F;
+    if constexpr (kVec) {
+      const uint32_t vectors = n / 4;
+      for (uint32_t v0 = t; v0 < vectors; v0 += kThreads * kLoadBatch) {
+        float4 x[kLoadBatch];
+#pragma unroll
+        for (int k = 0; k < kLoadBatch; ++k)
+          if (v0 + k * kThreads < vectors) x[k] = ld_stream(reinterpret_cast<const float4 *>(src) + v0 + k * kThreads);
+#pragma unroll
+        for (int k = 0; k < kLoadBatch; ++k) {
+          const uint32_t v = v0 + k * kThreads;
+          if (v < vectors) {
+            reinterpret_cast<float4 *>(slice_data)[v] = x[k];
+            maximum = max_nan(max_nan(maximum, x[k].x), max_nan(x[k].y, max_nan(x[k].z, x[k].w)));
+          }
+        }
+      }
+    } else {
+      for (uint32_t i = t; i < n; i += kThreads) {
+        const float x = ld_stream(src + i);
+        slice_data[i] = x;
+        maximum = max_nan(maximum, x);
+      }
+    }
+    maximum = warp_max_nan(maximum);
+    if (lane == 0) s_warp_max[warp] = maximum;
+    __syncthreads();
+    if (t == 0) {
+      float m = s_warp_max[0];
+#pragma unroll
+      for (int w = 1; w < kWarps; ++w) m = max_nan(m, s_warp_max[w]);
+      s_cta_max = m;
+    }
+    cluster.sync();  // barrier 1 (also a CTA barrier: the slice is visible to every thread)
+    if (warp == 0) {
+      float m = lane < cluster_size ? *cluster.map_shared_rank(&s_cta_max, lane) : -CUDART_INF_F;
+#pragma unroll
+      for (int o = kMaxCluster / 2; o > 0; o >>= 1) m = max_nan(m, __shfl_xor_sync(kFullMask, m, o));
+      if (lane == 0) s_row_max = m;
+    }
+    __syncthreads();
+    maximum = s_row_max;
+    // NaN or +inf anywhere, or nothing above -inf: the softmax outputs of the row are NaN.
+    const bool valid = maximum > -CUDART_INF_F && maximum < CUDART_INF_F;
+    const bool has_nan = maximum != maximum;
+
+    // ---- phase B: exponentials back into shared memory, sums, position of the maximum -----------
+    float thread_sum = 0.0f;
+    uint32_t thread_index = kNoIndex;
+    if (valid || (want_index && !has_nan)) {
+      if constexpr (kVec) {
+        for (uint32_t v = t; v < n / 4; v += kThreads) {
+          float4 x = reinterpret_cast<const float4 *>(slice_data)[v];
+          if (want_index && (x.x == maximum || x.y == maximum || x.z == maximum || x.w == maximum) &&
+              thread_index == kNoIndex) {
+            const uint32_t i = begin + v * 4;
+            thread_index = x.x == maximum ? i : x.y == maximum ? i + 1 : x.z == maximum ? i + 2 : i + 3;
+          }
+          if (valid) {
+            x = make_float4(expf(x.x - maximum), expf(x.y - maximum), expf(x.z - maximum), expf(x.w - maximum));
+            if constexpr (kMode != kLogF32) reinterpret_cast<float4 *>(slice_data)[v] = x;
+            thread_sum += (x.x + x.y) + (x.z + x.w);
+          }
+        }
+      } else {
+        for (uint32_t i = t; i < n; i += kThreads) {
+          const float x = slice_data[i];
+          if (want_index && x == maximum && thread_index == kNoIndex) thread_index = begin + i;
+          if (valid) {
+            const float e = expf(x - maximum);
+            if constexpr (kMode != kLogF32) slice_data[i] = e;
+            thread_sum += e;
+          }
+        }
+      }
+    }
+    const double warp_total = warp_sum(static_cast<double>(thread_sum));
+    const uint32_t warp_index = __reduce_min_sync(kFullMask, thread_index);
+    if (lane == 0) {
+      s_warp_sum[warp] = warp_total;
+      s_warp_index[warp] = warp_index;
+    }
+    __syncthreads();
+    if (t == 0) {
+      SumSlot slot{s_warp_sum[0], s_warp_index[0], 0u};
+#pragma unroll
+      for (int w = 1; w < kWarps; ++w) {
+        slot.sum += s_warp_sum[w];
+        slot.index = min(slot.index, s_warp_index[w]);
+      }
+      s_cta_sum = slot;
+    }
+    cluster.sync();  // barrier 2
+    if (warp == 0) {
+      SumSlot slot{0.0, kNoIndex, 0u};
+      if (lane < cluster_size) slot = *cluster.map_shared_rank(&s_cta_sum, lane);
+#pragma unroll
+      for (int o = kMaxCluster / 2; o > 0; o >>= 1) {  // fixed tree over the ranks
+        slot.sum += __shfl_xor_sync(kFullMask, slot.sum, o);
+        slot.index = min(slot.index, __shfl_xor_sync(kFullMask, slot.index, o));
+      }
+      if (lane == 0) s_row_sum = slot;
+    }
+    __syncthreads();
+    const double total = s_row_sum.sum;
+
+    if (rank == 0 && want_index) {
+      if (!has_nan) {
+        if (t == 0) {
+          if (p.index != nullptr) p.index[row] = static_cast<int32_t>(s_row_sum.index);
+          if (p.value != nullptr) p.value[row] = maximum;
+        }
+      } else {
+        rescan_argmax(p.in + row * p.cols, p.cols, p.index != nullptr ? p.index + row : nullptr,
+                      p.value != nullptr ? p.value + row : nullptr);
+      }
+    }
+
+    // ---- phase C: shared -> global -----------------------------------------------------------------
+    const float nan = CUDART_NAN_F;
+    const float inverse = valid ? static_cast<float>(1.0 / total) : nan;
+    const float shift = valid ? maximum + static_cast<float>(log(total)) : nan;
+    if (rank == 0 && t == 0 && p.lse != nullptr) p.lse[row] = shift;
+    if (p.out != nullptr) {
+      if constexpr (kMode == kProbsBf16) {
+        unsigned short *dst = static_cast<unsigned short *>(p.out) + row * p.cols + begin;
+        if constexpr (kVec) {
+          for (uint32_t g = t; g < n / 8; g += kThreads) {
+            const float4 a = reinterpret_cast<const float4 *>(slice_data)[2 * g];
+            const float4 b = reinterpret_cast<const float4 *>(slice_data)[2 * g + 1];
+            const uint4 o = valid ? make_uint4(pack_bf16x2(a.x * inverse, a.y * inverse),
+                                               pack_bf16x2(a.z * inverse, a.w * inverse),
+                                               pack_bf16x2(b.x * inverse, b.y * inverse),
+                                               pack_bf16x2(b.z * inverse, b.w * inverse))
+                                  : make_uint4(0x7fc07fc0u, 0x7fc07fc0u, 0x7fc07fc0u, 0x7fc07fc0u);
+            st_stream(reinterpret_cast<uint4 *>(dst) + g, o);
+          }
+        } else {
+          for (uint32_t i = t; i < n; i += kThreads)
+            dst[i] = valid ? f32_to_bf16(slice_data[i] * inverse) : static_cast<unsigned short>(0x7fc0);
+        }
+      } else {
+        float *dst = static_cast<float *>(p.out) + row * p.cols + begin;
+        if constexpr (kVec) {
+          for (uint32_t v = t; v < n / 4; v += kThreads) {
+            const float4 a = reinterpret_cast<const float4 *>(slice_data)[v];
+            float4 o;
+            if constexpr (kMode == kProbsF32) o = make_float4(a.x * inverse, a.y * inverse, a.z * inverse, a.w * inverse);
+            else o = make_float4(a.x - shift, a.y - shift, a.z - shift, a.w - shift);
+            if (!valid) o = make_float4(nan, nan, nan, nan);
+            st_stream(reinterpret_cast<float4 *>(dst) + v, o);
+          }
+        } else {
+          for (uint32_t i = t; i < n; i += kThreads) {
+            const float o = kMode == kProbsF32 ? slice_data[i] * inverse : slice_data[i] - shift;
+            dst[i] = valid ? o : nan;
+          }
+        }
+      }
+    }
+    // The next row's phase A rewrites the slice.  Peer reads of s_cta_max (after barrier 1) and
+    // s_cta_sum (after barrier 2) are ordered before their next writes by barrier 2 of this row
+    // and barrier 1 of the next row respectively.
+    __syncthreads();
+  }
+  cluster.sync();  // no CTA leaves while a peer may still read its shared memory
+}
+
+struct Plan {
+  int cluster;
+  uint32_t slice;
+  size_t shared_bytes;
+};
+
+bool make_plan(uint64_t cols, Plan &plan) {
+  for (int c = 1; c <= kMaxCluster; c *= 2) {
+    const uint64_t slice = ((cols + c - 1) / c + 7) / 8 * 8;
+    const size_t bytes = slice * sizeof(float);
+    if (bytes <= kTwoCtaSliceBytes || (c == kMaxCluster && bytes <= kMaxSliceBytes)) {
+      plan = {c, static_cast<uint32_t>(slice), bytes};
+      return true;
+    }
+  }
+  return false;
+}
+
+template <int kMode>
+int launch_logits(cudaStream_t stream, LogitsParams p, bool vec) {
+  Plan plan{};
+  if (p.cols == 0 || !make_plan(p.cols, plan)) return HYLE_B200_NOT_SUPPORTED;
+  p.slice = plan.slice;
+  const size_t shared = kMode == kArgmaxOnly ? 0 : plan.shared_bytes;
+  void (*kernel)(const LogitsParams);
+  if constexpr (kMode == kArgmaxOnly) kernel = vec ? argmax_kernel<true> : argmax_kernel<false>;
+  else kernel = vec ? logits_kernel<kMode, true> : logits_kernel<kMode, false>;
+  if (shared > 48 * 1024) {
+    const cudaError_t e = cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, static_cast<int>(shared));
+    if (e != cudaSuccess) return static_cast<int>(e);
+  }
+  const uint64_t clusters = p.rows < 65536 ? p.rows : 65536;
+  cudaLaunchConfig_t config{};
+  config.gridDim = dim3(static_cast<unsigned>(clusters * plan.cluster));
+  config.blockDim = dim3(kThreads);
+  config.dynamicSmemBytes = shared;
+  config.stream = stream;
+  cudaLaunchAttribute attribute{};
+  attribute.id = cudaLaunchAttributeClusterDimension;
+  attribute.val.clusterDim.x = plan.cluster;
+  attribute.val.clusterDim.y = 1;
+  attribute.val.clusterDim.z = 1;
+  config.attrs = &attribute;
+  config.numAttrs = 1;
+  return static_cast<int>(cudaLaunchKernelEx(&config, kernel, p));
+}
+
+}  // namespace
+}  // namespace hb
+
+using namespace hb;
+
+extern "C" int hyle_b200_logits_reduce_f32(hyle_b200_stream_t stream, const float *logits,
+                                           uint64_t rows, uint64_t cols, float *lse,
+                                           void *probs_bf16, int32_t *argmax_index,
+                                           float *argmax_value) {
+  if (rows == 0) return HYLE_B200_OK;
+  if (logits == nullptr || cols == 0 || cols > 0x7fffffffull) return HYLE_B200_INVALID_VALUE;
+  LogitsParams p{logits, rows, static_cast<uint32_t>(cols), 0, lse, probs_bf16, argmax_index, argmax_value};
+  const bool vec = aligned_to(logits, 16) && cols % 8 == 0 && (probs_bf16 == nullptr || aligned_to(probs_bf16, 16));
+  auto s = reinterpret_cast<cudaStream_t>(stream);
+  if (lse == nullptr && probs_bf16 == nullptr) return launch_logits<kArgmaxOnly>(s, p, vec);
+  return launch_logits<kProbsBf16>(s, p, vec);
+}
+
+extern "C" int hyle_b200_softmax_f32(hyle_b200_stream_t stream, int kind, const float *in,
+                                     float *out, uint64_t rows, uint64_t cols) {
+  if (rows == 0 || cols == 0) return HYLE_B200_OK;
+  if (in == nullptr || out == nullptr || cols > 0x7fffffffull) return HYLE_B200_INVALID_VALUE;
+  LogitsParams p{in, rows, static_cast<uint32_t>(cols), 0, nullptr, out, nullptr, nullptr};
+  const bool vec = aligned_to(in, 16) && aligned_to(out, 16) && cols % 8 == 0;
+  auto s = reinterpret_cast<cudaStream_t>(stream);
+  if (kind == HYLE_B200_SOFTMAX) return launch_logits<kProbsF32>(s, p, vec);
+  if (kind == HYLE_B200_LOG_SOFTMAX) return launch_logits<kLogF32>(s, p, vec);
+  return HYLE_B200_INVALID_VALUE;
+}

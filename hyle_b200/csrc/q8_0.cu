@@ -1,0 +1,369 @@
+// Q8_0 block quantise / dequantise and the global sum of squares.
+//
+// A Q8_0 block is 34 bytes: little-endian f16 scale, then 32 int8 codes
+// (src/compute_ops/low_precision.cc:28-29).  Arithmetic, per block of 32 inputs
+// (src/compute_provider_ggml/ggml_cpu_provider.cc:585-615 around ggml's reference row quantiser):
+//   amax = max|x|;  d = amax / 127.0f;  id = 1.0f / d;  q = roundf(x * id);  scale = f16_rne(d)
+//   f16 scale == 0, or any |x| non-finite or > 65504*127  ->  34 zero bytes (+ status bit)
+//   decode: bf16_rne(f32(scale) * q)
+//
+// Tiling: a CTA of 256 threads takes 256 consecutive blocks (8192 values, 16 KB of bf16) at a time.
+// Thread t owns the 16-byte vectors k*256+t, k = 0..3; four neighbouring lanes share a block, so
+// amax is two xor shuffles.  The 34-byte blocks are only 2-byte aligned, so the 8704 bytes a tile
+// produces are staged in shared memory and leave as 16-byte coalesced stores.
+#include "common.cuh"
+
+namespace hb {
+namespace {
+
+constexpr int kThreads = 256;
+constexpr int kVectorsPerThread = 4;
+constexpr int kTileBlocks = 256;
+constexpr int kTileBytes = kTileBlocks * 34;  // 8704 = 544 * 16
+constexpr int kMaxPartials = 4096;
+constexpr uint64_t kWorkspaceBytes = 64 + sizeof(double) * kMaxPartials;
+
+// |x| <= 65504*127 as an integer comparison on the magnitude bits; NaN and inf compare above it
+// (ggml_cpu_provider.cc:563-584).
+constexpr uint32_t kLimitBitsF32 = 0x4afde040u;  // bits of 8319008.0f = 65504 * 127
+
+// roundf for |v| < 2^22: add 0.5 with the sign of v rounding toward zero, then truncate.  The
+// round-toward-zero add keeps 0.49999997f + 0.5f below 1.
+__device__ __forceinline__ int round_half_away(float v) {
+  const float half = __uint_as_float((__float_as_uint(v) & 0x80000000u) | 0x3f000000u);
+  return __float2int_rz(__fadd_rz(v, half));
+}
+
+__device__ __forceinline__ uint32_t pack_codes(int a, int b, int c, int d) {
+  return (static_cast<uint32_t>(a) & 0xffu) | ((static_cast<uint32_t>(b) & 0xffu) << 8) |
+         ((static_cast<uint32_t>(c) & 0xffu) << 16) | (static_cast<uint32_t>(d) << 24);
+}
+
+// Eight consecutive values as f32 plus the largest magnitude bit pattern among them.
+template <int kDtype>
+__device__ __forceinline__ void load8(const void *in, uint64_t element, float v[8], uint32_t &amax_bits) {
+  if constexpr (kDtype == HYLE_B200_BF16) {
+    const uint4 raw = ld_stream(reinterpret_cast<const uint4 *>(static_cast<const unsigned short *>(in) + element));
+    v[0] = bf16_lo(raw.x); v[1] = bf16_hi(raw.x); v[2] = bf16_lo(raw.y); v[3] = bf16_hi(raw.y);
+    v[4] = bf16_lo(raw.z); v[5] = bf16_hi(raw.z); v[6] = bf16_lo(raw.w); v[7] = bf16_hi(raw.w);
+    const uint32_t m = __vmaxu2(__vmaxu2(raw.x & 0x7fff7fffu, raw.y & 0x7fff7fffu),
+                                __vmaxu2(raw.z & 0x7fff7fffu, raw.w & 0x7fff7fffu));
+    amax_bits = max(m & 0xffffu, m >> 16) << 16;
+  } else if constexpr (kDtype == HYLE_B200_F16) {
+    const uint4 raw = ld_stream(reinterpret_cast<const uint4 *>(static_cast<const unsigned short *>(in) + element));
+    const uint32_t w[4] = {raw.x, raw.y, raw.z, raw.w};
+    amax_bits = 0;
+#pragma unroll
+    for (int i = 0; i < 4; ++i) {
+      v[2 * i] = f16_to_f32(static_cast<unsigned short>(w[i] & 0xffffu));
+      v[2 * i + 1] = f16_to_f32(static_cast<unsigned short>(w[i] >> 16));
+      amax_bits = max(amax_bits, max(__float_as_uint(v[2 * i]) & 0x7fffffffu,
+                                     __float_as_uint(v[2 * i + 1]) & 0x7fffffffu));
+    }
+  } else {
+    const float4 a = ld_stream(reinterpret_cast<const float4 *>(static_cast<const float *>(in) + element));
+    const float4 b = ld_stream(reinterpret_cast<const float4 *>(static_cast<const float *>(in) + element) + 1);
+    v[0] = a.x; v[1] = a.y; v[2] = a.z; v[3] = a.w; v[4] = b.x; v[5] = b.y; v[6] = b.z; v[7] = b.w;
+    amax_bits = 0;
+#pragma unroll
+    for (int i = 0; i < 8; ++i) amax_bits = max(amax_bits, __float_as_uint(v[i]) & 0x7fffffffu);
+  }
+}
+
+struct SumSquaresState {
+  uint32_t *ticket;
+  double *partials;
+};
+
+__device__ __forceinline__ SumSquaresState workspace_state(void *workspace) {
+  return {static_cast<uint32_t *>(workspace),
+          reinterpret_cast<double *>(static_cast<unsigned char *>(workspace) + 64)};
+}
+
+// Deterministic grid-wide sum: fixed-order CTA reduction, one partial per CTA, and the CTA that
+// takes the last ticket adds the partials in index order.  Which CTA is last does not matter.
+__device__ __forceinline__ void finish_sum(double thread_sum, SumSquaresState ws, double *sum_out) {
+  __shared__ double s_warp[kThreads / 32];
+  __shared__ bool s_last;
+  const int t = threadIdx.x, lane = t & 31, warp = t >> 5;
+  const double w = warp_sum(thread_sum);
+  if (lane == 0) s_warp[warp] = w;
+  __syncthreads();
+  if (t == 0) {
+    double total = s_warp[0];
+#pragma unroll
+    for (int i = 1; i < kThreads / 32; ++i) total += s_warp[i];
+    ws.partials[blockIdx.x] = total;
+    __threadfence();
+    const uint32_t taken = atomicAdd(ws.ticket, 1u);
+    s_last = taken == gridDim.x - 1;
+  }
+  __syncthreads();
+  if (s_last && warp == 0) {
+    __threadfence();
+    double acc = 0.0;
+    for (uint32_t i = lane; i < gridDim.x; i += 32) acc += __ldcg(ws.partials + i);
+    acc = warp_sum(acc);
+    if (lane == 0) {
+      *sum_out = acc;
+      *ws.ticket = 0;  // the workspace is ready for the next stream-ordered launch
+    }
+  }
+}
+
+// kEncode: write Q8_0 blocks.  kDecode: write decoded bf16.  kSumSquares: accumulate sum x^2.
+template <int kDtype, bool kEncode, bool kDecode, bool kSumSquares>
+__global__ void __launch_bounds__(kThreads)
+q8_0_kernel(const void *__restrict__ in, uint64_t blocks, unsigned char *__restrict__ blocks_out,
+            unsigned short *__restrict__ decoded, double *sum_out, uint32_t *status_word,
+            void *workspace, int out_aligned) {
+  __shared__ __align__(16) unsigned char staged[2][kTileBytes];
+  const int t = threadIdx.x;
+  const int sub = t & 3;  // which quarter of a block this lane holds
+  const uint64_t tiles = (blocks + kTileBlocks - 1) / kTileBlocks;
+  double sum = 0.0;
+  bool invalid_seen = false;
+  int buffer = 0;
+  for (uint64_t tile = blockIdx.x; tile < tiles; tile += gridDim.x, buffer ^= 1) {
+    const uint64_t first_block = tile * kTileBlocks;
+    const uint32_t tile_blocks = static_cast<uint32_t>(min(static_cast<uint64_t>(kTileBlocks), blocks - first_block));
+    const bool full = tile_blocks == kTileBlocks;
+    float v[kVectorsPerThread][8];
+    uint32_t amax_bits[kVectorsPerThread];
+#pragma unroll
+    for (int k = 0; k < kVectorsPerThread; ++k) {
+      const uint32_t block = k * 64 + (t >> 2);
+      if (full || block < tile_blocks) {
+        load8<kDtype>(in, (first_block + block) * 32 + sub * 8, v[k], amax_bits[k]);
+      } else {
+#pragma unroll
+        for (int i = 0; i < 8; ++i) v[k][i] = 0.0f;
+        amax_bits[k] = 0;
+      }
+    }
+    float tile_sum = 0.0f;
+#pragma unroll
+    for (int k = 0; k < kVectorsPerThread; ++k) {
+      const uint32_t block = k * 64 + (t >> 2);
+      if constexpr (kSumSquares) {
+#pragma unroll
+        for (int i = 0; i < 8; ++i) tile_sum = fmaf(v[k][i], v[k][i], tile_sum);
+      }
+      uint32_t m = amax_bits[k];
+      m = max(m, __shfl_xor_sync(kFullMask, m, 1));
+      m = max(m, __shfl_xor_sync(kFullMask, m, 2));
+      const bool valid = m <= kLimitBitsF32;
+      const float d = __fdiv_rn(__uint_as_float(m), 127.0f);
+      const unsigned short scale = f32_to_f16(d);
+      const bool zero_block = !valid || scale == 0;
+      const float id = zero_block ? 0.0f : __fdiv_rn(1.0f, d);
+      invalid_seen |= !valid;
+      int q[8];
+#pragma unroll
+      for (int i = 0; i < 8; ++i) q[i] = zero_block ? 0 : round_half_away(__fmul_rn(v[k][i], id));
+      const unsigned short stored_scale = zero_block ? static_cast<unsigned short>(0) : scale;
+      if constexpr (kEncode) {
+        if (full || block < tile_blocks) {
+          unsigned short *dst = reinterpret_cast<unsigned short *>(staged[buffer] + block * 34);
+          const uint32_t w0 = pack_codes(q[0], q[1], q[2], q[3]);
+          const uint32_t w1 = pack_codes(q[4], q[5], q[6], q[7]);
+          if (sub == 0) dst[0] = stored_scale;
+          dst[1 + sub * 4 + 0] = static_cast<unsigned short>(w0 & 0xffffu);
+          dst[1 + sub * 4 + 1] = static_cast<unsigned short>(w0 >> 16);
+          dst[1 + sub * 4 + 2] = static_cast<unsigned short>(w1 & 0xffffu);
+          dst[1 + sub * 4 + 3] = static_cast<unsigned short>(w1 >> 16);
+        }
+      }
+      if constexpr (kDecode) {
+        if (full || block < tile_blocks) {
+          const float s = f16_to_f32(stored_scale);
+          const uint4 out = make_uint4(
+              pack_bf16x2(__fmul_rn(s, static_cast<float>(q[0])), __fmul_rn(s, static_cast<float>(q[1]))),
+              pack_bf16x2(__fmul_rn(s, static_cast<float>(q[2])), __fmul_rn(s, static_cast<float>(q[3]))),
+              pack_bf16x2(__fmul_rn(s, static_cast<float>(q[4])), __fmul_rn(s, static_cast<float>(q[5]))),
+              pack_bf16x2(__fmul_rn(s, static_cast<float>(q[6])), __fmul_rn(s, static_cast<float>(q[7]))));
+          st_stream(reinterpret_cast<uint4 *>(decoded + (first_block + block) * 32 + sub * 8), out);
+        }
+      }
+    }
+    if constexpr (kSumSquares) sum += static_cast<double>(tile_sum);
+    if constexpr (kEncode) {
+      // One barrier per tile: the staging buffer alternates, and this barrier also orders the
+      // previous tile's reads of the other buffer before the next tile's writes to it.
+      __syncthreads();
+      unsigned char *dst = blocks_out + first_block * 34;
+      if (full && out_aligned) {
+        const uint4 *src = reinterpret_cast<const uint4 *>(staged[buffer]);
+        for (int i = t; i < kTileBytes / 16; i += kThreads) st_stream(reinterpret_cast<uint4 *>(dst) + i, src[i]);
+      } else {
+        const unsigned short *src = reinterpret_cast<const unsigned short *>(staged[buffer]);
+        for (uint32_t i = t; i < tile_blocks * 17; i += kThreads) st_stream(reinterpret_cast<unsigned short *>(dst) + i, src[i]);
+      }
+    }
+  }
+  if (status_word != nullptr && invalid_seen) atomicOr(status_word, HYLE_B200_STATUS_INVALID_Q8_INPUT);
+  if constexpr (kSumSquares) finish_sum(sum, workspace_state(workspace), sum_out);
+}
+
+// Decode-only: a tile's 8704 bytes are pulled into shared memory with 16-byte loads, then every
+// thread rebuilds its four vectors.
+__global__ void __launch_bounds__(kThreads)
+q8_0_decode_kernel(const unsigned char *__restrict__ blocks_in, uint64_t blocks,
+                   unsigned short *__restrict__ decoded, int in_aligned) {
+  __shared__ __align__(16) unsigned char staged[2][kTileBytes];
+  const int t = threadIdx.x, sub = t & 3;
+  const uint64_t tiles = (blocks + kTileBlocks - 1) / kTileBlocks;
+  int buffer = 0;
+  for (uint64_t tile = blockIdx.x; tile < tiles; tile += gridDim.x, buffer ^= 1) {
+    const uint64_t first_block = tile * kTileBlocks;
+    const uint32_t tile_blocks = static_cast<uint32_t>(min(static_cast<uint64_t>(kTileBlocks), blocks - first_block));
+    const bool full = tile_blocks == kTileBlocks;
+    const unsigned char *src = blocks_in + first_block * 34;
+    if (full && in_aligned) {
+      uint4 *dst = reinterpret_cast<uint4 *>(staged[buffer]);
+      uint4 held[3];
+#pragma unroll
+      for (int j = 0; j < 3; ++j)
+        if (t + j * kThreads < kTileBytes / 16) held[j] = ld_stream(reinterpret_cast<const uint4 *>(src) + t + j * kThreads);
+#pragma unroll
+      for (int j = 0; j < 3; ++j)
+        if (t + j * kThreads < kTileBytes / 16) dst[t + j * kThreads] = held[j];
+    } else {
+      unsigned short *dst = reinterpret_cast<unsigned short *>(staged[buffer]);
+      for (uint32_t i = t; i < tile_blocks * 17; i += kThreads) dst[i] = ld_stream(reinterpret_cast<const unsigned short *>(src) + i);
+    }
+    __syncthreads();
+#pragma unroll
+    for (int k = 0; k < kVectorsPerThread; ++k) {
+      const uint32_t block = k * 64 + (t >> 2);
+      if (full || block < tile_blocks) {
+        const unsigned short *b = reinterpret_cast<const unsigned short *>(staged[buffer] + block * 34);
+        const float s = f16_to_f32(b[0]);
+        uint32_t out[4];
+#pragma unroll
+        for (int i = 0; i < 4; ++i) {
+          const unsigned short pair = b[1 + sub * 4 + i];
+          const float lo = static_cast<float>(static_cast<int>(static_cast<signed char>(pair & 0xffu)));
+          const float hi = static_cast<float>(static_cast<int>(static_cast<signed char>(pair >> 8)));
+          out[i] = pack_bf16x2(__fmul_rn(s, lo), __fmul_rn(s, hi));
+        }
+        st_stream(reinterpret_cast<uint4 *>(decoded + (first_block + block) * 32 + sub * 8),
+                  make_uint4(out[0], out[1], out[2], out[3]));
+      }
+    }
+  }
+}
+
+// Sum of squares alone: a pure read stream.
+__global__ void __launch_bounds__(kThreads)
+sum_squares_bf16_kernel(const uint4 *__restrict__ in, uint64_t vectors,
+                        const unsigned short *__restrict__ tail, uint32_t tail_count, double *sum_out,
+                        void *workspace) {
+  const uint64_t stride = static_cast<uint64_t>(gridDim.x) * kThreads;
+  uint64_t i = static_cast<uint64_t>(blockIdx.x) * kThreads + threadIdx.x;
+  double sum = 0.0;
+  auto squares8 = [](uint4 v, float acc) {
+    const uint32_t w[4] = {v.x, v.y, v.z, v.w};
+#pragma unroll
+    for (int j = 0; j < 4; ++j) {
+      const float lo = bf16_lo(w[j]), hi = bf16_hi(w[j]);
+      acc = fmaf(hi, hi, fmaf(lo, lo, acc));
+    }
+    return acc;
+  };
+  for (; i + 3 * stride < vectors; i += 4 * stride) {
+    uint4 v[4];
+#pragma unroll
+    for (int k = 0; k < 4; ++k) v[k] = ld_stream(in + i + k * stride);
+    float part = 0.0f;
+#pragma unroll
+    for (int k = 0; k < 4; ++k) part = squares8(v[k], part);
+    sum += static_cast<double>(part);
+  }
+  for (; i < vectors; i += stride) sum += static_cast<double>(squares8(ld_stream(in + i), 0.0f));
+  if (blockIdx.x == 0 && threadIdx.x < tail_count) {
+    const float f = bf16_to_f32(tail[threadIdx.x]);
+    sum += static_cast<double>(f * f);
+  }
+  finish_sum(sum, workspace_state(workspace), sum_out);
+}
+
+unsigned q8_grid(uint64_t blocks) {
+  const uint64_t tiles = (blocks + kTileBlocks - 1) / kTileBlocks;
+  return clamp_grid(tiles, min(static_cast<uint64_t>(kMaxPartials), static_cast<uint64_t>(sm_count()) * 6));
+}
+
+}  // namespace
+}  // namespace hb
+
+using namespace hb;
+
+extern "C" uint64_t hyle_b200_sum_squares_workspace_bytes(void) { return kWorkspaceBytes; }
+
+extern "C" int hyle_b200_q8_0_encode(hyle_b200_stream_t stream, int dtype, const void *in,
+                                     uint64_t count, void *blocks_out, uint32_t *status_word) {
+  if (count == 0) return HYLE_B200_OK;
+  if (in == nullptr || blocks_out == nullptr || count % 32 != 0 || !aligned_to(blocks_out, 2))
+    return HYLE_B200_INVALID_VALUE;
+  if (!aligned_to(in, 16)) return HYLE_B200_NOT_SUPPORTED;
+  auto s = reinterpret_cast<cudaStream_t>(stream);
+  const uint64_t blocks = count / 32;
+  const unsigned grid = q8_grid(blocks);
+  const int out_aligned = aligned_to(blocks_out, 16);
+  auto *out = static_cast<unsigned char *>(blocks_out);
+  if (dtype == HYLE_B200_BF16)
+    q8_0_kernel<HYLE_B200_BF16, true, false, false><<<grid, kThreads, 0, s>>>(in, blocks, out, nullptr, nullptr, status_word, nullptr, out_aligned);
+  else if (dtype == HYLE_B200_F16)
+    q8_0_kernel<HYLE_B200_F16, true, false, false><<<grid, kThreads, 0, s>>>(in, blocks, out, nullptr, nullptr, status_word, nullptr, out_aligned);
+  else if (dtype == HYLE_B200_F32)
+    q8_0_kernel<HYLE_B200_F32, true, false, false><<<grid, kThreads, 0, s>>>(in, blocks, out, nullptr, nullptr, status_word, nullptr, out_aligned);
+  else
+    return HYLE_B200_INVALID_VALUE;
+  return launch_result();
+}
+
+extern "C" int hyle_b200_q8_0_decode_bf16(hyle_b200_stream_t stream, const void *blocks,
+                                          uint64_t count, void *out_bf16) {
+  if (count == 0) return HYLE_B200_OK;
+  if (blocks == nullptr || out_bf16 == nullptr || count % 32 != 0 || !aligned_to(blocks, 2))
+    return HYLE_B200_INVALID_VALUE;
+  if (!aligned_to(out_bf16, 16)) return HYLE_B200_NOT_SUPPORTED;
+  const uint64_t n = count / 32;
+  q8_0_decode_kernel<<<q8_grid(n), kThreads, 0, reinterpret_cast<cudaStream_t>(stream)>>>(
+      static_cast<const unsigned char *>(blocks), n, static_cast<unsigned short *>(out_bf16),
+      aligned_to(blocks, 16));
+  return launch_result();
+}
+
+extern "C" int hyle_b200_sum_squares_bf16(hyle_b200_stream_t stream, const void *in, uint64_t count,
+                                          double *sum_out, void *workspace, uint64_t workspace_bytes) {
+  if (sum_out == nullptr || workspace == nullptr || workspace_bytes < kWorkspaceBytes ||
+      !aligned_to(workspace, 8) || (in == nullptr && count != 0))
+    return HYLE_B200_INVALID_VALUE;
+  if (!aligned_to(in, 16)) return HYLE_B200_NOT_SUPPORTED;
+  const uint64_t vectors = count / 8;
+  const uint32_t tail = static_cast<uint32_t>(count % 8);
+  const unsigned grid = clamp_grid((vectors + kThreads * 4 - 1) / (kThreads * 4),
+                                   min(static_cast<uint64_t>(kMaxPartials), static_cast<uint64_t>(sm_count()) * 8));
+  sum_squares_bf16_kernel<<<grid, kThreads, 0, reinterpret_cast<cudaStream_t>(stream)>>>(
+      static_cast<const uint4 *>(in), vectors, static_cast<const unsigned short *>(in) + vectors * 8, tail,
+      sum_out, workspace);
+  return launch_result();
+}
+
+extern "C" int hyle_b200_q8_0_roundtrip_bf16(hyle_b200_stream_t stream, const void *in,
+                                             uint64_t count, void *blocks_out, void *decoded_bf16,
+                                             double *sum_squares_out, uint32_t *status_word,
+                                             void *workspace, uint64_t workspace_bytes) {
+  if (in == nullptr && count != 0) return HYLE_B200_INVALID_VALUE;
+  if (blocks_out == nullptr || decoded_bf16 == nullptr || sum_squares_out == nullptr ||
+      workspace == nullptr || workspace_bytes < kWorkspaceBytes || !aligned_to(workspace, 8) ||
+      count % 32 != 0 || !aligned_to(blocks_out, 2))
+    return HYLE_B200_INVALID_VALUE;
+  if (!aligned_to(in, 16) || !aligned_to(decoded_bf16, 16)) return HYLE_B200_NOT_SUPPORTED;
+  const uint64_t blocks = count / 32;
+  q8_0_kernel<HYLE_B200_BF16, true, true, true><<<q8_grid(blocks), kThreads, 0, reinterpret_cast<cudaStream_t>(stream)>>>(
+      in, blocks, static_cast<unsigned char *>(blocks_out), static_cast<unsigned short *>(decoded_bf16),
+      sum_squares_out, status_word, workspace, aligned_to(blocks_out, 16));
+  return launch_result();
+}

@@ -1,0 +1,406 @@
+// Row-wise operators: Reduce{kSum|kMean|kMinimum|kMaximum} over the last axis of f32 rows, its
+// fusion with a bias add (one read of A, one write of C, reductions from registers), and bf16
+// RmsNorm with the optional fused residual add.  Each row is read from HBM exactly once.
+#include "common.cuh"
+
+#include <math_constants.h>
+#include <type_traits>
+
+namespace hb {
+namespace {
+
+constexpr int kThreads = 256;
+constexpr int kWarps = kThreads / kWarpSize;
+
+// ================================================================================================
+// f32 rows: optional op with a row vector, optional store, row sum / max / min.
+// One CTA owns one row at a time.  Column slot (k, t) = four columns starting at (k*256 + t)*4; a
+// thread adds its columns in (k, lane-of-vector) order, warps combine by xor butterfly, the eight
+// warp partials are added in warp order.  The order does not depend on the grid, on alignment or on
+// which outputs are requested, so a fused launch and separate launches agree bit for bit.
+// ================================================================================================
+constexpr int kOpNone = -1;
+
+struct RowF32Params {
+  const float *a;
+  const float *rhs;  // one row, or nullptr
+  float *c;          // elementwise output or nullptr
+  float *row_sum;    // nullptr to skip
+  float *row_max;
+  float *row_min;
+  uint64_t rows;
+  uint64_t cols;
+  int mean;          // row_sum receives sum / cols
+};
+
+template <int kOp>
+__device__ __forceinline__ float row_op(float a, float b) {
+  if constexpr (kOp == HYLE_B200_BINARY_ADD) return __fadd_rn(a, b);
+  if constexpr (kOp == HYLE_B200_BINARY_MULTIPLY) return __fmul_rn(a, b);
+  return a;
+}
+
+struct RowAcc {
+  float sum, mx, mn;
+  __device__ __forceinline__ RowAcc() : sum(0.0f), mx(-INFINITY), mn(INFINITY) {}
+  __device__ __forceinline__ void add(float v) {
+    sum = __fadd_rn(sum, v);
+    mx = max_nan(mx, v);
+    mn = min_nan(mn, v);
+  }
+};
+
+// kSlots > 0: cols == kSlots*1024 exactly, 16-byte aligned pointers, bias kept in registers.
+// kSlots == 0: any cols; kVec selects 16-byte accesses for full slots (needs cols % 4 == 0 and
+// aligned pointers), scalar accesses otherwise.
+template <int kSlots, bool kVec, int kOp>
+__global__ void __launch_bounds__(kThreads) row_f32_kernel(const RowF32Params p) {
+  __shared__ float s_sum[2][kWarps], s_max[2][kWarps], s_min[2][kWarps];
+  const int t = threadIdx.x, lane = t & 31, warp = t >> 5;
+  const uint64_t cols = p.cols;
+
+  float4 bias[kSlots > 0 ? kSlots : 1];
+  if constexpr (kSlots > 0 && kOp != kOpNone) {
+#pragma unroll
+    for (int k = 0; k < kSlots; ++k) bias[k] = __ldg(reinterpret_cast<const float4 *>(p.rhs) + k * kThreads + t);
+  }
+
+  int parity = 0;
+  for (uint64_t row = blockIdx.x; row < p.rows; row += gridDim.x, parity ^= 1) {
+    const float *a_row = p.a + row * cols;
+    float *c_row = p.c != nullptr ? p.c + row * cols : nullptr;
+    RowAcc acc;
+    if constexpr (kSlots > 0) {
+      float4 x[kSlots];
+#pragma unroll
+      for (int k = 0; k < kSlots; ++k) x[k] = ld_stream(reinterpret_cast<const float4 *>(a_row) + k * kThreads + t);
+#pragma unroll
+      for (int k = 0; k < kSlots; ++k) {
+        x[k] = make_float4(row_op<kOp>(x[k].x, bias[k].x), row_op<kOp>(x[k].y, bias[k].y),
+                           row_op<kOp>(x[k].z, bias[k].z), row_op<kOp>(x[k].w, bias[k].w));
+        if (c_row != nullptr) st_stream(reinterpret_cast<float4 *>(c_row) + k * kThreads + t, x[k]);
+        acc.add(x[k].x); acc.add(x[k].y); acc.add(x[k].z); acc.add(x[k].w);
+      }
+    } else {
+      for (uint64_t base = static_cast<uint64_t>(t) * 4; base < cols; base += kThreads * 4) {
+        if (kVec && base + 4 <= cols) {
+          float4 x = ld_stream(reinterpret_cast<const float4 *>(a_row + base));
+          if constexpr (kOp != kOpNone) {
+            const float4 b = __ldg(reinterpret_cast<const float4 *>(p.rhs + base));
+            x = make_float4(row_op<kOp>(x.x, b.x), row_op<kOp>(x.y, b.y), row_op<kOp>(x.z, b.z),
+                            row_op<kOp>(x.w, b.w));
+          }
+          if (c_row != nullptr) st_stream(reinterpret_cast<float4 *>(c_row + base), x);
+          acc.add(x.x); acc.add(x.y); acc.add(x.z); acc.add(x.w);
+        } else {
+          for (uint64_t col = base; col < base + 4 && col < cols; ++col) {
+            float x = ld_stream(a_row + col);
+            if constexpr (kOp != kOpNone) x = row_op<kOp>(x, __ldg(p.rhs + col));
+            if (c_row != nullptr) st_stream(c_row + col, x);
+            acc.add(x);
+          }
+        }
+      }
+    }
+    const float sum = warp_sum(acc.sum);
+    const float mx = warp_max_nan(acc.mx);
+    const float mn = warp_min_nan(acc.mn);
+    if (lane == 0) {
+      s_sum[parity][warp] = sum;
+      s_max[parity][warp] = mx;
+      s_min[parity][warp] = mn;
+    }
+    // One barrier per row: the partials are double buffered, and the barrier of the next row
+    // orders this row's read by thread 0 before the row after next overwrites the slot.
+    __syncthreads();
+    if (t == 0) {
+      float total = s_sum[parity][0], hi = s_max[parity][0], lo = s_min[parity][0];
+#pragma unroll
+      for (int w = 1; w < kWarps; ++w) {
+        total = __fadd_rn(total, s_sum[parity][w]);
+        hi = max_nan(hi, s_max[parity][w]);
+        lo = min_nan(lo, s_min[parity][w]);
+      }
+      if (p.row_sum != nullptr)
+        p.row_sum[row] = p.mean ? __fdiv_rn(total, static_cast<float>(cols)) : total;
+      if (p.row_max != nullptr) p.row_max[row] = hi;
+      if (p.row_min != nullptr) p.row_min[row] = lo;
+    }
+  }
+}
+
+template <int kOp>
+int launch_row_f32(cudaStream_t stream, const RowF32Params &p) {
+  if (p.rows == 0) return HYLE_B200_OK;
+  const bool aligned = aligned_to(p.a, 16) && (p.rhs == nullptr || aligned_to(p.rhs, 16)) &&
+                       (p.c == nullptr || aligned_to(p.c, 16)) && p.cols % 4 == 0;
+  // 48-64 registers per thread: five to eight CTAs share an SM.
+  const unsigned grid = clamp_grid(p.rows, static_cast<uint64_t>(sm_count()) * 8);
+  if (aligned && p.cols == 1024) row_f32_kernel<1, true, kOp><<<grid, kThreads, 0, stream>>>(p);
+  else if (aligned && p.cols == 2048) row_f32_kernel<2, true, kOp><<<grid, kThreads, 0, stream>>>(p);
+  else if (aligned && p.cols == 4096) row_f32_kernel<4, true, kOp><<<grid, kThreads, 0, stream>>>(p);
+  else if (aligned && p.cols == 8192) row_f32_kernel<8, true, kOp><<<grid, kThreads, 0, stream>>>(p);
+  else if (aligned) row_f32_kernel<0, true, kOp><<<grid, kThreads, 0, stream>>>(p);
+  else row_f32_kernel<0, false, kOp><<<grid, kThreads, 0, stream>>>(p);
+  return launch_result();
+}
+
+// ================================================================================================
+// bf16 RmsNorm, optional fused residual add.
+//   h = kResidual ? bf16_rne(f32 x + f32 r) : x;  ss = sum f32(h)^2 (fma, f32);
+//   inverse = 1.0f / sqrtf(ss / hidden + eps);     y = bf16_rne((f32(h) * inverse) * w)
+// (src/simd/math/activations.cc:124-146).  kWeight: 0 none, 1 bf16, 2 f32.
+// ================================================================================================
+__device__ __forceinline__ float inverse_rms(float sum_squares, uint32_t hidden, float eps) {
+  const float mean = __fdiv_rn(sum_squares, static_cast<float>(hidden));
+  return __fdiv_rn(1.0f, __fsqrt_rn(__fadd_rn(mean, eps)));
+}
+
+__device__ __forceinline__ uint32_t add_pair(uint32_t a, uint32_t b) {
+  return pack_bf16x2(__fadd_rn(bf16_lo(a), bf16_lo(b)), __fadd_rn(bf16_hi(a), bf16_hi(b)));
+}
+__device__ __forceinline__ uint4 add_vec(uint4 a, uint4 b) {
+  return make_uint4(add_pair(a.x, b.x), add_pair(a.y, b.y), add_pair(a.z, b.z), add_pair(a.w, b.w));
+}
+__device__ __forceinline__ float squares(uint32_t w, float acc) {
+  const float lo = bf16_lo(w), hi = bf16_hi(w);
+  return fmaf(hi, hi, fmaf(lo, lo, acc));
+}
+__device__ __forceinline__ float squares(uint4 v, float acc) {
+  return squares(v.w, squares(v.z, squares(v.y, squares(v.x, acc))));
+}
+
+// Scale eight packed bf16 values by inverse and the weight vector at element offset `element`.
+template <int kWeight>
+__device__ __forceinline__ uint4 scale_vec(uint4 h, float inverse, const void *weight, uint64_t element) {
+  float v[8] = {bf16_lo(h.x), bf16_hi(h.x), bf16_lo(h.y), bf16_hi(h.y),
+                bf16_lo(h.z), bf16_hi(h.z), bf16_lo(h.w), bf16_hi(h.w)};
+#pragma unroll
+  for (int i = 0; i < 8; ++i) v[i] = __fmul_rn(v[i], inverse);
+  if constexpr (kWeight == 1) {
+    const uint4 w = __ldg(reinterpret_cast<const uint4 *>(static_cast<const unsigned short *>(weight) + element));
+    const float f[8] = {bf16_lo(w.x), bf16_hi(w.x), bf16_lo(w.y), bf16_hi(w.y),
+                        bf16_lo(w.z), bf16_hi(w.z), bf16_lo(w.w), bf16_hi(w.w)};
+#pragma unroll
+    for (int i = 0; i < 8; ++i) v[i] = __fmul_rn(v[i], f[i]);
+  } else if constexpr (kWeight == 2) {
+    const float4 w0 = __ldg(reinterpret_cast<const float4 *>(static_cast<const float *>(weight) + element));
+    const float4 w1 = __ldg(reinterpret_cast<const float4 *>(static_cast<const float *>(weight) + element) + 1);
+    const float f[8] = {w0.x, w0.y, w0.z, w0.w, w1.x, w1.y, w1.z, w1.w};
+#pragma unroll
+    for (int i = 0; i < 8; ++i) v[i] = __fmul_rn(v[i], f[i]);
+  }
+  return make_uint4(pack_bf16x2(v[0], v[1]), pack_bf16x2(v[2], v[3]), pack_bf16x2(v[4], v[5]),
+                    pack_bf16x2(v[6], v[7]));
+}
+
+// One warp per row, the whole row in registers: hidden == kVectors*256.  No barrier, no shared
+// memory; every lane has 2*kVectors independent 16-byte loads in flight.
+template <int kVectors, bool kResidual, int kWeight>
+__global__ void __launch_bounds__(kThreads)
+rms_warp_kernel(const uint4 *x, const uint4 *residual, const void *__restrict__ weight, uint4 *y,
+                uint4 *h_out, uint64_t rows, float eps) {
+  constexpr uint32_t kHidden = kVectors * 256;
+  const int lane = threadIdx.x & 31;
+  const uint64_t warps = static_cast<uint64_t>(gridDim.x) * (blockDim.x >> 5);
+  for (uint64_t row = static_cast<uint64_t>(blockIdx.x) * (blockDim.x >> 5) + (threadIdx.x >> 5);
+       row < rows; row += warps) {
+    const uint64_t base = row * (kHidden / 8);
+    uint4 h[kVectors];
+    if constexpr (kResidual) {
+      uint4 r[kVectors];
+#pragma unroll
+      for (int k = 0; k < kVectors; ++k) {
+        h[k] = ld_stream(x + base + k * 32 + lane);
+        r[k] = ld_stream(residual + base + k * 32 + lane);
+      }
+#pragma unroll
+      for (int k = 0; k < kVectors; ++k) {
+        h[k] = add_vec(h[k], r[k]);
+        st_stream(h_out + base + k * 32 + lane, h[k]);
+      }
+    } else {
+#pragma unroll
+      for (int k = 0; k < kVectors; ++k) h[k] = ld_stream(x + base + k * 32 + lane);
+    }
+    float ss = 0.0f;
+#pragma unroll
+    for (int k = 0; k < kVectors; ++k) ss = squares(h[k], ss);
+    ss = warp_sum(ss);
+    const float inverse = inverse_rms(ss, kHidden, eps);
+#pragma unroll
+    for (int k = 0; k < kVectors; ++k)
+      st_stream(y + base + k * 32 + lane,
+                scale_vec<kWeight>(h[k], inverse, weight, static_cast<uint64_t>(k * 32 + lane) * 8));
+  }
+}
+
+// One CTA per row, the row staged in shared memory as bf16: any hidden up to kMaxStagedHidden.
+constexpr uint32_t kMaxStagedHidden = 32768;
+
+template <bool kVec, bool kResidual, int kWeight>
+__global__ void __launch_bounds__(kThreads)
+rms_cta_kernel(const unsigned short *x, const unsigned short *residual,
+               const void *__restrict__ weight, unsigned short *y, unsigned short *h_out,
+               uint64_t rows, uint32_t hidden, float eps) {
+  extern __shared__ __align__(16) unsigned char staged_bytes[];
+  __shared__ float s_partial[2][kWarps];
+  unsigned short *staged = reinterpret_cast<unsigned short *>(staged_bytes);
+  const int t = threadIdx.x, lane = t & 31, warp = t >> 5;
+  int parity = 0;
+  for (uint64_t row = blockIdx.x; row < rows; row += gridDim.x, parity ^= 1) {
+    const uint64_t base = row * hidden;
+    float ss = 0.0f;
+    if constexpr (kVec) {
+      for (uint32_t v = t; v < hidden / 8; v += kThreads) {
+        uint4 h = ld_stream(reinterpret_cast<const uint4 *>(x + base) + v);
+        if constexpr (kResidual) {
+          h = add_vec(h, ld_stream(reinterpret_cast<const uint4 *>(residual + base) + v));
+          st_stream(reinterpret_cast<uint4 *>(h_out + base) + v, h);
+        }
+        reinterpret_cast<uint4 *>(staged)[v] = h;
+        ss = squares(h, ss);
+      }
+    } else {
+      for (uint32_t i = t; i < hidden; i += kThreads) {
+        unsigned short h = x[base + i];
+        if constexpr (kResidual) {
+          h = f32_to_bf16(__fadd_rn(bf16_to_f32(h), bf16_to_f32(residual[base + i])));
+          h_out[base + i] = h;
+        }
+        staged[i] = h;
+        const float f = bf16_to_f32(h);
+        ss = fmaf(f, f, ss);
+      }
+    }
+    ss = warp_sum(ss);
+    if (lane == 0) s_partial[parity][warp] = ss;
+    __syncthreads();  // also publishes the staged row
+    float total = s_partial[parity][0];
+#pragma unroll
+    for (int w = 1; w < kWarps; ++w) total = __fadd_rn(total, s_partial[parity][w]);
+    const float inverse = inverse_rms(total, hidden, eps);
+    if constexpr (kVec) {
+      for (uint32_t v = t; v < hidden / 8; v += kThreads)
+        st_stream(reinterpret_cast<uint4 *>(y + base) + v,
+                  scale_vec<kWeight>(reinterpret_cast<const uint4 *>(staged)[v], inverse, weight,
+                                     static_cast<uint64_t>(v) * 8));
+    } else {
+      for (uint32_t i = t; i < hidden; i += kThreads) {
+        float v = __fmul_rn(bf16_to_f32(staged[i]), inverse);
+        if constexpr (kWeight == 1) v = __fmul_rn(v, bf16_to_f32(static_cast<const unsigned short *>(weight)[i]));
+        if constexpr (kWeight == 2) v = __fmul_rn(v, static_cast<const float *>(weight)[i]);
+        y[base + i] = f32_to_bf16(v);
+      }
+    }
+    __syncthreads();  // the staged row is rewritten by the next iteration
+  }
+}
+
+template <bool kResidual, int kWeight>
+int launch_rms(cudaStream_t stream, const void *x, const void *residual, const void *weight, void *y,
+               void *h, uint64_t rows, uint64_t hidden, float eps) {
+  const bool aligned = aligned_to(x, 16) && aligned_to(y, 16) && (weight == nullptr || aligned_to(weight, 16)) &&
+                       (!kResidual || (aligned_to(residual, 16) && aligned_to(h, 16))) && hidden % 8 == 0;
+  const int sms = sm_count();
+  auto warp_launch = [&](auto vectors_tag) {
+    constexpr int kVectors = decltype(vectors_tag)::value;
+    // Small row counts get small CTAs so the rows spread over all SMs.
+    int warps_per_cta = kWarps;
+    while (warps_per_cta > 1 && rows < static_cast<uint64_t>(sms) * warps_per_cta) warps_per_cta >>= 1;
+    const uint64_t ctas = (rows + warps_per_cta - 1) / warps_per_cta;
+    const unsigned grid = clamp_grid(ctas, static_cast<uint64_t>(sms) * (2048 / (warps_per_cta * 32)));
+    rms_warp_kernel<kVectors, kResidual, kWeight><<<grid, warps_per_cta * 32, 0, stream>>>(
+        static_cast<const uint4 *>(x), static_cast<const uint4 *>(residual), weight,
+        static_cast<uint4 *>(y), static_cast<uint4 *>(h), rows, eps);
+    return launch_result();
+  };
+  if (aligned && hidden == 256) return warp_launch(std::integral_constant<int, 1>{});
+  if (aligned && hidden == 512) return warp_launch(std::integral_constant<int, 2>{});
+  if (aligned && hidden == 1024) return warp_launch(std::integral_constant<int, 4>{});
+  if (aligned && hidden == 2048) return warp_launch(std::integral_constant<int, 8>{});
+  if (hidden > kMaxStagedHidden) return HYLE_B200_NOT_SUPPORTED;
+  const size_t staged = (static_cast<size_t>(hidden) * 2 + 15) & ~static_cast<size_t>(15);
+  const unsigned grid = clamp_grid(rows, static_cast<uint64_t>(sms) * 4);
+  if (aligned) {
+    auto kernel = rms_cta_kernel<true, kResidual, kWeight>;
+    if (staged > 48 * 1024) cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, 64 * 1024);
+    kernel<<<grid, kThreads, staged, stream>>>(
+        static_cast<const unsigned short *>(x), static_cast<const unsigned short *>(residual), weight,
+        static_cast<unsigned short *>(y), static_cast<unsigned short *>(h), rows,
+        static_cast<uint32_t>(hidden), eps);
+  } else {
+    auto kernel = rms_cta_kernel<false, kResidual, kWeight>;
+    if (staged > 48 * 1024) cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, 64 * 1024);
+    kernel<<<grid, kThreads, staged, stream>>>(
+        static_cast<const unsigned short *>(x), static_cast<const unsigned short *>(residual), weight,
+        static_cast<unsigned short *>(y), static_cast<unsigned short *>(h), rows,
+        static_cast<uint32_t>(hidden), eps);
+  }
+  return launch_result();
+}
+
+template <bool kResidual>
+int dispatch_rms(cudaStream_t stream, const void *x, const void *residual, const void *weight,
+                 int weight_dtype, void *y, void *h, uint64_t rows, uint64_t hidden, float eps) {
+  if (rows == 0 || hidden == 0) return HYLE_B200_OK;
+  if (x == nullptr || y == nullptr || (kResidual && (residual == nullptr || h == nullptr)))
+    return HYLE_B200_INVALID_VALUE;
+  if (weight == nullptr) return launch_rms<kResidual, 0>(stream, x, residual, nullptr, y, h, rows, hidden, eps);
+  if (weight_dtype == HYLE_B200_BF16) return launch_rms<kResidual, 1>(stream, x, residual, weight, y, h, rows, hidden, eps);
+  if (weight_dtype == HYLE_B200_F32) return launch_rms<kResidual, 2>(stream, x, residual, weight, y, h, rows, hidden, eps);
+  return HYLE_B200_INVALID_VALUE;
+}
+
+}  // namespace
+}  // namespace hb
+
+using namespace hb;
+
+extern "C" int hyle_b200_reduce_rows_f32(hyle_b200_stream_t stream, int kind, const float *in,
+                                         float *out, uint64_t rows, uint64_t cols) {
+  if (rows == 0) return HYLE_B200_OK;
+  if (out == nullptr || (in == nullptr && cols != 0) || kind < HYLE_B200_REDUCE_SUM ||
+      kind > HYLE_B200_REDUCE_MAXIMUM)
+    return HYLE_B200_INVALID_VALUE;
+  RowF32Params p{};
+  p.a = in;
+  p.rows = rows;
+  p.cols = cols;
+  p.mean = kind == HYLE_B200_REDUCE_MEAN;
+  if (kind == HYLE_B200_REDUCE_SUM || kind == HYLE_B200_REDUCE_MEAN) p.row_sum = out;
+  if (kind == HYLE_B200_REDUCE_MAXIMUM) p.row_max = out;
+  if (kind == HYLE_B200_REDUCE_MINIMUM) p.row_min = out;
+  return launch_row_f32<kOpNone>(reinterpret_cast<cudaStream_t>(stream), p);
+}
+
+extern "C" int hyle_b200_add_bias_row_sum_max_f32(hyle_b200_stream_t stream, const float *a,
+                                                  const float *bias, float *c, float *row_sum,
+                                                  float *row_max, uint64_t rows, uint64_t cols) {
+  if (rows == 0) return HYLE_B200_OK;
+  if ((a == nullptr || bias == nullptr) && cols != 0) return HYLE_B200_INVALID_VALUE;
+  RowF32Params p{};
+  p.a = a;
+  p.rhs = bias;
+  p.c = c;
+  p.row_sum = row_sum;
+  p.row_max = row_max;
+  p.rows = rows;
+  p.cols = cols;
+  return launch_row_f32<HYLE_B200_BINARY_ADD>(reinterpret_cast<cudaStream_t>(stream), p);
+}
+
+extern "C" int hyle_b200_rms_norm_bf16(hyle_b200_stream_t stream, const void *x, const void *weight,
+                                       int weight_dtype, void *y, uint64_t rows, uint64_t hidden,
+                                       float epsilon) {
+  return dispatch_rms<false>(reinterpret_cast<cudaStream_t>(stream), x, nullptr, weight, weight_dtype,
+                             y, nullptr, rows, hidden, epsilon);
+}
+
+extern "C" int hyle_b200_add_rms_norm_bf16(hyle_b200_stream_t stream, const void *x,
+                                           const void *residual, const void *weight,
+                                           int weight_dtype, void *y, void *h, uint64_t rows,
+                                           uint64_t hidden, float epsilon) {
+  return dispatch_rms<true>(reinterpret_cast<cudaStream_t>(stream), x, residual, weight, weight_dtype,
+                            y, h, rows, hidden, epsilon);
+}

@@ -1,0 +1,267 @@
+"""Operators of the B200 provider on torch CUDA tensors.
+
+torch is used here for device memory and the current stream only; every operator is one call
+through the C ABI (``include/hyle_b200.h``) into hand-written sm_100a kernels.  Names follow the
+reference's operator schema (include/hyle/compute/operation.h): Binary, Reduce, RmsNorm,
+GatedActivation, Softmax, TopK, Cast, CacheEncode.  There is no fallback: a missing library or a
+CPU tensor raises.
+"""
+from __future__ import annotations
+
+from typing import Optional, Tuple
+
+import torch
+
+from . import abi
+
+_DTYPE = {torch.float32: abi.F32, torch.bfloat16: abi.BF16, torch.float16: abi.F16}
+
+
+def _stream() -> int:
+    return torch.cuda.current_stream().cuda_stream
+
+
+def _device_tensor(t: torch.Tensor, name: str) -> torch.Tensor:
+    if not t.is_cuda:
+        raise ValueError(f"{name} must be a CUDA tensor (this provider has no CPU route)")
+    if not t.is_contiguous():
+        raise ValueError(f"{name} must be dense row-major")
+    return t
+
+
+def _ptr(t: Optional[torch.Tensor]) -> Optional[int]:
+    return None if t is None else t.data_ptr()
+
+
+def binary(kind: int, lhs: torch.Tensor, rhs: torch.Tensor, out: Optional[torch.Tensor] = None) -> torch.Tensor:
+    """Binary{kAdd|kMultiply}; ``rhs`` has lhs's shape or lhs's trailing axes (NumPy broadcast)."""
+    _device_tensor(lhs, "lhs"), _device_tensor(rhs, "rhs")
+    if lhs.dtype != rhs.dtype or lhs.dtype not in _DTYPE:
+        raise ValueError("lhs and rhs must share one of f32 / bf16 / f16")
+    if tuple(lhs.shape[lhs.dim() - rhs.dim():]) != tuple(rhs.shape):
+        raise ValueError("rhs must equal lhs's shape or its trailing axes")
+    if out is None:
+        out = torch.empty_like(lhs)
+    abi.check("hyle_b200_binary", abi.load().hyle_b200_binary(
+        _stream(), kind, _DTYPE[lhs.dtype], lhs.data_ptr(), rhs.data_ptr(), out.data_ptr(),
+        lhs.numel(), max(rhs.numel(), 1) if lhs.numel() else 1))
+    return out
+
+
+def add(lhs, rhs, out=None):
+    return binary(abi.BINARY_ADD, lhs, rhs, out)
+
+
+def multiply(lhs, rhs, out=None):
+    return binary(abi.BINARY_MULTIPLY, lhs, rhs, out)
+
+
+def reduce_rows(kind: int, x: torch.Tensor) -> torch.Tensor:
+    """Reduce{kind, axes={-1}} of an f32 tensor; output drops the last axis."""
+    _device_tensor(x, "x")
+    if x.dtype != torch.float32 or x.dim() < 1:
+        raise ValueError("reduce_rows takes an f32 tensor of rank >= 1")
+    cols = x.shape[-1]
+    rows = x.numel() // cols if cols else int(torch.Size(x.shape[:-1]).numel())
+    out = torch.empty(x.shape[:-1], dtype=torch.float32, device=x.device)
+    abi.check("hyle_b200_reduce_rows_f32", abi.load().hyle_b200_reduce_rows_f32(
+        _stream(), kind, x.data_ptr(), out.data_ptr(), rows, cols))
+    return out
+
+
+def add_bias_row_sum_max(a: torch.Tensor, bias: torch.Tensor) -> Tuple[torch.Tensor, torch.Tensor, torch.Tensor]:
+    """C = A + bias (broadcast over rows), per-row sum and per-row max of C, fused."""
+    _device_tensor(a, "a"), _device_tensor(bias, "bias")
+    if a.dtype != torch.float32 or bias.dtype != torch.float32 or a.dim() != 2 or bias.shape != a.shape[1:]:
+        raise ValueError("a must be f32 [rows, cols] and bias f32 [cols]")
+    rows, cols = a.shape
+    c = torch.empty_like(a)
+    row_sum = torch.empty(rows, dtype=torch.float32, device=a.device)
+    row_max = torch.empty(rows, dtype=torch.float32, device=a.device)
+    abi.check("hyle_b200_add_bias_row_sum_max_f32", abi.load().hyle_b200_add_bias_row_sum_max_f32(
+        _stream(), a.data_ptr(), bias.data_ptr(), c.data_ptr(), row_sum.data_ptr(), row_max.data_ptr(),
+        rows, cols))
+    return c, row_sum, row_max
+
+
+def _weight_args(weight: Optional[torch.Tensor], hidden: int):
+    if weight is None:
+        return None, abi.BF16
+    _device_tensor(weight, "weight")
+    if weight.numel() != hidden or weight.dtype not in (torch.bfloat16, torch.float32):
+        raise ValueError("weight must be bf16 or f32 with `hidden` elements")
+    return weight.data_ptr(), _DTYPE[weight.dtype]
+
+
+def rms_norm(x: torch.Tensor, weight: Optional[torch.Tensor], epsilon: float,
+             out: Optional[torch.Tensor] = None) -> torch.Tensor:
+    """RmsNorm{epsilon, accumulation=f32} over the last axis of a bf16 tensor."""
+    _device_tensor(x, "x")
+    if x.dtype != torch.bfloat16:
+        raise ValueError("rms_norm takes bf16 input")
+    hidden = x.shape[-1]
+    rows = x.numel() // hidden if hidden else 0
+    w_ptr, w_dtype = _weight_args(weight, hidden)
+    if out is None:
+        out = torch.empty_like(x)
+    abi.check("hyle_b200_rms_norm_bf16", abi.load().hyle_b200_rms_norm_bf16(
+        _stream(), x.data_ptr(), w_ptr, w_dtype, out.data_ptr(), rows, hidden, epsilon))
+    return out
+
+
+def add_rms_norm(x: torch.Tensor, residual: torch.Tensor, weight: Optional[torch.Tensor],
+                 epsilon: float) -> Tuple[torch.Tensor, torch.Tensor]:
+    """h = x + residual (bf16, one rounding); y = RmsNorm(h).  Returns (y, h)."""
+    _device_tensor(x, "x"), _device_tensor(residual, "residual")
+    if x.dtype != torch.bfloat16 or residual.dtype != torch.bfloat16 or x.shape != residual.shape:
+        raise ValueError("x and residual must be bf16 tensors of one shape")
+    hidden = x.shape[-1]
+    rows = x.numel() // hidden if hidden else 0
+    w_ptr, w_dtype = _weight_args(weight, hidden)
+    y, h = torch.empty_like(x), torch.empty_like(x)
+    abi.check("hyle_b200_add_rms_norm_bf16", abi.load().hyle_b200_add_rms_norm_bf16(
+        _stream(), x.data_ptr(), residual.data_ptr(), w_ptr, w_dtype, y.data_ptr(), h.data_ptr(),
+        rows, hidden, epsilon))
+    return y, h
+
+
+def swiglu(gate: torch.Tensor, up: torch.Tensor) -> torch.Tensor:
+    """GatedActivation{kSilu, kSeparate}: silu(gate) * up on bf16 tensors of one shape."""
+    _device_tensor(gate, "gate"), _device_tensor(up, "up")
+    if gate.dtype != torch.bfloat16 or up.dtype != torch.bfloat16 or gate.shape != up.shape:
+        raise ValueError("gate and up must be bf16 tensors of one shape")
+    cols = gate.shape[-1]
+    rows = gate.numel() // cols if cols else 0
+    out = torch.empty_like(gate)
+    abi.check("hyle_b200_swiglu_bf16", abi.load().hyle_b200_swiglu_bf16(
+        _stream(), gate.data_ptr(), up.data_ptr(), out.data_ptr(), rows, cols, cols, cols))
+    return out
+
+
+def swiglu_packed(packed: torch.Tensor) -> torch.Tensor:
+    """GatedActivation{kSilu, kPackedHalves}: the last axis holds [gate | up]."""
+    _device_tensor(packed, "packed")
+    if packed.dtype != torch.bfloat16 or packed.shape[-1] % 2:
+        raise ValueError("packed must be bf16 with an even last axis")
+    cols = packed.shape[-1] // 2
+    rows = packed.numel() // (2 * cols) if cols else 0
+    out = torch.empty(packed.shape[:-1] + (cols,), dtype=torch.bfloat16, device=packed.device)
+    abi.check("hyle_b200_swiglu_bf16", abi.load().hyle_b200_swiglu_bf16(
+        _stream(), packed.data_ptr(), packed.data_ptr() + 2 * cols, out.data_ptr(), rows, cols,
+        2 * cols, 2 * cols))
+    return out
+
+
+def logits_reduce(logits: torch.Tensor, want_probs: bool = True, want_lse: bool = True,
+                  want_argmax: bool = True):
+    """Fused log-sum-exp, softmax->bf16 and argmax of f32 [rows, cols] logits.
+
+    Returns (lse f32[rows], probs bf16[rows, cols], index i32[rows], value f32[rows]); entries not
+    asked for are None.
+    """
+    _device_tensor(logits, "logits")
+    if logits.dtype != torch.float32 or logits.dim() != 2:
+        raise ValueError("logits must be f32 [rows, cols]")
+    rows, cols = logits.shape
+    dev = logits.device
+    lse = torch.empty(rows, dtype=torch.float32, device=dev) if want_lse else None
+    probs = torch.empty(rows, cols, dtype=torch.bfloat16, device=dev) if want_probs else None
+    index = torch.empty(rows, dtype=torch.int32, device=dev) if want_argmax else None
+    value = torch.empty(rows, dtype=torch.float32, device=dev) if want_argmax else None
+    abi.check("hyle_b200_logits_reduce_f32", abi.load().hyle_b200_logits_reduce_f32(
+        _stream(), logits.data_ptr(), rows, cols, _ptr(lse), _ptr(probs), _ptr(index), _ptr(value)))
+    return lse, probs, index, value
+
+
+def argmax(logits: torch.Tensor) -> Tuple[torch.Tensor, torch.Tensor]:
+    """TopK{count=1}: (index i32[rows], value f32[rows]); lowest index on ties, NaN last."""
+    _, _, index, value = logits_reduce(logits, want_probs=False, want_lse=False)
+    return index, value
+
+
+def softmax(x: torch.Tensor, log: bool = False, out: Optional[torch.Tensor] = None) -> torch.Tensor:
+    """Softmax{axis=-1, kSoftmax|kLogSoftmax} on f32 rows, f32 output."""
+    _device_tensor(x, "x")
+    if x.dtype != torch.float32:
+        raise ValueError("softmax takes f32 input")
+    cols = x.shape[-1]
+    rows = x.numel() // cols if cols else 0
+    if out is None:
+        out = torch.empty_like(x)
+    abi.check("hyle_b200_softmax_f32", abi.load().hyle_b200_softmax_f32(
+        _stream(), abi.LOG_SOFTMAX if log else abi.SOFTMAX, x.data_ptr(), out.data_ptr(), rows, cols))
+    return out
+
+
+def cast_f32_to_bf16(x: torch.Tensor) -> torch.Tensor:
+    _device_tensor(x, "x")
+    if x.dtype != torch.float32:
+        raise ValueError("cast_f32_to_bf16 takes f32 input")
+    out = torch.empty(x.shape, dtype=torch.bfloat16, device=x.device)
+    abi.check("hyle_b200_cast_f32_to_bf16", abi.load().hyle_b200_cast_f32_to_bf16(
+        _stream(), x.data_ptr(), out.data_ptr(), x.numel()))
+    return out
+
+
+def q8_0_bytes(count: int) -> int:
+    """Size of the Q8_0 carrier for ``count`` values: 34 bytes per block of 32."""
+    if count % 32:
+        raise ValueError("Q8_0 needs a multiple of 32 values")
+    return count // 32 * 34
+
+
+def q8_0_encode(x: torch.Tensor, status: Optional[torch.Tensor] = None) -> torch.Tensor:
+    """CacheEncode{q8_0}: returns the U8 carrier [..., cols/32*34]."""
+    _device_tensor(x, "x")
+    if x.dtype not in _DTYPE or x.shape[-1] % 32:
+        raise ValueError("q8_0_encode takes f32/bf16/f16 with a last axis that is a multiple of 32")
+    out = torch.empty(x.shape[:-1] + (x.shape[-1] // 32 * 34,), dtype=torch.uint8, device=x.device)
+    abi.check("hyle_b200_q8_0_encode", abi.load().hyle_b200_q8_0_encode(
+        _stream(), _DTYPE[x.dtype], x.data_ptr(), x.numel(), out.data_ptr(), _ptr(status)))
+    return out
+
+
+def q8_0_decode(blocks: torch.Tensor, count: int) -> torch.Tensor:
+    _device_tensor(blocks, "blocks")
+    if blocks.dtype != torch.uint8 or blocks.numel() != q8_0_bytes(count):
+        raise ValueError("blocks must be the U8 carrier of `count` values")
+    out = torch.empty(count, dtype=torch.bfloat16, device=blocks.device)
+    abi.check("hyle_b200_q8_0_decode_bf16", abi.load().hyle_b200_q8_0_decode_bf16(
+        _stream(), blocks.data_ptr(), count, out.data_ptr()))
+    return out
+
+
+def make_workspace(device) -> torch.Tensor:
+    """Zero-filled scratch for sum_squares / q8_0_roundtrip; reusable across stream-ordered calls."""
+    return torch.zeros(abi.load().hyle_b200_sum_squares_workspace_bytes(), dtype=torch.uint8, device=device)
+
+
+def sum_squares(x: torch.Tensor, workspace: torch.Tensor, out: Optional[torch.Tensor] = None) -> torch.Tensor:
+    """Sum of squares of a bf16 tensor as a device f64 scalar."""
+    _device_tensor(x, "x")
+    if x.dtype != torch.bfloat16:
+        raise ValueError("sum_squares takes bf16 input")
+    if out is None:
+        out = torch.empty(1, dtype=torch.float64, device=x.device)
+    abi.check("hyle_b200_sum_squares_bf16", abi.load().hyle_b200_sum_squares_bf16(
+        _stream(), x.data_ptr(), x.numel(), out.data_ptr(), workspace.data_ptr(), workspace.numel()))
+    return out
+
+
+def q8_0_roundtrip(x: torch.Tensor, workspace: torch.Tensor, blocks: Optional[torch.Tensor] = None,
+                   decoded: Optional[torch.Tensor] = None, sum_out: Optional[torch.Tensor] = None,
+                   status: Optional[torch.Tensor] = None):
+    """One pass: Q8_0 blocks, decoded bf16 and sum of squares of a bf16 tensor."""
+    _device_tensor(x, "x")
+    if x.dtype != torch.bfloat16 or x.numel() % 32:
+        raise ValueError("q8_0_roundtrip takes bf16 input with a multiple of 32 values")
+    if blocks is None:
+        blocks = torch.empty(q8_0_bytes(x.numel()), dtype=torch.uint8, device=x.device)
+    if decoded is None:
+        decoded = torch.empty_like(x)
+    if sum_out is None:
+        sum_out = torch.empty(1, dtype=torch.float64, device=x.device)
+    abi.check("hyle_b200_q8_0_roundtrip_bf16", abi.load().hyle_b200_q8_0_roundtrip_bf16(
+        _stream(), x.data_ptr(), x.numel(), blocks.data_ptr(), decoded.data_ptr(), sum_out.data_ptr(),
+        _ptr(status), workspace.data_ptr(), workspace.numel()))
+    return blocks, decoded, sum_out

@@ -1,0 +1,229 @@
+/*
+ * hyle_b200 -- C ABI of the B200 (sm_100a) kernel library for HYLE's elementwise, broadcast and
+ * reduction operators.
+ *
+ * HYLE has no native FFI; its extension seam is the typed custom-kernel API
+ * (include/hyle/compute/custom_kernel.h:302-360) and the model for a kernel library behind it is
+ * the sample's `launch_affine(cudaStream_t, pointers, count, parameters) noexcept -> cudaError_t`
+ * (samples/package/graph/custom_kernel/cuda_kernel.h:16-19): "no HYLE runtime or provider SPI
+ * lives in this image".  Every entry point below has that shape:
+ *
+ *   - plain device pointers, element counts and scalars; no C++ or framework types;
+ *   - stream-ordered: work is recorded on `stream` and the call returns without synchronising;
+ *   - no allocation, no host synchronisation, no printing, safe under stream capture; scratch
+ *     memory is passed in by the caller and sized by the
+ *     matching *_workspace_bytes() query, the way a HYLE provider declares a caller-owned
+ *     WorkspaceRequirement (include/hyle/compute/custom_kernel.h:39-52);
+ *   - the return value is a cudaError_t-compatible int: 0 launched, 1 (cudaErrorInvalidValue)
+ *     for arguments outside the documented domain, 801 (cudaErrorNotSupported) for a shape this
+ *     library declines (the provider turns that into Status::Unimplemented so another provider
+ *     can take the request), anything else is the CUDA launch error;
+ *   - numeric problems found on the device are OR-ed into a caller-zeroed device status word,
+ *     the protocol of src/compute_backend_cuda/device_status_kernel.h:7-13.
+ *
+ * All tensors are dense row-major.  bf16/f16 values are passed as 16-bit storage words.
+ */
+#ifndef HYLE_B200_H_
+#define HYLE_B200_H_
+
+#include <stddef.h>
+#include <stdint.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+#if defined(HYLE_B200_BUILD)
+#define HYLE_B200_API __attribute__((visibility("default")))
+#else
+#define HYLE_B200_API
+#endif
+
+/* Same object as cudaStream_t; spelled out so C callers need no CUDA header. */
+typedef struct CUstream_st *hyle_b200_stream_t;
+
+#define HYLE_B200_ABI_VERSION 1
+
+enum hyle_b200_result {
+  HYLE_B200_OK = 0,
+  HYLE_B200_INVALID_VALUE = 1,   /* cudaErrorInvalidValue */
+  HYLE_B200_NOT_SUPPORTED = 801  /* cudaErrorNotSupported */
+};
+
+/* Storage types, numbered independently of hyle::compute::DataType. */
+enum hyle_b200_dtype {
+  HYLE_B200_F32 = 0,
+  HYLE_B200_BF16 = 1,
+  HYLE_B200_F16 = 2
+};
+
+/* hyle::compute::BinaryKind subset (include/hyle/compute/operation.h:75-82). */
+enum hyle_b200_binary_kind {
+  HYLE_B200_BINARY_ADD = 0,
+  HYLE_B200_BINARY_MULTIPLY = 1
+};
+
+/* hyle::compute::ReductionKind (include/hyle/compute/operation.h:84-89). */
+enum hyle_b200_reduce_kind {
+  HYLE_B200_REDUCE_SUM = 0,
+  HYLE_B200_REDUCE_MEAN = 1,
+  HYLE_B200_REDUCE_MINIMUM = 2,
+  HYLE_B200_REDUCE_MAXIMUM = 3
+};
+
+/* hyle::compute::SoftmaxKind (include/hyle/compute/operation.h:117-120). */
+enum hyle_b200_softmax_kind {
+  HYLE_B200_SOFTMAX = 0,
+  HYLE_B200_LOG_SOFTMAX = 1
+};
+
+/* Bits of the device status word. */
+enum hyle_b200_status_bits {
+  /* Q8_0 encode met a non-finite value or |x| > 65504*127; that block was written as 34 zero
+   * bytes (src/compute_provider_ggml/ggml_cpu_provider.cc:596-608). */
+  HYLE_B200_STATUS_INVALID_Q8_INPUT = 1u
+};
+
+HYLE_B200_API int hyle_b200_abi_version(void);
+/* Static string for a result code; never NULL. */
+HYLE_B200_API const char *hyle_b200_result_string(int result);
+
+/* ---------------------------------------------------------------------------------------------
+ * Binary{kAdd|kMultiply} with NumPy trailing-axis broadcast of the right operand.
+ * Replaces: Binary schema include/hyle/compute/operation.h:301-303, broadcast inference
+ * src/compute_ops/operation.cc:480-491, CPU route src/compute_provider_native/elementwise.cc:116-133
+ * (one dense call per broadcast chunk, :333-348,540-571).
+ * out[i] = lhs[i] (+|*) rhs[i % rhs_period] for i in [0,count).  rhs_period == count means no
+ * broadcast; rhs_period == last-axes extent is the bias-over-rows case; count % rhs_period == 0.
+ * f32: one IEEE operation per element (bit-exact).  bf16/f16: f32 operation, one RNE rounding.
+ * out may alias lhs exactly.
+ */
+HYLE_B200_API int hyle_b200_binary(hyle_b200_stream_t stream, int kind, int dtype,
+                                   const void *lhs, const void *rhs, void *out,
+                                   uint64_t count, uint64_t rhs_period);
+
+/* ---------------------------------------------------------------------------------------------
+ * Reduce{kind, axes={-1}} over dense f32 rows.
+ * Replaces: Reduce schema include/hyle/compute/operation.h:307-312, inference
+ * src/compute_ops/operation.cc:1345-1394, CPU route src/compute_provider_native/reduction.cc:34-110.
+ * Minimum/Maximum propagate NaN and order -0 < +0; empty rows give Sum=0, Mean=NaN,
+ * Minimum=+inf, Maximum=-inf.  Sum/Mean use a fixed summation order (deterministic).
+ */
+HYLE_B200_API int hyle_b200_reduce_rows_f32(hyle_b200_stream_t stream, int kind,
+                                            const float *in, float *out, uint64_t rows,
+                                            uint64_t cols);
+
+/* Fusion of Binary{kAdd}(A, bias[cols]) -> Reduce{kSum} and Reduce{kMaximum} over the last axis:
+ * one read of A, one write of C, both row reductions taken from registers.  Results equal the
+ * three separate calls above bit for bit (same summation order).  Any of c/row_sum/row_max may be
+ * NULL to skip that output.
+ */
+HYLE_B200_API int hyle_b200_add_bias_row_sum_max_f32(hyle_b200_stream_t stream, const float *a,
+                                                     const float *bias, float *c,
+                                                     float *row_sum, float *row_max,
+                                                     uint64_t rows, uint64_t cols);
+
+/* ---------------------------------------------------------------------------------------------
+ * RmsNorm{epsilon, accumulation=f32} on bf16 rows, weight bf16 or f32 (weight_dtype) or NULL.
+ * Replaces: RmsNorm schema include/hyle/compute/operation.h:323-328, CPU route
+ * src/compute_provider_native/normalization.cc:42-80 and the scalar floor
+ * src/simd/math/activations.cc:124-146:
+ *   inverse = 1.0f / sqrtf(sum(x*x)/hidden + epsilon);  y = bf16_rne((x * inverse) * w).
+ * y may alias x exactly.
+ */
+HYLE_B200_API int hyle_b200_rms_norm_bf16(hyle_b200_stream_t stream, const void *x,
+                                          const void *weight, int weight_dtype, void *y,
+                                          uint64_t rows, uint64_t hidden, float epsilon);
+
+/* Fusion of Binary{kAdd} (bf16: f32 add, one RNE) with the RmsNorm above:
+ *   h = bf16_rne(f32(x) + f32(residual));  y = RmsNorm(h)   -- the norm reads the ROUNDED h, so
+ * the pair equals the unfused composition bit for bit.  h may alias residual or x; y may alias x.
+ */
+HYLE_B200_API int hyle_b200_add_rms_norm_bf16(hyle_b200_stream_t stream, const void *x,
+                                              const void *residual, const void *weight,
+                                              int weight_dtype, void *y, void *h,
+                                              uint64_t rows, uint64_t hidden, float epsilon);
+
+/* ---------------------------------------------------------------------------------------------
+ * GatedActivation{kSilu}: out = bf16_rne(silu(f32 gate) * f32 up), silu(-inf) = 0.
+ * Replaces: GatedActivation schema include/hyle/compute/operation.h:91-100,362-365 and the scalar
+ * floor src/simd/math/activations.cc:21-25,44-47,114-122.
+ * Row strides are in elements: kSeparate passes gate/up with stride cols; kPackedHalves passes
+ * gate = packed, up = packed + cols, both strides 2*cols.
+ */
+HYLE_B200_API int hyle_b200_swiglu_bf16(hyle_b200_stream_t stream, const void *gate,
+                                        const void *up, void *out, uint64_t rows, uint64_t cols,
+                                        uint64_t gate_row_stride, uint64_t up_row_stride);
+
+/* ---------------------------------------------------------------------------------------------
+ * Logits reduction: per row of f32 logits, in one pass over HBM,
+ *   lse[row]          = max + float(log(double sum exp(x - max)))      (the LogSoftmax shift)
+ *   probs[row, :]     = bf16_rne(exp(x - max) * float(1 / sum))        (Softmax then Cast{bf16})
+ *   argmax_index[row] = lowest index of the maximum, NaN ordered last  (TopK{count=1})
+ *   argmax_value[row] = that element
+ * Replaces: Softmax include/hyle/compute/operation.h:403-409 with src/simd/math/activations.cc:301-334,
+ * Cast include/hyle/compute/operation.h:289-295, TopK include/hyle/compute/operation.h:411-417 with
+ * src/simd/sort/top_k.cc:17-27,51-69.
+ * Rows holding NaN or +inf, or only -inf, get NaN lse and NaN probs (include/hyle/simd/math.h:307-311);
+ * argmax is still defined for them.  Any output pointer may be NULL.  The kernel keeps each row in
+ * shared memory across a thread-block cluster; rows too wide for that return NOT_SUPPORTED.
+ */
+HYLE_B200_API int hyle_b200_logits_reduce_f32(hyle_b200_stream_t stream, const float *logits,
+                                              uint64_t rows, uint64_t cols, float *lse,
+                                              void *probs_bf16, int32_t *argmax_index,
+                                              float *argmax_value);
+
+/* Softmax{axis=-1, kind} with f32 output (output dtype = input dtype,
+ * src/compute_ops/operation.cc:1619). out may alias in. */
+HYLE_B200_API int hyle_b200_softmax_f32(hyle_b200_stream_t stream, int kind, const float *in,
+                                        float *out, uint64_t rows, uint64_t cols);
+
+/* Cast{f32 -> bf16}, round to nearest even (include/hyle/simd/dtype.h:114-121). */
+HYLE_B200_API int hyle_b200_cast_f32_to_bf16(hyle_b200_stream_t stream, const float *in,
+                                             void *out_bf16, uint64_t count);
+
+/* ---------------------------------------------------------------------------------------------
+ * Q8_0: blocks of 32 values -> 34 bytes {f16 scale (little endian), 32 x int8}
+ * (src/compute_ops/low_precision.cc:28-29).
+ *
+ * Encode replaces model_ops::CacheEncode{CacheStorage::q8_0()} (include/hyle/compute/model_ops.h:207-229),
+ * executor src/compute_provider_ggml/ggml_cpu_provider.cc:585-615:
+ *   d = amax/127.0f; id = 1.0f/d; q = roundf(x*id) (half away from zero); scale = f16_rne(d);
+ *   a block whose f16 scale is zero, or that holds an invalid value, is 34 zero bytes; invalid
+ *   values also set HYLE_B200_STATUS_INVALID_Q8_INPUT in *status_word (may be NULL).
+ * count must be a multiple of 32.  dtype is the input storage type.
+ */
+HYLE_B200_API int hyle_b200_q8_0_encode(hyle_b200_stream_t stream, int dtype, const void *in,
+                                        uint64_t count, void *blocks_out,
+                                        uint32_t *status_word);
+
+/* Decode: out = bf16_rne(f32(f16 scale) * q).  The reference has no standalone operator; the
+ * layout and arithmetic are those of the kGgufQ8_0 blocked tensors its MatMul/Gather consume
+ * (src/compute_ops/low_precision.cc:269-297). */
+HYLE_B200_API int hyle_b200_q8_0_decode_bf16(hyle_b200_stream_t stream, const void *blocks,
+                                             uint64_t count, void *out_bf16);
+
+/* Scratch for the two kernels below: a few KB holding per-CTA partial sums and a ticket counter.
+ * The caller zero-fills it once after allocation; each launch leaves it zeroed again, so one
+ * workspace serves any number of stream-ordered launches (not concurrent ones). */
+HYLE_B200_API uint64_t hyle_b200_sum_squares_workspace_bytes(void);
+
+/* Reduce{kSum, Axes::all()} of Cast(bf16->f32)^2 (include/hyle/compute/operation.h:232-248):
+ * deterministic two-pass sum (fixed per-thread order, fixed-order merge of CTA partials in f64).
+ * *sum_out is a device double; its float value is the operator result. */
+HYLE_B200_API int hyle_b200_sum_squares_bf16(hyle_b200_stream_t stream, const void *in,
+                                             uint64_t count, double *sum_out, void *workspace,
+                                             uint64_t workspace_bytes);
+
+/* One pass over a bf16 tensor producing its Q8_0 blocks, the decoded bf16 tensor and the sum of
+ * squares of the input: the input is read once (5.0625 bytes of traffic per element). */
+HYLE_B200_API int hyle_b200_q8_0_roundtrip_bf16(hyle_b200_stream_t stream, const void *in,
+                                                uint64_t count, void *blocks_out,
+                                                void *decoded_bf16, double *sum_squares_out,
+                                                uint32_t *status_word, void *workspace,
+                                                uint64_t workspace_bytes);
+
+#ifdef __cplusplus
+}
+#endif
+#endif /* HYLE_B200_H_ */

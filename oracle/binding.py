@@ -1,0 +1,267 @@
+"""ctypes binding of the CPU checker libraries -- TEST INFRASTRUCTURE.
+
+``Oracle``   oracle/libhyle_oracle.so, the from-scratch restatement (hyle_oracle.c), numpy in/out.
+``RefFloor`` oracle/_ref/libhyle_ref_floor.so, the reference's own scalar floor compiled from the
+             reference tree (ref_floor_shim.cc); present only where it was built.
+Only tests, the smoke check and the benchmark's CPU-baseline leg import this module.
+"""
+from __future__ import annotations
+
+import ctypes
+import os
+import subprocess
+
+import numpy as np
+
+ORACLE_DIR = os.path.dirname(os.path.abspath(__file__))
+ORACLE_LIB = os.path.join(ORACLE_DIR, "libhyle_oracle.so")
+REF_LIB = os.path.join(ORACLE_DIR, "_ref", "libhyle_ref_floor.so")
+
+F32, BF16, F16 = 0, 1, 2
+ADD, MULTIPLY = 0, 1
+SUM, MEAN, MINIMUM, MAXIMUM = 0, 1, 2, 3
+
+_vp, _u64, _i, _f = ctypes.c_void_p, ctypes.c_uint64, ctypes.c_int, ctypes.c_float
+
+
+def build(reference: bool = True) -> None:
+    """Compile the checker (and the reference floor when the reference tree is mounted)."""
+    target = "all" if reference else "libhyle_oracle.so"
+    result = subprocess.run(["make", "-C", ORACLE_DIR, target], capture_output=True, text=True)
+    if result.returncode != 0:
+        raise RuntimeError("building the oracle failed:\n" + result.stdout + result.stderr)
+
+
+def _ptr(a):
+    return None if a is None else a.ctypes.data_as(_vp)
+
+
+def _c(a, dtype):
+    a = np.ascontiguousarray(a)
+    assert a.dtype == dtype, (a.dtype, dtype)
+    return a
+
+
+class Oracle:
+    def __init__(self):
+        if not os.path.exists(ORACLE_LIB):
+            build(reference=False)
+        self.lib = ctypes.CDLL(ORACLE_LIB)
+        L = self.lib
+        L.hyle_oracle_max_threads.restype = _i
+        L.hyle_oracle_bf16_to_f32.restype = _f
+        L.hyle_oracle_bf16_to_f32.argtypes = [ctypes.c_uint16]
+        L.hyle_oracle_f32_to_bf16.restype = ctypes.c_uint16
+        L.hyle_oracle_f32_to_bf16.argtypes = [_f]
+        L.hyle_oracle_f16_to_f32.restype = _f
+        L.hyle_oracle_f16_to_f32.argtypes = [ctypes.c_uint16]
+        L.hyle_oracle_f32_to_f16.restype = ctypes.c_uint16
+        L.hyle_oracle_f32_to_f16.argtypes = [_f]
+        L.hyle_oracle_binary.argtypes = [_i, _i, _vp, _vp, _vp, _u64, _u64]
+        L.hyle_oracle_reduce_rows_f32.argtypes = [_i, _vp, _vp, _u64, _u64]
+        L.hyle_oracle_row_sum_f64.argtypes = [_vp, _vp, _vp, _u64, _u64]
+        L.hyle_oracle_rms_norm_bf16.argtypes = [_vp, _vp, _i, _vp, _vp, _u64, _u64, _f]
+        L.hyle_oracle_add_rms_norm_bf16.argtypes = [_vp, _vp, _vp, _i, _vp, _vp, _vp, _u64, _u64, _f]
+        L.hyle_oracle_swiglu_bf16.argtypes = [_vp, _vp, _vp, _vp, _u64, _u64, _u64, _u64]
+        L.hyle_oracle_softmax_f32.argtypes = [_i, _vp, _vp, _u64, _u64]
+        L.hyle_oracle_argmax_f32.argtypes = [_vp, _vp, _vp, _u64, _u64]
+        L.hyle_oracle_logits_reduce_f32.argtypes = [_vp, _u64, _u64, _vp, _vp, _vp, _vp, _vp]
+        L.hyle_oracle_cast_f32_to_bf16.argtypes = [_vp, _vp, _u64]
+        L.hyle_oracle_q8_0_encode.restype = _i
+        L.hyle_oracle_q8_0_encode.argtypes = [_i, _vp, _u64, _vp]
+        L.hyle_oracle_q8_0_decode_bf16.argtypes = [_vp, _u64, _vp]
+        L.hyle_oracle_sum_squares_bf16.restype = ctypes.c_double
+        L.hyle_oracle_sum_squares_bf16.argtypes = [_vp, _u64]
+        L.hyle_oracle_q8_0_roundtrip_bf16.restype = _i
+        L.hyle_oracle_q8_0_roundtrip_bf16.argtypes = [_vp, _u64, _vp, _vp, _vp]
+
+    # bf16 / f16 arrays are numpy uint16 storage words throughout.
+    def set_threads(self, n: int) -> None:
+        self.lib.hyle_oracle_set_threads(int(n))
+
+    def max_threads(self) -> int:
+        return self.lib.hyle_oracle_max_threads()
+
+    def f32_to_bf16(self, x):
+        x = _c(x, np.float32)
+        out = np.empty(x.shape, np.uint16)
+        self.lib.hyle_oracle_cast_f32_to_bf16(_ptr(x), _ptr(out), x.size)
+        return out
+
+    def bf16_to_f32(self, x):
+        return (_c(x, np.uint16).astype(np.uint32) << 16).view(np.float32)
+
+    def f32_to_f16_scalar(self, v: float) -> int:
+        return self.lib.hyle_oracle_f32_to_f16(float(v))
+
+    def f16_to_f32_scalar(self, h: int) -> float:
+        return self.lib.hyle_oracle_f16_to_f32(int(h))
+
+    def f32_to_bf16_scalar(self, v: float) -> int:
+        return self.lib.hyle_oracle_f32_to_bf16(float(v))
+
+    def binary(self, kind, dtype, lhs, rhs):
+        np_dtype = np.float32 if dtype == F32 else np.uint16
+        lhs, rhs = _c(lhs, np_dtype), _c(rhs, np_dtype)
+        out = np.empty_like(lhs)
+        self.lib.hyle_oracle_binary(kind, dtype, _ptr(lhs), _ptr(rhs), _ptr(out), lhs.size, max(rhs.size, 1))
+        return out
+
+    def reduce_rows(self, kind, x):
+        x = _c(x, np.float32)
+        rows, cols = x.shape
+        out = np.empty(rows, np.float32)
+        self.lib.hyle_oracle_reduce_rows_f32(kind, _ptr(x), _ptr(out), rows, cols)
+        return out
+
+    def row_sum_f64(self, x):
+        x = _c(x, np.float32)
+        rows, cols = x.shape
+        s, a = np.empty(rows, np.float64), np.empty(rows, np.float64)
+        self.lib.hyle_oracle_row_sum_f64(_ptr(x), _ptr(s), _ptr(a), rows, cols)
+        return s, a
+
+    @staticmethod
+    def _weight(weight):
+        if weight is None:
+            return None, BF16
+        if weight.dtype == np.float32:
+            return np.ascontiguousarray(weight), F32
+        return _c(weight, np.uint16), BF16
+
+    def rms_norm(self, x, weight, eps):
+        x = _c(x, np.uint16)
+        rows, hidden = x.shape
+        w, wdt = self._weight(weight)
+        y, y32 = np.empty_like(x), np.empty(x.shape, np.float32)
+        self.lib.hyle_oracle_rms_norm_bf16(_ptr(x), _ptr(w), wdt, _ptr(y), _ptr(y32), rows, hidden, eps)
+        return y, y32
+
+    def add_rms_norm(self, x, residual, weight, eps):
+        x, residual = _c(x, np.uint16), _c(residual, np.uint16)
+        rows, hidden = x.shape
+        w, wdt = self._weight(weight)
+        y, y32, h = np.empty_like(x), np.empty(x.shape, np.float32), np.empty_like(x)
+        self.lib.hyle_oracle_add_rms_norm_bf16(_ptr(x), _ptr(residual), _ptr(w), wdt, _ptr(y), _ptr(y32),
+                                               _ptr(h), rows, hidden, eps)
+        return y, y32, h
+
+    def swiglu(self, gate, up, cols=None, gate_stride=None, up_stride=None):
+        gate, up = _c(gate, np.uint16), _c(up, np.uint16)
+        rows = gate.shape[0]
+        cols = gate.shape[1] if cols is None else cols
+        gate_stride = cols if gate_stride is None else gate_stride
+        up_stride = cols if up_stride is None else up_stride
+        out, out32 = np.empty((rows, cols), np.uint16), np.empty((rows, cols), np.float32)
+        self.lib.hyle_oracle_swiglu_bf16(_ptr(gate), _ptr(up), _ptr(out), _ptr(out32), rows, cols,
+                                         gate_stride, up_stride)
+        return out, out32
+
+    def softmax(self, x, log=False):
+        x = _c(x, np.float32)
+        rows, cols = x.shape
+        out = np.empty_like(x)
+        self.lib.hyle_oracle_softmax_f32(1 if log else 0, _ptr(x), _ptr(out), rows, cols)
+        return out
+
+    def argmax(self, x):
+        x = _c(x, np.float32)
+        rows, cols = x.shape
+        index, value = np.empty(rows, np.int32), np.empty(rows, np.float32)
+        self.lib.hyle_oracle_argmax_f32(_ptr(x), _ptr(index), _ptr(value), rows, cols)
+        return index, value
+
+    def logits_reduce(self, x, want_probs=True):
+        x = _c(x, np.float32)
+        rows, cols = x.shape
+        lse = np.empty(rows, np.float32)
+        index, value = np.empty(rows, np.int32), np.empty(rows, np.float32)
+        probs = np.empty(x.shape, np.uint16) if want_probs else None
+        probs32 = np.empty(x.shape, np.float32) if want_probs else None
+        self.lib.hyle_oracle_logits_reduce_f32(_ptr(x), rows, cols, _ptr(lse), _ptr(probs), _ptr(probs32),
+                                               _ptr(index), _ptr(value))
+        return lse, probs, probs32, index, value
+
+    def q8_0_encode(self, dtype, x):
+        np_dtype = np.float32 if dtype == F32 else np.uint16
+        x = _c(x, np_dtype)
+        out = np.empty(x.size // 32 * 34, np.uint8)
+        invalid = self.lib.hyle_oracle_q8_0_encode(dtype, _ptr(x), x.size, _ptr(out))
+        return out, bool(invalid)
+
+    def q8_0_decode(self, blocks, count):
+        blocks = _c(blocks, np.uint8)
+        out = np.empty(count, np.uint16)
+        self.lib.hyle_oracle_q8_0_decode_bf16(_ptr(blocks), count, _ptr(out))
+        return out
+
+    def sum_squares(self, x):
+        x = _c(x, np.uint16)
+        return self.lib.hyle_oracle_sum_squares_bf16(_ptr(x), x.size)
+
+    def q8_0_roundtrip(self, x, blocks=None, decoded=None):
+        x = _c(x, np.uint16)
+        if blocks is None:
+            blocks = np.empty(x.size // 32 * 34, np.uint8)
+        if decoded is None:
+            decoded = np.empty(x.size, np.uint16)
+        total = ctypes.c_double()
+        invalid = self.lib.hyle_oracle_q8_0_roundtrip_bf16(_ptr(x), x.size, _ptr(blocks), _ptr(decoded),
+                                                           ctypes.byref(total))
+        return blocks, decoded, total.value, bool(invalid)
+
+
+class RefFloor:
+    """The reference's own scalar floor (when oracle/_ref was built from the reference tree)."""
+
+    @staticmethod
+    def available() -> bool:
+        return os.path.exists(REF_LIB)
+
+    def __init__(self):
+        self.lib = ctypes.CDLL(REF_LIB)
+        L = self.lib
+        L.hyle_ref_f32_to_bf16.restype = ctypes.c_uint16
+        L.hyle_ref_f32_to_bf16.argtypes = [_f]
+        L.hyle_ref_bf16_to_f32.restype = _f
+        L.hyle_ref_bf16_to_f32.argtypes = [ctypes.c_uint16]
+        L.hyle_ref_f32_to_f16.restype = ctypes.c_uint16
+        L.hyle_ref_f32_to_f16.argtypes = [_f]
+        L.hyle_ref_f16_to_f32.restype = _f
+        L.hyle_ref_f16_to_f32.argtypes = [ctypes.c_uint16]
+        L.hyle_ref_swiglu_bf16.argtypes = [_vp, _vp, _vp, _u64, _u64, _u64, _u64]
+        L.hyle_ref_rms_norm_bf16.argtypes = [_vp, _vp, _vp, _u64, _u64, _f]
+        L.hyle_ref_softmax_f32.argtypes = [_i, _vp, _vp, _u64, _u64]
+        L.hyle_ref_argmax_f32.argtypes = [_vp, _vp, _vp, _u64, _u64]
+
+    def set_threads(self, n: int) -> None:
+        self.lib.hyle_ref_set_threads(int(n))
+
+    def swiglu(self, gate, up):
+        gate, up = _c(gate, np.uint16), _c(up, np.uint16)
+        rows, cols = gate.shape
+        out = np.empty_like(gate)
+        self.lib.hyle_ref_swiglu_bf16(_ptr(gate), _ptr(up), _ptr(out), rows, cols, cols, cols)
+        return out
+
+    def rms_norm(self, x, weight, eps):
+        x = _c(x, np.uint16)
+        rows, hidden = x.shape
+        weight = None if weight is None else _c(weight, np.uint16)
+        y = np.empty_like(x)
+        self.lib.hyle_ref_rms_norm_bf16(_ptr(x), _ptr(weight), _ptr(y), rows, hidden, eps)
+        return y
+
+    def softmax(self, x, log=False):
+        x = _c(x, np.float32)
+        rows, cols = x.shape
+        out = np.empty_like(x)
+        self.lib.hyle_ref_softmax_f32(1 if log else 0, _ptr(x), _ptr(out), rows, cols)
+        return out
+
+    def argmax(self, x):
+        x = _c(x, np.float32)
+        rows, cols = x.shape
+        index, value = np.empty(rows, np.int32), np.empty(rows, np.float32)
+        self.lib.hyle_ref_argmax_f32(_ptr(x), _ptr(index), _ptr(value), rows, cols)
+        return index, value

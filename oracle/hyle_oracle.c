@@ -1,0 +1,412 @@
+/*
+ * CPU restatement of HYLE's elementwise / broadcast / reduction operators -- TEST INFRASTRUCTURE.
+ *
+ * This file is the checker for the CUDA kernels: only the tests, the smoke check and the CPU
+ * baseline leg of the benchmark may load it.  Nothing in the product path calls it.
+ *
+ * Every function restates, in plain scalar C, what the reference computes on its CPU route; the
+ * file:line beside each one is the reference source it follows (paths inside kiroeko/hyle).
+ * Third-party arithmetic that is not in the reference tree: Q8_0 row quantisation lives in ggml
+ * (module ggml_cpu, pinned at ggml-cpu-snapshot-ffa4e8b80930, called from
+ * src/compute_provider_ggml/ggml_cpu_provider.cc:598,613); its published reference algorithm
+ * (amax, d = amax/127, id = 1/d, roundf(x*id), f16 scale) is restated here and pinned by the
+ * independent formula in tests/compute_provider_ggml/native_paged_test.cc:255-326.
+ *
+ * Parity status: pinned.  tests/test_oracle.py checks these functions against the reference's
+ * own scalar floor compiled from the reference tree (oracle/_ref/libhyle_ref_floor.so, built by
+ * oracle/Makefile) and against known-answer vectors re-expressed from the reference's tests.
+ *
+ * Build: gcc -O2 -ffp-contract=off -fopenmp -shared -fPIC  (no -ffast-math: results are compared
+ * bit for bit).  Row loops are split over threads in contiguous ranges, the way the reference's
+ * parallel_for_ranges does (src/compute_provider_native/native_plan.h:94-111).
+ */
+#include <math.h>
+#include <stddef.h>
+#include <stdint.h>
+#include <string.h>
+
+#ifdef _OPENMP
+#include <omp.h>
+#endif
+
+#define ORACLE_API __attribute__((visibility("default")))
+
+enum { DT_F32 = 0, DT_BF16 = 1, DT_F16 = 2 };
+enum { BIN_ADD = 0, BIN_MUL = 1 };
+enum { RED_SUM = 0, RED_MEAN = 1, RED_MIN = 2, RED_MAX = 3 };
+enum { SM_SOFTMAX = 0, SM_LOG_SOFTMAX = 1 };
+
+ORACLE_API void hyle_oracle_set_threads(int threads) {
+#ifdef _OPENMP
+  if (threads > 0) omp_set_num_threads(threads);
+#else
+  (void)threads;
+#endif
+}
+
+ORACLE_API int hyle_oracle_max_threads(void) {
+#ifdef _OPENMP
+  return omp_get_max_threads();
+#else
+  return 1;
+#endif
+}
+
+/* ---- storage conversions: include/hyle/simd/dtype.h:55-121 ----------------------------------- */
+static inline float bits_to_f32(uint32_t b) { float f; memcpy(&f, &b, 4); return f; }
+static inline uint32_t f32_to_bits(float f) { uint32_t b; memcpy(&b, &f, 4); return b; }
+
+/* dtype.h:105-107 */
+ORACLE_API float hyle_oracle_bf16_to_f32(uint16_t b) { return bits_to_f32((uint32_t)b << 16); }
+
+/* dtype.h:114-121: RNE; inf/NaN are not incremented; NaN gets its quiet bit. */
+ORACLE_API uint16_t hyle_oracle_f32_to_bf16(float f) {
+  const uint32_t u = f32_to_bits(f);
+  const uint32_t a = u & 0x7fffffffu;
+  const uint32_t incr = a < 0x7f800000u ? 0x7fffu + ((u >> 16) & 1u) : 0u;
+  const uint32_t snan = a > 0x7f800000u ? (1u << 6) : 0u;
+  return (uint16_t)(snan | ((u + incr) >> 16));
+}
+
+/* dtype.h:55-68 */
+ORACLE_API float hyle_oracle_f16_to_f32(uint16_t h) {
+  const uint32_t sign = h >> 15, e = (h >> 10) & 0x1f, m = h & 0x3ff;
+  if (e == 0) {
+    const float sub = (1.0f / 16384) * ((float)m * (1.0f / 1024));
+    return sign ? -sub : sub;
+  }
+  const uint32_t e32 = e == 31 ? 0xff : e + (127 - 15);
+  return bits_to_f32((sign << 31) | (e32 << 23) | (m << 13));
+}
+
+/* dtype.h:73-101: RNE, overflow to inf, gradual underflow, NaN -> mantissa 0x3ff. */
+ORACLE_API uint16_t hyle_oracle_f32_to_f16(float f) {
+  const uint32_t b = f32_to_bits(f);
+  const uint32_t sign = b >> 31, e32 = (b >> 23) & 0xff, m32 = b & 0x7fffffu;
+  int idx = 126 - (int)e32;
+  idx = idx < 13 ? 13 : (idx > 24 ? 24 : idx);
+  const uint32_t odd = ((m32 | 0x800000u) >> idx) & 1u;
+  const uint32_t rounded = m32 + odd + (1u << (idx - 1)) - 1u;
+  const int carry = rounded >= (1u << 23);
+  const int e = (int)e32 - 127 + carry;
+  if (e < -24) return (uint16_t)(sign << 15);
+  const int is_nan = e32 == 255 && m32 != 0;
+  const int overflow = e >= 16;
+  int be = e + 15;
+  be = be < 0 ? 0 : (be > 31 ? 31 : be);
+  const int sub = (-14 - e) > 0 ? (-14 - e) : 0;
+  const uint32_t shifted = (rounded & 0x7fffffu) >> (13 + sub);
+  const uint32_t leading = sub == 0 ? 0u : (1024u >> sub);
+  const uint32_t m16 = is_nan ? 0x3ffu : (overflow ? 0u : leading + shifted);
+  return (uint16_t)((sign << 15) | ((uint32_t)be << 10) | m16);
+}
+
+static inline float load_as_f32(const void *p, size_t i, int dtype) {
+  if (dtype == DT_F32) return ((const float *)p)[i];
+  if (dtype == DT_BF16) return hyle_oracle_bf16_to_f32(((const uint16_t *)p)[i]);
+  return hyle_oracle_f16_to_f32(((const uint16_t *)p)[i]);
+}
+static inline void store_from_f32(void *p, size_t i, int dtype, float v) {
+  if (dtype == DT_F32) ((float *)p)[i] = v;
+  else if (dtype == DT_BF16) ((uint16_t *)p)[i] = hyle_oracle_f32_to_bf16(v);
+  else ((uint16_t *)p)[i] = hyle_oracle_f32_to_f16(v);
+}
+
+/* ---- Binary{kAdd|kMultiply}, trailing-axis broadcast ------------------------------------------
+ * src/compute_provider_native/elementwise.cc:116-133 (dense f32 route, one IEEE op per element),
+ * :135-147 (half types: f32 op on 128-element tiles, one rounding), :333-348,540-571 (one dense
+ * call per broadcast chunk = rhs repeats with period rhs_period). */
+ORACLE_API void hyle_oracle_binary(int kind, int dtype, const void *lhs, const void *rhs, void *out,
+                                   uint64_t count, uint64_t rhs_period) {
+  if (count == 0) return;
+  const uint64_t chunks = count / rhs_period;
+#pragma omp parallel for schedule(static)
+  for (uint64_t c = 0; c < chunks; ++c) {
+    for (uint64_t j = 0; j < rhs_period; ++j) {
+      const uint64_t i = c * rhs_period + j;
+      const float a = load_as_f32(lhs, i, dtype), b = load_as_f32(rhs, j, dtype);
+      store_from_f32(out, i, dtype, kind == BIN_ADD ? a + b : a * b);
+    }
+  }
+}
+
+/* ---- Reduce over the last axis ----------------------------------------------------------------
+ * Extrema: src/compute_provider_native/reduction.cc:22-47 (identities, NaN propagation, fmax/fmin
+ * otherwise) with the public zero rule of src/compute_provider_native/aten_cpu_provider.cc:484-496
+ * (a zero maximum is -0 only if every zero in the row is -0; a zero minimum is -0 if any is).
+ * Sum/Mean: docs/user/compute.md:384-388 (empty Sum = 0, Mean = NaN); summation order is a
+ * property of the executing route (src/simd/ops/kernel_impl.h:342-362 uses four accumulators), so
+ * the oracle gives the plain left-to-right f32 sum AND, through hyle_oracle_row_sum_f64, the f64
+ * sum with the sum of magnitudes that bounds any order's error. */
+ORACLE_API void hyle_oracle_reduce_rows_f32(int kind, const float *in, float *out, uint64_t rows,
+                                            uint64_t cols) {
+#pragma omp parallel for schedule(static)
+  for (uint64_t r = 0; r < rows; ++r) {
+    const float *x = in + r * cols;
+    if (kind == RED_SUM || kind == RED_MEAN) {
+      float s = 0.0f;
+      for (uint64_t i = 0; i < cols; ++i) s += x[i];
+      out[r] = kind == RED_SUM ? s : (cols == 0 ? NAN : s / (float)cols);
+    } else {
+      const int is_max = kind == RED_MAX;
+      float acc = is_max ? -INFINITY : INFINITY;
+      int any_nan = 0, zero_pos = 0, zero_neg = 0;
+      for (uint64_t i = 0; i < cols; ++i) {
+        const float v = x[i];
+        if (isnan(v)) { any_nan = 1; continue; }
+        if (v == 0.0f) { if (signbit(v)) zero_neg = 1; else zero_pos = 1; }
+        acc = is_max ? fmaxf(acc, v) : fminf(acc, v);
+      }
+      if (any_nan) acc = NAN;
+      else if (acc == 0.0f) acc = is_max ? (zero_pos ? 0.0f : -0.0f) : (zero_neg ? -0.0f : 0.0f);
+      out[r] = acc;
+    }
+  }
+}
+
+ORACLE_API void hyle_oracle_row_sum_f64(const float *in, double *sum, double *abs_sum, uint64_t rows,
+                                        uint64_t cols) {
+#pragma omp parallel for schedule(static)
+  for (uint64_t r = 0; r < rows; ++r) {
+    double s = 0.0, a = 0.0;
+    for (uint64_t i = 0; i < cols; ++i) { s += (double)in[r * cols + i]; a += fabs((double)in[r * cols + i]); }
+    sum[r] = s;
+    if (abs_sum) abs_sum[r] = a;
+  }
+}
+
+/* ---- RmsNorm (bf16 rows, f32 accumulation) ----------------------------------------------------
+ * src/simd/math/activations.cc:124-146: fma accumulation left to right,
+ * inverse = 1.0f / sqrtf(sum/n + eps), y = round((x * inverse) * w).
+ * weight_dtype DT_BF16 or DT_F32, weight may be NULL.  y_f32 (optional) receives the value before
+ * the final rounding, for tolerance checks. */
+static void rms_row(const uint16_t *x, const void *w, int wdt, uint16_t *y, float *y_f32, uint64_t n,
+                    float eps) {
+  if (n == 0) return;
+  float ss = 0.0f;
+  for (uint64_t i = 0; i < n; ++i) {
+    const float v = hyle_oracle_bf16_to_f32(x[i]);
+    ss = fmaf(v, v, ss);
+  }
+  const float inverse = 1.0f / sqrtf(ss / (float)n + eps);
+  for (uint64_t i = 0; i < n; ++i) {
+    float v = hyle_oracle_bf16_to_f32(x[i]) * inverse;
+    if (w != NULL) v = v * load_as_f32(w, i, wdt);
+    if (y_f32) y_f32[i] = v;
+    y[i] = hyle_oracle_f32_to_bf16(v);
+  }
+}
+
+ORACLE_API void hyle_oracle_rms_norm_bf16(const uint16_t *x, const void *weight, int weight_dtype,
+                                          uint16_t *y, float *y_f32, uint64_t rows, uint64_t hidden,
+                                          float eps) {
+#pragma omp parallel for schedule(static)
+  for (uint64_t r = 0; r < rows; ++r)
+    rms_row(x + r * hidden, weight, weight_dtype, y + r * hidden, y_f32 ? y_f32 + r * hidden : NULL,
+            hidden, eps);
+}
+
+/* Binary{kAdd} in bf16 (f32 add, one RNE; docs/user/compute.md:358-359) followed by the RmsNorm
+ * above reading the rounded sum: the unfused composition the fused kernel must equal. */
+ORACLE_API void hyle_oracle_add_rms_norm_bf16(const uint16_t *x, const uint16_t *residual,
+                                              const void *weight, int weight_dtype, uint16_t *y,
+                                              float *y_f32, uint16_t *h, uint64_t rows,
+                                              uint64_t hidden, float eps) {
+#pragma omp parallel for schedule(static)
+  for (uint64_t r = 0; r < rows; ++r) {
+    uint16_t *hr = h + r * hidden;
+    for (uint64_t i = 0; i < hidden; ++i)
+      hr[i] = hyle_oracle_f32_to_bf16(hyle_oracle_bf16_to_f32(x[r * hidden + i]) +
+                                      hyle_oracle_bf16_to_f32(residual[r * hidden + i]));
+    rms_row(hr, weight, weight_dtype, y + r * hidden, y_f32 ? y_f32 + r * hidden : NULL, hidden, eps);
+  }
+}
+
+/* ---- GatedActivation{kSilu} -------------------------------------------------------------------
+ * src/simd/math/activations.cc:21-25 (sigmoid without overflow), :44-47 (silu(-inf) = 0),
+ * :114-122 (out = round(silu(gate) * up)). */
+static inline float sigmoid_f32(float x) {
+  if (isnan(x)) return x;
+  const float e = expf(-fabsf(x));
+  return x < 0.0f ? e / (1.0f + e) : 1.0f / (1.0f + e);
+}
+static inline float silu_f32(float x) { return x == -INFINITY ? 0.0f : x * sigmoid_f32(x); }
+
+ORACLE_API void hyle_oracle_swiglu_bf16(const uint16_t *gate, const uint16_t *up, uint16_t *out,
+                                        float *out_f32, uint64_t rows, uint64_t cols,
+                                        uint64_t gate_stride, uint64_t up_stride) {
+#pragma omp parallel for schedule(static)
+  for (uint64_t r = 0; r < rows; ++r) {
+    for (uint64_t c = 0; c < cols; ++c) {
+      const float g = hyle_oracle_bf16_to_f32(gate[r * gate_stride + c]);
+      const float u = hyle_oracle_bf16_to_f32(up[r * up_stride + c]);
+      const float v = silu_f32(g) * u;
+      if (out_f32) out_f32[r * cols + c] = v;
+      out[r * cols + c] = hyle_oracle_f32_to_bf16(v);
+    }
+  }
+}
+
+/* ---- Softmax / LogSoftmax / log-sum-exp -------------------------------------------------------
+ * src/simd/math/activations.cc:274-334: finite_row_max rejects NaN and +inf and rows without a
+ * finite maximum (all outputs NaN); exp in f32, sum in f64, multiply by float(1/sum);
+ * log-softmax shift = max + float(log(sum)). */
+static int finite_row_max(const float *x, uint64_t n, float *maximum) {
+  float m = -INFINITY;
+  for (uint64_t i = 0; i < n; ++i) {
+    if (isnan(x[i]) || x[i] == INFINITY) return 0;
+    if (x[i] > m) m = x[i];
+  }
+  *maximum = m;
+  return isfinite(m);
+}
+
+ORACLE_API void hyle_oracle_softmax_f32(int kind, const float *in, float *out, uint64_t rows,
+                                        uint64_t cols) {
+  if (cols == 0) return;
+#pragma omp parallel for schedule(static)
+  for (uint64_t r = 0; r < rows; ++r) {
+    const float *x = in + r * cols;
+    float *y = out + r * cols;
+    float m;
+    if (!finite_row_max(x, cols, &m)) { for (uint64_t i = 0; i < cols; ++i) y[i] = NAN; continue; }
+    double sum = 0.0;
+    if (kind == SM_SOFTMAX) {
+      for (uint64_t i = 0; i < cols; ++i) { const float e = expf(x[i] - m); y[i] = e; sum += (double)e; }
+      const float inverse = (float)(1.0 / sum);
+      for (uint64_t i = 0; i < cols; ++i) y[i] *= inverse;
+    } else {
+      for (uint64_t i = 0; i < cols; ++i) sum += (double)expf(x[i] - m);
+      const float shift = m + (float)log(sum);
+      for (uint64_t i = 0; i < cols; ++i) y[i] = x[i] - shift;
+    }
+  }
+}
+
+/* TopK{count=1}: src/simd/sort/top_k.cc:13-27 (NaN last, larger value first, lower index on
+ * ties) and :51-69 (k == 1 scan starting from element 0). */
+static inline int better(float a, uint32_t ai, float b, uint32_t bi) {
+  const int an = isnan(a), bn = isnan(b);
+  if (an != bn) return !an;
+  if (!an) { if (a > b) return 1; if (a < b) return 0; }
+  return ai < bi;
+}
+
+ORACLE_API void hyle_oracle_argmax_f32(const float *in, int32_t *index, float *value, uint64_t rows,
+                                       uint64_t cols) {
+  if (cols == 0) return;
+#pragma omp parallel for schedule(static)
+  for (uint64_t r = 0; r < rows; ++r) {
+    const float *x = in + r * cols;
+    float best = x[0];
+    uint32_t bi = 0;
+    for (uint64_t i = 1; i < cols; ++i)
+      if (better(x[i], (uint32_t)i, best, bi)) { best = x[i]; bi = (uint32_t)i; }
+    if (index) index[r] = (int32_t)bi;
+    if (value) value[r] = best;
+  }
+}
+
+/* The fused logits reduction = LogSoftmax shift (lse) + Softmax -> Cast{bf16} + TopK{1}.
+ * probs_f32 (optional) receives the softmax before the bf16 rounding. */
+ORACLE_API void hyle_oracle_logits_reduce_f32(const float *in, uint64_t rows, uint64_t cols,
+                                              float *lse, uint16_t *probs_bf16, float *probs_f32,
+                                              int32_t *index, float *value) {
+  if (cols == 0) return;
+  if (index || value) hyle_oracle_argmax_f32(in, index, value, rows, cols);
+#pragma omp parallel for schedule(static)
+  for (uint64_t r = 0; r < rows; ++r) {
+    const float *x = in + r * cols;
+    float m;
+    if (!finite_row_max(x, cols, &m)) {
+      if (lse) lse[r] = NAN;
+      for (uint64_t i = 0; i < cols; ++i) {
+        if (probs_bf16) probs_bf16[r * cols + i] = hyle_oracle_f32_to_bf16(NAN);
+        if (probs_f32) probs_f32[r * cols + i] = NAN;
+      }
+      continue;
+    }
+    double sum = 0.0;
+    for (uint64_t i = 0; i < cols; ++i) sum += (double)expf(x[i] - m);
+    if (lse) lse[r] = m + (float)log(sum);
+    const float inverse = (float)(1.0 / sum);
+    if (probs_bf16 || probs_f32) {
+      for (uint64_t i = 0; i < cols; ++i) {
+        const float p = expf(x[i] - m) * inverse;
+        if (probs_f32) probs_f32[r * cols + i] = p;
+        if (probs_bf16) probs_bf16[r * cols + i] = hyle_oracle_f32_to_bf16(p);
+      }
+    }
+  }
+}
+
+/* Cast{f32 -> bf16}: include/hyle/simd/dtype.h:114-121. */
+ORACLE_API void hyle_oracle_cast_f32_to_bf16(const float *in, uint16_t *out, uint64_t count) {
+#pragma omp parallel for schedule(static)
+  for (uint64_t i = 0; i < count; ++i) out[i] = hyle_oracle_f32_to_bf16(in[i]);
+}
+
+/* ---- Q8_0 -------------------------------------------------------------------------------------
+ * Encode: src/compute_provider_ggml/ggml_cpu_provider.cc:585-615 around ggml's reference row
+ * quantiser; block layout src/compute_ops/low_precision.cc:28-29 (f16 scale little endian at
+ * bytes 0-1, then 32 int8).  Returns 1 when any block was invalid (the reference then completes
+ * with InvalidArgument, :1720-1721). */
+ORACLE_API int hyle_oracle_q8_0_encode(int dtype, const void *in, uint64_t count, uint8_t *out) {
+  const uint64_t blocks = count / 32;
+  int invalid = 0;
+#pragma omp parallel for schedule(static) reduction(| : invalid)
+  for (uint64_t b = 0; b < blocks; ++b) {
+    float v[32];
+    int valid = 1;
+    float amax = 0.0f;
+    for (int j = 0; j < 32; ++j) {
+      v[j] = load_as_f32(in, b * 32 + j, dtype);
+      valid &= isfinite(v[j]) && fabsf(v[j]) <= 65504.0f * 127.0f;
+      amax = fmaxf(amax, fabsf(v[j]));
+    }
+    uint8_t *dst = out + b * 34;
+    if (!valid) { invalid |= 1; memset(dst, 0, 34); continue; }
+    const float d = amax / 127.0f;
+    const uint16_t scale = hyle_oracle_f32_to_f16(d);
+    if (scale == 0) { memset(dst, 0, 34); continue; }
+    const float id = 1.0f / d;
+    dst[0] = (uint8_t)(scale & 0xff);
+    dst[1] = (uint8_t)(scale >> 8);
+    for (int j = 0; j < 32; ++j) dst[2 + j] = (uint8_t)(int8_t)roundf(v[j] * id);
+  }
+  return invalid;
+}
+
+/* Decode: value = f32(f16 scale) * code (exact in f32), one RNE to bf16.  The arithmetic the
+ * reference's kGgufQ8_0 consumers apply (src/compute_ops/low_precision.cc:269-297). */
+ORACLE_API void hyle_oracle_q8_0_decode_bf16(const uint8_t *blocks_in, uint64_t count, uint16_t *out) {
+  const uint64_t blocks = count / 32;
+#pragma omp parallel for schedule(static)
+  for (uint64_t b = 0; b < blocks; ++b) {
+    const uint8_t *src = blocks_in + b * 34;
+    const float d = hyle_oracle_f16_to_f32((uint16_t)(src[0] | (src[1] << 8)));
+    for (int j = 0; j < 32; ++j) out[b * 32 + j] = hyle_oracle_f32_to_bf16(d * (float)(int8_t)src[2 + j]);
+  }
+}
+
+/* Reduce{kSum, Axes::all()} of Cast(bf16->f32)^2 (include/hyle/compute/operation.h:232-248), with
+ * f64 accumulation: the value any f32 route must approach. */
+ORACLE_API double hyle_oracle_sum_squares_bf16(const uint16_t *in, uint64_t count) {
+  double total = 0.0;
+#pragma omp parallel for schedule(static) reduction(+ : total)
+  for (uint64_t i = 0; i < count; ++i) {
+    const double v = (double)hyle_oracle_bf16_to_f32(in[i]);
+    total += v * v;
+  }
+  return total;
+}
+
+/* The fused sweep step of the Q8_0 workload: encode, decode and sum of squares in one row-parallel
+ * pass (what a CPU provider would run per row range). */
+ORACLE_API int hyle_oracle_q8_0_roundtrip_bf16(const uint16_t *in, uint64_t count, uint8_t *blocks_out,
+                                               uint16_t *decoded, double *sum_squares) {
+  const int invalid = hyle_oracle_q8_0_encode(DT_BF16, in, count, blocks_out);
+  hyle_oracle_q8_0_decode_bf16(blocks_out, count, decoded);
+  *sum_squares = hyle_oracle_sum_squares_bf16(in, count);
+  return invalid;
+}

@@ -1,0 +1,85 @@
+"""Generate tests/golden/ref_floor.npz by RUNNING the reference's own scalar floor.
+
+Needs oracle/_ref/libhyle_ref_floor.so, i.e. the reference tree mounted at /root/reference when
+`make -C oracle` ran.  The fixture travels with the repository, so the oracle stays pinned to the
+reference's outputs where the reference tree is absent.  Inputs are seeded; special values follow
+the edge cases of the reference's tests (tests/simd/math_test.cc:1317-1331 invalid softmax rows,
+tests/compute_provider_native/matmul_gated_test.cc:360-372 gate specials,
+tests/simd/search_test.cc:157-194,269-279 argmax ties and NaN).
+
+Run from the repository root:  python tests/golden/make_golden.py
+"""
+import os
+import sys
+
+import numpy as np
+
+ROOT = os.path.dirname(os.path.dirname(os.path.dirname(os.path.abspath(__file__))))
+sys.path.insert(0, ROOT)
+
+from hyle_b200.workloads import f32_to_bf16  # noqa: E402
+from oracle.binding import RefFloor  # noqa: E402
+
+
+def main():
+    ref = RefFloor()
+    ref.set_threads(1)
+    rng = np.random.default_rng(20261125)
+    out = {}
+
+    # SwiGLU: random values plus specials in the gate and in the up operand.
+    specials = np.array([0.0, -0.0, np.inf, -np.inf, np.nan, 80.0, -80.0, 1e-30, -1e-30, 88.7, -88.7,
+                         1.0, -1.0, 0.5, -0.5, 20.0, -20.0], dtype=np.float32)
+    gate = (1.5 * rng.standard_normal((3, 257))).astype(np.float32)
+    up = (1.5 * rng.standard_normal((3, 257))).astype(np.float32)
+    gate[0, : specials.size] = specials
+    up[1, : specials.size] = specials
+    gate[2, : specials.size] = specials
+    up[2, : specials.size] = specials[::-1]
+    out["swiglu_gate"], out["swiglu_up"] = f32_to_bf16(gate), f32_to_bf16(up)
+    out["swiglu_out"] = ref.swiglu(out["swiglu_gate"], out["swiglu_up"])
+
+    # RMSNorm: the hidden sizes the reference's tests use (tests/compute_provider_native/
+    # normalization_test.cc:168-323), bf16 weight, eps 1e-6.
+    for hidden in (1, 127, 128, 129, 257, 2048, 4096):
+        x = f32_to_bf16(rng.standard_normal((2, hidden)).astype(np.float32))
+        w = f32_to_bf16(rng.uniform(0.5, 1.5, hidden).astype(np.float32))
+        out[f"rms_x_{hidden}"], out[f"rms_w_{hidden}"] = x, w
+        out[f"rms_y_{hidden}"] = ref.rms_norm(x, w, 1e-6)
+        out[f"rms_y_noweight_{hidden}"] = ref.rms_norm(x, None, 1e-6)
+
+    # Softmax / log-softmax: ordinary rows, wide-range rows, and the invalid rows (NaN, +inf, all -inf).
+    for cols in (1, 7, 1000):
+        x = (4.0 * rng.standard_normal((6, cols))).astype(np.float32)
+        x[1] *= 20.0
+        if cols >= 7:
+            x[2, 3] = np.nan
+            x[3, 5] = np.inf
+            x[4, :] = -np.inf
+            x[5, 0] = -np.inf
+        out[f"softmax_x_{cols}"] = x
+        out[f"softmax_y_{cols}"] = ref.softmax(x)
+        out[f"log_softmax_y_{cols}"] = ref.softmax(x, log=True)
+
+    # Argmax: ties (first wins), -0/+0, NaN first / last / everywhere, all -inf.
+    rows = np.zeros((10, 300), dtype=np.float32)
+    rows[0] = rng.standard_normal(300)
+    rows[1] = rows[0]; rows[1, 17] = rows[1, 200] = rows[1].max() + 1
+    rows[2] = -0.0; rows[2, 5] = 0.0
+    rows[3] = np.nan
+    rows[4] = np.nan; rows[4, 250] = -np.inf; rows[4, 260] = -np.inf
+    rows[5] = rng.standard_normal(300); rows[5, 0] = np.nan
+    rows[6] = rng.standard_normal(300); rows[6, 299] = np.nan; rows[6, 100] = np.inf; rows[6, 150] = np.inf
+    rows[7] = -np.inf
+    rows[8] = 3.0
+    rows[9] = rng.standard_normal(300); rows[9, 299] = 100.0
+    index, value = ref.argmax(rows)
+    out["argmax_x"], out["argmax_index"], out["argmax_value"] = rows, index, value
+
+    path = os.path.join(ROOT, "tests", "golden", "ref_floor.npz")
+    np.savez_compressed(path, **out)
+    print("wrote", path, os.path.getsize(path), "bytes")
+
+
+if __name__ == "__main__":
+    main()

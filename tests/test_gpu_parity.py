@@ -1,0 +1,430 @@
+"""Parity of the sm_100a kernels with the CPU checker, through the C ABI, on the same seeded inputs.
+
+Bars (from the workload definition): Q8_0 bytes and argmax indices bit-exact; f32 elementwise
+bit-exact; f32 reductions within 1e-5 (row sums relative to the sum of magnitudes); bf16
+elementwise within 1 bf16 ulp; bf16 RMSNorm and softmax within 2e-3 relative of the checker's
+unrounded value (and never more than 1 bf16 ulp from its rounded one).
+"""
+import numpy as np
+import pytest
+import torch
+
+from hyle_b200 import abi, ops
+from hyle_b200 import workloads as wl
+from oracle import binding as ob
+
+pytestmark = pytest.mark.gpu
+
+DEV = "cuda"
+F32_REL = 1e-5          # fp32 outputs
+BF16_REL = 2e-3         # bf16 RMSNorm / softmax against the unrounded checker value
+TINY = 1e-37            # absolute slack for subnormal results
+
+
+# ---- helpers ------------------------------------------------------------------------------------------------
+def to_dev_bf16(words: np.ndarray) -> torch.Tensor:
+    return torch.from_numpy(words.view(np.int16)).to(DEV).view(torch.bfloat16)
+
+
+def bf16_words(t: torch.Tensor) -> np.ndarray:
+    return t.view(torch.int16).cpu().numpy().view(np.uint16)
+
+
+def to_dev(a: np.ndarray) -> torch.Tensor:
+    return torch.from_numpy(a).to(DEV)
+
+
+def u32(a):
+    return np.ascontiguousarray(a, dtype=np.float32).view(np.uint32)
+
+
+def assert_f32_bits(got, want):
+    got, want = np.asarray(got, np.float32), np.asarray(want, np.float32)
+    assert np.array_equal(np.isnan(got), np.isnan(want))
+    ok = ~np.isnan(want)
+    assert np.array_equal(u32(got)[ok], u32(want)[ok])
+
+
+def bf16_ulp_distance(a_words, b_words):
+    """Distance in bf16 steps on the ordered integer line (handles sign); NaN must match NaN."""
+    def ordered(w):
+        w = w.astype(np.int32)
+        return np.where(w & 0x8000, -(w & 0x7FFF), w & 0x7FFF)
+    a_nan, b_nan = (a_words & 0x7FFF) > 0x7F80, (b_words & 0x7FFF) > 0x7F80
+    assert np.array_equal(a_nan, b_nan)
+    return np.abs(ordered(a_words) - ordered(b_words))[~a_nan]
+
+
+def assert_bf16_close(got_words, want_words, want_f32, rel):
+    dist = bf16_ulp_distance(got_words, want_words)
+    assert dist.max(initial=0) <= 1, f"max bf16 ulp distance {dist.max()}"
+    ok = np.isfinite(want_f32)
+    got = wl.bf16_to_f32(got_words)[ok].astype(np.float64)
+    ref = want_f32[ok].astype(np.float64)
+    # half a bf16 step of the result itself is the floor of any bf16 output; rel sits on top of it
+    assert np.all(np.abs(got - ref) <= rel * np.abs(ref) + TINY)
+    return float((dist != 0).mean()) if dist.size else 0.0
+
+
+@pytest.fixture(scope="module")
+def oracle():
+    return ob.Oracle()
+
+
+# ---- workload 1: broadcast add + row reductions (f32) ---------------------------------------------------------
+@pytest.mark.parametrize("rows,cols", [(4096, 4096), (37, 4096), (5, 1024), (3, 2048), (9, 8192), (7, 1000), (4, 1003), (3, 1)])
+def test_add_bias_row_sum_max(oracle, rows, cols):
+    a, bias = wl.broadcast_add_inputs(rows, cols)
+    c, row_sum, row_max = ops.add_bias_row_sum_max(to_dev(a), to_dev(bias))
+    want_c = oracle.binary(ob.ADD, ob.F32, a, bias)
+    assert_f32_bits(c.cpu().numpy(), want_c)                                   # one IEEE add: bit-exact
+    assert_f32_bits(row_max.cpu().numpy(), oracle.reduce_rows(ob.MAXIMUM, want_c))  # exact
+    s64, abs64 = oracle.row_sum_f64(want_c)
+    assert np.all(np.abs(row_sum.cpu().numpy().astype(np.float64) - s64) <= F32_REL * abs64)
+    # fused == separate launches, bit for bit
+    c2 = ops.add(to_dev(a), to_dev(bias))
+    assert torch.equal(c2, c)
+    assert torch.equal(ops.reduce_rows(abi.REDUCE_SUM, c2), row_sum)
+    assert torch.equal(ops.reduce_rows(abi.REDUCE_MAXIMUM, c2), row_max)
+
+
+def test_binary_variants_and_broadcast_periods(oracle):
+    rng = np.random.default_rng(3)
+    for count, period in [(4096 * 8, 4096), (1024, 1024), (96, 32), (1000, 8), (77, 7), (35, 1), (12, 12)]:
+        lhs = rng.standard_normal(count).astype(np.float32)
+        rhs = rng.standard_normal(period).astype(np.float32)
+        for kind, okind in [(abi.BINARY_ADD, ob.ADD), (abi.BINARY_MULTIPLY, ob.MULTIPLY)]:
+            out = torch.empty(count, dtype=torch.float32, device=DEV)
+            abi.check("binary", abi.load().hyle_b200_binary(
+                torch.cuda.current_stream().cuda_stream, kind, abi.F32, to_dev(lhs).data_ptr(),
+                to_dev(rhs).data_ptr(), out.data_ptr(), count, period))
+            want = oracle.binary(okind, ob.F32, lhs.reshape(-1, period), rhs).ravel()
+            assert_f32_bits(out.cpu().numpy(), want)
+    # bf16 and f16: f32 operation, one rounding (bit-exact against the checker)
+    x16, r16, _, _ = wl.rms_norm_inputs(33)
+    got = ops.add(to_dev_bf16(x16), to_dev_bf16(r16))
+    assert np.array_equal(bf16_words(got), oracle.binary(ob.ADD, ob.BF16, x16, r16))
+    got = ops.multiply(to_dev_bf16(x16), to_dev_bf16(r16[0]))
+    assert np.array_equal(bf16_words(got), oracle.binary(ob.MULTIPLY, ob.BF16, x16, r16[0]))
+    h = rng.standard_normal((5, 264)).astype(np.float16)
+    g = rng.standard_normal((5, 264)).astype(np.float16)
+    got = ops.add(to_dev(h), to_dev(g)).cpu().numpy()
+    want = oracle.binary(ob.ADD, ob.F16, h.view(np.uint16), g.view(np.uint16))
+    assert np.array_equal(got.view(np.uint16), want)
+    # in place
+    t = to_dev(lhs.copy())
+    ops.add(t, t.clone(), out=t)
+    assert_f32_bits(t.cpu().numpy(), lhs + lhs)
+
+
+def test_reduce_rules_nan_signed_zero_empty(oracle):
+    x = np.zeros((8, 1500), np.float32)
+    rng = np.random.default_rng(4)
+    x[:] = rng.standard_normal(x.shape)
+    x[0, 1499] = np.nan          # NaN in the last lane of the tail
+    x[1, 31] = np.nan            # at a warp boundary
+    x[2] = -0.0; x[2, 700] = 0.0
+    x[3] = -0.0
+    x[4, 5] = np.inf; x[5, 9] = -np.inf
+    x[6] = -np.inf
+    for kind, okind in [(abi.REDUCE_MAXIMUM, ob.MAXIMUM), (abi.REDUCE_MINIMUM, ob.MINIMUM)]:
+        got = ops.reduce_rows(kind, to_dev(x)).cpu().numpy()
+        assert_f32_bits(got, oracle.reduce_rows(okind, x))
+    mean = ops.reduce_rows(abi.REDUCE_MEAN, to_dev(x[7:8])).cpu().numpy()
+    s64, abs64 = oracle.row_sum_f64(x[7:8])
+    assert abs(float(mean[0]) - s64[0] / 1500) <= F32_REL * abs64[0] / 1500
+    empty = torch.zeros((3, 0), dtype=torch.float32, device=DEV)
+    assert torch.equal(ops.reduce_rows(abi.REDUCE_SUM, empty).cpu(), torch.zeros(3))
+    assert torch.isnan(ops.reduce_rows(abi.REDUCE_MEAN, empty)).all()
+    assert (ops.reduce_rows(abi.REDUCE_MINIMUM, empty) == float("inf")).all()
+    assert (ops.reduce_rows(abi.REDUCE_MAXIMUM, empty) == float("-inf")).all()
+
+
+# ---- workload 2: residual add + RMSNorm (bf16) ------------------------------------------------------------------
+@pytest.mark.parametrize("tokens", [1, 64, 4096])
+@pytest.mark.parametrize("weight_kind", ["bf16", "f32"])
+def test_add_rms_norm_config(oracle, tokens, weight_kind):
+    x, r, w16, w32 = wl.rms_norm_inputs(tokens)
+    w = w16 if weight_kind == "bf16" else w32
+    w_dev = to_dev_bf16(w16) if weight_kind == "bf16" else to_dev(w32)
+    y, h = ops.add_rms_norm(to_dev_bf16(x), to_dev_bf16(r), w_dev, 1e-6)
+    want_y, want_y32, want_h = oracle.add_rms_norm(x, r, w, 1e-6)
+    assert np.array_equal(bf16_words(h), want_h)          # f32 add + one RNE: bit-exact
+    assert_bf16_close(bf16_words(y), want_y, want_y32, BF16_REL)
+    # fused == unfused composition, bit for bit
+    y2 = ops.rms_norm(ops.add(to_dev_bf16(x), to_dev_bf16(r)), w_dev, 1e-6)
+    assert torch.equal(y2.view(torch.int16), y.view(torch.int16))
+
+
+@pytest.mark.parametrize("hidden", [1, 8, 127, 128, 129, 256, 257, 512, 1024, 2048, 4096, 5120, 8192])
+def test_rms_norm_hidden_sizes(oracle, hidden):
+    rng = np.random.default_rng(hidden)
+    x = wl.f32_to_bf16(rng.standard_normal((5, hidden)).astype(np.float32))
+    r = wl.f32_to_bf16(rng.standard_normal((5, hidden)).astype(np.float32))
+    w32 = rng.uniform(0.5, 1.5, hidden).astype(np.float32)
+    for w, w_dev in [(None, None), (wl.f32_to_bf16(w32), to_dev_bf16(wl.f32_to_bf16(w32))), (w32, to_dev(w32))]:
+        y = ops.rms_norm(to_dev_bf16(x), w_dev, 1e-6)
+        want_y, want_y32 = oracle.rms_norm(x, w, 1e-6)
+        assert_bf16_close(bf16_words(y), want_y, want_y32, BF16_REL)
+        y, h = ops.add_rms_norm(to_dev_bf16(x), to_dev_bf16(r), w_dev, 1e-6)
+        want_y, want_y32, want_h = oracle.add_rms_norm(x, r, w, 1e-6)
+        assert np.array_equal(bf16_words(h), want_h)
+        assert_bf16_close(bf16_words(y), want_y, want_y32, BF16_REL)
+    # y may alias x
+    t = to_dev_bf16(x)
+    ops.rms_norm(t, None, 1e-6, out=t)
+    assert_bf16_close(bf16_words(t), *oracle.rms_norm(x, None, 1e-6), BF16_REL)
+    assert ops.rms_norm(torch.empty((0, hidden), dtype=torch.bfloat16, device=DEV), None, 1e-6).numel() == 0
+
+
+# ---- workload 3: SwiGLU (bf16) ----------------------------------------------------------------------------------------
+@pytest.mark.parametrize("tokens", [1, 8, 32, 4096])
+def test_swiglu_config(oracle, tokens):
+    gate, up = wl.swiglu_inputs(tokens)
+    out = ops.swiglu(to_dev_bf16(gate), to_dev_bf16(up))
+    want, want32 = oracle.swiglu(gate, up)
+    dist = bf16_ulp_distance(bf16_words(out), want)
+    assert dist.max() <= 1                                   # <= 1 bf16 ulp
+    assert (dist != 0).mean() < 1e-3                         # and nearly always identical
+
+
+def test_swiglu_specials_packed_and_odd_shapes(oracle, ):
+    specials = np.array([0.0, -0.0, np.inf, -np.inf, np.nan, 80.0, -80.0, 1e-30, -1e-30, 88.7, -88.7, 100.0,
+                         -100.0, 1.0, -1.0, 20.0, -20.0, 3e38, -3e38], np.float32)
+    rng = np.random.default_rng(9)
+    for rows, cols in [(3, 264), (2, 257), (5, 6144), (1, 8)]:
+        gate = (1.5 * rng.standard_normal((rows, cols))).astype(np.float32)
+        up = (1.5 * rng.standard_normal((rows, cols))).astype(np.float32)
+        n = min(specials.size, cols)
+        gate[0, :n] = specials[:n]
+        up[-1, :n] = specials[:n][::-1]
+        g16, u16 = wl.f32_to_bf16(gate), wl.f32_to_bf16(up)
+        want, _ = oracle.swiglu(g16, u16)
+        out = ops.swiglu(to_dev_bf16(g16), to_dev_bf16(u16))
+        assert bf16_ulp_distance(bf16_words(out), want).max() <= 1
+        packed = np.concatenate([g16, u16], axis=1)
+        out_p = ops.swiglu_packed(to_dev_bf16(packed))
+        assert np.array_equal(bf16_words(out_p), bf16_words(out))
+    # silu(-inf) * finite = 0, not NaN
+    g = wl.f32_to_bf16(np.full((1, 8), -np.inf, np.float32))
+    u = wl.f32_to_bf16(np.full((1, 8), 2.0, np.float32))
+    assert np.all(wl.bf16_to_f32(bf16_words(ops.swiglu(to_dev_bf16(g), to_dev_bf16(u)))) == 0.0)
+
+
+# ---- workload 4: logits -> lse, softmax bf16, argmax ----------------------------------------------------------------------
+def check_logits(oracle, logits):
+    lse, probs, index, value = ops.logits_reduce(to_dev(logits))
+    want_lse, want_p, want_p32, want_i, want_v = oracle.logits_reduce(logits)
+    assert np.array_equal(index.cpu().numpy(), want_i)                  # bit-exact, lowest index on ties
+    assert_f32_bits(value.cpu().numpy(), want_v)
+    got_lse = lse.cpu().numpy()
+    assert np.array_equal(np.isnan(got_lse), np.isnan(want_lse))
+    ok = ~np.isnan(want_lse)
+    assert np.all(np.abs(got_lse[ok] - want_lse[ok]) <= F32_REL * np.abs(want_lse[ok]) + 1e-30)
+    mismatch = assert_bf16_close(bf16_words(probs), want_p, want_p32, BF16_REL)
+    assert mismatch < 1e-2
+    return index
+
+
+@pytest.mark.parametrize("batch", [1, 16])
+def test_logits_config(oracle, batch):
+    logits, tied = wl.logits_inputs(batch)
+    assert tied
+    index = check_logits(oracle, logits)
+    for row in tied:  # the duplicated maximum: the lower copy wins
+        peak = logits[row].max()
+        assert int(index[row]) == int(np.flatnonzero(logits[row] == peak)[0])
+
+
+def test_logits_config_256_rows_against_size_independent_properties(oracle):
+    """Full workload size: argmax and lse are compared with the checker on every row (cheap), the
+    155 MB of probabilities through row sums and a sampled set of rows."""
+    logits, tied = wl.logits_inputs(256)
+    dev = to_dev(logits)
+    lse, probs, index, value = ops.logits_reduce(dev)
+    want_i, want_v = oracle.argmax(logits)
+    assert np.array_equal(index.cpu().numpy(), want_i)
+    assert len(tied) >= 2
+    sums = probs.float().sum(dim=1).cpu().numpy()
+    assert np.all(np.abs(sums - 1.0) < 2e-3)
+    rows = sorted(set(tied + [0, 100, 255]))
+    want_lse, want_p, want_p32, _, _ = oracle.logits_reduce(logits[rows])
+    assert np.all(np.abs(lse.cpu().numpy()[rows] - want_lse) <= F32_REL * np.abs(want_lse))
+    assert_bf16_close(bf16_words(probs[rows]), want_p, want_p32, BF16_REL)
+    # standalone argmax and f32 softmax agree with the fused launch
+    idx2, val2 = ops.argmax(dev)
+    assert torch.equal(idx2, index) and torch.equal(val2, value)
+
+
+@pytest.mark.parametrize("cols", [1, 7, 8, 1000, 1024, 19000, 19456, 40000, 151936, 262144])
+def test_logits_shapes_and_invalid_rows(oracle, cols):
+    rng = np.random.default_rng(cols)
+    x = (4.0 * rng.standard_normal((7, cols))).astype(np.float32)
+    x[1] *= 20.0
+    if cols >= 7:
+        x[2, cols // 2] = np.nan
+        x[3, cols - 1] = np.inf
+        x[4, :] = -np.inf
+        x[5, 0] = -np.inf
+        x[6, :] = np.nan; x[6, cols - 2] = -np.inf
+    check_logits(oracle, x)
+    # Softmax / LogSoftmax with f32 output
+    for log in (False, True):
+        got = ops.softmax(to_dev(x), log=log).cpu().numpy()
+        want = oracle.softmax(x, log=log)
+        assert np.array_equal(np.isnan(got), np.isnan(want))
+        ok = np.isfinite(want)
+        tol = F32_REL * np.abs(want[ok]) + (1e-5 if log else 1e-37)
+        assert np.all(np.abs(got[ok] - want[ok]) <= tol)
+    idx, val = ops.argmax(to_dev(x))
+    want_i, want_v = oracle.argmax(x)
+    assert np.array_equal(idx.cpu().numpy(), want_i)
+    assert_f32_bits(val.cpu().numpy(), want_v)
+
+
+def test_argmax_golden_cases(oracle, golden):
+    x = golden["argmax_x"]
+    idx, val = ops.argmax(to_dev(x))
+    assert np.array_equal(idx.cpu().numpy(), golden["argmax_index"])
+    assert_f32_bits(val.cpu().numpy(), golden["argmax_value"])
+    _, _, idx2, _ = ops.logits_reduce(to_dev(x))
+    assert np.array_equal(idx2.cpu().numpy(), golden["argmax_index"])
+
+
+def test_cast_f32_to_bf16(oracle):
+    rng = np.random.default_rng(2)
+    for count in [1, 7, 8, 4096, 100003]:
+        x = rng.standard_normal(count).astype(np.float32)
+        x[0] = 1.00390625  # a tie: rounds to even
+        assert np.array_equal(bf16_words(ops.cast_f32_to_bf16(to_dev(x))), oracle.f32_to_bf16(x))
+
+
+# ---- workload 5: Q8_0 + sum of squares -----------------------------------------------------------------------------------------
+@pytest.mark.parametrize("rows", [1, 3, 1024])
+def test_q8_0_roundtrip_against_checker(oracle, rows):
+    w = wl.q8_sweep_inputs(rows)
+    dev = to_dev_bf16(w)
+    ws = ops.make_workspace(DEV)
+    status = torch.zeros(1, dtype=torch.int32, device=DEV)
+    for _ in range(2):  # the workspace is reusable
+        blocks, decoded, total = ops.q8_0_roundtrip(dev, ws, status=status)
+        want_blocks, want_decoded, want_total, invalid = oracle.q8_0_roundtrip(w)
+        assert np.array_equal(blocks.cpu().numpy(), want_blocks)              # bit-exact
+        assert np.array_equal(bf16_words(decoded).ravel(), want_decoded)      # bit-exact
+        assert abs(total.item() - want_total) <= F32_REL * want_total
+        assert status.item() == 0 and not invalid
+    # the separate operators give the same bytes
+    assert torch.equal(ops.q8_0_encode(dev).ravel(), blocks)
+    assert torch.equal(ops.q8_0_decode(blocks, w.size).view(torch.int16), decoded.view(torch.int16).ravel())
+    assert abs(ops.sum_squares(dev, ws).item() - want_total) <= F32_REL * want_total
+
+
+def _encode_case(oracle, values, dtype):
+    if dtype == "f32":
+        payload, kind, dev = values, ob.F32, to_dev(values)
+    elif dtype == "bf16":
+        payload, kind = wl.f32_to_bf16(values), ob.BF16
+        dev = to_dev_bf16(payload)
+    else:
+        with np.errstate(over="ignore"):
+            half = values.astype(np.float16)
+        payload, kind, dev = half.view(np.uint16), ob.F16, to_dev(half)
+    status = torch.zeros(1, dtype=torch.int32, device=DEV)
+    got = ops.q8_0_encode(dev.reshape(1, -1), status).cpu().numpy().ravel()
+    want, invalid = oracle.q8_0_encode(kind, payload)
+    assert np.array_equal(got, want)
+    assert bool(status.item() & abi.STATUS_INVALID_Q8_INPUT) == invalid
+    return got, invalid
+
+
+@pytest.mark.parametrize("dtype", ["f32", "bf16", "f16"])
+def test_q8_0_known_answers(oracle, dtype):
+    # tests/compute_provider_ggml/native_paged_test.cc:255-276: ties, zero block, three input types
+    values = np.array([float(int(i % 23) - 11) * 0.03125 for i in range(256)], np.float32)
+    values[:5] = [127.0, 0.5, 1.5, -0.5, -1.5]
+    values[32:64] = 0.0
+    got, invalid = _encode_case(oracle, values, dtype)
+    assert not invalid and got[3] == 1 and got[4] == 2 and got[5].view(np.int8) == -1
+    # :288-326: scale boundaries around the smallest non-zero f16 scale
+    zero_boundary = np.float32(127.0) * np.float32(2.0 ** -25)
+    minimum_scale = np.float32(127.0) * np.float32(2.0 ** -24)
+    nxt = lambda v, d: np.nextafter(np.float32(v), np.float32(d))
+    amplitudes = [0.0, np.float32(1e-45), np.finfo(np.float32).tiny, 2.0 ** -122, 2.0 ** -120, 2.0 ** -24,
+                  nxt(zero_boundary, 0), zero_boundary, nxt(zero_boundary, 1), nxt(minimum_scale, 0),
+                  minimum_scale, nxt(minimum_scale, 1), 2.0 ** -14, 65504.0]
+    if dtype == "f32":
+        amplitudes.append(65504.0 * 127.0)
+    values = np.zeros(len(amplitudes) * 64, np.float32)
+    for i in range(values.size):
+        a = np.float32(amplitudes[i // 64])
+        values[i] = [a, -a, a * np.float32(0.125), -a * np.float32(0.125), 0.0, -0.0, 0.0, 0.0][i % 8]
+    got, invalid = _encode_case(oracle, values, dtype)
+    assert not invalid
+    scales = got.reshape(-1, 34)[:, :2].copy().view(np.uint16).ravel()
+    assert np.any(scales == 0) and np.any(scales != 0)
+
+
+def test_q8_0_invalid_payload_sets_status_and_zeroes_the_block(oracle):
+    # native_paged_test.cc:339-348
+    for bad in (np.nan, np.inf, -np.inf, 9000000.0):
+        values = np.ones(64 * 9, np.float32)
+        values[19] = bad
+        got, invalid = _encode_case(oracle, values, "f32")
+        assert invalid and np.all(got[:34] == 0) and np.any(got[34:68] != 0)
+    values = np.ones(64, np.float32)
+    values[40] = np.inf
+    _, invalid = _encode_case(oracle, values, "bf16")
+    assert invalid
+    _, invalid = _encode_case(oracle, values, "f16")
+    assert invalid
+
+
+def test_q8_0_rounding_ties_and_ragged_tiles(oracle):
+    # every k + 0.5 tie and its neighbours with scale exactly 1 (amax 127)
+    ks = np.arange(-126, 127, dtype=np.float32)
+    ties = np.concatenate([ks + 0.5, np.nextafter(ks + np.float32(0.5), np.float32(1e9)),
+                           np.nextafter(ks + np.float32(0.5), np.float32(-1e9))]).astype(np.float32)
+    pad = (-ties.size) % 31
+    ties = np.concatenate([ties, np.zeros(pad, np.float32)]).reshape(-1, 31)
+    values = np.concatenate([np.full((ties.shape[0], 1), 127.0, np.float32), ties], axis=1).ravel()
+    _encode_case(oracle, values, "f32")
+    # block counts that are not multiples of the 256-block tile
+    rng = np.random.default_rng(8)
+    for blocks in [1, 3, 255, 257, 513, 1000]:
+        w = wl.f32_to_bf16((0.02 * rng.standard_normal(blocks * 32)).astype(np.float32))
+        dev = to_dev_bf16(w)
+        ws = ops.make_workspace(DEV)
+        got_b, got_d, got_s = ops.q8_0_roundtrip(dev, ws)
+        want_b, want_d, want_s, _ = oracle.q8_0_roundtrip(w)
+        assert np.array_equal(got_b.cpu().numpy(), want_b)
+        assert np.array_equal(bf16_words(got_d), want_d)
+        assert abs(got_s.item() - want_s) <= F32_REL * want_s
+        # unaligned carrier (2-byte aligned only)
+        carrier = torch.zeros(blocks * 34 + 16, dtype=torch.uint8, device=DEV)
+        view = carrier[2:2 + blocks * 34]
+        ops.q8_0_roundtrip(dev, ws, blocks=view)
+        assert np.array_equal(view.cpu().numpy(), want_b)
+        assert torch.equal(ops.q8_0_decode(view, w.size).view(torch.int16), got_d.view(torch.int16))
+
+
+def test_q8_0_full_size_properties():
+    """At a large size the checker is too slow; use what the format guarantees instead:
+    decode(encode(x)) from the fused kernel equals the separate decode of its own blocks,
+    encoding the decoded tensor reproduces the codes' scale class (idempotence of the grid),
+    the sum of squares is additive over row shards, and the error is within half a step."""
+    rows = 32768  # 512 MiB of bf16
+    shard = wl.shard_rows(rows, 1, 0)
+    w = wl.q8_sweep_device_shard(shard)
+    ws = ops.make_workspace(DEV)
+    blocks, decoded, total = ops.q8_0_roundtrip(w, ws)
+    assert torch.equal(ops.q8_0_decode(blocks, w.numel()).view(torch.int16), decoded.view(torch.int16).ravel())
+    b = blocks.view(-1, 34)
+    scale = b[:, :2].contiguous().view(torch.float16).float()
+    err = (decoded.float().view(-1, 32) - w.float().view(-1, 32)).abs()
+    bound = 0.5 * scale * (1 + 2 ** -10) + w.float().view(-1, 32).abs() * 2 ** -8 + 1e-12
+    assert bool((err <= bound).all())
+    assert int(b[:, 2:].view(torch.int8).abs().max()) == 127  # every block uses its full range
+    halves = [ops.sum_squares(w[: rows // 2], ws).item(), ops.sum_squares(w[rows // 2:], ws).item()]
+    assert abs(sum(halves) - total.item()) <= 1e-9 * total.item()
+    reference = (w.double() ** 2).sum().item()
+    assert abs(total.item() - reference) <= F32_REL * reference

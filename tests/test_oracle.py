@@ -1,0 +1,254 @@
+"""Pins the CPU checker (oracle/hyle_oracle.c) before anything trusts it.
+
+Three anchors: (1) golden outputs produced by running the reference's own scalar floor
+(tests/golden/ref_floor.npz, made by tests/golden/make_golden.py); (2) the reference floor itself,
+live, where oracle/_ref was built; (3) known-answer vectors and independent formulas re-expressed
+from the reference's tests.
+"""
+import math
+
+import numpy as np
+import pytest
+import torch
+
+from hyle_b200 import workloads as wl
+from oracle import binding as ob
+
+
+def bits(a):
+    return np.ascontiguousarray(a).view(np.uint32 if a.dtype == np.float32 else a.dtype)
+
+
+def same_f32(a, b):
+    """Bit equality, any NaN matching any NaN."""
+    a, b = np.asarray(a, np.float32), np.asarray(b, np.float32)
+    return np.array_equal(np.isnan(a), np.isnan(b)) and np.array_equal(bits(a)[~np.isnan(a)], bits(b)[~np.isnan(b)])
+
+
+# ---- golden vectors from the reference's scalar floor ------------------------------------------------
+def test_swiglu_matches_reference_golden(oracle, golden):
+    out, _ = oracle.swiglu(golden["swiglu_gate"], golden["swiglu_up"])
+    want = golden["swiglu_out"]
+    nan = (want & 0x7FFF) > 0x7F80
+    assert np.array_equal(nan, (out & 0x7FFF) > 0x7F80)
+    assert np.array_equal(out[~nan], want[~nan])
+
+
+@pytest.mark.parametrize("hidden", [1, 127, 128, 129, 257, 2048, 4096])
+def test_rms_norm_matches_reference_golden(oracle, golden, hidden):
+    x, w = golden[f"rms_x_{hidden}"], golden[f"rms_w_{hidden}"]
+    assert np.array_equal(oracle.rms_norm(x, w, 1e-6)[0], golden[f"rms_y_{hidden}"])
+    assert np.array_equal(oracle.rms_norm(x, None, 1e-6)[0], golden[f"rms_y_noweight_{hidden}"])
+
+
+@pytest.mark.parametrize("cols", [1, 7, 1000])
+def test_softmax_matches_reference_golden(oracle, golden, cols):
+    x = golden[f"softmax_x_{cols}"]
+    assert same_f32(oracle.softmax(x), golden[f"softmax_y_{cols}"])
+    assert same_f32(oracle.softmax(x, log=True), golden[f"log_softmax_y_{cols}"])
+    lse, probs, probs32, _, _ = oracle.logits_reduce(x)
+    assert same_f32(probs32, golden[f"softmax_y_{cols}"])
+    # the log-softmax shift is the log-sum-exp: x - lse == log_softmax
+    valid = ~np.isnan(lse)
+    assert same_f32((x[valid] - lse[valid, None]).astype(np.float32), golden[f"log_softmax_y_{cols}"][valid])
+
+
+def test_argmax_matches_reference_golden(oracle, golden):
+    index, value = oracle.argmax(golden["argmax_x"])
+    assert np.array_equal(index, golden["argmax_index"])
+    assert same_f32(value, golden["argmax_value"])
+    # spot-check the rules the golden encodes
+    assert list(index[:5]) == [int(np.argmax(golden["argmax_x"][0])), 17, 0, 0, 250]
+
+
+# ---- live against the reference floor, larger seeded inputs --------------------------------------------
+def test_oracle_equals_reference_floor_live(oracle, ref_floor):
+    gate, up = wl.swiglu_inputs(8)
+    assert np.array_equal(oracle.swiglu(gate, up)[0], ref_floor.swiglu(gate, up))
+    x, _, w16, _ = wl.rms_norm_inputs(64)
+    assert np.array_equal(oracle.rms_norm(x, w16, 1e-6)[0], ref_floor.rms_norm(x, w16, 1e-6))
+    logits, tied = wl.logits_inputs(2, cols=151936)
+    assert same_f32(oracle.softmax(logits), ref_floor.softmax(logits))
+    assert same_f32(oracle.softmax(logits, log=True), ref_floor.softmax(logits, log=True))
+    oi, ov = oracle.argmax(logits)
+    ri, rv = ref_floor.argmax(logits)
+    assert np.array_equal(oi, ri) and same_f32(ov, rv)
+    assert tied, "workload 4 must contain a tied row"
+
+
+def test_conversions_match_reference_floor(oracle, ref_floor):
+    rng = np.random.default_rng(5)
+    patterns = rng.integers(0, 2**32, 20000, dtype=np.uint64).astype(np.uint32)
+    edge = np.array([0x00000000, 0x80000000, 0x7F800000, 0xFF800000, 0x7FC00000, 0x7F800001, 0x3F808000,
+                     0x3F818000, 0x3F807FFF, 0x33000000, 0x33000001, 0x32FFFFFF, 0x387FC000, 0x477FF000,
+                     0x477FEFFF, 0x00000001, 0x007FFFFF], dtype=np.uint32)
+    for u in np.concatenate([patterns, edge]):
+        f = np.array([u], np.uint32).view(np.float32)[0]
+        assert oracle.lib.hyle_oracle_f32_to_bf16(f) == ref_floor.lib.hyle_ref_f32_to_bf16(f)
+        assert oracle.lib.hyle_oracle_f32_to_f16(f) == ref_floor.lib.hyle_ref_f32_to_f16(f)
+    for h in range(0, 65536, 7):
+        a, b = oracle.lib.hyle_oracle_f16_to_f32(h), ref_floor.lib.hyle_ref_f16_to_f32(h)
+        assert (math.isnan(a) and math.isnan(b)) or a == b
+
+
+# ---- independent anchors for the storage conversions ------------------------------------------------------
+def test_f16_conversions_against_numpy(oracle):
+    halves = np.arange(65536, dtype=np.uint16)
+    want = halves.view(np.float16).astype(np.float32)
+    got = np.array([oracle.f16_to_f32_scalar(int(h)) for h in halves], np.float32)
+    assert same_f32(got, want)  # exhaustive, as tests/simd/dtype_test.cc:168-209
+    rng = np.random.default_rng(11)
+    values = np.concatenate([rng.standard_normal(4000).astype(np.float32) * 100,
+                             np.array([65504, 65519.99, 65520, 1e-8, 5.96e-8, 2.98e-8, 2.9802322e-8, 6.1e-5,
+                                       0.0, -0.0, np.inf, -np.inf], np.float32)])
+    got = np.array([oracle.f32_to_f16_scalar(float(v)) for v in values], np.uint16)
+    with np.errstate(over="ignore"):
+        want = values.astype(np.float16).view(np.uint16)
+    assert np.array_equal(got, want)
+
+
+def test_bf16_rounding_against_torch_and_numpy_helper(oracle):
+    rng = np.random.default_rng(12)
+    values = np.concatenate([rng.standard_normal(50000).astype(np.float32),
+                             np.array([1.00390625, 1.01171875, 3.3895314e38, np.inf, -np.inf, 0.0, -0.0], np.float32)])
+    want = torch.from_numpy(values).to(torch.bfloat16).view(torch.int16).numpy().view(np.uint16)
+    assert np.array_equal(oracle.f32_to_bf16(values), want)
+    assert np.array_equal(wl.f32_to_bf16(values), want)
+    assert oracle.f32_to_bf16_scalar(float("nan")) & 0x7FC0 == 0x7FC0  # NaN stays a quiet NaN
+
+
+# ---- Binary / Reduce rules ----------------------------------------------------------------------------------
+def test_binary_broadcast_is_one_ieee_operation(oracle):
+    a, bias = wl.broadcast_add_inputs(64, 256)
+    assert np.array_equal(bits(oracle.binary(ob.ADD, ob.F32, a, bias)), bits(a + bias[None, :]))
+    assert np.array_equal(bits(oracle.binary(ob.MULTIPLY, ob.F32, a, bias)), bits(a * bias[None, :]))
+    x16, r16, _, _ = wl.rms_norm_inputs(4)
+    want = wl.f32_to_bf16(wl.bf16_to_f32(x16) + wl.bf16_to_f32(r16))
+    assert np.array_equal(oracle.binary(ob.ADD, ob.BF16, x16, r16), want)
+
+
+def test_reduce_rules_nan_zero_empty(oracle):
+    # docs/user/compute.md:384-388 and tests/compute_provider_native/reduction_test.cc:130-222,330-398
+    x = np.array([[1.0, np.nan, 3.0], [-0.0, 0.0, -0.0], [-0.0, -0.0, -0.0], [-1.0, -2.0, -np.inf],
+                  [np.inf, 1.0, 2.0]], np.float32)
+    mx, mn = oracle.reduce_rows(ob.MAXIMUM, x), oracle.reduce_rows(ob.MINIMUM, x)
+    assert np.isnan(mx[0]) and np.isnan(mn[0])
+    assert mx[1] == 0 and not np.signbit(mx[1]) and mn[1] == 0 and np.signbit(mn[1])
+    assert np.signbit(mx[2]) and np.signbit(mn[2])
+    assert mx[3] == -1.0 and mn[3] == -np.inf and mx[4] == np.inf
+    empty = np.zeros((3, 0), np.float32)
+    assert np.array_equal(oracle.reduce_rows(ob.SUM, empty), np.zeros(3, np.float32))
+    assert np.all(np.isnan(oracle.reduce_rows(ob.MEAN, empty)))
+    assert np.all(oracle.reduce_rows(ob.MINIMUM, empty) == np.inf)
+    assert np.all(oracle.reduce_rows(ob.MAXIMUM, empty) == -np.inf)
+    a, bias = wl.broadcast_add_inputs(16, 4096)
+    c = a + bias
+    s64, abs64 = oracle.row_sum_f64(c)
+    assert np.all(np.abs(oracle.reduce_rows(ob.SUM, c) - s64) <= 1e-5 * abs64)
+
+
+# ---- Q8_0 known answers (tests/compute_provider_ggml/native_paged_test.cc:255-348) ------------------------------
+def _q8_expected(values_f32):
+    """The independent formula of the reference test, in numpy, block by block."""
+    values = np.asarray(values_f32, np.float32)
+    out = np.zeros(values.size // 32 * 34, np.uint8)
+    for b in range(values.size // 32):
+        block = values[b * 32:(b + 1) * 32]
+        scale = np.float32(np.max(np.abs(block))) / np.float32(127.0)
+        stored = np.float32(scale).astype(np.float16).view(np.uint16)
+        if stored == 0:
+            continue
+        out[b * 34] = stored & 0xFF
+        out[b * 34 + 1] = stored >> 8
+        inverse = np.float32(1.0) / scale
+        prod = (block * inverse).astype(np.float32)
+        # np.round is half-to-even; the reference uses std::round (half away from zero)
+        exact_half = np.abs(prod - np.trunc(prod)) == 0.5
+        codes = np.where(exact_half, np.trunc(prod) + np.sign(prod), np.round(prod))
+        out[b * 34 + 2:b * 34 + 34] = codes.astype(np.int8).view(np.uint8)
+    return out
+
+
+@pytest.mark.parametrize("dtype", ["f32", "bf16", "f16"])
+def test_q8_reference_bytes_ties_zero_and_three_input_types(oracle, dtype):
+    values = np.array([float(int(i % 23) - 11) * 0.03125 for i in range(256)], np.float32)
+    values[:5] = [127.0, 0.5, 1.5, -0.5, -1.5]
+    values[32:64] = 0.0
+    if dtype == "f32":
+        payload, kind, rounded = values, ob.F32, values
+    elif dtype == "bf16":
+        payload, kind = wl.f32_to_bf16(values), ob.BF16
+        rounded = wl.bf16_to_f32(payload)
+    else:
+        payload, kind = values.astype(np.float16).view(np.uint16), ob.F16
+        rounded = values.astype(np.float16).astype(np.float32)
+    got, invalid = oracle.q8_0_encode(kind, payload)
+    assert not invalid and got.size == 8 * 34
+    assert np.array_equal(got, _q8_expected(rounded))
+    assert got[3] == 1 and got[4] == 2 and got[5].view(np.int8) == -1  # 0.5 -> 1, 1.5 -> 2, -0.5 -> -1
+    assert np.all(got[34:68] == 0)  # the all-zero block is 34 zero bytes
+
+
+@pytest.mark.parametrize("dtype", ["f32", "bf16", "f16"])
+def test_q8_scale_boundaries_have_canonical_zero_blocks(oracle, dtype):
+    zero_boundary = np.float32(127.0) * np.float32(2.0 ** -25)
+    minimum_scale = np.float32(127.0) * np.float32(2.0 ** -24)
+    nxt = lambda v, d: np.nextafter(np.float32(v), np.float32(d))
+    amplitudes = [0.0, np.float32(1e-45), np.finfo(np.float32).tiny, 2.0 ** -122, 2.0 ** -120, 2.0 ** -24,
+                  nxt(zero_boundary, 0), zero_boundary, nxt(zero_boundary, 1), nxt(minimum_scale, 0),
+                  minimum_scale, nxt(minimum_scale, 1), 2.0 ** -14, 65504.0]
+    if dtype == "f32":
+        amplitudes.append(65504.0 * 127.0)
+    values = np.zeros(len(amplitudes) * 64, np.float32)
+    for i in range(values.size):
+        a = np.float32(amplitudes[i // 64])
+        values[i] = [a, -a, a * np.float32(0.125), -a * np.float32(0.125), 0.0, -0.0, 0.0, 0.0][i % 8]
+    if dtype == "f32":
+        payload, kind, rounded = values, ob.F32, values
+    elif dtype == "bf16":
+        payload, kind = wl.f32_to_bf16(values), ob.BF16
+        rounded = wl.bf16_to_f32(payload)
+    else:
+        payload, kind = values.astype(np.float16).view(np.uint16), ob.F16
+        rounded = values.astype(np.float16).astype(np.float32)
+    got, invalid = oracle.q8_0_encode(kind, payload)
+    assert not invalid
+    want = _q8_expected(rounded)
+    assert np.array_equal(got, want)
+    scales = want.reshape(-1, 34)[:, :2].view(np.uint16).ravel()
+    assert np.any(scales == 0) and np.any(scales != 0)
+    codes = want.reshape(-1, 34)[:, 2:].view(np.int8)
+    assert codes.min() >= -127 and codes.max() <= 127
+
+
+def test_q8_invalid_payload_is_flagged_and_zeroed(oracle):
+    for bad in (np.nan, np.inf):
+        values = np.ones(64, np.float32)
+        values[19] = bad
+        got, invalid = oracle.q8_0_encode(ob.F32, values)
+        assert invalid and np.all(got[:34] == 0) and np.any(got[34:] != 0)
+    got, invalid = oracle.q8_0_encode(ob.F32, np.full(64, 9000000.0, np.float32))
+    assert invalid and np.all(got == 0)
+    # bf16 threshold: the largest bf16 not above 65504*127 is accepted, the next one is not
+    limit16 = np.array([0x4AFD, 0x4AFE], np.uint16)
+    for word, expect in zip(limit16, (False, True)):
+        payload = np.zeros(32, np.uint16)
+        payload[7] = word
+        assert oracle.q8_0_encode(ob.BF16, payload)[1] == expect
+
+
+def test_q8_decode_is_exact_product_then_rne(oracle):
+    w = wl.q8_sweep_inputs(4)
+    blocks, _ = oracle.q8_0_encode(ob.BF16, w)
+    decoded = oracle.q8_0_decode(blocks, w.size)
+    b = blocks.reshape(-1, 34)
+    scale = b[:, :2].copy().view(np.float16).astype(np.float32)
+    want = wl.f32_to_bf16((scale * b[:, 2:].view(np.int8).astype(np.float32)).astype(np.float32))
+    assert np.array_equal(decoded, want.ravel())
+    # the round trip stays within half a quantisation step (+ one bf16 rounding) of the input
+    x = wl.bf16_to_f32(w).reshape(-1, 32)
+    err = np.abs(wl.bf16_to_f32(decoded).reshape(-1, 32) - x)
+    assert np.all(err <= 0.5 * scale * (1 + 2 ** -10) + np.abs(x) * 2 ** -8 + 1e-12)
+    blocks2, decoded2, total, invalid = oracle.q8_0_roundtrip(w)
+    assert np.array_equal(blocks2, blocks) and np.array_equal(decoded2, decoded) and not invalid
+    assert total == pytest.approx(float(np.sum(wl.bf16_to_f32(w).astype(np.float64) ** 2)), rel=1e-12)
