@@ -173,12 +173,18 @@ def time_op(torch, launch, sets: int, iterations: int = 40, warmup: int = 5):
     return start.elapsed_time(stop) / iterations
 
 
-def other_ops(torch, peak_gbs):
-    """Largest single-GPU shape of workloads 1-4: GB/s against algorithmic bytes, rotating inputs."""
+def other_ops(torch, peak_gbs, only=None, iterations=40):
+    """Largest single-GPU shape of workloads 1-4: GB/s against algorithmic bytes, rotating inputs.
+
+    `only` restricts the run to some operators (for profiling one kernel on a short command)."""
     from hyle_b200 import abi, ops
 
     results = []
     dev = "cuda"
+    lib, stream = abi.load(), torch.cuda.current_stream().cuda_stream
+
+    def wanted(name):
+        return only is None or name in only
 
     def report(name, shape, elements, algorithmic_bytes, ms, sets):
         gbs = algorithmic_bytes / (ms * 1e-3) / 1e9
@@ -187,53 +193,57 @@ def other_ops(torch, peak_gbs):
                         "buffer_sets": sets})
 
     # 1: f32 broadcast add + row sum + row max, 4096 x 4096
-    sets = 8
-    a = [torch.randn(4096, 4096, device=dev) for _ in range(sets)]
-    bias = torch.rand(4096, device=dev) * 2 - 1
-    c = [torch.empty_like(a[0]) for _ in range(sets)]
-    rs, rm = torch.empty(4096, device=dev), torch.empty(4096, device=dev)
-    lib, stream = abi.load(), torch.cuda.current_stream().cuda_stream
-    ms = time_op(torch, lambda i: lib.hyle_b200_add_bias_row_sum_max_f32(
-        stream, a[i].data_ptr(), bias.data_ptr(), c[i].data_ptr(), rs.data_ptr(), rm.data_ptr(), 4096, 4096), sets)
-    report("add_bias_row_sum_max_f32", "4096x4096", 4096 * 4096, 2 * 4096 * 4096 * 4 + 3 * 4096 * 4, ms, sets)
-    del a, c
+    if wanted("add_bias_row_sum_max_f32"):
+        sets = 8
+        a = [torch.randn(4096, 4096, device=dev) for _ in range(sets)]
+        bias = torch.rand(4096, device=dev) * 2 - 1
+        c = [torch.empty_like(a[0]) for _ in range(sets)]
+        rs, rm = torch.empty(4096, device=dev), torch.empty(4096, device=dev)
+        ms = time_op(torch, lambda i: lib.hyle_b200_add_bias_row_sum_max_f32(
+            stream, a[i].data_ptr(), bias.data_ptr(), c[i].data_ptr(), rs.data_ptr(), rm.data_ptr(), 4096, 4096),
+            sets, iterations)
+        report("add_bias_row_sum_max_f32", "4096x4096", 4096 * 4096, 2 * 4096 * 4096 * 4 + 3 * 4096 * 4, ms, sets)
+        del a, c
 
     # 2: bf16 residual add + RMSNorm, T = 4096, hidden 2048
-    sets = 16
-    x = [torch.randn(4096, 2048, device=dev).bfloat16() for _ in range(sets)]
-    r = [torch.randn(4096, 2048, device=dev).bfloat16() for _ in range(sets)]
-    w = (torch.rand(2048, device=dev) + 0.5).bfloat16()
-    y = [torch.empty_like(x[0]) for _ in range(sets)]
-    h = [torch.empty_like(x[0]) for _ in range(sets)]
-    ms = time_op(torch, lambda i: lib.hyle_b200_add_rms_norm_bf16(
-        stream, x[i].data_ptr(), r[i].data_ptr(), w.data_ptr(), abi.BF16, y[i].data_ptr(), h[i].data_ptr(),
-        4096, 2048, 1e-6), sets)
-    report("add_rms_norm_bf16", "4096x2048", 4096 * 2048, 4 * 4096 * 2048 * 2 + 2048 * 2, ms, sets)
-    del x, r, y, h
+    if wanted("add_rms_norm_bf16"):
+        sets = 16
+        x = [torch.randn(4096, 2048, device=dev).bfloat16() for _ in range(sets)]
+        r = [torch.randn(4096, 2048, device=dev).bfloat16() for _ in range(sets)]
+        w = (torch.rand(2048, device=dev) + 0.5).bfloat16()
+        y = [torch.empty_like(x[0]) for _ in range(sets)]
+        h = [torch.empty_like(x[0]) for _ in range(sets)]
+        ms = time_op(torch, lambda i: lib.hyle_b200_add_rms_norm_bf16(
+            stream, x[i].data_ptr(), r[i].data_ptr(), w.data_ptr(), abi.BF16, y[i].data_ptr(), h[i].data_ptr(),
+            4096, 2048, 1e-6), sets, iterations)
+        report("add_rms_norm_bf16", "4096x2048", 4096 * 2048, 4 * 4096 * 2048 * 2 + 2048 * 2, ms, sets)
+        del x, r, y, h
 
     # 3: bf16 SwiGLU, T = 4096, 6144 columns
-    sets = 8
-    g = [(1.5 * torch.randn(4096, 6144, device=dev)).bfloat16() for _ in range(sets)]
-    u = [(1.5 * torch.randn(4096, 6144, device=dev)).bfloat16() for _ in range(sets)]
-    o = [torch.empty_like(g[0]) for _ in range(sets)]
-    ms = time_op(torch, lambda i: lib.hyle_b200_swiglu_bf16(
-        stream, g[i].data_ptr(), u[i].data_ptr(), o[i].data_ptr(), 4096, 6144, 6144, 6144), sets)
-    report("swiglu_bf16", "4096x6144", 4096 * 6144, 3 * 4096 * 6144 * 2, ms, sets)
-    del g, u, o
+    if wanted("swiglu_bf16"):
+        sets = 8
+        g = [(1.5 * torch.randn(4096, 6144, device=dev)).bfloat16() for _ in range(sets)]
+        u = [(1.5 * torch.randn(4096, 6144, device=dev)).bfloat16() for _ in range(sets)]
+        o = [torch.empty_like(g[0]) for _ in range(sets)]
+        ms = time_op(torch, lambda i: lib.hyle_b200_swiglu_bf16(
+            stream, g[i].data_ptr(), u[i].data_ptr(), o[i].data_ptr(), 4096, 6144, 6144, 6144), sets, iterations)
+        report("swiglu_bf16", "4096x6144", 4096 * 6144, 3 * 4096 * 6144 * 2, ms, sets)
+        del g, u, o
 
     # 4: f32 logits -> lse, softmax bf16, argmax, B = 256, vocabulary 151936
-    sets = 4
-    rows, cols = 256, 151936
-    logits = [4.0 * torch.randn(rows, cols, device=dev) for _ in range(sets)]
-    probs = [torch.empty(rows, cols, dtype=torch.bfloat16, device=dev) for _ in range(sets)]
-    lse = torch.empty(rows, device=dev)
-    idx = torch.empty(rows, dtype=torch.int32, device=dev)
-    val = torch.empty(rows, device=dev)
-    ms = time_op(torch, lambda i: lib.hyle_b200_logits_reduce_f32(
-        stream, logits[i].data_ptr(), rows, cols, lse.data_ptr(), probs[i].data_ptr(), idx.data_ptr(),
-        val.data_ptr()), sets, iterations=20)
-    report("logits_reduce_f32", "256x151936", rows * cols, rows * cols * 6 + rows * 12, ms, sets)
-    del logits, probs
+    if wanted("logits_reduce_f32"):
+        sets = 4
+        rows, cols = 256, 151936
+        logits = [4.0 * torch.randn(rows, cols, device=dev) for _ in range(sets)]
+        probs = [torch.empty(rows, cols, dtype=torch.bfloat16, device=dev) for _ in range(sets)]
+        lse = torch.empty(rows, device=dev)
+        idx = torch.empty(rows, dtype=torch.int32, device=dev)
+        val = torch.empty(rows, device=dev)
+        ms = time_op(torch, lambda i: lib.hyle_b200_logits_reduce_f32(
+            stream, logits[i].data_ptr(), rows, cols, lse.data_ptr(), probs[i].data_ptr(), idx.data_ptr(),
+            val.data_ptr()), sets, max(1, iterations // 2))
+        report("logits_reduce_f32", "256x151936", rows * cols, rows * cols * 6 + rows * 12, ms, sets)
+        del logits, probs
     torch.cuda.empty_cache()
     return results
 
@@ -288,6 +298,20 @@ def run_e2e(torch, ops, abi, shard_rows: int, steps: int, warmup: int):
     h2d = shard_rows * SWEEP_COLS * 2
     d2h = shard_rows * block_bytes_per_row + shard_rows * SWEEP_COLS * 2 + chunks * 8
     return seconds, h2d, d2h, total
+
+
+def run_ops_only(args):
+    """Time only the named operators of workloads 1-4 (short command for profiling one kernel)."""
+    import torch
+
+    from hyle_b200 import abi
+
+    torch.cuda.set_device(0)
+    abi.load()
+    peak_gbs, peak_kind = hbm_peak()
+    names = set(args.ops_only.split(","))
+    print(json.dumps({"ops": other_ops(torch, peak_gbs, names, args.steps), "peak_gbs": peak_gbs,
+                      "peak_kind": peak_kind}), flush=True)
 
 
 def run_gpu(args):
@@ -375,7 +399,10 @@ def run_gpu(args):
             e2e_rows //= 2
     except ImportError:
         pass
-    e2e_seconds, h2d, d2h, _ = run_e2e(torch, ops, abi, e2e_rows, e2e_steps, 1)
+    if args.skip_e2e:
+        e2e_seconds, h2d, d2h = float("nan"), 0, 0
+    else:
+        e2e_seconds, h2d, d2h, _ = run_e2e(torch, ops, abi, e2e_rows, e2e_steps, 1)
     e2e_seconds *= shard.rows / e2e_rows
     h2d, d2h = h2d * shard.rows // e2e_rows, d2h * shard.rows // e2e_rows
     e2e_t = torch.tensor([e2e_seconds], dtype=torch.float64, device="cuda")
@@ -442,10 +469,16 @@ def main():
     parser.add_argument("--rows", type=int, default=DEFAULT_ROWS, help="total rows of the sweep point")
     parser.add_argument("--skip-ops", action="store_true", help="do not time workloads 1-4")
     parser.add_argument("--skip-cpu", action="store_true", help="do not time the CPU baseline")
+    parser.add_argument("--skip-e2e", action="store_true", help="do not time the host-buffer pass (profiling runs)")
+    parser.add_argument("--ops-only", default=None,
+                        help="comma list of add_bias_row_sum_max_f32,add_rms_norm_bf16,swiglu_bf16,logits_reduce_f32: "
+                             "time only these, --steps iterations each")
     args = parser.parse_args()
     if args.warmup < 3:
         args.warmup = 3
-    if args.impl == "reference":
+    if args.ops_only:
+        run_ops_only(args)
+    elif args.impl == "reference":
         run_reference(args)
     else:
         run_gpu(args)

@@ -79,7 +79,7 @@ __device__ __forceinline__ Best warp_best(Best best) {
 // Full TopK{1} order for one row, by one CTA, from global memory: larger value first, NaN last,
 // lower index on ties.  Used for rows the fast paths cannot decide (NaN present, or nothing above
 // -inf).  All threads of the CTA must call it.
-__device__ void rescan_argmax(const float *whole, uint32_t cols, int32_t *index_out, float *value_out) {
+__device__ __noinline__ void rescan_argmax(const float *whole, uint32_t cols, int32_t *index_out, float *value_out) {
   __shared__ Best s_best[kWarps];
   __shared__ uint32_t s_first[kWarps];
   const int t = threadIdx.x, lane = t & 31, warp = t >> 5;
@@ -388,6 +388,198 @@ logits_kernel(const LogitsParams p) {
   cluster.sync();  // no CTA leaves while a peer may still read its shared memory
 }
 
+// ================================================================================================
+// Fast path: the row lives in REGISTERS.  512 threads x 10 float4 = 20 480 values per CTA, so a
+// cluster of eight covers a 151 936-wide row with one float4 slot to spare per thread.  Each warp
+// works against its OWN maximum, so nothing waits on another warp until the single cluster
+// barrier of the row:
+//   [row i+1 streams into shared memory by cp.async while row i is processed]
+//   shared -> registers (each thread reads back exactly the 10 x 16 B it fetched itself, so no
+//   CTA barrier is involved) -> thread max -> warp max (shuffles)
+//   -> [lanes holding the warp max find its first position]         (only when an index is wanted)
+//   -> e = 2^((x - m_warp) log2 e) in place, thread sum -> warp sum -> publish (m, s, index)
+//   == cluster barrier ==
+//   every warp reads the <= 128 published entries through distributed shared memory and combines
+//   them (M = max m;  S = sum s 2^((m - M) log2 e);  index = min index among entries with m == M)
+//   -> p = e * 2^((m_warp - M) log2 e) / S -> bf16/f32 -> global
+// Shared memory is only a prefetch queue (one 16-byte read per four values); ~8 instructions per
+// element, one exponential per element.  The asynchronous prefetch is what keeps HBM busy: without
+// it the two CTAs of an SM load, compute, wait at the barrier and store in lock step.
+// ================================================================================================
+constexpr int kRegVectors = 10;
+constexpr uint32_t kRegSlice = kThreads * kRegVectors * 4;  // 20480 values per CTA
+constexpr float kLog2e = 1.4426950408889634f;
+
+struct __align__(16) WarpEntry {
+  float maximum;
+  float sum;
+  uint32_t index;
+  uint32_t pad;
+};
+
+__device__ __forceinline__ float exp2_approx(float x) {
+  float r;
+  asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(r) : "f"(x));
+  return r;
+}
+
+__device__ __forceinline__ void cp_async_16(void *shared_dst, const void *global_src) {
+  asm volatile("cp.async.cg.shared.global [%0], [%1], 16;" ::"r"(static_cast<uint32_t>(__cvta_generic_to_shared(shared_dst))),
+               "l"(global_src)
+               : "memory");
+}
+__device__ __forceinline__ void cp_async_commit() { asm volatile("cp.async.commit_group;" ::: "memory"); }
+__device__ __forceinline__ void cp_async_wait_all() { asm volatile("cp.async.wait_group 0;" ::: "memory"); }
+
+constexpr size_t kRegStageBytes = static_cast<size_t>(kThreads) * kRegVectors * sizeof(float4);  // 80 KB
+
+template <int kMode>
+__global__ void __launch_bounds__(kThreads, 2)
+logits_regs_kernel(const LogitsParams p) {
+  extern __shared__ __align__(16) float4 stage[];  // [kRegVectors][kThreads]: slot (j, t) belongs to thread t
+  __shared__ WarpEntry s_entry[2][kWarps];  // by row parity: one barrier per row
+  cg::cluster_group cluster = cg::this_cluster();
+  const unsigned rank = cluster.block_rank();
+  const unsigned cluster_size = cluster.num_blocks();
+  const int t = threadIdx.x, lane = t & 31, warp = t >> 5;
+  const uint64_t cluster_id = blockIdx.x / cluster_size;
+  const uint64_t cluster_count = gridDim.x / cluster_size;
+  const bool want_index = p.index != nullptr || p.value != nullptr;
+  const uint32_t begin = min(rank * p.slice, p.cols);
+  const uint32_t end = min(begin + p.slice, p.cols);
+  const uint32_t vectors = (end - begin) / 4;
+  // float4 slots of this thread that lie inside the slice: slot j is valid when j < slots
+  const int slots = vectors > static_cast<uint32_t>(t) ? static_cast<int>((vectors - t + kThreads - 1) / kThreads) : 0;
+  const float neg_inf = -CUDART_INF_F;
+
+  auto prefetch = [&](uint64_t row) {
+    const float4 *src = reinterpret_cast<const float4 *>(p.in + row * p.cols + begin);
+#pragma unroll
+    for (int j = 0; j < kRegVectors; ++j)
+      if (j < slots) cp_async_16(&stage[j * kThreads + t], src + j * kThreads + t);
+    cp_async_commit();
+  };
+  if (cluster_id < p.rows) prefetch(cluster_id);
+
+  int parity = 0;
+  for (uint64_t row = cluster_id; row < p.rows; row += cluster_count, parity ^= 1) {
+    cp_async_wait_all();  // this thread's own copies have landed; nobody else touches its slots
+    float4 x[kRegVectors];
+#pragma unroll
+    for (int j = 0; j < kRegVectors; ++j)
+      x[j] = j < slots ? stage[j * kThreads + t] : make_float4(neg_inf, neg_inf, neg_inf, neg_inf);
+    if (row + cluster_count < p.rows) prefetch(row + cluster_count);  // overlaps everything below
+    float thread_max = neg_inf;
+#pragma unroll
+    for (int j = 0; j < kRegVectors; ++j)
+      thread_max = max_nan(max_nan(thread_max, max_nan(x[j].x, x[j].y)), max_nan(x[j].z, x[j].w));
+    const float warp_max = warp_max_nan(thread_max);
+
+    uint32_t index = kNoIndex;
+    if (want_index && thread_max == warp_max) {  // few lanes; never true for NaN
+#pragma unroll
+      for (int j = kRegVectors - 1; j >= 0; --j) {  // descending, so the lowest position is written last
+        if (j < slots) {
+          const uint32_t base = begin + (j * kThreads + t) * 4;
+          if (x[j].w == warp_max) index = base + 3;
+          if (x[j].z == warp_max) index = base + 2;
+          if (x[j].y == warp_max) index = base + 1;
+          if (x[j].x == warp_max) index = base;
+        }
+      }
+    }
+    if (want_index) index = __reduce_min_sync(kFullMask, index);
+
+    // Exponentials against the warp's own maximum (0 stands in when the warp saw only -inf), as
+    // 2^(x log2e - c) with c = fl(max * log2e): one fused multiply-add and one ex2 per value.  The
+    // same c is used again when the warp's weight is formed below, so its rounding cancels.
+    const float reference = warp_max == neg_inf ? 0.0f : warp_max;
+    const float neg_c = -__fmul_rn(reference, kLog2e);
+    float thread_sum = 0.0f;
+#pragma unroll
+    for (int j = 0; j < kRegVectors; ++j) {
+      const float4 e = make_float4(exp2_approx(fmaf(x[j].x, kLog2e, neg_c)), exp2_approx(fmaf(x[j].y, kLog2e, neg_c)),
+                                   exp2_approx(fmaf(x[j].z, kLog2e, neg_c)), exp2_approx(fmaf(x[j].w, kLog2e, neg_c)));
+      thread_sum += (e.x + e.y) + (e.z + e.w);
+      if constexpr (kMode != kLogF32) x[j] = e;
+    }
+    const float warp_total = warp_sum(thread_sum);
+    if (lane == 0) s_entry[parity][warp] = WarpEntry{warp_max, warp_total, index, 0u};
+
+    cluster.sync();  // the only barrier of the row: every warp of every CTA has published
+
+    // Combine all entries; every warp does it for itself (fixed order -> identical results).
+    // (Two sweeps over the entries instead of holding them: registers are full of the row.)
+    const unsigned entries = cluster_size * kWarps;
+    float maximum = neg_inf;
+#pragma unroll
+    for (int k = 0; k < kMaxCluster * kWarps / 32; ++k) {
+      const unsigned e = k * 32 + lane;
+      if (e < entries) maximum = max_nan(maximum, cluster.map_shared_rank(&s_entry[parity][e % kWarps], e / kWarps)->maximum);
+    }
+    maximum = warp_max_nan(maximum);
+    const float row_c = __fmul_rn(maximum, kLog2e);
+    float total = 0.0f;
+    uint32_t best_index = kNoIndex;
+#pragma unroll
+    for (int k = 0; k < kMaxCluster * kWarps / 32; ++k) {
+      const unsigned e = k * 32 + lane;
+      if (e < entries) {
+        const WarpEntry entry = *cluster.map_shared_rank(&s_entry[parity][e % kWarps], e / kWarps);
+        // an entry at -inf carries sum 0; its weight must not become 0 * inf
+        const float weight = entry.maximum == neg_inf ? 0.0f : exp2_approx(__fmul_rn(entry.maximum, kLog2e) - row_c);
+        total = fmaf(entry.sum, weight, total);
+        if (entry.maximum == maximum) best_index = min(best_index, entry.index);
+      }
+    }
+    total = warp_sum(total);
+    best_index = __reduce_min_sync(kFullMask, best_index);
+
+    const bool valid = maximum > neg_inf && maximum < CUDART_INF_F;  // false for NaN too
+    const bool has_nan = maximum != maximum;
+    const float nan = CUDART_NAN_F;
+    const float shift = valid ? maximum + logf(total) : nan;  // f32 log: within an ulp of float(log(double))
+    if (rank == 0 && warp == 0 && lane == 0) {
+      if (p.lse != nullptr) p.lse[row] = shift;
+      if (want_index && !has_nan) {
+        if (p.index != nullptr) p.index[row] = static_cast<int32_t>(best_index);
+        if (p.value != nullptr) p.value[row] = maximum;
+      }
+    }
+
+    if (p.out != nullptr) {
+      float scale = nan;
+      if (valid) scale = warp_max == neg_inf ? 0.0f : __fdiv_rn(exp2_approx(-neg_c - row_c), total);
+      if constexpr (kMode == kProbsBf16) {
+        uint2 *dst = reinterpret_cast<uint2 *>(static_cast<unsigned short *>(p.out) + row * p.cols + begin);
+#pragma unroll
+        for (int j = 0; j < kRegVectors; ++j) {
+          if (j < slots)
+            st_stream(dst + j * kThreads + t, make_uint2(pack_bf16x2(x[j].x * scale, x[j].y * scale),
+                                          pack_bf16x2(x[j].z * scale, x[j].w * scale)));
+        }
+      } else {
+        float4 *dst = reinterpret_cast<float4 *>(static_cast<float *>(p.out) + row * p.cols + begin);
+#pragma unroll
+        for (int j = 0; j < kRegVectors; ++j) {
+          if (j < slots) {
+            float4 o;
+            if constexpr (kMode == kProbsF32) o = make_float4(x[j].x * scale, x[j].y * scale, x[j].z * scale, x[j].w * scale);
+            else o = make_float4(x[j].x - shift, x[j].y - shift, x[j].z - shift, x[j].w - shift);
+            st_stream(dst + j * kThreads + t, o);
+          }
+        }
+      }
+    }
+    // NaN rows take the full TopK order from global memory.  Placed last, when the row's registers
+    // are dead, so the rare path costs the common one no register pressure.  CTA-uniform condition.
+    if (rank == 0 && want_index && has_nan)  // CTA-uniform: NaN rows take the full TopK order
+      rescan_argmax(p.in + row * p.cols, p.cols, p.index != nullptr ? p.index + row : nullptr,
+                    p.value != nullptr ? p.value + row : nullptr);
+  }
+  cluster.sync();  // no CTA leaves while a peer may still read its shared memory
+}
+
 struct Plan {
   int cluster;
   uint32_t slice;
@@ -406,10 +598,69 @@ bool make_plan(uint64_t cols, Plan &plan) {
   return false;
 }
 
+int launch_cluster_kernel(cudaStream_t stream, void (*kernel)(const LogitsParams), const LogitsParams &p,
+                          int cluster, uint64_t clusters, size_t shared) {
+  cudaLaunchConfig_t config{};
+  config.gridDim = dim3(static_cast<unsigned>(clusters * cluster));
+  config.blockDim = dim3(kThreads);
+  config.dynamicSmemBytes = shared;
+  config.stream = stream;
+  cudaLaunchAttribute attribute{};
+  attribute.id = cudaLaunchAttributeClusterDimension;
+  attribute.val.clusterDim.x = cluster;
+  attribute.val.clusterDim.y = 1;
+  attribute.val.clusterDim.z = 1;
+  config.attrs = &attribute;
+  config.numAttrs = 1;
+  return static_cast<int>(cudaLaunchKernelEx(&config, kernel, p));
+}
+
+// Clusters of `cluster` CTAs that can be resident at once (two CTAs per SM), cached per size.
+template <int kMode>
+int resident_clusters(int cluster) {
+  static int cached[4][64] = {};
+  int device = 0;
+  cudaGetDevice(&device);
+  int slot = cluster == 1 ? 0 : cluster == 2 ? 1 : cluster == 4 ? 2 : 3;
+  if (device < 0 || device >= 64) device = 0;
+  if (cached[slot][device] == 0) {
+    cudaLaunchConfig_t config{};
+    config.gridDim = dim3(cluster * 1024);
+    config.blockDim = dim3(kThreads);
+    config.dynamicSmemBytes = kRegStageBytes;
+    cudaFuncSetAttribute(logits_regs_kernel<kMode>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                         static_cast<int>(kRegStageBytes));
+    cudaLaunchAttribute attribute{};
+    attribute.id = cudaLaunchAttributeClusterDimension;
+    attribute.val.clusterDim.x = cluster;
+    attribute.val.clusterDim.y = 1;
+    attribute.val.clusterDim.z = 1;
+    config.attrs = &attribute;
+    config.numAttrs = 1;
+    int count = 0;
+    if (cudaOccupancyMaxActiveClusters(&count, logits_regs_kernel<kMode>, &config) != cudaSuccess || count <= 0)
+      count = sm_count() * 2 / cluster;
+    cached[slot][device] = count;
+  }
+  return cached[slot][device];
+}
+
 template <int kMode>
 int launch_logits(cudaStream_t stream, LogitsParams p, bool vec) {
+  if (p.cols == 0) return HYLE_B200_NOT_SUPPORTED;
+  if constexpr (kMode != kArgmaxOnly) {
+    // Register-resident fast path: aligned rows of at most 8 x 20480 values.
+    if (vec && p.cols <= static_cast<uint64_t>(kMaxCluster) * kRegSlice) {
+      int cluster = 1;
+      while (static_cast<uint64_t>(cluster) * kRegSlice < p.cols) cluster *= 2;
+      p.slice = static_cast<uint32_t>(((p.cols + cluster - 1) / cluster + 7) / 8 * 8);
+      const uint64_t resident = static_cast<uint64_t>(resident_clusters<kMode>(cluster));
+      return launch_cluster_kernel(stream, logits_regs_kernel<kMode>, p, cluster,
+                                   p.rows < resident ? p.rows : resident, kRegStageBytes);
+    }
+  }
   Plan plan{};
-  if (p.cols == 0 || !make_plan(p.cols, plan)) return HYLE_B200_NOT_SUPPORTED;
+  if (!make_plan(p.cols, plan)) return HYLE_B200_NOT_SUPPORTED;
   p.slice = plan.slice;
   const size_t shared = kMode == kArgmaxOnly ? 0 : plan.shared_bytes;
   void (*kernel)(const LogitsParams);
@@ -419,20 +670,7 @@ int launch_logits(cudaStream_t stream, LogitsParams p, bool vec) {
     const cudaError_t e = cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, static_cast<int>(shared));
     if (e != cudaSuccess) return static_cast<int>(e);
   }
-  const uint64_t clusters = p.rows < 65536 ? p.rows : 65536;
-  cudaLaunchConfig_t config{};
-  config.gridDim = dim3(static_cast<unsigned>(clusters * plan.cluster));
-  config.blockDim = dim3(kThreads);
-  config.dynamicSmemBytes = shared;
-  config.stream = stream;
-  cudaLaunchAttribute attribute{};
-  attribute.id = cudaLaunchAttributeClusterDimension;
-  attribute.val.clusterDim.x = plan.cluster;
-  attribute.val.clusterDim.y = 1;
-  attribute.val.clusterDim.z = 1;
-  config.attrs = &attribute;
-  config.numAttrs = 1;
-  return static_cast<int>(cudaLaunchKernelEx(&config, kernel, p));
+  return launch_cluster_kernel(stream, kernel, p, plan.cluster, p.rows < 65536 ? p.rows : 65536, shared);
 }
 
 }  // namespace

@@ -27,16 +27,31 @@ constexpr uint64_t kWorkspaceBytes = 64 + sizeof(double) * kMaxPartials;
 // (ggml_cpu_provider.cc:563-584).
 constexpr uint32_t kLimitBitsF32 = 0x4afde040u;  // bits of 8319008.0f = 65504 * 127
 
-// roundf for |v| < 2^22: add 0.5 with the sign of v rounding toward zero, then truncate.  The
-// round-toward-zero add keeps 0.49999997f + 0.5f below 1.
-__device__ __forceinline__ int round_half_away(float v) {
-  const float half = __uint_as_float((__float_as_uint(v) & 0x80000000u) | 0x3f000000u);
-  return __float2int_rz(__fadd_rz(v, half));
+// Round half away from zero WITHOUT the conversion unit (F2I/I2F run at a quarter of the FP32 rate
+// and this kernel needs one rounding per value).  For |p| < 2^22:
+//   s = RZ(|p| + 0.5)            never crosses an integer upward (0.49999997 + 0.5 stays below 1)
+//   f = RZ(s + 2^23)             = 2^23 + floor(s): the integer sits in the low mantissa bits
+//   magnitude = f - 2^23         exact
+// The signed integer is then formed as 1.5 * 2^23 + sign * magnitude, whose bit pattern holds the
+// two's-complement code in its low byte; subtracting 1.5 * 2^23 again gives the code as a float.
+struct Rounded {
+  float value;     // roundf(p) as a float; +0 when the code is 0, like (float)(int8_t)code
+  uint32_t bits;   // bit pattern whose low byte is the int8 code
+};
+__device__ __forceinline__ Rounded round_half_away(float p) {
+  const float f = __fadd_rz(__fadd_rz(fabsf(p), 0.5f), 8388608.0f);
+  const float magnitude = __fadd_rn(f, -8388608.0f);
+  const float sign = __uint_as_float((__float_as_uint(p) & 0x80000000u) | 0x3f800000u);  // +-1
+  const float shifted = fmaf(magnitude, sign, 12582912.0f);  // 1.5 * 2^23 + signed integer, exact
+  Rounded r;
+  r.bits = __float_as_uint(shifted);
+  r.value = __fadd_rn(shifted, -12582912.0f);
+  return r;
 }
 
-__device__ __forceinline__ uint32_t pack_codes(int a, int b, int c, int d) {
-  return (static_cast<uint32_t>(a) & 0xffu) | ((static_cast<uint32_t>(b) & 0xffu) << 8) |
-         ((static_cast<uint32_t>(c) & 0xffu) << 16) | (static_cast<uint32_t>(d) << 24);
+// Low bytes of four words -> one word.
+__device__ __forceinline__ uint32_t pack_low_bytes(uint32_t a, uint32_t b, uint32_t c, uint32_t d) {
+  return __byte_perm(__byte_perm(a, b, 0x0040), __byte_perm(c, d, 0x0040), 0x5410);
 }
 
 // Eight consecutive values as f32 plus the largest magnitude bit pattern among them.
@@ -142,32 +157,45 @@ q8_0_kernel(const void *__restrict__ in, uint64_t blocks, unsigned char *__restr
       }
     }
     float tile_sum = 0.0f;
+    // Block maxima: after two xor shuffles all four lanes of a group hold the maximum of each of
+    // their four blocks.  The two IEEE divisions per block are then done ONCE: lane `sub` of the
+    // group handles block `sub` and the group shares the results by shuffle.
+    uint32_t mine = 0;
+#pragma unroll
+    for (int k = 0; k < kVectorsPerThread; ++k) {
+      uint32_t m = amax_bits[k];
+      m = max(m, __shfl_xor_sync(kFullMask, m, 1));
+      m = max(m, __shfl_xor_sync(kFullMask, m, 2));
+      if (k == sub) mine = m;
+    }
+    const bool valid = mine <= kLimitBitsF32;
+    const float d = __fdiv_rn(__uint_as_float(mine), 127.0f);
+    const unsigned short scale = f32_to_f16(d);
+    const bool zero_block = !valid || scale == 0;
+    const float my_inverse = zero_block ? 0.0f : __fdiv_rn(1.0f, d);   // 0 marks a zero block
+    const uint32_t my_scale = zero_block ? 0u : static_cast<uint32_t>(scale);
+    invalid_seen |= !valid;
 #pragma unroll
     for (int k = 0; k < kVectorsPerThread; ++k) {
       const uint32_t block = k * 64 + (t >> 2);
+      const int source = (threadIdx.x & 28) + k;  // lane within the warp that divided for block k
+      const float inverse = __shfl_sync(kFullMask, my_inverse, source);
+      const uint32_t stored_scale = __shfl_sync(kFullMask, my_scale, source);
       if constexpr (kSumSquares) {
 #pragma unroll
         for (int i = 0; i < 8; ++i) tile_sum = fmaf(v[k][i], v[k][i], tile_sum);
       }
-      uint32_t m = amax_bits[k];
-      m = max(m, __shfl_xor_sync(kFullMask, m, 1));
-      m = max(m, __shfl_xor_sync(kFullMask, m, 2));
-      const bool valid = m <= kLimitBitsF32;
-      const float d = __fdiv_rn(__uint_as_float(m), 127.0f);
-      const unsigned short scale = f32_to_f16(d);
-      const bool zero_block = !valid || scale == 0;
-      const float id = zero_block ? 0.0f : __fdiv_rn(1.0f, d);
-      invalid_seen |= !valid;
-      int q[8];
+      Rounded q[8];
 #pragma unroll
-      for (int i = 0; i < 8; ++i) q[i] = zero_block ? 0 : round_half_away(__fmul_rn(v[k][i], id));
-      const unsigned short stored_scale = zero_block ? static_cast<unsigned short>(0) : scale;
+      for (int i = 0; i < 8; ++i) q[i] = round_half_away(__fmul_rn(v[k][i], inverse));
+      uint32_t w0 = pack_low_bytes(q[0].bits, q[1].bits, q[2].bits, q[3].bits);
+      uint32_t w1 = pack_low_bytes(q[4].bits, q[5].bits, q[6].bits, q[7].bits);
+      const bool zero = inverse == 0.0f;  // also covers invalid input, where the products are NaN
+      if (zero) w0 = w1 = 0u;
       if constexpr (kEncode) {
         if (full || block < tile_blocks) {
           unsigned short *dst = reinterpret_cast<unsigned short *>(staged[buffer] + block * 34);
-          const uint32_t w0 = pack_codes(q[0], q[1], q[2], q[3]);
-          const uint32_t w1 = pack_codes(q[4], q[5], q[6], q[7]);
-          if (sub == 0) dst[0] = stored_scale;
+          if (sub == 0) dst[0] = static_cast<unsigned short>(stored_scale);
           dst[1 + sub * 4 + 0] = static_cast<unsigned short>(w0 & 0xffffu);
           dst[1 + sub * 4 + 1] = static_cast<unsigned short>(w0 >> 16);
           dst[1 + sub * 4 + 2] = static_cast<unsigned short>(w1 & 0xffffu);
@@ -176,12 +204,12 @@ q8_0_kernel(const void *__restrict__ in, uint64_t blocks, unsigned char *__restr
       }
       if constexpr (kDecode) {
         if (full || block < tile_blocks) {
-          const float s = f16_to_f32(stored_scale);
-          const uint4 out = make_uint4(
-              pack_bf16x2(__fmul_rn(s, static_cast<float>(q[0])), __fmul_rn(s, static_cast<float>(q[1]))),
-              pack_bf16x2(__fmul_rn(s, static_cast<float>(q[2])), __fmul_rn(s, static_cast<float>(q[3]))),
-              pack_bf16x2(__fmul_rn(s, static_cast<float>(q[4])), __fmul_rn(s, static_cast<float>(q[5]))),
-              pack_bf16x2(__fmul_rn(s, static_cast<float>(q[6])), __fmul_rn(s, static_cast<float>(q[7]))));
+          const float s = f16_to_f32(static_cast<unsigned short>(stored_scale));
+          uint4 out = make_uint4(pack_bf16x2(__fmul_rn(s, q[0].value), __fmul_rn(s, q[1].value)),
+                                 pack_bf16x2(__fmul_rn(s, q[2].value), __fmul_rn(s, q[3].value)),
+                                 pack_bf16x2(__fmul_rn(s, q[4].value), __fmul_rn(s, q[5].value)),
+                                 pack_bf16x2(__fmul_rn(s, q[6].value), __fmul_rn(s, q[7].value)));
+          if (zero) out = make_uint4(0u, 0u, 0u, 0u);
           st_stream(reinterpret_cast<uint4 *>(decoded + (first_block + block) * 32 + sub * 8), out);
         }
       }

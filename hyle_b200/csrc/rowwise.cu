@@ -305,11 +305,12 @@ int launch_rms(cudaStream_t stream, const void *x, const void *residual, const v
   const int sms = sm_count();
   auto warp_launch = [&](auto vectors_tag) {
     constexpr int kVectors = decltype(vectors_tag)::value;
-    // Small row counts get small CTAs so the rows spread over all SMs.
-    int warps_per_cta = kWarps;
-    while (warps_per_cta > 1 && rows < static_cast<uint64_t>(sms) * warps_per_cta) warps_per_cta >>= 1;
+    // Two rows per CTA: many small CTAs keep the tail of the grid short (the hardware hands a freed
+    // slot to the next CTA), and small row counts still spread over all SMs.
+    int warps_per_cta = 2;
+    if (rows < static_cast<uint64_t>(sms) * 2) warps_per_cta = 1;
     const uint64_t ctas = (rows + warps_per_cta - 1) / warps_per_cta;
-    const unsigned grid = clamp_grid(ctas, static_cast<uint64_t>(sms) * (2048 / (warps_per_cta * 32)));
+    const unsigned grid = clamp_grid(ctas, 1u << 20);
     rms_warp_kernel<kVectors, kResidual, kWeight><<<grid, warps_per_cta * 32, 0, stream>>>(
         static_cast<const uint4 *>(x), static_cast<const uint4 *>(residual), weight,
         static_cast<uint4 *>(y), static_cast<uint4 *>(h), rows, eps);
