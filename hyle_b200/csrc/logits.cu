@@ -433,11 +433,31 @@ __device__ __forceinline__ void cp_async_wait_all() { asm volatile("cp.async.wai
 
 constexpr size_t kRegStageBytes = static_cast<size_t>(kThreads) * kRegVectors * sizeof(float4);  // 80 KB
 
+// Fold one (maximum, sum relative to 2^(maximum log2e), index) entry per lane into the warp-wide
+// result.  Lanes without an entry pass (-inf, 0, none).  Fixed shuffle tree: every caller with the
+// same inputs gets the same bits.
+struct Combined {
+  float maximum;
+  float total;
+  uint32_t index;
+};
+__device__ __forceinline__ Combined combine(WarpEntry mine) {
+  Combined r;
+  r.maximum = warp_max_nan(mine.maximum);
+  const float row_c = __fmul_rn(r.maximum, kLog2e);
+  // an entry at -inf carries sum 0; its weight must not become 0 * inf
+  const float weight = mine.maximum == -CUDART_INF_F ? 0.0f : exp2_approx(__fmul_rn(mine.maximum, kLog2e) - row_c);
+  r.total = warp_sum(mine.sum * weight);
+  r.index = __reduce_min_sync(kFullMask, mine.maximum == r.maximum ? mine.index : kNoIndex);
+  return r;
+}
+
 template <int kMode>
 __global__ void __launch_bounds__(kThreads, 2)
 logits_regs_kernel(const LogitsParams p) {
   extern __shared__ __align__(16) float4 stage[];  // [kRegVectors][kThreads]: slot (j, t) belongs to thread t
-  __shared__ WarpEntry s_entry[2][kWarps];  // by row parity: one barrier per row
+  __shared__ WarpEntry s_entry[kWarps];  // this CTA's warps; read by warp 0 before the cluster barrier
+  __shared__ WarpEntry s_cta[2];         // this CTA's entry, by row parity; read by the peers after it
   cg::cluster_group cluster = cg::this_cluster();
   const unsigned rank = cluster.block_rank();
   const unsigned cluster_size = cluster.num_blocks();
@@ -504,41 +524,31 @@ logits_regs_kernel(const LogitsParams p) {
       if constexpr (kMode != kLogF32) x[j] = e;
     }
     const float warp_total = warp_sum(thread_sum);
-    if (lane == 0) s_entry[parity][warp] = WarpEntry{warp_max, warp_total, index, 0u};
+    if (lane == 0) s_entry[warp] = WarpEntry{warp_max, warp_total, index, 0u};
 
-    cluster.sync();  // the only barrier of the row: every warp of every CTA has published
-
-    // Combine all entries; every warp does it for itself (fixed order -> identical results).
-    // (Two sweeps over the entries instead of holding them: registers are full of the row.)
-    const unsigned entries = cluster_size * kWarps;
-    float maximum = neg_inf;
-#pragma unroll
-    for (int k = 0; k < kMaxCluster * kWarps / 32; ++k) {
-      const unsigned e = k * 32 + lane;
-      if (e < entries) maximum = max_nan(maximum, cluster.map_shared_rank(&s_entry[parity][e % kWarps], e / kWarps)->maximum);
+    // Two-level exchange.  Inside the CTA: warp 0 folds the 16 warp entries into one CTA entry.
+    // Across the cluster: after the barrier every warp reads the (at most eight) CTA entries, one
+    // per lane, through distributed shared memory and folds them itself -- eight small remote
+    // reads per warp.  (Letting every warp read every warp's entry costs 128 remote reads per
+    // warp and more than doubles the kernel time.)
+    __syncthreads();
+    if (warp == 0) {
+      const Combined cta = combine(lane < kWarps ? s_entry[lane] : WarpEntry{neg_inf, 0.0f, kNoIndex, 0u});
+      if (lane == 0) s_cta[parity] = WarpEntry{cta.maximum, cta.total, cta.index, 0u};
     }
-    maximum = warp_max_nan(maximum);
-    const float row_c = __fmul_rn(maximum, kLog2e);
-    float total = 0.0f;
-    uint32_t best_index = kNoIndex;
-#pragma unroll
-    for (int k = 0; k < kMaxCluster * kWarps / 32; ++k) {
-      const unsigned e = k * 32 + lane;
-      if (e < entries) {
-        const WarpEntry entry = *cluster.map_shared_rank(&s_entry[parity][e % kWarps], e / kWarps);
-        // an entry at -inf carries sum 0; its weight must not become 0 * inf
-        const float weight = entry.maximum == neg_inf ? 0.0f : exp2_approx(__fmul_rn(entry.maximum, kLog2e) - row_c);
-        total = fmaf(entry.sum, weight, total);
-        if (entry.maximum == maximum) best_index = min(best_index, entry.index);
-      }
-    }
-    total = warp_sum(total);
-    best_index = __reduce_min_sync(kFullMask, best_index);
+    cluster.sync();  // the only cluster barrier of the row: every CTA has published its entry
+    const Combined all = combine(lane < cluster_size ? *cluster.map_shared_rank(&s_cta[parity], lane)
+                                                     : WarpEntry{neg_inf, 0.0f, kNoIndex, 0u});
+    const float maximum = all.maximum, total = all.total, row_c = __fmul_rn(all.maximum, kLog2e);
+    const uint32_t best_index = all.index;
 
     const bool valid = maximum > neg_inf && maximum < CUDART_INF_F;  // false for NaN too
     const bool has_nan = maximum != maximum;
     const float nan = CUDART_NAN_F;
-    const float shift = valid ? maximum + logf(total) : nan;  // f32 log: within an ulp of float(log(double))
+    // total is relative to 2^row_c with row_c = fl(maximum * log2e); the rounding of that product
+    // (up to 3e-5 for |maximum| of a few hundred) is taken back out of the logarithm.
+    const float residual = fmaf(maximum, kLog2e, -row_c);
+    const float shift = valid ? maximum + (logf(total) - residual * 0.6931471805599453f) : nan;
     if (rank == 0 && warp == 0 && lane == 0) {
       if (p.lse != nullptr) p.lse[row] = shift;
       if (want_index && !has_nan) {
