@@ -20,7 +20,8 @@ REDUCE_SUM, REDUCE_MEAN, REDUCE_MINIMUM, REDUCE_MAXIMUM = 0, 1, 2, 3
 # enum hyle_b200_softmax_kind
 SOFTMAX, LOG_SOFTMAX = 0, 1
 # enum hyle_b200_result
-OK, INVALID_VALUE, NOT_SUPPORTED = 0, 1, 801
+OK, INVALID_VALUE, NOT_SUPPORTED, STATIC_SCRATCH_EXCEEDED = 0, 1, 801, 100001
+STATIC_MAX_VALUES = 1 << 31
 # enum hyle_b200_status_bits
 STATUS_INVALID_Q8_INPUT = 1
 
@@ -49,6 +50,7 @@ SIGNATURES = {
     "hyle_b200_sum_squares_workspace_bytes": (_u64, []),
     "hyle_b200_sum_squares_bf16": (_i, [_p, _p, _u64, _p, _p, _u64]),
     "hyle_b200_q8_0_roundtrip_bf16": (_i, [_p, _p, _u64, _p, _p, _p, _p, _p, _u64]),
+    "hyle_b200_q8_0_roundtrip_bf16_static": (_i, [_p, _p, _u64, _p, _p, _p, _p]),
 }
 
 _library = None

@@ -395,3 +395,77 @@ extern "C" int hyle_b200_q8_0_roundtrip_bf16(hyle_b200_stream_t stream, const vo
       sum_squares_out, status_word, workspace, aligned_to(blocks_out, 16));
   return launch_result();
 }
+
+// ------------------------------------------------------------------------------------------------
+// Round trip for callers that cannot allocate.
+//
+// Some hosts of this library never get to call cudaMalloc: code running inside a framework that
+// owns every byte of device memory through its own pool, a provider whose enqueue() contract
+// forbids allocation and that was handed no workspace, or a process that must not disturb a
+// memory budget fixed at start-up.  For them the per-CTA partial sums and the ticket counter of
+// the sum of squares live in the library image itself: a file-scope device array of fixed size,
+// resident on every GPU that loads the library until the process exits.
+//
+// The array bounds the launch: at most kStaticPartials CTAs, and the entry point accepts at most
+// HYLE_B200_STATIC_MAX_VALUES values per call.  All calls on a device share the one array, so two
+// calls whose kernels may run at the same time (different streams) race on it; calls ordered on
+// one stream are fine.  The array keeps what the previous call left behind, so the ticket counter
+// is cleared on the stream before every launch.
+// ------------------------------------------------------------------------------------------------
+namespace hb {
+namespace {
+
+constexpr int kStaticPartials = 1024;
+constexpr uint64_t kStaticScratchBytes = 64 + sizeof(double) * kStaticPartials;  // 8256 bytes
+static_assert(kStaticPartials <= kMaxPartials, "the kernel indexes partials by CTA");
+
+static __device__ __align__(256) unsigned char g_static_scratch[kStaticScratchBytes];
+
+// In host code `g_static_scratch` names a host-side shadow of the symbol, not device memory.  The
+// device address comes from cudaGetSymbolAddress, asked once per device with that device current.
+int static_scratch_address(void **address) {
+  constexpr int kMaxDevices = 64;
+  static void *cached[kMaxDevices] = {};
+  int device = 0;
+  cudaError_t error = cudaGetDevice(&device);
+  if (error != cudaSuccess) return static_cast<int>(error);
+  if (device < 0 || device >= kMaxDevices) return HYLE_B200_NOT_SUPPORTED;
+  if (cached[device] == nullptr) {
+    void *pointer = nullptr;
+    error = cudaGetSymbolAddress(&pointer, g_static_scratch);
+    if (error != cudaSuccess) return static_cast<int>(error);
+    if (pointer == nullptr) return HYLE_B200_NOT_SUPPORTED;
+    cached[device] = pointer;  // benign race: every thread stores the same address
+  }
+  *address = cached[device];
+  return HYLE_B200_OK;
+}
+
+}  // namespace
+}  // namespace hb
+
+extern "C" int hyle_b200_q8_0_roundtrip_bf16_static(hyle_b200_stream_t stream, const void *in,
+                                                    uint64_t count, void *blocks_out,
+                                                    void *decoded_bf16, double *sum_squares_out,
+                                                    uint32_t *status_word) {
+  if (count > HYLE_B200_STATIC_MAX_VALUES) return HYLE_B200_STATIC_SCRATCH_EXCEEDED;
+  if (in == nullptr && count != 0) return HYLE_B200_INVALID_VALUE;
+  if (blocks_out == nullptr || decoded_bf16 == nullptr || sum_squares_out == nullptr ||
+      count % 32 != 0 || !aligned_to(blocks_out, 2))
+    return HYLE_B200_INVALID_VALUE;
+  if (!aligned_to(in, 16) || !aligned_to(decoded_bf16, 16)) return HYLE_B200_NOT_SUPPORTED;
+  void *scratch = nullptr;
+  const int status = static_scratch_address(&scratch);
+  if (status != HYLE_B200_OK) return status;
+  auto s = reinterpret_cast<cudaStream_t>(stream);
+  // The ticket counter must start at zero whatever an earlier call (or an aborted one) left.
+  const cudaError_t cleared = cudaMemsetAsync(scratch, 0, 64, s);
+  if (cleared != cudaSuccess) return static_cast<int>(cleared);
+  const uint64_t blocks = count / 32;
+  const uint64_t tiles = (blocks + kTileBlocks - 1) / kTileBlocks;
+  const unsigned grid = clamp_grid(tiles, min(static_cast<uint64_t>(kStaticPartials), static_cast<uint64_t>(sm_count()) * 6));
+  q8_0_kernel<HYLE_B200_BF16, true, true, true><<<grid, kThreads, 0, s>>>(
+      in, blocks, static_cast<unsigned char *>(blocks_out), static_cast<unsigned short *>(decoded_bf16),
+      sum_squares_out, status_word, scratch, aligned_to(blocks_out, 16));
+  return launch_result();
+}

@@ -265,3 +265,27 @@ def q8_0_roundtrip(x: torch.Tensor, workspace: torch.Tensor, blocks: Optional[to
         _stream(), x.data_ptr(), x.numel(), blocks.data_ptr(), decoded.data_ptr(), sum_out.data_ptr(),
         _ptr(status), workspace.data_ptr(), workspace.numel()))
     return blocks, decoded, sum_out
+
+
+def q8_0_roundtrip_static(x: torch.Tensor, blocks: Optional[torch.Tensor] = None,
+                          decoded: Optional[torch.Tensor] = None, sum_out: Optional[torch.Tensor] = None,
+                          status: Optional[torch.Tensor] = None):
+    """`q8_0_roundtrip` without a workspace: the kernel's scratch is a fixed array inside the library.
+
+    For callers that must not allocate device memory.  At most ``abi.STATIC_MAX_VALUES`` values per
+    call; calls on one device share the scratch, so only stream-ordered calls are safe.  (The
+    outputs are still the caller's; pass them in to avoid torch allocating them here.)
+    """
+    _device_tensor(x, "x")
+    if x.dtype != torch.bfloat16 or x.numel() % 32:
+        raise ValueError("q8_0_roundtrip_static takes bf16 input with a multiple of 32 values")
+    if blocks is None:
+        blocks = torch.empty(q8_0_bytes(x.numel()), dtype=torch.uint8, device=x.device)
+    if decoded is None:
+        decoded = torch.empty_like(x)
+    if sum_out is None:
+        sum_out = torch.empty(1, dtype=torch.float64, device=x.device)
+    abi.check("hyle_b200_q8_0_roundtrip_bf16_static", abi.load().hyle_b200_q8_0_roundtrip_bf16_static(
+        _stream(), x.data_ptr(), x.numel(), blocks.data_ptr(), decoded.data_ptr(), sum_out.data_ptr(),
+        _ptr(status)))
+    return blocks, decoded, sum_out

@@ -47,7 +47,9 @@ typedef struct CUstream_st *hyle_b200_stream_t;
 enum hyle_b200_result {
   HYLE_B200_OK = 0,
   HYLE_B200_INVALID_VALUE = 1,   /* cudaErrorInvalidValue */
-  HYLE_B200_NOT_SUPPORTED = 801  /* cudaErrorNotSupported */
+  HYLE_B200_NOT_SUPPORTED = 801, /* cudaErrorNotSupported */
+  /* hyle_b200_q8_0_roundtrip_bf16_static: count is above HYLE_B200_STATIC_MAX_VALUES. */
+  HYLE_B200_STATIC_SCRATCH_EXCEEDED = 100001
 };
 
 /* Storage types, numbered independently of hyle::compute::DataType. */
@@ -222,6 +224,33 @@ HYLE_B200_API int hyle_b200_q8_0_roundtrip_bf16(hyle_b200_stream_t stream, const
                                                 void *decoded_bf16, double *sum_squares_out,
                                                 uint32_t *status_word, void *workspace,
                                                 uint64_t workspace_bytes);
+
+/* ---------------------------------------------------------------------------------------------
+ * The same round trip for callers that cannot allocate device memory.  (No counterpart in the
+ * reference: its providers always receive caller-owned workspace.)
+ *
+ * Who needs it: code embedded in a host that owns all device memory through its own pool, a
+ * provider whose enqueue path may not allocate and was given no workspace, or a process whose
+ * memory budget is fixed at start-up.  Instead of a caller-supplied workspace the kernel's scratch
+ * (per-CTA partial sums and a ticket counter, 8256 bytes) is a fixed array inside the library image;
+ * every GPU that loads the library holds it until the process exits.  The call performs no
+ * cudaMalloc/cudaFree and uses no allocating library routine.
+ *
+ * Limits and rules:
+ *  - at most HYLE_B200_STATIC_MAX_VALUES values per call; more returns
+ *    HYLE_B200_STATIC_SCRATCH_EXCEEDED and launches nothing;
+ *  - the first call on each device looks up the array's device address (cudaGetSymbolAddress,
+ *    with that device current); make that first call outside any stream capture;
+ *  - all calls on a device share the array: calls that can overlap on the GPU (different
+ *    streams without ordering) race on it; stream-ordered calls are safe, each one clears the
+ *    counter on its stream before launching.
+ * Inputs, outputs, results and error codes are otherwise those of hyle_b200_q8_0_roundtrip_bf16.
+ */
+#define HYLE_B200_STATIC_MAX_VALUES (UINT64_C(1) << 31)
+HYLE_B200_API int hyle_b200_q8_0_roundtrip_bf16_static(hyle_b200_stream_t stream, const void *in,
+                                                       uint64_t count, void *blocks_out,
+                                                       void *decoded_bf16, double *sum_squares_out,
+                                                       uint32_t *status_word);
 
 #ifdef __cplusplus
 }
