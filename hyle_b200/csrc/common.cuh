@@ -102,6 +102,34 @@ __device__ __forceinline__ float warp_min_nan(float v) {
 // ---- launch helpers ----------------------------------------------------------------------------
 inline int launch_result() { return static_cast<int>(cudaPeekAtLastError()); }
 
+// Programmatic dependent launch.  Most of these operators run for 10-30 us, where the few
+// microseconds between the end of one grid and the first CTA of the next are a visible fraction.
+// Every kernel is launched with programmatic stream serialisation allowed and begins with
+// grid_dependency_sync(): the CTAs of the next grid in the stream may be placed on SMs while the
+// previous grid drains, but none of them touches global memory before the previous grid has
+// completed and flushed (griddepcontrol.wait).  With a predecessor that never signals, or without
+// the launch attribute, both instructions do nothing, so stream order is unchanged in every case.
+__device__ __forceinline__ void grid_dependency_sync() {
+  asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
+  asm volatile("griddepcontrol.wait;" ::: "memory");
+}
+
+template <class... Params, class... Args>
+inline int launch(void (*kernel)(Params...), dim3 grid, dim3 block, size_t shared_bytes, cudaStream_t stream,
+                  Args &&...args) {
+  cudaLaunchConfig_t config{};
+  config.gridDim = grid;
+  config.blockDim = block;
+  config.dynamicSmemBytes = shared_bytes;
+  config.stream = stream;
+  cudaLaunchAttribute attribute{};
+  attribute.id = cudaLaunchAttributeProgrammaticStreamSerialization;
+  attribute.val.programmaticStreamSerializationAllowed = 1;
+  config.attrs = &attribute;
+  config.numAttrs = 1;
+  return static_cast<int>(cudaLaunchKernelEx(&config, kernel, static_cast<Params>(args)...));
+}
+
 inline unsigned clamp_grid(uint64_t blocks, uint64_t limit) {
   if (blocks < 1) blocks = 1;
   return static_cast<unsigned>(blocks < limit ? blocks : limit);

@@ -79,6 +79,7 @@ __global__ void __launch_bounds__(kThreads)
 binary_flat_kernel(const typename Storage<kDtype>::Vec *lhs,
                    const typename Storage<kDtype>::Vec *__restrict__ rhs,
                    typename Storage<kDtype>::Vec *out, uint64_t vectors) {
+  grid_dependency_sync();
   using Vec = typename Storage<kDtype>::Vec;
   const uint64_t stride = static_cast<uint64_t>(gridDim.x) * kThreads;
   uint64_t i = static_cast<uint64_t>(blockIdx.x) * kThreads + threadIdx.x;
@@ -107,6 +108,7 @@ binary_rowvec_kernel(const typename Storage<kDtype>::Vec *lhs,
                      const typename Storage<kDtype>::Vec *__restrict__ rhs,
                      typename Storage<kDtype>::Vec *out, uint64_t rows,
                      uint32_t row_vectors) {
+  grid_dependency_sync();
   using Vec = typename Storage<kDtype>::Vec;
   const uint32_t column = blockIdx.x * kThreads + threadIdx.x;
   if (column >= row_vectors) return;
@@ -133,6 +135,7 @@ binary_scalar_kernel(const typename Storage<kDtype>::Scalar *lhs,
                      const typename Storage<kDtype>::Scalar *__restrict__ rhs,
                      typename Storage<kDtype>::Scalar *out, uint64_t count,
                      uint64_t period) {
+  grid_dependency_sync();
   const uint64_t stride = static_cast<uint64_t>(gridDim.x) * kThreads;
   for (uint64_t i = static_cast<uint64_t>(blockIdx.x) * kThreads + threadIdx.x; i < count;
        i += stride) {
@@ -160,9 +163,8 @@ int launch_binary(cudaStream_t stream, const void *lhs, const void *rhs, void *o
   if (vector_ok && period == count) {
     const uint64_t vectors = count / kLanes;
     const unsigned grid = clamp_grid((vectors + kThreads * kUnroll - 1) / (kThreads * kUnroll), resident);
-    binary_flat_kernel<kKind, kDtype><<<grid, kThreads, 0, stream>>>(
+    return launch(binary_flat_kernel<kKind, kDtype>, dim3(grid), dim3(kThreads), 0, stream, 
         static_cast<const Vec *>(lhs), static_cast<const Vec *>(rhs), static_cast<Vec *>(out), vectors);
-    return launch_result();
   }
   const uint64_t row_vectors = period / kLanes;
   if (vector_ok && row_vectors >= 64 && row_vectors <= 0x7fffffffull) {
@@ -174,16 +176,14 @@ int launch_binary(cudaStream_t stream, const void *lhs, const void *rhs, void *o
     if (groups > useful) groups = useful;
     if (groups > 65535) groups = 65535;
     if (groups < 1) groups = 1;
-    binary_rowvec_kernel<kKind, kDtype><<<dim3(tiles, static_cast<unsigned>(groups)), kThreads, 0, stream>>>(
+    return launch(binary_rowvec_kernel<kKind, kDtype>, dim3(dim3(tiles, static_cast<unsigned>(groups))), dim3(kThreads), 0, stream, 
         static_cast<const Vec *>(lhs), static_cast<const Vec *>(rhs), static_cast<Vec *>(out), rows,
         static_cast<uint32_t>(row_vectors));
-    return launch_result();
   }
   const unsigned grid = clamp_grid((count + kThreads - 1) / kThreads, resident);
-  binary_scalar_kernel<kKind, kDtype><<<grid, kThreads, 0, stream>>>(
+  return launch(binary_scalar_kernel<kKind, kDtype>, dim3(grid), dim3(kThreads), 0, stream, 
       static_cast<const Scalar *>(lhs), static_cast<const Scalar *>(rhs), static_cast<Scalar *>(out),
       count, period);
-  return launch_result();
 }
 
 // ---- SwiGLU --------------------------------------------------------------------------------------
@@ -221,6 +221,7 @@ __device__ __forceinline__ uint4 swiglu_vec(uint4 g, uint4 u) {
 __global__ void __launch_bounds__(kThreads)
 swiglu_flat_kernel(const uint4 *__restrict__ gate, const uint4 *__restrict__ up,
                    uint4 *__restrict__ out, uint64_t vectors) {
+  grid_dependency_sync();
   const uint64_t stride = static_cast<uint64_t>(gridDim.x) * kThreads;
   uint64_t i = static_cast<uint64_t>(blockIdx.x) * kThreads + threadIdx.x;
   for (; i + (kUnroll - 1) * stride < vectors; i += kUnroll * stride) {
@@ -241,6 +242,7 @@ __global__ void __launch_bounds__(kThreads)
 swiglu_rows_kernel(const uint4 *__restrict__ gate, const uint4 *__restrict__ up,
                    uint4 *__restrict__ out, uint64_t rows, uint32_t row_vectors,
                    uint64_t gate_stride_vectors, uint64_t up_stride_vectors) {
+  grid_dependency_sync();
   const uint32_t column = blockIdx.x * kThreads + threadIdx.x;
   if (column >= row_vectors) return;
   const uint64_t step = gridDim.y;
@@ -267,6 +269,7 @@ __global__ void __launch_bounds__(kThreads)
 swiglu_scalar_kernel(const unsigned short *__restrict__ gate, const unsigned short *__restrict__ up,
                      unsigned short *__restrict__ out, uint64_t rows, uint64_t cols,
                      uint64_t gate_stride, uint64_t up_stride) {
+  grid_dependency_sync();
   const uint64_t stride = static_cast<uint64_t>(gridDim.x) * kThreads;
   const uint64_t count = rows * cols;
   for (uint64_t i = static_cast<uint64_t>(blockIdx.x) * kThreads + threadIdx.x; i < count;
@@ -281,6 +284,7 @@ swiglu_scalar_kernel(const unsigned short *__restrict__ gate, const unsigned sho
 // ---- Cast f32 -> bf16 -----------------------------------------------------------------------------
 __global__ void __launch_bounds__(kThreads)
 cast_f32_bf16_kernel(const float4 *__restrict__ in, uint4 *__restrict__ out, uint64_t vectors) {
+  grid_dependency_sync();
   const uint64_t stride = static_cast<uint64_t>(gridDim.x) * kThreads;
   uint64_t i = static_cast<uint64_t>(blockIdx.x) * kThreads + threadIdx.x;
   for (; i + (kUnroll - 1) * stride < vectors; i += kUnroll * stride) {
@@ -306,6 +310,7 @@ cast_f32_bf16_kernel(const float4 *__restrict__ in, uint4 *__restrict__ out, uin
 __global__ void __launch_bounds__(kThreads)
 cast_f32_bf16_scalar_kernel(const float *__restrict__ in, unsigned short *__restrict__ out,
                             uint64_t count) {
+  grid_dependency_sync();
   const uint64_t stride = static_cast<uint64_t>(gridDim.x) * kThreads;
   for (uint64_t i = static_cast<uint64_t>(blockIdx.x) * kThreads + threadIdx.x; i < count; i += stride)
     out[i] = f32_to_bf16(in[i]);
@@ -349,10 +354,9 @@ extern "C" int hyle_b200_swiglu_bf16(hyle_b200_stream_t stream, const void *gate
   if (vector_ok && gate_row_stride == cols && up_row_stride == cols) {
     const uint64_t vectors = rows * cols / 8;
     const unsigned grid = clamp_grid((vectors + kThreads * kUnroll - 1) / (kThreads * kUnroll), resident);
-    swiglu_flat_kernel<<<grid, kThreads, 0, s>>>(static_cast<const uint4 *>(gate),
+    return launch(swiglu_flat_kernel, dim3(grid), dim3(kThreads), 0, s, static_cast<const uint4 *>(gate),
                                                  static_cast<const uint4 *>(up),
                                                  static_cast<uint4 *>(out), vectors);
-    return launch_result();
   }
   if (vector_ok && cols / 8 <= 0x7fffffffull) {
     const uint64_t row_vectors = cols / 8;
@@ -362,17 +366,15 @@ extern "C" int hyle_b200_swiglu_bf16(hyle_b200_stream_t stream, const void *gate
     if (groups > useful) groups = useful;
     if (groups > 65535) groups = 65535;
     if (groups < 1) groups = 1;
-    swiglu_rows_kernel<<<dim3(tiles, static_cast<unsigned>(groups)), kThreads, 0, s>>>(
+    return launch(swiglu_rows_kernel, dim3(dim3(tiles, static_cast<unsigned>(groups))), dim3(kThreads), 0, s, 
         static_cast<const uint4 *>(gate), static_cast<const uint4 *>(up), static_cast<uint4 *>(out),
         rows, static_cast<uint32_t>(row_vectors), gate_row_stride / 8, up_row_stride / 8);
-    return launch_result();
   }
   const unsigned grid = clamp_grid((rows * cols + kThreads - 1) / kThreads, resident);
-  swiglu_scalar_kernel<<<grid, kThreads, 0, s>>>(static_cast<const unsigned short *>(gate),
+  return launch(swiglu_scalar_kernel, dim3(grid), dim3(kThreads), 0, s, static_cast<const unsigned short *>(gate),
                                                  static_cast<const unsigned short *>(up),
                                                  static_cast<unsigned short *>(out), rows, cols,
                                                  gate_row_stride, up_row_stride);
-  return launch_result();
 }
 
 extern "C" int hyle_b200_cast_f32_to_bf16(hyle_b200_stream_t stream, const float *in,
@@ -384,11 +386,9 @@ extern "C" int hyle_b200_cast_f32_to_bf16(hyle_b200_stream_t stream, const float
   if (aligned_to(in, 16) && aligned_to(out_bf16, 16) && count % 8 == 0) {
     const uint64_t vectors = count / 8;
     const unsigned grid = clamp_grid((vectors + kThreads * kUnroll - 1) / (kThreads * kUnroll), resident);
-    cast_f32_bf16_kernel<<<grid, kThreads, 0, s>>>(reinterpret_cast<const float4 *>(in),
+    return launch(cast_f32_bf16_kernel, dim3(grid), dim3(kThreads), 0, s, reinterpret_cast<const float4 *>(in),
                                                    static_cast<uint4 *>(out_bf16), vectors);
-    return launch_result();
   }
   const unsigned grid = clamp_grid((count + kThreads - 1) / kThreads, resident);
-  cast_f32_bf16_scalar_kernel<<<grid, kThreads, 0, s>>>(in, static_cast<unsigned short *>(out_bf16), count);
-  return launch_result();
+  return launch(cast_f32_bf16_scalar_kernel, dim3(grid), dim3(kThreads), 0, s, in, static_cast<unsigned short *>(out_bf16), count);
 }

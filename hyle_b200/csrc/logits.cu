@@ -114,6 +114,7 @@ __device__ __noinline__ void rescan_argmax(const float *whole, uint32_t cols, in
 template <bool kVec>
 __global__ void __launch_bounds__(kThreads)
 argmax_kernel(const LogitsParams p) {
+  grid_dependency_sync();
   __shared__ Best s_warp_best[kWarps];
   __shared__ Best s_cta_best[2];  // by row parity; read by the peers after the barrier
   __shared__ Best s_row_best;
@@ -195,6 +196,7 @@ struct SumSlot {
 template <int kMode, bool kVec>
 __global__ void __launch_bounds__(kThreads)
 logits_kernel(const LogitsParams p) {
+  grid_dependency_sync();
   extern __shared__ __align__(16) float slice_data[];
   __shared__ float s_warp_max[kWarps];
   __shared__ double s_warp_sum[kWarps];
@@ -455,6 +457,7 @@ __device__ __forceinline__ Combined combine(WarpEntry mine) {
 template <int kMode>
 __global__ void __launch_bounds__(kThreads, 2)
 logits_regs_kernel(const LogitsParams p) {
+  grid_dependency_sync();
   extern __shared__ __align__(16) float4 stage[];  // [kRegVectors][kThreads]: slot (j, t) belongs to thread t
   __shared__ WarpEntry s_entry[kWarps];  // this CTA's warps; read by warp 0 before the cluster barrier
   __shared__ WarpEntry s_cta[2];         // this CTA's entry, by row parity; read by the peers after it
@@ -615,13 +618,15 @@ int launch_cluster_kernel(cudaStream_t stream, void (*kernel)(const LogitsParams
   config.blockDim = dim3(kThreads);
   config.dynamicSmemBytes = shared;
   config.stream = stream;
-  cudaLaunchAttribute attribute{};
-  attribute.id = cudaLaunchAttributeClusterDimension;
-  attribute.val.clusterDim.x = cluster;
-  attribute.val.clusterDim.y = 1;
-  attribute.val.clusterDim.z = 1;
-  config.attrs = &attribute;
-  config.numAttrs = 1;
+  cudaLaunchAttribute attributes[2]{};
+  attributes[0].id = cudaLaunchAttributeClusterDimension;
+  attributes[0].val.clusterDim.x = cluster;
+  attributes[0].val.clusterDim.y = 1;
+  attributes[0].val.clusterDim.z = 1;
+  attributes[1].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+  attributes[1].val.programmaticStreamSerializationAllowed = 1;
+  config.attrs = attributes;
+  config.numAttrs = 2;
   return static_cast<int>(cudaLaunchKernelEx(&config, kernel, p));
 }
 

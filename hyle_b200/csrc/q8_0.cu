@@ -132,6 +132,7 @@ __global__ void __launch_bounds__(kThreads)
 q8_0_kernel(const void *__restrict__ in, uint64_t blocks, unsigned char *__restrict__ blocks_out,
             unsigned short *__restrict__ decoded, double *sum_out, uint32_t *status_word,
             void *workspace, int out_aligned) {
+  grid_dependency_sync();
   __shared__ __align__(16) unsigned char staged[2][kTileBytes];
   const int t = threadIdx.x;
   const int sub = t & 3;  // which quarter of a block this lane holds
@@ -238,6 +239,7 @@ q8_0_kernel(const void *__restrict__ in, uint64_t blocks, unsigned char *__restr
 __global__ void __launch_bounds__(kThreads)
 q8_0_decode_kernel(const unsigned char *__restrict__ blocks_in, uint64_t blocks,
                    unsigned short *__restrict__ decoded, int in_aligned) {
+  grid_dependency_sync();
   __shared__ __align__(16) unsigned char staged[2][kTileBytes];
   const int t = threadIdx.x, sub = t & 3;
   const uint64_t tiles = (blocks + kTileBlocks - 1) / kTileBlocks;
@@ -287,6 +289,7 @@ __global__ void __launch_bounds__(kThreads)
 sum_squares_bf16_kernel(const uint4 *__restrict__ in, uint64_t vectors,
                         const unsigned short *__restrict__ tail, uint32_t tail_count, double *sum_out,
                         void *workspace) {
+  grid_dependency_sync();
   const uint64_t stride = static_cast<uint64_t>(gridDim.x) * kThreads;
   uint64_t i = static_cast<uint64_t>(blockIdx.x) * kThreads + threadIdx.x;
   double sum = 0.0;
@@ -339,15 +342,16 @@ extern "C" int hyle_b200_q8_0_encode(hyle_b200_stream_t stream, int dtype, const
   const unsigned grid = q8_grid(blocks);
   const int out_aligned = aligned_to(blocks_out, 16);
   auto *out = static_cast<unsigned char *>(blocks_out);
+  int launch_status = HYLE_B200_OK;
   if (dtype == HYLE_B200_BF16)
-    q8_0_kernel<HYLE_B200_BF16, true, false, false><<<grid, kThreads, 0, s>>>(in, blocks, out, nullptr, nullptr, status_word, nullptr, out_aligned);
+    launch_status = launch(q8_0_kernel<HYLE_B200_BF16, true, false, false>, dim3(grid), dim3(kThreads), 0, s, in, blocks, out, nullptr, nullptr, status_word, nullptr, out_aligned);
   else if (dtype == HYLE_B200_F16)
-    q8_0_kernel<HYLE_B200_F16, true, false, false><<<grid, kThreads, 0, s>>>(in, blocks, out, nullptr, nullptr, status_word, nullptr, out_aligned);
+    launch_status = launch(q8_0_kernel<HYLE_B200_F16, true, false, false>, dim3(grid), dim3(kThreads), 0, s, in, blocks, out, nullptr, nullptr, status_word, nullptr, out_aligned);
   else if (dtype == HYLE_B200_F32)
-    q8_0_kernel<HYLE_B200_F32, true, false, false><<<grid, kThreads, 0, s>>>(in, blocks, out, nullptr, nullptr, status_word, nullptr, out_aligned);
+    launch_status = launch(q8_0_kernel<HYLE_B200_F32, true, false, false>, dim3(grid), dim3(kThreads), 0, s, in, blocks, out, nullptr, nullptr, status_word, nullptr, out_aligned);
   else
     return HYLE_B200_INVALID_VALUE;
-  return launch_result();
+  return launch_status;
 }
 
 extern "C" int hyle_b200_q8_0_decode_bf16(hyle_b200_stream_t stream, const void *blocks,
@@ -357,10 +361,9 @@ extern "C" int hyle_b200_q8_0_decode_bf16(hyle_b200_stream_t stream, const void 
     return HYLE_B200_INVALID_VALUE;
   if (!aligned_to(out_bf16, 16)) return HYLE_B200_NOT_SUPPORTED;
   const uint64_t n = count / 32;
-  q8_0_decode_kernel<<<q8_grid(n), kThreads, 0, reinterpret_cast<cudaStream_t>(stream)>>>(
+  return launch(q8_0_decode_kernel, dim3(q8_grid(n)), dim3(kThreads), 0, reinterpret_cast<cudaStream_t>(stream), 
       static_cast<const unsigned char *>(blocks), n, static_cast<unsigned short *>(out_bf16),
       aligned_to(blocks, 16));
-  return launch_result();
 }
 
 extern "C" int hyle_b200_sum_squares_bf16(hyle_b200_stream_t stream, const void *in, uint64_t count,
@@ -373,10 +376,9 @@ extern "C" int hyle_b200_sum_squares_bf16(hyle_b200_stream_t stream, const void 
   const uint32_t tail = static_cast<uint32_t>(count % 8);
   const unsigned grid = clamp_grid((vectors + kThreads * 4 - 1) / (kThreads * 4),
                                    min(static_cast<uint64_t>(kMaxPartials), static_cast<uint64_t>(sm_count()) * 8));
-  sum_squares_bf16_kernel<<<grid, kThreads, 0, reinterpret_cast<cudaStream_t>(stream)>>>(
+  return launch(sum_squares_bf16_kernel, dim3(grid), dim3(kThreads), 0, reinterpret_cast<cudaStream_t>(stream), 
       static_cast<const uint4 *>(in), vectors, static_cast<const unsigned short *>(in) + vectors * 8, tail,
       sum_out, workspace);
-  return launch_result();
 }
 
 extern "C" int hyle_b200_q8_0_roundtrip_bf16(hyle_b200_stream_t stream, const void *in,
@@ -390,10 +392,9 @@ extern "C" int hyle_b200_q8_0_roundtrip_bf16(hyle_b200_stream_t stream, const vo
     return HYLE_B200_INVALID_VALUE;
   if (!aligned_to(in, 16) || !aligned_to(decoded_bf16, 16)) return HYLE_B200_NOT_SUPPORTED;
   const uint64_t blocks = count / 32;
-  q8_0_kernel<HYLE_B200_BF16, true, true, true><<<q8_grid(blocks), kThreads, 0, reinterpret_cast<cudaStream_t>(stream)>>>(
+  return launch(q8_0_kernel<HYLE_B200_BF16, true, true, true>, dim3(q8_grid(blocks)), dim3(kThreads), 0, reinterpret_cast<cudaStream_t>(stream), 
       in, blocks, static_cast<unsigned char *>(blocks_out), static_cast<unsigned short *>(decoded_bf16),
       sum_squares_out, status_word, workspace, aligned_to(blocks_out, 16));
-  return launch_result();
 }
 
 // ------------------------------------------------------------------------------------------------
@@ -464,8 +465,7 @@ extern "C" int hyle_b200_q8_0_roundtrip_bf16_static(hyle_b200_stream_t stream, c
   const uint64_t blocks = count / 32;
   const uint64_t tiles = (blocks + kTileBlocks - 1) / kTileBlocks;
   const unsigned grid = clamp_grid(tiles, min(static_cast<uint64_t>(kStaticPartials), static_cast<uint64_t>(sm_count()) * 6));
-  q8_0_kernel<HYLE_B200_BF16, true, true, true><<<grid, kThreads, 0, s>>>(
+  return launch(q8_0_kernel<HYLE_B200_BF16, true, true, true>, dim3(grid), dim3(kThreads), 0, s, 
       in, blocks, static_cast<unsigned char *>(blocks_out), static_cast<unsigned short *>(decoded_bf16),
       sum_squares_out, status_word, scratch, aligned_to(blocks_out, 16));
-  return launch_result();
 }

@@ -55,6 +55,7 @@ struct RowAcc {
 // aligned pointers), scalar accesses otherwise.
 template <int kSlots, bool kVec, int kOp>
 __global__ void __launch_bounds__(kThreads) row_f32_kernel(const RowF32Params p) {
+  grid_dependency_sync();
   __shared__ float s_sum[2][kWarps], s_max[2][kWarps], s_min[2][kWarps];
   const int t = threadIdx.x, lane = t & 31, warp = t >> 5;
   const uint64_t cols = p.cols;
@@ -136,13 +137,14 @@ int launch_row_f32(cudaStream_t stream, const RowF32Params &p) {
                        (p.c == nullptr || aligned_to(p.c, 16)) && p.cols % 4 == 0;
   // 48-64 registers per thread: five to eight CTAs share an SM.
   const unsigned grid = clamp_grid(p.rows, static_cast<uint64_t>(sm_count()) * 8);
-  if (aligned && p.cols == 1024) row_f32_kernel<1, true, kOp><<<grid, kThreads, 0, stream>>>(p);
-  else if (aligned && p.cols == 2048) row_f32_kernel<2, true, kOp><<<grid, kThreads, 0, stream>>>(p);
-  else if (aligned && p.cols == 4096) row_f32_kernel<4, true, kOp><<<grid, kThreads, 0, stream>>>(p);
-  else if (aligned && p.cols == 8192) row_f32_kernel<8, true, kOp><<<grid, kThreads, 0, stream>>>(p);
-  else if (aligned) row_f32_kernel<0, true, kOp><<<grid, kThreads, 0, stream>>>(p);
-  else row_f32_kernel<0, false, kOp><<<grid, kThreads, 0, stream>>>(p);
-  return launch_result();
+  int launch_status = HYLE_B200_OK;
+  if (aligned && p.cols == 1024) launch_status = launch(row_f32_kernel<1, true, kOp>, dim3(grid), dim3(kThreads), 0, stream, p);
+  else if (aligned && p.cols == 2048) launch_status = launch(row_f32_kernel<2, true, kOp>, dim3(grid), dim3(kThreads), 0, stream, p);
+  else if (aligned && p.cols == 4096) launch_status = launch(row_f32_kernel<4, true, kOp>, dim3(grid), dim3(kThreads), 0, stream, p);
+  else if (aligned && p.cols == 8192) launch_status = launch(row_f32_kernel<8, true, kOp>, dim3(grid), dim3(kThreads), 0, stream, p);
+  else if (aligned) launch_status = launch(row_f32_kernel<0, true, kOp>, dim3(grid), dim3(kThreads), 0, stream, p);
+  else launch_status = launch(row_f32_kernel<0, false, kOp>, dim3(grid), dim3(kThreads), 0, stream, p);
+  return launch_status;
 }
 
 // ================================================================================================
@@ -200,6 +202,7 @@ template <int kVectors, bool kResidual, int kWeight>
 __global__ void __launch_bounds__(kThreads)
 rms_warp_kernel(const uint4 *x, const uint4 *residual, const void *__restrict__ weight, uint4 *y,
                 uint4 *h_out, uint64_t rows, float eps) {
+  grid_dependency_sync();
   constexpr uint32_t kHidden = kVectors * 256;
   const int lane = threadIdx.x & 31;
   const uint64_t warps = static_cast<uint64_t>(gridDim.x) * (blockDim.x >> 5);
@@ -243,6 +246,7 @@ __global__ void __launch_bounds__(kThreads)
 rms_cta_kernel(const unsigned short *x, const unsigned short *residual,
                const void *__restrict__ weight, unsigned short *y, unsigned short *h_out,
                uint64_t rows, uint32_t hidden, float eps) {
+  grid_dependency_sync();
   extern __shared__ __align__(16) unsigned char staged_bytes[];
   __shared__ float s_partial[2][kWarps];
   unsigned short *staged = reinterpret_cast<unsigned short *>(staged_bytes);
@@ -311,10 +315,9 @@ int launch_rms(cudaStream_t stream, const void *x, const void *residual, const v
     if (rows < static_cast<uint64_t>(sms) * 2) warps_per_cta = 1;
     const uint64_t ctas = (rows + warps_per_cta - 1) / warps_per_cta;
     const unsigned grid = clamp_grid(ctas, 1u << 20);
-    rms_warp_kernel<kVectors, kResidual, kWeight><<<grid, warps_per_cta * 32, 0, stream>>>(
+    return launch(rms_warp_kernel<kVectors, kResidual, kWeight>, dim3(grid), dim3(warps_per_cta * 32), 0, stream, 
         static_cast<const uint4 *>(x), static_cast<const uint4 *>(residual), weight,
         static_cast<uint4 *>(y), static_cast<uint4 *>(h), rows, eps);
-    return launch_result();
   };
   if (aligned && hidden == 256) return warp_launch(std::integral_constant<int, 1>{});
   if (aligned && hidden == 512) return warp_launch(std::integral_constant<int, 2>{});
@@ -323,22 +326,23 @@ int launch_rms(cudaStream_t stream, const void *x, const void *residual, const v
   if (hidden > kMaxStagedHidden) return HYLE_B200_NOT_SUPPORTED;
   const size_t staged = (static_cast<size_t>(hidden) * 2 + 15) & ~static_cast<size_t>(15);
   const unsigned grid = clamp_grid(rows, static_cast<uint64_t>(sms) * 4);
+  int launch_status = HYLE_B200_OK;
   if (aligned) {
     auto kernel = rms_cta_kernel<true, kResidual, kWeight>;
     if (staged > 48 * 1024) cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, 64 * 1024);
-    kernel<<<grid, kThreads, staged, stream>>>(
+    launch_status = launch(kernel, dim3(grid), dim3(kThreads), staged, stream, 
         static_cast<const unsigned short *>(x), static_cast<const unsigned short *>(residual), weight,
         static_cast<unsigned short *>(y), static_cast<unsigned short *>(h), rows,
         static_cast<uint32_t>(hidden), eps);
   } else {
     auto kernel = rms_cta_kernel<false, kResidual, kWeight>;
     if (staged > 48 * 1024) cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, 64 * 1024);
-    kernel<<<grid, kThreads, staged, stream>>>(
+    launch_status = launch(kernel, dim3(grid), dim3(kThreads), staged, stream, 
         static_cast<const unsigned short *>(x), static_cast<const unsigned short *>(residual), weight,
         static_cast<unsigned short *>(y), static_cast<unsigned short *>(h), rows,
         static_cast<uint32_t>(hidden), eps);
   }
-  return launch_result();
+  return launch_status;
 }
 
 template <bool kResidual>
