@@ -47,49 +47,77 @@ def hbm_peak():
 
 
 class ClockSampler:
-    """nvidia-smi clocks and throttle reasons, sampled every 200 ms while the timed region runs."""
+    """SM clock and throttle reasons sampled every few milliseconds while the timed region runs.
 
-    QUERY = ("index,clocks.sm,clocks.max.sm,power.draw,clocks_event_reasons.active,"
-             "clocks_event_reasons.hw_slowdown,clocks_event_reasons.hw_thermal_slowdown,"
-             "clocks_event_reasons.sw_thermal_slowdown,clocks_event_reasons.sw_power_cap")
+    Reads only (NVML queries); nothing about the GPU is changed.  Falls back to one `nvidia-smi`
+    query when the NVML binding is missing.
+    """
 
-    def __init__(self, device_index: int):
+    REASONS = {  # nvmlClocksEventReasons bits
+        0x0000000000000004: "sw_power_cap",
+        0x0000000000000008: "hw_slowdown",
+        0x0000000000000020: "sw_thermal_slowdown",
+        0x0000000000000040: "hw_thermal_slowdown",
+    }
+
+    def __init__(self, device_index: int, period_s: float = 0.005):
         self.device_index = device_index
-        self.process = None
+        self.period_s = period_s
+        self.samples, self.reason_bits, self.max_clock = [], 0, None
+        self._stop = None
+        self._thread = None
+        self._nvml = None
+
+    def _physical_index(self) -> int:
+        visible = os.environ.get("CUDA_VISIBLE_DEVICES")
+        if visible:
+            entries = [e.strip() for e in visible.split(",") if e.strip()]
+            if self.device_index < len(entries) and entries[self.device_index].isdigit():
+                return int(entries[self.device_index])
+        return self.device_index
 
     def start(self):
+        import threading
         try:
-            self.process = subprocess.Popen(
-                ["nvidia-smi", f"--query-gpu={self.QUERY}", "--format=csv,noheader,nounits", "-lms", "200",
-                 "-i", str(self.device_index)], stdout=subprocess.PIPE, stderr=subprocess.DEVNULL, text=True)
-        except OSError:
-            self.process = None
+            import pynvml
+            pynvml.nvmlInit()
+            handle = pynvml.nvmlDeviceGetHandleByIndex(self._physical_index())
+            self.max_clock = float(pynvml.nvmlDeviceGetMaxClockInfo(handle, pynvml.NVML_CLOCK_SM))
+        except Exception:
+            self._nvml = None
+            return
+        self._nvml = pynvml
+        self._stop = threading.Event()
+
+        def loop():
+            while not self._stop.is_set():
+                try:
+                    self.samples.append(float(pynvml.nvmlDeviceGetClockInfo(handle, pynvml.NVML_CLOCK_SM)))
+                    self.reason_bits |= int(pynvml.nvmlDeviceGetCurrentClocksEventReasons(handle))
+                except Exception:
+                    pass
+                self._stop.wait(self.period_s)
+
+        self._thread = threading.Thread(target=loop, daemon=True)
+        self._thread.start()
 
     def stop(self):
-        if self.process is None:
-            return {"sm_mhz": None, "sm_max_mhz": None, "reasons": ["nvidia-smi unavailable"]}
-        self.process.terminate()
+        if self._nvml is None:
+            return self._smi_once()
+        self._stop.set()
+        self._thread.join(timeout=2)
+        reasons = sorted(name for bit, name in self.REASONS.items() if self.reason_bits & bit)
+        return {"sm_mhz": statistics.median(self.samples) if self.samples else None, "sm_max_mhz": self.max_clock,
+                "reasons": reasons, "samples": len(self.samples), "source": "nvml"}
+
+    def _smi_once(self):
         try:
-            out, _ = self.process.communicate(timeout=5)
-        except subprocess.TimeoutExpired:
-            self.process.kill()
-            out, _ = self.process.communicate()
-        clocks, max_clock, reasons = [], None, set()
-        names = ["hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap"]
-        for line in out.strip().splitlines():
-            parts = [p.strip() for p in line.split(",")]
-            if len(parts) < 9:
-                continue
-            try:
-                clocks.append(float(parts[1]))
-                max_clock = float(parts[2])
-            except ValueError:
-                continue
-            for name, flag in zip(names, parts[5:9]):
-                if flag.lower().startswith("active"):
-                    reasons.add(name)
-        return {"sm_mhz": statistics.median(clocks) if clocks else None, "sm_max_mhz": max_clock,
-                "reasons": sorted(reasons), "samples": len(clocks)}
+            out = subprocess.run(["nvidia-smi", "--query-gpu=clocks.sm,clocks.max.sm", "--format=csv,noheader,nounits",
+                                  "-i", str(self.device_index)], capture_output=True, text=True, timeout=20).stdout
+            clock, maximum = [float(v) for v in out.strip().splitlines()[0].split(",")]
+            return {"sm_mhz": clock, "sm_max_mhz": maximum, "reasons": [], "samples": 1, "source": "nvidia-smi after the run"}
+        except Exception:
+            return {"sm_mhz": None, "sm_max_mhz": None, "reasons": ["clock query unavailable"], "samples": 0}
 
 
 # ---------------------------------------------------------------------------------------------------------
@@ -463,7 +491,7 @@ def run_gpu(args):
 def main():
     parser = argparse.ArgumentParser()
     parser.add_argument("--gpus", type=int, default=1)
-    parser.add_argument("--steps", type=int, default=20)
+    parser.add_argument("--steps", type=int, default=50)
     parser.add_argument("--warmup", type=int, default=5)
     parser.add_argument("--impl", default="b200", choices=["b200", "reference"])
     parser.add_argument("--rows", type=int, default=DEFAULT_ROWS, help="total rows of the sweep point")

@@ -392,21 +392,30 @@ logits_kernel(const LogitsParams p) {
 
 // ================================================================================================
 // Fast path: the row lives in REGISTERS.  512 threads x 10 float4 = 20 480 values per CTA, so a
-// cluster of eight covers a 151 936-wide row with one float4 slot to spare per thread.  Each warp
-// works against its OWN maximum, so nothing waits on another warp until the single cluster
-// barrier of the row:
+// cluster of eight covers a 151 936-wide row with one float4 slot to spare per thread, and two
+// CTAs share an SM.  Per row and CTA:
 //   [row i+1 streams into shared memory by cp.async while row i is processed]
 //   shared -> registers (each thread reads back exactly the 10 x 16 B it fetched itself, so no
-//   CTA barrier is involved) -> thread max -> warp max (shuffles)
-//   -> [lanes holding the warp max find its first position]         (only when an index is wanted)
-//   -> e = 2^((x - m_warp) log2 e) in place, thread sum -> warp sum -> publish (m, s, index)
-//   == cluster barrier ==
-//   every warp reads the <= 128 published entries through distributed shared memory and combines
-//   them (M = max m;  S = sum s 2^((m - M) log2 e);  index = min index among entries with m == M)
-//   -> p = e * 2^((m_warp - M) log2 e) / S -> bf16/f32 -> global
-// Shared memory is only a prefetch queue (one 16-byte read per four values); ~8 instructions per
-// element, one exponential per element.  The asynchronous prefetch is what keeps HBM busy: without
-// it the two CTAs of an SM load, compute, wait at the barrier and store in lock step.
+//   CTA barrier is involved)
+//   -> thread max (remembering the slot) -> warp max (shuffles) -> [the lane holding the warp max
+//      re-reads that one float4 from the staging buffer to find the position] -> refill issued
+//   -> e = 2^(x log2e - c_warp) in place, thread sum -> warp sum -> warp entry (m, s, index)
+//   == CTA barrier ==  warp 0 folds the 16 warp entries into the CTA entry
+//   == cluster barrier ==  every warp reads the (at most eight) CTA entries through distributed
+//      shared memory and folds them (M = max m;  S = sum s 2^(c - C);  index = min index at m == M)
+//   -> p = e * 2^(c_warp - C) / S -> bf16/f32 -> global
+// Each warp works against its OWN maximum, so nothing waits on another warp before the exchange;
+// the constants c = fl(max * log2e) are formed once and reused, so their rounding cancels between
+// numerator and denominator.  About 12 instructions and one ex2 per value.
+//
+// Measured alternatives on 256 x 151 936 (kept out of the code):
+//   every warp reading all 128 warp entries through DSMEM          104 us  (remote reads dominate)
+//   entries pushed by remote stores, split arrive/wait              54 us
+//   st.async + transaction mbarriers instead of the cluster barrier 60 us  (warp 0's serial fold
+//                                                                           and logf stall the CTA)
+//   warp-specialised exchange warp, two rows in registers, 1 CTA/SM 56 us  (only 15 clusters of 8
+//                                                                           fit at one CTA per SM)
+//   this version                                                    53 us; 5.1 TB/s at 1024 rows
 // ================================================================================================
 constexpr int kRegVectors = 10;
 constexpr uint32_t kRegSlice = kThreads * kRegVectors * 4;  // 20480 values per CTA
@@ -454,7 +463,7 @@ __device__ __forceinline__ Combined combine(WarpEntry mine) {
   return r;
 }
 
-template <int kMode>
+template <int kMode, int kFull>
 __global__ void __launch_bounds__(kThreads, 2)
 logits_regs_kernel(const LogitsParams p) {
   grid_dependency_sync();
@@ -479,7 +488,7 @@ logits_regs_kernel(const LogitsParams p) {
     const float4 *src = reinterpret_cast<const float4 *>(p.in + row * p.cols + begin);
 #pragma unroll
     for (int j = 0; j < kRegVectors; ++j)
-      if (j < slots) cp_async_16(&stage[j * kThreads + t], src + j * kThreads + t);
+      if (j < kFull || j < slots) cp_async_16(&stage[j * kThreads + t], src + j * kThreads + t);
     cp_async_commit();
   };
   if (cluster_id < p.rows) prefetch(cluster_id);
@@ -490,28 +499,26 @@ logits_regs_kernel(const LogitsParams p) {
     float4 x[kRegVectors];
 #pragma unroll
     for (int j = 0; j < kRegVectors; ++j)
-      x[j] = j < slots ? stage[j * kThreads + t] : make_float4(neg_inf, neg_inf, neg_inf, neg_inf);
-    if (row + cluster_count < p.rows) prefetch(row + cluster_count);  // overlaps everything below
+      x[j] = (j < kFull || j < slots) ? stage[j * kThreads + t] : make_float4(neg_inf, neg_inf, neg_inf, neg_inf);
     float thread_max = neg_inf;
+    int best_slot = 0;
 #pragma unroll
-    for (int j = 0; j < kRegVectors; ++j)
-      thread_max = max_nan(max_nan(thread_max, max_nan(x[j].x, x[j].y)), max_nan(x[j].z, x[j].w));
-    const float warp_max = warp_max_nan(thread_max);
-
-    uint32_t index = kNoIndex;
-    if (want_index && thread_max == warp_max) {  // few lanes; never true for NaN
-#pragma unroll
-      for (int j = kRegVectors - 1; j >= 0; --j) {  // descending, so the lowest position is written last
-        if (j < slots) {
-          const uint32_t base = begin + (j * kThreads + t) * 4;
-          if (x[j].w == warp_max) index = base + 3;
-          if (x[j].z == warp_max) index = base + 2;
-          if (x[j].y == warp_max) index = base + 1;
-          if (x[j].x == warp_max) index = base;
-        }
-      }
+    for (int j = 0; j < kRegVectors; ++j) {
+      const float slot_max = max_nan(max_nan(x[j].x, x[j].y), max_nan(x[j].z, x[j].w));
+      if (slot_max > thread_max) best_slot = j;
+      thread_max = max_nan(thread_max, slot_max);
     }
-    if (want_index) index = __reduce_min_sync(kFullMask, index);
+    const float warp_max = warp_max_nan(thread_max);
+    uint32_t index = kNoIndex;
+    if (want_index) {
+      if (thread_max == warp_max) {
+        const float4 v = stage[best_slot * kThreads + t];
+        const uint32_t base = begin + (best_slot * kThreads + t) * 4;
+        index = v.x == warp_max ? base : v.y == warp_max ? base + 1 : v.z == warp_max ? base + 2 : base + 3;
+      }
+      index = __reduce_min_sync(kFullMask, index);
+    }
+    if (row + cluster_count < p.rows) prefetch(row + cluster_count);
 
     // Exponentials against the warp's own maximum (0 stands in when the warp saw only -inf), as
     // 2^(x log2e - c) with c = fl(max * log2e): one fused multiply-add and one ex2 per value.  The
@@ -567,7 +574,7 @@ logits_regs_kernel(const LogitsParams p) {
         uint2 *dst = reinterpret_cast<uint2 *>(static_cast<unsigned short *>(p.out) + row * p.cols + begin);
 #pragma unroll
         for (int j = 0; j < kRegVectors; ++j) {
-          if (j < slots)
+          if (j < kFull || j < slots)
             st_stream(dst + j * kThreads + t, make_uint2(pack_bf16x2(x[j].x * scale, x[j].y * scale),
                                           pack_bf16x2(x[j].z * scale, x[j].w * scale)));
         }
@@ -575,7 +582,7 @@ logits_regs_kernel(const LogitsParams p) {
         float4 *dst = reinterpret_cast<float4 *>(static_cast<float *>(p.out) + row * p.cols + begin);
 #pragma unroll
         for (int j = 0; j < kRegVectors; ++j) {
-          if (j < slots) {
+          if (j < kFull || j < slots) {
             float4 o;
             if constexpr (kMode == kProbsF32) o = make_float4(x[j].x * scale, x[j].y * scale, x[j].z * scale, x[j].w * scale);
             else o = make_float4(x[j].x - shift, x[j].y - shift, x[j].z - shift, x[j].w - shift);
@@ -643,7 +650,9 @@ int resident_clusters(int cluster) {
     config.gridDim = dim3(cluster * 1024);
     config.blockDim = dim3(kThreads);
     config.dynamicSmemBytes = kRegStageBytes;
-    cudaFuncSetAttribute(logits_regs_kernel<kMode>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+    cudaFuncSetAttribute(logits_regs_kernel<kMode, 0>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                         static_cast<int>(kRegStageBytes));
+    cudaFuncSetAttribute(logits_regs_kernel<kMode, 9>, cudaFuncAttributeMaxDynamicSharedMemorySize,
                          static_cast<int>(kRegStageBytes));
     cudaLaunchAttribute attribute{};
     attribute.id = cudaLaunchAttributeClusterDimension;
@@ -653,7 +662,7 @@ int resident_clusters(int cluster) {
     config.attrs = &attribute;
     config.numAttrs = 1;
     int count = 0;
-    if (cudaOccupancyMaxActiveClusters(&count, logits_regs_kernel<kMode>, &config) != cudaSuccess || count <= 0)
+    if (cudaOccupancyMaxActiveClusters(&count, logits_regs_kernel<kMode, 0>, &config) != cudaSuccess || count <= 0)
       count = sm_count() * 2 / cluster;
     cached[slot][device] = count;
   }
@@ -670,7 +679,9 @@ int launch_logits(cudaStream_t stream, LogitsParams p, bool vec) {
       while (static_cast<uint64_t>(cluster) * kRegSlice < p.cols) cluster *= 2;
       p.slice = static_cast<uint32_t>(((p.cols + cluster - 1) / cluster + 7) / 8 * 8);
       const uint64_t resident = static_cast<uint64_t>(resident_clusters<kMode>(cluster));
-      return launch_cluster_kernel(stream, logits_regs_kernel<kMode>, p, cluster,
+      const uint64_t last = p.cols - static_cast<uint64_t>(cluster - 1) * p.slice;
+      const bool nine_full = p.cols > static_cast<uint64_t>(cluster - 1) * p.slice && last / 4 >= 9ull * kThreads;
+      return launch_cluster_kernel(stream, nine_full ? logits_regs_kernel<kMode, 9> : logits_regs_kernel<kMode, 0>, p, cluster,
                                    p.rows < resident ? p.rows : resident, kRegStageBytes);
     }
   }
