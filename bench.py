@@ -276,6 +276,55 @@ def other_ops(torch, peak_gbs, only=None, iterations=40):
     return results
 
 
+def sweep(torch, dist, ops, abi, wl, world: int, rank: int, peak_gbs: float, iterations: int = 20):
+    """The whole sweep R = 1024 ... 262144 (16 MiB ... 4 GiB of bf16), row-sharded over the ranks:
+    per point the step time (kernel + all-reduce, max over ranks), Gelem/s and GB/s per GPU."""
+    points = []
+    lib = abi.load()
+    stream = torch.cuda.current_stream().cuda_stream
+    workspace = ops.make_workspace("cuda")
+    partial = torch.zeros(1, dtype=torch.float64, device="cuda")
+    for total_rows in wl.SWEEP_ROWS:
+        shard = wl.shard_rows(total_rows, world, rank)
+        # small points rotate over several buffers so that no launch finds its input in L2
+        sets = max(1, min(8, int(600e6 // max(1, shard.rows * SWEEP_COLS * 2))))
+        w = [wl.q8_sweep_device_shard(shard) for _ in range(sets)]
+        count = w[0].numel()
+        blocks = [torch.empty(ops.q8_0_bytes(count), dtype=torch.uint8, device="cuda") for _ in range(sets)]
+        decoded = [torch.empty_like(w[0]) for _ in range(sets)]
+
+        def one(i):
+            abi.check("roundtrip", lib.hyle_b200_q8_0_roundtrip_bf16(
+                stream, w[i % sets].data_ptr(), count, blocks[i % sets].data_ptr(), decoded[i % sets].data_ptr(),
+                partial.data_ptr(), None, workspace.data_ptr(), workspace.numel()))
+            if world > 1:
+                dist.all_reduce(partial)
+
+        for i in range(3):
+            one(i)
+        if world > 1:
+            dist.barrier()
+        torch.cuda.synchronize()
+        start, stop = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        start.record()
+        for i in range(iterations):
+            one(i)
+        stop.record()
+        torch.cuda.synchronize()
+        ms = torch.tensor([start.elapsed_time(stop) / iterations], dtype=torch.float64, device="cuda")
+        if world > 1:
+            dist.all_reduce(ms, op=dist.ReduceOp.MAX)
+        seconds = float(ms.item()) * 1e-3
+        elements = total_rows * SWEEP_COLS
+        gbs_per_gpu = BYTES_PER_ELEMENT * count / seconds / 1e9
+        points.append({"rows": total_rows, "MiB_in": elements * 2 // 2**20, "us_per_step": seconds * 1e6,
+                       "Gelem/s": elements / seconds / 1e9, "GB/s_per_gpu": gbs_per_gpu,
+                       "roofline_frac": gbs_per_gpu / peak_gbs, "buffer_sets": sets})
+        del w, blocks, decoded
+        torch.cuda.empty_cache()
+    return points
+
+
 def run_e2e(torch, ops, abi, shard_rows: int, steps: int, warmup: int):
     """One pass from pinned host buffers: chunks flow host -> device -> kernel -> host on rotating
     streams so both copy directions and the kernels overlap."""
@@ -437,6 +486,12 @@ def run_gpu(args):
     if world > 1:
         dist.all_reduce(e2e_t, op=dist.ReduceOp.MAX)
 
+    sweep_points = None
+    if args.sweep:
+        del w, blocks, decoded
+        torch.cuda.empty_cache()
+        sweep_points = sweep(torch, dist, ops, abi, wl, world, rank, peak_gbs)
+
     if rank != 0:
         if world > 1:
             dist.destroy_process_group()
@@ -470,6 +525,8 @@ def run_gpu(args):
         "sum_squares": sum_squares,
     }
 
+    if args.sweep:
+        line["sweep"] = sweep_points
     if world == 1:
         if not args.skip_ops:
             line["ops"] = other_ops(torch, peak_gbs)
@@ -497,6 +554,7 @@ def main():
     parser.add_argument("--rows", type=int, default=DEFAULT_ROWS, help="total rows of the sweep point")
     parser.add_argument("--skip-ops", action="store_true", help="do not time workloads 1-4")
     parser.add_argument("--skip-cpu", action="store_true", help="do not time the CPU baseline")
+    parser.add_argument("--sweep", action="store_true", help="also time every sweep point R = 1024 ... 262144")
     parser.add_argument("--skip-e2e", action="store_true", help="do not time the host-buffer pass (profiling runs)")
     parser.add_argument("--ops-only", default=None,
                         help="comma list of add_bias_row_sum_max_f32,add_rms_norm_bf16,swiglu_bf16,logits_reduce_f32: "
