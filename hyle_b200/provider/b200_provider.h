@@ -1,0 +1,394 @@
+// HYLE provider adapter for libhyle_b200.so (C++23, against the reference's public headers).
+//
+// The provider is a custom-kernel Factory/Kernel pair (include/hyle/compute/custom_kernel.h:157-174,
+// 302-315) exactly like the reference's CUDA sample (samples/package/graph/custom_kernel/cuda_main.cc:33-126):
+// propose()/prepare() match a request against the operators the kernel library implements and
+// decline everything else with Status::Unimplemented; enqueue() takes the Queue's stream and the
+// tensors' device pointers and makes ONE call through the C ABI (include/hyle_b200.h).  Nothing here
+// allocates, synchronises or falls back to another implementation.
+//
+// The backend is a template parameter because the two things the adapter needs from it -- the
+// cudaStream_t of a QueueSequence and the device pointer of a BufferView -- come from
+// include/hyle/compute/backends/cuda.h, which needs CUDA >= 13.3.  `CudaBackend` (below, compiled
+// only when that header is usable) is the production binding; tests may supply another Backend to
+// drive the cold path on the reference's CPU backend.
+#pragma once
+
+#include <array>
+#include <cstdint>
+#include <optional>
+#include <span>
+#include <utility>
+
+#include <hyle/compute/custom_kernel.h>
+#include <hyle/compute/model_ops.h>
+#include <hyle/compute/operation.h>
+
+#include "b200_ops.h"
+#include "hyle_b200.h"
+
+namespace hyle::compute::b200 {
+
+inline constexpr ProviderIdentity kIdentity{{kNamespace, 1}, "hyle-b200", "1"};
+inline constexpr ProviderRuntimeProperties kRuntime{.replay_class = ProviderReplayClass::kPrepared,
+                                                    .capture_compatible = true};
+
+enum class Entry : std::uint8_t {
+  kBinary, kReduceRows, kRmsNorm, kSwiglu, kSoftmax, kCastF32ToBf16, kArgmax, kQ8Encode,
+  kAddRmsNorm, kBiasRowSumMax, kLogitsReduce, kQ8Roundtrip
+};
+
+// Everything enqueue() needs, frozen at prepare time.  Trivially copyable.
+struct Plan final {
+  Entry entry{};
+  int kind = 0;            // binary / reduce / softmax kind in the C ABI's numbering
+  int dtype = 0;           // hyle_b200_dtype of the data (or of the norm weight for the norms)
+  std::uint64_t count = 0; // total elements of input 0
+  std::uint64_t rows = 0;
+  std::uint64_t cols = 0;
+  std::uint64_t rhs_period = 0;
+  std::uint64_t gate_stride = 0, up_stride = 0, up_offset = 0;  // SwiGLU layouts, in elements
+  float epsilon = 0.0F;
+  bool has_weight = false;
+  std::size_t workspace_bytes = 0;
+};
+
+inline std::optional<int> abi_dtype(DataType type) noexcept {
+  switch (type) {
+    case DataType::kFloat32: return HYLE_B200_F32;
+    case DataType::kBFloat16: return HYLE_B200_BF16;
+    case DataType::kFloat16: return HYLE_B200_F16;
+    default: return std::nullopt;
+  }
+}
+
+inline std::uint64_t elements(const TensorDesc &d) noexcept {
+  const auto n = d.element_count();
+  return n ? static_cast<std::uint64_t>(*n) : 0;
+}
+inline std::uint64_t last_extent(const TensorDesc &d) noexcept {
+  return d.rank() == 0 ? 1 : static_cast<std::uint64_t>(d.dimensions().back());
+}
+inline bool all_dense(std::span<const TensorDesc> a, std::span<const TensorDesc> b) noexcept {
+  for (const auto &d : a) if (!d.is_dense() || !d.is_plain()) return false;
+  for (const auto &d : b) if (!d.is_dense() || !d.is_plain()) return false;
+  return true;
+}
+// rhs equals lhs, or is lhs's trailing axes (NumPy broadcast of a lower-rank right operand).
+inline bool trailing_axes(const TensorDesc &lhs, const TensorDesc &rhs) noexcept {
+  if (rhs.rank() > lhs.rank()) return false;
+  const auto l = lhs.dimensions(), r = rhs.dimensions();
+  for (std::size_t i = 0; i < r.size(); ++i)
+    if (r[r.size() - 1 - i] != l[l.size() - 1 - i]) return false;
+  return true;
+}
+
+// The provider's domain.  nullopt = decline (another provider may take the request).
+inline std::optional<Plan> match(const Operation &op, std::span<const TensorDesc> in,
+                                 std::span<const TensorDesc> out) noexcept {
+  if (in.empty() || out.empty() || !all_dense(in, out)) return std::nullopt;
+  Plan p{};
+  p.count = elements(in[0]);
+  p.cols = last_extent(in[0]);
+  p.rows = p.cols ? p.count / p.cols : 0;
+  const auto type = abi_dtype(in[0].data_type());
+
+  if (const auto *binary = op.get_if<Binary>()) {
+    if (in.size() != 2 || out.size() != 1 || !type || in[1].data_type() != in[0].data_type() ||
+        out[0] != in[0] || !trailing_axes(in[0], in[1]))
+      return std::nullopt;
+    if (binary->kind == BinaryKind::kAdd) p.kind = HYLE_B200_BINARY_ADD;
+    else if (binary->kind == BinaryKind::kMultiply) p.kind = HYLE_B200_BINARY_MULTIPLY;
+    else return std::nullopt;
+    p.entry = Entry::kBinary;
+    p.dtype = *type;
+    p.rhs_period = elements(in[1]) ? elements(in[1]) : 1;
+    return p;
+  }
+  if (const auto *reduce = op.get_if<Reduce>()) {
+    // last axis only, f32, dense output without the reduced axis
+    if (in.size() != 1 || out.size() != 1 || in[0].data_type() != DataType::kFloat32 || in[0].rank() == 0 ||
+        reduce->keep_dimensions || elements(out[0]) != p.rows || out[0].data_type() != DataType::kFloat32)
+      return std::nullopt;
+    const auto axes = reduce->axes.values();
+    const auto last = static_cast<int>(in[0].rank()) - 1;
+    if (reduce->axes.is_all() ? in[0].rank() != 1 : (axes.size() != 1 || (axes[0] != -1 && axes[0] != last)))
+      return std::nullopt;
+    switch (reduce->kind) {
+      case ReductionKind::kSum: p.kind = HYLE_B200_REDUCE_SUM; break;
+      case ReductionKind::kMean: p.kind = HYLE_B200_REDUCE_MEAN; break;
+      case ReductionKind::kMinimum: p.kind = HYLE_B200_REDUCE_MINIMUM; break;
+      case ReductionKind::kMaximum: p.kind = HYLE_B200_REDUCE_MAXIMUM; break;
+      default: return std::nullopt;
+    }
+    p.entry = Entry::kReduceRows;
+    return p;
+  }
+  if (const auto *norm = op.get_if<RmsNorm>()) {
+    if (in.empty() || in.size() > 2 || out.size() != 1 || in[0].data_type() != DataType::kBFloat16 ||
+        out[0] != in[0] || norm->accumulation_type != DataType::kFloat32)
+      return std::nullopt;
+    p.has_weight = in.size() == 2;
+    if (p.has_weight) {
+      const auto weight = abi_dtype(in[1].data_type());
+      if (!weight || *weight == HYLE_B200_F16 || elements(in[1]) != p.cols) return std::nullopt;
+      p.dtype = *weight;
+    }
+    p.entry = Entry::kRmsNorm;
+    p.epsilon = norm->epsilon;
+    return p;
+  }
+  if (const auto *gated = op.get_if<GatedActivation>()) {
+    if (gated->activation != GatedActivationKind::kSilu || in[0].data_type() != DataType::kBFloat16 ||
+        out.size() != 1 || out[0].data_type() != DataType::kBFloat16)
+      return std::nullopt;
+    p.entry = Entry::kSwiglu;
+    if (gated->inputs == GatedInputKind::kPackedHalves) {
+      if (in.size() != 1 || p.cols % 2 != 0 || last_extent(out[0]) * 2 != p.cols) return std::nullopt;
+      p.cols /= 2;
+      p.gate_stride = p.up_stride = 2 * p.cols;
+      p.up_offset = p.cols;
+    } else {
+      if (in.size() != 2 || in[1] != in[0] || out[0] != in[0]) return std::nullopt;
+      p.gate_stride = p.up_stride = p.cols;
+    }
+    return p;
+  }
+  if (const auto *softmax = op.get_if<Softmax>()) {
+    if (in.size() != 1 || out.size() != 1 || in[0].data_type() != DataType::kFloat32 || out[0] != in[0] ||
+        softmax->scale != 1.0F || softmax->mask != MaskKind::kNone || in[0].rank() == 0 ||
+        (softmax->axis != -1 && softmax->axis != static_cast<std::int32_t>(in[0].rank()) - 1))
+      return std::nullopt;
+    p.entry = Entry::kSoftmax;
+    p.kind = softmax->kind == SoftmaxKind::kLogSoftmax ? HYLE_B200_LOG_SOFTMAX : HYLE_B200_SOFTMAX;
+    return p;
+  }
+  if (const auto *cast = op.get_if<Cast>()) {
+    if (in.size() != 1 || out.size() != 1 || in[0].data_type() != DataType::kFloat32 ||
+        cast->output_type != DataType::kBFloat16 || elements(out[0]) != p.count)
+      return std::nullopt;
+    p.entry = Entry::kCastF32ToBf16;
+    return p;
+  }
+  if (const auto *top = op.get_if<TopK>()) {
+    // greedy token: values f32[..., 1] and indices i32[..., 1] over the last axis
+    if (in.size() != 1 || out.size() != 2 || top->count != 1 || !top->largest || in[0].rank() == 0 ||
+        in[0].data_type() != DataType::kFloat32 || out[0].data_type() != DataType::kFloat32 ||
+        out[1].data_type() != DataType::kInt32 ||
+        (top->axis != -1 && top->axis != static_cast<std::int32_t>(in[0].rank()) - 1))
+      return std::nullopt;
+    p.entry = Entry::kArgmax;
+    return p;
+  }
+  if (const auto encode = op.custom_as<model_ops::CacheEncode>()) {
+    if (in.size() != 1 || out.size() != 1 || !type || !(encode->storage == CacheStorage::q8_0().value()) ||
+        p.cols % 32 != 0 || out[0].data_type() != DataType::kUInt8)
+      return std::nullopt;
+    p.entry = Entry::kQ8Encode;
+    p.dtype = *type;
+    return p;
+  }
+  if (const auto fused = op.custom_as<FusedAddRmsNorm>()) {
+    const auto weight = in.size() == 3 ? abi_dtype(in[2].data_type()) : std::nullopt;
+    if (in.size() != 3 || out.size() != 2 || in[0].data_type() != DataType::kBFloat16 || in[1] != in[0] ||
+        !weight || *weight == HYLE_B200_F16)
+      return std::nullopt;
+    p.entry = Entry::kAddRmsNorm;
+    p.dtype = *weight;
+    p.has_weight = true;
+    p.epsilon = fused->epsilon;
+    return p;
+  }
+  if (op.custom_as<BiasRowSumMax>()) {
+    if (in.size() != 2 || out.size() != 3 || in[0].data_type() != DataType::kFloat32 ||
+        in[1].data_type() != DataType::kFloat32)
+      return std::nullopt;
+    p.entry = Entry::kBiasRowSumMax;
+    return p;
+  }
+  if (op.custom_as<LogitsReduce>()) {
+    if (in.size() != 1 || out.size() != 4 || in[0].data_type() != DataType::kFloat32) return std::nullopt;
+    p.entry = Entry::kLogitsReduce;
+    return p;
+  }
+  if (op.custom_as<Q8_0Roundtrip>()) {
+    if (in.size() != 1 || out.size() != 3 || in[0].data_type() != DataType::kBFloat16) return std::nullopt;
+    p.entry = Entry::kQ8Roundtrip;
+    p.workspace_bytes = static_cast<std::size_t>(hyle_b200_sum_squares_workspace_bytes());
+    return p;
+  }
+  return std::nullopt;
+}
+
+// One call through the C ABI.  Returns its cudaError_t-compatible result.
+inline int launch(const Plan &p, hyle_b200_stream_t stream, const void *const *in, void *const *out,
+                  void *workspace) noexcept {
+  switch (p.entry) {
+    case Entry::kBinary:
+      return hyle_b200_binary(stream, p.kind, p.dtype, in[0], in[1], out[0], p.count, p.rhs_period);
+    case Entry::kReduceRows:
+      return hyle_b200_reduce_rows_f32(stream, p.kind, static_cast<const float *>(in[0]),
+                                       static_cast<float *>(out[0]), p.rows, p.cols);
+    case Entry::kRmsNorm:
+      return hyle_b200_rms_norm_bf16(stream, in[0], p.has_weight ? in[1] : nullptr, p.dtype, out[0], p.rows, p.cols,
+                                     p.epsilon);
+    case Entry::kSwiglu: {
+      const auto *gate = static_cast<const std::uint16_t *>(in[0]);
+      const void *up = p.up_offset ? static_cast<const void *>(gate + p.up_offset) : in[1];
+      return hyle_b200_swiglu_bf16(stream, gate, up, out[0], p.rows, p.cols, p.gate_stride, p.up_stride);
+    }
+    case Entry::kSoftmax:
+      return hyle_b200_softmax_f32(stream, p.kind, static_cast<const float *>(in[0]), static_cast<float *>(out[0]),
+                                   p.rows, p.cols);
+    case Entry::kCastF32ToBf16:
+      return hyle_b200_cast_f32_to_bf16(stream, static_cast<const float *>(in[0]), out[0], p.count);
+    case Entry::kArgmax:
+      return hyle_b200_logits_reduce_f32(stream, static_cast<const float *>(in[0]), p.rows, p.cols, nullptr, nullptr,
+                                         static_cast<std::int32_t *>(out[1]), static_cast<float *>(out[0]));
+    case Entry::kQ8Encode:
+      return hyle_b200_q8_0_encode(stream, p.dtype, in[0], p.count, out[0], nullptr);
+    case Entry::kAddRmsNorm:
+      return hyle_b200_add_rms_norm_bf16(stream, in[0], in[1], in[2], p.dtype, out[0], out[1], p.rows, p.cols,
+                                         p.epsilon);
+    case Entry::kBiasRowSumMax:
+      return hyle_b200_add_bias_row_sum_max_f32(stream, static_cast<const float *>(in[0]),
+                                                static_cast<const float *>(in[1]), static_cast<float *>(out[0]),
+                                                static_cast<float *>(out[1]), static_cast<float *>(out[2]), p.rows,
+                                                p.cols);
+    case Entry::kLogitsReduce:
+      return hyle_b200_logits_reduce_f32(stream, static_cast<const float *>(in[0]), p.rows, p.cols,
+                                         static_cast<float *>(out[0]), out[1], static_cast<std::int32_t *>(out[2]),
+                                         static_cast<float *>(out[3]));
+    case Entry::kQ8Roundtrip:
+      return hyle_b200_q8_0_roundtrip_bf16(stream, in[0], p.count, out[0], out[1], static_cast<double *>(out[2]),
+                                           nullptr, workspace, p.workspace_bytes);
+  }
+  return HYLE_B200_INVALID_VALUE;
+}
+
+inline AliasSupport alias_support(const Plan &p, std::size_t output, std::size_t input) noexcept {
+  const bool in_place = (p.entry == Entry::kBinary || p.entry == Entry::kRmsNorm || p.entry == Entry::kSoftmax) &&
+                        output == 0 && input == 0;
+  return {in_place, 0};
+}
+
+// Backend concept:
+//   static constexpr BackendId id();                         which backend the provider serves
+//   static constexpr mem::MemoryProperty memory();           what the tensors must be
+//   static Result<hyle_b200_stream_t> stream(detail::QueueSequence &);
+//   static Result<const void *> pointer(mem::ConstBufferView);
+//   static Result<void *> mutable_pointer(mem::BufferView);
+//   static Status status(int abi_result);                    C ABI result -> Status
+template <class Backend>
+struct Kernel final {
+  Plan plan;
+  struct Invocation final {
+    void *workspace = nullptr;
+  };
+
+  Result<Invocation> create_invocation(mem::BufferView workspace, mem::AllocatorRef) const noexcept {
+    Invocation invocation{};
+    if (plan.workspace_bytes != 0) {
+      auto pointer = Backend::mutable_pointer(workspace);
+      if (!pointer) return std::unexpected(std::move(pointer).error());
+      invocation.workspace = *pointer;
+    }
+    return invocation;
+  }
+  AliasSupport alias_support(std::size_t output, std::size_t input) const noexcept {
+    return b200::alias_support(plan, output, input);
+  }
+  KernelCommandResult enqueue(Invocation &invocation, detail::QueueSequence &sequence,
+                              std::span<const ConstTensorView> inputs,
+                              std::span<const TensorView> outputs) const noexcept {
+    auto stream = Backend::stream(sequence);
+    if (!stream) return KernelCommandResult::rejected(std::move(stream).error());
+    std::array<const void *, 4> in{};
+    std::array<void *, 4> out{};
+    if (inputs.size() > in.size() || outputs.size() > out.size())
+      return KernelCommandResult::rejected(Status::Internal("hyle-b200: binding count changed after prepare"));
+    for (std::size_t i = 0; i < inputs.size(); ++i) {
+      auto pointer = Backend::pointer(inputs[i].storage());
+      if (!pointer) return KernelCommandResult::rejected(std::move(pointer).error());
+      in[i] = *pointer;
+    }
+    for (std::size_t i = 0; i < outputs.size(); ++i) {
+      auto pointer = Backend::mutable_pointer(outputs[i].storage());
+      if (!pointer) return KernelCommandResult::rejected(std::move(pointer).error());
+      out[i] = *pointer;
+    }
+    if (plan.count == 0 && plan.entry != Entry::kReduceRows) return KernelCommandResult::no_op();
+    // Recorded on the Queue's stream: no synchronisation, no allocation, no second Completion
+    // (docs/user/compute.md:1560-1565).  A failed launch is the Completion's terminal status.
+    return KernelCommandResult::accepted_command(
+        Backend::status(launch(plan, *stream, in.data(), out.data(), invocation.workspace)));
+  }
+};
+
+template <class Backend>
+struct Factory final {
+  Result<KernelProposal> propose(const KernelRequest &request, std::span<ResourceRequirement> inputs,
+                                 std::span<ResourceRequirement> outputs) const noexcept {
+    const auto plan = match(request.operation, request.inputs, request.outputs);
+    if (!plan) return std::unexpected(Status::Unimplemented("hyle-b200: operation outside the provider's domain"));
+    const ResourceRequirement storage{.required_properties = Backend::memory(), .minimum_alignment = 16};
+    for (auto &requirement : inputs) requirement = storage;
+    for (auto &requirement : outputs) requirement = storage;
+    const WorkspaceRequirement workspace{.size = plan->workspace_bytes, .alignment = 256};
+    return KernelProposal{.route = static_cast<std::uint64_t>(plan->entry),
+                          .runtime = kRuntime,
+                          .workspace_resource = {.required_properties = Backend::memory(), .minimum_alignment = 256},
+                          .cost = {.workspace = workspace,
+                                   .persistent_bytes = 0,
+                                   .copy_bytes = 0,
+                                   .repack_bytes = 0,
+                                   .synchronization_count = 0,
+                                   .dispatch_count = 1},
+                          .implementation = ProviderImplementationId{static_cast<std::uint64_t>(plan->entry) + 1}};
+  }
+  KernelPreparation prepare(const KernelPrepareRequest &request, mem::AllocatorRef allocator) const noexcept {
+    const auto plan = match(request.operation, request.inputs, request.outputs);
+    if (!plan) return KernelPreparation::unsupported(Status::Unimplemented("hyle-b200: declined at prepare"));
+    auto kernel = make_custom_kernel(
+        Kernel<Backend>{*plan},
+        {.workspace = {.size = plan->workspace_bytes, .alignment = 256}, .runtime = kRuntime, .persistent_bytes = 0},
+        allocator);
+    if (!kernel) return KernelPreparation::error(std::move(kernel).error());
+    return KernelPreparation::prepared(std::move(*kernel));
+  }
+};
+
+template <class Backend>
+Result<Provider> make_provider() noexcept {
+  return make_custom_provider(kIdentity, Backend::id(), Factory<Backend>{});
+}
+
+}  // namespace hyle::compute::b200
+
+#if defined(HYLE_B200_WITH_REFERENCE_CUDA_BACKEND)
+// Production binding: needs the reference's CUDA backend (CUDA Toolkit >= 13.3).
+#include <hyle/compute/backends/cuda.h>
+namespace hyle::compute::b200 {
+struct CudaBackend final {
+  static constexpr BackendId id() noexcept { return cuda::kBackendId; }
+  static constexpr mem::MemoryProperty memory() noexcept { return mem::MemoryProperty::kDeviceAccessible; }
+  static Result<hyle_b200_stream_t> stream(detail::QueueSequence &sequence) noexcept {
+    auto s = cuda::stream(sequence);
+    if (!s) return std::unexpected(std::move(s).error());
+    return reinterpret_cast<hyle_b200_stream_t>(*s);
+  }
+  static Result<const void *> pointer(mem::ConstBufferView view) noexcept {
+    auto p = cuda::pointer<std::byte>(view);
+    if (!p) return std::unexpected(std::move(p).error());
+    return static_cast<const void *>(*p);
+  }
+  static Result<void *> mutable_pointer(mem::BufferView view) noexcept {
+    auto p = cuda::pointer<std::byte>(view);
+    if (!p) return std::unexpected(std::move(p).error());
+    return static_cast<void *>(*p);
+  }
+  static Status status(int result) noexcept { return cuda::status(static_cast<cudaError_t>(result)); }
+};
+inline Result<Provider> provider() noexcept { return make_provider<CudaBackend>(); }
+}  // namespace hyle::compute::b200
+#endif

@@ -1,0 +1,174 @@
+// Drives the adapter's cold path (propose / prepare / decline) through the REFERENCE's own
+// runtime: Context::create -> compute::prepare -> provider search, on the reference's CPU backend.
+// A probe backend stands in for the CUDA one (which needs CUDA >= 13.3): it serves the CPU backend
+// id and host memory, and refuses to hand out a stream, so nothing is ever launched -- this program
+// checks WHICH requests the provider takes and how it declines, not arithmetic.
+//
+// Built by hyle_b200/provider/Makefile against the reference tree in place; prints one line per
+// check and exits non-zero on the first failure.
+#include <array>
+#include <cstdio>
+#include <cstdlib>
+
+#include <hyle/compute/backends/cpu.h>
+#include <hyle/compute/device.h>
+#include <hyle/compute/prepared_operation.h>
+#include <hyle/mem/buffer.h>
+#include <hyle/mem/resource.h>
+
+#include "b200_provider.h"
+
+using namespace hyle::compute;
+using hyle::Result;
+using hyle::Status;
+
+struct ProbeBackend final {
+  static constexpr BackendId id() noexcept { return cpu::kBackendId; }
+  static constexpr hyle::mem::MemoryProperty memory() noexcept { return hyle::mem::MemoryProperty::kHostAccessible; }
+  static Result<hyle_b200_stream_t> stream(detail::QueueSequence &) noexcept {
+    return std::unexpected(Status::Unimplemented("probe backend: no CUDA stream behind a CPU queue"));
+  }
+  static Result<const void *> pointer(hyle::mem::ConstBufferView) noexcept {
+    return std::unexpected(Status::Unimplemented("probe backend"));
+  }
+  static Result<void *> mutable_pointer(hyle::mem::BufferView) noexcept {
+    return std::unexpected(Status::Unimplemented("probe backend"));
+  }
+  static Status status(int) noexcept { return Status::Internal("probe backend never launches"); }
+};
+
+static int failures = 0;
+static void check(bool ok, const char *what) {
+  std::printf("%s  %s\n", ok ? "ok  " : "FAIL", what);
+  if (!ok) ++failures;
+}
+
+template <std::size_t N>
+static TensorDesc dense(DataType type, const std::int64_t (&dims)[N]) {
+  return TensorDesc::dense(type, std::span<const std::int64_t>(dims, N)).value();
+}
+
+// prepare() through the reference runtime with explicit input/output descriptions.
+static bool taken(const Context &context, const Operation &op, std::span<const TensorDesc> in,
+                  std::span<const TensorDesc> out) {
+  auto prepared = prepare(context, op, in, out, hyle::mem::system_resource());
+  return prepared.has_value() && prepared->provider().id == b200::kIdentity.id;
+}
+static bool declined(const Context &context, const Operation &op, std::span<const TensorDesc> in,
+                     std::span<const TensorDesc> out) {
+  auto prepared = prepare(context, op, in, out, hyle::mem::system_resource());
+  return !prepared.has_value() && prepared.error().IsUnimplemented();
+}
+
+int main() {
+  auto provider = b200::make_provider<ProbeBackend>();
+  check(provider.has_value(), "make_custom_provider accepts the factory");
+  if (!provider) return 1;
+  auto context = Context::create(cpu::device(), std::move(*provider));
+  check(context.has_value(), "Context::create with the b200 provider as the only provider");
+  if (!context) return 1;
+
+  const auto f32_mat = dense(DataType::kFloat32, {64, 4096});
+  const auto f32_row = dense(DataType::kFloat32, {4096});
+  const auto f32_rows = dense(DataType::kFloat32, {64});
+  const auto bf16_mat = dense(DataType::kBFloat16, {64, 2048});
+  const auto bf16_w = dense(DataType::kBFloat16, {2048});
+  const auto f32_w = dense(DataType::kFloat32, {2048});
+  const auto f16_w = dense(DataType::kFloat16, {2048});
+
+  {  // Binary: add/multiply with trailing-axis broadcast are taken, subtract is declined
+    const std::array in{f32_mat, f32_row};
+    const std::array out{f32_mat};
+    check(taken(*context, Operation(Binary{BinaryKind::kAdd}), in, out), "Binary{kAdd} f32 [64,4096] + [4096]");
+    check(taken(*context, Operation(Binary{BinaryKind::kMultiply}), in, out), "Binary{kMultiply} f32 broadcast");
+    check(declined(*context, Operation(Binary{BinaryKind::kSubtract}), in, out), "Binary{kSubtract} declined (Unimplemented)");
+    const std::array same{bf16_mat, bf16_mat};
+    const std::array out16{bf16_mat};
+    check(taken(*context, Operation(Binary{BinaryKind::kAdd}), same, out16), "Binary{kAdd} bf16 same shape (residual add)");
+  }
+  {  // Reduce over the last axis
+    const std::array in{f32_mat};
+    const std::array out{f32_rows};
+    const std::array<std::int32_t, 1> last{-1};
+    Reduce reduce{.kind = ReductionKind::kMaximum, .axes = Axes::from(last).value()};
+    check(taken(*context, Operation(reduce), in, out), "Reduce{kMaximum, axes={-1}} f32");
+    reduce.kind = ReductionKind::kSum;
+    check(taken(*context, Operation(reduce), in, out), "Reduce{kSum, axes={-1}} f32");
+    const std::array<std::int32_t, 1> first{0};
+    reduce.axes = Axes::from(first).value();
+    const std::array out0{f32_row};
+    check(declined(*context, Operation(reduce), in, out0), "Reduce over axis 0 declined");
+  }
+  {  // RmsNorm bf16 with bf16 / f32 weight; f16 weight and non-f32 accumulation are declined
+    const std::array out{bf16_mat};
+    const std::array in16{bf16_mat, bf16_w};
+    const std::array in32{bf16_mat, f32_w};
+    const std::array inh{bf16_mat, f16_w};
+    check(taken(*context, Operation(RmsNorm{.epsilon = 1e-6F}), in16, out), "RmsNorm bf16, bf16 weight");
+    check(taken(*context, Operation(RmsNorm{.epsilon = 1e-6F}), in32, out), "RmsNorm bf16, f32 weight");
+    check(!taken(*context, Operation(RmsNorm{.epsilon = 1e-6F}), inh, out), "RmsNorm with f16 weight not taken");
+  }
+  {  // GatedActivation: separate and packed halves
+    const auto gate = dense(DataType::kBFloat16, {32, 6144});
+    const auto packed = dense(DataType::kBFloat16, {32, 12288});
+    const std::array separate{gate, gate};
+    const std::array one{packed};
+    const std::array out{gate};
+    check(taken(*context, Operation(GatedActivation{GatedActivationKind::kSilu, GatedInputKind::kSeparate}), separate, out),
+          "GatedActivation{kSilu, kSeparate} bf16");
+    check(taken(*context, Operation(GatedActivation{GatedActivationKind::kSilu, GatedInputKind::kPackedHalves}), one, out),
+          "GatedActivation{kSilu, kPackedHalves} bf16");
+    check(!taken(*context, Operation(GatedActivation{GatedActivationKind::kGelu, GatedInputKind::kSeparate}), separate, out),
+          "GatedActivation{kGelu} not taken");
+  }
+  {  // Softmax / LogSoftmax / Cast / TopK{1}
+    const auto logits = dense(DataType::kFloat32, {16, 151936});
+    const auto probs16 = dense(DataType::kBFloat16, {16, 151936});
+    const auto values = dense(DataType::kFloat32, {16, 1});
+    const auto indices = dense(DataType::kInt32, {16, 1});
+    const std::array in{logits};
+    const std::array out{logits};
+    check(taken(*context, Operation(Softmax{}), in, out), "Softmax{axis=-1} f32");
+    check(taken(*context, Operation(Softmax{.kind = SoftmaxKind::kLogSoftmax}), in, out), "Softmax{kLogSoftmax} f32");
+    check(!taken(*context, Operation(Softmax{.scale = 0.5F}), in, out), "scaled Softmax not taken");
+    const std::array cast_out{probs16};
+    check(taken(*context, Operation(Cast{DataType::kBFloat16}), in, cast_out), "Cast{f32 -> bf16}");
+    const std::array top_out{values, indices};
+    check(taken(*context, Operation(TopK{.count = 1}), in, top_out), "TopK{count=1} -> values f32, indices i32");
+  }
+  {  // the fused operators and CacheEncode{q8_0}, with inferred outputs
+    const std::array in3{bf16_mat, bf16_mat, bf16_w};
+    std::array<TensorDesc, 2> out2{};
+    check(b200::FusedAddRmsNorm{}.infer_output_descriptions(in3, out2).ok() &&
+              taken(*context, Operation::custom(b200::FusedAddRmsNorm{.epsilon = 1e-6F}), in3, out2),
+          "custom b200-add-rms-norm");
+    const std::array in2{f32_mat, f32_row};
+    std::array<TensorDesc, 3> out3{};
+    check(b200::BiasRowSumMax{}.infer_output_descriptions(in2, out3).ok() &&
+              taken(*context, Operation::custom(b200::BiasRowSumMax{}), in2, out3),
+          "custom b200-bias-row-sum-max");
+    const auto logits = dense(DataType::kFloat32, {16, 151936});
+    const std::array in1{logits};
+    std::array<TensorDesc, 4> out4{};
+    check(b200::LogitsReduce{}.infer_output_descriptions(in1, out4).ok() &&
+              taken(*context, Operation::custom(b200::LogitsReduce{}), in1, out4),
+          "custom b200-logits-reduce");
+    const auto weights = dense(DataType::kBFloat16, {1024, 8192});
+    const std::array inw{weights};
+    std::array<TensorDesc, 3> outw{};
+    check(b200::Q8_0Roundtrip{}.infer_output_descriptions(inw, outw).ok() && outw[0].dimensions()[1] == 8704,
+          "b200-q8_0-roundtrip infers the U8[rows, cols/32*34] carrier");
+    auto prepared = prepare(*context, Operation::custom(b200::Q8_0Roundtrip{}), std::span<const TensorDesc>(inw),
+                            std::span<const TensorDesc>(outw), hyle::mem::system_resource());
+    check(prepared.has_value() && prepared->workspace_requirement().size == hyle_b200_sum_squares_workspace_bytes() &&
+              prepared->capture_compatible(),
+          "b200-q8_0-roundtrip prepared; caller-owned workspace = hyle_b200_sum_squares_workspace_bytes()");
+    model_ops::CacheEncode encode{CacheStorage::q8_0().value()};
+    std::array<TensorDesc, 1> carrier{};
+    check(encode.infer_output_descriptions(inw, carrier).ok() &&
+              taken(*context, Operation::custom(encode), inw, carrier),
+          "model_ops::CacheEncode{q8_0} bf16");
+  }
+  std::printf("%d failure(s)\n", failures);
+  return failures == 0 ? 0 : 1;
+}
