@@ -282,7 +282,7 @@ def sweep(torch, dist, ops, abi, wl, world: int, rank: int, peak_gbs: float, ite
     points = []
     lib = abi.load()
     stream = torch.cuda.current_stream().cuda_stream
-    workspace = ops.make_workspace("cuda")
+    workspace = ops.make_workspace("cuda", (wl.SWEEP_ROWS[-1] + world - 1) // world * SWEEP_COLS)
     partial = torch.zeros(1, dtype=torch.float64, device="cuda")
     for total_rows in wl.SWEEP_ROWS:
         shard = wl.shard_rows(total_rows, world, rank)
@@ -341,7 +341,7 @@ def run_e2e(torch, ops, abi, shard_rows: int, steps: int, warmup: int):
     dev_blocks = [torch.empty(chunk_rows * SWEEP_COLS // 32 * 34, dtype=torch.uint8, device="cuda") for _ in range(lanes)]
     dev_decoded = [torch.empty((chunk_rows, SWEEP_COLS), dtype=torch.bfloat16, device="cuda") for _ in range(lanes)]
     dev_sums = torch.zeros(chunks, dtype=torch.float64, device="cuda")
-    workspaces = [ops.make_workspace("cuda") for _ in range(lanes)]
+    workspaces = [ops.make_workspace("cuda", chunk_rows * SWEEP_COLS) for _ in range(lanes)]
     lib = abi.load()
     block_bytes_per_row = SWEEP_COLS // 32 * 34
 
@@ -418,7 +418,7 @@ def run_gpu(args):
     decoded = torch.empty_like(w)
     partial = torch.zeros(1, dtype=torch.float64, device="cuda")
     status = torch.zeros(1, dtype=torch.int32, device="cuda")
-    workspace = ops.make_workspace("cuda")
+    workspace = ops.make_workspace("cuda", count)
     lib = abi.load()
     stream = torch.cuda.current_stream().cuda_stream
 

@@ -25,7 +25,7 @@ STATIC_MAX_VALUES = 1 << 31
 # enum hyle_b200_status_bits
 STATUS_INVALID_Q8_INPUT = 1
 
-ABI_VERSION = 1
+ABI_VERSION = 2
 
 _p = ctypes.c_void_p
 _u64 = ctypes.c_uint64
@@ -47,7 +47,7 @@ SIGNATURES = {
     "hyle_b200_cast_f32_to_bf16": (_i, [_p, _p, _p, _u64]),
     "hyle_b200_q8_0_encode": (_i, [_p, _i, _p, _u64, _p, _p]),
     "hyle_b200_q8_0_decode_bf16": (_i, [_p, _p, _u64, _p]),
-    "hyle_b200_sum_squares_workspace_bytes": (_u64, []),
+    "hyle_b200_sum_squares_workspace_bytes": (_u64, [_u64]),
     "hyle_b200_sum_squares_bf16": (_i, [_p, _p, _u64, _p, _p, _u64]),
     "hyle_b200_q8_0_roundtrip_bf16": (_i, [_p, _p, _u64, _p, _p, _p, _p, _p, _u64]),
     "hyle_b200_q8_0_roundtrip_bf16_static": (_i, [_p, _p, _u64, _p, _p, _p, _p]),

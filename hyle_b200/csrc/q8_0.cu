@@ -21,7 +21,7 @@ constexpr int kVectorsPerThread = 4;
 constexpr int kTileBlocks = 256;
 constexpr int kTileBytes = kTileBlocks * 34;  // 8704 = 544 * 16
 constexpr int kMaxPartials = 4096;
-constexpr uint64_t kWorkspaceBytes = 64 + sizeof(double) * kMaxPartials;
+constexpr uint64_t kWorkspaceBytes = 64 + sizeof(double) * kMaxPartials;  // static scheme: header + CTA partials
 
 // |x| <= 65504*127 as an integer comparison on the magnitude bits; NaN and inf compare above it
 // (ggml_cpu_provider.cc:563-584).
@@ -95,6 +95,30 @@ __device__ __forceinline__ SumSquaresState workspace_state(void *workspace) {
           reinterpret_cast<double *>(static_cast<unsigned char *>(workspace) + 64)};
 }
 
+// ---- dynamic tile scheduling with an order-independent result ---------------------------------
+// On this GPU a persistent grid that pulls tiles from one atomic counter finishes the 4 GiB sweep
+// point 6 % sooner than a static tile-to-CTA assignment (all CTAs stay within a narrow window of
+// addresses and nobody waits for the slowest SM).  The price is that "which CTA summed which tile"
+// is no longer fixed, so the sum of squares is built from per-TILE sums instead of per-CTA sums:
+//   tile_sums[tile]   f32 per thread over its 32 values, f32 warp tree, 8 warp values added in f64;
+//                     a plain store, no fence and no atomic per tile (a fence would wait for the
+//                     tile's streaming stores: measured, that cost more than the scheduling gains)
+//   *sum_out          the CTA that leaves last adds all tile sums: thread t takes t, t+256, ... in
+//                     order, then the fixed warp / CTA tree (2 MB of f64 at the largest point)
+// Every value is a function of the data only, so the result is bit-identical from run to run and
+// for any grid size.  The tile sums live after the static scheme's area of the workspace.
+struct DynamicState {
+  uint32_t *ticket;                 // CTAs that have left
+  unsigned long long *next_tile;    // tile counter (tiles gridDim.x.. are handed out through it)
+  double *tile_sums;
+};
+__host__ __device__ inline uint64_t dynamic_bytes(uint64_t tiles) { return tiles * 8; }
+__device__ __forceinline__ DynamicState dynamic_state(void *workspace) {
+  unsigned char *base = static_cast<unsigned char *>(workspace);
+  return {reinterpret_cast<uint32_t *>(base), reinterpret_cast<unsigned long long *>(base + 16),
+          reinterpret_cast<double *>(base + kWorkspaceBytes)};
+}
+
 // Deterministic grid-wide sum: fixed-order CTA reduction, one partial per CTA, and the CTA that
 // takes the last ticket adds the partials in index order.  Which CTA is last does not matter.
 __device__ __forceinline__ void finish_sum(double thread_sum, SumSquaresState ws, double *sum_out) {
@@ -127,7 +151,8 @@ __device__ __forceinline__ void finish_sum(double thread_sum, SumSquaresState ws
 }
 
 // kEncode: write Q8_0 blocks.  kDecode: write decoded bf16.  kSumSquares: accumulate sum x^2.
-template <int kDtype, bool kEncode, bool kDecode, bool kSumSquares>
+// kDynamic (needs kEncode and kSumSquares): tiles come from the workspace's counter.
+template <int kDtype, bool kEncode, bool kDecode, bool kSumSquares, bool kDynamic = false>
 __global__ void __launch_bounds__(kThreads)
 q8_0_kernel(const void *__restrict__ in, uint64_t blocks, unsigned char *__restrict__ blocks_out,
             unsigned short *__restrict__ decoded, double *sum_out, uint32_t *status_word,
@@ -137,10 +162,19 @@ q8_0_kernel(const void *__restrict__ in, uint64_t blocks, unsigned char *__restr
   const int t = threadIdx.x;
   const int sub = t & 3;  // which quarter of a block this lane holds
   const uint64_t tiles = (blocks + kTileBlocks - 1) / kTileBlocks;
+  static_assert(!kDynamic || (kEncode && kSumSquares), "the dynamic scheme rides on the encode barrier");
+  __shared__ float s_warp_sum[2][kThreads / 32];
+  __shared__ unsigned long long s_next_tile[2];
+  DynamicState dynamic{};
+  if constexpr (kDynamic) dynamic = dynamic_state(workspace);
   double sum = 0.0;
   bool invalid_seen = false;
   int buffer = 0;
-  for (uint64_t tile = blockIdx.x; tile < tiles; tile += gridDim.x, buffer ^= 1) {
+  for (uint64_t tile = blockIdx.x; tile < tiles; buffer ^= 1) {
+    // The next tile is requested now and read after this tile's barrier: no barrier of its own.
+    if constexpr (kDynamic) {
+      if (t == 0) s_next_tile[buffer] = gridDim.x + atomicAdd(dynamic.next_tile, 1ull);
+    }
     const uint64_t first_block = tile * kTileBlocks;
     const uint32_t tile_blocks = static_cast<uint32_t>(min(static_cast<uint64_t>(kTileBlocks), blocks - first_block));
     const bool full = tile_blocks == kTileBlocks;
@@ -215,11 +249,25 @@ q8_0_kernel(const void *__restrict__ in, uint64_t blocks, unsigned char *__restr
         }
       }
     }
-    if constexpr (kSumSquares) sum += static_cast<double>(tile_sum);
+    if constexpr (kSumSquares && !kDynamic) sum += static_cast<double>(tile_sum);
+    if constexpr (kDynamic) {
+      const float warp_total = warp_sum(tile_sum);
+      if ((t & 31) == 0) s_warp_sum[buffer][t >> 5] = warp_total;
+    }
+    uint64_t next_tile = tile + gridDim.x;
     if constexpr (kEncode) {
       // One barrier per tile: the staging buffer alternates, and this barrier also orders the
       // previous tile's reads of the other buffer before the next tile's writes to it.
       __syncthreads();
+      if constexpr (kDynamic) {
+        next_tile = s_next_tile[buffer];
+        if (t == 0) {
+          double tile_total = static_cast<double>(s_warp_sum[buffer][0]);
+#pragma unroll
+          for (int w = 1; w < kThreads / 32; ++w) tile_total += static_cast<double>(s_warp_sum[buffer][w]);
+          dynamic.tile_sums[tile] = tile_total;
+        }
+      }
       unsigned char *dst = blocks_out + first_block * 34;
       if (full && out_aligned) {
         const uint4 *src = reinterpret_cast<const uint4 *>(staged[buffer]);
@@ -229,9 +277,38 @@ q8_0_kernel(const void *__restrict__ in, uint64_t blocks, unsigned char *__restr
         for (uint32_t i = t; i < tile_blocks * 17; i += kThreads) st_stream(reinterpret_cast<unsigned short *>(dst) + i, src[i]);
       }
     }
+    tile = next_tile;
   }
   if (status_word != nullptr && invalid_seen) atomicOr(status_word, HYLE_B200_STATUS_INVALID_Q8_INPUT);
-  if constexpr (kSumSquares) finish_sum(sum, workspace_state(workspace), sum_out);
+  if constexpr (kDynamic) {
+    // The CTA that leaves last adds the tile sums in a fixed order and re-arms the workspace.
+    __shared__ bool s_last;
+    __shared__ double s_final[kThreads / 32];
+    __syncthreads();
+    if (t == 0) {
+      __threadfence();  // this CTA's tile sums are visible before its ticket
+      s_last = atomicAdd(dynamic.ticket, 1u) == gridDim.x - 1;
+    }
+    __syncthreads();
+    if (s_last) {
+      __threadfence();
+      double acc = 0.0;
+      for (uint64_t i = t; i < tiles; i += kThreads) acc += __ldcg(dynamic.tile_sums + i);
+      acc = warp_sum(acc);
+      if ((t & 31) == 0) s_final[t >> 5] = acc;
+      __syncthreads();
+      if (t == 0) {
+        double total = s_final[0];
+#pragma unroll
+        for (int w = 1; w < kThreads / 32; ++w) total += s_final[w];
+        *sum_out = total;
+        *dynamic.ticket = 0u;
+        *dynamic.next_tile = 0ull;
+      }
+    }
+  } else if constexpr (kSumSquares) {
+    finish_sum(sum, workspace_state(workspace), sum_out);
+  }
 }
 
 // Decode-only: a tile's 8704 bytes are pulled into shared memory with 16-byte loads, then every
@@ -329,7 +406,10 @@ unsigned q8_grid(uint64_t blocks) {
 
 using namespace hb;
 
-extern "C" uint64_t hyle_b200_sum_squares_workspace_bytes(void) { return kWorkspaceBytes; }
+extern "C" uint64_t hyle_b200_sum_squares_workspace_bytes(uint64_t count) {
+  const uint64_t tiles = (count / 32 + kTileBlocks - 1) / kTileBlocks;
+  return kWorkspaceBytes + dynamic_bytes(tiles);
+}
 
 extern "C" int hyle_b200_q8_0_encode(hyle_b200_stream_t stream, int dtype, const void *in,
                                      uint64_t count, void *blocks_out, uint32_t *status_word) {
@@ -387,14 +467,19 @@ extern "C" int hyle_b200_q8_0_roundtrip_bf16(hyle_b200_stream_t stream, const vo
                                              void *workspace, uint64_t workspace_bytes) {
   if (in == nullptr && count != 0) return HYLE_B200_INVALID_VALUE;
   if (blocks_out == nullptr || decoded_bf16 == nullptr || sum_squares_out == nullptr ||
-      workspace == nullptr || workspace_bytes < kWorkspaceBytes || !aligned_to(workspace, 8) ||
-      count % 32 != 0 || !aligned_to(blocks_out, 2))
+      workspace == nullptr || workspace_bytes < hyle_b200_sum_squares_workspace_bytes(count) ||
+      !aligned_to(workspace, 8) || count % 32 != 0 || !aligned_to(blocks_out, 2))
     return HYLE_B200_INVALID_VALUE;
   if (!aligned_to(in, 16) || !aligned_to(decoded_bf16, 16)) return HYLE_B200_NOT_SUPPORTED;
   const uint64_t blocks = count / 32;
-  return launch(q8_0_kernel<HYLE_B200_BF16, true, true, true>, dim3(q8_grid(blocks)), dim3(kThreads), 0, reinterpret_cast<cudaStream_t>(stream), 
-      in, blocks, static_cast<unsigned char *>(blocks_out), static_cast<unsigned short *>(decoded_bf16),
-      sum_squares_out, status_word, workspace, aligned_to(blocks_out, 16));
+  const uint64_t tiles = (blocks + kTileBlocks - 1) / kTileBlocks;
+  // Persistent grid of what fits at once (four CTAs per SM at 64 registers); the rest of the tiles
+  // are pulled from the workspace's counter.
+  const unsigned grid = clamp_grid(tiles, static_cast<uint64_t>(sm_count()) * 4);
+  return launch(q8_0_kernel<HYLE_B200_BF16, true, true, true, true>, dim3(grid), dim3(kThreads), 0,
+                reinterpret_cast<cudaStream_t>(stream), in, blocks, static_cast<unsigned char *>(blocks_out),
+                static_cast<unsigned short *>(decoded_bf16), sum_squares_out, status_word, workspace,
+                aligned_to(blocks_out, 16));
 }
 
 // ------------------------------------------------------------------------------------------------

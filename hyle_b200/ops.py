@@ -231,9 +231,10 @@ def q8_0_decode(blocks: torch.Tensor, count: int) -> torch.Tensor:
     return out
 
 
-def make_workspace(device) -> torch.Tensor:
-    """Zero-filled scratch for sum_squares / q8_0_roundtrip; reusable across stream-ordered calls."""
-    return torch.zeros(abi.load().hyle_b200_sum_squares_workspace_bytes(), dtype=torch.uint8, device=device)
+def make_workspace(device, count: int = 0) -> torch.Tensor:
+    """Zero-filled scratch for sum_squares / q8_0_roundtrip of up to ``count`` values; reusable
+    across stream-ordered calls."""
+    return torch.zeros(abi.load().hyle_b200_sum_squares_workspace_bytes(count), dtype=torch.uint8, device=device)
 
 
 def sum_squares(x: torch.Tensor, workspace: torch.Tensor, out: Optional[torch.Tensor] = None) -> torch.Tensor:

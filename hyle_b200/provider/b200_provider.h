@@ -214,7 +214,7 @@ inline std::optional<Plan> match(const Operation &op, std::span<const TensorDesc
   if (op.custom_as<Q8_0Roundtrip>()) {
     if (in.size() != 1 || out.size() != 3 || in[0].data_type() != DataType::kBFloat16) return std::nullopt;
     p.entry = Entry::kQ8Roundtrip;
-    p.workspace_bytes = static_cast<std::size_t>(hyle_b200_sum_squares_workspace_bytes());
+    p.workspace_bytes = static_cast<std::size_t>(hyle_b200_sum_squares_workspace_bytes(p.count));
     return p;
   }
   return std::nullopt;

@@ -160,9 +160,9 @@ int main() {
           "b200-q8_0-roundtrip infers the U8[rows, cols/32*34] carrier");
     auto prepared = prepare(*context, Operation::custom(b200::Q8_0Roundtrip{}), std::span<const TensorDesc>(inw),
                             std::span<const TensorDesc>(outw), hyle::mem::system_resource());
-    check(prepared.has_value() && prepared->workspace_requirement().size == hyle_b200_sum_squares_workspace_bytes() &&
+    check(prepared.has_value() && prepared->workspace_requirement().size == hyle_b200_sum_squares_workspace_bytes(1024ull * 8192) &&
               prepared->capture_compatible(),
-          "b200-q8_0-roundtrip prepared; caller-owned workspace = hyle_b200_sum_squares_workspace_bytes()");
+          "b200-q8_0-roundtrip prepared; caller-owned workspace = hyle_b200_sum_squares_workspace_bytes(count)");
     model_ops::CacheEncode encode{CacheStorage::q8_0().value()};
     std::array<TensorDesc, 1> carrier{};
     check(encode.infer_output_descriptions(inw, carrier).ok() &&

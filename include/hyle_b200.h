@@ -42,7 +42,7 @@ extern "C" {
 /* Same object as cudaStream_t; spelled out so C callers need no CUDA header. */
 typedef struct CUstream_st *hyle_b200_stream_t;
 
-#define HYLE_B200_ABI_VERSION 1
+#define HYLE_B200_ABI_VERSION 2
 
 enum hyle_b200_result {
   HYLE_B200_OK = 0,
@@ -205,10 +205,12 @@ HYLE_B200_API int hyle_b200_q8_0_encode(hyle_b200_stream_t stream, int dtype, co
 HYLE_B200_API int hyle_b200_q8_0_decode_bf16(hyle_b200_stream_t stream, const void *blocks,
                                              uint64_t count, void *out_bf16);
 
-/* Scratch for the two kernels below: a few KB holding per-CTA partial sums and a ticket counter.
- * The caller zero-fills it once after allocation; each launch leaves it zeroed again, so one
- * workspace serves any number of stream-ordered launches (not concurrent ones). */
-HYLE_B200_API uint64_t hyle_b200_sum_squares_workspace_bytes(void);
+/* Scratch for the two kernels below, for a tensor of `count` values: a header (ticket and tile
+ * counters), per-CTA partial sums, and for the fused round trip one f64 per tile of 8192 values
+ * (count/1024 bytes + 33 KB).  The caller zero-fills it once after
+ * allocation; each launch leaves every counter zeroed again, so one workspace serves any number of
+ * stream-ordered launches (not concurrent ones), also for smaller counts. */
+HYLE_B200_API uint64_t hyle_b200_sum_squares_workspace_bytes(uint64_t count);
 
 /* Reduce{kSum, Axes::all()} of Cast(bf16->f32)^2 (include/hyle/compute/operation.h:232-248):
  * deterministic two-pass sum (fixed per-thread order, fixed-order merge of CTA partials in f64).
@@ -218,7 +220,9 @@ HYLE_B200_API int hyle_b200_sum_squares_bf16(hyle_b200_stream_t stream, const vo
                                              uint64_t workspace_bytes);
 
 /* One pass over a bf16 tensor producing its Q8_0 blocks, the decoded bf16 tensor and the sum of
- * squares of the input: the input is read once (5.0625 bytes of traffic per element). */
+ * squares of the input: the input is read once (5.0625 bytes of traffic per element).  Tiles are
+ * handed to the CTAs dynamically; the sum is built from per-tile sums added in index order, so it is
+ * bit-identical from run to run. */
 HYLE_B200_API int hyle_b200_q8_0_roundtrip_bf16(hyle_b200_stream_t stream, const void *in,
                                                 uint64_t count, void *blocks_out,
                                                 void *decoded_bf16, double *sum_squares_out,

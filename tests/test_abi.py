@@ -41,7 +41,10 @@ def test_version_strings_and_pure_host_queries(library):
     assert library.hyle_b200_result_string(0) == b"ok"
     assert b"invalid" in library.hyle_b200_result_string(abi.INVALID_VALUE)
     assert b"not supported" in library.hyle_b200_result_string(abi.NOT_SUPPORTED)
-    assert library.hyle_b200_sum_squares_workspace_bytes() >= 64 + 8 * 148
+    assert library.hyle_b200_sum_squares_workspace_bytes(0) >= 64 + 8 * 148
+    # one f64 per tile of 8192 values on top of the fixed part
+    grown = library.hyle_b200_sum_squares_workspace_bytes(1 << 31) - library.hyle_b200_sum_squares_workspace_bytes(0)
+    assert (1 << 31) // 8192 * 8 <= grown <= (1 << 31) // 8192 * 8 * 1.02
 
 
 def test_argument_errors_are_reported_before_any_launch(library):

@@ -330,7 +330,7 @@ def test_cast_f32_to_bf16(oracle):
 def test_q8_0_roundtrip_against_checker(oracle, rows):
     w = wl.q8_sweep_inputs(rows)
     dev = to_dev_bf16(w)
-    ws = ops.make_workspace(DEV)
+    ws = ops.make_workspace(DEV, w.size)
     status = torch.zeros(1, dtype=torch.int32, device=DEV)
     for _ in range(2):  # the workspace is reusable
         blocks, decoded, total = ops.q8_0_roundtrip(dev, ws, status=status)
@@ -419,7 +419,7 @@ def test_q8_0_rounding_ties_and_ragged_tiles(oracle):
     for blocks in [1, 3, 255, 257, 513, 1000]:
         w = wl.f32_to_bf16((0.02 * rng.standard_normal(blocks * 32)).astype(np.float32))
         dev = to_dev_bf16(w)
-        ws = ops.make_workspace(DEV)
+        ws = ops.make_workspace(DEV, w.size)
         got_b, got_d, got_s = ops.q8_0_roundtrip(dev, ws)
         want_b, want_d, want_s, _ = oracle.q8_0_roundtrip(w)
         assert np.array_equal(got_b.cpu().numpy(), want_b)
@@ -441,8 +441,10 @@ def test_q8_0_full_size_properties():
     rows = 32768  # 512 MiB of bf16
     shard = wl.shard_rows(rows, 1, 0)
     w = wl.q8_sweep_device_shard(shard)
-    ws = ops.make_workspace(DEV)
+    ws = ops.make_workspace(DEV, w.numel())
     blocks, decoded, total = ops.q8_0_roundtrip(w, ws)
+    again = ops.q8_0_roundtrip(w, ws)[2]
+    assert again.item() == total.item()  # dynamic tile scheduling, yet the same bits every run
     assert torch.equal(ops.q8_0_decode(blocks, w.numel()).view(torch.int16), decoded.view(torch.int16).ravel())
     b = blocks.view(-1, 34)
     scale = b[:, :2].contiguous().view(torch.float16).float()

@@ -30,7 +30,7 @@ def test_static_scratch_round_trip_matches_workspace_round_trip_twice(rows):
     x = _bf16_dev(wl.q8_sweep_inputs(rows))
     count = x.numel()
     # reference results from the existing entry point (caller-supplied workspace)
-    workspace = ops.make_workspace("cuda")
+    workspace = ops.make_workspace("cuda", count)
     want_blocks, want_decoded, want_sum = ops.q8_0_roundtrip(x, workspace)
     torch.cuda.synchronize()
 
