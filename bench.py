@@ -31,7 +31,7 @@ DEFAULT_ROWS = 262144                       # 4 GiB of bf16: the largest sweep p
 BYTES_PER_ELEMENT = 2 + 34 / 32 + 2         # read bf16, write Q8_0 block share, write decoded bf16
 # dram__bytes_read.sum + dram__bytes_write.sum per element of the roundtrip kernel, from the ncu
 # capture summarised in profiles/ (the rest of the 3.06 B/value of output is written back from L2 after the kernel).
-NCU_TRAFFIC_BYTES_PER_ELEMENT = 4.68  # profiles/q8_0_roundtrip_R16384.md: 2.00 read + 2.68 written by kernel end
+NCU_TRAFFIC_BYTES_PER_ELEMENT = 4.66  # profiles/q8_0_roundtrip_R16384.md: 2.00 read + 2.66 written by kernel end
 FALLBACK_HBM_GBS = 6650.0
 METRIC = "Q8_0 quantise+dequantise+sum-of-squares sweep throughput"
 UNIT = "Gelem/s"
