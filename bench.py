@@ -276,7 +276,7 @@ def other_ops(torch, peak_gbs, only=None, iterations=40):
     return results
 
 
-def sweep(torch, dist, ops, abi, wl, world: int, rank: int, peak_gbs: float, iterations: int = 20):
+def sweep(torch, dist, ops, abi, wl, world: int, rank: int, peak_gbs: float, reducer, iterations: int = 20):
     """The whole sweep R = 1024 ... 262144 (16 MiB ... 4 GiB of bf16), row-sharded over the ranks:
     per point the step time (kernel + all-reduce, max over ranks), Gelem/s and GB/s per GPU."""
     points = []
@@ -298,7 +298,7 @@ def sweep(torch, dist, ops, abi, wl, world: int, rank: int, peak_gbs: float, ite
                 stream, w[i % sets].data_ptr(), count, blocks[i % sets].data_ptr(), decoded[i % sets].data_ptr(),
                 partial.data_ptr(), None, workspace.data_ptr(), workspace.numel()))
             if world > 1:
-                dist.all_reduce(partial)
+                reducer.sum_f64(partial, stream)
 
         for i in range(3):
             one(i)
@@ -427,9 +427,15 @@ def run_gpu(args):
             stream, w.data_ptr(), count, blocks.data_ptr(), decoded.data_ptr(), partial.data_ptr(),
             status.data_ptr(), workspace.data_ptr(), workspace.numel()))
 
+    reducer = None
+    if world > 1:
+        from hyle_b200.collective import StreamAllReduce
+
+        reducer = StreamAllReduce()
+
     def combine():
         if world > 1:
-            dist.all_reduce(partial)  # the one exchange of the path: 8 bytes per rank over NVLink
+            reducer.sum_f64(partial, stream)  # the one exchange of the path: 8 bytes per rank over NVLink
 
     for _ in range(args.warmup):
         step()
@@ -490,10 +496,11 @@ def run_gpu(args):
     if args.sweep:
         del w, blocks, decoded
         torch.cuda.empty_cache()
-        sweep_points = sweep(torch, dist, ops, abi, wl, world, rank, peak_gbs)
+        sweep_points = sweep(torch, dist, ops, abi, wl, world, rank, peak_gbs, reducer)
 
     if rank != 0:
         if world > 1:
+            reducer.close()
             dist.destroy_process_group()
         return
 
@@ -542,6 +549,7 @@ def run_gpu(args):
                                     "sample": f"{rows} of {args.rows} rows x {SWEEP_COLS} per step, 3 timed steps"}
     print(json.dumps(line), flush=True)
     if world > 1:
+        reducer.close()
         dist.destroy_process_group()
 
 
