@@ -276,7 +276,7 @@ def other_ops(torch, peak_gbs, only=None, iterations=40):
     return results
 
 
-def sweep(torch, dist, ops, abi, wl, world: int, rank: int, peak_gbs: float, reducer, iterations: int = 20):
+def sweep(torch, dist, ops, abi, wl, world: int, rank: int, peak_gbs: float, reducer, peers, iterations: int = 20):
     """The whole sweep R = 1024 ... 262144 (16 MiB ... 4 GiB of bf16), row-sharded over the ranks:
     per point the step time (kernel + all-reduce, max over ranks), Gelem/s and GB/s per GPU."""
     points = []
@@ -294,10 +294,16 @@ def sweep(torch, dist, ops, abi, wl, world: int, rank: int, peak_gbs: float, red
         decoded = [torch.empty_like(w[0]) for _ in range(sets)]
 
         def one(i):
+            if peers is not None:
+                abi.check("roundtrip_exchange", lib.hyle_b200_q8_0_roundtrip_bf16_exchange(
+                    stream, w[i % sets].data_ptr(), count, blocks[i % sets].data_ptr(), decoded[i % sets].data_ptr(),
+                    partial.data_ptr(), None, workspace.data_ptr(), workspace.numel(), peers.pointers, world, rank,
+                    peers.next_epoch(), 0))
+                return
             abi.check("roundtrip", lib.hyle_b200_q8_0_roundtrip_bf16(
                 stream, w[i % sets].data_ptr(), count, blocks[i % sets].data_ptr(), decoded[i % sets].data_ptr(),
                 partial.data_ptr(), None, workspace.data_ptr(), workspace.numel()))
-            if world > 1:
+            if reducer is not None:
                 reducer.sum_f64(partial, stream)
 
         for i in range(3):
@@ -422,20 +428,34 @@ def run_gpu(args):
     lib = abi.load()
     stream = torch.cuda.current_stream().cuda_stream
 
-    def step():
-        abi.check("roundtrip", lib.hyle_b200_q8_0_roundtrip_bf16(
-            stream, w.data_ptr(), count, blocks.data_ptr(), decoded.data_ptr(), partial.data_ptr(),
-            status.data_ptr(), workspace.data_ptr(), workspace.numel()))
-
-    reducer = None
+    # The one exchange of the path: 8 bytes per rank.  "fused": the kernel's finishing CTA writes
+    # them into the peers' mailboxes over NVLink and adds what it receives (one kernel per step).
+    # "nccl": kernel, then ncclAllReduce on the same stream.
+    reducer, peers, exchange = None, None, "none"
     if world > 1:
-        from hyle_b200.collective import StreamAllReduce
+        from hyle_b200.collective import PeerExchange, StreamAllReduce
 
-        reducer = StreamAllReduce()
+        if args.exchange == "fused":
+            peers = PeerExchange()
+            exchange = "fused into the kernel: 8-byte stores to peer mailboxes over NVLink, summed in rank order"
+        else:
+            reducer = StreamAllReduce()
+            exchange = "ncclAllReduce of one f64 on the kernels' stream"
+
+    def step():
+        if peers is not None:
+            abi.check("roundtrip_exchange", lib.hyle_b200_q8_0_roundtrip_bf16_exchange(
+                stream, w.data_ptr(), count, blocks.data_ptr(), decoded.data_ptr(), partial.data_ptr(),
+                status.data_ptr(), workspace.data_ptr(), workspace.numel(), peers.pointers, world, rank,
+                peers.next_epoch(), 0))
+        else:
+            abi.check("roundtrip", lib.hyle_b200_q8_0_roundtrip_bf16(
+                stream, w.data_ptr(), count, blocks.data_ptr(), decoded.data_ptr(), partial.data_ptr(),
+                status.data_ptr(), workspace.data_ptr(), workspace.numel()))
 
     def combine():
-        if world > 1:
-            reducer.sum_f64(partial, stream)  # the one exchange of the path: 8 bytes per rank over NVLink
+        if reducer is not None:
+            reducer.sum_f64(partial, stream)
 
     for _ in range(args.warmup):
         step()
@@ -496,12 +516,19 @@ def run_gpu(args):
     if args.sweep:
         del w, blocks, decoded
         torch.cuda.empty_cache()
-        sweep_points = sweep(torch, dist, ops, abi, wl, world, rank, peak_gbs, reducer)
+        sweep_points = sweep(torch, dist, ops, abi, wl, world, rank, peak_gbs, reducer, peers)
+
+    if peers is not None:
+        peers.close()  # collective (it ends with a barrier), so before rank 0 goes on alone
+
+    def shut_down():
+        if world > 1:
+            if reducer is not None:
+                reducer.close()
+            dist.destroy_process_group()
 
     if rank != 0:
-        if world > 1:
-            reducer.close()
-            dist.destroy_process_group()
+        shut_down()
         return
 
     total_elements = args.rows * SWEEP_COLS
@@ -521,7 +548,7 @@ def run_gpu(args):
         "warmup": args.warmup, "ms_per_step": ms_per_step, "higher_is_better": True, "scaling": "strong",
         "vs_baseline": None, "dtype": "bf16->q8_0(int8+f16)", "data": "synthetic",
         "config": {"workload": f"Q8_0 sweep R={args.rows} x {SWEEP_COLS} bf16 -> Q8_0 + decoded bf16 + sum of squares",
-                   "rows_per_gpu": shard.rows, "parallelism": f"row-sharded x{world}, one all-reduce of 8 bytes",
+                   "rows_per_gpu": shard.rows, "parallelism": f"row-sharded x{world}, one exchange of 8 bytes per rank", "exchange": exchange,
                    "l2": "inputs larger than L2 (no flush needed)" if count * 2 > 4 * 126e6 else "input fits L2: cold-cache not guaranteed"},
         "roofline": roofline,
         "e2e": {"value": total_elements / float(e2e_t.item()) / 1e9, "unit": UNIT,
@@ -548,9 +575,7 @@ def run_gpu(args):
             line["cpu_baseline"] = {"value": cpu_value, "unit": UNIT, "cores": cores, "kind": "port",
                                     "sample": f"{rows} of {args.rows} rows x {SWEEP_COLS} per step, 3 timed steps"}
     print(json.dumps(line), flush=True)
-    if world > 1:
-        reducer.close()
-        dist.destroy_process_group()
+    shut_down()
 
 
 def main():
@@ -564,6 +589,8 @@ def main():
     parser.add_argument("--skip-cpu", action="store_true", help="do not time the CPU baseline")
     parser.add_argument("--sweep", action="store_true", help="also time every sweep point R = 1024 ... 262144")
     parser.add_argument("--skip-e2e", action="store_true", help="do not time the host-buffer pass (profiling runs)")
+    parser.add_argument("--exchange", default="fused", choices=["fused", "nccl"],
+                        help="how the per-GPU sums of squares are combined when --gpus > 1")
     parser.add_argument("--ops-only", default=None,
                         help="comma list of add_bias_row_sum_max_f32,add_rms_norm_bf16,swiglu_bf16,logits_reduce_f32: "
                              "time only these, --steps iterations each")

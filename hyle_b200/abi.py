@@ -24,13 +24,16 @@ OK, INVALID_VALUE, NOT_SUPPORTED, STATIC_SCRATCH_EXCEEDED = 0, 1, 801, 100001
 STATIC_MAX_VALUES = 1 << 31
 # enum hyle_b200_status_bits
 STATUS_INVALID_Q8_INPUT = 1
+STATUS_EXCHANGE_TIMEOUT = 2
+EXCHANGE_MAX_RANKS, EXCHANGE_MAILBOX_BYTES, EXCHANGE_HANDLE_BYTES = 8, 256, 64
 
-ABI_VERSION = 2
+ABI_VERSION = 3
 
 _p = ctypes.c_void_p
 _u64 = ctypes.c_uint64
 _i = ctypes.c_int
 _f = ctypes.c_float
+_u32 = ctypes.c_uint32
 
 # name -> (restype, argtypes); the complete export list of include/hyle_b200.h
 SIGNATURES = {
@@ -51,6 +54,12 @@ SIGNATURES = {
     "hyle_b200_sum_squares_bf16": (_i, [_p, _p, _u64, _p, _p, _u64]),
     "hyle_b200_q8_0_roundtrip_bf16": (_i, [_p, _p, _u64, _p, _p, _p, _p, _p, _u64]),
     "hyle_b200_q8_0_roundtrip_bf16_static": (_i, [_p, _p, _u64, _p, _p, _p, _p]),
+    "hyle_b200_q8_0_roundtrip_bf16_exchange": (_i, [_p, _p, _u64, _p, _p, _p, _p, _p, _u64,
+                                                     ctypes.POINTER(_p), _u32, _u32, _u32, _u32]),
+    "hyle_b200_exchange_create": (_i, [ctypes.POINTER(_p), ctypes.c_char_p]),
+    "hyle_b200_exchange_open": (_i, [ctypes.c_char_p, ctypes.POINTER(_p)]),
+    "hyle_b200_exchange_close": (_i, [_p]),
+    "hyle_b200_exchange_destroy": (_i, [_p]),
 }
 
 _library = None

@@ -1,4 +1,8 @@
-"""The one exchange of the sharded sweep: an NCCL all-reduce of the per-GPU sums of squares.
+"""The one exchange of the sharded sweep: the sum over GPUs of the per-GPU sums of squares.
+
+Two forms.  `PeerExchange` sets up what `hyle_b200_q8_0_roundtrip_bf16_exchange` needs: the kernel's
+finishing CTA itself writes the 8 bytes into every peer's mailbox over NVLink and adds what it
+receives, so a step is ONE kernel.  `StreamAllReduce` is the library form, kernel + ncclAllReduce:
 
 `torch.distributed` provides rendezvous; the all-reduce itself is issued straight on the stream the
 kernels run on (ncclAllReduce through ctypes on the NCCL library torch ships), so a step is
@@ -63,3 +67,57 @@ class StreamAllReduce:
             self.lib.ncclCommDestroy.argtypes = [ctypes.c_void_p]
             self.lib.ncclCommDestroy(self.comm)
             self.comm = ctypes.c_void_p()
+
+
+class PeerExchange:
+    """Mailboxes for `hyle_b200_q8_0_roundtrip_bf16_exchange`, one process per GPU.
+
+    Every rank creates a mailbox on its own GPU, the CUDA IPC handles travel through
+    `torch.distributed` (any backend), and every rank maps the others' mailboxes.  `pointers` is the
+    array the entry point takes; `next_epoch()` numbers the collective calls 1, 2, 3, ...
+    """
+
+    def __init__(self):
+        import torch.distributed as dist
+
+        from . import abi
+
+        self.abi = abi
+        self.lib = abi.load()
+        self.world, self.rank = dist.get_world_size(), dist.get_rank()
+        if self.world > abi.EXCHANGE_MAX_RANKS:
+            raise ValueError(f"at most {abi.EXCHANGE_MAX_RANKS} ranks")
+        self.mailbox = ctypes.c_void_p()
+        handle = ctypes.create_string_buffer(abi.EXCHANGE_HANDLE_BYTES)
+        abi.check("hyle_b200_exchange_create", self.lib.hyle_b200_exchange_create(ctypes.byref(self.mailbox), handle))
+        handles = [None] * self.world
+        dist.all_gather_object(handles, handle.raw)
+        self.pointers = (ctypes.c_void_p * self.world)()
+        self.opened = []
+        for peer, raw in enumerate(handles):
+            if peer == self.rank:
+                self.pointers[peer] = self.mailbox.value
+                continue
+            mapped = ctypes.c_void_p()
+            abi.check("hyle_b200_exchange_open", self.lib.hyle_b200_exchange_open(raw, ctypes.byref(mapped)))
+            self.pointers[peer] = mapped.value
+            self.opened.append(mapped)
+        self.epoch = 0
+        dist.barrier()  # nobody starts a step before every mailbox is mapped everywhere
+
+    def next_epoch(self) -> int:
+        self.epoch = self.epoch % 0xFFFFFFFE + 1  # 1 ... 2^32-2, so consecutive values always differ in parity
+        return self.epoch
+
+    def close(self) -> None:
+        import torch
+        import torch.distributed as dist
+
+        torch.cuda.synchronize()
+        dist.barrier()  # no peer is still writing into a mailbox that is about to go
+        for mapped in self.opened:
+            self.lib.hyle_b200_exchange_close(mapped)
+        self.opened = []
+        if self.mailbox:
+            self.lib.hyle_b200_exchange_destroy(self.mailbox)
+            self.mailbox = ctypes.c_void_p()

@@ -13,6 +13,8 @@
 // produces are staged in shared memory and leave as 16-byte coalesced stores.
 #include "common.cuh"
 
+#include <cstring>
+
 namespace hb {
 namespace {
 
@@ -119,6 +121,76 @@ __device__ __forceinline__ DynamicState dynamic_state(void *workspace) {
           reinterpret_cast<double *>(base + kWorkspaceBytes)};
 }
 
+// ---- sum of squares across GPUs: the exchange fused into the kernel's tail -----------------------
+// When the tensor is row-sharded over several GPUs, each GPU's finishing CTA holds that GPU's sum.
+// Instead of ending the kernel and launching a collective, the finishing CTA's first warp sends the
+// eight bytes straight into every peer's mailbox (plain stores to peer-mapped memory, over NVLink)
+// and waits for the peers' values in its own.  Lane r talks to rank r.
+//   mailbox of one rank: words[2 parities][kMaxRanks senders][2], 8 bytes each.  A value travels as
+//   two words {low half, epoch} and {high half, epoch}: an 8-byte store is atomic, so a word whose
+//   epoch matches carries valid data and no fence or separate flag is needed (the same idea as
+//   NCCL's LL protocol).  Consecutive epochs use different parities, so a fast rank that is already
+//   one call ahead never overwrites a word a slow rank is still waiting for; it cannot be two
+//   calls ahead, because its previous call needed the slow rank's word of that call.
+//   The received values are added in rank order, so every rank gets the same bits.
+// Every wait is bounded: after `poll_limit` polls the rank gives up, reports NaN and sets
+// HYLE_B200_STATUS_EXCHANGE_TIMEOUT; the kernel ends normally and the context stays usable.
+constexpr int kMaxRanks = HYLE_B200_EXCHANGE_MAX_RANKS;
+struct Exchange {
+  unsigned long long *mailbox[kMaxRanks];  // mailbox[r]: rank r's mailbox as this GPU addresses it
+  uint32_t world = 0, rank = 0, epoch = 0, poll_limit = 0;
+};
+static_assert(HYLE_B200_EXCHANGE_MAILBOX_BYTES == 2 * kMaxRanks * 2 * 8, "mailbox layout");
+
+__device__ __forceinline__ void store_relaxed_sys(unsigned long long *p, unsigned long long v) {
+  asm volatile("st.relaxed.sys.global.u64 [%0], %1;" ::"l"(__cvta_generic_to_global(p)), "l"(v) : "memory");
+}
+__device__ __forceinline__ unsigned long long load_relaxed_sys(const unsigned long long *p) {
+  unsigned long long v;
+  asm volatile("ld.relaxed.sys.global.u64 %0, [%1];" : "=l"(v) : "l"(__cvta_generic_to_global(p)) : "memory");
+  return v;
+}
+
+// Called by one full warp.  Returns the sum over all ranks (NaN after a timeout) in every lane.
+__device__ __forceinline__ double exchange_sum(double mine, const Exchange &ex, uint32_t *status_word) {
+  const uint32_t lane = threadIdx.x & 31;
+  const unsigned long long epoch = static_cast<unsigned long long>(ex.epoch) << 32;
+  const uint32_t slot = (ex.epoch & 1u) * kMaxRanks;
+  double value = 0.0;
+  bool arrived = true;
+  if (lane < ex.world) {
+    const unsigned long long bits = static_cast<unsigned long long>(__double_as_longlong(mine));
+    unsigned long long *peer = nullptr;
+#pragma unroll
+    for (int r = 0; r < kMaxRanks; ++r)
+      if (lane == r) peer = ex.mailbox[r];
+    unsigned long long *dst = peer + (slot + ex.rank) * 2;
+    store_relaxed_sys(dst, (bits & 0xffffffffull) | epoch);
+    store_relaxed_sys(dst + 1, (bits >> 32) | epoch);
+    unsigned long long *own = nullptr;
+#pragma unroll
+    for (int r = 0; r < kMaxRanks; ++r)
+      if (ex.rank == r) own = ex.mailbox[r];
+    const unsigned long long *src = own + (slot + lane) * 2;
+    unsigned long long low = load_relaxed_sys(src), high = load_relaxed_sys(src + 1);
+    for (uint32_t polls = 0; ((low ^ epoch) >> 32 != 0 || (high ^ epoch) >> 32 != 0) && polls < ex.poll_limit; ++polls) {
+      __nanosleep(64);
+      low = load_relaxed_sys(src);
+      high = load_relaxed_sys(src + 1);
+    }
+    arrived = (low ^ epoch) >> 32 == 0 && (high ^ epoch) >> 32 == 0;
+    value = __longlong_as_double(static_cast<long long>((low & 0xffffffffull) | (high << 32)));
+  }
+  arrived = __all_sync(kFullMask, arrived);
+  double total = 0.0;
+  for (uint32_t r = 0; r < ex.world; ++r) total += __shfl_sync(kFullMask, value, r);  // rank order
+  if (!arrived) {
+    total = __longlong_as_double(0x7ff8000000000000ll);
+    if (lane == 0 && status_word != nullptr) atomicOr(status_word, HYLE_B200_STATUS_EXCHANGE_TIMEOUT);
+  }
+  return total;
+}
+
 // Deterministic grid-wide sum: fixed-order CTA reduction, one partial per CTA, and the CTA that
 // takes the last ticket adds the partials in index order.  Which CTA is last does not matter.
 __device__ __forceinline__ void finish_sum(double thread_sum, SumSquaresState ws, double *sum_out) {
@@ -156,7 +228,7 @@ template <int kDtype, bool kEncode, bool kDecode, bool kSumSquares, bool kDynami
 __global__ void __launch_bounds__(kThreads)
 q8_0_kernel(const void *__restrict__ in, uint64_t blocks, unsigned char *__restrict__ blocks_out,
             unsigned short *__restrict__ decoded, double *sum_out, uint32_t *status_word,
-            void *workspace, int out_aligned) {
+            void *workspace, int out_aligned, const Exchange exchange) {
   grid_dependency_sync();
   __shared__ __align__(16) unsigned char staged[2][kTileBytes];
   const int t = threadIdx.x;
@@ -297,13 +369,16 @@ q8_0_kernel(const void *__restrict__ in, uint64_t blocks, unsigned char *__restr
       acc = warp_sum(acc);
       if ((t & 31) == 0) s_final[t >> 5] = acc;
       __syncthreads();
-      if (t == 0) {
+      if (t < 32) {
         double total = s_final[0];
 #pragma unroll
         for (int w = 1; w < kThreads / 32; ++w) total += s_final[w];
-        *sum_out = total;
-        *dynamic.ticket = 0u;
-        *dynamic.next_tile = 0ull;
+        if (exchange.world > 1) total = exchange_sum(total, exchange, status_word);
+        if (t == 0) {
+          *sum_out = total;
+          *dynamic.ticket = 0u;
+          *dynamic.next_tile = 0ull;
+        }
       }
     }
   } else if constexpr (kSumSquares) {
@@ -424,11 +499,11 @@ extern "C" int hyle_b200_q8_0_encode(hyle_b200_stream_t stream, int dtype, const
   auto *out = static_cast<unsigned char *>(blocks_out);
   int launch_status = HYLE_B200_OK;
   if (dtype == HYLE_B200_BF16)
-    launch_status = launch(q8_0_kernel<HYLE_B200_BF16, true, false, false>, dim3(grid), dim3(kThreads), 0, s, in, blocks, out, nullptr, nullptr, status_word, nullptr, out_aligned);
+    launch_status = launch(q8_0_kernel<HYLE_B200_BF16, true, false, false>, dim3(grid), dim3(kThreads), 0, s, in, blocks, out, nullptr, nullptr, status_word, nullptr, out_aligned, Exchange{});
   else if (dtype == HYLE_B200_F16)
-    launch_status = launch(q8_0_kernel<HYLE_B200_F16, true, false, false>, dim3(grid), dim3(kThreads), 0, s, in, blocks, out, nullptr, nullptr, status_word, nullptr, out_aligned);
+    launch_status = launch(q8_0_kernel<HYLE_B200_F16, true, false, false>, dim3(grid), dim3(kThreads), 0, s, in, blocks, out, nullptr, nullptr, status_word, nullptr, out_aligned, Exchange{});
   else if (dtype == HYLE_B200_F32)
-    launch_status = launch(q8_0_kernel<HYLE_B200_F32, true, false, false>, dim3(grid), dim3(kThreads), 0, s, in, blocks, out, nullptr, nullptr, status_word, nullptr, out_aligned);
+    launch_status = launch(q8_0_kernel<HYLE_B200_F32, true, false, false>, dim3(grid), dim3(kThreads), 0, s, in, blocks, out, nullptr, nullptr, status_word, nullptr, out_aligned, Exchange{});
   else
     return HYLE_B200_INVALID_VALUE;
   return launch_status;
@@ -461,10 +536,13 @@ extern "C" int hyle_b200_sum_squares_bf16(hyle_b200_stream_t stream, const void 
       sum_out, workspace);
 }
 
-extern "C" int hyle_b200_q8_0_roundtrip_bf16(hyle_b200_stream_t stream, const void *in,
-                                             uint64_t count, void *blocks_out, void *decoded_bf16,
-                                             double *sum_squares_out, uint32_t *status_word,
-                                             void *workspace, uint64_t workspace_bytes) {
+namespace {
+// About ten seconds of polling (each poll sleeps at least 64 ns and reads two words through L2).
+constexpr uint32_t kDefaultPollLimit = 1u << 23;
+
+int roundtrip(hyle_b200_stream_t stream, const void *in, uint64_t count, void *blocks_out, void *decoded_bf16,
+              double *sum_squares_out, uint32_t *status_word, void *workspace, uint64_t workspace_bytes,
+              const Exchange &exchange) {
   if (in == nullptr && count != 0) return HYLE_B200_INVALID_VALUE;
   if (blocks_out == nullptr || decoded_bf16 == nullptr || sum_squares_out == nullptr ||
       workspace == nullptr || workspace_bytes < hyle_b200_sum_squares_workspace_bytes(count) ||
@@ -479,7 +557,69 @@ extern "C" int hyle_b200_q8_0_roundtrip_bf16(hyle_b200_stream_t stream, const vo
   return launch(q8_0_kernel<HYLE_B200_BF16, true, true, true, true>, dim3(grid), dim3(kThreads), 0,
                 reinterpret_cast<cudaStream_t>(stream), in, blocks, static_cast<unsigned char *>(blocks_out),
                 static_cast<unsigned short *>(decoded_bf16), sum_squares_out, status_word, workspace,
-                aligned_to(blocks_out, 16));
+                aligned_to(blocks_out, 16), exchange);
+}
+
+}  // namespace
+
+extern "C" int hyle_b200_q8_0_roundtrip_bf16(hyle_b200_stream_t stream, const void *in,
+                                             uint64_t count, void *blocks_out, void *decoded_bf16,
+                                             double *sum_squares_out, uint32_t *status_word,
+                                             void *workspace, uint64_t workspace_bytes) {
+  return roundtrip(stream, in, count, blocks_out, decoded_bf16, sum_squares_out, status_word, workspace,
+                   workspace_bytes, Exchange{});
+}
+
+extern "C" int hyle_b200_q8_0_roundtrip_bf16_exchange(
+    hyle_b200_stream_t stream, const void *in, uint64_t count, void *blocks_out, void *decoded_bf16,
+    double *sum_squares_out, uint32_t *status_word, void *workspace, uint64_t workspace_bytes,
+    void *const *mailboxes, uint32_t world, uint32_t rank, uint32_t epoch, uint32_t poll_limit) {
+  if (world == 0 || world > HYLE_B200_EXCHANGE_MAX_RANKS || rank >= world || epoch == 0 || mailboxes == nullptr)
+    return HYLE_B200_INVALID_VALUE;
+  Exchange exchange{};
+  for (uint32_t r = 0; r < world; ++r) {
+    if (mailboxes[r] == nullptr || !aligned_to(mailboxes[r], 8)) return HYLE_B200_INVALID_VALUE;
+    exchange.mailbox[r] = static_cast<unsigned long long *>(mailboxes[r]);
+  }
+  exchange.world = world;
+  exchange.rank = rank;
+  exchange.epoch = epoch;
+  exchange.poll_limit = poll_limit != 0 ? poll_limit : kDefaultPollLimit;
+  return roundtrip(stream, in, count, blocks_out, decoded_bf16, sum_squares_out, status_word, workspace,
+                   workspace_bytes, exchange);
+}
+
+extern "C" int hyle_b200_exchange_create(void **mailbox, unsigned char *handle_out) {
+  if (mailbox == nullptr || handle_out == nullptr) return HYLE_B200_INVALID_VALUE;
+  static_assert(sizeof(cudaIpcMemHandle_t) == HYLE_B200_EXCHANGE_HANDLE_BYTES, "handle size");
+  void *pointer = nullptr;
+  cudaError_t error = cudaMalloc(&pointer, HYLE_B200_EXCHANGE_MAILBOX_BYTES);
+  if (error != cudaSuccess) return static_cast<int>(error);
+  error = cudaMemset(pointer, 0, HYLE_B200_EXCHANGE_MAILBOX_BYTES);
+  cudaIpcMemHandle_t handle;
+  if (error == cudaSuccess) error = cudaIpcGetMemHandle(&handle, pointer);
+  if (error != cudaSuccess) {
+    cudaFree(pointer);
+    return static_cast<int>(error);
+  }
+  memcpy(handle_out, &handle, sizeof handle);
+  *mailbox = pointer;
+  return HYLE_B200_OK;
+}
+
+extern "C" int hyle_b200_exchange_open(const unsigned char *handle, void **peer_mailbox) {
+  if (handle == nullptr || peer_mailbox == nullptr) return HYLE_B200_INVALID_VALUE;
+  cudaIpcMemHandle_t copy;
+  memcpy(&copy, handle, sizeof copy);
+  return static_cast<int>(cudaIpcOpenMemHandle(peer_mailbox, copy, cudaIpcMemLazyEnablePeerAccess));
+}
+
+extern "C" int hyle_b200_exchange_close(void *peer_mailbox) {
+  return peer_mailbox == nullptr ? HYLE_B200_INVALID_VALUE : static_cast<int>(cudaIpcCloseMemHandle(peer_mailbox));
+}
+
+extern "C" int hyle_b200_exchange_destroy(void *mailbox) {
+  return mailbox == nullptr ? HYLE_B200_INVALID_VALUE : static_cast<int>(cudaFree(mailbox));
 }
 
 // ------------------------------------------------------------------------------------------------
@@ -552,5 +692,5 @@ extern "C" int hyle_b200_q8_0_roundtrip_bf16_static(hyle_b200_stream_t stream, c
   const unsigned grid = clamp_grid(tiles, min(static_cast<uint64_t>(kStaticPartials), static_cast<uint64_t>(sm_count()) * 6));
   return launch(q8_0_kernel<HYLE_B200_BF16, true, true, true>, dim3(grid), dim3(kThreads), 0, s, 
       in, blocks, static_cast<unsigned char *>(blocks_out), static_cast<unsigned short *>(decoded_bf16),
-      sum_squares_out, status_word, scratch, aligned_to(blocks_out, 16));
+      sum_squares_out, status_word, scratch, aligned_to(blocks_out, 16), Exchange{});
 }

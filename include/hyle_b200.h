@@ -42,7 +42,7 @@ extern "C" {
 /* Same object as cudaStream_t; spelled out so C callers need no CUDA header. */
 typedef struct CUstream_st *hyle_b200_stream_t;
 
-#define HYLE_B200_ABI_VERSION 2
+#define HYLE_B200_ABI_VERSION 3
 
 enum hyle_b200_result {
   HYLE_B200_OK = 0,
@@ -83,7 +83,10 @@ enum hyle_b200_softmax_kind {
 enum hyle_b200_status_bits {
   /* Q8_0 encode met a non-finite value or |x| > 65504*127; that block was written as 34 zero
    * bytes (src/compute_provider_ggml/ggml_cpu_provider.cc:596-608). */
-  HYLE_B200_STATUS_INVALID_Q8_INPUT = 1u
+  HYLE_B200_STATUS_INVALID_Q8_INPUT = 1u,
+  /* hyle_b200_q8_0_roundtrip_bf16_exchange: a peer's sum did not arrive within poll_limit polls;
+   * *sum_squares_out is NaN. */
+  HYLE_B200_STATUS_EXCHANGE_TIMEOUT = 2u
 };
 
 HYLE_B200_API int hyle_b200_abi_version(void);
@@ -255,6 +258,51 @@ HYLE_B200_API int hyle_b200_q8_0_roundtrip_bf16_static(hyle_b200_stream_t stream
                                                        uint64_t count, void *blocks_out,
                                                        void *decoded_bf16, double *sum_squares_out,
                                                        uint32_t *status_word);
+
+/* ---------------------------------------------------------------------------------------------
+ * The round trip on a row-sharded tensor, with the cross-GPU sum fused into the kernel.
+ *
+ * Each of `world` GPUs (one process or thread per GPU) calls this on its own shard, all with the
+ * same `epoch`.  The kernel is hyle_b200_q8_0_roundtrip_bf16; where that one stores the shard's
+ * sum of squares, this one's finishing CTA writes it into every rank's MAILBOX (peer-mapped
+ * device memory, plain 8-byte stores over NVLink), waits for the other ranks' sums in its own
+ * mailbox and stores the sum over all ranks, added in rank order: every rank gets the same bits.
+ * It replaces kernel + ncclAllReduce(8 bytes) + the launch gaps around it by one kernel.
+ * (The reference has no multi-GPU form of this path; the partition is the one its Q8_0 block
+ * layout allows: 32-value blocks never cross a row, src/compute_provider_ggml/ggml_cpu_provider.cc:596-608.)
+ *
+ *  mailboxes   host array of `world` device pointers; mailboxes[r] is rank r's mailbox as THIS GPU
+ *              addresses it (for r == rank the local pointer).  A mailbox is
+ *              HYLE_B200_EXCHANGE_MAILBOX_BYTES of device memory, zero-filled once at creation,
+ *              8-byte aligned, used by no one else.  Between processes, map it with the CUDA IPC
+ *              calls (hyle_b200_exchange_* below); within one process, enable peer access and pass
+ *              the pointers as they are.
+ *  world       2..HYLE_B200_EXCHANGE_MAX_RANKS (1 is accepted and exchanges nothing)
+ *  epoch       non-zero, the same on every rank for one collective call, different from the
+ *              previous call's by an odd amount (count calls: 1, 2, 3, ...)
+ *  poll_limit  polls (about 0.1 us apart at least) before a rank gives up on a peer; then its
+ *              *sum_squares_out is NaN and HYLE_B200_STATUS_EXCHANGE_TIMEOUT is set in *status_word.
+ *              The kernel never waits longer than that: no rank can hang a GPU.  0 selects the
+ *              default of about ten seconds.
+ * All ranks must be running the call at the same time on DIFFERENT GPUs (kernels that wait for
+ * each other must not share a GPU).  Everything else is as for hyle_b200_q8_0_roundtrip_bf16.
+ */
+#define HYLE_B200_EXCHANGE_MAX_RANKS 8
+#define HYLE_B200_EXCHANGE_MAILBOX_BYTES 256
+#define HYLE_B200_EXCHANGE_HANDLE_BYTES 64
+HYLE_B200_API int hyle_b200_q8_0_roundtrip_bf16_exchange(
+    hyle_b200_stream_t stream, const void *in, uint64_t count, void *blocks_out, void *decoded_bf16,
+    double *sum_squares_out, uint32_t *status_word, void *workspace, uint64_t workspace_bytes,
+    void *const *mailboxes, uint32_t world, uint32_t rank, uint32_t epoch, uint32_t poll_limit);
+
+/* Mailbox plumbing for one process per GPU, on the current device: create allocates and clears a
+ * mailbox and writes the HYLE_B200_EXCHANGE_HANDLE_BYTES handle another process opens (thin
+ * wrappers over cudaMalloc / cudaIpcGetMemHandle / cudaIpcOpenMemHandle / cudaIpcCloseMemHandle /
+ * cudaFree; these four calls allocate or map memory and belong in set-up code, not in a step). */
+HYLE_B200_API int hyle_b200_exchange_create(void **mailbox, unsigned char *handle_out);
+HYLE_B200_API int hyle_b200_exchange_open(const unsigned char *handle, void **peer_mailbox);
+HYLE_B200_API int hyle_b200_exchange_close(void *peer_mailbox);
+HYLE_B200_API int hyle_b200_exchange_destroy(void *mailbox);
 
 #ifdef __cplusplus
 }
