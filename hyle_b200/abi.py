@@ -27,7 +27,7 @@ STATUS_INVALID_Q8_INPUT = 1
 STATUS_EXCHANGE_TIMEOUT = 2
 EXCHANGE_MAX_RANKS, EXCHANGE_MAILBOX_BYTES, EXCHANGE_HANDLE_BYTES = 8, 256, 64
 
-ABI_VERSION = 3
+ABI_VERSION = 4
 
 _p = ctypes.c_void_p
 _u64 = ctypes.c_uint64
@@ -45,8 +45,9 @@ SIGNATURES = {
     "hyle_b200_rms_norm_bf16": (_i, [_p, _p, _p, _i, _p, _u64, _u64, _f]),
     "hyle_b200_add_rms_norm_bf16": (_i, [_p, _p, _p, _p, _i, _p, _p, _u64, _u64, _f]),
     "hyle_b200_swiglu_bf16": (_i, [_p, _p, _p, _p, _u64, _u64, _u64, _u64]),
-    "hyle_b200_logits_reduce_f32": (_i, [_p, _p, _u64, _u64, _p, _p, _p, _p]),
-    "hyle_b200_softmax_f32": (_i, [_p, _i, _p, _p, _u64, _u64]),
+    "hyle_b200_logits_workspace_bytes": (_u64, [_u64, _u64]),
+    "hyle_b200_logits_reduce_f32": (_i, [_p, _p, _u64, _u64, _p, _p, _p, _p, _p, _u64]),
+    "hyle_b200_softmax_f32": (_i, [_p, _i, _p, _p, _u64, _u64, _p, _u64]),
     "hyle_b200_cast_f32_to_bf16": (_i, [_p, _p, _p, _u64]),
     "hyle_b200_q8_0_encode": (_i, [_p, _i, _p, _u64, _p, _p]),
     "hyle_b200_q8_0_decode_bf16": (_i, [_p, _p, _u64, _p]),

@@ -85,7 +85,7 @@ __device__ __noinline__ void rescan_argmax(const float *whole, uint32_t cols, in
   const int t = threadIdx.x, lane = t & 31, warp = t >> 5;
   Best best{-CUDART_INF_F, kNoIndex};
   uint32_t first_floor = kNoIndex;  // first -inf
-  for (uint32_t i = t; i < cols; i += kThreads) {
+  for (uint32_t i = t; i < cols; i += blockDim.x) {
     const float x = whole[i];
     consider(x, i, best);
     if (x == -CUDART_INF_F && first_floor == kNoIndex) first_floor = i;
@@ -98,7 +98,7 @@ __device__ __noinline__ void rescan_argmax(const float *whole, uint32_t cols, in
   }
   __syncthreads();
   if (t == 0) {
-    for (int w = 1; w < kWarps; ++w) {
+    for (int w = 1; w < static_cast<int>(blockDim.x / 32); ++w) {
       best = better_of(best, s_best[w]);
       first_floor = min(first_floor, s_first[w]);
     }
@@ -600,6 +600,269 @@ logits_regs_kernel(const LogitsParams p) {
   cluster.sync();  // no CTA leaves while a peer may still read its shared memory
 }
 
+// ================================================================================================
+// Streaming path for many rows: two passes over a row, the second one out of L2.
+//
+// The cluster path above keeps 33 rows in flight and every row pays a chain of barriers; with
+// hundreds of rows there is a better trade.  The row is cut into chunks of at most 10 240 values
+// (256 threads x 10 float4, held in registers for the length of one task) and the kernel works
+// through a global, ordered list of chunk TASKS handed out by an atomic counter:
+//   first pass  (row, chunk): load the chunk (kept in L2), chunk maximum, first index of it,
+//                sum of 2^(x log2e - c) against each warp's own maximum -> one 16-byte partial;
+//                fence; count the chunk in row_done[row]
+//   second pass (row, chunk): wait until row_done[row] says all partials are there (bounded),
+//                fold them (every warp by itself, one partial per lane), load the chunk again --
+//                an L2 hit, the row was read a few microseconds ago -- and write the
+//                probabilities (streaming stores).  Chunk 0 also writes lse / argmax.
+// The list interleaves the passes with a fixed lag of `window` rows:
+//   P1(0) ... P1(w-1), P2(0), P1(w), P2(1), P1(w+1), ...            (each entry = all its chunks)
+// so a second-pass task is claimed w x chunks claims after the first-pass tasks it depends on, by
+// which time those have finished (they never wait on anything, and a claimed task is running):
+// the wait is almost always satisfied on the first poll and can never deadlock.  HBM sees every
+// logit once and every probability once; the window (64 rows = 39 MB) stays far below the 126 MB
+// of L2.  No cluster, no shared-memory staging, no barrier between CTAs.
+// ================================================================================================
+constexpr int kStreamThreads = 256;
+constexpr int kStreamWarps = kStreamThreads / 32;
+constexpr int kStreamVectors = 10;
+constexpr uint32_t kStreamChunk = kStreamThreads * kStreamVectors * 4;  // values per chunk, at most
+constexpr uint32_t kStreamMaxChunks = 32;                               // one partial per lane
+constexpr uint32_t kStreamWindow = 64;
+constexpr uint64_t kStreamMinRows = 32;
+constexpr uint32_t kStreamPollLimit = 1u << 22;
+constexpr uint64_t kStreamHeaderBytes = 64;
+
+enum StreamPass : uint32_t { kStreamFirst = 0, kStreamSecond = 1, kStreamEnd = 2 };
+struct StreamTask {
+  uint64_t row;
+  uint32_t chunk_id;
+  uint32_t pass;
+};
+
+struct StreamParams {
+  LogitsParams p;
+  uint32_t chunks;  // per row
+  uint32_t chunk;   // values per chunk, a multiple of 16
+  uint32_t window;  // rows between the passes, at most p.rows
+  unsigned long long *next_task;
+  uint32_t *ticket;
+  uint32_t *row_done;   // [rows]
+  WarpEntry *partials;  // [rows][chunks]
+};
+
+__host__ __device__ inline uint32_t stream_chunks(uint64_t cols) {
+  return static_cast<uint32_t>((cols + kStreamChunk - 1) / kStreamChunk);
+}
+__host__ __device__ inline uint64_t stream_counter_bytes(uint64_t rows) { return (rows * 4 + 15) / 16 * 16; }
+
+__device__ __forceinline__ float4 load_keep(const float4 *p) {  // stays in L2 for the second pass
+  float4 v;
+  asm volatile("ld.global.nc.L1::no_allocate.v4.f32 {%0, %1, %2, %3}, [%4];"
+               : "=f"(v.x), "=f"(v.y), "=f"(v.z), "=f"(v.w)
+               : "l"(p));
+  return v;
+}
+
+template <int kMode, int kFull>
+__global__ void __launch_bounds__(kStreamThreads, 4)
+logits_stream_kernel(const StreamParams s) {
+  grid_dependency_sync();
+  __shared__ WarpEntry s_entry[kStreamWarps];
+  __shared__ StreamTask s_tasks[2];
+  __shared__ uint32_t s_flag;
+  const LogitsParams &p = s.p;
+  const int t = threadIdx.x, lane = t & 31, warp = t >> 5;
+  const bool want_index = p.index != nullptr || p.value != nullptr;
+  const float neg_inf = -CUDART_INF_F;
+  const WarpEntry nothing{neg_inf, 0.0f, kNoIndex, 0u};
+
+  // Position `task` of the ordered list -> (pass, row, chunk).  Thread 0 does this (a 64-bit
+  // division) for the NEXT task while the CTA works on the current one.
+  auto decode = [&](uint64_t task) {
+    const uint64_t paired = p.rows - s.window;  // rows whose first pass is interleaved with a second pass
+    StreamTask r;
+    if (task >= 2 * p.rows * s.chunks) {
+      r.row = 0;
+      r.chunk_id = 0;
+      r.pass = kStreamEnd;
+      return r;
+    }
+    const uint64_t entry = task / s.chunks;
+    r.chunk_id = static_cast<uint32_t>(task - entry * s.chunks);
+    if (entry < s.window) {
+      r.pass = kStreamFirst;
+      r.row = entry;
+    } else if (entry < s.window + 2 * paired) {
+      const bool second = ((entry - s.window) & 1) == 0;
+      r.pass = second ? kStreamSecond : kStreamFirst;
+      r.row = (entry - s.window) / 2 + (second ? 0 : s.window);
+    } else {
+      r.pass = kStreamSecond;
+      r.row = paired + (entry - s.window - 2 * paired);
+    }
+    return r;
+  };
+  auto claim_next = [&](int into) {
+    if (t == 0) s_tasks[into] = decode(gridDim.x + atomicAdd(s.next_task, 1ull));
+  };
+
+  if (t == 0) s_tasks[0] = decode(blockIdx.x);  // the first task of every CTA is fixed
+  __syncthreads();
+  int buffer = 0;
+  for (;;) {
+    const StreamTask now = s_tasks[buffer];
+    if (now.pass == kStreamEnd) break;
+    const bool second = now.pass == kStreamSecond;
+    const uint64_t row = now.row;
+    const uint32_t chunk_id = now.chunk_id;
+    const uint32_t begin = chunk_id * s.chunk;
+    const uint32_t vectors = (min(begin + s.chunk, p.cols) - begin) / 4;
+    const float4 *src = reinterpret_cast<const float4 *>(p.in + row * p.cols + begin) + t;
+
+    if (!second) {
+      float4 x[kStreamVectors];
+#pragma unroll
+      for (int j = 0; j < kStreamVectors; ++j)
+        x[j] = (j < kFull || j * kStreamThreads + t < vectors) ? load_keep(src + j * kStreamThreads) : make_float4(neg_inf, neg_inf, neg_inf, neg_inf);
+      claim_next(buffer ^ 1);  // after the loads are in flight
+      float thread_max = neg_inf;
+      int best_slot = 0;
+#pragma unroll
+      for (int j = 0; j < kStreamVectors; ++j) {
+        const float slot_max = max_nan(max_nan(x[j].x, x[j].y), max_nan(x[j].z, x[j].w));
+        if (slot_max > thread_max) best_slot = j;
+        thread_max = max_nan(thread_max, slot_max);
+      }
+      const float warp_max = warp_max_nan(thread_max);
+      uint32_t index = kNoIndex;
+      if (want_index) {
+        if (thread_max == warp_max) {  // a few lanes; never true for NaN.  The float4 is still in L2.
+          const float4 v = load_keep(src + best_slot * kStreamThreads);
+          const uint32_t base = begin + (best_slot * kStreamThreads + t) * 4;
+          index = v.x == warp_max ? base : v.y == warp_max ? base + 1 : v.z == warp_max ? base + 2 : base + 3;
+        }
+        index = __reduce_min_sync(kFullMask, index);
+      }
+      const float reference = warp_max == neg_inf ? 0.0f : warp_max;
+      const float neg_c = -__fmul_rn(reference, kLog2e);
+      float thread_sum = 0.0f;
+#pragma unroll
+      for (int j = 0; j < kStreamVectors; ++j)
+        thread_sum += (exp2_approx(fmaf(x[j].x, kLog2e, neg_c)) + exp2_approx(fmaf(x[j].y, kLog2e, neg_c))) +
+                      (exp2_approx(fmaf(x[j].z, kLog2e, neg_c)) + exp2_approx(fmaf(x[j].w, kLog2e, neg_c)));
+      const float warp_total = warp_sum(thread_sum);
+      if (lane == 0) s_entry[warp] = WarpEntry{warp_max, warp_total, index, 0u};
+      __syncthreads();
+      if (warp == 0) {
+        const Combined cta = combine(lane < kStreamWarps ? s_entry[lane] : nothing);
+        if (lane == 0) {
+          s.partials[row * s.chunks + chunk_id] = WarpEntry{cta.maximum, cta.total, cta.index, 0u};
+          __threadfence();  // the partial is visible before it is counted
+          atomicAdd(s.row_done + row, 1u);
+        }
+      }
+    } else {
+      if (t == 0) {
+        const volatile uint32_t *done = s.row_done + row;
+        uint32_t polls = 0;
+        while (*done != s.chunks && polls < kStreamPollLimit) ++polls;
+        s_flag = *done == s.chunks;
+        __threadfence();
+      }
+      claim_next(buffer ^ 1);
+      __syncthreads();
+      const bool complete = s_flag != 0u;
+      WarpEntry mine = nothing;
+      if (lane < s.chunks) {
+        const uint4 raw = __ldcg(reinterpret_cast<const uint4 *>(s.partials + row * s.chunks + lane));
+        mine = WarpEntry{__uint_as_float(raw.x), __uint_as_float(raw.y), raw.z, 0u};
+      }
+      const Combined all = combine(mine);
+      const float maximum = all.maximum, total_sum = all.total, row_c = __fmul_rn(all.maximum, kLog2e);
+      const bool valid = complete && maximum > neg_inf && maximum < CUDART_INF_F;  // false for NaN too
+      const bool has_nan = maximum != maximum;
+      const float nan = CUDART_NAN_F;
+      const float residual = fmaf(maximum, kLog2e, -row_c);
+      const float shift = valid ? maximum + (logf(total_sum) - residual * 0.6931471805599453f) : nan;
+      if (chunk_id == 0 && t == 0) {
+        if (p.lse != nullptr) p.lse[row] = shift;
+        if (want_index && !has_nan && complete) {
+          if (p.index != nullptr) p.index[row] = static_cast<int32_t>(all.index);
+          if (p.value != nullptr) p.value[row] = maximum;
+        }
+      }
+      const float inverse = valid ? __fdiv_rn(1.0f, total_sum) : nan;
+      const float neg_row_c = -row_c;
+      if constexpr (kMode == kProbsBf16) {
+        uint2 *dst = reinterpret_cast<uint2 *>(static_cast<unsigned short *>(p.out) + row * p.cols + begin) + t;
+#pragma unroll
+        for (int half = 0; half < 2; ++half) {  // two batches of five loads: fewer live registers than ten
+          float4 x[kStreamVectors / 2];
+#pragma unroll
+          for (int j = 0; j < kStreamVectors / 2; ++j) {
+            const int slot = half * (kStreamVectors / 2) + j;
+            if (slot < kFull || slot * kStreamThreads + t < vectors) x[j] = ld_stream(src + slot * kStreamThreads);
+          }
+#pragma unroll
+          for (int j = 0; j < kStreamVectors / 2; ++j) {
+            const int slot = half * (kStreamVectors / 2) + j;
+            if (slot < kFull || slot * kStreamThreads + t < vectors)
+              st_stream(dst + slot * kStreamThreads,
+                        make_uint2(pack_bf16x2(exp2_approx(fmaf(x[j].x, kLog2e, neg_row_c)) * inverse,
+                                               exp2_approx(fmaf(x[j].y, kLog2e, neg_row_c)) * inverse),
+                                   pack_bf16x2(exp2_approx(fmaf(x[j].z, kLog2e, neg_row_c)) * inverse,
+                                               exp2_approx(fmaf(x[j].w, kLog2e, neg_row_c)) * inverse)));
+          }
+        }
+      } else {
+        float4 *dst = reinterpret_cast<float4 *>(static_cast<float *>(p.out) + row * p.cols + begin) + t;
+#pragma unroll
+        for (int half = 0; half < 2; ++half) {
+          float4 x[kStreamVectors / 2];
+#pragma unroll
+          for (int j = 0; j < kStreamVectors / 2; ++j) {
+            const int slot = half * (kStreamVectors / 2) + j;
+            if (slot < kFull || slot * kStreamThreads + t < vectors) x[j] = ld_stream(src + slot * kStreamThreads);
+          }
+#pragma unroll
+          for (int j = 0; j < kStreamVectors / 2; ++j) {
+            const int slot = half * (kStreamVectors / 2) + j;
+            if (slot < kFull || slot * kStreamThreads + t < vectors) {
+              float4 o;
+              if constexpr (kMode == kProbsF32)
+                o = make_float4(exp2_approx(fmaf(x[j].x, kLog2e, neg_row_c)) * inverse, exp2_approx(fmaf(x[j].y, kLog2e, neg_row_c)) * inverse,
+                                exp2_approx(fmaf(x[j].z, kLog2e, neg_row_c)) * inverse, exp2_approx(fmaf(x[j].w, kLog2e, neg_row_c)) * inverse);
+              else
+                o = make_float4(x[j].x - shift, x[j].y - shift, x[j].z - shift, x[j].w - shift);
+              st_stream(dst + slot * kStreamThreads, o);
+            }
+          }
+        }
+      }
+      // NaN rows take the full TopK order from global memory (CTA-uniform condition).
+      if (chunk_id == 0 && want_index && has_nan)
+        rescan_argmax(p.in + row * p.cols, p.cols, p.index != nullptr ? p.index + row : nullptr,
+                      p.value != nullptr ? p.value + row : nullptr);
+    }
+    __syncthreads();  // the next claim is visible; s_entry and s_flag may be reused
+    buffer ^= 1;
+  }
+
+  // The CTA that leaves last re-arms the workspace for the next stream-ordered launch.
+  if (t == 0) {
+    __threadfence();
+    s_flag = atomicAdd(s.ticket, 1u) == gridDim.x - 1;
+  }
+  __syncthreads();
+  if (s_flag != 0u) {
+    for (uint64_t i = t; i < p.rows; i += kStreamThreads) s.row_done[i] = 0u;
+    if (t == 0) {
+      *s.next_task = 0ull;
+      *s.ticket = 0u;
+    }
+  }
+}
+
 struct Plan {
   int cluster;
   uint32_t slice;
@@ -669,9 +932,41 @@ int resident_clusters(int cluster) {
   return cached[slot][device];
 }
 
+uint64_t stream_workspace_bytes(uint64_t rows, uint64_t cols) {
+  return kStreamHeaderBytes + stream_counter_bytes(rows) + rows * stream_chunks(cols) * sizeof(WarpEntry);
+}
+
 template <int kMode>
-int launch_logits(cudaStream_t stream, LogitsParams p, bool vec) {
+int launch_stream(cudaStream_t stream, const LogitsParams &p, void *workspace) {
+  StreamParams s{};
+  s.p = p;
+  s.chunks = stream_chunks(p.cols);
+  s.chunk = (p.cols / s.chunks + 15) / 16 * 16;
+  if (static_cast<uint64_t>(s.chunk) * s.chunks < p.cols) s.chunk += 16;
+  s.window = static_cast<uint32_t>(p.rows < kStreamWindow ? p.rows : kStreamWindow);
+  unsigned char *base = static_cast<unsigned char *>(workspace);
+  s.next_task = reinterpret_cast<unsigned long long *>(base);
+  s.ticket = reinterpret_cast<uint32_t *>(base + 8);
+  s.row_done = reinterpret_cast<uint32_t *>(base + kStreamHeaderBytes);
+  s.partials = reinterpret_cast<WarpEntry *>(base + kStreamHeaderBytes + stream_counter_bytes(p.rows));
+  const uint64_t tasks = 2 * p.rows * s.chunks;
+  const unsigned grid = clamp_grid(tasks, static_cast<uint64_t>(sm_count()) * 4);
+  const uint32_t last = p.cols - (s.chunks - 1) * s.chunk;  // the shortest chunk
+  const bool nine_full = s.chunk / 4 >= 9u * kStreamThreads && last / 4 >= 9u * kStreamThreads;
+  return launch(nine_full ? logits_stream_kernel<kMode, 9> : logits_stream_kernel<kMode, 0>, dim3(grid),
+                dim3(kStreamThreads), 0, stream, s);
+}
+
+template <int kMode>
+int launch_logits(cudaStream_t stream, LogitsParams p, bool vec, void *workspace, uint64_t workspace_bytes) {
   if (p.cols == 0) return HYLE_B200_NOT_SUPPORTED;
+  if constexpr (kMode != kArgmaxOnly) {
+    // Many rows with an output tensor: the two-pass streaming kernel (needs the caller's workspace).
+    if (vec && p.out != nullptr && p.out != static_cast<const void *>(p.in) && workspace != nullptr && p.rows >= kStreamMinRows && p.cols % 16 == 0 &&
+        stream_chunks(p.cols) <= kStreamMaxChunks && p.cols >= kStreamThreads * 4 &&
+        workspace_bytes >= stream_workspace_bytes(p.rows, p.cols))
+      return launch_stream<kMode>(stream, p, workspace);
+  }
   if constexpr (kMode != kArgmaxOnly) {
     // Register-resident fast path: aligned rows of at most 8 x 20480 values.
     if (vec && p.cols <= static_cast<uint64_t>(kMaxCluster) * kRegSlice) {
@@ -704,27 +999,35 @@ int launch_logits(cudaStream_t stream, LogitsParams p, bool vec) {
 
 using namespace hb;
 
+extern "C" uint64_t hyle_b200_logits_workspace_bytes(uint64_t rows, uint64_t cols) {
+  return stream_workspace_bytes(rows, cols);
+}
+
 extern "C" int hyle_b200_logits_reduce_f32(hyle_b200_stream_t stream, const float *logits,
                                            uint64_t rows, uint64_t cols, float *lse,
                                            void *probs_bf16, int32_t *argmax_index,
-                                           float *argmax_value) {
+                                           float *argmax_value, void *workspace,
+                                           uint64_t workspace_bytes) {
   if (rows == 0) return HYLE_B200_OK;
   if (logits == nullptr || cols == 0 || cols > 0x7fffffffull) return HYLE_B200_INVALID_VALUE;
+  if (workspace != nullptr && !aligned_to(workspace, 16)) return HYLE_B200_INVALID_VALUE;
   LogitsParams p{logits, rows, static_cast<uint32_t>(cols), 0, lse, probs_bf16, argmax_index, argmax_value};
   const bool vec = aligned_to(logits, 16) && cols % 8 == 0 && (probs_bf16 == nullptr || aligned_to(probs_bf16, 16));
   auto s = reinterpret_cast<cudaStream_t>(stream);
-  if (lse == nullptr && probs_bf16 == nullptr) return launch_logits<kArgmaxOnly>(s, p, vec);
-  return launch_logits<kProbsBf16>(s, p, vec);
+  if (lse == nullptr && probs_bf16 == nullptr) return launch_logits<kArgmaxOnly>(s, p, vec, nullptr, 0);
+  return launch_logits<kProbsBf16>(s, p, vec, workspace, workspace_bytes);
 }
 
 extern "C" int hyle_b200_softmax_f32(hyle_b200_stream_t stream, int kind, const float *in,
-                                     float *out, uint64_t rows, uint64_t cols) {
+                                     float *out, uint64_t rows, uint64_t cols, void *workspace,
+                                     uint64_t workspace_bytes) {
   if (rows == 0 || cols == 0) return HYLE_B200_OK;
   if (in == nullptr || out == nullptr || cols > 0x7fffffffull) return HYLE_B200_INVALID_VALUE;
+  if (workspace != nullptr && !aligned_to(workspace, 16)) return HYLE_B200_INVALID_VALUE;
   LogitsParams p{in, rows, static_cast<uint32_t>(cols), 0, nullptr, out, nullptr, nullptr};
   const bool vec = aligned_to(in, 16) && aligned_to(out, 16) && cols % 8 == 0;
   auto s = reinterpret_cast<cudaStream_t>(stream);
-  if (kind == HYLE_B200_SOFTMAX) return launch_logits<kProbsF32>(s, p, vec);
-  if (kind == HYLE_B200_LOG_SOFTMAX) return launch_logits<kLogF32>(s, p, vec);
+  if (kind == HYLE_B200_SOFTMAX) return launch_logits<kProbsF32>(s, p, vec, workspace, workspace_bytes);
+  if (kind == HYLE_B200_LOG_SOFTMAX) return launch_logits<kLogF32>(s, p, vec, workspace, workspace_bytes);
   return HYLE_B200_INVALID_VALUE;
 }

@@ -152,12 +152,19 @@ def swiglu_packed(packed: torch.Tensor) -> torch.Tensor:
     return out
 
 
+def make_logits_workspace(device, rows: int, cols: int) -> torch.Tensor:
+    """Zero-filled scratch for `logits_reduce` / `softmax` on batches of 32 rows or more (the
+    streaming kernel); reusable by any number of stream-ordered calls of at most this shape."""
+    return torch.zeros(abi.load().hyle_b200_logits_workspace_bytes(rows, cols), dtype=torch.uint8, device=device)
+
+
 def logits_reduce(logits: torch.Tensor, want_probs: bool = True, want_lse: bool = True,
-                  want_argmax: bool = True):
+                  want_argmax: bool = True, workspace: Optional[torch.Tensor] = None):
     """Fused log-sum-exp, softmax->bf16 and argmax of f32 [rows, cols] logits.
 
     Returns (lse f32[rows], probs bf16[rows, cols], index i32[rows], value f32[rows]); entries not
-    asked for are None.
+    asked for are None.  With a `workspace` (`make_logits_workspace`) large batches take the
+    streaming kernel; without one every batch takes the cluster kernel.
     """
     _device_tensor(logits, "logits")
     if logits.dtype != torch.float32 or logits.dim() != 2:
@@ -169,7 +176,8 @@ def logits_reduce(logits: torch.Tensor, want_probs: bool = True, want_lse: bool 
     index = torch.empty(rows, dtype=torch.int32, device=dev) if want_argmax else None
     value = torch.empty(rows, dtype=torch.float32, device=dev) if want_argmax else None
     abi.check("hyle_b200_logits_reduce_f32", abi.load().hyle_b200_logits_reduce_f32(
-        _stream(), logits.data_ptr(), rows, cols, _ptr(lse), _ptr(probs), _ptr(index), _ptr(value)))
+        _stream(), logits.data_ptr(), rows, cols, _ptr(lse), _ptr(probs), _ptr(index), _ptr(value),
+        _ptr(workspace), 0 if workspace is None else workspace.numel()))
     return lse, probs, index, value
 
 
@@ -179,7 +187,8 @@ def argmax(logits: torch.Tensor) -> Tuple[torch.Tensor, torch.Tensor]:
     return index, value
 
 
-def softmax(x: torch.Tensor, log: bool = False, out: Optional[torch.Tensor] = None) -> torch.Tensor:
+def softmax(x: torch.Tensor, log: bool = False, out: Optional[torch.Tensor] = None,
+            workspace: Optional[torch.Tensor] = None) -> torch.Tensor:
     """Softmax{axis=-1, kSoftmax|kLogSoftmax} on f32 rows, f32 output."""
     _device_tensor(x, "x")
     if x.dtype != torch.float32:
@@ -189,7 +198,8 @@ def softmax(x: torch.Tensor, log: bool = False, out: Optional[torch.Tensor] = No
     if out is None:
         out = torch.empty_like(x)
     abi.check("hyle_b200_softmax_f32", abi.load().hyle_b200_softmax_f32(
-        _stream(), abi.LOG_SOFTMAX if log else abi.SOFTMAX, x.data_ptr(), out.data_ptr(), rows, cols))
+        _stream(), abi.LOG_SOFTMAX if log else abi.SOFTMAX, x.data_ptr(), out.data_ptr(), rows, cols,
+        _ptr(workspace), 0 if workspace is None else workspace.numel()))
     return out
 
 

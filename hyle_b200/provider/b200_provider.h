@@ -161,6 +161,7 @@ inline std::optional<Plan> match(const Operation &op, std::span<const TensorDesc
       return std::nullopt;
     p.entry = Entry::kSoftmax;
     p.kind = softmax->kind == SoftmaxKind::kLogSoftmax ? HYLE_B200_LOG_SOFTMAX : HYLE_B200_SOFTMAX;
+    p.workspace_bytes = static_cast<std::size_t>(hyle_b200_logits_workspace_bytes(p.rows, p.cols));
     return p;
   }
   if (const auto *cast = op.get_if<Cast>()) {
@@ -209,6 +210,7 @@ inline std::optional<Plan> match(const Operation &op, std::span<const TensorDesc
   if (op.custom_as<LogitsReduce>()) {
     if (in.size() != 1 || out.size() != 4 || in[0].data_type() != DataType::kFloat32) return std::nullopt;
     p.entry = Entry::kLogitsReduce;
+    p.workspace_bytes = static_cast<std::size_t>(hyle_b200_logits_workspace_bytes(p.rows, p.cols));
     return p;
   }
   if (op.custom_as<Q8_0Roundtrip>()) {
@@ -239,12 +241,12 @@ inline int launch(const Plan &p, hyle_b200_stream_t stream, const void *const *i
     }
     case Entry::kSoftmax:
       return hyle_b200_softmax_f32(stream, p.kind, static_cast<const float *>(in[0]), static_cast<float *>(out[0]),
-                                   p.rows, p.cols);
+                                   p.rows, p.cols, workspace, p.workspace_bytes);
     case Entry::kCastF32ToBf16:
       return hyle_b200_cast_f32_to_bf16(stream, static_cast<const float *>(in[0]), out[0], p.count);
     case Entry::kArgmax:
       return hyle_b200_logits_reduce_f32(stream, static_cast<const float *>(in[0]), p.rows, p.cols, nullptr, nullptr,
-                                         static_cast<std::int32_t *>(out[1]), static_cast<float *>(out[0]));
+                                         static_cast<std::int32_t *>(out[1]), static_cast<float *>(out[0]), nullptr, 0);
     case Entry::kQ8Encode:
       return hyle_b200_q8_0_encode(stream, p.dtype, in[0], p.count, out[0], nullptr);
     case Entry::kAddRmsNorm:
@@ -258,7 +260,7 @@ inline int launch(const Plan &p, hyle_b200_stream_t stream, const void *const *i
     case Entry::kLogitsReduce:
       return hyle_b200_logits_reduce_f32(stream, static_cast<const float *>(in[0]), p.rows, p.cols,
                                          static_cast<float *>(out[0]), out[1], static_cast<std::int32_t *>(out[2]),
-                                         static_cast<float *>(out[3]));
+                                         static_cast<float *>(out[3]), workspace, p.workspace_bytes);
     case Entry::kQ8Roundtrip:
       return hyle_b200_q8_0_roundtrip_bf16(stream, in[0], p.count, out[0], out[1], static_cast<double *>(out[2]),
                                            nullptr, workspace, p.workspace_bytes);

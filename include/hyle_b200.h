@@ -42,7 +42,7 @@ extern "C" {
 /* Same object as cudaStream_t; spelled out so C callers need no CUDA header. */
 typedef struct CUstream_st *hyle_b200_stream_t;
 
-#define HYLE_B200_ABI_VERSION 3
+#define HYLE_B200_ABI_VERSION 4
 
 enum hyle_b200_result {
   HYLE_B200_OK = 0,
@@ -170,18 +170,28 @@ HYLE_B200_API int hyle_b200_swiglu_bf16(hyle_b200_stream_t stream, const void *g
  * Cast include/hyle/compute/operation.h:289-295, TopK include/hyle/compute/operation.h:411-417 with
  * src/simd/sort/top_k.cc:17-27,51-69.
  * Rows holding NaN or +inf, or only -inf, get NaN lse and NaN probs (include/hyle/simd/math.h:307-311);
- * argmax is still defined for them.  Any output pointer may be NULL.  The kernel keeps each row in
- * shared memory across a thread-block cluster; rows too wide for that return NOT_SUPPORTED.
+ * argmax is still defined for them.  Any output pointer may be NULL.
+ *
+ * Two kernels.  Without a workspace, or for fewer than 32 rows, a thread-block cluster keeps each
+ * row in registers / shared memory (rows too wide for that return NOT_SUPPORTED).  With a
+ * workspace of hyle_b200_logits_workspace_bytes(rows, cols) bytes (16-byte aligned, zero-filled
+ * once after allocation; each launch leaves it zeroed again; stream-ordered launches only) and an
+ * output tensor, batches of 32 rows or more take a two-pass streaming kernel whose second pass
+ * reads the row back from L2: HBM traffic is the same, throughput is higher.
  */
+HYLE_B200_API uint64_t hyle_b200_logits_workspace_bytes(uint64_t rows, uint64_t cols);
 HYLE_B200_API int hyle_b200_logits_reduce_f32(hyle_b200_stream_t stream, const float *logits,
                                               uint64_t rows, uint64_t cols, float *lse,
                                               void *probs_bf16, int32_t *argmax_index,
-                                              float *argmax_value);
+                                              float *argmax_value, void *workspace,
+                                              uint64_t workspace_bytes);
 
 /* Softmax{axis=-1, kind} with f32 output (output dtype = input dtype,
- * src/compute_ops/operation.cc:1619). out may alias in. */
+ * src/compute_ops/operation.cc:1619). out may alias in (the cluster kernel is used then).
+ * workspace: as for hyle_b200_logits_reduce_f32, may be NULL. */
 HYLE_B200_API int hyle_b200_softmax_f32(hyle_b200_stream_t stream, int kind, const float *in,
-                                        float *out, uint64_t rows, uint64_t cols);
+                                        float *out, uint64_t rows, uint64_t cols, void *workspace,
+                                        uint64_t workspace_bytes);
 
 /* Cast{f32 -> bf16}, round to nearest even (include/hyle/simd/dtype.h:114-121). */
 HYLE_B200_API int hyle_b200_cast_f32_to_bf16(hyle_b200_stream_t stream, const float *in,

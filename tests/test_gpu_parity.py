@@ -238,8 +238,8 @@ def test_swiglu_specials_packed_and_odd_shapes(oracle, ):
 
 
 # ---- workload 4: logits -> lse, softmax bf16, argmax ----------------------------------------------------------------------
-def check_logits(oracle, logits):
-    lse, probs, index, value = ops.logits_reduce(to_dev(logits))
+def check_logits(oracle, logits, workspace=None):
+    lse, probs, index, value = ops.logits_reduce(to_dev(logits), workspace=workspace)
     want_lse, want_p, want_p32, want_i, want_v = oracle.logits_reduce(logits)
     assert np.array_equal(index.cpu().numpy(), want_i)                  # bit-exact, lowest index on ties
     assert_f32_bits(value.cpu().numpy(), want_v)
@@ -280,6 +280,44 @@ def test_logits_config_256_rows_against_size_independent_properties(oracle):
     # standalone argmax and f32 softmax agree with the fused launch
     idx2, val2 = ops.argmax(dev)
     assert torch.equal(idx2, index) and torch.equal(val2, value)
+    # the streaming kernel (taken when a workspace is given) against the same checks
+    scratch = ops.make_logits_workspace("cuda", 256, logits.shape[1])
+    for _ in range(2):  # twice: every launch leaves the workspace re-armed
+        lse_s, probs_s, index_s, value_s = ops.logits_reduce(dev, workspace=scratch)
+        assert torch.equal(index_s, index) and torch.equal(value_s, value)
+        assert np.all(np.abs(lse_s.cpu().numpy()[rows] - want_lse) <= F32_REL * np.abs(want_lse))
+        assert_bf16_close(bf16_words(probs_s[rows]), want_p, want_p32, BF16_REL)
+        assert np.all(np.abs(probs_s.float().sum(dim=1).cpu().numpy() - 1.0) < 2e-3)
+
+
+@pytest.mark.parametrize("cols", [1024, 4112, 19456, 40000, 151936, 327680])
+def test_logits_streaming_kernel_shapes_and_invalid_rows(oracle, cols):
+    """Batches of 32 rows or more with a workspace take the two-pass streaming kernel."""
+    rng = np.random.default_rng(cols + 1)
+    rows = 40 if cols <= 151936 else 33
+    x = (4.0 * rng.standard_normal((rows, cols))).astype(np.float32)
+    x[1] *= 20.0
+    x[2, cols // 2] = np.nan
+    x[3, cols - 1] = np.inf
+    x[4, :] = -np.inf
+    x[5, 0] = -np.inf
+    x[6, :] = np.nan; x[6, cols - 2] = -np.inf
+    x[7, 5] = x[7, cols - 3] = x[7].max() + 1.0          # a tie across chunks: the lower index wins
+    x[8, : cols // 2] = -np.inf                           # whole chunks at -inf
+    x[rows - 1, cols - 1] = 1000.0                        # maximum in the last element of the last row
+    scratch = ops.make_logits_workspace("cuda", rows, cols)
+    for _ in range(2):
+        index = check_logits(oracle, x, workspace=scratch)
+    assert int(index[7]) == 5
+    for log in (False, True):
+        got = ops.softmax(to_dev(x), log=log, workspace=scratch).cpu().numpy()
+        want = oracle.softmax(x, log=log)
+        assert np.array_equal(np.isnan(got), np.isnan(want))
+        ok = np.isfinite(want)
+        tol = F32_REL * np.abs(want[ok]) + (1e-5 if log else 1e-37)
+        assert np.all(np.abs(got[ok] - want[ok]) <= tol)
+    # a smaller batch reuses the same workspace
+    check_logits(oracle, x[:32], workspace=scratch)
 
 
 @pytest.mark.parametrize("cols", [1, 7, 8, 1000, 1024, 19000, 19456, 40000, 151936, 262144])
