@@ -14,7 +14,7 @@ from .build import LIBRARY_PATH
 # enum hyle_b200_dtype
 F32, BF16, F16 = 0, 1, 2
 # enum hyle_b200_binary_kind
-BINARY_ADD, BINARY_MULTIPLY = 0, 1
+BINARY_ADD, BINARY_MULTIPLY, BINARY_SUBTRACT, BINARY_DIVIDE, BINARY_MINIMUM, BINARY_MAXIMUM = 0, 1, 2, 3, 4, 5
 # enum hyle_b200_reduce_kind
 REDUCE_SUM, REDUCE_MEAN, REDUCE_MINIMUM, REDUCE_MAXIMUM = 0, 1, 2, 3
 # enum hyle_b200_softmax_kind

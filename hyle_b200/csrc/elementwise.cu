@@ -1,4 +1,4 @@
-// Streaming elementwise operators: Binary{kAdd|kMultiply} with trailing-axis broadcast,
+// Streaming elementwise operators: Binary{all six kinds} with trailing-axis broadcast,
 // GatedActivation{kSilu} (SwiGLU) and Cast{f32->bf16}.  All are HBM-bound: every thread keeps
 // several independent 16-byte loads in flight, computes in f32 and writes 16-byte vectors.
 #include "common.cuh"
@@ -14,7 +14,17 @@ constexpr int kCtasPerSm = 8;    // 8 x 256 threads fill an SM
 template <int kKind>
 __device__ __forceinline__ float binary_op(float a, float b) {
   if constexpr (kKind == HYLE_B200_BINARY_ADD) return __fadd_rn(a, b);
-  return __fmul_rn(a, b);
+  if constexpr (kKind == HYLE_B200_BINARY_MULTIPLY) return __fmul_rn(a, b);
+  if constexpr (kKind == HYLE_B200_BINARY_SUBTRACT) return __fsub_rn(a, b);
+  if constexpr (kKind == HYLE_B200_BINARY_DIVIDE) return __fdiv_rn(a, b);
+  // Number minimum / maximum.  fminf / fmaxf return the other operand for one NaN; for two zeros
+  // the sign is fixed by hand: OR of the sign bits for the minimum, AND for the maximum.
+  if constexpr (kKind == HYLE_B200_BINARY_MINIMUM) {
+    const float r = fminf(a, b);
+    return (a == 0.0f && b == 0.0f) ? __uint_as_float(__float_as_uint(a) | __float_as_uint(b)) : r;
+  }
+  const float r = fmaxf(a, b);
+  return (a == 0.0f && b == 0.0f) ? __uint_as_float(__float_as_uint(a) & __float_as_uint(b)) : r;
 }
 
 template <int kKind>
@@ -330,12 +340,17 @@ extern "C" int hyle_b200_binary(hyle_b200_stream_t stream, int kind, int dtype, 
   auto s = reinterpret_cast<cudaStream_t>(stream);
 #define HB_BINARY_CASE(K, D) \
   if (kind == K && dtype == D) return launch_binary<K, D>(s, lhs, rhs, out, count, rhs_period)
-  HB_BINARY_CASE(HYLE_B200_BINARY_ADD, HYLE_B200_F32);
-  HB_BINARY_CASE(HYLE_B200_BINARY_MULTIPLY, HYLE_B200_F32);
-  HB_BINARY_CASE(HYLE_B200_BINARY_ADD, HYLE_B200_BF16);
-  HB_BINARY_CASE(HYLE_B200_BINARY_MULTIPLY, HYLE_B200_BF16);
-  HB_BINARY_CASE(HYLE_B200_BINARY_ADD, HYLE_B200_F16);
-  HB_BINARY_CASE(HYLE_B200_BINARY_MULTIPLY, HYLE_B200_F16);
+#define HB_BINARY_KIND(K) \
+  HB_BINARY_CASE(K, HYLE_B200_F32); \
+  HB_BINARY_CASE(K, HYLE_B200_BF16); \
+  HB_BINARY_CASE(K, HYLE_B200_F16)
+  HB_BINARY_KIND(HYLE_B200_BINARY_ADD);
+  HB_BINARY_KIND(HYLE_B200_BINARY_MULTIPLY);
+  HB_BINARY_KIND(HYLE_B200_BINARY_SUBTRACT);
+  HB_BINARY_KIND(HYLE_B200_BINARY_DIVIDE);
+  HB_BINARY_KIND(HYLE_B200_BINARY_MINIMUM);
+  HB_BINARY_KIND(HYLE_B200_BINARY_MAXIMUM);
+#undef HB_BINARY_KIND
 #undef HB_BINARY_CASE
   return HYLE_B200_INVALID_VALUE;
 }

@@ -607,20 +607,22 @@ logits_regs_kernel(const LogitsParams p) {
 // hundreds of rows there is a better trade.  The row is cut into chunks of at most 10 240 values
 // (256 threads x 10 float4, held in registers for the length of one task) and the kernel works
 // through a global, ordered list of chunk TASKS handed out by an atomic counter:
-//   first pass  (row, chunk): load the chunk (kept in L2), chunk maximum, first index of it,
-//                sum of 2^(x log2e - c) against each warp's own maximum -> one 16-byte partial;
-//                fence; count the chunk in row_done[row]
-//   second pass (row, chunk): wait until row_done[row] says all partials are there (bounded),
-//                fold them (every warp by itself, one partial per lane), load the chunk again --
-//                an L2 hit, the row was read a few microseconds ago -- and write the
-//                probabilities (streaming stores).  Chunk 0 also writes lse / argmax.
+//   first pass  (row, chunk): chunk maximum, first index of it, sum of 2^(x log2e - c) against
+//                each warp's own maximum -> one partial (three tagged 8-byte words, no fence)
+//   second pass (row, chunk): every warp reads the row's partials (bounded wait for the tags),
+//                folds them, and writes the probabilities of the chunk (streaming stores).
+//                Chunk 0 also writes lse / argmax.
+// A task's chunk reaches the CTA by ONE bulk copy (TMA, cp.async.bulk) into shared memory, issued
+// a whole task ahead: while the CTA computes on registers, the next chunk is in flight.  First-pass
+// copies carry an L2 evict-last policy, second-pass copies evict-first: the second pass finds the
+// row in L2 (measured: DRAM reads = the logits once), so HBM sees every logit once and every
+// probability once, as in the cluster path.
 // The list interleaves the passes with a fixed lag of `window` rows:
 //   P1(0) ... P1(w-1), P2(0), P1(w), P2(1), P1(w+1), ...            (each entry = all its chunks)
 // so a second-pass task is claimed w x chunks claims after the first-pass tasks it depends on, by
 // which time those have finished (they never wait on anything, and a claimed task is running):
-// the wait is almost always satisfied on the first poll and can never deadlock.  HBM sees every
-// logit once and every probability once; the window (64 rows = 39 MB) stays far below the 126 MB
-// of L2.  No cluster, no shared-memory staging, no barrier between CTAs.
+// the wait is almost always satisfied on the first look and can never deadlock.  The window
+// (64 rows = 39 MB) stays far below the 126 MB of L2.  No cluster, no barrier between CTAs.
 // ================================================================================================
 constexpr int kStreamThreads = 256;
 constexpr int kStreamWarps = kStreamThreads / 32;
@@ -639,6 +641,13 @@ struct StreamTask {
   uint32_t pass;
 };
 
+// One first-pass result.  Three 8-byte words, each carrying the launch tag in its upper half: an
+// 8-byte store is atomic, so a word whose tag matches holds valid data -- the writer needs no
+// fence and no counter, the reader polls the words themselves (the idea of NCCL's LL protocol).
+struct __align__(32) StreamPartial {
+  unsigned long long maximum, sum, index, pad;
+};
+
 struct StreamParams {
   LogitsParams p;
   uint32_t chunks;  // per row
@@ -646,29 +655,83 @@ struct StreamParams {
   uint32_t window;  // rows between the passes, at most p.rows
   unsigned long long *next_task;
   uint32_t *ticket;
-  uint32_t *row_done;   // [rows]
-  WarpEntry *partials;  // [rows][chunks]
+  uint32_t *epoch;          // launches so far on this workspace; tag = epoch + 1, never 0
+  StreamPartial *partials;  // [rows][chunks]
 };
 
 __host__ __device__ inline uint32_t stream_chunks(uint64_t cols) {
   return static_cast<uint32_t>((cols + kStreamChunk - 1) / kStreamChunk);
 }
-__host__ __device__ inline uint64_t stream_counter_bytes(uint64_t rows) { return (rows * 4 + 15) / 16 * 16; }
 
-__device__ __forceinline__ float4 load_keep(const float4 *p) {  // stays in L2 for the second pass
+// L2 policies for the two passes: a first-pass line should survive until the second pass reads it
+// again (evict-last); the second pass is the last use (evict-first).
+__device__ __forceinline__ uint64_t policy_evict_last() {
+  uint64_t policy;
+  asm volatile("createpolicy.fractional.L2::evict_last.b64 %0, 1.0;" : "=l"(policy));
+  return policy;
+}
+__device__ __forceinline__ uint64_t policy_evict_first() {
+  uint64_t policy;
+  asm volatile("createpolicy.fractional.L2::evict_first.b64 %0, 1.0;" : "=l"(policy));
+  return policy;
+}
+__device__ __forceinline__ float4 load_hinted(const float4 *p, uint64_t policy) {
   float4 v;
-  asm volatile("ld.global.nc.L1::no_allocate.v4.f32 {%0, %1, %2, %3}, [%4];"
+  asm volatile("ld.global.nc.L1::no_allocate.L2::cache_hint.v4.f32 {%0, %1, %2, %3}, [%4], %5;"
                : "=f"(v.x), "=f"(v.y), "=f"(v.z), "=f"(v.w)
-               : "l"(p));
+               : "l"(p), "l"(policy));
   return v;
 }
+
+__device__ __forceinline__ uint32_t shared_address(const void *p) {
+  return static_cast<uint32_t>(__cvta_generic_to_shared(p));
+}
+__device__ __forceinline__ void mbarrier_init(uint64_t *barrier, uint32_t arrivals) {
+  asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" ::"r"(shared_address(barrier)), "r"(arrivals) : "memory");
+}
+__device__ __forceinline__ void mbarrier_expect(uint64_t *barrier, uint32_t bytes) {
+  asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(shared_address(barrier)), "r"(bytes) : "memory");
+}
+__device__ __forceinline__ bool mbarrier_try_wait(uint64_t *barrier, uint32_t phase) {
+  uint32_t done;
+  asm volatile(
+      "{\n\t.reg .pred p;\n\t"
+      "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n\t"
+      "selp.u32 %0, 1, 0, p;\n\t}"
+      : "=r"(done)
+      : "r"(shared_address(barrier)), "r"(phase)
+      : "memory");
+  return done != 0;
+}
+// One bulk copy (TMA, untiled) global -> this CTA's shared memory with an L2 policy; the bytes are
+// counted on `barrier`.  Both addresses and the size are multiples of 16 bytes.
+__device__ __forceinline__ void bulk_load(void *shared_dst, const void *global_src, uint32_t bytes, uint64_t *barrier,
+                                          uint64_t policy) {
+  asm volatile(
+      "cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes.L2::cache_hint [%0], [%1], %2, [%3], %4;" ::"r"(
+          shared_address(shared_dst)),
+      "l"(global_src), "r"(bytes), "r"(shared_address(barrier)), "l"(policy)
+      : "memory");
+}
+__device__ __forceinline__ void store_relaxed(unsigned long long *p, unsigned long long v) {
+  asm volatile("st.relaxed.gpu.global.u64 [%0], %1;" ::"l"(p), "l"(v) : "memory");
+}
+__device__ __forceinline__ unsigned long long load_relaxed(const unsigned long long *p) {
+  unsigned long long v;
+  asm volatile("ld.relaxed.gpu.global.u64 %0, [%1];" : "=l"(v) : "l"(p) : "memory");
+  return v;
+}
+constexpr uint32_t kStreamLoadPollLimit = 1u << 24;
+constexpr size_t kStreamStageBytes = static_cast<size_t>(kStreamThreads) * kStreamVectors * sizeof(float4);  // 40 KB
 
 template <int kMode, int kFull>
 __global__ void __launch_bounds__(kStreamThreads, 4)
 logits_stream_kernel(const StreamParams s) {
   grid_dependency_sync();
+  extern __shared__ __align__(128) float4 stream_stage[];  // the chunk of the task that comes next
+  __shared__ __align__(8) uint64_t s_full;                 // counts the bytes of the bulk load in flight
   __shared__ WarpEntry s_entry[kStreamWarps];
-  __shared__ StreamTask s_tasks[2];
+  __shared__ StreamTask s_tasks[3];                        // ring: current, next (being loaded), the one after
   __shared__ uint32_t s_flag;
   const LogitsParams &p = s.p;
   const int t = threadIdx.x, lane = t & 31, warp = t >> 5;
@@ -677,7 +740,7 @@ logits_stream_kernel(const StreamParams s) {
   const WarpEntry nothing{neg_inf, 0.0f, kNoIndex, 0u};
 
   // Position `task` of the ordered list -> (pass, row, chunk).  Thread 0 does this (a 64-bit
-  // division) for the NEXT task while the CTA works on the current one.
+  // division) two tasks ahead, while the CTA works.
   auto decode = [&](uint64_t task) {
     const uint64_t paired = p.rows - s.window;  // rows whose first pass is interleaved with a second pass
     StreamTask r;
@@ -702,29 +765,57 @@ logits_stream_kernel(const StreamParams s) {
     }
     return r;
   };
-  auto claim_next = [&](int into) {
-    if (t == 0) s_tasks[into] = decode(gridDim.x + atomicAdd(s.next_task, 1ull));
+  auto claim = [&]() { return gridDim.x + atomicAdd(s.next_task, 1ull); };
+  // The chunk of `task` -> shared memory, one bulk copy issued by one thread.
+  auto issue_load = [&](const StreamTask &task) {
+    if (task.pass == kStreamEnd) return;
+    const uint32_t begin = task.chunk_id * s.chunk;
+    const uint32_t bytes = (min(begin + s.chunk, p.cols) - begin) * 4u;
+    mbarrier_expect(&s_full, bytes);
+    bulk_load(stream_stage, p.in + task.row * p.cols + begin, bytes, &s_full,
+              task.pass == kStreamFirst ? policy_evict_last() : policy_evict_first());
   };
 
-  if (t == 0) s_tasks[0] = decode(blockIdx.x);  // the first task of every CTA is fixed
+  if (t == 0) {
+    mbarrier_init(&s_full, 1);
+    asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+    s_tasks[0] = decode(blockIdx.x);  // the first task of every CTA is fixed, the rest come from the counter
+    issue_load(s_tasks[0]);
+    s_tasks[1] = decode(claim());
+  }
+  const unsigned long long tag = static_cast<unsigned long long>(*s.epoch + 1u) << 32;
   __syncthreads();
-  int buffer = 0;
+
+  uint32_t phase = 0;
+  int slot = 0;  // position of the current task in the ring
   for (;;) {
-    const StreamTask now = s_tasks[buffer];
+    const StreamTask now = s_tasks[slot];
     if (now.pass == kStreamEnd) break;
+    const int slot_next = slot == 2 ? 0 : slot + 1, slot_after = slot_next == 2 ? 0 : slot_next + 1;
     const bool second = now.pass == kStreamSecond;
     const uint64_t row = now.row;
     const uint32_t chunk_id = now.chunk_id;
     const uint32_t begin = chunk_id * s.chunk;
     const uint32_t vectors = (min(begin + s.chunk, p.cols) - begin) / 4;
-    const float4 *src = reinterpret_cast<const float4 *>(p.in + row * p.cols + begin) + t;
+
+    // The chunk has been on its way since the previous task; take it into registers.
+    bool landed = mbarrier_try_wait(&s_full, phase);
+    for (uint32_t polls = 0; !landed && polls < kStreamLoadPollLimit; ++polls) landed = mbarrier_try_wait(&s_full, phase);
+    phase ^= 1u;
+    float4 x[kStreamVectors];
+#pragma unroll
+    for (int j = 0; j < kStreamVectors; ++j)
+      x[j] = (j < kFull || j * kStreamThreads + t < vectors) ? stream_stage[j * kStreamThreads + t]
+                                                             : make_float4(neg_inf, neg_inf, neg_inf, neg_inf);
+    if (!landed) x[0].x = CUDART_NAN_F;  // the load never completed: the row is reported as NaN
+    __syncthreads();  // everyone holds its values: the stage is free for the next chunk
+    if (t == 32) issue_load(s_tasks[slot_next]);  // in flight during everything below
+    // The claim for the task after the next: the atomic is issued now and its result is used at
+    // the end of this task, so nobody waits for the round trip.
+    unsigned long long claimed = 0;
+    if (t == 64) claimed = claim();
 
     if (!second) {
-      float4 x[kStreamVectors];
-#pragma unroll
-      for (int j = 0; j < kStreamVectors; ++j)
-        x[j] = (j < kFull || j * kStreamThreads + t < vectors) ? load_keep(src + j * kStreamThreads) : make_float4(neg_inf, neg_inf, neg_inf, neg_inf);
-      claim_next(buffer ^ 1);  // after the loads are in flight
       float thread_max = neg_inf;
       int best_slot = 0;
 #pragma unroll
@@ -736,8 +827,9 @@ logits_stream_kernel(const StreamParams s) {
       const float warp_max = warp_max_nan(thread_max);
       uint32_t index = kNoIndex;
       if (want_index) {
-        if (thread_max == warp_max) {  // a few lanes; never true for NaN.  The float4 is still in L2.
-          const float4 v = load_keep(src + best_slot * kStreamThreads);
+        if (thread_max == warp_max) {  // a few lanes; never true for NaN.  The float4 is in L2.
+          const float4 v = load_hinted(reinterpret_cast<const float4 *>(p.in + row * p.cols + begin) + best_slot * kStreamThreads + t,
+                                       policy_evict_last());
           const uint32_t base = begin + (best_slot * kStreamThreads + t) * 4;
           index = v.x == warp_max ? base : v.y == warp_max ? base + 1 : v.z == warp_max ? base + 2 : base + 3;
         }
@@ -756,30 +848,34 @@ logits_stream_kernel(const StreamParams s) {
       if (warp == 0) {
         const Combined cta = combine(lane < kStreamWarps ? s_entry[lane] : nothing);
         if (lane == 0) {
-          s.partials[row * s.chunks + chunk_id] = WarpEntry{cta.maximum, cta.total, cta.index, 0u};
-          __threadfence();  // the partial is visible before it is counted
-          atomicAdd(s.row_done + row, 1u);
+          StreamPartial *out = s.partials + row * s.chunks + chunk_id;
+          store_relaxed(&out->maximum, tag | __float_as_uint(cta.maximum));
+          store_relaxed(&out->sum, tag | __float_as_uint(cta.total));
+          store_relaxed(&out->index, tag | cta.index);
         }
       }
     } else {
-      if (t == 0) {
-        const volatile uint32_t *done = s.row_done + row;
-        uint32_t polls = 0;
-        while (*done != s.chunks && polls < kStreamPollLimit) ++polls;
-        s_flag = *done == s.chunks;
-        __threadfence();
-      }
-      claim_next(buffer ^ 1);
-      __syncthreads();
-      const bool complete = s_flag != 0u;
+      // Every warp fetches the row's partials itself, one per lane, and waits (bounded) until all
+      // carry this launch's tag.  They were written `window` rows ago: the first look succeeds.
       WarpEntry mine = nothing;
+      bool complete = true;
       if (lane < s.chunks) {
-        const uint4 raw = __ldcg(reinterpret_cast<const uint4 *>(s.partials + row * s.chunks + lane));
-        mine = WarpEntry{__uint_as_float(raw.x), __uint_as_float(raw.y), raw.z, 0u};
+        const StreamPartial *in = s.partials + row * s.chunks + lane;
+        unsigned long long m = load_relaxed(&in->maximum), q = load_relaxed(&in->sum), i = load_relaxed(&in->index);
+        for (uint32_t polls = 0; ((m ^ tag) >> 32 != 0 || (q ^ tag) >> 32 != 0 || (i ^ tag) >> 32 != 0) && polls < kStreamPollLimit;
+             ++polls) {
+          m = load_relaxed(&in->maximum);
+          q = load_relaxed(&in->sum);
+          i = load_relaxed(&in->index);
+        }
+        complete = (m ^ tag) >> 32 == 0 && (q ^ tag) >> 32 == 0 && (i ^ tag) >> 32 == 0;
+        mine = WarpEntry{__uint_as_float(static_cast<uint32_t>(m)), __uint_as_float(static_cast<uint32_t>(q)),
+                         static_cast<uint32_t>(i), 0u};
       }
+      complete = __all_sync(kFullMask, complete);
       const Combined all = combine(mine);
       const float maximum = all.maximum, total_sum = all.total, row_c = __fmul_rn(all.maximum, kLog2e);
-      const bool valid = complete && maximum > neg_inf && maximum < CUDART_INF_F;  // false for NaN too
+      const bool valid = complete && landed && maximum > neg_inf && maximum < CUDART_INF_F;  // false for NaN too
       const bool has_nan = maximum != maximum;
       const float nan = CUDART_NAN_F;
       const float residual = fmaf(maximum, kLog2e, -row_c);
@@ -796,46 +892,26 @@ logits_stream_kernel(const StreamParams s) {
       if constexpr (kMode == kProbsBf16) {
         uint2 *dst = reinterpret_cast<uint2 *>(static_cast<unsigned short *>(p.out) + row * p.cols + begin) + t;
 #pragma unroll
-        for (int half = 0; half < 2; ++half) {  // two batches of five loads: fewer live registers than ten
-          float4 x[kStreamVectors / 2];
-#pragma unroll
-          for (int j = 0; j < kStreamVectors / 2; ++j) {
-            const int slot = half * (kStreamVectors / 2) + j;
-            if (slot < kFull || slot * kStreamThreads + t < vectors) x[j] = ld_stream(src + slot * kStreamThreads);
-          }
-#pragma unroll
-          for (int j = 0; j < kStreamVectors / 2; ++j) {
-            const int slot = half * (kStreamVectors / 2) + j;
-            if (slot < kFull || slot * kStreamThreads + t < vectors)
-              st_stream(dst + slot * kStreamThreads,
-                        make_uint2(pack_bf16x2(exp2_approx(fmaf(x[j].x, kLog2e, neg_row_c)) * inverse,
-                                               exp2_approx(fmaf(x[j].y, kLog2e, neg_row_c)) * inverse),
-                                   pack_bf16x2(exp2_approx(fmaf(x[j].z, kLog2e, neg_row_c)) * inverse,
-                                               exp2_approx(fmaf(x[j].w, kLog2e, neg_row_c)) * inverse)));
-          }
+        for (int j = 0; j < kStreamVectors; ++j) {
+          if (j < kFull || j * kStreamThreads + t < vectors)
+            st_stream(dst + j * kStreamThreads,
+                      make_uint2(pack_bf16x2(exp2_approx(fmaf(x[j].x, kLog2e, neg_row_c)) * inverse,
+                                             exp2_approx(fmaf(x[j].y, kLog2e, neg_row_c)) * inverse),
+                                 pack_bf16x2(exp2_approx(fmaf(x[j].z, kLog2e, neg_row_c)) * inverse,
+                                             exp2_approx(fmaf(x[j].w, kLog2e, neg_row_c)) * inverse)));
         }
       } else {
         float4 *dst = reinterpret_cast<float4 *>(static_cast<float *>(p.out) + row * p.cols + begin) + t;
 #pragma unroll
-        for (int half = 0; half < 2; ++half) {
-          float4 x[kStreamVectors / 2];
-#pragma unroll
-          for (int j = 0; j < kStreamVectors / 2; ++j) {
-            const int slot = half * (kStreamVectors / 2) + j;
-            if (slot < kFull || slot * kStreamThreads + t < vectors) x[j] = ld_stream(src + slot * kStreamThreads);
-          }
-#pragma unroll
-          for (int j = 0; j < kStreamVectors / 2; ++j) {
-            const int slot = half * (kStreamVectors / 2) + j;
-            if (slot < kFull || slot * kStreamThreads + t < vectors) {
-              float4 o;
-              if constexpr (kMode == kProbsF32)
-                o = make_float4(exp2_approx(fmaf(x[j].x, kLog2e, neg_row_c)) * inverse, exp2_approx(fmaf(x[j].y, kLog2e, neg_row_c)) * inverse,
-                                exp2_approx(fmaf(x[j].z, kLog2e, neg_row_c)) * inverse, exp2_approx(fmaf(x[j].w, kLog2e, neg_row_c)) * inverse);
-              else
-                o = make_float4(x[j].x - shift, x[j].y - shift, x[j].z - shift, x[j].w - shift);
-              st_stream(dst + slot * kStreamThreads, o);
-            }
+        for (int j = 0; j < kStreamVectors; ++j) {
+          if (j < kFull || j * kStreamThreads + t < vectors) {
+            float4 o;
+            if constexpr (kMode == kProbsF32)
+              o = make_float4(exp2_approx(fmaf(x[j].x, kLog2e, neg_row_c)) * inverse, exp2_approx(fmaf(x[j].y, kLog2e, neg_row_c)) * inverse,
+                              exp2_approx(fmaf(x[j].z, kLog2e, neg_row_c)) * inverse, exp2_approx(fmaf(x[j].w, kLog2e, neg_row_c)) * inverse);
+            else
+              o = make_float4(x[j].x - shift, x[j].y - shift, x[j].z - shift, x[j].w - shift);
+            st_stream(dst + j * kStreamThreads, o);
           }
         }
       }
@@ -844,8 +920,10 @@ logits_stream_kernel(const StreamParams s) {
         rescan_argmax(p.in + row * p.cols, p.cols, p.index != nullptr ? p.index + row : nullptr,
                       p.value != nullptr ? p.value + row : nullptr);
     }
-    __syncthreads();  // the next claim is visible; s_entry and s_flag may be reused
-    buffer ^= 1;
+    // No barrier here: the next task's first barrier separates this task's shared-memory reads
+    // from the next one's writes, and a ring entry is read two tasks after it is written.
+    if (t == 64) s_tasks[slot_after] = decode(claimed);
+    slot = slot_next;
   }
 
   // The CTA that leaves last re-arms the workspace for the next stream-ordered launch.
@@ -854,12 +932,10 @@ logits_stream_kernel(const StreamParams s) {
     s_flag = atomicAdd(s.ticket, 1u) == gridDim.x - 1;
   }
   __syncthreads();
-  if (s_flag != 0u) {
-    for (uint64_t i = t; i < p.rows; i += kStreamThreads) s.row_done[i] = 0u;
-    if (t == 0) {
-      *s.next_task = 0ull;
-      *s.ticket = 0u;
-    }
+  if (s_flag != 0u && t == 0) {
+    *s.next_task = 0ull;
+    *s.ticket = 0u;
+    *s.epoch = *s.epoch >= 0xfffffffeu ? 0u : *s.epoch + 1u;  // the next launch's partials carry another tag
   }
 }
 
@@ -933,7 +1009,7 @@ int resident_clusters(int cluster) {
 }
 
 uint64_t stream_workspace_bytes(uint64_t rows, uint64_t cols) {
-  return kStreamHeaderBytes + stream_counter_bytes(rows) + rows * stream_chunks(cols) * sizeof(WarpEntry);
+  return kStreamHeaderBytes + rows * stream_chunks(cols) * sizeof(StreamPartial);
 }
 
 template <int kMode>
@@ -947,14 +1023,14 @@ int launch_stream(cudaStream_t stream, const LogitsParams &p, void *workspace) {
   unsigned char *base = static_cast<unsigned char *>(workspace);
   s.next_task = reinterpret_cast<unsigned long long *>(base);
   s.ticket = reinterpret_cast<uint32_t *>(base + 8);
-  s.row_done = reinterpret_cast<uint32_t *>(base + kStreamHeaderBytes);
-  s.partials = reinterpret_cast<WarpEntry *>(base + kStreamHeaderBytes + stream_counter_bytes(p.rows));
+  s.epoch = reinterpret_cast<uint32_t *>(base + 12);
+  s.partials = reinterpret_cast<StreamPartial *>(base + kStreamHeaderBytes);
   const uint64_t tasks = 2 * p.rows * s.chunks;
   const unsigned grid = clamp_grid(tasks, static_cast<uint64_t>(sm_count()) * 4);
   const uint32_t last = p.cols - (s.chunks - 1) * s.chunk;  // the shortest chunk
   const bool nine_full = s.chunk / 4 >= 9u * kStreamThreads && last / 4 >= 9u * kStreamThreads;
   return launch(nine_full ? logits_stream_kernel<kMode, 9> : logits_stream_kernel<kMode, 0>, dim3(grid),
-                dim3(kStreamThreads), 0, stream, s);
+                dim3(kStreamThreads), kStreamStageBytes, stream, s);
 }
 
 template <int kMode>

@@ -34,7 +34,7 @@ def _ptr(t: Optional[torch.Tensor]) -> Optional[int]:
 
 
 def binary(kind: int, lhs: torch.Tensor, rhs: torch.Tensor, out: Optional[torch.Tensor] = None) -> torch.Tensor:
-    """Binary{kAdd|kMultiply}; ``rhs`` has lhs's shape or lhs's trailing axes (NumPy broadcast)."""
+    """Binary{kind}; ``rhs`` has lhs's shape or lhs's trailing axes (NumPy broadcast)."""
     _device_tensor(lhs, "lhs"), _device_tensor(rhs, "rhs")
     if lhs.dtype != rhs.dtype or lhs.dtype not in _DTYPE:
         raise ValueError("lhs and rhs must share one of f32 / bf16 / f16")
@@ -54,6 +54,24 @@ def add(lhs, rhs, out=None):
 
 def multiply(lhs, rhs, out=None):
     return binary(abi.BINARY_MULTIPLY, lhs, rhs, out)
+
+
+def subtract(lhs, rhs, out=None):
+    return binary(abi.BINARY_SUBTRACT, lhs, rhs, out)
+
+
+def divide(lhs, rhs, out=None):
+    return binary(abi.BINARY_DIVIDE, lhs, rhs, out)
+
+
+def minimum(lhs, rhs, out=None):
+    """Number minimum: a NaN operand yields the other one; min(+0, -0) = -0 in either order."""
+    return binary(abi.BINARY_MINIMUM, lhs, rhs, out)
+
+
+def maximum(lhs, rhs, out=None):
+    """Number maximum: a NaN operand yields the other one; max(+0, -0) = +0 in either order."""
+    return binary(abi.BINARY_MAXIMUM, lhs, rhs, out)
 
 
 def reduce_rows(kind: int, x: torch.Tensor) -> torch.Tensor:

@@ -59,10 +59,17 @@ enum hyle_b200_dtype {
   HYLE_B200_F16 = 2
 };
 
-/* hyle::compute::BinaryKind subset (include/hyle/compute/operation.h:75-82). */
+/* hyle::compute::BinaryKind (include/hyle/compute/operation.h:75-82); numbered independently. */
 enum hyle_b200_binary_kind {
   HYLE_B200_BINARY_ADD = 0,
-  HYLE_B200_BINARY_MULTIPLY = 1
+  HYLE_B200_BINARY_MULTIPLY = 1,
+  HYLE_B200_BINARY_SUBTRACT = 2,
+  HYLE_B200_BINARY_DIVIDE = 3,
+  /* Number minimum / maximum: a NaN operand yields the other operand (NaN only if both are);
+   * zeros of opposite sign give -0 for the minimum and +0 for the maximum whatever the operand
+   * order (src/simd/ops/kernel_impl.h:256-267, include/hyle/simd/ops.h:77-79). */
+  HYLE_B200_BINARY_MINIMUM = 4,
+  HYLE_B200_BINARY_MAXIMUM = 5
 };
 
 /* hyle::compute::ReductionKind (include/hyle/compute/operation.h:84-89). */
@@ -94,11 +101,12 @@ HYLE_B200_API int hyle_b200_abi_version(void);
 HYLE_B200_API const char *hyle_b200_result_string(int result);
 
 /* ---------------------------------------------------------------------------------------------
- * Binary{kAdd|kMultiply} with NumPy trailing-axis broadcast of the right operand.
+ * Binary{kAdd|kSubtract|kMultiply|kDivide|kMinimum|kMaximum} with NumPy trailing-axis broadcast of
+ * the right operand.
  * Replaces: Binary schema include/hyle/compute/operation.h:301-303, broadcast inference
  * src/compute_ops/operation.cc:480-491, CPU route src/compute_provider_native/elementwise.cc:116-133
  * (one dense call per broadcast chunk, :333-348,540-571).
- * out[i] = lhs[i] (+|*) rhs[i % rhs_period] for i in [0,count).  rhs_period == count means no
+ * out[i] = lhs[i] (op) rhs[i % rhs_period] for i in [0,count).  rhs_period == count means no
  * broadcast; rhs_period == last-axes extent is the bias-over-rows case; count % rhs_period == 0.
  * f32: one IEEE operation per element (bit-exact).  bf16/f16: f32 operation, one RNE rounding.
  * out may alias lhs exactly.

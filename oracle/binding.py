@@ -18,7 +18,7 @@ ORACLE_LIB = os.path.join(ORACLE_DIR, "libhyle_oracle.so")
 REF_LIB = os.path.join(ORACLE_DIR, "_ref", "libhyle_ref_floor.so")
 
 F32, BF16, F16 = 0, 1, 2
-ADD, MULTIPLY = 0, 1
+ADD, MULTIPLY, SUBTRACT, DIVIDE, NUMBER_MINIMUM, NUMBER_MAXIMUM = 0, 1, 2, 3, 4, 5  # Binary kinds
 SUM, MEAN, MINIMUM, MAXIMUM = 0, 1, 2, 3
 
 _vp, _u64, _i, _f = ctypes.c_void_p, ctypes.c_uint64, ctypes.c_int, ctypes.c_float

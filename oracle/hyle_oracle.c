@@ -32,7 +32,7 @@
 #define ORACLE_API __attribute__((visibility("default")))
 
 enum { DT_F32 = 0, DT_BF16 = 1, DT_F16 = 2 };
-enum { BIN_ADD = 0, BIN_MUL = 1 };
+enum { BIN_ADD = 0, BIN_MUL = 1, BIN_SUB = 2, BIN_DIV = 3, BIN_MIN = 4, BIN_MAX = 5 };
 enum { RED_SUM = 0, RED_MEAN = 1, RED_MIN = 2, RED_MAX = 3 };
 enum { SM_SOFTMAX = 0, SM_LOG_SOFTMAX = 1 };
 
@@ -112,10 +112,35 @@ static inline void store_from_f32(void *p, size_t i, int dtype, float v) {
   else ((uint16_t *)p)[i] = hyle_oracle_f32_to_f16(v);
 }
 
-/* ---- Binary{kAdd|kMultiply}, trailing-axis broadcast ------------------------------------------
- * src/compute_provider_native/elementwise.cc:116-133 (dense f32 route, one IEEE op per element),
+/* ---- Binary{all six kinds}, trailing-axis broadcast ---------------------------------------------
+ * src/compute_provider_native/elementwise.cc:101-133 (dense f32 route, one IEEE op per element),
  * :135-147 (half types: f32 op on 128-element tiles, one rounding), :333-348,540-571 (one dense
- * call per broadcast chunk = rhs repeats with period rhs_period). */
+ * call per broadcast chunk = rhs repeats with period rhs_period).
+ * Minimum / Maximum are "number" extrema (include/hyle/simd/ops.h:77-79): one NaN operand gives the
+ * other operand, two zeros give OR (minimum) / AND (maximum) of their bits, so the sign does not
+ * depend on operand order (src/simd/ops/kernel_impl.h:256-267). */
+static inline float binary_value(int kind, float a, float b) {
+  switch (kind) {
+    case BIN_ADD: return a + b;
+    case BIN_MUL: return a * b;
+    case BIN_SUB: return a - b;
+    case BIN_DIV: return a / b;
+    default: break;
+  }
+  if (isnan(a)) return b;  /* NaN if b is NaN too */
+  if (isnan(b)) return a;
+  if (a == 0.0f && b == 0.0f) {
+    uint32_t x, y;
+    memcpy(&x, &a, 4);
+    memcpy(&y, &b, 4);
+    x = kind == BIN_MIN ? (x | y) : (x & y);
+    memcpy(&a, &x, 4);
+    return a;
+  }
+  if (kind == BIN_MIN) return a < b ? a : b;
+  return a > b ? a : b;
+}
+
 ORACLE_API void hyle_oracle_binary(int kind, int dtype, const void *lhs, const void *rhs, void *out,
                                    uint64_t count, uint64_t rhs_period) {
   if (count == 0) return;
@@ -125,7 +150,7 @@ ORACLE_API void hyle_oracle_binary(int kind, int dtype, const void *lhs, const v
     for (uint64_t j = 0; j < rhs_period; ++j) {
       const uint64_t i = c * rhs_period + j;
       const float a = load_as_f32(lhs, i, dtype), b = load_as_f32(rhs, j, dtype);
-      store_from_f32(out, i, dtype, kind == BIN_ADD ? a + b : a * b);
+      store_from_f32(out, i, dtype, binary_value(kind, a, b));
     }
   }
 }

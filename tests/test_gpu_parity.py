@@ -137,6 +137,37 @@ def test_binary_variants_and_broadcast_periods(oracle):
     got = ops.add(to_dev(h), to_dev(g)).cpu().numpy()
     want = oracle.binary(ob.ADD, ob.F16, h.view(np.uint16), g.view(np.uint16))
     assert np.array_equal(got.view(np.uint16), want)
+    # subtract, divide, number minimum / maximum: bit-exact in all three storage types, including
+    # NaN operands, infinities, subnormals and zeros of either sign in either order
+    special = np.array([0.0, -0.0, np.nan, np.inf, -np.inf, 1.0, -1.0, 3.0e38, 1e-40, -1e-40], np.float32)
+    a32 = np.concatenate([np.repeat(special, special.size), rng.standard_normal(4000).astype(np.float32)])
+    b32 = np.concatenate([np.tile(special, special.size), rng.standard_normal(4000).astype(np.float32)])
+    kinds = [(abi.BINARY_SUBTRACT, ob.SUBTRACT), (abi.BINARY_DIVIDE, ob.DIVIDE),
+             (abi.BINARY_MINIMUM, ob.NUMBER_MINIMUM), (abi.BINARY_MAXIMUM, ob.NUMBER_MAXIMUM)]
+    for kind, okind in kinds:
+        want = oracle.binary(okind, ob.F32, a32, b32)
+        got = ops.binary(kind, to_dev(a32), to_dev(b32)).cpu().numpy()
+        assert np.array_equal(np.isnan(got), np.isnan(want))
+        assert np.array_equal(got.view(np.uint32)[~np.isnan(want)], want.view(np.uint32)[~np.isnan(want)])
+        a16, b16 = wl.f32_to_bf16(a32), wl.f32_to_bf16(b32)
+        want16 = oracle.binary(okind, ob.BF16, a16, b16)
+        got16 = bf16_words(ops.binary(kind, to_dev_bf16(a16), to_dev_bf16(b16)))
+        nan16 = (want16 & 0x7FFF) > 0x7F80
+        assert np.array_equal((got16 & 0x7FFF) > 0x7F80, nan16)
+        assert np.array_equal(got16[~nan16], want16[~nan16])
+        with np.errstate(all="ignore"):
+            ah, bh = a32.astype(np.float16), b32.astype(np.float16)
+        wanth = oracle.binary(okind, ob.F16, ah.view(np.uint16), bh.view(np.uint16))
+        goth = ops.binary(kind, to_dev(ah), to_dev(bh)).cpu().numpy().view(np.uint16)
+        nanh = (wanth & 0x7FFF) > 0x7C00
+        assert np.array_equal((goth & 0x7FFF) > 0x7C00, nanh)
+        assert np.array_equal(goth[~nanh], wanth[~nanh])
+        # broadcast of the right operand
+        rowvec = b32[:40]
+        want = oracle.binary(okind, ob.F32, a32[:4000].reshape(100, 40), rowvec)
+        got = ops.binary(kind, to_dev(a32[:4000].reshape(100, 40)), to_dev(rowvec)).cpu().numpy()
+        assert np.array_equal(np.isnan(got), np.isnan(want))
+        assert np.array_equal(got.view(np.uint32)[~np.isnan(want)], want.view(np.uint32)[~np.isnan(want)])
     # in place
     t = to_dev(lhs.copy())
     ops.add(t, t.clone(), out=t)

@@ -127,6 +127,43 @@ def test_binary_broadcast_is_one_ieee_operation(oracle):
     assert np.array_equal(oracle.binary(ob.ADD, ob.BF16, x16, r16), want)
 
 
+def _number_extreme(a, b, minimum):
+    """The formula the reference's own test checks simd::fmin / fmax against
+    (tests/simd/ops_test.cc:424-444), re-expressed with numpy."""
+    both_zero = (a == 0) & (b == 0)
+    zero_bits = (a.view(np.uint32) | b.view(np.uint32)) if minimum else (a.view(np.uint32) & b.view(np.uint32))
+    with np.errstate(invalid="ignore"):
+        picked = np.where(a < b, a, b) if minimum else np.where(a > b, a, b)
+    out = np.where(np.isnan(a), b, np.where(np.isnan(b), a, picked)).astype(np.float32)
+    return np.where(both_zero, zero_bits.view(np.float32), out)
+
+
+def test_binary_subtract_divide_and_number_extrema(oracle):
+    rng = np.random.default_rng(11)
+    special = np.array([0.0, -0.0, np.nan, np.inf, -np.inf, 1.0, -1.0, 3.5e38, 1e-45], np.float32)
+    a = np.concatenate([np.repeat(special, special.size), rng.standard_normal(1000).astype(np.float32)])
+    b = np.concatenate([np.tile(special, special.size), rng.standard_normal(1000).astype(np.float32)])
+    with np.errstate(all="ignore"):
+        assert np.array_equal(bits(oracle.binary(ob.SUBTRACT, ob.F32, a, b)), bits(a - b))
+        got, want = oracle.binary(ob.DIVIDE, ob.F32, a, b), a / b
+        assert np.array_equal(np.isnan(got), np.isnan(want))  # the sign of a produced NaN is not specified
+        assert np.array_equal(bits(got)[~np.isnan(want)], bits(want)[~np.isnan(want)])
+    for kind, minimum in ((ob.NUMBER_MINIMUM, True), (ob.NUMBER_MAXIMUM, False)):
+        got, want = oracle.binary(kind, ob.F32, a, b), _number_extreme(a, b, minimum)
+        assert np.array_equal(np.isnan(got), np.isnan(want))
+        assert np.array_equal(bits(got)[~np.isnan(want)], bits(want)[~np.isnan(want)])
+    # operand order does not decide the sign of a zero
+    z = oracle.binary(ob.NUMBER_MINIMUM, ob.F32, np.array([0.0, -0.0], np.float32), np.array([-0.0, 0.0], np.float32))
+    assert np.all(np.signbit(z))
+    z = oracle.binary(ob.NUMBER_MAXIMUM, ob.F32, np.array([0.0, -0.0], np.float32), np.array([-0.0, 0.0], np.float32))
+    assert not np.any(np.signbit(z))
+    # half types: f32 operation, one rounding
+    x16, r16, _, _ = wl.rms_norm_inputs(4)
+    with np.errstate(all="ignore"):
+        want = wl.f32_to_bf16(wl.bf16_to_f32(x16) / wl.bf16_to_f32(r16))
+    assert np.array_equal(oracle.binary(ob.DIVIDE, ob.BF16, x16, r16), want)
+
+
 def test_reduce_rules_nan_zero_empty(oracle):
     # docs/user/compute.md:384-388 and tests/compute_provider_native/reduction_test.cc:130-222,330-398
     x = np.array([[1.0, np.nan, 3.0], [-0.0, 0.0, -0.0], [-0.0, -0.0, -0.0], [-1.0, -2.0, -np.inf],
