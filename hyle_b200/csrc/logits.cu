@@ -629,8 +629,11 @@ constexpr int kStreamWarps = kStreamThreads / 32;
 constexpr int kStreamVectors = 10;
 constexpr uint32_t kStreamChunk = kStreamThreads * kStreamVectors * 4;  // values per chunk, at most
 constexpr uint32_t kStreamMaxChunks = 32;                               // one partial per lane
+// Rows between a row's two passes.  Measured at 256 / 1024 rows of 151 936: 32 -> 0.71 / 0.88 of the
+// copy peak (second-pass tasks wait for partials), 40..64 -> 0.77-0.79 / 0.94-0.95, 96 -> 0.72 / 0.83
+// (the window no longer stays in L2).
 constexpr uint32_t kStreamWindow = 64;
-constexpr uint64_t kStreamMinRows = 32;
+constexpr uint64_t kStreamMinRows = 64;  // below this the cluster kernel is as fast or faster
 constexpr uint32_t kStreamPollLimit = 1u << 22;
 constexpr uint64_t kStreamHeaderBytes = 64;
 
@@ -692,14 +695,17 @@ __device__ __forceinline__ void mbarrier_init(uint64_t *barrier, uint32_t arriva
 __device__ __forceinline__ void mbarrier_expect(uint64_t *barrier, uint32_t bytes) {
   asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(shared_address(barrier)), "r"(bytes) : "memory");
 }
+// The hint lets the hardware keep the thread suspended (no issue slots used) until the phase
+// completes or the time runs out; the caller's loop bounds the total wait.
+constexpr uint32_t kSuspendHint = 20000;  // nanoseconds
 __device__ __forceinline__ bool mbarrier_try_wait(uint64_t *barrier, uint32_t phase) {
   uint32_t done;
   asm volatile(
       "{\n\t.reg .pred p;\n\t"
-      "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n\t"
+      "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2, %3;\n\t"
       "selp.u32 %0, 1, 0, p;\n\t}"
       : "=r"(done)
-      : "r"(shared_address(barrier)), "r"(phase)
+      : "r"(shared_address(barrier)), "r"(phase), "r"(kSuspendHint)
       : "memory");
   return done != 0;
 }
@@ -721,7 +727,7 @@ __device__ __forceinline__ unsigned long long load_relaxed(const unsigned long l
   asm volatile("ld.relaxed.gpu.global.u64 %0, [%1];" : "=l"(v) : "l"(p) : "memory");
   return v;
 }
-constexpr uint32_t kStreamLoadPollLimit = 1u << 24;
+constexpr uint32_t kStreamLoadPollLimit = 1u << 20;  // x up to 20 us each
 constexpr size_t kStreamStageBytes = static_cast<size_t>(kStreamThreads) * kStreamVectors * sizeof(float4);  // 40 KB
 
 template <int kMode, int kFull>
@@ -765,7 +771,8 @@ logits_stream_kernel(const StreamParams s) {
     }
     return r;
   };
-  auto claim = [&]() { return gridDim.x + atomicAdd(s.next_task, 1ull); };
+  // Every CTA's first two tasks are fixed (no atomic before the first load); the rest are claimed.
+  auto claim = [&]() { return 2ull * gridDim.x + atomicAdd(s.next_task, 1ull); };
   // The chunk of `task` -> shared memory, one bulk copy issued by one thread.
   auto issue_load = [&](const StreamTask &task) {
     if (task.pass == kStreamEnd) return;
@@ -779,10 +786,10 @@ logits_stream_kernel(const StreamParams s) {
   if (t == 0) {
     mbarrier_init(&s_full, 1);
     asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
-    s_tasks[0] = decode(blockIdx.x);  // the first task of every CTA is fixed, the rest come from the counter
+    s_tasks[0] = decode(blockIdx.x);
     issue_load(s_tasks[0]);
-    s_tasks[1] = decode(claim());
   }
+  if (t == 64) s_tasks[1] = decode(static_cast<uint64_t>(gridDim.x) + blockIdx.x);
   const unsigned long long tag = static_cast<unsigned long long>(*s.epoch + 1u) << 32;
   __syncthreads();
 

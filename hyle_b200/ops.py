@@ -171,7 +171,7 @@ def swiglu_packed(packed: torch.Tensor) -> torch.Tensor:
 
 
 def make_logits_workspace(device, rows: int, cols: int) -> torch.Tensor:
-    """Zero-filled scratch for `logits_reduce` / `softmax` on batches of 32 rows or more (the
+    """Zero-filled scratch for `logits_reduce` / `softmax` on batches of 64 rows or more (the
     streaming kernel); reusable by any number of stream-ordered calls of at most this shape."""
     return torch.zeros(abi.load().hyle_b200_logits_workspace_bytes(rows, cols), dtype=torch.uint8, device=device)
 

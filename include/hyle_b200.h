@@ -180,11 +180,11 @@ HYLE_B200_API int hyle_b200_swiglu_bf16(hyle_b200_stream_t stream, const void *g
  * Rows holding NaN or +inf, or only -inf, get NaN lse and NaN probs (include/hyle/simd/math.h:307-311);
  * argmax is still defined for them.  Any output pointer may be NULL.
  *
- * Two kernels.  Without a workspace, or for fewer than 32 rows, a thread-block cluster keeps each
+ * Two kernels.  Without a workspace, or for fewer than 64 rows, a thread-block cluster keeps each
  * row in registers / shared memory (rows too wide for that return NOT_SUPPORTED).  With a
  * workspace of hyle_b200_logits_workspace_bytes(rows, cols) bytes (16-byte aligned, zero-filled
  * once after allocation; each launch leaves it zeroed again; stream-ordered launches only) and an
- * output tensor, batches of 32 rows or more take a two-pass streaming kernel whose second pass
+ * output tensor, batches of 64 rows or more take a two-pass streaming kernel whose second pass
  * reads the row back from L2: HBM traffic is the same, throughput is higher.
  */
 HYLE_B200_API uint64_t hyle_b200_logits_workspace_bytes(uint64_t rows, uint64_t cols);

@@ -323,9 +323,9 @@ def test_logits_config_256_rows_against_size_independent_properties(oracle):
 
 @pytest.mark.parametrize("cols", [1024, 4112, 19456, 40000, 151936, 327680])
 def test_logits_streaming_kernel_shapes_and_invalid_rows(oracle, cols):
-    """Batches of 32 rows or more with a workspace take the two-pass streaming kernel."""
+    """Batches of 64 rows or more with a workspace take the two-pass streaming kernel."""
     rng = np.random.default_rng(cols + 1)
-    rows = 40 if cols <= 151936 else 33
+    rows = 72 if cols <= 151936 else 65
     x = (4.0 * rng.standard_normal((rows, cols))).astype(np.float32)
     x[1] *= 20.0
     x[2, cols // 2] = np.nan
@@ -348,7 +348,7 @@ def test_logits_streaming_kernel_shapes_and_invalid_rows(oracle, cols):
         tol = F32_REL * np.abs(want[ok]) + (1e-5 if log else 1e-37)
         assert np.all(np.abs(got[ok] - want[ok]) <= tol)
     # a smaller batch reuses the same workspace
-    check_logits(oracle, x[:32], workspace=scratch)
+    check_logits(oracle, x[:64], workspace=scratch)
 
 
 @pytest.mark.parametrize("cols", [1, 7, 8, 1000, 1024, 19000, 19456, 40000, 151936, 262144])
