@@ -733,7 +733,9 @@ constexpr size_t kStreamStageBytes = static_cast<size_t>(kStreamThreads) * kStre
 template <int kMode, int kFull>
 __global__ void __launch_bounds__(kStreamThreads, 4)
 logits_stream_kernel(const StreamParams s) {
-  grid_dependency_sync();
+  // What needs no global memory (task decoding, barrier set-up) runs before the wait for the
+  // previous grid: it overlaps that grid's tail.
+  asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
   extern __shared__ __align__(128) float4 stream_stage[];  // the chunk of the task that comes next
   __shared__ __align__(8) uint64_t s_full;                 // counts the bytes of the bulk load in flight
   __shared__ WarpEntry s_entry[kStreamWarps];
@@ -787,9 +789,10 @@ logits_stream_kernel(const StreamParams s) {
     mbarrier_init(&s_full, 1);
     asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
     s_tasks[0] = decode(blockIdx.x);
-    issue_load(s_tasks[0]);
   }
   if (t == 64) s_tasks[1] = decode(static_cast<uint64_t>(gridDim.x) + blockIdx.x);
+  asm volatile("griddepcontrol.wait;" ::: "memory");  // the previous grid has completed and flushed
+  if (t == 0) issue_load(s_tasks[0]);
   const unsigned long long tag = static_cast<unsigned long long>(*s.epoch + 1u) << 32;
   __syncthreads();
 

@@ -97,9 +97,15 @@ inline std::optional<Plan> match(const Operation &op, std::span<const TensorDesc
     if (in.size() != 2 || out.size() != 1 || !type || in[1].data_type() != in[0].data_type() ||
         out[0] != in[0] || !trailing_axes(in[0], in[1]))
       return std::nullopt;
-    if (binary->kind == BinaryKind::kAdd) p.kind = HYLE_B200_BINARY_ADD;
-    else if (binary->kind == BinaryKind::kMultiply) p.kind = HYLE_B200_BINARY_MULTIPLY;
-    else return std::nullopt;
+    switch (binary->kind) {
+      case BinaryKind::kAdd: p.kind = HYLE_B200_BINARY_ADD; break;
+      case BinaryKind::kSubtract: p.kind = HYLE_B200_BINARY_SUBTRACT; break;
+      case BinaryKind::kMultiply: p.kind = HYLE_B200_BINARY_MULTIPLY; break;
+      case BinaryKind::kDivide: p.kind = HYLE_B200_BINARY_DIVIDE; break;
+      case BinaryKind::kMinimum: p.kind = HYLE_B200_BINARY_MINIMUM; break;
+      case BinaryKind::kMaximum: p.kind = HYLE_B200_BINARY_MAXIMUM; break;
+      default: return std::nullopt;
+    }
     p.entry = Entry::kBinary;
     p.dtype = *type;
     p.rhs_period = elements(in[1]) ? elements(in[1]) : 1;

@@ -76,12 +76,13 @@ int main() {
   const auto f32_w = dense(DataType::kFloat32, {2048});
   const auto f16_w = dense(DataType::kFloat16, {2048});
 
-  {  // Binary: add/multiply with trailing-axis broadcast are taken, subtract is declined
+  {  // Binary: all six kinds with trailing-axis broadcast are taken, other broadcasts are declined
     const std::array in{f32_mat, f32_row};
     const std::array out{f32_mat};
     check(taken(*context, Operation(Binary{BinaryKind::kAdd}), in, out), "Binary{kAdd} f32 [64,4096] + [4096]");
     check(taken(*context, Operation(Binary{BinaryKind::kMultiply}), in, out), "Binary{kMultiply} f32 broadcast");
-    check(declined(*context, Operation(Binary{BinaryKind::kSubtract}), in, out), "Binary{kSubtract} declined (Unimplemented)");
+    check(taken(*context, Operation(Binary{BinaryKind::kSubtract}), in, out), "Binary{kSubtract} f32 broadcast");
+    check(taken(*context, Operation(Binary{BinaryKind::kMinimum}), in, out), "Binary{kMinimum} f32 broadcast");
     const std::array same{bf16_mat, bf16_mat};
     const std::array out16{bf16_mat};
     check(taken(*context, Operation(Binary{BinaryKind::kAdd}), same, out16), "Binary{kAdd} bf16 same shape (residual add)");
