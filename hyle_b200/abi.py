@@ -15,6 +15,9 @@ from .build import LIBRARY_PATH
 F32, BF16, F16 = 0, 1, 2
 # enum hyle_b200_binary_kind
 BINARY_ADD, BINARY_MULTIPLY, BINARY_SUBTRACT, BINARY_DIVIDE, BINARY_MINIMUM, BINARY_MAXIMUM = 0, 1, 2, 3, 4, 5
+# enum hyle_b200_unary_kind
+(UNARY_ABS, UNARY_NEG, UNARY_EXP, UNARY_LOG, UNARY_SQRT, UNARY_RSQRT, UNARY_TANH, UNARY_SIGMOID, UNARY_RELU,
+ UNARY_GELU, UNARY_GELU_TANH, UNARY_SILU, UNARY_SOFTPLUS) = range(13)
 # enum hyle_b200_reduce_kind
 REDUCE_SUM, REDUCE_MEAN, REDUCE_MINIMUM, REDUCE_MAXIMUM = 0, 1, 2, 3
 # enum hyle_b200_softmax_kind
@@ -27,7 +30,7 @@ STATUS_INVALID_Q8_INPUT = 1
 STATUS_EXCHANGE_TIMEOUT = 2
 EXCHANGE_MAX_RANKS, EXCHANGE_MAILBOX_BYTES, EXCHANGE_HANDLE_BYTES = 8, 256, 64
 
-ABI_VERSION = 4
+ABI_VERSION = 5
 
 _p = ctypes.c_void_p
 _u64 = ctypes.c_uint64
@@ -40,6 +43,7 @@ SIGNATURES = {
     "hyle_b200_abi_version": (_i, []),
     "hyle_b200_result_string": (ctypes.c_char_p, [_i]),
     "hyle_b200_binary": (_i, [_p, _i, _i, _p, _p, _p, _u64, _u64]),
+    "hyle_b200_unary": (_i, [_p, _i, _i, _p, _p, _u64]),
     "hyle_b200_reduce_rows_f32": (_i, [_p, _i, _p, _p, _u64, _u64]),
     "hyle_b200_add_bias_row_sum_max_f32": (_i, [_p, _p, _p, _p, _p, _p, _u64, _u64]),
     "hyle_b200_rms_norm_bf16": (_i, [_p, _p, _p, _i, _p, _u64, _u64, _f]),

@@ -1,4 +1,4 @@
-// Streaming elementwise operators: Binary{all six kinds} with trailing-axis broadcast,
+// Streaming elementwise operators: Unary{13 kinds}, Binary{all six kinds} with trailing-axis broadcast,
 // GatedActivation{kSilu} (SwiGLU) and Cast{f32->bf16}.  All are HBM-bound: every thread keeps
 // several independent 16-byte loads in flight, computes in f32 and writes 16-byte vectors.
 #include "common.cuh"
@@ -196,6 +196,103 @@ int launch_binary(cudaStream_t stream, const void *lhs, const void *rhs, void *o
       count, period);
 }
 
+// ---- Unary ---------------------------------------------------------------------------------------
+// Element math follows the scalar route of the reference: libm calls for Exp/Log/Sqrt/Tanh,
+// 1.0f / sqrt(x) for Rsqrt (src/compute_provider_native/elementwise.cc:30-55), the overflow-free
+// sigmoid and the GELU / SiLU definitions of src/simd/math/activations.cc:21-47 (silu(-inf) =
+// gelu(-inf) = 0, NaN propagates), ReLU keeping NaN (:49-52), Softplus = log1p(exp(x)) with the
+// identity above 20 (src/compute_provider_native/aten_cpu_provider.cc:627-628).  Abs, Neg, Sqrt,
+// Rsqrt and ReLU are bit-exact; the transcendental ones use CUDA's full-accuracy single-precision
+// functions (1-2 ulp), well inside the 1e-5 relative bound of the parity tests.
+__device__ __forceinline__ float sigmoid_exact(float x) {
+  const float e = expf(-fabsf(x));
+  return x < 0.0f ? __fdiv_rn(e, 1.0f + e) : __fdiv_rn(1.0f, 1.0f + e);  // NaN falls through both compares
+}
+
+template <int kKind>
+__device__ __forceinline__ float unary_op(float x) {
+  if constexpr (kKind == HYLE_B200_UNARY_ABS) return fabsf(x);
+  if constexpr (kKind == HYLE_B200_UNARY_NEG) return -x;
+  if constexpr (kKind == HYLE_B200_UNARY_EXP) return expf(x);
+  if constexpr (kKind == HYLE_B200_UNARY_LOG) return logf(x);
+  if constexpr (kKind == HYLE_B200_UNARY_SQRT) return __fsqrt_rn(x);
+  if constexpr (kKind == HYLE_B200_UNARY_RSQRT) return __fdiv_rn(1.0f, __fsqrt_rn(x));
+  if constexpr (kKind == HYLE_B200_UNARY_TANH) return tanhf(x);
+  if constexpr (kKind == HYLE_B200_UNARY_SIGMOID) return sigmoid_exact(x);
+  if constexpr (kKind == HYLE_B200_UNARY_RELU) return x != x ? x : (x > 0.0f ? x : 0.0f);
+  if constexpr (kKind == HYLE_B200_UNARY_GELU)
+    return x == -INFINITY ? 0.0f : 0.5f * x * (1.0f + erff(x * 0.70710678118654752440f));
+  if constexpr (kKind == HYLE_B200_UNARY_GELU_TANH) {
+    if (x == -INFINITY) return 0.0f;
+    const float inner = 0.79788456080286535588f * x * fmaf(0.044715f, x * x, 1.0f);
+    return 0.5f * x * (1.0f + tanhf(inner));
+  }
+  if constexpr (kKind == HYLE_B200_UNARY_SILU) return x == -INFINITY ? 0.0f : x * sigmoid_exact(x);
+  return x > 20.0f ? x : log1pf(expf(x));  // Softplus; NaN compares false and propagates through expf
+}
+
+template <int kKind, int kDtype, class Vec>
+__device__ __forceinline__ Vec unary_vec(Vec a) {
+  if constexpr (kDtype == HYLE_B200_F32) {
+    return make_float4(unary_op<kKind>(a.x), unary_op<kKind>(a.y), unary_op<kKind>(a.z), unary_op<kKind>(a.w));
+  } else {
+    auto pair = [](uint32_t w) {
+      return narrow_pack<kDtype>(unary_op<kKind>(narrow_lo<kDtype>(w)), unary_op<kKind>(narrow_hi<kDtype>(w)));
+    };
+    return make_uint4(pair(a.x), pair(a.y), pair(a.z), pair(a.w));
+  }
+}
+
+template <int kKind, int kDtype>
+__global__ void __launch_bounds__(kThreads)
+unary_flat_kernel(const typename Storage<kDtype>::Vec *in, typename Storage<kDtype>::Vec *out, uint64_t vectors) {
+  grid_dependency_sync();
+  using Vec = typename Storage<kDtype>::Vec;
+  const uint64_t stride = static_cast<uint64_t>(gridDim.x) * kThreads;
+  uint64_t i = static_cast<uint64_t>(blockIdx.x) * kThreads + threadIdx.x;
+  for (; i + (kUnroll - 1) * stride < vectors; i += kUnroll * stride) {
+    Vec a[kUnroll];
+#pragma unroll
+    for (int k = 0; k < kUnroll; ++k) a[k] = ld_stream(in + i + k * stride);
+#pragma unroll
+    for (int k = 0; k < kUnroll; ++k) st_stream(out + i + k * stride, unary_vec<kKind, kDtype>(a[k]));
+  }
+  for (; i < vectors; i += stride) st_stream(out + i, unary_vec<kKind, kDtype>(ld_stream(in + i)));
+}
+
+// Unaligned tensors and the tail behind the last whole vector.
+template <int kKind, int kDtype>
+__global__ void __launch_bounds__(kThreads)
+unary_scalar_kernel(const typename Storage<kDtype>::Scalar *in, typename Storage<kDtype>::Scalar *out, uint64_t count) {
+  grid_dependency_sync();
+  const uint64_t stride = static_cast<uint64_t>(gridDim.x) * kThreads;
+  for (uint64_t i = static_cast<uint64_t>(blockIdx.x) * kThreads + threadIdx.x; i < count; i += stride) {
+    if constexpr (kDtype == HYLE_B200_F32) out[i] = unary_op<kKind>(in[i]);
+    else out[i] = narrow_store<kDtype>(unary_op<kKind>(narrow_scalar<kDtype>(in[i])));
+  }
+}
+
+template <int kKind, int kDtype>
+int launch_unary(cudaStream_t stream, const void *in, void *out, uint64_t count) {
+  using Vec = typename Storage<kDtype>::Vec;
+  using Scalar = typename Storage<kDtype>::Scalar;
+  constexpr uint64_t kLanes = sizeof(Vec) / sizeof(Scalar);
+  const uint64_t resident = static_cast<uint64_t>(sm_count()) * kCtasPerSm;
+  const bool vector_ok = aligned_to(in, 16) && aligned_to(out, 16);
+  const uint64_t vectors = vector_ok ? count / kLanes : 0;
+  if (vectors != 0) {
+    const unsigned grid = clamp_grid((vectors + kThreads * kUnroll - 1) / (kThreads * kUnroll), resident);
+    const int status = launch(unary_flat_kernel<kKind, kDtype>, dim3(grid), dim3(kThreads), 0, stream,
+                              static_cast<const Vec *>(in), static_cast<Vec *>(out), vectors);
+    if (status != HYLE_B200_OK) return status;
+  }
+  const uint64_t done = vectors * kLanes;
+  if (done == count) return HYLE_B200_OK;
+  const unsigned grid = clamp_grid((count - done + kThreads - 1) / kThreads, resident);
+  return launch(unary_scalar_kernel<kKind, kDtype>, dim3(grid), dim3(kThreads), 0, stream,
+                static_cast<const Scalar *>(in) + done, static_cast<Scalar *>(out) + done, count - done);
+}
+
 // ---- SwiGLU --------------------------------------------------------------------------------------
 // silu(x) = x * sigmoid(x) with the overflow-free sigmoid of src/simd/math/activations.cc:21-25:
 // e = exp(-|x|); sigmoid = x < 0 ? e/(1+e) : 1/(1+e); silu(-inf) = 0 (:44-47).
@@ -390,6 +487,37 @@ extern "C" int hyle_b200_swiglu_bf16(hyle_b200_stream_t stream, const void *gate
                                                  static_cast<const unsigned short *>(up),
                                                  static_cast<unsigned short *>(out), rows, cols,
                                                  gate_row_stride, up_row_stride);
+}
+
+extern "C" int hyle_b200_unary(hyle_b200_stream_t stream, int kind, int dtype, const void *in, void *out,
+                               uint64_t count) {
+  if (count == 0) return HYLE_B200_OK;
+  if (in == nullptr || out == nullptr) return HYLE_B200_INVALID_VALUE;
+  const size_t width = dtype == HYLE_B200_F32 ? 4 : 2;
+  if (!aligned_to(in, width) || !aligned_to(out, width)) return HYLE_B200_INVALID_VALUE;
+  auto s = reinterpret_cast<cudaStream_t>(stream);
+#define HB_UNARY_CASE(K) \
+  if (kind == K) { \
+    if (dtype == HYLE_B200_F32) return launch_unary<K, HYLE_B200_F32>(s, in, out, count); \
+    if (dtype == HYLE_B200_BF16) return launch_unary<K, HYLE_B200_BF16>(s, in, out, count); \
+    if (dtype == HYLE_B200_F16) return launch_unary<K, HYLE_B200_F16>(s, in, out, count); \
+    return HYLE_B200_INVALID_VALUE; \
+  }
+  HB_UNARY_CASE(HYLE_B200_UNARY_ABS)
+  HB_UNARY_CASE(HYLE_B200_UNARY_NEG)
+  HB_UNARY_CASE(HYLE_B200_UNARY_EXP)
+  HB_UNARY_CASE(HYLE_B200_UNARY_LOG)
+  HB_UNARY_CASE(HYLE_B200_UNARY_SQRT)
+  HB_UNARY_CASE(HYLE_B200_UNARY_RSQRT)
+  HB_UNARY_CASE(HYLE_B200_UNARY_TANH)
+  HB_UNARY_CASE(HYLE_B200_UNARY_SIGMOID)
+  HB_UNARY_CASE(HYLE_B200_UNARY_RELU)
+  HB_UNARY_CASE(HYLE_B200_UNARY_GELU)
+  HB_UNARY_CASE(HYLE_B200_UNARY_GELU_TANH)
+  HB_UNARY_CASE(HYLE_B200_UNARY_SILU)
+  HB_UNARY_CASE(HYLE_B200_UNARY_SOFTPLUS)
+#undef HB_UNARY_CASE
+  return HYLE_B200_INVALID_VALUE;
 }
 
 extern "C" int hyle_b200_cast_f32_to_bf16(hyle_b200_stream_t stream, const float *in,

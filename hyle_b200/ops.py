@@ -74,6 +74,18 @@ def maximum(lhs, rhs, out=None):
     return binary(abi.BINARY_MAXIMUM, lhs, rhs, out)
 
 
+def unary(kind: int, x: torch.Tensor, out: Optional[torch.Tensor] = None) -> torch.Tensor:
+    """Unary{kind} (``abi.UNARY_*``) on a dense f32 / bf16 / f16 tensor."""
+    _device_tensor(x, "x")
+    if x.dtype not in _DTYPE:
+        raise ValueError("x must be f32 / bf16 / f16")
+    if out is None:
+        out = torch.empty_like(x)
+    abi.check("hyle_b200_unary", abi.load().hyle_b200_unary(
+        _stream(), kind, _DTYPE[x.dtype], x.data_ptr(), out.data_ptr(), x.numel()))
+    return out
+
+
 def reduce_rows(kind: int, x: torch.Tensor) -> torch.Tensor:
     """Reduce{kind, axes={-1}} of an f32 tensor; output drops the last axis."""
     _device_tensor(x, "x")

@@ -34,14 +34,14 @@ inline constexpr ProviderRuntimeProperties kRuntime{.replay_class = ProviderRepl
                                                     .capture_compatible = true};
 
 enum class Entry : std::uint8_t {
-  kBinary, kReduceRows, kRmsNorm, kSwiglu, kSoftmax, kCastF32ToBf16, kArgmax, kQ8Encode,
+  kUnary, kBinary, kReduceRows, kRmsNorm, kSwiglu, kSoftmax, kCastF32ToBf16, kArgmax, kQ8Encode,
   kAddRmsNorm, kBiasRowSumMax, kLogitsReduce, kQ8Roundtrip
 };
 
 // Everything enqueue() needs, frozen at prepare time.  Trivially copyable.
 struct Plan final {
   Entry entry{};
-  int kind = 0;            // binary / reduce / softmax kind in the C ABI's numbering
+  int kind = 0;            // unary / binary / reduce / softmax kind in the C ABI's numbering
   int dtype = 0;           // hyle_b200_dtype of the data (or of the norm weight for the norms)
   std::uint64_t count = 0; // total elements of input 0
   std::uint64_t rows = 0;
@@ -93,6 +93,16 @@ inline std::optional<Plan> match(const Operation &op, std::span<const TensorDesc
   p.rows = p.cols ? p.count / p.cols : 0;
   const auto type = abi_dtype(in[0].data_type());
 
+  if (const auto *unary = op.get_if<Unary>()) {
+    // hyle_b200_unary_kind follows UnaryKind's order (include/hyle/compute/operation.h:57-73)
+    if (in.size() != 1 || out.size() != 1 || !type || out[0] != in[0] ||
+        static_cast<int>(unary->kind) > HYLE_B200_UNARY_SOFTPLUS)
+      return std::nullopt;
+    p.entry = Entry::kUnary;
+    p.kind = static_cast<int>(unary->kind);
+    p.dtype = *type;
+    return p;
+  }
   if (const auto *binary = op.get_if<Binary>()) {
     if (in.size() != 2 || out.size() != 1 || !type || in[1].data_type() != in[0].data_type() ||
         out[0] != in[0] || !trailing_axes(in[0], in[1]))
@@ -232,6 +242,8 @@ inline std::optional<Plan> match(const Operation &op, std::span<const TensorDesc
 inline int launch(const Plan &p, hyle_b200_stream_t stream, const void *const *in, void *const *out,
                   void *workspace) noexcept {
   switch (p.entry) {
+    case Entry::kUnary:
+      return hyle_b200_unary(stream, p.kind, p.dtype, in[0], out[0], p.count);
     case Entry::kBinary:
       return hyle_b200_binary(stream, p.kind, p.dtype, in[0], in[1], out[0], p.count, p.rhs_period);
     case Entry::kReduceRows:
@@ -275,7 +287,7 @@ inline int launch(const Plan &p, hyle_b200_stream_t stream, const void *const *i
 }
 
 inline AliasSupport alias_support(const Plan &p, std::size_t output, std::size_t input) noexcept {
-  const bool in_place = (p.entry == Entry::kBinary || p.entry == Entry::kRmsNorm || p.entry == Entry::kSoftmax) &&
+  const bool in_place = (p.entry == Entry::kUnary || p.entry == Entry::kBinary || p.entry == Entry::kRmsNorm || p.entry == Entry::kSoftmax) &&
                         output == 0 && input == 0;
   return {in_place, 0};
 }

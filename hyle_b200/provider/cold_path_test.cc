@@ -87,6 +87,15 @@ int main() {
     const std::array out16{bf16_mat};
     check(taken(*context, Operation(Binary{BinaryKind::kAdd}), same, out16), "Binary{kAdd} bf16 same shape (residual add)");
   }
+  {  // Unary: every kind on the three floating storage types
+    const std::array in{f32_mat};
+    const std::array out{f32_mat};
+    check(taken(*context, Operation(Unary{UnaryKind::kTanh}), in, out), "Unary{kTanh} f32");
+    check(taken(*context, Operation(Unary{UnaryKind::kSoftplus}), in, out), "Unary{kSoftplus} f32");
+    const std::array in16{bf16_mat};
+    const std::array out16{bf16_mat};
+    check(taken(*context, Operation(Unary{UnaryKind::kGelu}), in16, out16), "Unary{kGelu} bf16");
+  }
   {  // Reduce over the last axis
     const std::array in{f32_mat};
     const std::array out{f32_rows};

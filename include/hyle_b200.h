@@ -42,7 +42,7 @@ extern "C" {
 /* Same object as cudaStream_t; spelled out so C callers need no CUDA header. */
 typedef struct CUstream_st *hyle_b200_stream_t;
 
-#define HYLE_B200_ABI_VERSION 4
+#define HYLE_B200_ABI_VERSION 5
 
 enum hyle_b200_result {
   HYLE_B200_OK = 0,
@@ -70,6 +70,23 @@ enum hyle_b200_binary_kind {
    * order (src/simd/ops/kernel_impl.h:256-267, include/hyle/simd/ops.h:77-79). */
   HYLE_B200_BINARY_MINIMUM = 4,
   HYLE_B200_BINARY_MAXIMUM = 5
+};
+
+/* hyle::compute::UnaryKind, same order (include/hyle/compute/operation.h:57-73). */
+enum hyle_b200_unary_kind {
+  HYLE_B200_UNARY_ABS = 0,
+  HYLE_B200_UNARY_NEG = 1,
+  HYLE_B200_UNARY_EXP = 2,
+  HYLE_B200_UNARY_LOG = 3,
+  HYLE_B200_UNARY_SQRT = 4,
+  HYLE_B200_UNARY_RSQRT = 5, /* 1.0f / sqrt(x), not an approximation */
+  HYLE_B200_UNARY_TANH = 6,
+  HYLE_B200_UNARY_SIGMOID = 7,
+  HYLE_B200_UNARY_RELU = 8,  /* NaN stays NaN */
+  HYLE_B200_UNARY_GELU = 9,  /* erf form; gelu(-inf) = 0 */
+  HYLE_B200_UNARY_GELU_TANH = 10,
+  HYLE_B200_UNARY_SILU = 11, /* silu(-inf) = 0 */
+  HYLE_B200_UNARY_SOFTPLUS = 12 /* log1p(exp(x)), x above 20 returned unchanged; softplus(-inf) = +0 */
 };
 
 /* hyle::compute::ReductionKind (include/hyle/compute/operation.h:84-89). */
@@ -114,6 +131,18 @@ HYLE_B200_API const char *hyle_b200_result_string(int result);
 HYLE_B200_API int hyle_b200_binary(hyle_b200_stream_t stream, int kind, int dtype,
                                    const void *lhs, const void *rhs, void *out,
                                    uint64_t count, uint64_t rhs_period);
+
+/* ---------------------------------------------------------------------------------------------
+ * Unary{kind} on a dense tensor of f32 / bf16 / f16 (16-bit types: f32 math, one RNE rounding).
+ * Replaces: Unary schema include/hyle/compute/operation.h:57-73, CPU route
+ * src/compute_provider_native/elementwise.cc:30-100 (Neg, Exp, Log, Sqrt, Rsqrt, Tanh, Relu, Silu),
+ * activation definitions src/simd/math/activations.cc:21-52 (Sigmoid, Gelu, GeluTanh, Silu, Relu),
+ * Softplus src/compute_provider_native/aten_cpu_provider.cc:627-628.
+ * Abs, Neg, Sqrt, Rsqrt, Relu are bit-exact; the others within 1e-5 relative in f32 and one
+ * storage step in bf16 / f16.  out may alias in exactly.
+ */
+HYLE_B200_API int hyle_b200_unary(hyle_b200_stream_t stream, int kind, int dtype, const void *in,
+                                  void *out, uint64_t count);
 
 /* ---------------------------------------------------------------------------------------------
  * Reduce{kind, axes={-1}} over dense f32 rows.

@@ -19,6 +19,7 @@ REF_LIB = os.path.join(ORACLE_DIR, "_ref", "libhyle_ref_floor.so")
 
 F32, BF16, F16 = 0, 1, 2
 ADD, MULTIPLY, SUBTRACT, DIVIDE, NUMBER_MINIMUM, NUMBER_MAXIMUM = 0, 1, 2, 3, 4, 5  # Binary kinds
+(ABS, NEG, EXP, LOG, SQRT, RSQRT, TANH, SIGMOID, RELU, GELU, GELU_TANH, SILU, SOFTPLUS) = range(13)  # Unary kinds
 SUM, MEAN, MINIMUM, MAXIMUM = 0, 1, 2, 3
 
 _vp, _u64, _i, _f = ctypes.c_void_p, ctypes.c_uint64, ctypes.c_int, ctypes.c_float
@@ -58,6 +59,7 @@ class Oracle:
         L.hyle_oracle_f32_to_f16.restype = ctypes.c_uint16
         L.hyle_oracle_f32_to_f16.argtypes = [_f]
         L.hyle_oracle_binary.argtypes = [_i, _i, _vp, _vp, _vp, _u64, _u64]
+        L.hyle_oracle_unary.argtypes = [_i, _i, _vp, _vp, _u64]
         L.hyle_oracle_reduce_rows_f32.argtypes = [_i, _vp, _vp, _u64, _u64]
         L.hyle_oracle_row_sum_f64.argtypes = [_vp, _vp, _vp, _u64, _u64]
         L.hyle_oracle_rms_norm_bf16.argtypes = [_vp, _vp, _i, _vp, _vp, _u64, _u64, _f]
@@ -105,6 +107,13 @@ class Oracle:
         lhs, rhs = _c(lhs, np_dtype), _c(rhs, np_dtype)
         out = np.empty_like(lhs)
         self.lib.hyle_oracle_binary(kind, dtype, _ptr(lhs), _ptr(rhs), _ptr(out), lhs.size, max(rhs.size, 1))
+        return out
+
+    def unary(self, kind, dtype, x):
+        np_dtype = np.float32 if dtype == F32 else np.uint16
+        x = _c(x, np_dtype)
+        out = np.empty_like(x)
+        self.lib.hyle_oracle_unary(kind, dtype, _ptr(x), _ptr(out), x.size)
         return out
 
     def reduce_rows(self, kind, x):
@@ -233,9 +242,19 @@ class RefFloor:
         L.hyle_ref_rms_norm_bf16.argtypes = [_vp, _vp, _vp, _u64, _u64, _f]
         L.hyle_ref_softmax_f32.argtypes = [_i, _vp, _vp, _u64, _u64]
         L.hyle_ref_argmax_f32.argtypes = [_vp, _vp, _vp, _u64, _u64]
+        L.hyle_ref_activation_f32.argtypes = [_i, _vp, _vp, _u64]
+        L.hyle_ref_activation_f32.restype = _i
 
     def set_threads(self, n: int) -> None:
         self.lib.hyle_ref_set_threads(int(n))
+
+    def activation(self, kind, x):
+        """sigmoid / relu / gelu / gelu_tanh / silu (UnaryKind numbers 7..11) by the reference's scalar floor."""
+        x = _c(x, np.float32)
+        out = np.empty_like(x)
+        if self.lib.hyle_ref_activation_f32(kind, _ptr(x), _ptr(out), x.size) != 0:
+            raise ValueError(f"no reference floor for unary kind {kind}")
+        return out
 
     def swiglu(self, gate, up):
         gate, up = _c(gate, np.uint16), _c(up, np.uint16)

@@ -257,6 +257,39 @@ static inline float sigmoid_f32(float x) {
 }
 static inline float silu_f32(float x) { return x == -INFINITY ? 0.0f : x * sigmoid_f32(x); }
 
+/* ---- Unary{kind} ------------------------------------------------------------------------------
+ * src/compute_provider_native/elementwise.cc:30-55 (Neg, Exp, Log, Sqrt, Rsqrt = 1.0f / sqrt, Tanh,
+ * Relu keeping NaN, Silu) and :84-100 (16-bit storage: f32 value, one rounding);
+ * src/simd/math/activations.cc:21-37 (sigmoid, gelu with erf, gelu_tanh; gelu(-inf) = 0);
+ * Softplus: at::softplus(x, 1, 20), src/compute_provider_native/aten_cpu_provider.cc:627-628. */
+enum { UN_ABS = 0, UN_NEG, UN_EXP, UN_LOG, UN_SQRT, UN_RSQRT, UN_TANH, UN_SIGMOID, UN_RELU, UN_GELU,
+       UN_GELU_TANH, UN_SILU, UN_SOFTPLUS };
+static inline float unary_value(int kind, float x) {
+  switch (kind) {
+    case UN_ABS: return fabsf(x);
+    case UN_NEG: return -x;
+    case UN_EXP: return expf(x);
+    case UN_LOG: return logf(x);
+    case UN_SQRT: return sqrtf(x);
+    case UN_RSQRT: return 1.0f / sqrtf(x);
+    case UN_TANH: return tanhf(x);
+    case UN_SIGMOID: return sigmoid_f32(x);
+    case UN_RELU: return isnan(x) ? x : (x > 0.0f ? x : 0.0f);
+    case UN_GELU: return x == -INFINITY ? 0.0f : 0.5f * x * (1.0f + erff(x * 0.70710678118654752440f));
+    case UN_GELU_TANH: {
+      if (x == -INFINITY) return 0.0f;
+      const float inner = 0.79788456080286535588f * x * fmaf(0.044715f, x * x, 1.0f);
+      return 0.5f * x * (1.0f + tanhf(inner));
+    }
+    case UN_SILU: return silu_f32(x);
+    default: return x > 20.0f ? x : log1pf(expf(x));
+  }
+}
+ORACLE_API void hyle_oracle_unary(int kind, int dtype, const void *in, void *out, uint64_t count) {
+#pragma omp parallel for schedule(static)
+  for (uint64_t i = 0; i < count; ++i) store_from_f32(out, i, dtype, unary_value(kind, load_as_f32(in, i, dtype)));
+}
+
 ORACLE_API void hyle_oracle_swiglu_bf16(const uint16_t *gate, const uint16_t *up, uint16_t *out,
                                         float *out_f32, uint64_t rows, uint64_t cols,
                                         uint64_t gate_stride, uint64_t up_stride) {

@@ -3,7 +3,7 @@
 // This translation unit contains no arithmetic of its own.  It is compiled together with the
 // reference's Highway-free sources, in place from the mounted reference tree (oracle/Makefile):
 //   src/simd/math/activations.cc   swiglu_bf16_scalar, rms_norm_bf16_scalar, softmax_f32_scalar,
-//                                  log_softmax_f32_scalar
+//                                  log_softmax_f32_scalar, {sigmoid,gelu,gelu_tanh,silu,relu}_f32_scalar
 //   src/simd/sort/top_k.cc         top_k_f32
 //   include/hyle/simd/dtype.h      f32_to_bf16, bf16_to_f32, f32_to_f16, f16_to_f32
 // and only forwards row by row, so tests can pin oracle/hyle_oracle.c against the reference's code
@@ -54,6 +54,18 @@ REF_API void hyle_ref_rms_norm_bf16(const uint16_t *x, const uint16_t *weight, u
     simd::detail::rms_norm_bf16_scalar(reinterpret_cast<const simd::bfloat16_t *>(x + r * hidden),
                                        reinterpret_cast<const simd::bfloat16_t *>(weight),
                                        reinterpret_cast<simd::bfloat16_t *>(y + r * hidden), hidden, eps);
+}
+
+// kind: 7 sigmoid, 8 relu, 9 gelu, 10 gelu_tanh, 11 silu (the numbering of hyle::compute::UnaryKind)
+REF_API int hyle_ref_activation_f32(int kind, const float *in, float *out, uint64_t count) {
+  switch (kind) {
+    case 7: simd::detail::sigmoid_f32_scalar(in, out, count); return 0;
+    case 8: simd::detail::relu_f32_scalar(in, out, count); return 0;
+    case 9: simd::detail::gelu_f32_scalar(in, out, count); return 0;
+    case 10: simd::detail::gelu_tanh_f32_scalar(in, out, count); return 0;
+    case 11: simd::detail::silu_f32_scalar(in, out, count); return 0;
+    default: return 1;
+  }
 }
 
 REF_API void hyle_ref_softmax_f32(int log_kind, const float *in, float *out, uint64_t rows, uint64_t cols) {

@@ -76,6 +76,15 @@ def main():
     index, value = ref.argmax(rows)
     out["argmax_x"], out["argmax_index"], out["argmax_value"] = rows, index, value
 
+    # Unary activations of the scalar floor (UnaryKind numbers): sigmoid 7, relu 8, gelu 9,
+    # gelu_tanh 10, silu 11, on specials and a spread of ordinary values.
+    special = np.array([0.0, -0.0, np.nan, np.inf, -np.inf, 1.0, -1.0, 20.0, -20.0, 88.0, -104.0, 1e-40, -1e-40,
+                        3.0e38, 0.5, 7.0, -7.0], dtype=np.float32)
+    x = np.concatenate([special, (4.0 * rng.standard_normal(1000)).astype(np.float32)])
+    out["unary_x"] = x
+    for kind in (7, 8, 9, 10, 11):
+        out[f"unary_y_{kind}"] = ref.activation(kind, x)
+
     path = os.path.join(ROOT, "tests", "golden", "ref_floor.npz")
     np.savez_compressed(path, **out)
     print("wrote", path, os.path.getsize(path), "bytes")

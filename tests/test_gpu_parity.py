@@ -386,6 +386,77 @@ def test_argmax_golden_cases(oracle, golden):
     assert np.array_equal(idx2.cpu().numpy(), golden["argmax_index"])
 
 
+# ---- Unary -----------------------------------------------------------------------------------------------------------------
+UNARY_BIT_EXACT = {abi.UNARY_ABS, abi.UNARY_NEG, abi.UNARY_SQRT, abi.UNARY_RSQRT, abi.UNARY_RELU}
+# gelu = 0.5 x (1 + erf(x / sqrt 2)) and its tanh form cancel for negative x: an error of one ulp in
+# erf / tanh (libm and the GPU's functions round differently) is an ABSOLUTE error of about
+# 2^-24 |x| in the result, however small the result is.  The bound below allows four such ulps.
+UNARY_CANCELLING = {abi.UNARY_GELU, abi.UNARY_GELU_TANH}
+
+
+@pytest.mark.parametrize("kind", range(13))
+def test_unary_all_kinds_and_storage_types(oracle, kind):
+    rng = np.random.default_rng(100 + kind)
+    special = np.array([0.0, -0.0, np.nan, np.inf, -np.inf, 1.0, -1.0, 20.0, 20.5, -20.0, 88.0, 89.0, -104.0,
+                        1e-40, -1e-40, 3.0e38, 0.5, 7.0, -7.0, 1.0000001, 0.9999999], np.float32)
+    x = np.concatenate([special, (4.0 * rng.standard_normal(70001)).astype(np.float32),
+                        rng.uniform(-30, 30, 4099).astype(np.float32)])
+    with np.errstate(all="ignore"):
+        slack = 2.5e-7 * np.abs(x) if kind in UNARY_CANCELLING else np.zeros_like(x)
+    want = oracle.unary(kind, ob.F32, x)
+    got = ops.unary(kind, to_dev(x)).cpu().numpy()
+    assert np.array_equal(np.isnan(got), np.isnan(want))
+    ok = ~np.isnan(want)
+    if kind in UNARY_BIT_EXACT:
+        assert np.array_equal(got.view(np.uint32)[ok], want.view(np.uint32)[ok])
+    else:
+        finite = ok & np.isfinite(want)
+        assert np.array_equal(got[ok & ~finite], want[ok & ~finite])        # infinities agree
+        # 1e-5 relative; results in the subnormal range within one subnormal step (the CPU's libm
+        # and the GPU's functions round there differently)
+        assert np.all(np.abs(got[finite] - want[finite]) <= F32_REL * np.abs(want[finite]) + 1.5e-45 + slack[finite])
+    # unaligned start and a ragged tail take the scalar kernel
+    base = to_dev(x)
+    got_tail = ops.unary(kind, base[1:1000]).cpu().numpy()
+    assert np.array_equal(got_tail.view(np.uint32), got.view(np.uint32)[1:1000])
+    # 16-bit storage: f32 math, one rounding -> at most one storage step from the checker
+    for name in ("bf16", "f16"):
+        with np.errstate(all="ignore"):
+            if name == "bf16":
+                x16 = wl.f32_to_bf16(x)
+                x_back = wl.bf16_to_f32(x16)
+                got16 = bf16_words(ops.unary(kind, to_dev_bf16(x16)))
+                want16 = oracle.unary(kind, ob.BF16, x16)
+                decode, exp_mask, step = wl.bf16_to_f32, 0x7F80, 2.0 ** -7
+            else:
+                x16 = x.astype(np.float16).view(np.uint16)
+                x_back = x16.view(np.float16).astype(np.float32)
+                got16 = ops.unary(kind, to_dev(x16.view(np.float16))).cpu().numpy().view(np.uint16)
+                want16 = oracle.unary(kind, ob.F16, x16)
+                decode, exp_mask, step = (lambda w: w.view(np.float16).astype(np.float32)), 0x7C00, 2.0 ** -10
+        nan16 = (want16 & 0x7FFF) > exp_mask
+        assert np.array_equal((got16 & 0x7FFF) > exp_mask, nan16)
+        if kind in UNARY_BIT_EXACT:
+            assert np.array_equal(got16[~nan16], want16[~nan16])
+            continue
+        distance = np.abs(ordered16(got16[~nan16]) - ordered16(want16[~nan16]))
+        if kind in UNARY_CANCELLING:
+            with np.errstate(all="ignore"):
+                g, w = decode(got16[~nan16]), decode(want16[~nan16])
+                bound = step * np.abs(w) + 2.5e-7 * np.abs(x_back[~nan16]) + (6e-8 if name == "f16" else 1e-40)
+                same = (g == w) | (np.abs(g - w) <= bound)
+            assert np.all(same)
+        else:
+            assert distance.max() <= 1
+            assert (distance != 0).mean() < 1e-2
+
+
+def ordered16(words):
+    """16-bit float words as integers that increase with the value (sign-magnitude -> two's complement)."""
+    w = words.astype(np.int32)
+    return np.where(w & 0x8000, -(w & 0x7FFF), w)
+
+
 def test_cast_f32_to_bf16(oracle):
     rng = np.random.default_rng(2)
     for count in [1, 7, 8, 4096, 100003]:

@@ -164,6 +164,62 @@ def test_binary_subtract_divide_and_number_extrema(oracle):
     assert np.array_equal(oracle.binary(ob.DIVIDE, ob.BF16, x16, r16), want)
 
 
+def _unary_inputs():
+    rng = np.random.default_rng(17)
+    special = np.array([0.0, -0.0, np.nan, np.inf, -np.inf, 1.0, -1.0, 20.0, 20.5, -20.0, 88.0, 89.0, -104.0,
+                        1e-40, -1e-40, 3.0e38, 0.5, 7.0, -7.0], np.float32)
+    return np.concatenate([special, (4.0 * rng.standard_normal(4096)).astype(np.float32),
+                           rng.uniform(-30, 30, 2048).astype(np.float32)])
+
+
+def test_unary_activations_match_reference_floor(oracle, ref_floor):
+    """sigmoid, relu, gelu, gelu_tanh, silu: the restatement equals the reference's scalar floor bit for bit."""
+    x = _unary_inputs()
+    for kind in (ob.SIGMOID, ob.RELU, ob.GELU, ob.GELU_TANH, ob.SILU):
+        got, want = oracle.unary(kind, ob.F32, x), ref_floor.activation(kind, x)
+        assert np.array_equal(np.isnan(got), np.isnan(want)), kind
+        assert np.array_equal(bits(got)[~np.isnan(want)], bits(want)[~np.isnan(want)]), kind
+
+
+def test_unary_activations_match_golden(oracle, golden):
+    """The same pin from the committed vectors, for machines without the reference tree."""
+    x = golden["unary_x"]
+    for kind in (ob.SIGMOID, ob.RELU, ob.GELU, ob.GELU_TANH, ob.SILU):
+        got, want = oracle.unary(kind, ob.F32, x), golden[f"unary_y_{kind}"]
+        assert np.array_equal(np.isnan(got), np.isnan(want)), kind
+        assert np.array_equal(bits(got)[~np.isnan(want)], bits(want)[~np.isnan(want)]), kind
+
+
+def test_unary_rules(oracle):
+    x = _unary_inputs()
+    with np.errstate(all="ignore"):
+        assert np.array_equal(bits(oracle.unary(ob.ABS, ob.F32, x)), bits(np.abs(x)))
+        assert np.array_equal(bits(oracle.unary(ob.NEG, ob.F32, x)), bits(-x))
+        got, want = oracle.unary(ob.SQRT, ob.F32, x), np.sqrt(x)
+        assert np.array_equal(bits(got)[~np.isnan(want)], bits(want)[~np.isnan(want)])
+        got, want = oracle.unary(ob.RSQRT, ob.F32, x), np.float32(1.0) / np.sqrt(x)
+        assert np.array_equal(bits(got)[~np.isnan(want)], bits(want)[~np.isnan(want)])
+        for kind, fn in ((ob.EXP, np.exp), (ob.LOG, np.log), (ob.TANH, np.tanh)):
+            got, want = oracle.unary(kind, ob.F32, x), fn(x.astype(np.float64))
+            ok = np.isfinite(want) & (np.abs(want) < 3.0e38)
+            assert np.array_equal(np.isnan(got), np.isnan(want))
+            assert np.all(np.abs(got[ok] - want[ok]) <= 2e-7 * np.abs(want[ok]) + 2e-45)  # + half a subnormal step
+    # the special values the operator schema spells out (include/hyle/compute/operation.h:70-72)
+    sp = oracle.unary(ob.SOFTPLUS, ob.F32, np.array([-np.inf, np.nan, 100.0, 0.0], np.float32))
+    assert sp[0] == 0.0 and not np.signbit(sp[0]) and np.isnan(sp[1]) and sp[2] == 100.0
+    assert abs(sp[3] - np.log(2.0)) < 1e-7
+    for kind in (ob.GELU, ob.GELU_TANH, ob.SILU):
+        assert oracle.unary(kind, ob.F32, np.array([-np.inf], np.float32))[0] == 0.0
+    assert np.isnan(oracle.unary(ob.RELU, ob.F32, np.array([np.nan], np.float32))[0])
+    # 16-bit storage: f32 value, one rounding
+    x16 = wl.f32_to_bf16(x)
+    with np.errstate(all="ignore"):
+        want = wl.f32_to_bf16(np.tanh(wl.bf16_to_f32(x16).astype(np.float64)).astype(np.float32))
+    got = oracle.unary(ob.TANH, ob.BF16, x16)
+    nan = (want & 0x7FFF) > 0x7F80
+    assert np.all(np.abs(got[~nan].astype(np.int32) - want[~nan].astype(np.int32)) <= 1)
+
+
 def test_reduce_rules_nan_zero_empty(oracle):
     # docs/user/compute.md:384-388 and tests/compute_provider_native/reduction_test.cc:130-222,330-398
     x = np.array([[1.0, np.nan, 3.0], [-0.0, 0.0, -0.0], [-0.0, -0.0, -0.0], [-1.0, -2.0, -np.inf],
