@@ -258,6 +258,32 @@ def other_ops(torch, peak_gbs, only=None, iterations=40):
         report("swiglu_bf16", "4096x6144", 4096 * 6144, 3 * 4096 * 6144 * 2, ms, sets)
         del g, u, o
 
+    # the widened elementwise catalogue on the same shapes: one Unary and one Binary kind per storage type
+    if wanted("unary_binary"):
+        sets = 8
+        x32 = [torch.randn(4096, 4096, device=dev) for _ in range(sets)]
+        y32 = [torch.empty_like(x32[0]) for _ in range(sets)]
+        for name, kind in (("unary_tanh_f32", abi.UNARY_TANH), ("unary_gelu_f32", abi.UNARY_GELU)):
+            ms = time_op(torch, lambda i: lib.hyle_b200_unary(
+                stream, kind, abi.F32, x32[i].data_ptr(), y32[i].data_ptr(), 4096 * 4096), sets, iterations)
+            report(name, "4096x4096", 4096 * 4096, 2 * 4096 * 4096 * 4, ms, sets)
+        ms = time_op(torch, lambda i: lib.hyle_b200_binary(
+            stream, abi.BINARY_DIVIDE, abi.F32, x32[i].data_ptr(), x32[(i + 1) % sets].data_ptr(), y32[i].data_ptr(),
+            4096 * 4096, 4096 * 4096), sets, iterations)
+        report("binary_divide_f32", "4096x4096", 4096 * 4096, 3 * 4096 * 4096 * 4, ms, sets)
+        del x32, y32
+        x16 = [(torch.randn(4096, 6144, device=dev) * 1.5).to(torch.bfloat16) for _ in range(sets)]
+        y16 = [torch.empty_like(x16[0]) for _ in range(sets)]
+        for name, kind in (("unary_silu_bf16", abi.UNARY_SILU), ("unary_gelu_tanh_bf16", abi.UNARY_GELU_TANH)):
+            ms = time_op(torch, lambda i: lib.hyle_b200_unary(
+                stream, kind, abi.BF16, x16[i].data_ptr(), y16[i].data_ptr(), 4096 * 6144), sets, iterations)
+            report(name, "4096x6144", 4096 * 6144, 2 * 4096 * 6144 * 2, ms, sets)
+        ms = time_op(torch, lambda i: lib.hyle_b200_binary(
+            stream, abi.BINARY_MAXIMUM, abi.BF16, x16[i].data_ptr(), x16[(i + 1) % sets].data_ptr(), y16[i].data_ptr(),
+            4096 * 6144, 4096 * 6144), sets, iterations)
+        report("binary_maximum_bf16", "4096x6144", 4096 * 6144, 3 * 4096 * 6144 * 2, ms, sets)
+        del x16, y16
+
     # 4: f32 logits -> lse, softmax bf16, argmax, B = 256, vocabulary 151936
     if wanted("logits_reduce_f32"):
         sets = 4

@@ -48,6 +48,7 @@ SIGNATURES = {
     "hyle_b200_add_bias_row_sum_max_f32": (_i, [_p, _p, _p, _p, _p, _p, _u64, _u64]),
     "hyle_b200_rms_norm_bf16": (_i, [_p, _p, _p, _i, _p, _u64, _u64, _f]),
     "hyle_b200_add_rms_norm_bf16": (_i, [_p, _p, _p, _p, _i, _p, _p, _u64, _u64, _f]),
+    "hyle_b200_layer_norm_bf16": (_i, [_p, _p, _p, _p, _p, _u64, _u64, _f]),
     "hyle_b200_swiglu_bf16": (_i, [_p, _p, _p, _p, _u64, _u64, _u64, _u64]),
     "hyle_b200_logits_workspace_bytes": (_u64, [_u64, _u64]),
     "hyle_b200_logits_reduce_f32": (_i, [_p, _p, _u64, _u64, _p, _p, _p, _p, _p, _u64]),

@@ -209,8 +209,37 @@ __device__ __forceinline__ float sigmoid_exact(float x) {
   return x < 0.0f ? __fdiv_rn(e, 1.0f + e) : __fdiv_rn(1.0f, 1.0f + e);  // NaN falls through both compares
 }
 
-template <int kKind>
+// sigmoid to about 1e-6 relative in some six instructions, for results that are rounded to 16-bit
+// storage anyway: e = 2^(24 - |x| log2 e) so that ex2.approx (which flushes subnormal results)
+// still resolves exp(-|x|) down to 2^-150; the bias is removed inside the reciprocal.
+__device__ __forceinline__ float sigmoid_fast(float x) {
+  constexpr float kLog2e = 1.4426950408889634f;
+  constexpr float kBias = 16777216.0f;               // 2^24
+  constexpr float kUnbias = 5.9604644775390625e-8f;  // 2^-24
+  float e24;
+  asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(e24) : "f"(fmaf(-fabsf(x), kLog2e, 24.0f)));
+  float r;
+  asm("rcp.approx.ftz.f32 %0, %1;" : "=f"(r) : "f"(fmaf(e24, kUnbias, 1.0f)));  // 1 / (1 + e), in (0.5, 1]
+  const float numerator = x < 0.0f ? e24 : kBias;    // 2^24 * (e or 1)
+  return __fmul_rn(numerator, __fmul_rn(r, kUnbias));
+}
+
+// kFast (16-bit storage): the sigmoid-shaped kinds go through sigmoid_fast.  tanh(|x|) = 2 s(2|x|) - 1
+// cancels near zero, where the odd series takes over; gelu_tanh = x s(2 inner) needs no 1 + tanh.
+template <int kKind, bool kFast>
 __device__ __forceinline__ float unary_op(float x) {
+  if constexpr (kFast && kKind == HYLE_B200_UNARY_SIGMOID) return sigmoid_fast(x);
+  if constexpr (kFast && kKind == HYLE_B200_UNARY_SILU) return x == -INFINITY ? 0.0f : __fmul_rn(x, sigmoid_fast(x));
+  if constexpr (kFast && kKind == HYLE_B200_UNARY_GELU_TANH) {
+    const float inner = 0.79788456080286535588f * x * fmaf(0.044715f, x * x, 1.0f);
+    return x == -INFINITY ? 0.0f : __fmul_rn(x, sigmoid_fast(2.0f * inner));
+  }
+  if constexpr (kFast && kKind == HYLE_B200_UNARY_TANH) {
+    const float a = fabsf(x), a2 = a * a;
+    const float series = a * fmaf(a2, fmaf(a2, 0.13333333333f, -0.33333333333f), 1.0f);
+    const float large = fmaf(2.0f, sigmoid_fast(2.0f * a), -1.0f);
+    return copysignf(a < 0.04f ? series : large, x);  // NaN: both candidates are NaN
+  }
   if constexpr (kKind == HYLE_B200_UNARY_ABS) return fabsf(x);
   if constexpr (kKind == HYLE_B200_UNARY_NEG) return -x;
   if constexpr (kKind == HYLE_B200_UNARY_EXP) return expf(x);
@@ -234,10 +263,10 @@ __device__ __forceinline__ float unary_op(float x) {
 template <int kKind, int kDtype, class Vec>
 __device__ __forceinline__ Vec unary_vec(Vec a) {
   if constexpr (kDtype == HYLE_B200_F32) {
-    return make_float4(unary_op<kKind>(a.x), unary_op<kKind>(a.y), unary_op<kKind>(a.z), unary_op<kKind>(a.w));
+    return make_float4(unary_op<kKind, false>(a.x), unary_op<kKind, false>(a.y), unary_op<kKind, false>(a.z), unary_op<kKind, false>(a.w));
   } else {
     auto pair = [](uint32_t w) {
-      return narrow_pack<kDtype>(unary_op<kKind>(narrow_lo<kDtype>(w)), unary_op<kKind>(narrow_hi<kDtype>(w)));
+      return narrow_pack<kDtype>(unary_op<kKind, true>(narrow_lo<kDtype>(w)), unary_op<kKind, true>(narrow_hi<kDtype>(w)));
     };
     return make_uint4(pair(a.x), pair(a.y), pair(a.z), pair(a.w));
   }
@@ -267,8 +296,8 @@ unary_scalar_kernel(const typename Storage<kDtype>::Scalar *in, typename Storage
   grid_dependency_sync();
   const uint64_t stride = static_cast<uint64_t>(gridDim.x) * kThreads;
   for (uint64_t i = static_cast<uint64_t>(blockIdx.x) * kThreads + threadIdx.x; i < count; i += stride) {
-    if constexpr (kDtype == HYLE_B200_F32) out[i] = unary_op<kKind>(in[i]);
-    else out[i] = narrow_store<kDtype>(unary_op<kKind>(narrow_scalar<kDtype>(in[i])));
+    if constexpr (kDtype == HYLE_B200_F32) out[i] = unary_op<kKind, false>(in[i]);
+    else out[i] = narrow_store<kDtype>(unary_op<kKind, true>(narrow_scalar<kDtype>(in[i])));
   }
 }
 
@@ -304,16 +333,7 @@ int launch_unary(cudaStream_t stream, const void *in, void *out, uint64_t count)
 // 1e-6 relative, i.e. the result differs from the checker only when the bf16 rounding is within
 // that distance of a tie.
 __device__ __forceinline__ float silu(float x) {
-  constexpr float kLog2e = 1.4426950408889634f;
-  constexpr float kBias = 16777216.0f;           // 2^24
-  constexpr float kUnbias = 5.9604644775390625e-8f;  // 2^-24
-  float e24;
-  asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(e24) : "f"(fmaf(-fabsf(x), kLog2e, 24.0f)));
-  float r;
-  asm("rcp.approx.ftz.f32 %0, %1;" : "=f"(r) : "f"(fmaf(e24, kUnbias, 1.0f)));  // 1 / (1 + e), in (0.5, 1]
-  const float numerator = x < 0.0f ? e24 : kBias;    // 2^24 * (e or 1)
-  const float sigmoid = __fmul_rn(numerator, __fmul_rn(r, kUnbias));
-  return x == -INFINITY ? 0.0f : __fmul_rn(x, sigmoid);  // -inf * 0 would be NaN
+  return x == -INFINITY ? 0.0f : __fmul_rn(x, sigmoid_fast(x));  // -inf * 0 would be NaN
 }
 
 __device__ __forceinline__ uint32_t swiglu_pair(uint32_t g, uint32_t u) {

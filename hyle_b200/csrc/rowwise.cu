@@ -357,6 +357,150 @@ int dispatch_rms(cudaStream_t stream, const void *x, const void *residual, const
   return HYLE_B200_INVALID_VALUE;
 }
 
+// ================================================================================================
+// bf16 LayerNorm with optional bf16 scale and bias (both or neither).
+//   mean = (sum f32(x)) / hidden;  ss = sum (f32(x) - mean)^2 (fma, f32);
+//   inverse = 1.0f / sqrtf(ss / hidden + eps);
+//   y = bf16_rne(fma((f32(x) - mean) * inverse, scale, bias))         without scale: no fma
+// (src/simd/math/activations.cc:148-174).  Both sums run over values the warp / CTA already holds,
+// so HBM sees the row once in and once out.
+// ================================================================================================
+__device__ __forceinline__ float sum_vec(uint4 v, float acc) {
+  acc = __fadd_rn(acc, __fadd_rn(bf16_lo(v.x), bf16_hi(v.x)));
+  acc = __fadd_rn(acc, __fadd_rn(bf16_lo(v.y), bf16_hi(v.y)));
+  acc = __fadd_rn(acc, __fadd_rn(bf16_lo(v.z), bf16_hi(v.z)));
+  return __fadd_rn(acc, __fadd_rn(bf16_lo(v.w), bf16_hi(v.w)));
+}
+__device__ __forceinline__ float centered_squares(uint4 v, float mean, float acc) {
+  const uint32_t w[4] = {v.x, v.y, v.z, v.w};
+#pragma unroll
+  for (int i = 0; i < 4; ++i) {
+    const float lo = __fsub_rn(bf16_lo(w[i]), mean), hi = __fsub_rn(bf16_hi(w[i]), mean);
+    acc = fmaf(hi, hi, fmaf(lo, lo, acc));
+  }
+  return acc;
+}
+__device__ __forceinline__ float layer_value(float x, float mean, float inverse, bool affine, float scale, float bias) {
+  const float normalized = __fmul_rn(__fsub_rn(x, mean), inverse);
+  return affine ? fmaf(normalized, scale, bias) : normalized;
+}
+template <bool kAffine>
+__device__ __forceinline__ uint4 layer_vec(uint4 h, float mean, float inverse, const unsigned short *scale,
+                                           const unsigned short *bias, uint64_t element) {
+  uint4 s = make_uint4(0, 0, 0, 0), b = s;
+  if constexpr (kAffine) {
+    s = __ldg(reinterpret_cast<const uint4 *>(scale + element));
+    b = __ldg(reinterpret_cast<const uint4 *>(bias + element));
+  }
+  const uint32_t hw[4] = {h.x, h.y, h.z, h.w}, sw[4] = {s.x, s.y, s.z, s.w}, bw[4] = {b.x, b.y, b.z, b.w};
+  uint32_t out[4];
+#pragma unroll
+  for (int i = 0; i < 4; ++i)
+    out[i] = pack_bf16x2(layer_value(bf16_lo(hw[i]), mean, inverse, kAffine, bf16_lo(sw[i]), bf16_lo(bw[i])),
+                         layer_value(bf16_hi(hw[i]), mean, inverse, kAffine, bf16_hi(sw[i]), bf16_hi(bw[i])));
+  return make_uint4(out[0], out[1], out[2], out[3]);
+}
+
+// One warp per row, the row in registers: hidden == kVectors * 256.
+template <int kVectors, bool kAffine>
+__global__ void __launch_bounds__(kThreads)
+layer_norm_warp_kernel(const uint4 *x, const unsigned short *__restrict__ scale, const unsigned short *__restrict__ bias,
+                       uint4 *y, uint64_t rows, float eps) {
+  grid_dependency_sync();
+  constexpr uint32_t kHidden = kVectors * 256;
+  const int lane = threadIdx.x & 31;
+  const uint64_t warps = static_cast<uint64_t>(gridDim.x) * (blockDim.x >> 5);
+  for (uint64_t row = static_cast<uint64_t>(blockIdx.x) * (blockDim.x >> 5) + (threadIdx.x >> 5); row < rows;
+       row += warps) {
+    const uint64_t base = row * (kHidden / 8);
+    uint4 h[kVectors];
+#pragma unroll
+    for (int k = 0; k < kVectors; ++k) h[k] = ld_stream(x + base + k * 32 + lane);
+    float sum = 0.0f;
+#pragma unroll
+    for (int k = 0; k < kVectors; ++k) sum = sum_vec(h[k], sum);
+    const float mean = __fdiv_rn(warp_sum(sum), static_cast<float>(kHidden));
+    float ss = 0.0f;
+#pragma unroll
+    for (int k = 0; k < kVectors; ++k) ss = centered_squares(h[k], mean, ss);
+    const float inverse = inverse_rms(warp_sum(ss), kHidden, eps);
+#pragma unroll
+    for (int k = 0; k < kVectors; ++k)
+      st_stream(y + base + k * 32 + lane,
+                layer_vec<kAffine>(h[k], mean, inverse, scale, bias, static_cast<uint64_t>(k * 32 + lane) * 8));
+  }
+}
+
+// One CTA per row, the row staged in shared memory: any hidden up to kMaxStagedHidden.
+template <bool kAffine>
+__global__ void __launch_bounds__(kThreads)
+layer_norm_cta_kernel(const unsigned short *x, const unsigned short *__restrict__ scale,
+                      const unsigned short *__restrict__ bias, unsigned short *y, uint64_t rows, uint32_t hidden,
+                      float eps) {
+  grid_dependency_sync();
+  extern __shared__ __align__(16) unsigned char staged_bytes[];
+  __shared__ float s_partial[2][kWarps];
+  unsigned short *staged = reinterpret_cast<unsigned short *>(staged_bytes);
+  const int t = threadIdx.x, lane = t & 31, warp = t >> 5;
+  auto cta_sum = [&](float v, int slot) {
+    v = warp_sum(v);
+    if (lane == 0) s_partial[slot][warp] = v;
+    __syncthreads();
+    float total = s_partial[slot][0];
+#pragma unroll
+    for (int w = 1; w < kWarps; ++w) total = __fadd_rn(total, s_partial[slot][w]);
+    return total;
+  };
+  for (uint64_t row = blockIdx.x; row < rows; row += gridDim.x) {
+    const uint64_t base = row * hidden;
+    float sum = 0.0f;
+    for (uint32_t i = t; i < hidden; i += kThreads) {
+      const unsigned short h = x[base + i];
+      staged[i] = h;
+      sum = __fadd_rn(sum, bf16_to_f32(h));
+    }
+    const float mean = __fdiv_rn(cta_sum(sum, 0), static_cast<float>(hidden));
+    float ss = 0.0f;
+    for (uint32_t i = t; i < hidden; i += kThreads) {
+      const float c = __fsub_rn(bf16_to_f32(staged[i]), mean);
+      ss = fmaf(c, c, ss);
+    }
+    const float inverse = inverse_rms(cta_sum(ss, 1), hidden, eps);
+    for (uint32_t i = t; i < hidden; i += kThreads)
+      y[base + i] = f32_to_bf16(layer_value(bf16_to_f32(staged[i]), mean, inverse, kAffine,
+                                            kAffine ? bf16_to_f32(scale[i]) : 0.0f, kAffine ? bf16_to_f32(bias[i]) : 0.0f));
+    __syncthreads();  // the staged row and the partial slots are rewritten by the next iteration
+  }
+}
+
+template <bool kAffine>
+int launch_layer_norm(cudaStream_t stream, const void *x, const void *scale, const void *bias, void *y, uint64_t rows,
+                      uint64_t hidden, float eps) {
+  const bool aligned = aligned_to(x, 16) && aligned_to(y, 16) && (!kAffine || (aligned_to(scale, 16) && aligned_to(bias, 16)));
+  const int sms = sm_count();
+  auto warp_launch = [&](auto vectors_tag) {
+    constexpr int kVectors = decltype(vectors_tag)::value;
+    int warps_per_cta = 2;
+    if (rows < static_cast<uint64_t>(sms) * 2) warps_per_cta = 1;
+    const unsigned grid = clamp_grid((rows + warps_per_cta - 1) / warps_per_cta, 1u << 20);
+    return launch(layer_norm_warp_kernel<kVectors, kAffine>, dim3(grid), dim3(warps_per_cta * 32), 0, stream,
+                  static_cast<const uint4 *>(x), static_cast<const unsigned short *>(scale),
+                  static_cast<const unsigned short *>(bias), static_cast<uint4 *>(y), rows, eps);
+  };
+  if (aligned && hidden == 256) return warp_launch(std::integral_constant<int, 1>{});
+  if (aligned && hidden == 512) return warp_launch(std::integral_constant<int, 2>{});
+  if (aligned && hidden == 1024) return warp_launch(std::integral_constant<int, 4>{});
+  if (aligned && hidden == 2048) return warp_launch(std::integral_constant<int, 8>{});
+  if (hidden > kMaxStagedHidden) return HYLE_B200_NOT_SUPPORTED;
+  const size_t staged = (static_cast<size_t>(hidden) * 2 + 15) & ~static_cast<size_t>(15);
+  auto kernel = layer_norm_cta_kernel<kAffine>;
+  if (staged > 48 * 1024) cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, 64 * 1024);
+  return launch(kernel, dim3(clamp_grid(rows, static_cast<uint64_t>(sms) * 4)), dim3(kThreads), staged, stream,
+                static_cast<const unsigned short *>(x), static_cast<const unsigned short *>(scale),
+                static_cast<const unsigned short *>(bias), static_cast<unsigned short *>(y), rows,
+                static_cast<uint32_t>(hidden), eps);
+}
+
 }  // namespace
 }  // namespace hb
 
@@ -408,4 +552,14 @@ extern "C" int hyle_b200_add_rms_norm_bf16(hyle_b200_stream_t stream, const void
                                            uint64_t hidden, float epsilon) {
   return dispatch_rms<true>(reinterpret_cast<cudaStream_t>(stream), x, residual, weight, weight_dtype,
                             y, h, rows, hidden, epsilon);
+}
+
+extern "C" int hyle_b200_layer_norm_bf16(hyle_b200_stream_t stream, const void *x, const void *scale,
+                                         const void *bias, void *y, uint64_t rows, uint64_t hidden,
+                                         float epsilon) {
+  if (rows == 0 || hidden == 0) return HYLE_B200_OK;
+  if (x == nullptr || y == nullptr || (scale == nullptr) != (bias == nullptr)) return HYLE_B200_INVALID_VALUE;
+  auto s = reinterpret_cast<cudaStream_t>(stream);
+  if (scale == nullptr) return launch_layer_norm<false>(s, x, nullptr, nullptr, y, rows, hidden, epsilon);
+  return launch_layer_norm<true>(s, x, scale, bias, y, rows, hidden, epsilon);
 }

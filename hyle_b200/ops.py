@@ -155,6 +155,21 @@ def add_rms_norm(x: torch.Tensor, residual: torch.Tensor, weight: Optional[torch
     return y, h
 
 
+def layer_norm(x: torch.Tensor, scale: Optional[torch.Tensor], bias: Optional[torch.Tensor], eps: float = 1e-5,
+               out: Optional[torch.Tensor] = None) -> torch.Tensor:
+    """LayerNorm over the last axis of a bf16 tensor; bf16 ``scale`` and ``bias`` of [hidden], both or neither."""
+    _device_tensor(x, "x")
+    if x.dtype != torch.bfloat16 or (scale is None) != (bias is None):
+        raise ValueError("layer_norm takes bf16 x and bf16 scale and bias (both or neither)")
+    hidden = x.shape[-1]
+    rows = x.numel() // hidden if hidden else 0
+    if out is None:
+        out = torch.empty_like(x)
+    abi.check("hyle_b200_layer_norm_bf16", abi.load().hyle_b200_layer_norm_bf16(
+        _stream(), x.data_ptr(), _ptr(scale), _ptr(bias), out.data_ptr(), rows, hidden, eps))
+    return out
+
+
 def swiglu(gate: torch.Tensor, up: torch.Tensor) -> torch.Tensor:
     """GatedActivation{kSilu, kSeparate}: silu(gate) * up on bf16 tensors of one shape."""
     _device_tensor(gate, "gate"), _device_tensor(up, "up")

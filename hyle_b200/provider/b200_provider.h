@@ -34,7 +34,7 @@ inline constexpr ProviderRuntimeProperties kRuntime{.replay_class = ProviderRepl
                                                     .capture_compatible = true};
 
 enum class Entry : std::uint8_t {
-  kUnary, kBinary, kReduceRows, kRmsNorm, kSwiglu, kSoftmax, kCastF32ToBf16, kArgmax, kQ8Encode,
+  kUnary, kBinary, kReduceRows, kRmsNorm, kLayerNorm, kSwiglu, kSoftmax, kCastF32ToBf16, kArgmax, kQ8Encode,
   kAddRmsNorm, kBiasRowSumMax, kLogitsReduce, kQ8Roundtrip
 };
 
@@ -154,6 +154,19 @@ inline std::optional<Plan> match(const Operation &op, std::span<const TensorDesc
     p.epsilon = norm->epsilon;
     return p;
   }
+  if (const auto *norm = op.get_if<LayerNorm>()) {
+    // x alone, or x with scale and bias of [hidden], all bf16 (scale without bias is left to others)
+    if ((in.size() != 1 && in.size() != 3) || out.size() != 1 || in[0].data_type() != DataType::kBFloat16 ||
+        out[0] != in[0] || norm->accumulation_type != DataType::kFloat32 || p.cols > 32768)
+      return std::nullopt;
+    p.has_weight = in.size() == 3;
+    if (p.has_weight && (in[1].data_type() != DataType::kBFloat16 || in[2].data_type() != DataType::kBFloat16 ||
+                         elements(in[1]) != p.cols || elements(in[2]) != p.cols))
+      return std::nullopt;
+    p.entry = Entry::kLayerNorm;
+    p.epsilon = norm->epsilon;
+    return p;
+  }
   if (const auto *gated = op.get_if<GatedActivation>()) {
     if (gated->activation != GatedActivationKind::kSilu || in[0].data_type() != DataType::kBFloat16 ||
         out.size() != 1 || out[0].data_type() != DataType::kBFloat16)
@@ -252,6 +265,9 @@ inline int launch(const Plan &p, hyle_b200_stream_t stream, const void *const *i
     case Entry::kRmsNorm:
       return hyle_b200_rms_norm_bf16(stream, in[0], p.has_weight ? in[1] : nullptr, p.dtype, out[0], p.rows, p.cols,
                                      p.epsilon);
+    case Entry::kLayerNorm:
+      return hyle_b200_layer_norm_bf16(stream, in[0], p.has_weight ? in[1] : nullptr, p.has_weight ? in[2] : nullptr,
+                                       out[0], p.rows, p.cols, p.epsilon);
     case Entry::kSwiglu: {
       const auto *gate = static_cast<const std::uint16_t *>(in[0]);
       const void *up = p.up_offset ? static_cast<const void *>(gate + p.up_offset) : in[1];
@@ -287,7 +303,8 @@ inline int launch(const Plan &p, hyle_b200_stream_t stream, const void *const *i
 }
 
 inline AliasSupport alias_support(const Plan &p, std::size_t output, std::size_t input) noexcept {
-  const bool in_place = (p.entry == Entry::kUnary || p.entry == Entry::kBinary || p.entry == Entry::kRmsNorm || p.entry == Entry::kSoftmax) &&
+  const bool in_place = (p.entry == Entry::kUnary || p.entry == Entry::kBinary || p.entry == Entry::kRmsNorm ||
+                         p.entry == Entry::kLayerNorm || p.entry == Entry::kSoftmax) &&
                         output == 0 && input == 0;
   return {in_place, 0};
 }

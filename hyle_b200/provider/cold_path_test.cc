@@ -118,6 +118,13 @@ int main() {
     check(taken(*context, Operation(RmsNorm{.epsilon = 1e-6F}), in32, out), "RmsNorm bf16, f32 weight");
     check(!taken(*context, Operation(RmsNorm{.epsilon = 1e-6F}), inh, out), "RmsNorm with f16 weight not taken");
   }
+  {  // LayerNorm bf16: alone, or with bf16 scale and bias
+    const std::array out{bf16_mat};
+    const std::array plain{bf16_mat};
+    const std::array affine{bf16_mat, bf16_w, bf16_w};
+    check(taken(*context, Operation(LayerNorm{.epsilon = 1e-5F}), plain, out), "LayerNorm bf16 without parameters");
+    check(taken(*context, Operation(LayerNorm{.epsilon = 1e-5F}), affine, out), "LayerNorm bf16, bf16 scale and bias");
+  }
   {  // GatedActivation: separate and packed halves
     const auto gate = dense(DataType::kBFloat16, {32, 6144});
     const auto packed = dense(DataType::kBFloat16, {32, 12288});

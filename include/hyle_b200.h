@@ -187,6 +187,20 @@ HYLE_B200_API int hyle_b200_add_rms_norm_bf16(hyle_b200_stream_t stream, const v
                                               uint64_t rows, uint64_t hidden, float epsilon);
 
 /* ---------------------------------------------------------------------------------------------
+ * LayerNorm{epsilon, accumulation=f32} over the last axis of a bf16 tensor, with a bf16 scale and
+ * bias of [hidden] (both or neither).
+ * Replaces: LayerNorm schema include/hyle/compute/operation.h:330-333, scalar floor
+ * src/simd/math/activations.cc:148-174:
+ *   mean = sum(x) / hidden; inverse = 1.0f / sqrt(sum((x - mean)^2) / hidden + epsilon);
+ *   y = bf16_rne(fma((x - mean) * inverse, scale, bias)).
+ * hidden <= 32768.  The sums are taken in a fixed (tree) order; y is within one bf16 step of the
+ * sequential-order result.
+ */
+HYLE_B200_API int hyle_b200_layer_norm_bf16(hyle_b200_stream_t stream, const void *x,
+                                            const void *scale, const void *bias, void *y,
+                                            uint64_t rows, uint64_t hidden, float epsilon);
+
+/* ---------------------------------------------------------------------------------------------
  * GatedActivation{kSilu}: out = bf16_rne(silu(f32 gate) * f32 up), silu(-inf) = 0.
  * Replaces: GatedActivation schema include/hyle/compute/operation.h:91-100,362-365 and the scalar
  * floor src/simd/math/activations.cc:21-25,44-47,114-122.

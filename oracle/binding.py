@@ -60,6 +60,7 @@ class Oracle:
         L.hyle_oracle_f32_to_f16.argtypes = [_f]
         L.hyle_oracle_binary.argtypes = [_i, _i, _vp, _vp, _vp, _u64, _u64]
         L.hyle_oracle_unary.argtypes = [_i, _i, _vp, _vp, _u64]
+        L.hyle_oracle_layer_norm_bf16.argtypes = [_vp, _vp, _vp, _vp, _vp, _u64, _u64, _f]
         L.hyle_oracle_reduce_rows_f32.argtypes = [_i, _vp, _vp, _u64, _u64]
         L.hyle_oracle_row_sum_f64.argtypes = [_vp, _vp, _vp, _u64, _u64]
         L.hyle_oracle_rms_norm_bf16.argtypes = [_vp, _vp, _i, _vp, _vp, _u64, _u64, _f]
@@ -144,6 +145,15 @@ class Oracle:
         w, wdt = self._weight(weight)
         y, y32 = np.empty_like(x), np.empty(x.shape, np.float32)
         self.lib.hyle_oracle_rms_norm_bf16(_ptr(x), _ptr(w), wdt, _ptr(y), _ptr(y32), rows, hidden, eps)
+        return y, y32
+
+    def layer_norm(self, x, scale, bias, eps):
+        x = _c(x, np.uint16)
+        rows, hidden = x.shape
+        scale = None if scale is None else _c(scale, np.uint16)
+        bias = None if bias is None else _c(bias, np.uint16)
+        y, y32 = np.empty_like(x), np.empty(x.shape, np.float32)
+        self.lib.hyle_oracle_layer_norm_bf16(_ptr(x), _ptr(scale), _ptr(bias), _ptr(y), _ptr(y32), rows, hidden, eps)
         return y, y32
 
     def add_rms_norm(self, x, residual, weight, eps):
@@ -243,6 +253,7 @@ class RefFloor:
         L.hyle_ref_softmax_f32.argtypes = [_i, _vp, _vp, _u64, _u64]
         L.hyle_ref_argmax_f32.argtypes = [_vp, _vp, _vp, _u64, _u64]
         L.hyle_ref_activation_f32.argtypes = [_i, _vp, _vp, _u64]
+        L.hyle_ref_layer_norm_bf16.argtypes = [_vp, _vp, _vp, _vp, _u64, _u64, _f]
         L.hyle_ref_activation_f32.restype = _i
 
     def set_threads(self, n: int) -> None:
@@ -269,6 +280,15 @@ class RefFloor:
         weight = None if weight is None else _c(weight, np.uint16)
         y = np.empty_like(x)
         self.lib.hyle_ref_rms_norm_bf16(_ptr(x), _ptr(weight), _ptr(y), rows, hidden, eps)
+        return y
+
+    def layer_norm(self, x, scale, bias, eps):
+        x = _c(x, np.uint16)
+        rows, hidden = x.shape
+        scale = None if scale is None else _c(scale, np.uint16)
+        bias = None if bias is None else _c(bias, np.uint16)
+        y = np.empty_like(x)
+        self.lib.hyle_ref_layer_norm_bf16(_ptr(x), _ptr(scale), _ptr(bias), _ptr(y), rows, hidden, eps)
         return y
 
     def softmax(self, x, log=False):

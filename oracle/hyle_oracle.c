@@ -231,6 +231,35 @@ ORACLE_API void hyle_oracle_rms_norm_bf16(const uint16_t *x, const void *weight,
             hidden, eps);
 }
 
+/* ---- LayerNorm, bf16 storage, f32 accumulation ------------------------------------------------
+ * src/simd/math/activations.cc:148-174: sequential f32 sum -> mean; fma-accumulated centered squares;
+ * inverse = 1.0f / sqrt(ss / n + eps); y = round(fma((x - mean) * inverse, scale, bias)) or, without
+ * scale and bias, round((x - mean) * inverse). */
+ORACLE_API void hyle_oracle_layer_norm_bf16(const uint16_t *x, const uint16_t *scale, const uint16_t *bias,
+                                            uint16_t *y, float *y_f32, uint64_t rows, uint64_t hidden,
+                                            float eps) {
+#pragma omp parallel for schedule(static)
+  for (uint64_t r = 0; r < rows; ++r) {
+    const uint16_t *row = x + r * hidden;
+    float sum = 0.0f;
+    for (uint64_t i = 0; i < hidden; ++i) sum += hyle_oracle_bf16_to_f32(row[i]);
+    const float mean = sum / (float)hidden;
+    float ss = 0.0f;
+    for (uint64_t i = 0; i < hidden; ++i) {
+      const float c = hyle_oracle_bf16_to_f32(row[i]) - mean;
+      ss = fmaf(c, c, ss);
+    }
+    const float inverse = 1.0f / sqrtf(ss / (float)hidden + eps);
+    for (uint64_t i = 0; i < hidden; ++i) {
+      const float normalized = (hyle_oracle_bf16_to_f32(row[i]) - mean) * inverse;
+      const float v = scale ? fmaf(normalized, hyle_oracle_bf16_to_f32(scale[i]), hyle_oracle_bf16_to_f32(bias[i]))
+                            : normalized;
+      y[r * hidden + i] = hyle_oracle_f32_to_bf16(v);
+      if (y_f32) y_f32[r * hidden + i] = v;
+    }
+  }
+}
+
 /* Binary{kAdd} in bf16 (f32 add, one RNE; docs/user/compute.md:358-359) followed by the RmsNorm
  * above reading the rounded sum: the unfused composition the fused kernel must equal. */
 ORACLE_API void hyle_oracle_add_rms_norm_bf16(const uint16_t *x, const uint16_t *residual,

@@ -3,7 +3,7 @@
 // This translation unit contains no arithmetic of its own.  It is compiled together with the
 // reference's Highway-free sources, in place from the mounted reference tree (oracle/Makefile):
 //   src/simd/math/activations.cc   swiglu_bf16_scalar, rms_norm_bf16_scalar, softmax_f32_scalar,
-//                                  log_softmax_f32_scalar, {sigmoid,gelu,gelu_tanh,silu,relu}_f32_scalar
+//                                  log_softmax_f32_scalar, {sigmoid,gelu,gelu_tanh,silu,relu}_f32_scalar, layer_norm_bf16_scalar
 //   src/simd/sort/top_k.cc         top_k_f32
 //   include/hyle/simd/dtype.h      f32_to_bf16, bf16_to_f32, f32_to_f16, f16_to_f32
 // and only forwards row by row, so tests can pin oracle/hyle_oracle.c against the reference's code
@@ -54,6 +54,16 @@ REF_API void hyle_ref_rms_norm_bf16(const uint16_t *x, const uint16_t *weight, u
     simd::detail::rms_norm_bf16_scalar(reinterpret_cast<const simd::bfloat16_t *>(x + r * hidden),
                                        reinterpret_cast<const simd::bfloat16_t *>(weight),
                                        reinterpret_cast<simd::bfloat16_t *>(y + r * hidden), hidden, eps);
+}
+
+REF_API void hyle_ref_layer_norm_bf16(const uint16_t *x, const uint16_t *scale, const uint16_t *bias, uint16_t *y,
+                                      uint64_t rows, uint64_t hidden, float eps) {
+#pragma omp parallel for schedule(static)
+  for (uint64_t r = 0; r < rows; ++r)
+    simd::detail::layer_norm_bf16_scalar(reinterpret_cast<const simd::bfloat16_t *>(x + r * hidden),
+                                         reinterpret_cast<const simd::bfloat16_t *>(scale),
+                                         reinterpret_cast<const simd::bfloat16_t *>(bias),
+                                         reinterpret_cast<simd::bfloat16_t *>(y + r * hidden), hidden, eps);
 }
 
 // kind: 7 sigmoid, 8 relu, 9 gelu, 10 gelu_tanh, 11 silu (the numbering of hyle::compute::UnaryKind)

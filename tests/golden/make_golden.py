@@ -76,6 +76,15 @@ def main():
     index, value = ref.argmax(rows)
     out["argmax_x"], out["argmax_index"], out["argmax_value"] = rows, index, value
 
+    # LayerNorm: bf16, eps 1e-5, with and without scale and bias; rows with a large common offset.
+    for hidden in (1, 7, 129, 2048, 4100):
+        x = f32_to_bf16((3.0 * rng.standard_normal((3, hidden)) + np.array([[0.0], [5.0], [-40.0]])).astype(np.float32))
+        scale = f32_to_bf16(rng.uniform(0.5, 1.5, hidden).astype(np.float32))
+        bias = f32_to_bf16(rng.standard_normal(hidden).astype(np.float32))
+        out[f"layer_x_{hidden}"], out[f"layer_scale_{hidden}"], out[f"layer_bias_{hidden}"] = x, scale, bias
+        out[f"layer_y_{hidden}"] = ref.layer_norm(x, scale, bias, 1e-5)
+        out[f"layer_y_plain_{hidden}"] = ref.layer_norm(x, None, None, 1e-5)
+
     # Unary activations of the scalar floor (UnaryKind numbers): sigmoid 7, relu 8, gelu 9,
     # gelu_tanh 10, silu 11, on specials and a spread of ordinary values.
     special = np.array([0.0, -0.0, np.nan, np.inf, -np.inf, 1.0, -1.0, 20.0, -20.0, 88.0, -104.0, 1e-40, -1e-40,

@@ -386,6 +386,36 @@ def test_argmax_golden_cases(oracle, golden):
     assert np.array_equal(idx2.cpu().numpy(), golden["argmax_index"])
 
 
+# ---- LayerNorm ------------------------------------------------------------------------------------------------------------
+@pytest.mark.parametrize("hidden", [1, 8, 100, 256, 1000, 2048, 4096, 5000, 32768])
+def test_layer_norm_hidden_sizes(oracle, hidden):
+    """One bf16 step from the checker's rounded output, plus the conditioning of x - mean: the
+    mean from another summation order differs by a few 1e-7 of the row's magnitude, which is an
+    ABSOLUTE difference of that size (times inverse and scale) in every output, however small."""
+    rng = np.random.default_rng(hidden)
+    rows = 37 if hidden <= 4096 else 5
+    x32 = (3.0 * rng.standard_normal((rows, hidden)) + rng.uniform(-20, 20, (rows, 1))).astype(np.float32)
+    x = wl.f32_to_bf16(x32)
+    scale = wl.f32_to_bf16(rng.uniform(0.5, 1.5, hidden).astype(np.float32))
+    bias = wl.f32_to_bf16(rng.standard_normal(hidden).astype(np.float32))
+    xf = wl.bf16_to_f32(x).astype(np.float64)
+    inverse = 1.0 / np.sqrt(xf.var(axis=1, keepdims=True) + 1e-5)
+    magnitude = np.abs(xf).max(axis=1, keepdims=True)
+    for affine in (True, False):
+        s, b = (scale, bias) if affine else (None, None)
+        want, want32 = oracle.layer_norm(x, s, b, 1e-5)
+        got = bf16_words(ops.layer_norm(to_dev_bf16(x), None if s is None else to_dev_bf16(s),
+                                        None if b is None else to_dev_bf16(b), 1e-5))
+        g, w = wl.bf16_to_f32(got).astype(np.float64), wl.bf16_to_f32(want).astype(np.float64)
+        gain = np.abs(wl.bf16_to_f32(scale).astype(np.float64))[None, :] if affine else 1.0
+        slack = 2e-6 * magnitude * inverse * gain * (1.0 + np.log2(max(hidden, 2)))
+        assert np.all(np.abs(g - w) <= 2.0 ** -7 * np.abs(w) + slack + TINY)
+        for g_row, w_row in zip(g, w):
+            assert np.sqrt(np.sum((g_row - w_row) ** 2)) <= BF16_REL * np.sqrt(np.sum(w_row ** 2)) + TINY
+        if hidden > 1:
+            assert (got != want).mean() < 2e-2
+
+
 # ---- Unary -----------------------------------------------------------------------------------------------------------------
 UNARY_BIT_EXACT = {abi.UNARY_ABS, abi.UNARY_NEG, abi.UNARY_SQRT, abi.UNARY_RSQRT, abi.UNARY_RELU}
 # gelu = 0.5 x (1 + erf(x / sqrt 2)) and its tanh form cancel for negative x: an error of one ulp in

@@ -181,6 +181,17 @@ def test_unary_activations_match_reference_floor(oracle, ref_floor):
         assert np.array_equal(bits(got)[~np.isnan(want)], bits(want)[~np.isnan(want)]), kind
 
 
+@pytest.mark.parametrize("hidden", [1, 7, 129, 2048, 4100])
+def test_layer_norm_matches_reference_floor_and_golden(oracle, golden, hidden, request):
+    x, scale, bias = golden[f"layer_x_{hidden}"], golden[f"layer_scale_{hidden}"], golden[f"layer_bias_{hidden}"]
+    assert np.array_equal(oracle.layer_norm(x, scale, bias, 1e-5)[0], golden[f"layer_y_{hidden}"])
+    assert np.array_equal(oracle.layer_norm(x, None, None, 1e-5)[0], golden[f"layer_y_plain_{hidden}"])
+    from oracle.binding import RefFloor
+    if RefFloor.available():
+        ref = request.getfixturevalue("ref_floor")
+        assert np.array_equal(oracle.layer_norm(x, scale, bias, 1e-5)[0], ref.layer_norm(x, scale, bias, 1e-5))
+
+
 def test_unary_activations_match_golden(oracle, golden):
     """The same pin from the committed vectors, for machines without the reference tree."""
     x = golden["unary_x"]
