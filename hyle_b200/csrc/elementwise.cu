@@ -229,10 +229,14 @@ __device__ __forceinline__ float sigmoid_fast(float x) {
 template <int kKind, bool kFast>
 __device__ __forceinline__ float unary_op(float x) {
   if constexpr (kFast && kKind == HYLE_B200_UNARY_SIGMOID) return sigmoid_fast(x);
-  if constexpr (kFast && kKind == HYLE_B200_UNARY_SILU) return x == -INFINITY ? 0.0f : __fmul_rn(x, sigmoid_fast(x));
+  if constexpr (kFast && kKind == HYLE_B200_UNARY_SILU) {
+    const float product = __fmul_rn(x, sigmoid_fast(x));  // unconditional: a select, not a branch
+    return x == -INFINITY ? 0.0f : product;
+  }
   if constexpr (kFast && kKind == HYLE_B200_UNARY_GELU_TANH) {
     const float inner = 0.79788456080286535588f * x * fmaf(0.044715f, x * x, 1.0f);
-    return x == -INFINITY ? 0.0f : __fmul_rn(x, sigmoid_fast(2.0f * inner));
+    const float product = __fmul_rn(x, sigmoid_fast(2.0f * inner));
+    return x == -INFINITY ? 0.0f : product;
   }
   if constexpr (kFast && kKind == HYLE_B200_UNARY_TANH) {
     const float a = fabsf(x), a2 = a * a;
@@ -333,7 +337,8 @@ int launch_unary(cudaStream_t stream, const void *in, void *out, uint64_t count)
 // 1e-6 relative, i.e. the result differs from the checker only when the bf16 rounding is within
 // that distance of a tie.
 __device__ __forceinline__ float silu(float x) {
-  return x == -INFINITY ? 0.0f : __fmul_rn(x, sigmoid_fast(x));  // -inf * 0 would be NaN
+  const float product = __fmul_rn(x, sigmoid_fast(x));  // computed unconditionally: a select, not a branch
+  return x == -INFINITY ? 0.0f : product;               // -inf * 0 would be NaN
 }
 
 __device__ __forceinline__ uint32_t swiglu_pair(uint32_t g, uint32_t u) {
