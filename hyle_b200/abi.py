@@ -12,7 +12,7 @@ import os
 from .build import LIBRARY_PATH
 
 # enum hyle_b200_dtype
-F32, BF16, F16 = 0, 1, 2
+F32, BF16, F16, E4M3, E5M2, BOOL, I32 = 0, 1, 2, 3, 4, 5, 6
 # enum hyle_b200_binary_kind
 BINARY_ADD, BINARY_MULTIPLY, BINARY_SUBTRACT, BINARY_DIVIDE, BINARY_MINIMUM, BINARY_MAXIMUM = 0, 1, 2, 3, 4, 5
 # enum hyle_b200_unary_kind
@@ -30,7 +30,7 @@ STATUS_INVALID_Q8_INPUT = 1
 STATUS_EXCHANGE_TIMEOUT = 2
 EXCHANGE_MAX_RANKS, EXCHANGE_MAILBOX_BYTES, EXCHANGE_HANDLE_BYTES = 8, 256, 64
 
-ABI_VERSION = 5
+ABI_VERSION = 6
 
 _p = ctypes.c_void_p
 _u64 = ctypes.c_uint64
@@ -53,6 +53,7 @@ SIGNATURES = {
     "hyle_b200_logits_workspace_bytes": (_u64, [_u64, _u64]),
     "hyle_b200_logits_reduce_f32": (_i, [_p, _p, _u64, _u64, _p, _p, _p, _p, _p, _u64]),
     "hyle_b200_softmax_f32": (_i, [_p, _i, _p, _p, _u64, _u64, _p, _u64]),
+    "hyle_b200_cast": (_i, [_p, _i, _i, _p, _p, _u64]),
     "hyle_b200_cast_f32_to_bf16": (_i, [_p, _p, _p, _u64]),
     "hyle_b200_q8_0_encode": (_i, [_p, _i, _p, _u64, _p, _p]),
     "hyle_b200_q8_0_decode_bf16": (_i, [_p, _p, _u64, _p]),

@@ -1,0 +1,275 @@
+// Cast between the storage types of the tensor library: f32 / bf16 / f16 among themselves, the two
+// 8-bit floating formats, bool and i32 -> f32.  Every pair is a pure function of one element and
+// bit-exact against the CPU route (src/compute_provider_native/cast.cc:20-176 with the conversions
+// of include/hyle/simd/dtype.h):
+//   * wide -> narrow floating types round to nearest even once;
+//   * E4M3 (bias 7, no infinity, NaN = 0x7F) and E5M2 (bias 15, IEEE-like) encode with
+//     round-to-nearest-even and SATURATE finite overflow to the largest normal; an infinite input
+//     saturates for E4M3 and stays infinite for E5M2 (dtype.h:163-213);
+//   * bool is truth: a floating value converts to 1 unless its magnitude bits are all zero (NaN and
+//     subnormals are true, -0 is false); a bool byte converts to 1.0 when non-zero (cast.cc:78-91);
+//   * i32 -> f32 rounds to nearest even (cast.cc:21-41).
+// HBM-bound: a thread moves eight consecutive elements per step with the widest loads and stores the
+// two element sizes allow (8 to 32 bytes), four steps in flight.
+#include "common.cuh"
+
+namespace hb {
+namespace {
+
+constexpr int kThreads = 256;
+constexpr int kCtasPerSm = 8;
+
+// ---- 8-bit floating formats ----------------------------------------------------------------------
+template <int kExpBits, int kManBits, int kBias, bool kHasInf>
+__device__ __forceinline__ float f8_to_f32(uint32_t byte) {
+  const uint32_t sign = (byte & 0x80u) << 24;
+  const uint32_t exponent = (byte >> kManBits) & ((1u << kExpBits) - 1u);
+  const uint32_t mantissa = byte & ((1u << kManBits) - 1u);
+  constexpr uint32_t kMaxExp = (1u << kExpBits) - 1u;
+  if (kHasInf && exponent == kMaxExp) return __uint_as_float(sign | 0x7f800000u | (mantissa << (23 - kManBits)));
+  if (!kHasInf && exponent == kMaxExp && mantissa == (1u << kManBits) - 1u) return __uint_as_float(sign | 0x7fc00000u);
+  if (exponent == 0) {  // zero or subnormal: mantissa * 2^(1 - bias - kManBits), exact in f32
+    const float magnitude = static_cast<float>(mantissa) * __uint_as_float((127u + 1 - kBias - kManBits) << 23);
+    return __uint_as_float(sign | __float_as_uint(magnitude));
+  }
+  return __uint_as_float(sign | ((exponent - kBias + 127u) << 23) | (mantissa << (23 - kManBits)));
+}
+
+template <int kExpBits, int kManBits, int kBias, bool kHasInf>
+__device__ __forceinline__ uint32_t f32_to_f8(float value, uint32_t max_normal_f32_bits, uint32_t max_normal_bits,
+                                              uint32_t nan_bits) {
+  const uint32_t u = __float_as_uint(value);
+  const uint32_t sign = (u >> 31) << 7;
+  const uint32_t magnitude = u & 0x7fffffffu;
+  if (magnitude > 0x7f800000u) return sign | nan_bits;
+  if (magnitude == 0x7f800000u) return kHasInf ? sign | (((1u << kExpBits) - 1u) << kManBits) : sign | max_normal_bits;
+  if (magnitude > max_normal_f32_bits) return sign | max_normal_bits;  // finite overflow saturates
+  const int exponent = static_cast<int>(magnitude >> 23) - 127 + kBias;  // biased for the 8-bit format
+  const uint32_t fraction = magnitude & 0x7fffffu;
+  if (exponent >= 1) {
+    constexpr int kDrop = 23 - kManBits;
+    uint32_t mantissa = fraction >> kDrop;
+    const uint32_t rest = fraction & ((1u << kDrop) - 1u), half = 1u << (kDrop - 1);
+    uint32_t biased = static_cast<uint32_t>(exponent);
+    if (rest > half || (rest == half && (mantissa & 1u))) ++mantissa;
+    if (mantissa >> kManBits) {
+      mantissa = 0;
+      ++biased;
+    }
+    if (biased >= (1u << kExpBits) - (kHasInf ? 1u : 0u)) return sign | max_normal_bits;
+    return sign | (biased << kManBits) | (mantissa & ((1u << kManBits) - 1u));
+  }
+  const int shift = 1 - exponent;
+  if (shift > kManBits + 1) return sign;  // underflow to a signed zero
+  const uint32_t whole = fraction | 0x800000u;
+  const int drop = (23 - kManBits) + shift;
+  uint32_t mantissa = whole >> drop;
+  const uint32_t rest = whole & ((1u << drop) - 1u), half = 1u << (drop - 1);
+  if (rest > half || (rest == half && (mantissa & 1u))) ++mantissa;  // may carry into the first normal
+  return sign | (mantissa & 0xffu);
+}
+
+__device__ __forceinline__ float e4m3_to_f32(uint32_t b) { return f8_to_f32<4, 3, 7, false>(b); }
+__device__ __forceinline__ float e5m2_to_f32(uint32_t b) { return f8_to_f32<5, 2, 15, true>(b); }
+__device__ __forceinline__ uint32_t f32_to_e4m3(float v) { return f32_to_f8<4, 3, 7, false>(v, 0x43e00000u, 0x7eu, 0x7fu); }
+
+// ---- one element: storage word -> f32 -> storage word -------------------------------------------------
+template <int kDtype> struct Element;  // bytes per element and the unsigned word that holds it
+template <> struct Element<HYLE_B200_F32> { using Word = uint32_t; };
+template <> struct Element<HYLE_B200_I32> { using Word = uint32_t; };
+template <> struct Element<HYLE_B200_BF16> { using Word = unsigned short; };
+template <> struct Element<HYLE_B200_F16> { using Word = unsigned short; };
+template <> struct Element<HYLE_B200_E4M3> { using Word = unsigned char; };
+template <> struct Element<HYLE_B200_E5M2> { using Word = unsigned char; };
+template <> struct Element<HYLE_B200_BOOL> { using Word = unsigned char; };
+
+template <int kSrc>
+__device__ __forceinline__ float decode(uint32_t word) {
+  if constexpr (kSrc == HYLE_B200_F32) return __uint_as_float(word);
+  if constexpr (kSrc == HYLE_B200_I32) return __int2float_rn(static_cast<int>(word));
+  if constexpr (kSrc == HYLE_B200_BF16) return bf16_to_f32(static_cast<unsigned short>(word));
+  if constexpr (kSrc == HYLE_B200_F16) {
+    // cvt.f32.f16 turns every NaN into the positive canonical one; the 8-bit encoders keep a NaN's sign
+    if ((word & 0x7fffu) > 0x7c00u) return __uint_as_float(((word & 0x8000u) << 16) | 0x7fc00000u);
+    return f16_to_f32(static_cast<unsigned short>(word));
+  }
+  if constexpr (kSrc == HYLE_B200_E4M3) return e4m3_to_f32(word);
+  if constexpr (kSrc == HYLE_B200_E5M2) return e5m2_to_f32(word);
+  return word != 0 ? 1.0f : 0.0f;  // bool
+}
+
+template <int kDst>
+__device__ __forceinline__ uint32_t encode(float value) {
+  if constexpr (kDst == HYLE_B200_F32) return __float_as_uint(value);
+  if constexpr (kDst == HYLE_B200_BF16) return f32_to_bf16(value);
+  if constexpr (kDst == HYLE_B200_F16) return f32_to_f16(value);
+  if constexpr (kDst == HYLE_B200_E4M3) return f32_to_e4m3(value);
+  // bool: the decoded value is exact for every source type, so "magnitude bits non-zero" is
+  // "not equal to zero" (NaN compares unequal; no flush-to-zero is in effect)
+  return value == 0.0f ? 0u : 1u;
+}
+
+template <int kSrc, int kDst>
+__device__ __forceinline__ uint32_t convert(uint32_t word) {
+  return encode<kDst>(decode<kSrc>(word));
+}
+
+// ---- eight elements per thread-step -----------------------------------------------------------------
+template <int kBytes> struct Pack;  // eight elements of kBytes each
+template <> struct Pack<1> { uint2 v; };
+template <> struct Pack<2> { uint4 v; };
+template <> struct Pack<4> { uint4 v[2]; };
+
+template <int kBytes>
+__device__ __forceinline__ Pack<kBytes> load_pack(const void *base, uint64_t index) {
+  Pack<kBytes> p;
+  if constexpr (kBytes == 1) p.v = ld_stream(static_cast<const uint2 *>(base) + index);
+  else if constexpr (kBytes == 2) p.v = ld_stream(static_cast<const uint4 *>(base) + index);
+  else {
+    p.v[0] = ld_stream(static_cast<const uint4 *>(base) + 2 * index);
+    p.v[1] = ld_stream(static_cast<const uint4 *>(base) + 2 * index + 1);
+  }
+  return p;
+}
+template <int kBytes>
+__device__ __forceinline__ void store_pack(void *base, uint64_t index, const Pack<kBytes> &p) {
+  if constexpr (kBytes == 1) st_stream(static_cast<uint2 *>(base) + index, p.v);
+  else if constexpr (kBytes == 2) st_stream(static_cast<uint4 *>(base) + index, p.v);
+  else {
+    st_stream(static_cast<uint4 *>(base) + 2 * index, p.v[0]);
+    st_stream(static_cast<uint4 *>(base) + 2 * index + 1, p.v[1]);
+  }
+}
+template <int kBytes>
+__device__ __forceinline__ void unpack(const Pack<kBytes> &p, uint32_t (&w)[8]) {
+  if constexpr (kBytes == 1) {
+#pragma unroll
+    for (int i = 0; i < 4; ++i) {
+      w[i] = (p.v.x >> (8 * i)) & 0xffu;
+      w[4 + i] = (p.v.y >> (8 * i)) & 0xffu;
+    }
+  } else if constexpr (kBytes == 2) {
+    const uint32_t q[4] = {p.v.x, p.v.y, p.v.z, p.v.w};
+#pragma unroll
+    for (int i = 0; i < 4; ++i) {
+      w[2 * i] = q[i] & 0xffffu;
+      w[2 * i + 1] = q[i] >> 16;
+    }
+  } else {
+    w[0] = p.v[0].x; w[1] = p.v[0].y; w[2] = p.v[0].z; w[3] = p.v[0].w;
+    w[4] = p.v[1].x; w[5] = p.v[1].y; w[6] = p.v[1].z; w[7] = p.v[1].w;
+  }
+}
+template <int kBytes>
+__device__ __forceinline__ Pack<kBytes> pack(const uint32_t (&w)[8]) {
+  Pack<kBytes> p;
+  if constexpr (kBytes == 1) {
+    p.v.x = w[0] | (w[1] << 8) | (w[2] << 16) | (w[3] << 24);
+    p.v.y = w[4] | (w[5] << 8) | (w[6] << 16) | (w[7] << 24);
+  } else if constexpr (kBytes == 2) {
+    p.v = make_uint4(w[0] | (w[1] << 16), w[2] | (w[3] << 16), w[4] | (w[5] << 16), w[6] | (w[7] << 16));
+  } else {
+    p.v[0] = make_uint4(w[0], w[1], w[2], w[3]);
+    p.v[1] = make_uint4(w[4], w[5], w[6], w[7]);
+  }
+  return p;
+}
+
+template <int kSrc, int kDst>
+__global__ void __launch_bounds__(kThreads)
+cast_kernel(const void *in, void *out, uint64_t packs) {
+  grid_dependency_sync();
+  constexpr int kIn = sizeof(typename Element<kSrc>::Word), kOut = sizeof(typename Element<kDst>::Word);
+  constexpr int kUnroll = kIn == 4 ? 2 : 4;  // bytes in flight per thread: 64 (4-byte source) to 32 (1-byte)
+  const uint64_t stride = static_cast<uint64_t>(gridDim.x) * kThreads;
+  uint64_t i = static_cast<uint64_t>(blockIdx.x) * kThreads + threadIdx.x;
+  for (; i + (kUnroll - 1) * stride < packs; i += kUnroll * stride) {
+    Pack<kIn> source[kUnroll];
+#pragma unroll
+    for (int k = 0; k < kUnroll; ++k) source[k] = load_pack<kIn>(in, i + k * stride);
+#pragma unroll
+    for (int k = 0; k < kUnroll; ++k) {
+      uint32_t w[8];
+      unpack<kIn>(source[k], w);
+#pragma unroll
+      for (int e = 0; e < 8; ++e) w[e] = convert<kSrc, kDst>(w[e]);
+      store_pack<kOut>(out, i + k * stride, pack<kOut>(w));
+    }
+  }
+  for (; i < packs; i += stride) {
+    uint32_t w[8];
+    unpack<kIn>(load_pack<kIn>(in, i), w);
+#pragma unroll
+    for (int e = 0; e < 8; ++e) w[e] = convert<kSrc, kDst>(w[e]);
+    store_pack<kOut>(out, i, pack<kOut>(w));
+  }
+}
+
+// Unaligned tensors and the tail behind the last whole pack.
+template <int kSrc, int kDst>
+__global__ void __launch_bounds__(kThreads)
+cast_scalar_kernel(const typename Element<kSrc>::Word *in, typename Element<kDst>::Word *out, uint64_t count) {
+  grid_dependency_sync();
+  const uint64_t stride = static_cast<uint64_t>(gridDim.x) * kThreads;
+  for (uint64_t i = static_cast<uint64_t>(blockIdx.x) * kThreads + threadIdx.x; i < count; i += stride)
+    out[i] = static_cast<typename Element<kDst>::Word>(convert<kSrc, kDst>(in[i]));
+}
+
+template <int kSrc, int kDst>
+int launch_cast(cudaStream_t stream, const void *in, void *out, uint64_t count) {
+  using In = typename Element<kSrc>::Word;
+  using Out = typename Element<kDst>::Word;
+  if (!aligned_to(in, sizeof(In)) || !aligned_to(out, sizeof(Out))) return HYLE_B200_INVALID_VALUE;
+  const uint64_t resident = static_cast<uint64_t>(sm_count()) * kCtasPerSm;
+  const bool vector_ok = aligned_to(in, 8 * sizeof(In) > 16 ? 16 : 8 * sizeof(In)) &&
+                         aligned_to(out, 8 * sizeof(Out) > 16 ? 16 : 8 * sizeof(Out));
+  const uint64_t packs = vector_ok ? count / 8 : 0;
+  if (packs != 0) {
+    const unsigned grid = clamp_grid((packs + kThreads * 4 - 1) / (kThreads * 4), resident);
+    const int status = launch(cast_kernel<kSrc, kDst>, dim3(grid), dim3(kThreads), 0, stream, in, out, packs);
+    if (status != HYLE_B200_OK) return status;
+  }
+  const uint64_t done = packs * 8;
+  if (done == count) return HYLE_B200_OK;
+  const unsigned grid = clamp_grid((count - done + kThreads - 1) / kThreads, resident);
+  return launch(cast_scalar_kernel<kSrc, kDst>, dim3(grid), dim3(kThreads), 0, stream, static_cast<const In *>(in) + done,
+                static_cast<Out *>(out) + done, count - done);
+}
+
+}  // namespace
+}  // namespace hb
+
+using namespace hb;
+
+extern "C" int hyle_b200_cast(hyle_b200_stream_t stream, int source_dtype, int destination_dtype, const void *in,
+                              void *out, uint64_t count) {
+  if (count == 0) return HYLE_B200_OK;
+  if (in == nullptr || out == nullptr) return HYLE_B200_INVALID_VALUE;
+  auto s = reinterpret_cast<cudaStream_t>(stream);
+#define HB_CAST(S, D) \
+  if (source_dtype == S && destination_dtype == D) return launch_cast<S, D>(s, in, out, count)
+  // the pairs of src/compute_provider_native/cast.cc:128-176
+  HB_CAST(HYLE_B200_F32, HYLE_B200_BF16);
+  HB_CAST(HYLE_B200_F32, HYLE_B200_F16);
+  HB_CAST(HYLE_B200_BF16, HYLE_B200_F32);
+  HB_CAST(HYLE_B200_F16, HYLE_B200_F32);
+  HB_CAST(HYLE_B200_BF16, HYLE_B200_F16);
+  HB_CAST(HYLE_B200_F16, HYLE_B200_BF16);
+  HB_CAST(HYLE_B200_I32, HYLE_B200_F32);
+  HB_CAST(HYLE_B200_F32, HYLE_B200_BOOL);
+  HB_CAST(HYLE_B200_BF16, HYLE_B200_BOOL);
+  HB_CAST(HYLE_B200_F16, HYLE_B200_BOOL);
+  HB_CAST(HYLE_B200_BOOL, HYLE_B200_F32);
+  HB_CAST(HYLE_B200_BOOL, HYLE_B200_BF16);
+  HB_CAST(HYLE_B200_BOOL, HYLE_B200_F16);
+  HB_CAST(HYLE_B200_F32, HYLE_B200_E4M3);
+  HB_CAST(HYLE_B200_BF16, HYLE_B200_E4M3);
+  HB_CAST(HYLE_B200_F16, HYLE_B200_E4M3);
+  HB_CAST(HYLE_B200_E4M3, HYLE_B200_F32);
+  HB_CAST(HYLE_B200_E4M3, HYLE_B200_BF16);
+  HB_CAST(HYLE_B200_E4M3, HYLE_B200_F16);
+  HB_CAST(HYLE_B200_E5M2, HYLE_B200_BF16);
+  HB_CAST(HYLE_B200_E5M2, HYLE_B200_E4M3);
+#undef HB_CAST
+  return HYLE_B200_NOT_SUPPORTED;
+}

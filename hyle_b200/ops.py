@@ -248,6 +248,22 @@ def softmax(x: torch.Tensor, log: bool = False, out: Optional[torch.Tensor] = No
     return out
 
 
+_CAST_TORCH = {abi.F32: torch.float32, abi.BF16: torch.bfloat16, abi.F16: torch.float16, abi.E4M3: torch.uint8,
+               abi.E5M2: torch.uint8, abi.BOOL: torch.uint8, abi.I32: torch.int32}
+
+
+def cast(x: torch.Tensor, source: int, destination: int) -> torch.Tensor:
+    """Cast between storage types (``abi.F32`` ... ``abi.I32``).  The 8-bit floating formats and bool
+    travel as uint8 tensors of their storage bytes."""
+    _device_tensor(x, "x")
+    if x.dtype != _CAST_TORCH[source]:
+        raise ValueError(f"source type {source} is carried by {_CAST_TORCH[source]}, got {x.dtype}")
+    out = torch.empty(x.shape, dtype=_CAST_TORCH[destination], device=x.device)
+    abi.check("hyle_b200_cast", abi.load().hyle_b200_cast(
+        _stream(), source, destination, x.data_ptr(), out.data_ptr(), x.numel()))
+    return out
+
+
 def cast_f32_to_bf16(x: torch.Tensor) -> torch.Tensor:
     _device_tensor(x, "x")
     if x.dtype != torch.float32:

@@ -34,7 +34,7 @@ inline constexpr ProviderRuntimeProperties kRuntime{.replay_class = ProviderRepl
                                                     .capture_compatible = true};
 
 enum class Entry : std::uint8_t {
-  kUnary, kBinary, kReduceRows, kRmsNorm, kLayerNorm, kSwiglu, kSoftmax, kCastF32ToBf16, kArgmax, kQ8Encode,
+  kUnary, kBinary, kReduceRows, kRmsNorm, kLayerNorm, kSwiglu, kSoftmax, kCast, kArgmax, kQ8Encode,
   kAddRmsNorm, kBiasRowSumMax, kLogitsReduce, kQ8Roundtrip
 };
 
@@ -43,6 +43,7 @@ struct Plan final {
   Entry entry{};
   int kind = 0;            // unary / binary / reduce / softmax kind in the C ABI's numbering
   int dtype = 0;           // hyle_b200_dtype of the data (or of the norm weight for the norms)
+  int to_dtype = 0;        // Cast: hyle_b200_dtype of the output
   std::uint64_t count = 0; // total elements of input 0
   std::uint64_t rows = 0;
   std::uint64_t cols = 0;
@@ -52,6 +53,28 @@ struct Plan final {
   bool has_weight = false;
   std::size_t workspace_bytes = 0;
 };
+
+// Storage types hyle_b200_cast knows.
+inline std::optional<int> cast_dtype(DataType type) noexcept {
+  switch (type) {
+    case DataType::kFloat32: return HYLE_B200_F32;
+    case DataType::kBFloat16: return HYLE_B200_BF16;
+    case DataType::kFloat16: return HYLE_B200_F16;
+    case DataType::kFloat8E4M3FN: return HYLE_B200_E4M3;
+    case DataType::kFloat8E5M2: return HYLE_B200_E5M2;
+    case DataType::kBool: return HYLE_B200_BOOL;
+    case DataType::kInt32: return HYLE_B200_I32;
+    default: return std::nullopt;
+  }
+}
+// The pairs of src/compute_provider_native/cast.cc:128-176 (and of hyle_b200_cast).
+inline bool cast_pair(int from, int to) noexcept {
+  const auto wide = [](int t) { return t == HYLE_B200_F32 || t == HYLE_B200_BF16 || t == HYLE_B200_F16; };
+  return (wide(from) && wide(to) && from != to) || (from == HYLE_B200_I32 && to == HYLE_B200_F32) ||
+         (wide(from) && (to == HYLE_B200_BOOL || to == HYLE_B200_E4M3)) ||
+         ((from == HYLE_B200_BOOL || from == HYLE_B200_E4M3) && wide(to)) ||
+         (from == HYLE_B200_E5M2 && (to == HYLE_B200_BF16 || to == HYLE_B200_E4M3));
+}
 
 inline std::optional<int> abi_dtype(DataType type) noexcept {
   switch (type) {
@@ -194,10 +217,14 @@ inline std::optional<Plan> match(const Operation &op, std::span<const TensorDesc
     return p;
   }
   if (const auto *cast = op.get_if<Cast>()) {
-    if (in.size() != 1 || out.size() != 1 || in[0].data_type() != DataType::kFloat32 ||
-        cast->output_type != DataType::kBFloat16 || elements(out[0]) != p.count)
+    const auto from = cast_dtype(in[0].data_type());
+    const auto to = cast_dtype(cast->output_type);
+    if (in.size() != 1 || out.size() != 1 || !from || !to || out[0].data_type() != cast->output_type ||
+        elements(out[0]) != p.count || !cast_pair(*from, *to))
       return std::nullopt;
-    p.entry = Entry::kCastF32ToBf16;
+    p.entry = Entry::kCast;
+    p.dtype = *from;
+    p.to_dtype = *to;
     return p;
   }
   if (const auto *top = op.get_if<TopK>()) {
@@ -276,8 +303,8 @@ inline int launch(const Plan &p, hyle_b200_stream_t stream, const void *const *i
     case Entry::kSoftmax:
       return hyle_b200_softmax_f32(stream, p.kind, static_cast<const float *>(in[0]), static_cast<float *>(out[0]),
                                    p.rows, p.cols, workspace, p.workspace_bytes);
-    case Entry::kCastF32ToBf16:
-      return hyle_b200_cast_f32_to_bf16(stream, static_cast<const float *>(in[0]), out[0], p.count);
+    case Entry::kCast:
+      return hyle_b200_cast(stream, p.dtype, p.to_dtype, in[0], out[0], p.count);
     case Entry::kArgmax:
       return hyle_b200_logits_reduce_f32(stream, static_cast<const float *>(in[0]), p.rows, p.cols, nullptr, nullptr,
                                          static_cast<std::int32_t *>(out[1]), static_cast<float *>(out[0]), nullptr, 0);

@@ -150,6 +150,13 @@ int main() {
     check(!taken(*context, Operation(Softmax{.scale = 0.5F}), in, out), "scaled Softmax not taken");
     const std::array cast_out{probs16};
     check(taken(*context, Operation(Cast{DataType::kBFloat16}), in, cast_out), "Cast{f32 -> bf16}");
+    const std::array fp8_out{dense(DataType::kFloat8E4M3FN, {16, 151936})};
+    check(taken(*context, Operation(Cast{DataType::kFloat8E4M3FN}), in, fp8_out), "Cast{f32 -> E4M3}");
+    const std::array half_in{probs16};
+    const std::array bool_out{dense(DataType::kBool, {16, 151936})};
+    check(taken(*context, Operation(Cast{DataType::kBool}), half_in, bool_out), "Cast{bf16 -> bool}");
+    const std::array e5m2_out{dense(DataType::kFloat8E5M2, {16, 151936})};
+    check(!taken(*context, Operation(Cast{DataType::kFloat8E5M2}), in, e5m2_out), "Cast{f32 -> E5M2} not taken (no such CPU pair)");
     const std::array top_out{values, indices};
     check(taken(*context, Operation(TopK{.count = 1}), in, top_out), "TopK{count=1} -> values f32, indices i32");
   }

@@ -42,7 +42,7 @@ extern "C" {
 /* Same object as cudaStream_t; spelled out so C callers need no CUDA header. */
 typedef struct CUstream_st *hyle_b200_stream_t;
 
-#define HYLE_B200_ABI_VERSION 5
+#define HYLE_B200_ABI_VERSION 6
 
 enum hyle_b200_result {
   HYLE_B200_OK = 0,
@@ -56,7 +56,12 @@ enum hyle_b200_result {
 enum hyle_b200_dtype {
   HYLE_B200_F32 = 0,
   HYLE_B200_BF16 = 1,
-  HYLE_B200_F16 = 2
+  HYLE_B200_F16 = 2,
+  /* the remaining types are accepted by hyle_b200_cast only */
+  HYLE_B200_E4M3 = 3, /* DataType::kFloat8E4M3FN: bias 7, no infinity, NaN 0x7F, largest normal 448 */
+  HYLE_B200_E5M2 = 4, /* DataType::kFloat8E5M2: bias 15, IEEE-like */
+  HYLE_B200_BOOL = 5, /* one byte, any non-zero value is true */
+  HYLE_B200_I32 = 6
 };
 
 /* hyle::compute::BinaryKind (include/hyle/compute/operation.h:75-82); numbered independently. */
@@ -243,6 +248,15 @@ HYLE_B200_API int hyle_b200_logits_reduce_f32(hyle_b200_stream_t stream, const f
 HYLE_B200_API int hyle_b200_softmax_f32(hyle_b200_stream_t stream, int kind, const float *in,
                                         float *out, uint64_t rows, uint64_t cols, void *workspace,
                                         uint64_t workspace_bytes);
+
+/* Cast{destination type} (include/hyle/compute/operation.h:289-295) for the pairs of the CPU route
+ * (src/compute_provider_native/cast.cc:128-176): f32/bf16/f16 among themselves, i32 -> f32,
+ * f32/bf16/f16 <-> bool, f32/bf16/f16 <-> E4M3, E5M2 -> bf16, E5M2 -> E4M3.  Bit-exact:
+ * round to nearest even; the 8-bit formats saturate finite overflow to their largest normal
+ * (include/hyle/simd/dtype.h:163-213); bool is "magnitude bits non-zero" (cast.cc:78-91).
+ * Other pairs return NOT_SUPPORTED. */
+HYLE_B200_API int hyle_b200_cast(hyle_b200_stream_t stream, int source_dtype, int destination_dtype,
+                                 const void *in, void *out, uint64_t count);
 
 /* Cast{f32 -> bf16}, round to nearest even (include/hyle/simd/dtype.h:114-121). */
 HYLE_B200_API int hyle_b200_cast_f32_to_bf16(hyle_b200_stream_t stream, const float *in,

@@ -19,6 +19,8 @@ REF_LIB = os.path.join(ORACLE_DIR, "_ref", "libhyle_ref_floor.so")
 
 F32, BF16, F16 = 0, 1, 2
 ADD, MULTIPLY, SUBTRACT, DIVIDE, NUMBER_MINIMUM, NUMBER_MAXIMUM = 0, 1, 2, 3, 4, 5  # Binary kinds
+E4M3, E5M2, BOOL, I32 = 3, 4, 5, 6  # storage types of Cast, after F32, BF16, F16
+CAST_WORD = {0: np.float32, 1: np.uint16, 2: np.uint16, 3: np.uint8, 4: np.uint8, 5: np.uint8, 6: np.int32}
 (ABS, NEG, EXP, LOG, SQRT, RSQRT, TANH, SIGMOID, RELU, GELU, GELU_TANH, SILU, SOFTPLUS) = range(13)  # Unary kinds
 SUM, MEAN, MINIMUM, MAXIMUM = 0, 1, 2, 3
 
@@ -60,6 +62,13 @@ class Oracle:
         L.hyle_oracle_f32_to_f16.argtypes = [_f]
         L.hyle_oracle_binary.argtypes = [_i, _i, _vp, _vp, _vp, _u64, _u64]
         L.hyle_oracle_unary.argtypes = [_i, _i, _vp, _vp, _u64]
+        L.hyle_oracle_cast.argtypes = [_i, _i, _vp, _vp, _u64]
+        L.hyle_oracle_cast.restype = _i
+        for name in ("e4m3", "e5m2"):
+            getattr(L, f"hyle_oracle_f32_to_{name}").argtypes = [_f]
+            getattr(L, f"hyle_oracle_f32_to_{name}").restype = ctypes.c_uint8
+            getattr(L, f"hyle_oracle_{name}_to_f32").argtypes = [ctypes.c_uint8]
+            getattr(L, f"hyle_oracle_{name}_to_f32").restype = _f
         L.hyle_oracle_layer_norm_bf16.argtypes = [_vp, _vp, _vp, _vp, _vp, _u64, _u64, _f]
         L.hyle_oracle_reduce_rows_f32.argtypes = [_i, _vp, _vp, _u64, _u64]
         L.hyle_oracle_row_sum_f64.argtypes = [_vp, _vp, _vp, _u64, _u64]
@@ -115,6 +124,14 @@ class Oracle:
         x = _c(x, np_dtype)
         out = np.empty_like(x)
         self.lib.hyle_oracle_unary(kind, dtype, _ptr(x), _ptr(out), x.size)
+        return out
+
+    def cast(self, src, dst, x):
+        """Cast between storage types; x and the result are arrays of the storage words."""
+        x = _c(x, CAST_WORD[src])
+        out = np.empty(x.shape, CAST_WORD[dst])
+        if self.lib.hyle_oracle_cast(src, dst, _ptr(x), _ptr(out), x.size) != 0:
+            raise ValueError(f"no Cast from {src} to {dst} on the CPU route")
         return out
 
     def reduce_rows(self, kind, x):
@@ -253,6 +270,11 @@ class RefFloor:
         L.hyle_ref_softmax_f32.argtypes = [_i, _vp, _vp, _u64, _u64]
         L.hyle_ref_argmax_f32.argtypes = [_vp, _vp, _vp, _u64, _u64]
         L.hyle_ref_activation_f32.argtypes = [_i, _vp, _vp, _u64]
+        for name in ("e4m3", "e5m2"):
+            getattr(L, f"hyle_ref_f32_to_{name}").argtypes = [_f]
+            getattr(L, f"hyle_ref_f32_to_{name}").restype = ctypes.c_uint8
+            getattr(L, f"hyle_ref_{name}_to_f32").argtypes = [ctypes.c_uint8]
+            getattr(L, f"hyle_ref_{name}_to_f32").restype = _f
         L.hyle_ref_layer_norm_bf16.argtypes = [_vp, _vp, _vp, _vp, _u64, _u64, _f]
         L.hyle_ref_activation_f32.restype = _i
 

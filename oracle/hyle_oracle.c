@@ -286,6 +286,118 @@ static inline float sigmoid_f32(float x) {
 }
 static inline float silu_f32(float x) { return x == -INFINITY ? 0.0f : x * sigmoid_f32(x); }
 
+/* ---- Cast --------------------------------------------------------------------------------------
+ * src/compute_provider_native/cast.cc:20-91 (element rules), :128-176 (supported pairs) and the 8-bit
+ * formats of include/hyle/simd/dtype.h:125-227: decode is exact; encode rounds to nearest even,
+ * saturates finite overflow to the largest normal, keeps infinity only where the format has one
+ * (E5M2), emits the canonical NaN with the input's sign, and underflows to a signed zero. */
+enum { DT_E4M3 = 3, DT_E5M2 = 4, DT_BOOL = 5, DT_I32 = 6 };
+
+static float f8_decode(uint8_t byte, int exp_bits, int man_bits, int bias, int has_inf) {
+  const uint32_t sign = (uint32_t)(byte >> 7), exponent = (byte >> man_bits) & ((1u << exp_bits) - 1u);
+  const uint32_t mantissa = byte & ((1u << man_bits) - 1u), max_exp = (1u << exp_bits) - 1u;
+  uint32_t bits;
+  if (exponent == max_exp && has_inf) bits = (sign << 31) | 0x7f800000u | (mantissa << (23 - man_bits));
+  else if (exponent == max_exp && mantissa == (1u << man_bits) - 1u) bits = (sign << 31) | 0x7fc00000u;
+  else if (exponent == 0) {
+    const float magnitude = ldexpf((float)mantissa, 1 - bias - man_bits);
+    return sign ? -magnitude : magnitude;
+  } else bits = (sign << 31) | ((exponent - (uint32_t)bias + 127u) << 23) | (mantissa << (23 - man_bits));
+  float out;
+  memcpy(&out, &bits, 4);
+  return out;
+}
+
+static uint8_t f8_encode(float value, int exp_bits, int man_bits, int bias, int has_inf, float max_normal,
+                         uint8_t max_normal_bits, uint8_t nan_bits) {
+  uint32_t u;
+  memcpy(&u, &value, 4);
+  const uint8_t sign = (uint8_t)((u >> 31) << 7);
+  const uint32_t magnitude = u & 0x7fffffffu;
+  if (magnitude > 0x7f800000u) return sign | nan_bits;
+  if (magnitude == 0x7f800000u)
+    return has_inf ? (uint8_t)(sign | (((1u << exp_bits) - 1u) << man_bits)) : (uint8_t)(sign | max_normal_bits);
+  if (fabsf(value) > max_normal) return sign | max_normal_bits;
+  const int exponent = (int)(magnitude >> 23) - 127 + bias;
+  const uint32_t fraction = magnitude & 0x7fffffu;
+  if (exponent >= 1) {
+    const int drop = 23 - man_bits;
+    uint32_t mantissa = fraction >> drop, biased = (uint32_t)exponent;
+    const uint32_t rest = fraction & ((1u << drop) - 1u), half = 1u << (drop - 1);
+    if (rest > half || (rest == half && (mantissa & 1u))) ++mantissa;
+    if (mantissa >> man_bits) {
+      mantissa = 0;
+      ++biased;
+    }
+    if ((int)biased >= (1 << exp_bits) - (has_inf ? 1 : 0)) return sign | max_normal_bits;
+    return (uint8_t)(sign | (biased << man_bits) | (mantissa & ((1u << man_bits) - 1u)));
+  }
+  const int shift = 1 - exponent;
+  if (shift > man_bits + 1) return sign;
+  const uint32_t whole = fraction | 0x800000u;
+  const int drop = (23 - man_bits) + shift;
+  uint32_t mantissa = whole >> drop;
+  const uint32_t rest = whole & ((1u << drop) - 1u), half = 1u << (drop - 1);
+  if (rest > half || (rest == half && (mantissa & 1u))) ++mantissa;
+  return (uint8_t)(sign | (mantissa & 0xffu));
+}
+
+ORACLE_API float hyle_oracle_e4m3_to_f32(uint8_t b) { return f8_decode(b, 4, 3, 7, 0); }
+ORACLE_API float hyle_oracle_e5m2_to_f32(uint8_t b) { return f8_decode(b, 5, 2, 15, 1); }
+ORACLE_API uint8_t hyle_oracle_f32_to_e4m3(float v) { return f8_encode(v, 4, 3, 7, 0, 448.0f, 0x7e, 0x7f); }
+ORACLE_API uint8_t hyle_oracle_f32_to_e5m2(float v) { return f8_encode(v, 5, 2, 15, 1, 57344.0f, 0x7b, 0x7e); }
+
+/* i32 -> f32, round to nearest even on the integer's bits (cast.cc:21-41). */
+static float i32_to_f32(int32_t value) {
+  const uint32_t raw = (uint32_t)value, sign = raw & 0x80000000u;
+  const uint32_t magnitude = value < 0 ? 0u - raw : raw;
+  if (magnitude == 0) return 0.0f;
+  uint32_t exponent = 31u - (uint32_t)__builtin_clz(magnitude), significand;
+  if (exponent <= 23) significand = magnitude << (23 - exponent);
+  else {
+    const uint32_t shift = exponent - 23, rest = magnitude & ((1u << shift) - 1u), half = 1u << (shift - 1);
+    significand = magnitude >> shift;
+    if (rest > half || (rest == half && (significand & 1u))) ++significand;
+    if (significand == (1u << 24)) {
+      significand >>= 1;
+      ++exponent;
+    }
+  }
+  const uint32_t bits = sign | ((exponent + 127u) << 23) | (significand & 0x7fffffu);
+  float out;
+  memcpy(&out, &bits, 4);
+  return out;
+}
+
+static size_t cast_width(int dtype) { return dtype == DT_F32 || dtype == DT_I32 ? 4 : (dtype == DT_BF16 || dtype == DT_F16 ? 2 : 1); }
+
+/* Returns 0, or 1 for a pair the CPU route does not have. */
+ORACLE_API int hyle_oracle_cast(int src, int dst, const void *in, void *out, uint64_t count) {
+  const int wide_src = src == DT_F32 || src == DT_BF16 || src == DT_F16, wide_dst = dst == DT_F32 || dst == DT_BF16 || dst == DT_F16;
+  const int ok = (wide_src && wide_dst && src != dst) || (src == DT_I32 && dst == DT_F32) || (wide_src && dst == DT_BOOL) ||
+                 (src == DT_BOOL && wide_dst) || (wide_src && dst == DT_E4M3) || (src == DT_E4M3 && wide_dst) ||
+                 (src == DT_E5M2 && (dst == DT_BF16 || dst == DT_E4M3));
+  if (!ok) return 1;
+  (void)cast_width;
+#pragma omp parallel for schedule(static)
+  for (uint64_t i = 0; i < count; ++i) {
+    float v;
+    if (src == DT_I32) v = i32_to_f32(((const int32_t *)in)[i]);
+    else if (src == DT_BOOL) v = ((const uint8_t *)in)[i] != 0 ? 1.0f : 0.0f;
+    else if (src == DT_E4M3) v = hyle_oracle_e4m3_to_f32(((const uint8_t *)in)[i]);
+    else if (src == DT_E5M2) v = hyle_oracle_e5m2_to_f32(((const uint8_t *)in)[i]);
+    else v = load_as_f32(in, i, src);
+    if (dst == DT_BOOL) {  /* truth of the STORAGE bits: anything but +-0 */
+      uint32_t bits;
+      if (src == DT_F32) memcpy(&bits, (const float *)in + i, 4), bits &= 0x7fffffffu;
+      else bits = ((const uint16_t *)in)[i] & 0x7fffu;
+      ((uint8_t *)out)[i] = bits != 0;
+    } else if (dst == DT_E4M3) ((uint8_t *)out)[i] = hyle_oracle_f32_to_e4m3(v);
+    else store_from_f32(out, i, dst, v);
+  }
+  return 0;
+}
+
 /* ---- Unary{kind} ------------------------------------------------------------------------------
  * src/compute_provider_native/elementwise.cc:30-55 (Neg, Exp, Log, Sqrt, Rsqrt = 1.0f / sqrt, Tanh,
  * Relu keeping NaN, Silu) and :84-100 (16-bit storage: f32 value, one rounding);

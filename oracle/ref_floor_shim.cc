@@ -5,7 +5,8 @@
 //   src/simd/math/activations.cc   swiglu_bf16_scalar, rms_norm_bf16_scalar, softmax_f32_scalar,
 //                                  log_softmax_f32_scalar, {sigmoid,gelu,gelu_tanh,silu,relu}_f32_scalar, layer_norm_bf16_scalar
 //   src/simd/sort/top_k.cc         top_k_f32
-//   include/hyle/simd/dtype.h      f32_to_bf16, bf16_to_f32, f32_to_f16, f16_to_f32
+//   include/hyle/simd/dtype.h      f32_to_bf16, bf16_to_f32, f32_to_f16, f16_to_f32, f32_to_f8e4m3, f8e4m3_to_f32,
+//                                  f32_to_f8e5m2, f8e5m2_to_f32
 // and only forwards row by row, so tests can pin oracle/hyle_oracle.c against the reference's code
 // and the benchmark can time the reference's code on the host cores.  Rows are split over threads
 // in contiguous ranges like the reference's parallel_for_ranges
@@ -37,6 +38,11 @@ REF_API uint16_t hyle_ref_f32_to_bf16(float v) { return simd::f32_to_bf16(v).bit
 REF_API float hyle_ref_bf16_to_f32(uint16_t v) { return simd::bf16_to_f32(simd::bfloat16_t::from_bits(v)); }
 REF_API uint16_t hyle_ref_f32_to_f16(float v) { return simd::f32_to_f16(v).bits; }
 REF_API float hyle_ref_f16_to_f32(uint16_t v) { return simd::f16_to_f32(simd::float16_t::from_bits(v)); }
+
+REF_API uint8_t hyle_ref_f32_to_e4m3(float v) { return simd::f32_to_f8e4m3(v).bits; }
+REF_API float hyle_ref_e4m3_to_f32(uint8_t v) { return simd::f8e4m3_to_f32(simd::float8_e4m3_t::from_bits(v)); }
+REF_API uint8_t hyle_ref_f32_to_e5m2(float v) { return simd::f32_to_f8e5m2(v).bits; }
+REF_API float hyle_ref_e5m2_to_f32(uint8_t v) { return simd::f8e5m2_to_f32(simd::float8_e5m2_t::from_bits(v)); }
 
 REF_API void hyle_ref_swiglu_bf16(const uint16_t *gate, const uint16_t *up, uint16_t *out, uint64_t rows,
                                   uint64_t cols, uint64_t gate_stride, uint64_t up_stride) {

@@ -85,6 +85,19 @@ def main():
         out[f"layer_y_{hidden}"] = ref.layer_norm(x, scale, bias, 1e-5)
         out[f"layer_y_plain_{hidden}"] = ref.layer_norm(x, None, None, 1e-5)
 
+    # The 8-bit floating formats: every code decoded, and a spread of values encoded.
+    with np.errstate(all="ignore"):
+        half = np.arange(0, 65536, 5, dtype=np.uint16).view(np.float16).astype(np.float32)
+    edge = np.array([448.0, 449.0, 464.0, 465.0, 480.0, 57344.0, 61440.0, 65536.0, 2.0 ** -9, 2.0 ** -10,
+                     1.5 * 2.0 ** -10, 2.0 ** -16, 2.0 ** -17, 3.0e38, -3.0e38, np.inf, -np.inf, np.nan], np.float32)
+    values = np.concatenate([half, edge])
+    out["fp8_values"] = values
+    for name in ("e4m3", "e5m2"):
+        encode = getattr(ref.lib, f"hyle_ref_f32_to_{name}")
+        decode = getattr(ref.lib, f"hyle_ref_{name}_to_f32")
+        out[f"fp8_{name}_codes"] = np.array([encode(float(v)) for v in values], np.uint8)
+        out[f"fp8_{name}_decoded"] = np.array([decode(c) for c in range(256)], np.float32)
+
     # Unary activations of the scalar floor (UnaryKind numbers): sigmoid 7, relu 8, gelu 9,
     # gelu_tanh 10, silu 11, on specials and a spread of ordinary values.
     special = np.array([0.0, -0.0, np.nan, np.inf, -np.inf, 1.0, -1.0, 20.0, -20.0, 88.0, -104.0, 1e-40, -1e-40,

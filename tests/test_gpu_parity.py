@@ -487,6 +487,62 @@ def ordered16(words):
     return np.where(w & 0x8000, -(w & 0x7FFF), w)
 
 
+CAST_PAIRS = [(abi.F32, abi.BF16), (abi.F32, abi.F16), (abi.BF16, abi.F32), (abi.F16, abi.F32), (abi.BF16, abi.F16),
+              (abi.F16, abi.BF16), (abi.I32, abi.F32), (abi.F32, abi.BOOL), (abi.BF16, abi.BOOL), (abi.F16, abi.BOOL),
+              (abi.BOOL, abi.F32), (abi.BOOL, abi.BF16), (abi.BOOL, abi.F16), (abi.F32, abi.E4M3), (abi.BF16, abi.E4M3),
+              (abi.F16, abi.E4M3), (abi.E4M3, abi.F32), (abi.E4M3, abi.BF16), (abi.E4M3, abi.F16), (abi.E5M2, abi.BF16),
+              (abi.E5M2, abi.E4M3)]
+
+
+@pytest.mark.parametrize("pair", CAST_PAIRS, ids=lambda p: f"{p[0]}to{p[1]}")
+def test_cast_pairs_bit_exact(oracle, pair):
+    source, destination = pair
+    rng = np.random.default_rng(source * 16 + destination)
+    with np.errstate(all="ignore"):
+        half = np.arange(65536, dtype=np.uint16).view(np.float16).astype(np.float32)   # every f16 value
+        wide = (rng.standard_normal(70003) * np.exp(rng.uniform(-40, 40, 70003))).astype(np.float32)
+        edge = np.array([0.0, -0.0, 448.0, 449.0, 464.0, 465.0, 480.0, 57344.0, 65504.0, 65520.0, 2.0 ** -9, 2.0 ** -10,
+                         2.0 ** -24, 2.0 ** -25, 1e-45, 3.4e38, -3.4e38, np.inf, -np.inf, np.nan], np.float32)
+        values = np.concatenate([half, wide, edge])
+        if source == abi.F32:
+            words = values
+        elif source == abi.BF16:
+            words = wl.f32_to_bf16(values)
+        elif source == abi.F16:
+            words = values.astype(np.float16).view(np.uint16)
+        elif source == abi.I32:
+            words = np.concatenate([rng.integers(-2 ** 31, 2 ** 31 - 1, 70001, dtype=np.int64).astype(np.int32),
+                                    np.array([0, 1, -1, 16777217, 16777219, -16777217, 2 ** 31 - 1, -2 ** 31], np.int32)])
+        else:  # the one-byte types: every byte value, many times, at an odd length
+            words = np.tile(np.arange(256, dtype=np.uint8), 300)[:70001]
+    want = oracle.cast(source, destination, words)
+    carrier = {abi.BF16: torch.bfloat16, abi.F16: torch.float16}
+    dev = to_dev(words)
+    if source in carrier:
+        dev = dev.view(carrier[source])
+    got = ops.cast(dev, source, destination)
+    got_words = got.view(torch.int16 if destination in carrier else got.dtype).cpu().numpy().view(want.dtype)
+    if destination in (abi.F32, abi.BF16, abi.F16):  # NaN payloads are not part of the contract, NaN-ness is
+        exp_mask, frac = {abi.F32: (0x7F800000, 0x7FFFFF), abi.BF16: (0x7F80, 0x7F), abi.F16: (0x7C00, 0x3FF)}[destination]
+        as_int = {abi.F32: np.uint32, abi.BF16: np.uint16, abi.F16: np.uint16}[destination]
+        w, g = want.view(as_int), got_words.view(as_int)
+        nan = ((w & exp_mask) == exp_mask) & ((w & frac) != 0)
+        assert np.array_equal(((g & exp_mask) == exp_mask) & ((g & frac) != 0), nan)
+        assert np.array_equal(g[~nan], w[~nan])
+    else:
+        assert np.array_equal(got_words, want)
+    # an unaligned slice takes the scalar kernel and agrees
+    tail = ops.cast(dev[3:1003], source, destination)
+    raw = {torch.float32: torch.int32, torch.bfloat16: torch.int16, torch.float16: torch.int16}.get(got.dtype, got.dtype)
+    assert torch.equal(tail.view(raw), got[3:1003].view(raw))  # compared as bits: NaN is not equal to itself
+
+
+def test_cast_rejects_other_pairs():
+    x = torch.zeros(16, device=DEV)
+    with pytest.raises(abi.KernelError):
+        ops.cast(x, abi.F32, abi.E5M2)
+
+
 def test_cast_f32_to_bf16(oracle):
     rng = np.random.default_rng(2)
     for count in [1, 7, 8, 4096, 100003]:

@@ -164,6 +164,64 @@ def test_binary_subtract_divide_and_number_extrema(oracle):
     assert np.array_equal(oracle.binary(ob.DIVIDE, ob.BF16, x16, r16), want)
 
 
+# ---- Cast ----------------------------------------------------------------------------------------------------------------------
+def _fp8_probe_values():
+    """Every f16 value (covers both 8-bit formats' ranges, ties and subnormals densely) plus wide f32 values."""
+    with np.errstate(all="ignore"):
+        half = np.arange(65536, dtype=np.uint16).view(np.float16).astype(np.float32)
+    rng = np.random.default_rng(23)
+    wide = (rng.standard_normal(4096) * np.exp(rng.uniform(-30, 30, 4096))).astype(np.float32)
+    edge = np.array([448.0, 449.0, 464.0, 465.0, 480.0, 57344.0, 61440.0, 65536.0, 2.0 ** -9, 2.0 ** -10, 1.5 * 2.0 ** -10,
+                     2.0 ** -16, 2.0 ** -17, 3.0e38, -3.0e38, np.inf, -np.inf, np.nan, -np.nan], np.float32)
+    return np.concatenate([half, wide, edge])
+
+
+def test_fp8_conversions_match_reference(oracle, ref_floor, golden):
+    values = _fp8_probe_values()
+    for name in ("e4m3", "e5m2"):
+        encode_o, encode_r = getattr(oracle.lib, f"hyle_oracle_f32_to_{name}"), getattr(ref_floor.lib, f"hyle_ref_f32_to_{name}")
+        decode_o, decode_r = getattr(oracle.lib, f"hyle_oracle_{name}_to_f32"), getattr(ref_floor.lib, f"hyle_ref_{name}_to_f32")
+        for v in values[::7]:
+            assert encode_o(float(v)) == encode_r(float(v)), (name, v)
+        for code in range(256):
+            a, b = decode_o(code), decode_r(code)
+            assert (np.isnan(a) and np.isnan(b)) or np.float32(a).view(np.uint32) == np.float32(b).view(np.uint32), (name, code)
+
+
+def test_fp8_conversions_match_golden(oracle, golden):
+    values = golden["fp8_values"]
+    for name in ("e4m3", "e5m2"):
+        encode = getattr(oracle.lib, f"hyle_oracle_f32_to_{name}")
+        assert [encode(float(v)) for v in values] == list(golden[f"fp8_{name}_codes"])
+        decode = getattr(oracle.lib, f"hyle_oracle_{name}_to_f32")
+        got = np.array([decode(c) for c in range(256)], np.float32)
+        want = golden[f"fp8_{name}_decoded"]
+        assert np.array_equal(np.isnan(got), np.isnan(want))
+        assert np.array_equal(bits(got)[~np.isnan(want)], bits(want)[~np.isnan(want)])
+
+
+def test_cast_rules(oracle):
+    # the largest normal saturates, the tie below it rounds to even, infinity saturates in E4M3
+    e4 = oracle.cast(ob.F32, ob.E4M3, np.array([448.0, 1e9, np.inf, -np.inf, 464.0, 2.0 ** -9, 2.0 ** -10, 1.5 * 2.0 ** -10, np.nan], np.float32))
+    # 2^-9 is the smallest subnormal; 2^-10 is the tie between it and zero and goes to the even one (zero)
+    assert list(e4[:8]) == [0x7E, 0x7E, 0x7E, 0xFE, 0x7E, 0x01, 0x00, 0x01] and e4[8] & 0x7F == 0x7F
+    # bool is truth of the storage bits; i32 rounds to nearest even
+    x = np.array([0.0, -0.0, 1e-45, np.nan, -3.0], np.float32)
+    assert list(oracle.cast(ob.F32, ob.BOOL, x)) == [0, 0, 1, 1, 1]
+    assert list(oracle.cast(ob.BOOL, ob.F32, np.array([0, 1, 7, 255], np.uint8))) == [0.0, 1.0, 1.0, 1.0]
+    ints = np.array([0, 1, -1, 16777217, 16777219, -16777217, 2147483647, -2147483648], np.int32)
+    assert np.array_equal(oracle.cast(ob.I32, ob.F32, ints), ints.astype(np.float32))
+    # wide pairs go through f32 with one rounding
+    h = np.arange(0, 65536, 3, dtype=np.uint16)
+    with np.errstate(all="ignore"):
+        want = wl.f32_to_bf16(h.view(np.float16).astype(np.float32))
+    got = oracle.cast(ob.F16, ob.BF16, h)
+    nan = (want & 0x7FFF) > 0x7F80
+    assert np.array_equal(got[~nan], want[~nan]) and np.all((got[nan] & 0x7FFF) > 0x7F80)
+    with pytest.raises(ValueError):
+        oracle.cast(ob.E5M2, ob.F32, np.zeros(4, np.uint8))  # not a pair of the CPU route
+
+
 def _unary_inputs():
     rng = np.random.default_rng(17)
     special = np.array([0.0, -0.0, np.nan, np.inf, -np.inf, 1.0, -1.0, 20.0, 20.5, -20.0, 88.0, 89.0, -104.0,
