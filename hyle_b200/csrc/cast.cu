@@ -236,6 +236,68 @@ int launch_cast(cudaStream_t stream, const void *in, void *out, uint64_t count) 
                 static_cast<Out *>(out) + done, count - done);
 }
 
+// ---- CacheEncode{float8(scale)}: value / scale -> E4M3, a non-finite value -> byte 0 and a status bit -------
+// (src/compute_provider_ggml/ggml_cpu_provider.cc:589-596).  One IEEE division per element.
+template <int kSrc>
+__device__ __forceinline__ uint32_t cache_code(uint32_t word, float scale, bool &invalid) {
+  const float value = decode<kSrc>(word);
+  if (!isfinite(value)) {
+    invalid = true;
+    return 0u;
+  }
+  return f32_to_e4m3(__fdiv_rn(value, scale));
+}
+
+template <int kSrc>
+__global__ void __launch_bounds__(kThreads)
+cache_encode_e4m3_kernel(const void *in, void *out, uint64_t packs, float scale, uint32_t *status_word) {
+  grid_dependency_sync();
+  constexpr int kIn = sizeof(typename Element<kSrc>::Word);
+  const uint64_t stride = static_cast<uint64_t>(gridDim.x) * kThreads;
+  bool invalid = false;
+  for (uint64_t i = static_cast<uint64_t>(blockIdx.x) * kThreads + threadIdx.x; i < packs; i += stride) {
+    uint32_t w[8];
+    unpack<kIn>(load_pack<kIn>(in, i), w);
+#pragma unroll
+    for (int e = 0; e < 8; ++e) w[e] = cache_code<kSrc>(w[e], scale, invalid);
+    store_pack<1>(out, i, pack<1>(w));
+  }
+  if (status_word != nullptr && __any_sync(kFullMask, invalid) && (threadIdx.x & 31) == 0)
+    atomicOr(status_word, HYLE_B200_STATUS_INVALID_FP8_INPUT);
+}
+
+template <int kSrc>
+__global__ void __launch_bounds__(kThreads)
+cache_encode_e4m3_scalar_kernel(const typename Element<kSrc>::Word *in, unsigned char *out, uint64_t count, float scale,
+                                uint32_t *status_word) {
+  grid_dependency_sync();
+  const uint64_t stride = static_cast<uint64_t>(gridDim.x) * kThreads;
+  bool invalid = false;
+  for (uint64_t i = static_cast<uint64_t>(blockIdx.x) * kThreads + threadIdx.x; i < count; i += stride)
+    out[i] = static_cast<unsigned char>(cache_code<kSrc>(in[i], scale, invalid));
+  if (status_word != nullptr && invalid) atomicOr(status_word, HYLE_B200_STATUS_INVALID_FP8_INPUT);
+}
+
+template <int kSrc>
+int launch_cache_encode(cudaStream_t stream, const void *in, void *out, uint64_t count, float scale, uint32_t *status_word) {
+  using In = typename Element<kSrc>::Word;
+  if (!aligned_to(in, sizeof(In))) return HYLE_B200_INVALID_VALUE;
+  const uint64_t resident = static_cast<uint64_t>(sm_count()) * kCtasPerSm;
+  const bool vector_ok = aligned_to(in, 16) && aligned_to(out, 8);
+  const uint64_t packs = vector_ok ? count / 8 : 0;
+  if (packs != 0) {
+    const unsigned grid = clamp_grid((packs + kThreads * 4 - 1) / (kThreads * 4), resident);
+    const int status = launch(cache_encode_e4m3_kernel<kSrc>, dim3(grid), dim3(kThreads), 0, stream, in, out, packs, scale,
+                              status_word);
+    if (status != HYLE_B200_OK) return status;
+  }
+  const uint64_t done = packs * 8;
+  if (done == count) return HYLE_B200_OK;
+  const unsigned grid = clamp_grid((count - done + kThreads - 1) / kThreads, resident);
+  return launch(cache_encode_e4m3_scalar_kernel<kSrc>, dim3(grid), dim3(kThreads), 0, stream,
+                static_cast<const In *>(in) + done, static_cast<unsigned char *>(out) + done, count - done, scale, status_word);
+}
+
 }  // namespace
 }  // namespace hb
 
@@ -272,4 +334,15 @@ extern "C" int hyle_b200_cast(hyle_b200_stream_t stream, int source_dtype, int d
   HB_CAST(HYLE_B200_E5M2, HYLE_B200_E4M3);
 #undef HB_CAST
   return HYLE_B200_NOT_SUPPORTED;
+}
+
+extern "C" int hyle_b200_fp8_e4m3_encode(hyle_b200_stream_t stream, int dtype, const void *in, uint64_t count,
+                                         float scale, void *out, uint32_t *status_word) {
+  if (count == 0) return HYLE_B200_OK;
+  if (in == nullptr || out == nullptr || !(scale > 0.0f) || !(scale < INFINITY)) return HYLE_B200_INVALID_VALUE;
+  auto s = reinterpret_cast<cudaStream_t>(stream);
+  if (dtype == HYLE_B200_F32) return launch_cache_encode<HYLE_B200_F32>(s, in, out, count, scale, status_word);
+  if (dtype == HYLE_B200_BF16) return launch_cache_encode<HYLE_B200_BF16>(s, in, out, count, scale, status_word);
+  if (dtype == HYLE_B200_F16) return launch_cache_encode<HYLE_B200_F16>(s, in, out, count, scale, status_word);
+  return HYLE_B200_INVALID_VALUE;
 }

@@ -264,6 +264,17 @@ def cast(x: torch.Tensor, source: int, destination: int) -> torch.Tensor:
     return out
 
 
+def fp8_e4m3_encode(x: torch.Tensor, scale: float, status: Optional[torch.Tensor] = None) -> torch.Tensor:
+    """CacheEncode{float8(scale)}: uint8 E4M3 codes of x / scale; a non-finite value gives 0 and a status bit."""
+    _device_tensor(x, "x")
+    if x.dtype not in _DTYPE:
+        raise ValueError("x must be f32 / bf16 / f16")
+    out = torch.empty(x.shape, dtype=torch.uint8, device=x.device)
+    abi.check("hyle_b200_fp8_e4m3_encode", abi.load().hyle_b200_fp8_e4m3_encode(
+        _stream(), _DTYPE[x.dtype], x.data_ptr(), x.numel(), scale, out.data_ptr(), _ptr(status)))
+    return out
+
+
 def cast_f32_to_bf16(x: torch.Tensor) -> torch.Tensor:
     _device_tensor(x, "x")
     if x.dtype != torch.float32:

@@ -34,7 +34,7 @@ inline constexpr ProviderRuntimeProperties kRuntime{.replay_class = ProviderRepl
                                                     .capture_compatible = true};
 
 enum class Entry : std::uint8_t {
-  kUnary, kBinary, kReduceRows, kRmsNorm, kLayerNorm, kSwiglu, kSoftmax, kCast, kArgmax, kQ8Encode,
+  kUnary, kBinary, kReduceRows, kRmsNorm, kLayerNorm, kSwiglu, kSoftmax, kCast, kArgmax, kQ8Encode, kFp8Encode,
   kAddRmsNorm, kBiasRowSumMax, kLogitsReduce, kQ8Roundtrip
 };
 
@@ -49,7 +49,7 @@ struct Plan final {
   std::uint64_t cols = 0;
   std::uint64_t rhs_period = 0;
   std::uint64_t gate_stride = 0, up_stride = 0, up_offset = 0;  // SwiGLU layouts, in elements
-  float epsilon = 0.0F;
+  float epsilon = 0.0F;    // norm epsilon, or the scale of CacheStorage::float8
   bool has_weight = false;
   std::size_t workspace_bytes = 0;
 };
@@ -238,8 +238,15 @@ inline std::optional<Plan> match(const Operation &op, std::span<const TensorDesc
     return p;
   }
   if (const auto encode = op.custom_as<model_ops::CacheEncode>()) {
-    if (in.size() != 1 || out.size() != 1 || !type || !(encode->storage == CacheStorage::q8_0().value()) ||
-        p.cols % 32 != 0 || out[0].data_type() != DataType::kUInt8)
+    if (in.size() != 1 || out.size() != 1 || !type) return std::nullopt;
+    if (encode->storage.data_type() == DataType::kFloat8E4M3FN) {  // CacheStorage::float8(scale)
+      if (out[0].data_type() != DataType::kFloat8E4M3FN || elements(out[0]) != p.count) return std::nullopt;
+      p.entry = Entry::kFp8Encode;
+      p.dtype = *type;
+      p.epsilon = encode->storage.scale();
+      return p;
+    }
+    if (!(encode->storage == CacheStorage::q8_0().value()) || p.cols % 32 != 0 || out[0].data_type() != DataType::kUInt8)
       return std::nullopt;
     p.entry = Entry::kQ8Encode;
     p.dtype = *type;
@@ -310,6 +317,8 @@ inline int launch(const Plan &p, hyle_b200_stream_t stream, const void *const *i
                                          static_cast<std::int32_t *>(out[1]), static_cast<float *>(out[0]), nullptr, 0);
     case Entry::kQ8Encode:
       return hyle_b200_q8_0_encode(stream, p.dtype, in[0], p.count, out[0], nullptr);
+    case Entry::kFp8Encode:
+      return hyle_b200_fp8_e4m3_encode(stream, p.dtype, in[0], p.count, p.epsilon, out[0], nullptr);
     case Entry::kAddRmsNorm:
       return hyle_b200_add_rms_norm_bf16(stream, in[0], in[1], in[2], p.dtype, out[0], out[1], p.rows, p.cols,
                                          p.epsilon);

@@ -192,6 +192,11 @@ int main() {
     check(encode.infer_output_descriptions(inw, carrier).ok() &&
               taken(*context, Operation::custom(encode), inw, carrier),
           "model_ops::CacheEncode{q8_0} bf16");
+    model_ops::CacheEncode encode8{CacheStorage::float8(0.25F).value()};
+    std::array<TensorDesc, 1> carrier8{};
+    check(encode8.infer_output_descriptions(inw, carrier8).ok() &&
+              taken(*context, Operation::custom(encode8), inw, carrier8),
+          "model_ops::CacheEncode{float8(0.25)} bf16");
   }
   std::printf("%d failure(s)\n", failures);
   return failures == 0 ? 0 : 1;

@@ -42,7 +42,7 @@ extern "C" {
 /* Same object as cudaStream_t; spelled out so C callers need no CUDA header. */
 typedef struct CUstream_st *hyle_b200_stream_t;
 
-#define HYLE_B200_ABI_VERSION 6
+#define HYLE_B200_ABI_VERSION 7
 
 enum hyle_b200_result {
   HYLE_B200_OK = 0,
@@ -115,7 +115,10 @@ enum hyle_b200_status_bits {
   HYLE_B200_STATUS_INVALID_Q8_INPUT = 1u,
   /* hyle_b200_q8_0_roundtrip_bf16_exchange: a peer's sum did not arrive within poll_limit polls;
    * *sum_squares_out is NaN. */
-  HYLE_B200_STATUS_EXCHANGE_TIMEOUT = 2u
+  HYLE_B200_STATUS_EXCHANGE_TIMEOUT = 2u,
+  /* hyle_b200_fp8_e4m3_encode met a non-finite value; that byte was written as 0
+   * (src/compute_provider_ggml/ggml_cpu_provider.cc:591-594). */
+  HYLE_B200_STATUS_INVALID_FP8_INPUT = 4u
 };
 
 HYLE_B200_API int hyle_b200_abi_version(void);
@@ -282,6 +285,15 @@ HYLE_B200_API int hyle_b200_q8_0_encode(hyle_b200_stream_t stream, int dtype, co
  * (src/compute_ops/low_precision.cc:269-297). */
 HYLE_B200_API int hyle_b200_q8_0_decode_bf16(hyle_b200_stream_t stream, const void *blocks,
                                              uint64_t count, void *out_bf16);
+
+/* model_ops::CacheEncode{CacheStorage::float8(scale)} (include/hyle/compute/model_ops.h:207-229,
+ * include/hyle/compute/low_precision.h:94), executor src/compute_provider_ggml/ggml_cpu_provider.cc:589-596:
+ *   out[i] = e4m3_satfinite_rne(in[i] / scale), one byte per value; a non-finite input writes 0 and
+ *   sets HYLE_B200_STATUS_INVALID_FP8_INPUT in *status_word (may be NULL).
+ * dtype = F32 / BF16 / F16 of the input; scale finite and positive. */
+HYLE_B200_API int hyle_b200_fp8_e4m3_encode(hyle_b200_stream_t stream, int dtype, const void *in,
+                                            uint64_t count, float scale, void *out,
+                                            uint32_t *status_word);
 
 /* Scratch for the two kernels below, for a tensor of `count` values: a header (ticket and tile
  * counters), per-CTA partial sums, and for the fused round trip one f64 per tile of 8192 values

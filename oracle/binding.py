@@ -64,6 +64,8 @@ class Oracle:
         L.hyle_oracle_unary.argtypes = [_i, _i, _vp, _vp, _u64]
         L.hyle_oracle_cast.argtypes = [_i, _i, _vp, _vp, _u64]
         L.hyle_oracle_cast.restype = _i
+        L.hyle_oracle_fp8_e4m3_encode.argtypes = [_i, _vp, _u64, _f, _vp]
+        L.hyle_oracle_fp8_e4m3_encode.restype = ctypes.c_uint32
         for name in ("e4m3", "e5m2"):
             getattr(L, f"hyle_oracle_f32_to_{name}").argtypes = [_f]
             getattr(L, f"hyle_oracle_f32_to_{name}").restype = ctypes.c_uint8
@@ -133,6 +135,12 @@ class Oracle:
         if self.lib.hyle_oracle_cast(src, dst, _ptr(x), _ptr(out), x.size) != 0:
             raise ValueError(f"no Cast from {src} to {dst} on the CPU route")
         return out
+
+    def fp8_e4m3_encode(self, dtype, x, scale):
+        x = _c(x, np.float32 if dtype == F32 else np.uint16)
+        out = np.empty(x.shape, np.uint8)
+        status = self.lib.hyle_oracle_fp8_e4m3_encode(dtype, _ptr(x), x.size, scale, _ptr(out))
+        return out, int(status)
 
     def reduce_rows(self, kind, x):
         x = _c(x, np.float32)

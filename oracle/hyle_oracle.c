@@ -398,6 +398,21 @@ ORACLE_API int hyle_oracle_cast(int src, int dst, const void *in, void *out, uin
   return 0;
 }
 
+/* CacheEncode{float8(scale)}: src/compute_provider_ggml/ggml_cpu_provider.cc:589-596.  Returns the
+ * status bit (4) if any input was not finite; such a value is stored as byte 0. */
+ORACLE_API uint32_t hyle_oracle_fp8_e4m3_encode(int dtype, const void *in, uint64_t count, float scale, uint8_t *out) {
+  uint32_t status = 0;
+#pragma omp parallel for schedule(static) reduction(| : status)
+  for (uint64_t i = 0; i < count; ++i) {
+    const float v = load_as_f32(in, i, dtype);
+    if (!isfinite(v)) {
+      out[i] = 0;
+      status |= 4u;
+    } else out[i] = hyle_oracle_f32_to_e4m3(v / scale);
+  }
+  return status;
+}
+
 /* ---- Unary{kind} ------------------------------------------------------------------------------
  * src/compute_provider_native/elementwise.cc:30-55 (Neg, Exp, Log, Sqrt, Rsqrt = 1.0f / sqrt, Tanh,
  * Relu keeping NaN, Silu) and :84-100 (16-bit storage: f32 value, one rounding);

@@ -537,6 +537,35 @@ def test_cast_pairs_bit_exact(oracle, pair):
     assert torch.equal(tail.view(raw), got[3:1003].view(raw))  # compared as bits: NaN is not equal to itself
 
 
+@pytest.mark.parametrize("dtype", [abi.F32, abi.BF16, abi.F16])
+def test_fp8_cache_encode(oracle, dtype):
+    rng = np.random.default_rng(40 + dtype)
+    x = (rng.standard_normal(100003) * np.exp(rng.uniform(-12, 8, 100003))).astype(np.float32)
+    x[:6] = [0.0, -0.0, 448.0 * 0.37, 1e9, -1e9, 2.0 ** -12]
+    if dtype == abi.F32:
+        words, dev = x, to_dev(x)
+    elif dtype == abi.BF16:
+        words = wl.f32_to_bf16(x); dev = to_dev_bf16(words)
+    else:
+        with np.errstate(all="ignore"):
+            words = x.astype(np.float16).view(np.uint16)
+        dev = to_dev(words.view(np.float16))
+    for scale in (1.0, 0.37, 3.0):
+        want, want_status = oracle.fp8_e4m3_encode({abi.F32: ob.F32, abi.BF16: ob.BF16, abi.F16: ob.F16}[dtype], words, scale)
+        status = torch.zeros(1, dtype=torch.int32, device=DEV)
+        got = ops.fp8_e4m3_encode(dev, scale, status)
+        assert np.array_equal(got.cpu().numpy(), want)
+        assert int(status.item()) == want_status
+        assert torch.equal(ops.fp8_e4m3_encode(dev[1:2001], scale), got[1:2001])      # unaligned: scalar kernel
+    if dtype == abi.F32:
+        bad = x.copy(); bad[7] = np.nan; bad[70001] = np.inf
+        status = torch.zeros(1, dtype=torch.int32, device=DEV)
+        got = ops.fp8_e4m3_encode(to_dev(bad), 1.0, status).cpu().numpy()
+        want, want_status = oracle.fp8_e4m3_encode(ob.F32, bad, 1.0)
+        assert np.array_equal(got, want) and got[7] == 0 and got[70001] == 0
+        assert int(status.item()) == abi.STATUS_INVALID_FP8_INPUT == want_status
+
+
 def test_cast_rejects_other_pairs():
     x = torch.zeros(16, device=DEV)
     with pytest.raises(abi.KernelError):

@@ -222,6 +222,19 @@ def test_cast_rules(oracle):
         oracle.cast(ob.E5M2, ob.F32, np.zeros(4, np.uint8))  # not a pair of the CPU route
 
 
+def test_fp8_cache_encode_rules(oracle, ref_floor):
+    """value / scale, then the reference's own E4M3 conversion; non-finite inputs give byte 0 and the status bit."""
+    rng = np.random.default_rng(31)
+    x = (rng.standard_normal(4096) * 30).astype(np.float32)
+    codes, status = oracle.fp8_e4m3_encode(ob.F32, x, 0.25)
+    assert status == 0
+    encode = ref_floor.lib.hyle_ref_f32_to_e4m3
+    assert list(codes[:512]) == [encode(float(np.float32(v) / np.float32(0.25))) for v in x[:512]]
+    x[5], x[9] = np.nan, -np.inf
+    codes, status = oracle.fp8_e4m3_encode(ob.F32, x, 0.25)
+    assert status == 4 and codes[5] == 0 and codes[9] == 0
+
+
 def _unary_inputs():
     rng = np.random.default_rng(17)
     special = np.array([0.0, -0.0, np.nan, np.inf, -np.inf, 1.0, -1.0, 20.0, 20.5, -20.0, 88.0, 89.0, -104.0,
