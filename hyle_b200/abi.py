@@ -29,9 +29,10 @@ STATIC_MAX_VALUES = 1 << 31
 STATUS_INVALID_Q8_INPUT = 1
 STATUS_EXCHANGE_TIMEOUT = 2
 STATUS_INVALID_FP8_INPUT = 4
+STATUS_INVALID_CATEGORICAL_ROW = 8
 EXCHANGE_MAX_RANKS, EXCHANGE_MAILBOX_BYTES, EXCHANGE_HANDLE_BYTES = 8, 256, 64
 
-ABI_VERSION = 7
+ABI_VERSION = 8
 
 _p = ctypes.c_void_p
 _u64 = ctypes.c_uint64
@@ -69,6 +70,8 @@ SIGNATURES = {
     "hyle_b200_exchange_open": (_i, [ctypes.c_char_p, ctypes.POINTER(_p)]),
     "hyle_b200_exchange_close": (_i, [_p]),
     "hyle_b200_exchange_destroy": (_i, [_p]),
+    "hyle_b200_random_bits": (_i, [_p, _p, _u64, _u32, _p]),
+    "hyle_b200_categorical": (_i, [_p, _i, _p, _p, _u64, _u64, _p, _p, _p]),
 }
 
 _library = None

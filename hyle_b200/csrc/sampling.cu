@@ -1,0 +1,243 @@
+// sampling_ops::RandomBits and sampling_ops::Categorical (include/hyle/compute/sampling_ops.h:21-68).
+//
+// RandomBits is a counter-based generator with bit equality across backends: word w of row r is lane
+// w % 4 of Philox-4x32-10 (Salmon et al., "Parallel random numbers: as easy as 1, 2, 3", 2011) with
+// key = identity[r][0..1] and counter = (w / 4 as 64 bits, identity[r][2], identity[r][3])
+// (src/compute_provider_native/sampling.cc:76-88).  Pure 32-bit integer work, one block of four
+// words per thread.
+//
+// Categorical draws one index per row of log-weights by inverting the cumulative distribution at
+//   u = ((x0 * 2^20 + (x1 >> 12)) + 0.5) * 2^-52,   (x0, x1, ..) = block 0 of the row's identity
+// (sampling.cc:157-161): the first index whose cumulative weight exp(x - max) exceeds total * u.
+// The operator's contract leaves the draw algorithm and the floating math to each backend ("selected
+// IDs need not match across backends"); what is fixed is the uniform above, that -inf has zero mass,
+// that a row with NaN, +inf or no finite value is rejected, and the optional output
+// log p = x[selected] - max - log(total).  Here: one CTA per row, three passes over the row (the
+// second and third hit L2: a 151 936-wide f32 row is 608 KB), weights and sums in f64 from the warp
+// up, and a fixed reduction / scan order, so a row's result does not depend on the other rows, the
+// grid, or the run.
+#include "common.cuh"
+
+#include <math_constants.h>
+
+namespace hb {
+namespace {
+
+// ---- Philox-4x32-10 ------------------------------------------------------------------------------
+struct Words {
+  uint32_t x0, x1, x2, x3;
+};
+
+__device__ __forceinline__ Words philox_block(const uint32_t *identity, uint64_t index) {
+  Words v{static_cast<uint32_t>(index), static_cast<uint32_t>(index >> 32), identity[2], identity[3]};
+  uint32_t key0 = identity[0], key1 = identity[1];
+#pragma unroll
+  for (int round = 0; round < 10; ++round) {
+    const uint32_t hi0 = __umulhi(0xd2511f53u, v.x0), lo0 = 0xd2511f53u * v.x0;
+    const uint32_t hi1 = __umulhi(0xcd9e8d57u, v.x2), lo1 = 0xcd9e8d57u * v.x2;
+    v = Words{hi1 ^ v.x1 ^ key0, lo1, hi0 ^ v.x3 ^ key1, lo0};
+    key0 += 0x9e3779b9u;
+    key1 += 0xbb67ae85u;
+  }
+  return v;
+}
+
+constexpr int kBitsThreads = 256;
+
+__global__ void __launch_bounds__(kBitsThreads)
+random_bits_kernel(const uint32_t *__restrict__ identities, uint32_t *out, uint64_t rows, uint32_t words) {
+  grid_dependency_sync();
+  const uint64_t blocks_per_row = (static_cast<uint64_t>(words) + 3) / 4;
+  const uint64_t total = rows * blocks_per_row;
+  const uint64_t stride = static_cast<uint64_t>(gridDim.x) * kBitsThreads;
+  for (uint64_t i = static_cast<uint64_t>(blockIdx.x) * kBitsThreads + threadIdx.x; i < total; i += stride) {
+    const uint64_t row = i / blocks_per_row, block = i - row * blocks_per_row;
+    const Words w = philox_block(identities + row * 4, block);
+    uint32_t *dst = out + row * words + block * 4;
+    const uint32_t left = words - static_cast<uint32_t>(block * 4);
+    if (left >= 4 && (reinterpret_cast<uintptr_t>(dst) & 15) == 0) {
+      *reinterpret_cast<uint4 *>(dst) = make_uint4(w.x0, w.x1, w.x2, w.x3);
+    } else {
+      dst[0] = w.x0;
+      if (left > 1) dst[1] = w.x1;
+      if (left > 2) dst[2] = w.x2;
+      if (left > 3) dst[3] = w.x3;
+    }
+  }
+}
+
+// ---- Categorical ---------------------------------------------------------------------------------
+constexpr int kDrawThreads = 1024;
+constexpr int kDrawWarps = kDrawThreads / 32;
+
+template <int kDtype>
+__device__ __forceinline__ float load_logit(const void *row, uint32_t i) {
+  if constexpr (kDtype == HYLE_B200_F32) return static_cast<const float *>(row)[i];
+  if constexpr (kDtype == HYLE_B200_BF16) return bf16_to_f32(static_cast<const unsigned short *>(row)[i]);
+  return f16_to_f32(static_cast<const unsigned short *>(row)[i]);
+}
+
+__device__ __forceinline__ double warp_inclusive_scan(double v, int lane) {
+#pragma unroll
+  for (int o = 1; o < 32; o <<= 1) {
+    const double up = __shfl_up_sync(kFullMask, v, o);
+    if (lane >= o) v += up;
+  }
+  return v;
+}
+
+// One CTA per row.  A warp owns a contiguous run of the row (coalesced loads, 32 elements per step),
+// so "the first index whose cumulative weight exceeds the threshold" is found by locating the warp
+// from the scanned warp totals and then walking that warp's run 32 elements at a time.
+template <int kDtype>
+__global__ void __launch_bounds__(kDrawThreads)
+categorical_kernel(const void *logits, const uint32_t *__restrict__ identities, int32_t *index_out, float *log_probability,
+                   uint64_t rows, uint32_t cols, uint32_t *status_word) {
+  grid_dependency_sync();
+  __shared__ float s_max[kDrawWarps];
+  __shared__ uint32_t s_bad[kDrawWarps];
+  __shared__ double s_sum[kDrawWarps];
+  __shared__ double s_before[kDrawWarps + 1];
+  __shared__ int32_t s_selected;
+  const int t = threadIdx.x, lane = t & 31, warp = t >> 5;
+  const uint32_t run = (cols + kDrawWarps - 1) / kDrawWarps;  // elements per warp
+  const uint32_t begin = min(warp * run, cols), end = min(begin + run, cols);
+  constexpr size_t kWidth = kDtype == HYLE_B200_F32 ? 4 : 2;
+
+  for (uint64_t row = blockIdx.x; row < rows; row += gridDim.x) {
+    const void *x = static_cast<const unsigned char *>(logits) + row * cols * kWidth;
+    // pass 1: maximum; NaN or +inf anywhere makes the row invalid
+    float maximum = -CUDART_INF_F;
+    uint32_t bad = 0;
+    for (uint32_t i = begin + lane; i < end; i += 32) {
+      const float v = load_logit<kDtype>(x, i);
+      bad |= (v != v || v == CUDART_INF_F) ? 1u : 0u;
+      maximum = fmaxf(maximum, v);
+    }
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) maximum = fmaxf(maximum, __shfl_xor_sync(kFullMask, maximum, o));
+    bad = __any_sync(kFullMask, bad != 0) ? 1u : 0u;
+    if (lane == 0) {
+      s_max[warp] = maximum;
+      s_bad[warp] = bad;
+    }
+    __syncthreads();
+    maximum = s_max[0];
+    bad = s_bad[0];
+#pragma unroll
+    for (int w = 1; w < kDrawWarps; ++w) {
+      maximum = fmaxf(maximum, s_max[w]);
+      bad |= s_bad[w];
+    }
+    if (bad != 0 || !(maximum > -CUDART_INF_F)) {  // CTA-uniform: reject the row
+      if (t == 0) {
+        index_out[row] = -1;
+        if (log_probability != nullptr) log_probability[row] = CUDART_NAN_F;
+        if (status_word != nullptr) atomicOr(status_word, HYLE_B200_STATUS_INVALID_CATEGORICAL_ROW);
+      }
+      __syncthreads();
+      continue;
+    }
+    // pass 2: the warp's total of exp(x - max) (f32 weights, f64 sums), built as the last value of the
+    // same 32-wide inclusive scan chain that pass 3 walks, so the two agree to the last bit
+    double carried = 0.0;
+    for (uint32_t base = begin; base < end; base += 32) {
+      const uint32_t i = base + lane;
+      const double weight = i < end ? static_cast<double>(expf(load_logit<kDtype>(x, i) - maximum)) : 0.0;
+      carried = __shfl_sync(kFullMask, carried + warp_inclusive_scan(weight, lane), 31);
+    }
+    if (lane == 0) s_sum[warp] = carried;
+    __syncthreads();
+    if (t == 0) {
+      double running = 0.0;
+      for (int w = 0; w < kDrawWarps; ++w) {
+        s_before[w] = running;
+        running += s_sum[w];
+      }
+      s_before[kDrawWarps] = running;
+      s_selected = -1;
+    }
+    __syncthreads();
+    const double total = s_before[kDrawWarps];
+    const Words random = philox_block(identities + row * 4, 0);
+    const double uniform =
+        (static_cast<double>(random.x0) * 1048576.0 + static_cast<double>(random.x1 >> 12) + 0.5) * 2.220446049250313e-16;
+    const double threshold = total * uniform;
+    // pass 3: the warp whose span of the cumulative sum holds the threshold walks its run
+    const bool mine = s_before[warp] <= threshold && (warp == kDrawWarps - 1 || threshold < s_before[warp + 1]) && begin < end;
+    if (mine) {
+      const double before = s_before[warp];
+      double local = 0.0;  // the scan chain of pass 2, replayed
+      int32_t found = -1;
+      for (uint32_t base = begin; base < end && found < 0; base += 32) {
+        const uint32_t i = base + lane;
+        const double weight = i < end ? static_cast<double>(expf(load_logit<kDtype>(x, i) - maximum)) : 0.0;
+        const double inclusive = local + warp_inclusive_scan(weight, lane);
+        const unsigned crossed = __ballot_sync(kFullMask, i < end && before + inclusive > threshold);
+        if (crossed != 0) found = static_cast<int32_t>(base + __ffs(crossed) - 1);
+        local = __shfl_sync(kFullMask, inclusive, 31);
+      }
+      if (lane == 0) s_selected = found;
+    }
+    __syncthreads();
+    int32_t selected = s_selected;
+    if (selected < 0) {
+      // rounding left the threshold at or above the last cumulative value: take the last element of
+      // positive mass, never a masked tail (src/compute_provider_native/sampling.cc:171-176)
+      __shared__ int32_t s_last;
+      if (t == 0) s_last = -1;
+      __syncthreads();
+      int32_t last = -1;
+      for (uint32_t i = t; i < cols; i += kDrawThreads)
+        if (load_logit<kDtype>(x, i) == maximum) last = static_cast<int32_t>(i);
+      if (last >= 0) atomicMax(&s_last, last);
+      __syncthreads();
+      selected = s_last;
+    }
+    if (t == 0) {
+      index_out[row] = selected;
+      if (log_probability != nullptr)
+        log_probability[row] = static_cast<float>(static_cast<double>(load_logit<kDtype>(x, static_cast<uint32_t>(selected))) -
+                                                  static_cast<double>(maximum) - log(total));
+    }
+    __syncthreads();  // shared scratch is reused by the next row
+  }
+}
+
+}  // namespace
+}  // namespace hb
+
+using namespace hb;
+
+extern "C" int hyle_b200_random_bits(hyle_b200_stream_t stream, const uint32_t *identities, uint64_t rows,
+                                     uint32_t word_count, uint32_t *out) {
+  if (rows == 0 || word_count == 0) return HYLE_B200_OK;
+  if (identities == nullptr || out == nullptr || word_count > 0x7fffffffu || !aligned_to(identities, 4) ||
+      !aligned_to(out, 4))
+    return HYLE_B200_INVALID_VALUE;
+  const uint64_t blocks = rows * ((static_cast<uint64_t>(word_count) + 3) / 4);
+  const unsigned grid = clamp_grid((blocks + kBitsThreads - 1) / kBitsThreads, static_cast<uint64_t>(sm_count()) * 8);
+  return launch(random_bits_kernel, dim3(grid), dim3(kBitsThreads), 0, reinterpret_cast<cudaStream_t>(stream), identities,
+                out, rows, word_count);
+}
+
+extern "C" int hyle_b200_categorical(hyle_b200_stream_t stream, int dtype, const void *log_weights,
+                                     const uint32_t *identities, uint64_t rows, uint64_t cols, int32_t *index_out,
+                                     float *log_probability_out, uint32_t *status_word) {
+  if (rows == 0) return HYLE_B200_OK;
+  if (log_weights == nullptr || identities == nullptr || index_out == nullptr || cols == 0 || cols > 0x7fffffffull)
+    return HYLE_B200_INVALID_VALUE;
+  auto s = reinterpret_cast<cudaStream_t>(stream);
+  const unsigned grid = clamp_grid(rows, static_cast<uint64_t>(sm_count()) * 2);
+  const uint32_t width = static_cast<uint32_t>(cols);
+  if (dtype == HYLE_B200_F32)
+    return launch(categorical_kernel<HYLE_B200_F32>, dim3(grid), dim3(kDrawThreads), 0, s, log_weights, identities, index_out,
+                  log_probability_out, rows, width, status_word);
+  if (dtype == HYLE_B200_BF16)
+    return launch(categorical_kernel<HYLE_B200_BF16>, dim3(grid), dim3(kDrawThreads), 0, s, log_weights, identities, index_out,
+                  log_probability_out, rows, width, status_word);
+  if (dtype == HYLE_B200_F16)
+    return launch(categorical_kernel<HYLE_B200_F16>, dim3(grid), dim3(kDrawThreads), 0, s, log_weights, identities, index_out,
+                  log_probability_out, rows, width, status_word);
+  return HYLE_B200_INVALID_VALUE;
+}

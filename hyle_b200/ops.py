@@ -372,3 +372,31 @@ def q8_0_roundtrip_static(x: torch.Tensor, blocks: Optional[torch.Tensor] = None
         _stream(), x.data_ptr(), x.numel(), blocks.data_ptr(), decoded.data_ptr(), sum_out.data_ptr(),
         _ptr(status)))
     return blocks, decoded, sum_out
+
+
+def random_bits(identities: torch.Tensor, word_count: int) -> torch.Tensor:
+    """sampling_ops::RandomBits: u32 identities [rows, 4] (carried as int32) -> counter-generator words [rows, word_count]."""
+    _device_tensor(identities, "identities")
+    if identities.dtype != torch.int32 or identities.dim() != 2 or identities.shape[1] != 4:
+        raise ValueError("identities must be int32 [rows, 4] holding the u32 words")
+    out = torch.empty(identities.shape[0], word_count, dtype=torch.int32, device=identities.device)
+    abi.check("hyle_b200_random_bits", abi.load().hyle_b200_random_bits(
+        _stream(), identities.data_ptr(), identities.shape[0], word_count, out.data_ptr()))
+    return out
+
+
+def categorical(log_weights: torch.Tensor, identities: torch.Tensor, want_log_probability: bool = True,
+                status: Optional[torch.Tensor] = None):
+    """sampling_ops::Categorical: one index per row (i32; -1 for a rejected row) and optionally its log-probability."""
+    _device_tensor(log_weights, "log_weights"), _device_tensor(identities, "identities")
+    if log_weights.dtype not in _DTYPE or log_weights.dim() != 2:
+        raise ValueError("log_weights must be f32 / bf16 / f16 [rows, cols]")
+    rows, cols = log_weights.shape
+    if identities.dtype != torch.int32 or tuple(identities.shape) != (rows, 4):
+        raise ValueError("identities must be int32 [rows, 4] holding the u32 words")
+    index = torch.empty(rows, dtype=torch.int32, device=log_weights.device)
+    logp = torch.empty(rows, dtype=torch.float32, device=log_weights.device) if want_log_probability else None
+    abi.check("hyle_b200_categorical", abi.load().hyle_b200_categorical(
+        _stream(), _DTYPE[log_weights.dtype], log_weights.data_ptr(), identities.data_ptr(), rows, cols,
+        index.data_ptr(), _ptr(logp), _ptr(status)))
+    return index, logp

@@ -24,6 +24,8 @@
 #include <hyle/compute/model_ops.h>
 #include <hyle/compute/operation.h>
 
+#include <hyle/compute/sampling_ops.h>
+
 #include "b200_ops.h"
 #include "hyle_b200.h"
 
@@ -34,7 +36,7 @@ inline constexpr ProviderRuntimeProperties kRuntime{.replay_class = ProviderRepl
                                                     .capture_compatible = true};
 
 enum class Entry : std::uint8_t {
-  kUnary, kBinary, kReduceRows, kRmsNorm, kLayerNorm, kSwiglu, kSoftmax, kCast, kArgmax, kQ8Encode, kFp8Encode,
+  kUnary, kBinary, kReduceRows, kRmsNorm, kLayerNorm, kSwiglu, kSoftmax, kCast, kArgmax, kQ8Encode, kFp8Encode, kRandomBits, kCategorical,
   kAddRmsNorm, kBiasRowSumMax, kLogitsReduce, kQ8Roundtrip
 };
 
@@ -252,6 +254,27 @@ inline std::optional<Plan> match(const Operation &op, std::span<const TensorDesc
     p.dtype = *type;
     return p;
   }
+  if (const auto bits = op.custom_as<sampling_ops::RandomBits>()) {
+    // identities u32[rows, 4] -> words u32[rows, word_count]
+    if (in.size() != 1 || out.size() != 1 || in[0].data_type() != DataType::kUInt32 || in[0].rank() != 2 ||
+        in[0].dimensions()[1] != 4 || out[0].data_type() != DataType::kUInt32)
+      return std::nullopt;
+    p.entry = Entry::kRandomBits;
+    p.rows = static_cast<std::uint64_t>(in[0].dimensions()[0]);
+    p.cols = bits->word_count;
+    return p;
+  }
+  if (const auto draw = op.custom_as<sampling_ops::Categorical>()) {
+    // (log-weights [rows, cols], identities u32[rows, 4]) -> indices i32[rows] (, log p f32[rows])
+    if (in.size() != 2 || out.empty() || out.size() > 2 || !type || in[0].rank() != 2 ||
+        in[1].data_type() != DataType::kUInt32 || out[0].data_type() != DataType::kInt32 ||
+        (out.size() == 2) != draw->return_log_probability)
+      return std::nullopt;
+    p.entry = Entry::kCategorical;
+    p.dtype = *type;
+    p.has_weight = draw->return_log_probability;
+    return p;
+  }
   if (const auto fused = op.custom_as<FusedAddRmsNorm>()) {
     const auto weight = in.size() == 3 ? abi_dtype(in[2].data_type()) : std::nullopt;
     if (in.size() != 3 || out.size() != 2 || in[0].data_type() != DataType::kBFloat16 || in[1] != in[0] ||
@@ -319,6 +342,13 @@ inline int launch(const Plan &p, hyle_b200_stream_t stream, const void *const *i
       return hyle_b200_q8_0_encode(stream, p.dtype, in[0], p.count, out[0], nullptr);
     case Entry::kFp8Encode:
       return hyle_b200_fp8_e4m3_encode(stream, p.dtype, in[0], p.count, p.epsilon, out[0], nullptr);
+    case Entry::kRandomBits:
+      return hyle_b200_random_bits(stream, static_cast<const std::uint32_t *>(in[0]), p.rows,
+                                   static_cast<std::uint32_t>(p.cols), static_cast<std::uint32_t *>(out[0]));
+    case Entry::kCategorical:
+      return hyle_b200_categorical(stream, p.dtype, in[0], static_cast<const std::uint32_t *>(in[1]), p.rows, p.cols,
+                                   static_cast<std::int32_t *>(out[0]),
+                                   p.has_weight ? static_cast<float *>(out[1]) : nullptr, nullptr);
     case Entry::kAddRmsNorm:
       return hyle_b200_add_rms_norm_bf16(stream, in[0], in[1], in[2], p.dtype, out[0], out[1], p.rows, p.cols,
                                          p.epsilon);

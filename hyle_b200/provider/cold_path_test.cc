@@ -16,6 +16,8 @@
 #include <hyle/mem/buffer.h>
 #include <hyle/mem/resource.h>
 
+#include <hyle/compute/sampling_ops.h>
+
 #include "b200_provider.h"
 
 using namespace hyle::compute;
@@ -197,6 +199,22 @@ int main() {
     check(encode8.infer_output_descriptions(inw, carrier8).ok() &&
               taken(*context, Operation::custom(encode8), inw, carrier8),
           "model_ops::CacheEncode{float8(0.25)} bf16");
+  }
+  {  // sampling_ops: the counter generator and the categorical draw
+    const auto identities = dense(DataType::kUInt32, {16, 4});
+    const auto logits = dense(DataType::kFloat32, {16, 151936});
+    const std::array bits_in{identities};
+    std::array<TensorDesc, 1> bits_out{};
+    const sampling_ops::RandomBits bits{8};
+    check(bits.infer_output_descriptions(bits_in, bits_out).ok() &&
+              taken(*context, Operation::custom(bits), bits_in, bits_out),
+          "sampling_ops::RandomBits{8}");
+    const std::array draw_in{logits, identities};
+    std::array<TensorDesc, 2> draw_out{};
+    const sampling_ops::Categorical draw{true};
+    check(draw.infer_output_descriptions(draw_in, draw_out).ok() &&
+              taken(*context, Operation::custom(draw), draw_in, draw_out),
+          "sampling_ops::Categorical{log probability} f32");
   }
   std::printf("%d failure(s)\n", failures);
   return failures == 0 ? 0 : 1;

@@ -42,7 +42,7 @@ extern "C" {
 /* Same object as cudaStream_t; spelled out so C callers need no CUDA header. */
 typedef struct CUstream_st *hyle_b200_stream_t;
 
-#define HYLE_B200_ABI_VERSION 7
+#define HYLE_B200_ABI_VERSION 8
 
 enum hyle_b200_result {
   HYLE_B200_OK = 0,
@@ -118,7 +118,9 @@ enum hyle_b200_status_bits {
   HYLE_B200_STATUS_EXCHANGE_TIMEOUT = 2u,
   /* hyle_b200_fp8_e4m3_encode met a non-finite value; that byte was written as 0
    * (src/compute_provider_ggml/ggml_cpu_provider.cc:591-594). */
-  HYLE_B200_STATUS_INVALID_FP8_INPUT = 4u
+  HYLE_B200_STATUS_INVALID_FP8_INPUT = 4u,
+  /* hyle_b200_categorical met a row with NaN, +inf or no finite value; its index is -1. */
+  HYLE_B200_STATUS_INVALID_CATEGORICAL_ROW = 8u
 };
 
 HYLE_B200_API int hyle_b200_abi_version(void);
@@ -390,6 +392,31 @@ HYLE_B200_API int hyle_b200_exchange_create(void **mailbox, unsigned char *handl
 HYLE_B200_API int hyle_b200_exchange_open(const unsigned char *handle, void **peer_mailbox);
 HYLE_B200_API int hyle_b200_exchange_close(void *peer_mailbox);
 HYLE_B200_API int hyle_b200_exchange_destroy(void *mailbox);
+
+/* ---------------------------------------------------------------------------------------------
+ * sampling_ops::RandomBits{word_count} (include/hyle/compute/sampling_ops.h:21-34), CPU route
+ * src/compute_provider_native/sampling.cc:76-88: out[r, w] = lane w % 4 of Philox-4x32-10 with key
+ * identities[r, 0..1] and counter (w / 4, identities[r, 2], identities[r, 3]).  identities is
+ * u32[rows, 4], out u32[rows, word_count].  Bit-exact on every backend.
+ */
+HYLE_B200_API int hyle_b200_random_bits(hyle_b200_stream_t stream, const uint32_t *identities,
+                                        uint64_t rows, uint32_t word_count, uint32_t *out);
+
+/* sampling_ops::Categorical{return_log_probability} (include/hyle/compute/sampling_ops.h:36-68),
+ * CPU route src/compute_provider_native/sampling.cc:112-181: one index per row of f32 / bf16 / f16
+ * log-weights [rows, cols], drawn by inverting the cumulative weights exp(x - max) at
+ * u = ((x0 * 2^20 + (x1 >> 12)) + 0.5) * 2^-52 with (x0, x1) from block 0 of the row's identity;
+ * -inf has zero mass; log_probability_out (may be NULL) = x[index] - max - log(total).
+ * The operator leaves the floating math to each backend (indices of borderline draws need not match
+ * another backend's); a row's result here depends only on that row and its identity.
+ * A row with NaN, +inf or no finite value gets index -1, NaN log-probability and
+ * HYLE_B200_STATUS_INVALID_CATEGORICAL_ROW in *status_word (may be NULL); the adapter turns that into
+ * the InvalidArgument completion the CPU route reports.
+ */
+HYLE_B200_API int hyle_b200_categorical(hyle_b200_stream_t stream, int dtype, const void *log_weights,
+                                        const uint32_t *identities, uint64_t rows, uint64_t cols,
+                                        int32_t *index_out, float *log_probability_out,
+                                        uint32_t *status_word);
 
 #ifdef __cplusplus
 }

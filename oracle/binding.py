@@ -64,6 +64,9 @@ class Oracle:
         L.hyle_oracle_unary.argtypes = [_i, _i, _vp, _vp, _u64]
         L.hyle_oracle_cast.argtypes = [_i, _i, _vp, _vp, _u64]
         L.hyle_oracle_cast.restype = _i
+        L.hyle_oracle_random_bits.argtypes = [_vp, _u64, ctypes.c_uint32, _vp]
+        L.hyle_oracle_categorical.argtypes = [_i, _vp, _vp, _u64, _u64, _vp, _vp, _vp]
+        L.hyle_oracle_categorical.restype = _u64
         L.hyle_oracle_fp8_e4m3_encode.argtypes = [_i, _vp, _u64, _f, _vp]
         L.hyle_oracle_fp8_e4m3_encode.restype = ctypes.c_uint32
         for name in ("e4m3", "e5m2"):
@@ -141,6 +144,22 @@ class Oracle:
         out = np.empty(x.shape, np.uint8)
         status = self.lib.hyle_oracle_fp8_e4m3_encode(dtype, _ptr(x), x.size, scale, _ptr(out))
         return out, int(status)
+
+    def random_bits(self, identities, words):
+        identities = _c(identities, np.uint32)
+        rows = identities.shape[0]
+        out = np.empty((rows, words), np.uint32)
+        self.lib.hyle_oracle_random_bits(_ptr(identities), rows, words, _ptr(out))
+        return out
+
+    def categorical(self, dtype, logits, identities):
+        """(index i32[rows], log p f32[rows], uniform f64[rows], invalid rows)"""
+        logits = _c(logits, np.float32 if dtype == F32 else np.uint16)
+        identities = _c(identities, np.uint32)
+        rows, cols = logits.shape
+        index, logp, uniform = np.empty(rows, np.int32), np.empty(rows, np.float32), np.empty(rows, np.float64)
+        invalid = self.lib.hyle_oracle_categorical(dtype, _ptr(logits), _ptr(identities), rows, cols, _ptr(index), _ptr(logp), _ptr(uniform))
+        return index, logp, uniform, int(invalid)
 
     def reduce_rows(self, kind, x):
         x = _c(x, np.float32)
@@ -278,6 +297,8 @@ class RefFloor:
         L.hyle_ref_softmax_f32.argtypes = [_i, _vp, _vp, _u64, _u64]
         L.hyle_ref_argmax_f32.argtypes = [_vp, _vp, _vp, _u64, _u64]
         L.hyle_ref_activation_f32.argtypes = [_i, _vp, _vp, _u64]
+        L.hyle_ref_random_word.argtypes = [_vp, _u64]
+        L.hyle_ref_random_word.restype = ctypes.c_uint32
         for name in ("e4m3", "e5m2"):
             getattr(L, f"hyle_ref_f32_to_{name}").argtypes = [_f]
             getattr(L, f"hyle_ref_f32_to_{name}").restype = ctypes.c_uint8

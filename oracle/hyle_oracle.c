@@ -413,6 +413,86 @@ ORACLE_API uint32_t hyle_oracle_fp8_e4m3_encode(int dtype, const void *in, uint6
   return status;
 }
 
+/* ---- sampling_ops::RandomBits / Categorical ---------------------------------------------------
+ * Philox-4x32-10 (Salmon, Moraes, Dror, Shaw 2011) keyed as the CPU route keys it
+ * (src/compute_provider_native/sampling.cc:76-88): key = identity[0..1], counter = (index low,
+ * index high, identity[2], identity[3]); word w of a row is lane w % 4 of block w / 4. */
+static void philox_block(const uint32_t *identity, uint64_t index, uint32_t out[4]) {
+  uint32_t x0 = (uint32_t)index, x1 = (uint32_t)(index >> 32), x2 = identity[2], x3 = identity[3];
+  uint32_t k0 = identity[0], k1 = identity[1];
+  for (int round = 0; round < 10; ++round) {
+    const uint64_t a = (uint64_t)0xd2511f53u * x0, b = (uint64_t)0xcd9e8d57u * x2;
+    const uint32_t n0 = (uint32_t)(b >> 32) ^ x1 ^ k0, n1 = (uint32_t)b, n2 = (uint32_t)(a >> 32) ^ x3 ^ k1, n3 = (uint32_t)a;
+    x0 = n0, x1 = n1, x2 = n2, x3 = n3;
+    k0 += 0x9e3779b9u;
+    k1 += 0xbb67ae85u;
+  }
+  out[0] = x0, out[1] = x1, out[2] = x2, out[3] = x3;
+}
+
+ORACLE_API void hyle_oracle_random_bits(const uint32_t *identities, uint64_t rows, uint32_t words, uint32_t *out) {
+#pragma omp parallel for schedule(static)
+  for (uint64_t r = 0; r < rows; ++r)
+    for (uint32_t w = 0; w < words; w += 4) {
+      uint32_t block[4];
+      philox_block(identities + r * 4, w / 4, block);
+      for (uint32_t lane = 0; lane < 4 && w + lane < words; ++lane) out[r * words + w + lane] = block[lane];
+    }
+}
+
+/* Categorical, src/compute_provider_native/sampling.cc:112-181: reject NaN / +inf / all -inf rows;
+ * weights exp(x - max) in f32, total and cumulative sums sequential in f64; the uniform is the
+ * 52-bit midpoint of the row's first Philox block; the first index whose cumulative weight exceeds
+ * total * uniform, else the last index holding the maximum; log p = x - max - log(total).
+ * Returns the number of invalid rows (their index is -1).  uniform_out (may be NULL) receives the
+ * uniforms so that tests can judge a draw made with another summation order. */
+ORACLE_API uint64_t hyle_oracle_categorical(int dtype, const void *logits, const uint32_t *identities, uint64_t rows,
+                                            uint64_t cols, int32_t *index, float *log_probability, double *uniform_out) {
+  uint64_t invalid = 0;
+#pragma omp parallel for schedule(static) reduction(+ : invalid)
+  for (uint64_t r = 0; r < rows; ++r) {
+    float maximum = -INFINITY;
+    int bad = 0;
+    for (uint64_t c = 0; c < cols; ++c) {
+      const float v = load_as_f32(logits, r * cols + c, dtype);
+      if (isnan(v) || v == INFINITY) bad = 1;
+      if (v > maximum) maximum = v;
+    }
+    uint32_t block[4];
+    philox_block(identities + r * 4, 0, block);
+    const double uniform = ((double)block[0] * 0x1p20 + (double)(block[1] >> 12) + .5) * 0x1p-52;
+    if (uniform_out) uniform_out[r] = uniform;
+    if (bad || !isfinite(maximum)) {
+      index[r] = -1;
+      if (log_probability) log_probability[r] = NAN;
+      ++invalid;
+      continue;
+    }
+    double total = 0;
+    for (uint64_t c = 0; c < cols; ++c) total += (double)expf(load_as_f32(logits, r * cols + c, dtype) - maximum);
+    const double threshold = total * uniform;
+    double cumulative = 0;
+    uint64_t selected = cols;
+    for (uint64_t c = 0; c < cols; ++c) {
+      cumulative += (double)expf(load_as_f32(logits, r * cols + c, dtype) - maximum);
+      if (cumulative > threshold) {
+        selected = c;
+        break;
+      }
+    }
+    if (selected == cols)
+      for (selected = cols; selected > 0; --selected)
+        if (load_as_f32(logits, r * cols + selected - 1, dtype) == maximum) {
+          --selected;
+          break;
+        }
+    index[r] = (int32_t)selected;
+    if (log_probability)
+      log_probability[r] = (float)((double)load_as_f32(logits, r * cols + selected, dtype) - (double)maximum - log(total));
+  }
+  return invalid;
+}
+
 /* ---- Unary{kind} ------------------------------------------------------------------------------
  * src/compute_provider_native/elementwise.cc:30-55 (Neg, Exp, Log, Sqrt, Rsqrt = 1.0f / sqrt, Tanh,
  * Relu keeping NaN, Silu) and :84-100 (16-bit storage: f32 value, one rounding);

@@ -5,6 +5,7 @@
 //   src/simd/math/activations.cc   swiglu_bf16_scalar, rms_norm_bf16_scalar, softmax_f32_scalar,
 //                                  log_softmax_f32_scalar, {sigmoid,gelu,gelu_tanh,silu,relu}_f32_scalar, layer_norm_bf16_scalar
 //   src/simd/sort/top_k.cc         top_k_f32
+//   third_party/random123_counter/philox.h   word (the counter generator behind RandomBits)
 //   include/hyle/simd/dtype.h      f32_to_bf16, bf16_to_f32, f32_to_f16, f16_to_f32, f32_to_f8e4m3, f8e4m3_to_f32,
 //                                  f32_to_f8e5m2, f8e5m2_to_f32
 // and only forwards row by row, so tests can pin oracle/hyle_oracle.c against the reference's code
@@ -17,6 +18,7 @@
 #include "hyle/simd/dtype.h"
 #include "hyle/simd/sort.h"
 #include "src/simd/math/kernels.h"
+#include "third_party/random123_counter/philox.h"
 
 #ifdef _OPENMP
 #include <omp.h>
@@ -43,6 +45,11 @@ REF_API uint8_t hyle_ref_f32_to_e4m3(float v) { return simd::f32_to_f8e4m3(v).bi
 REF_API float hyle_ref_e4m3_to_f32(uint8_t v) { return simd::f8e4m3_to_f32(simd::float8_e4m3_t::from_bits(v)); }
 REF_API uint8_t hyle_ref_f32_to_e5m2(float v) { return simd::f32_to_f8e5m2(v).bits; }
 REF_API float hyle_ref_e5m2_to_f32(uint8_t v) { return simd::f8e5m2_to_f32(simd::float8_e5m2_t::from_bits(v)); }
+
+// word `index` of the counter stream of one identity (third_party/random123_counter/philox.h)
+REF_API uint32_t hyle_ref_random_word(const uint32_t *identity, uint64_t index) {
+  return hyle::borrowed::random123_counter::word(identity, index);
+}
 
 REF_API void hyle_ref_swiglu_bf16(const uint16_t *gate, const uint16_t *up, uint16_t *out, uint64_t rows,
                                   uint64_t cols, uint64_t gate_stride, uint64_t up_stride) {

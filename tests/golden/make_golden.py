@@ -98,6 +98,16 @@ def main():
         out[f"fp8_{name}_codes"] = np.array([encode(float(v)) for v in values], np.uint8)
         out[f"fp8_{name}_decoded"] = np.array([decode(c) for c in range(256)], np.float32)
 
+    # The counter generator behind RandomBits: words 0..39 of a few identities.
+    identities = np.array([[0, 0, 0, 0], [1, 2, 3, 4], [0xFFFFFFFF] * 4, [0x243F6A88, 0x85A308D3, 0x13198A2E, 0x03707344],
+                           [7, 0, 0xDEADBEEF, 5]], dtype=np.uint32)
+    out["random_identities"] = identities
+    out["random_words"] = np.array([[ref.lib.hyle_ref_random_word(row.ctypes.data, w) for w in range(40)]
+                                    for row in np.ascontiguousarray(identities)], np.uint32)
+    high = 4 * ((1 << 32) + 5)  # a counter above 2^32: both counter words in use
+    out["random_words_high"] = np.array([ref.lib.hyle_ref_random_word(row.ctypes.data, high + 1)
+                                         for row in np.ascontiguousarray(identities)], np.uint32)
+
     # Unary activations of the scalar floor (UnaryKind numbers): sigmoid 7, relu 8, gelu 9,
     # gelu_tanh 10, silu 11, on specials and a spread of ordinary values.
     special = np.array([0.0, -0.0, np.nan, np.inf, -np.inf, 1.0, -1.0, 20.0, -20.0, 88.0, -104.0, 1e-40, -1e-40,

@@ -566,6 +566,75 @@ def test_fp8_cache_encode(oracle, dtype):
         assert int(status.item()) == abi.STATUS_INVALID_FP8_INPUT == want_status
 
 
+# ---- sampling --------------------------------------------------------------------------------------------------------------
+def _identities(rng, rows):
+    return rng.integers(0, 2 ** 32, (rows, 4), dtype=np.uint64).astype(np.uint32)
+
+
+@pytest.mark.parametrize("words", [1, 3, 4, 7, 64, 1001])
+def test_random_bits_bit_exact(oracle, golden, words):
+    rng = np.random.default_rng(words)
+    identities = np.concatenate([golden["random_identities"], _identities(rng, 700)])
+    got = ops.random_bits(to_dev(identities.view(np.int32)), words).cpu().numpy().view(np.uint32)
+    assert np.array_equal(got, oracle.random_bits(identities, words))
+    if words >= 4:
+        assert np.array_equal(got[:5, :min(words, 40)], golden["random_words"][:, :min(words, 40)])
+
+
+@pytest.mark.parametrize("dtype", [abi.F32, abi.BF16, abi.F16])
+@pytest.mark.parametrize("cols", [1, 5, 1000, 4099, 151936])
+def test_categorical_draws(oracle, dtype, cols):
+    """Indices agree with the CPU restatement except where the two summation orders put the threshold
+    on different sides of a cumulative boundary; every draw is checked against the cumulative
+    distribution itself, and log p against x - lse."""
+    rng = np.random.default_rng(cols + dtype)
+    rows = 48 if cols > 10000 else 300
+    x = (3.0 * rng.standard_normal((rows, cols))).astype(np.float32)
+    if cols >= 1000:
+        x[3, 10:] = -np.inf
+        x[4, :] = -np.inf; x[4, 777] = 0.0
+        x[5, : cols // 2] = -np.inf
+    identities = _identities(rng, rows)
+    if dtype == abi.F32:
+        words, dev, odt = x, to_dev(x), ob.F32
+    elif dtype == abi.BF16:
+        words = wl.f32_to_bf16(x); dev, odt = to_dev_bf16(words), ob.BF16
+        x = wl.bf16_to_f32(words)
+    else:
+        h = x.astype(np.float16); words = h.view(np.uint16); dev, odt = to_dev(h), ob.F16
+        x = h.astype(np.float32)
+    status = torch.zeros(1, dtype=torch.int32, device=DEV)
+    index, logp = ops.categorical(dev, to_dev(identities.view(np.int32)), True, status)
+    index, logp = index.cpu().numpy(), logp.cpu().numpy()
+    want_index, want_logp, uniform, invalid = oracle.categorical(odt, words, identities)
+    assert invalid == 0 and int(status.item()) == 0
+    assert (index == want_index).mean() >= 0.99
+    w = np.exp((x - x.max(axis=1, keepdims=True)).astype(np.float32)).astype(np.float64)
+    c = np.cumsum(w, axis=1)
+    for r in range(rows):
+        t = c[r, -1] * uniform[r]
+        i = int(index[r])
+        assert 0 <= i < cols and w[r, i] > 0
+        assert c[r, i] > t * (1 - 1e-9) and (i == 0 or c[r, i - 1] <= t * (1 + 1e-9))
+        assert abs(logp[r] - (x[r, i] - x[r].max() - np.log(c[r, -1]))) < 2e-5
+    if cols >= 1000:
+        assert index[4] == 777 and 0 <= index[3] < 10 and index[5] >= cols // 2
+    # a row's draw does not depend on where the row sits or on the batch
+    perm = rng.permutation(rows)
+    index_p, _ = ops.categorical(dev[torch.from_numpy(perm).to(DEV)].contiguous(), to_dev(identities[perm].view(np.int32)), False)
+    assert np.array_equal(index_p.cpu().numpy(), index[perm])
+
+
+def test_categorical_rejects_invalid_rows():
+    x = torch.randn(4, 100, device=DEV)
+    x[0, 5] = float("nan"); x[1, 6] = float("inf"); x[2, :] = float("-inf")
+    identities = torch.arange(16, dtype=torch.int32, device=DEV).reshape(4, 4)
+    status = torch.zeros(1, dtype=torch.int32, device=DEV)
+    index, logp = ops.categorical(x, identities, True, status)
+    assert index[:3].tolist() == [-1, -1, -1] and int(index[3]) >= 0
+    assert bool(torch.isnan(logp[:3]).all()) and int(status.item()) == abi.STATUS_INVALID_CATEGORICAL_ROW
+
+
 def test_cast_rejects_other_pairs():
     x = torch.zeros(16, device=DEV)
     with pytest.raises(abi.KernelError):

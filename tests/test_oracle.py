@@ -235,6 +235,49 @@ def test_fp8_cache_encode_rules(oracle, ref_floor):
     assert status == 4 and codes[5] == 0 and codes[9] == 0
 
 
+# ---- sampling ----------------------------------------------------------------------------------------------------------------
+def test_random_bits_match_reference_generator(oracle, golden):
+    identities = golden["random_identities"]
+    assert np.array_equal(oracle.random_bits(identities, 40), golden["random_words"])
+    assert np.array_equal(oracle.random_bits(identities, 37), golden["random_words"][:, :37])   # ragged last block
+    from oracle.binding import RefFloor
+    if RefFloor.available():
+        ref = RefFloor()
+        rng = np.random.default_rng(3)
+        more = rng.integers(0, 2 ** 32, (16, 4), dtype=np.uint64).astype(np.uint32)
+        got = oracle.random_bits(more, 24)
+        want = np.array([[ref.lib.hyle_ref_random_word(row.ctypes.data, w) for w in range(24)]
+                         for row in np.ascontiguousarray(more)], np.uint32)
+        assert np.array_equal(got, want)
+
+
+def test_categorical_rules(oracle):
+    rng = np.random.default_rng(8)
+    rows, cols = 64, 1000
+    x = (3.0 * rng.standard_normal((rows, cols))).astype(np.float32)
+    x[3, 10:] = -np.inf                       # mass on the first ten entries only
+    x[4, :] = -np.inf; x[4, 777] = 0.0       # a single entry with mass
+    identities = rng.integers(0, 2 ** 32, (rows, 4), dtype=np.uint64).astype(np.uint32)
+    index, logp, uniform, invalid = oracle.categorical(ob.F32, x, identities)
+    assert invalid == 0 and index[4] == 777 and abs(logp[4]) < 1e-6 and 0 <= index[3] < 10
+    assert np.all((uniform > 0) & (uniform < 1))
+    # the draw inverts the cumulative distribution at the row's uniform
+    w = np.exp((x - x.max(axis=1, keepdims=True)).astype(np.float32)).astype(np.float64)
+    c = np.cumsum(w, axis=1)
+    for r in range(rows):
+        t = c[r, -1] * uniform[r]
+        assert c[r, index[r]] > t * (1 - 1e-12) and (index[r] == 0 or c[r, index[r] - 1] <= t * (1 + 1e-12))
+        assert abs(logp[r] - (x[r, index[r]] - x[r].max() - np.log(c[r, -1]))) < 1e-5
+    # the same identity and row give the same draw wherever the row sits
+    perm = rng.permutation(rows)
+    index_p, _, _, _ = oracle.categorical(ob.F32, x[perm], identities[perm])
+    assert np.array_equal(index_p, index[perm])
+    # rejected rows
+    bad = x[:4].copy(); bad[0, 5] = np.nan; bad[1, 6] = np.inf; bad[2, :] = -np.inf
+    index_b, _, _, invalid = oracle.categorical(ob.F32, bad, identities[:4])
+    assert invalid == 3 and list(index_b[:3]) == [-1, -1, -1] and index_b[3] >= 0
+
+
 def _unary_inputs():
     rng = np.random.default_rng(17)
     special = np.array([0.0, -0.0, np.nan, np.inf, -np.inf, 1.0, -1.0, 20.0, 20.5, -20.0, 88.0, 89.0, -104.0,
