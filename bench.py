@@ -284,6 +284,45 @@ def other_ops(torch, peak_gbs, only=None, iterations=40):
         report("binary_maximum_bf16", "4096x6144", 4096 * 6144, 3 * 4096 * 6144 * 2, ms, sets)
         del x16, y16
 
+    # LayerNorm, Cast, FP8 cache encode and the sampling operators
+    if wanted("norm_cast_sampling"):
+        sets = 8
+        x16 = [torch.randn(4096, 2048, device=dev).to(torch.bfloat16) for _ in range(sets)]
+        y16 = [torch.empty_like(x16[0]) for _ in range(sets)]
+        scale = (torch.rand(2048, device=dev) + 0.5).to(torch.bfloat16)
+        bias = torch.randn(2048, device=dev).to(torch.bfloat16)
+        ms = time_op(torch, lambda i: lib.hyle_b200_layer_norm_bf16(
+            stream, x16[i].data_ptr(), scale.data_ptr(), bias.data_ptr(), y16[i].data_ptr(), 4096, 2048, 1e-5), sets, iterations)
+        report("layer_norm_bf16", "4096x2048", 4096 * 2048, 2 * 4096 * 2048 * 2, ms, sets)
+        del x16, y16
+        x32 = [torch.randn(4096, 4096, device=dev) for _ in range(sets)]
+        codes = [torch.empty(4096, 4096, dtype=torch.uint8, device=dev) for _ in range(sets)]
+        ms = time_op(torch, lambda i: lib.hyle_b200_cast(
+            stream, abi.F32, abi.E4M3, x32[i].data_ptr(), codes[i].data_ptr(), 4096 * 4096), sets, iterations)
+        report("cast_f32_to_e4m3", "4096x4096", 4096 * 4096, 4096 * 4096 * 5, ms, sets)
+        ms = time_op(torch, lambda i: lib.hyle_b200_fp8_e4m3_encode(
+            stream, abi.F32, x32[i].data_ptr(), 4096 * 4096, 0.37, codes[i].data_ptr(), None), sets, iterations)
+        report("fp8_e4m3_encode_f32", "4096x4096", 4096 * 4096, 4096 * 4096 * 5, ms, sets)
+        ms = time_op(torch, lambda i: lib.hyle_b200_cast(
+            stream, abi.E4M3, abi.F32, codes[i].data_ptr(), x32[i].data_ptr(), 4096 * 4096), sets, iterations)
+        report("cast_e4m3_to_f32", "4096x4096", 4096 * 4096, 4096 * 4096 * 5, ms, sets)
+        del x32, codes
+        identities = torch.randint(-2 ** 31, 2 ** 31 - 1, (4096, 4), dtype=torch.int32, device=dev)
+        words = [torch.empty(4096, 4096, dtype=torch.int32, device=dev) for _ in range(sets)]
+        ms = time_op(torch, lambda i: lib.hyle_b200_random_bits(
+            stream, identities.data_ptr(), 4096, 4096, words[i].data_ptr()), sets, iterations)
+        report("random_bits", "4096x4096 words", 4096 * 4096, 4096 * 4096 * 4, ms, sets)
+        del words
+        rows, cols = 256, 151936
+        logits = [4.0 * torch.randn(rows, cols, device=dev) for _ in range(2)]
+        ids = torch.randint(-2 ** 31, 2 ** 31 - 1, (rows, 4), dtype=torch.int32, device=dev)
+        picked, logp = torch.empty(rows, dtype=torch.int32, device=dev), torch.empty(rows, device=dev)
+        ms = time_op(torch, lambda i: lib.hyle_b200_categorical(
+            stream, abi.F32, logits[i].data_ptr(), ids.data_ptr(), rows, cols, picked.data_ptr(), logp.data_ptr(), None),
+            2, max(1, iterations // 2))
+        report("categorical_f32", "256x151936", rows * cols, rows * cols * 4, ms, 2)
+        del logits
+
     # 4: f32 logits -> lse, softmax bf16, argmax, B = 256, vocabulary 151936
     if wanted("logits_reduce_f32"):
         sets = 4

@@ -13,9 +13,8 @@
 // IDs need not match across backends"); what is fixed is the uniform above, that -inf has zero mass,
 // that a row with NaN, +inf or no finite value is rejected, and the optional output
 // log p = x[selected] - max - log(total).  Here: one CTA per row, three passes over the row (the
-// second and third hit L2: a 151 936-wide f32 row is 608 KB), weights and sums in f64 from the warp
-// up, and a fixed reduction / scan order, so a row's result does not depend on the other rows, the
-// grid, or the run.
+// second and third hit L2: a 151 936-wide f32 row is 608 KB), f32 weights 2^((x - max) log2e) added
+// in f64, fixed reduction orders: a row's result does not depend on the other rows, the grid or the run.
 #include "common.cuh"
 
 #include <math_constants.h>
@@ -67,7 +66,7 @@ random_bits_kernel(const uint32_t *__restrict__ identities, uint32_t *out, uint6
 }
 
 // ---- Categorical ---------------------------------------------------------------------------------
-constexpr int kDrawThreads = 1024;
+constexpr int kDrawThreads = 512;  // two CTAs per SM: 296 rows in flight
 constexpr int kDrawWarps = kDrawThreads / 32;
 
 template <int kDtype>
@@ -86,11 +85,26 @@ __device__ __forceinline__ double warp_inclusive_scan(double v, int lane) {
   return v;
 }
 
-// One CTA per row.  A warp owns a contiguous run of the row (coalesced loads, 32 elements per step),
-// so "the first index whose cumulative weight exceeds the threshold" is found by locating the warp
-// from the scanned warp totals and then walking that warp's run 32 elements at a time.
+__device__ __forceinline__ float weight_of(float x, float neg_scaled_max) {
+  // exp(x - max) as 2^(x log2e - max log2e): one fused multiply-add and one ex2; -inf gives 0
+  float r;
+  asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(r) : "f"(fmaf(x, 1.4426950408889634f, neg_scaled_max)));
+  return r;
+}
+
+// One CTA per row, a warp owns a contiguous run of the row (coalesced loads, 32 elements per step).
+//   pass 1  maximum and validity
+//   pass 2  warp totals of the weights: per-lane f64 sums, one fixed tree per warp; thread 0 chains
+//           the 32 totals -> the threshold total * u falls into one warp's span
+//   pass 3  that warp walks its run chunk by chunk (chunk total by the fixed tree, chained in f64)
+//           to the chunk where the cumulative weight first exceeds the threshold, then scans the 32
+//           elements of that chunk.
+// Pass 2 and pass 3 add the same weights in different orders, so when the threshold lies within
+// rounding of a boundary the walk can end without a crossing; the draw then is the next element
+// of positive mass (what exact arithmetic would give), or, at the very end of the row, the last
+// index holding the maximum (src/compute_provider_native/sampling.cc:171-176).
 template <int kDtype>
-__global__ void __launch_bounds__(kDrawThreads)
+__global__ void __launch_bounds__(kDrawThreads, 2)
 categorical_kernel(const void *logits, const uint32_t *__restrict__ identities, int32_t *index_out, float *log_probability,
                    uint64_t rows, uint32_t cols, uint32_t *status_word) {
   grid_dependency_sync();
@@ -98,9 +112,12 @@ categorical_kernel(const void *logits, const uint32_t *__restrict__ identities, 
   __shared__ uint32_t s_bad[kDrawWarps];
   __shared__ double s_sum[kDrawWarps];
   __shared__ double s_before[kDrawWarps + 1];
-  __shared__ int32_t s_selected;
+  __shared__ int32_t s_selected;   // >= 0: the draw;  -1: not found yet
+  __shared__ uint32_t s_resume;    // where to look for the next element of positive mass
+  __shared__ uint32_t s_next;
+  __shared__ int32_t s_last;
   const int t = threadIdx.x, lane = t & 31, warp = t >> 5;
-  const uint32_t run = (cols + kDrawWarps - 1) / kDrawWarps;  // elements per warp
+  const uint32_t run = ((cols + kDrawWarps - 1) / kDrawWarps + 31) / 32 * 32;  // elements per warp, whole chunks
   const uint32_t begin = min(warp * run, cols), end = min(begin + run, cols);
   constexpr size_t kWidth = kDtype == HYLE_B200_F32 ? 4 : 2;
 
@@ -138,15 +155,12 @@ categorical_kernel(const void *logits, const uint32_t *__restrict__ identities, 
       __syncthreads();
       continue;
     }
-    // pass 2: the warp's total of exp(x - max) (f32 weights, f64 sums), built as the last value of the
-    // same 32-wide inclusive scan chain that pass 3 walks, so the two agree to the last bit
-    double carried = 0.0;
-    for (uint32_t base = begin; base < end; base += 32) {
-      const uint32_t i = base + lane;
-      const double weight = i < end ? static_cast<double>(expf(load_logit<kDtype>(x, i) - maximum)) : 0.0;
-      carried = __shfl_sync(kFullMask, carried + warp_inclusive_scan(weight, lane), 31);
-    }
-    if (lane == 0) s_sum[warp] = carried;
+    const float neg_scaled_max = -__fmul_rn(maximum, 1.4426950408889634f);
+    // pass 2
+    double sum = 0.0;
+    for (uint32_t i = begin + lane; i < end; i += 32) sum += static_cast<double>(weight_of(load_logit<kDtype>(x, i), neg_scaled_max));
+    sum = warp_sum(sum);
+    if (lane == 0) s_sum[warp] = sum;
     __syncthreads();
     if (t == 0) {
       double running = 0.0;
@@ -156,6 +170,9 @@ categorical_kernel(const void *logits, const uint32_t *__restrict__ identities, 
       }
       s_before[kDrawWarps] = running;
       s_selected = -1;
+      s_resume = cols;
+      s_next = cols;
+      s_last = -1;
     }
     __syncthreads();
     const double total = s_before[kDrawWarps];
@@ -166,35 +183,54 @@ categorical_kernel(const void *logits, const uint32_t *__restrict__ identities, 
     // pass 3: the warp whose span of the cumulative sum holds the threshold walks its run
     const bool mine = s_before[warp] <= threshold && (warp == kDrawWarps - 1 || threshold < s_before[warp + 1]) && begin < end;
     if (mine) {
-      const double before = s_before[warp];
-      double local = 0.0;  // the scan chain of pass 2, replayed
+      double cumulative = s_before[warp];
       int32_t found = -1;
-      for (uint32_t base = begin; base < end && found < 0; base += 32) {
-        const uint32_t i = base + lane;
-        const double weight = i < end ? static_cast<double>(expf(load_logit<kDtype>(x, i) - maximum)) : 0.0;
-        const double inclusive = local + warp_inclusive_scan(weight, lane);
-        const unsigned crossed = __ballot_sync(kFullMask, i < end && before + inclusive > threshold);
-        if (crossed != 0) found = static_cast<int32_t>(base + __ffs(crossed) - 1);
-        local = __shfl_sync(kFullMask, inclusive, 31);
+      constexpr int kStep = 4;  // chunks whose totals are formed together: their tree sums overlap
+      for (uint32_t base = begin; base < end && found < 0; base += 32 * kStep) {
+        double weight[kStep], chunk_total[kStep];
+#pragma unroll
+        for (int k = 0; k < kStep; ++k) {
+          const uint32_t i = base + 32 * k + lane;
+          weight[k] = i < end ? static_cast<double>(weight_of(load_logit<kDtype>(x, i), neg_scaled_max)) : 0.0;
+        }
+#pragma unroll
+        for (int k = 0; k < kStep; ++k) chunk_total[k] = warp_sum(weight[k]);
+#pragma unroll
+        for (int k = 0; k < kStep; ++k) {
+          const double after = cumulative + chunk_total[k];
+          if (found < 0 && after > threshold) {  // the crossing is inside this chunk (warp-uniform)
+            const double inclusive = cumulative + warp_inclusive_scan(weight[k], lane);
+            const unsigned crossed = __ballot_sync(kFullMask, weight[k] > 0.0 && inclusive > threshold);
+            const unsigned massive = __ballot_sync(kFullMask, weight[k] > 0.0);
+            // the scan and the tree may disagree in the last bit: then the chunk's last element of mass
+            found = static_cast<int32_t>(base + 32 * k + (crossed != 0 ? __ffs(crossed) - 1 : 31 - __clz(massive)));
+          }
+          cumulative = after;
+        }
       }
-      if (lane == 0) s_selected = found;
+      if (lane == 0) {
+        s_selected = found;
+        s_resume = end;  // only read when found < 0
+      }
     }
     __syncthreads();
-    int32_t selected = s_selected;
-    if (selected < 0) {
-      // rounding left the threshold at or above the last cumulative value: take the last element of
-      // positive mass, never a masked tail (src/compute_provider_native/sampling.cc:171-176)
-      __shared__ int32_t s_last;
-      if (t == 0) s_last = -1;
-      __syncthreads();
+    if (s_selected < 0) {  // CTA-uniform; rare
+      const uint32_t resume = s_resume;
+      uint32_t next = cols;
       int32_t last = -1;
-      for (uint32_t i = t; i < cols; i += kDrawThreads)
-        if (load_logit<kDtype>(x, i) == maximum) last = static_cast<int32_t>(i);
+      for (uint32_t i = t; i < cols; i += kDrawThreads) {
+        const float v = load_logit<kDtype>(x, i);
+        if (i >= resume && v > -CUDART_INF_F && weight_of(v, neg_scaled_max) > 0.0f) next = min(next, i);
+        if (v == maximum) last = static_cast<int32_t>(i);
+      }
+      if (next < cols) atomicMin(&s_next, next);
       if (last >= 0) atomicMax(&s_last, last);
       __syncthreads();
-      selected = s_last;
+      if (t == 0) s_selected = s_next < cols ? static_cast<int32_t>(s_next) : s_last;
+      __syncthreads();
     }
     if (t == 0) {
+      const int32_t selected = s_selected;
       index_out[row] = selected;
       if (log_probability != nullptr)
         log_probability[row] = static_cast<float>(static_cast<double>(load_logit<kDtype>(x, static_cast<uint32_t>(selected))) -
@@ -228,7 +264,7 @@ extern "C" int hyle_b200_categorical(hyle_b200_stream_t stream, int dtype, const
   if (log_weights == nullptr || identities == nullptr || index_out == nullptr || cols == 0 || cols > 0x7fffffffull)
     return HYLE_B200_INVALID_VALUE;
   auto s = reinterpret_cast<cudaStream_t>(stream);
-  const unsigned grid = clamp_grid(rows, static_cast<uint64_t>(sm_count()) * 2);
+  const unsigned grid = clamp_grid(rows, static_cast<uint64_t>(sm_count()) * 2);  // two CTAs of 512 threads per SM
   const uint32_t width = static_cast<uint32_t>(cols);
   if (dtype == HYLE_B200_F32)
     return launch(categorical_kernel<HYLE_B200_F32>, dim3(grid), dim3(kDrawThreads), 0, s, log_weights, identities, index_out,
