@@ -504,14 +504,18 @@ def run_gpu(args):
     # "nccl": kernel, then ncclAllReduce on the same stream.
     reducer, peers, exchange = None, None, "none"
     if world > 1:
-        from hyle_b200.collective import PeerExchange, StreamAllReduce
+        from hyle_b200.collective import PeerExchange, PeerMappingUnavailable, StreamAllReduce
 
         if args.exchange == "fused":
-            peers = PeerExchange()
-            exchange = "fused into the kernel: 8-byte stores to peer mailboxes over NVLink, summed in rank order"
-        else:
+            try:
+                peers = PeerExchange()
+                exchange = "fused into the kernel: 8-byte stores to peer mailboxes over NVLink, summed in rank order"
+            except PeerMappingUnavailable as problem:  # raised on every rank together
+                exchange = f"ncclAllReduce of one f64 on the kernels' stream (peer mapping unavailable: {problem})"
+        if peers is None:
             reducer = StreamAllReduce()
-            exchange = "ncclAllReduce of one f64 on the kernels' stream"
+            if args.exchange != "fused":
+                exchange = "ncclAllReduce of one f64 on the kernels' stream"
 
     def step():
         if peers is not None:

@@ -69,6 +69,10 @@ class StreamAllReduce:
             self.comm = ctypes.c_void_p()
 
 
+class PeerMappingUnavailable(RuntimeError):
+    """The GPUs' memory could not be mapped between the processes (CUDA IPC refused on this machine)."""
+
+
 class PeerExchange:
     """Mailboxes for `hyle_b200_q8_0_roundtrip_bf16_exchange`, one process per GPU.
 
@@ -88,26 +92,51 @@ class PeerExchange:
         if self.world > abi.EXCHANGE_MAX_RANKS:
             raise ValueError(f"at most {abi.EXCHANGE_MAX_RANKS} ranks")
         self.mailbox = ctypes.c_void_p()
-        handle = ctypes.create_string_buffer(abi.EXCHANGE_HANDLE_BYTES)
-        abi.check("hyle_b200_exchange_create", self.lib.hyle_b200_exchange_create(ctypes.byref(self.mailbox), handle))
-        handles = [None] * self.world
-        dist.all_gather_object(handles, handle.raw)
         self.pointers = (ctypes.c_void_p * self.world)()
         self.opened = []
-        for peer, raw in enumerate(handles):
-            if peer == self.rank:
-                self.pointers[peer] = self.mailbox.value
-                continue
-            mapped = ctypes.c_void_p()
-            abi.check("hyle_b200_exchange_open", self.lib.hyle_b200_exchange_open(raw, ctypes.byref(mapped)))
-            self.pointers[peer] = mapped.value
-            self.opened.append(mapped)
         self.epoch = 0
-        dist.barrier()  # nobody starts a step before every mailbox is mapped everywhere
+        # Set-up is collective: every step (create, exchange handles, map) is attempted by every rank
+        # and the outcome agreed on, so that either all ranks hold a complete table or all raise
+        # PeerMappingUnavailable -- never a mixture that would leave some ranks waiting in a kernel.
+        handle = ctypes.create_string_buffer(abi.EXCHANGE_HANDLE_BYTES)
+        failure = None
+        code = self.lib.hyle_b200_exchange_create(ctypes.byref(self.mailbox), handle)
+        if code != abi.OK:
+            failure = f"hyle_b200_exchange_create returned {code}"
+        handles = [None] * self.world
+        dist.all_gather_object(handles, handle.raw if failure is None else None)
+        if failure is None and any(raw is None for raw in handles):
+            failure = "a peer could not create its mailbox"
+        if failure is None:
+            for peer, raw in enumerate(handles):
+                if peer == self.rank:
+                    self.pointers[peer] = self.mailbox.value
+                    continue
+                mapped = ctypes.c_void_p()
+                code = self.lib.hyle_b200_exchange_open(raw, ctypes.byref(mapped))
+                if code != abi.OK:
+                    failure = f"hyle_b200_exchange_open returned {code} for rank {peer}"
+                    break
+                self.pointers[peer] = mapped.value
+                self.opened.append(mapped)
+        outcomes = [None] * self.world
+        dist.all_gather_object(outcomes, failure)  # also the barrier: every mailbox is mapped everywhere
+        problems = [f"rank {r}: {text}" for r, text in enumerate(outcomes) if text is not None]
+        if problems:
+            self._release()
+            raise PeerMappingUnavailable("; ".join(problems))
 
     def next_epoch(self) -> int:
         self.epoch = self.epoch % 0xFFFFFFFE + 1  # 1 ... 2^32-2, so consecutive values always differ in parity
         return self.epoch
+
+    def _release(self) -> None:
+        for mapped in self.opened:
+            self.lib.hyle_b200_exchange_close(mapped)
+        self.opened = []
+        if self.mailbox:
+            self.lib.hyle_b200_exchange_destroy(self.mailbox)
+            self.mailbox = ctypes.c_void_p()
 
     def close(self) -> None:
         import torch
@@ -115,9 +144,4 @@ class PeerExchange:
 
         torch.cuda.synchronize()
         dist.barrier()  # no peer is still writing into a mailbox that is about to go
-        for mapped in self.opened:
-            self.lib.hyle_b200_exchange_close(mapped)
-        self.opened = []
-        if self.mailbox:
-            self.lib.hyle_b200_exchange_destroy(self.mailbox)
-            self.mailbox = ctypes.c_void_p()
+        self._release()
