@@ -68,6 +68,7 @@ random_bits_kernel(const uint32_t *__restrict__ identities, uint32_t *out, uint6
 // ---- Categorical ---------------------------------------------------------------------------------
 constexpr int kDrawThreads = 512;  // two CTAs per SM: 296 rows in flight
 constexpr int kDrawWarps = kDrawThreads / 32;
+constexpr uint32_t kDrawMaxChunks = 1024;  // chunk totals of one run kept in shared memory (rows up to 524 288 wide)
 
 template <int kDtype>
 __device__ __forceinline__ float load_logit(const void *row, uint32_t i) {
@@ -96,9 +97,9 @@ __device__ __forceinline__ float weight_of(float x, float neg_scaled_max) {
 //   pass 1  maximum and validity
 //   pass 2  warp totals of the weights: per-lane f64 sums, one fixed tree per warp; thread 0 chains
 //           the 32 totals -> the threshold total * u falls into one warp's span
-//   pass 3  that warp walks its run chunk by chunk (chunk total by the fixed tree, chained in f64)
-//           to the chunk where the cumulative weight first exceeds the threshold, then scans the 32
-//           elements of that chunk.
+//   pass 3  all warps form the chunk totals of that run (32 elements each, fixed tree); warp 0 chains
+//           them in f64 to the chunk where the cumulative weight first exceeds the threshold and
+//           scans the 32 elements of that chunk.
 // Pass 2 and pass 3 add the same weights in different orders, so when the threshold lies within
 // rounding of a boundary the walk can end without a crossing; the draw then is the next element
 // of positive mass (what exact arithmetic would give), or, at the very end of the row, the last
@@ -112,6 +113,7 @@ categorical_kernel(const void *logits, const uint32_t *__restrict__ identities, 
   __shared__ uint32_t s_bad[kDrawWarps];
   __shared__ double s_sum[kDrawWarps];
   __shared__ double s_before[kDrawWarps + 1];
+  __shared__ double s_chunk[kDrawMaxChunks];
   __shared__ int32_t s_selected;   // >= 0: the draw;  -1: not found yet
   __shared__ uint32_t s_resume;    // where to look for the next element of positive mass
   __shared__ uint32_t s_next;
@@ -126,7 +128,19 @@ categorical_kernel(const void *logits, const uint32_t *__restrict__ identities, 
     // pass 1: maximum; NaN or +inf anywhere makes the row invalid
     float maximum = -CUDART_INF_F;
     uint32_t bad = 0;
-    for (uint32_t i = begin + lane; i < end; i += 32) {
+    // f32 rows whose start is 16-byte aligned are read as float4 in passes 1 and 2 (neither depends
+    // on the order of the elements inside a warp's run); runs start at multiples of 32 elements
+    const bool vectors = kDtype == HYLE_B200_F32 && (reinterpret_cast<uintptr_t>(x) & 15) == 0;
+    const uint32_t vector_end = vectors ? begin + (end - begin) / 4 * 4 : begin;
+    for (uint32_t i = begin + 4 * lane; i < vector_end; i += 128) {
+      const float4 v = *reinterpret_cast<const float4 *>(static_cast<const float *>(x) + i);
+      const float high = fmaxf(fmaxf(v.x, v.y), fmaxf(v.z, v.w));
+      // NaN: fminf / fmaxf drop it, so test the sum (inf - inf cannot occur: +inf is rejected anyway)
+      const float probe = (v.x + v.y) + (v.z + v.w);
+      bad |= (probe != probe || high == CUDART_INF_F) ? 1u : 0u;
+      maximum = fmaxf(maximum, high);
+    }
+    for (uint32_t i = vector_end + lane; i < end; i += 32) {
       const float v = load_logit<kDtype>(x, i);
       bad |= (v != v || v == CUDART_INF_F) ? 1u : 0u;
       maximum = fmaxf(maximum, v);
@@ -158,7 +172,12 @@ categorical_kernel(const void *logits, const uint32_t *__restrict__ identities, 
     const float neg_scaled_max = -__fmul_rn(maximum, 1.4426950408889634f);
     // pass 2
     double sum = 0.0;
-    for (uint32_t i = begin + lane; i < end; i += 32) sum += static_cast<double>(weight_of(load_logit<kDtype>(x, i), neg_scaled_max));
+    for (uint32_t i = begin + 4 * lane; i < vector_end; i += 128) {
+      const float4 v = *reinterpret_cast<const float4 *>(static_cast<const float *>(x) + i);
+      sum += (static_cast<double>(weight_of(v.x, neg_scaled_max)) + static_cast<double>(weight_of(v.y, neg_scaled_max))) +
+             (static_cast<double>(weight_of(v.z, neg_scaled_max)) + static_cast<double>(weight_of(v.w, neg_scaled_max)));
+    }
+    for (uint32_t i = vector_end + lane; i < end; i += 32) sum += static_cast<double>(weight_of(load_logit<kDtype>(x, i), neg_scaled_max));
     sum = warp_sum(sum);
     if (lane == 0) s_sum[warp] = sum;
     __syncthreads();
@@ -180,9 +199,54 @@ categorical_kernel(const void *logits, const uint32_t *__restrict__ identities, 
     const double uniform =
         (static_cast<double>(random.x0) * 1048576.0 + static_cast<double>(random.x1 >> 12) + 0.5) * 2.220446049250313e-16;
     const double threshold = total * uniform;
-    // pass 3: the warp whose span of the cumulative sum holds the threshold walks its run
-    const bool mine = s_before[warp] <= threshold && (warp == kDrawWarps - 1 || threshold < s_before[warp + 1]) && begin < end;
-    if (mine) {
+    // pass 3: the run whose span of the cumulative sum holds the threshold.  Every thread finds the
+    // owner from the same shared values, so the choice is CTA-uniform.
+    int owner = kDrawWarps - 1;
+#pragma unroll
+    for (int w = kDrawWarps - 2; w >= 0; --w)
+      if (threshold < s_before[w + 1]) owner = w;
+    const uint32_t owner_begin = min(owner * run, cols), owner_end = min(owner_begin + run, cols);
+    const uint32_t chunks = (owner_end - owner_begin + 31) / 32;
+    if (chunks <= kDrawMaxChunks) {
+      // all warps share the owner's run: chunk totals (fixed tree) into shared memory ...
+      for (uint32_t c = warp; c < chunks; c += kDrawWarps) {
+        const uint32_t i = owner_begin + 32 * c + lane;
+        const double weight = i < owner_end ? static_cast<double>(weight_of(load_logit<kDtype>(x, i), neg_scaled_max)) : 0.0;
+        const double chunk_total = warp_sum(weight);
+        if (lane == 0) s_chunk[c] = chunk_total;
+      }
+      __syncthreads();
+      // ... then warp 0 chains them, 32 at a time, to the chunk where the cumulative weight first
+      // exceeds the threshold, and scans the 32 elements of that chunk
+      if (warp == 0) {
+        double cumulative = s_before[owner];
+        int32_t found = -1;
+        for (uint32_t group = 0; group < chunks && found < 0; group += 32) {
+          const uint32_t c = group + lane;
+          const double inclusive = cumulative + warp_inclusive_scan(c < chunks ? s_chunk[c] : 0.0, lane);
+          const unsigned crossed = __ballot_sync(kFullMask, c < chunks && inclusive > threshold);
+          if (crossed != 0) {
+            const int first = __ffs(crossed) - 1;
+            const double previous = __shfl_sync(kFullMask, inclusive, first > 0 ? first - 1 : 0);
+            const double before = first > 0 ? previous : cumulative;
+            const uint32_t base = owner_begin + 32 * (group + first);
+            const uint32_t i = base + lane;
+            const double weight = i < owner_end ? static_cast<double>(weight_of(load_logit<kDtype>(x, i), neg_scaled_max)) : 0.0;
+            const double within = before + warp_inclusive_scan(weight, lane);
+            const unsigned hit = __ballot_sync(kFullMask, weight > 0.0 && within > threshold);
+            const unsigned massive = __ballot_sync(kFullMask, weight > 0.0);
+            // the scan and the tree may disagree in the last bit: then the chunk's last element of mass
+            found = static_cast<int32_t>(base + (hit != 0 ? __ffs(hit) - 1 : 31 - __clz(massive)));
+          }
+          cumulative = __shfl_sync(kFullMask, inclusive, 31);
+        }
+        if (lane == 0) {
+          s_selected = found;
+          s_resume = owner_end;  // only read when found < 0
+        }
+      }
+    } else if (warp == owner) {
+      // a run too long for the shared table: the owning warp walks it alone
       double cumulative = s_before[warp];
       int32_t found = -1;
       constexpr int kStep = 4;  // chunks whose totals are formed together: their tree sums overlap
@@ -202,7 +266,6 @@ categorical_kernel(const void *logits, const uint32_t *__restrict__ identities, 
             const double inclusive = cumulative + warp_inclusive_scan(weight[k], lane);
             const unsigned crossed = __ballot_sync(kFullMask, weight[k] > 0.0 && inclusive > threshold);
             const unsigned massive = __ballot_sync(kFullMask, weight[k] > 0.0);
-            // the scan and the tree may disagree in the last bit: then the chunk's last element of mass
             found = static_cast<int32_t>(base + 32 * k + (crossed != 0 ? __ffs(crossed) - 1 : 31 - __clz(massive)));
           }
           cumulative = after;
@@ -210,7 +273,7 @@ categorical_kernel(const void *logits, const uint32_t *__restrict__ identities, 
       }
       if (lane == 0) {
         s_selected = found;
-        s_resume = end;  // only read when found < 0
+        s_resume = end;
       }
     }
     __syncthreads();
