@@ -81,13 +81,15 @@ class PeerExchange:
     array the entry point takes; `next_epoch()` numbers the collective calls 1, 2, 3, ...
     """
 
-    def __init__(self):
+    def __init__(self, library=None):
+        """`library`: an object with the four hyle_b200_exchange_* functions (tests pass a stand-in
+        to exercise the set-up protocol without GPUs); by default the kernel library."""
         import torch.distributed as dist
 
         from . import abi
 
         self.abi = abi
-        self.lib = abi.load()
+        self.lib = abi.load() if library is None else library
         self.world, self.rank = dist.get_world_size(), dist.get_rank()
         if self.world > abi.EXCHANGE_MAX_RANKS:
             raise ValueError(f"at most {abi.EXCHANGE_MAX_RANKS} ranks")
@@ -142,6 +144,7 @@ class PeerExchange:
         import torch
         import torch.distributed as dist
 
-        torch.cuda.synchronize()
+        if torch.cuda.is_available():
+            torch.cuda.synchronize()
         dist.barrier()  # no peer is still writing into a mailbox that is about to go
         self._release()

@@ -84,3 +84,74 @@ def test_two_rank_sweep_over_gloo(tmp_path):
         env=env, capture_output=True, text=True, timeout=300)
     assert result.returncode == 0, result.stdout[-2000:] + result.stderr[-2000:]
     assert result.stdout.count("ok") == 2
+
+
+EXCHANGE_SCRIPT = textwrap.dedent("""
+    import ctypes, os, sys
+    sys.path.insert(0, os.environ["HYLE_ROOT"])
+    import torch.distributed as dist
+    from hyle_b200.collective import PeerExchange, PeerMappingUnavailable
+
+    class FakeLibrary:
+        # The four set-up calls of the kernel library, on host memory; `refuse` makes this rank's
+        # mapping of rank 0's mailbox fail the way a refused CUDA IPC open does.
+        def __init__(self, rank, refuse):
+            self.rank, self.refuse, self.live = rank, refuse, 0
+        def hyle_b200_exchange_create(self, mailbox, handle):
+            mailbox._obj.value = 0x1000 * (self.rank + 1)
+            handle.raw = bytes([self.rank + 1]) * 64
+            self.live += 1
+            return 0
+        def hyle_b200_exchange_open(self, raw, mapped):
+            if self.refuse and raw[0] == 1:
+                return 201
+            mapped._obj.value = 0x100000 * raw[0]
+            self.live += 1
+            return 0
+        def hyle_b200_exchange_close(self, mapped):
+            self.live -= 1
+            return 0
+        def hyle_b200_exchange_destroy(self, mailbox):
+            self.live -= 1
+            return 0
+
+    dist.init_process_group("gloo")
+    rank, world = dist.get_rank(), dist.get_world_size()
+    # 1: everything maps -> a complete pointer table on every rank, epochs 1, 2, 3
+    library = FakeLibrary(rank, refuse=False)
+    peers = PeerExchange(library)
+    table = [peers.pointers[r] for r in range(world)]
+    assert table[rank] == 0x1000 * (rank + 1)
+    assert all(table[r] == 0x100000 * (r + 1) for r in range(world) if r != rank)
+    assert [peers.next_epoch() for _ in range(3)] == [1, 2, 3]
+    peers.epoch = 0xFFFFFFFE
+    assert peers.next_epoch() == 1                      # wraps without repeating a parity
+    peers.close()
+    assert library.live == 0
+    # 2: one rank cannot map a peer -> EVERY rank raises, nothing stays mapped
+    library = FakeLibrary(rank, refuse=(rank == 1))
+    try:
+        PeerExchange(library)
+        raise SystemExit("no exception on rank %d" % rank)
+    except PeerMappingUnavailable as problem:
+        assert "rank 1" in str(problem)
+    assert library.live == 0
+    dist.barrier(); dist.destroy_process_group()
+    print("rank", rank, "ok")
+""")
+
+
+def test_peer_exchange_setup_is_collective_over_gloo(tmp_path):
+    """The mailbox set-up of the fused exchange with a stand-in for the kernel library: either all
+    ranks end with a full table or all raise together."""
+    script = tmp_path / "exchange.py"
+    script.write_text(EXCHANGE_SCRIPT)
+    with socket.socket() as s:
+        s.bind(("127.0.0.1", 0))
+        port = s.getsockname()[1]
+    result = subprocess.run(
+        [sys.executable, "-m", "torch.distributed.run", "--nnodes=1", "--nproc-per-node=2",
+         "--master-addr", "127.0.0.1", "--master-port", str(port), str(script)],
+        env=dict(os.environ, HYLE_ROOT=ROOT), capture_output=True, text=True, timeout=300)
+    assert result.returncode == 0, result.stdout[-2000:] + result.stderr[-2000:]
+    assert result.stdout.count("ok") == 2
