@@ -13,6 +13,8 @@
 // two element sizes allow (8 to 32 bytes), four steps in flight.
 #include "common.cuh"
 
+#include <type_traits>
+
 namespace hb {
 namespace {
 
@@ -249,6 +251,62 @@ int launch_cast(cudaStream_t stream, const void *in, void *out, uint64_t count) 
                 static_cast<Out *>(out) + done, count - done);
 }
 
+// ---- Select: out = condition ? when_true : when_false, elements moved as bits ------------------------------
+// (include/hyle/compute/operation.h:305, src/compute_ops/operation.cc:1309-1328; any non-zero
+// condition byte is true, include/hyle/simd/ops.h:80).  Either branch may be the full tensor or repeat
+// with a period over the trailing axes (period 1 = one scalar, the masking case).
+template <int kBytes>
+__global__ void __launch_bounds__(kThreads)
+select_kernel(const void *condition, const void *when_true, const void *when_false, void *out, uint64_t packs) {
+  grid_dependency_sync();
+  const uint64_t stride = static_cast<uint64_t>(gridDim.x) * kThreads;
+  for (uint64_t i = static_cast<uint64_t>(blockIdx.x) * kThreads + threadIdx.x; i < packs; i += stride) {
+    uint32_t c[8], a[8], b[8];
+    unpack<1>(load_pack<1>(condition, i), c);
+    unpack<kBytes>(load_pack<kBytes>(when_true, i), a);
+    unpack<kBytes>(load_pack<kBytes>(when_false, i), b);
+#pragma unroll
+    for (int e = 0; e < 8; ++e) a[e] = c[e] != 0 ? a[e] : b[e];
+    store_pack<kBytes>(out, i, pack<kBytes>(a));
+  }
+}
+
+// Broadcast branches, unaligned tensors and tails: one element per thread-step.
+template <class Word>
+__global__ void __launch_bounds__(kThreads)
+select_scalar_kernel(const unsigned char *condition, const Word *when_true, const Word *when_false, Word *out,
+                     uint64_t first, uint64_t count, uint64_t true_period, uint64_t false_period) {
+  grid_dependency_sync();
+  const uint64_t stride = static_cast<uint64_t>(gridDim.x) * kThreads;
+  for (uint64_t i = first + static_cast<uint64_t>(blockIdx.x) * kThreads + threadIdx.x; i < count; i += stride)
+    out[i] = condition[i] != 0 ? when_true[i % true_period] : when_false[i % false_period];
+}
+
+template <int kBytes>
+int launch_select(cudaStream_t stream, const void *condition, const void *when_true, const void *when_false, void *out,
+                  uint64_t count, uint64_t true_period, uint64_t false_period) {
+  using Word = typename std::conditional<kBytes == 4, uint32_t, unsigned short>::type;
+  if (!aligned_to(when_true, kBytes) || !aligned_to(when_false, kBytes) || !aligned_to(out, kBytes))
+    return HYLE_B200_INVALID_VALUE;
+  const uint64_t resident = static_cast<uint64_t>(sm_count()) * kCtasPerSm;
+  const bool vector_ok = true_period == count && false_period == count && aligned_to(condition, 8) && aligned_to(out, 16) &&
+                         aligned_to(when_true, 16) && aligned_to(when_false, 16);
+  uint64_t done = 0;
+  if (vector_ok && count >= 8) {
+    const uint64_t packs = count / 8;
+    const unsigned grid = clamp_grid((packs + kThreads * 2 - 1) / (kThreads * 2), resident);
+    const int status = launch(select_kernel<kBytes>, dim3(grid), dim3(kThreads), 0, stream, condition, when_true, when_false,
+                              out, packs);
+    if (status != HYLE_B200_OK) return status;
+    done = packs * 8;
+  }
+  if (done == count) return HYLE_B200_OK;
+  const unsigned grid = clamp_grid((count - done + kThreads - 1) / kThreads, resident);
+  return launch(select_scalar_kernel<Word>, dim3(grid), dim3(kThreads), 0, stream, static_cast<const unsigned char *>(condition),
+                static_cast<const Word *>(when_true), static_cast<const Word *>(when_false), static_cast<Word *>(out), done,
+                count, true_period, false_period);
+}
+
 // ---- CacheEncode{float8(scale)}: value / scale -> E4M3, a non-finite value -> byte 0 and a status bit -------
 // (src/compute_provider_ggml/ggml_cpu_provider.cc:589-596).  One IEEE division per element.
 template <int kSrc>
@@ -357,5 +415,20 @@ extern "C" int hyle_b200_fp8_e4m3_encode(hyle_b200_stream_t stream, int dtype, c
   if (dtype == HYLE_B200_F32) return launch_cache_encode<HYLE_B200_F32>(s, in, out, count, scale, status_word);
   if (dtype == HYLE_B200_BF16) return launch_cache_encode<HYLE_B200_BF16>(s, in, out, count, scale, status_word);
   if (dtype == HYLE_B200_F16) return launch_cache_encode<HYLE_B200_F16>(s, in, out, count, scale, status_word);
+  return HYLE_B200_INVALID_VALUE;
+}
+
+extern "C" int hyle_b200_select(hyle_b200_stream_t stream, int dtype, const void *condition, const void *when_true,
+                                const void *when_false, void *out, uint64_t count, uint64_t true_period,
+                                uint64_t false_period) {
+  if (count == 0) return HYLE_B200_OK;
+  if (condition == nullptr || when_true == nullptr || when_false == nullptr || out == nullptr || true_period == 0 ||
+      false_period == 0 || count % true_period != 0 || count % false_period != 0)
+    return HYLE_B200_INVALID_VALUE;
+  auto s = reinterpret_cast<cudaStream_t>(stream);
+  if (dtype == HYLE_B200_F32 || dtype == HYLE_B200_I32)
+    return launch_select<4>(s, condition, when_true, when_false, out, count, true_period, false_period);
+  if (dtype == HYLE_B200_BF16 || dtype == HYLE_B200_F16)
+    return launch_select<2>(s, condition, when_true, when_false, out, count, true_period, false_period);
   return HYLE_B200_INVALID_VALUE;
 }

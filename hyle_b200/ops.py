@@ -400,3 +400,17 @@ def categorical(log_weights: torch.Tensor, identities: torch.Tensor, want_log_pr
         _stream(), _DTYPE[log_weights.dtype], log_weights.data_ptr(), identities.data_ptr(), rows, cols,
         index.data_ptr(), _ptr(logp), _ptr(status)))
     return index, logp
+
+
+def select(condition: torch.Tensor, when_true: torch.Tensor, when_false: torch.Tensor) -> torch.Tensor:
+    """Select: condition (uint8 / bool bytes, shape of the result) picks when_true or when_false; each branch has
+    the result's shape or its trailing axes (a one-element tensor is a scalar)."""
+    _device_tensor(condition, "condition"), _device_tensor(when_true, "when_true"), _device_tensor(when_false, "when_false")
+    if when_true.dtype != when_false.dtype or condition.element_size() != 1:
+        raise ValueError("branches must share a type and the condition must be one byte per element")
+    code = {torch.float32: abi.F32, torch.int32: abi.I32, torch.bfloat16: abi.BF16, torch.float16: abi.F16}[when_true.dtype]
+    out = torch.empty(condition.shape, dtype=when_true.dtype, device=condition.device)
+    abi.check("hyle_b200_select", abi.load().hyle_b200_select(
+        _stream(), code, condition.data_ptr(), when_true.data_ptr(), when_false.data_ptr(), out.data_ptr(),
+        condition.numel(), max(when_true.numel(), 1), max(when_false.numel(), 1)))
+    return out

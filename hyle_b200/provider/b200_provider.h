@@ -36,7 +36,7 @@ inline constexpr ProviderRuntimeProperties kRuntime{.replay_class = ProviderRepl
                                                     .capture_compatible = true};
 
 enum class Entry : std::uint8_t {
-  kUnary, kBinary, kReduceRows, kRmsNorm, kLayerNorm, kSwiglu, kSoftmax, kCast, kArgmax, kQ8Encode, kFp8Encode, kRandomBits, kCategorical,
+  kUnary, kBinary, kSelect, kReduceRows, kRmsNorm, kLayerNorm, kSwiglu, kSoftmax, kCast, kArgmax, kQ8Encode, kFp8Encode, kRandomBits, kCategorical,
   kAddRmsNorm, kBiasRowSumMax, kLogitsReduce, kQ8Roundtrip
 };
 
@@ -126,6 +126,22 @@ inline std::optional<Plan> match(const Operation &op, std::span<const TensorDesc
     p.entry = Entry::kUnary;
     p.kind = static_cast<int>(unary->kind);
     p.dtype = *type;
+    return p;
+  }
+  if (op.get_if<Select>() != nullptr) {
+    // condition Bool of the output's shape; each branch of that shape or of its trailing axes
+    if (in.size() != 3 || out.size() != 1 || in[0].data_type() != DataType::kBool || in[1].data_type() != in[2].data_type() ||
+        out[0].data_type() != in[1].data_type() || in[0].dimensions().size() != out[0].dimensions().size() ||
+        elements(in[0]) != elements(out[0]) || !trailing_axes(out[0], in[1]) || !trailing_axes(out[0], in[2]))
+      return std::nullopt;
+    const auto branch = cast_dtype(in[1].data_type());
+    if (!branch || (*branch != HYLE_B200_F32 && *branch != HYLE_B200_I32 && *branch != HYLE_B200_BF16 && *branch != HYLE_B200_F16))
+      return std::nullopt;
+    p.entry = Entry::kSelect;
+    p.dtype = *branch;
+    p.count = elements(out[0]);
+    p.rhs_period = elements(in[1]) ? elements(in[1]) : 1;   // period of when_true
+    p.gate_stride = elements(in[2]) ? elements(in[2]) : 1;  // period of when_false
     return p;
   }
   if (const auto *binary = op.get_if<Binary>()) {
@@ -314,6 +330,8 @@ inline int launch(const Plan &p, hyle_b200_stream_t stream, const void *const *i
   switch (p.entry) {
     case Entry::kUnary:
       return hyle_b200_unary(stream, p.kind, p.dtype, in[0], out[0], p.count);
+    case Entry::kSelect:
+      return hyle_b200_select(stream, p.dtype, in[0], in[1], in[2], out[0], p.count, p.rhs_period, p.gate_stride);
     case Entry::kBinary:
       return hyle_b200_binary(stream, p.kind, p.dtype, in[0], in[1], out[0], p.count, p.rhs_period);
     case Entry::kReduceRows:

@@ -98,6 +98,12 @@ int main() {
     const std::array out16{bf16_mat};
     check(taken(*context, Operation(Unary{UnaryKind::kGelu}), in16, out16), "Unary{kGelu} bf16");
   }
+  {  // Select: Bool condition, branches of the full shape or of the trailing axes
+    const auto mask = dense(DataType::kBool, {64, 4096});
+    const std::array in{mask, f32_mat, f32_row};
+    const std::array out{f32_mat};
+    check(taken(*context, Operation(Select{}), in, out), "Select{} f32, when_false broadcast over rows");
+  }
   {  // Reduce over the last axis
     const std::array in{f32_mat};
     const std::array out{f32_rows};

@@ -42,7 +42,7 @@ extern "C" {
 /* Same object as cudaStream_t; spelled out so C callers need no CUDA header. */
 typedef struct CUstream_st *hyle_b200_stream_t;
 
-#define HYLE_B200_ABI_VERSION 8
+#define HYLE_B200_ABI_VERSION 9
 
 enum hyle_b200_result {
   HYLE_B200_OK = 0,
@@ -262,6 +262,15 @@ HYLE_B200_API int hyle_b200_softmax_f32(hyle_b200_stream_t stream, int kind, con
  * Other pairs return NOT_SUPPORTED. */
 HYLE_B200_API int hyle_b200_cast(hyle_b200_stream_t stream, int source_dtype, int destination_dtype,
                                  const void *in, void *out, uint64_t count);
+
+/* Select (include/hyle/compute/operation.h:305, inference src/compute_ops/operation.cc:1309-1328):
+ * out[i] = condition[i] != 0 ? when_true[i % true_period] : when_false[i % false_period]; elements
+ * are moved as bits (NaN payloads included).  condition is one byte per element, any non-zero value is
+ * true (include/hyle/simd/ops.h:80).  dtype F32 / I32 (4-byte) or BF16 / F16 (2-byte) elements; a
+ * period equals count (same shape) or divides it (trailing-axes broadcast; 1 = one scalar). */
+HYLE_B200_API int hyle_b200_select(hyle_b200_stream_t stream, int dtype, const void *condition,
+                                   const void *when_true, const void *when_false, void *out,
+                                   uint64_t count, uint64_t true_period, uint64_t false_period);
 
 /* Cast{f32 -> bf16}, round to nearest even (include/hyle/simd/dtype.h:114-121). */
 HYLE_B200_API int hyle_b200_cast_f32_to_bf16(hyle_b200_stream_t stream, const float *in,

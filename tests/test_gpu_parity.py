@@ -635,6 +635,34 @@ def test_categorical_rejects_invalid_rows():
     assert bool(torch.isnan(logp[:3]).all()) and int(status.item()) == abi.STATUS_INVALID_CATEGORICAL_ROW
 
 
+@pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16, torch.float16, torch.int32])
+def test_select_moves_bits(dtype):
+    """out = condition ? a : b, bit for bit (NaN payloads, -0), any non-zero byte is true; branches of the full
+    shape, of the trailing axes, or scalars; an unaligned slice takes the element-wise kernel."""
+    gen = torch.Generator(device="cpu").manual_seed(5)
+    shape = (97, 264)
+    raw = {torch.float32: torch.int32, torch.int32: torch.int32}.get(dtype, torch.int16)
+    bits_a = torch.randint(-2 ** 15, 2 ** 15 - 1, shape, generator=gen).to(raw)
+    bits_b = torch.randint(-2 ** 15, 2 ** 15 - 1, shape, generator=gen).to(raw)
+    if raw == torch.int32:
+        bits_a = bits_a * 65536 + 12345
+        bits_b = bits_b * 65536 - 54321
+    a, b = bits_a.to(DEV).view(dtype), bits_b.to(DEV).view(dtype)
+    condition = torch.randint(0, 3, shape, generator=gen).to(torch.uint8)
+    condition[condition == 2] = 200
+    cond = condition.to(DEV)
+    want = torch.where(cond != 0, a.view(raw), b.view(raw))
+    assert torch.equal(ops.select(cond, a, b).view(raw), want)
+    row = b[0].contiguous()
+    want_row = torch.where(cond != 0, a.view(raw), row.view(raw)[None, :])
+    assert torch.equal(ops.select(cond, a, row).view(raw), want_row)
+    scalar = a[3, 5:6].contiguous()
+    want_scalar = torch.where(cond != 0, scalar.view(raw), b.view(raw))
+    assert torch.equal(ops.select(cond, scalar, b).view(raw), want_scalar)
+    flat_c, flat_a, flat_b = cond.reshape(-1)[3:2000], a.reshape(-1)[3:2000], b.reshape(-1)[3:2000]
+    assert torch.equal(ops.select(flat_c, flat_a, flat_b).view(raw), want.reshape(-1)[3:2000])
+
+
 def test_cast_rejects_other_pairs():
     x = torch.zeros(16, device=DEV)
     with pytest.raises(abi.KernelError):
