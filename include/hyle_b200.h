@@ -6,7 +6,8 @@
  * (include/hyle/compute/custom_kernel.h:302-360) and the model for a kernel library behind it is
  * the sample's `launch_affine(cudaStream_t, pointers, count, parameters) noexcept -> cudaError_t`
  * (samples/package/graph/custom_kernel/cuda_kernel.h:16-19): "no HYLE runtime or provider SPI
- * lives in this image".  Every entry point below has that shape:
+ * lives in this image".  Every operator entry point below has that shape (the four
+ * hyle_b200_exchange_* helpers at the end are set-up code: they allocate and map memory):
  *
  *   - plain device pointers, element counts and scalars; no C++ or framework types;
  *   - stream-ordered: work is recorded on `stream` and the call returns without synchronising;
