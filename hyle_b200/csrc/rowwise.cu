@@ -501,6 +501,82 @@ int launch_layer_norm(cudaStream_t stream, const void *x, const void *scale, con
                 static_cast<uint32_t>(hidden), eps);
 }
 
+// ================================================================================================
+// Softmax{kSoftmax, scale, mask = kBoolean} on f16 rows, the attention-score form the CPU route
+// keeps (src/compute_provider_native/transformer.cc:44-57,228-275):
+//   v = f32(x) * scale;  v = -inf where the mask byte is 0;  y = f16_rne(softmax_f32(v))
+// with softmax_f32 as in src/simd/math/activations.cc:301-317 (f32 exp of v - max, multiply by
+// float(1 / sum); a row with NaN or +inf, or with every element masked, is all NaN).
+// One CTA per row; the row stays in registers (16 values per thread) up to 4096 columns and is
+// re-read from L1/L2 beyond that.  The mask has the tensor's shape or repeats over the leading
+// axes with a period that is a multiple of the row length.
+// ================================================================================================
+constexpr int kScoreSlots = 16;
+
+__global__ void __launch_bounds__(kThreads)
+masked_softmax_f16_kernel(const unsigned short *x, const unsigned char *__restrict__ mask, unsigned short *y, uint64_t rows,
+                          uint32_t cols, uint64_t mask_rows, float scale) {
+  grid_dependency_sync();
+  __shared__ float s_part[2][kWarps];
+  const int t = threadIdx.x, lane = t & 31, warp = t >> 5;
+  const bool resident = cols <= kThreads * kScoreSlots;
+  auto value_at = [&](const unsigned short *row, const unsigned char *row_mask, uint32_t i) {
+    const float v = __fmul_rn(f16_to_f32(row[i]), scale);
+    return row_mask[i] == 0 ? -CUDART_INF_F : v;
+  };
+  auto cta_reduce = [&](float v, int slot, bool maximum) {
+    v = maximum ? warp_max_nan(v) : warp_sum(v);
+    if (lane == 0) s_part[slot][warp] = v;
+    __syncthreads();
+    float total = s_part[slot][0];
+#pragma unroll
+    for (int w = 1; w < kWarps; ++w) total = maximum ? max_nan(total, s_part[slot][w]) : __fadd_rn(total, s_part[slot][w]);
+    return total;
+  };
+  for (uint64_t row = blockIdx.x; row < rows; row += gridDim.x) {
+    const unsigned short *in = x + row * cols;
+    const unsigned char *row_mask = mask + (row % mask_rows) * cols;
+    unsigned short *out = y + row * cols;
+    float v[kScoreSlots];
+    float peak = -CUDART_INF_F;
+    if (resident) {
+#pragma unroll
+      for (int k = 0; k < kScoreSlots; ++k) {
+        const uint32_t i = k * kThreads + t;
+        v[k] = i < cols ? value_at(in, row_mask, i) : -CUDART_INF_F;
+        peak = max_nan(peak, v[k]);
+      }
+    } else {
+      for (uint32_t i = t; i < cols; i += kThreads) peak = max_nan(peak, value_at(in, row_mask, i));
+    }
+    peak = cta_reduce(peak, 0, true);
+    const bool valid = peak > -CUDART_INF_F && peak < CUDART_INF_F;  // false for NaN too
+    float sum = 0.0f;
+    if (resident) {
+#pragma unroll
+      for (int k = 0; k < kScoreSlots; ++k) {
+        v[k] = expf(v[k] - peak);  // exp(-inf) = 0 for masked and padding slots
+        sum += v[k];
+      }
+    } else {
+      for (uint32_t i = t; i < cols; i += kThreads) sum += expf(value_at(in, row_mask, i) - peak);
+    }
+    sum = cta_reduce(sum, 1, false);
+    const float inverse = valid ? __fdiv_rn(1.0f, sum) : CUDART_NAN_F;
+    if (resident) {
+#pragma unroll
+      for (int k = 0; k < kScoreSlots; ++k) {
+        const uint32_t i = k * kThreads + t;
+        if (i < cols) out[i] = f32_to_f16(valid ? __fmul_rn(v[k], inverse) : CUDART_NAN_F);
+      }
+    } else {
+      for (uint32_t i = t; i < cols; i += kThreads)
+        out[i] = f32_to_f16(valid ? __fmul_rn(expf(value_at(in, row_mask, i) - peak), inverse) : CUDART_NAN_F);
+    }
+    __syncthreads();  // the partial slots are rewritten by the next row
+  }
+}
+
 }  // namespace
 }  // namespace hb
 
@@ -562,4 +638,17 @@ extern "C" int hyle_b200_layer_norm_bf16(hyle_b200_stream_t stream, const void *
   auto s = reinterpret_cast<cudaStream_t>(stream);
   if (scale == nullptr) return launch_layer_norm<false>(s, x, nullptr, nullptr, y, rows, hidden, epsilon);
   return launch_layer_norm<true>(s, x, scale, bias, y, rows, hidden, epsilon);
+}
+
+extern "C" int hyle_b200_masked_softmax_f16(hyle_b200_stream_t stream, const void *in, const unsigned char *mask,
+                                            uint64_t mask_count, float scale, void *out, uint64_t rows,
+                                            uint64_t cols) {
+  if (rows == 0 || cols == 0) return HYLE_B200_OK;
+  if (in == nullptr || mask == nullptr || out == nullptr || cols > 0x7fffffffull || mask_count == 0 ||
+      mask_count % cols != 0 || (rows * cols) % mask_count != 0 || !aligned_to(in, 2) || !aligned_to(out, 2))
+    return HYLE_B200_INVALID_VALUE;
+  const unsigned grid = clamp_grid(rows, static_cast<uint64_t>(sm_count()) * 8);
+  return launch(masked_softmax_f16_kernel, dim3(grid), dim3(kThreads), 0, reinterpret_cast<cudaStream_t>(stream),
+                static_cast<const unsigned short *>(in), mask, static_cast<unsigned short *>(out), rows,
+                static_cast<uint32_t>(cols), mask_count / cols, scale);
 }

@@ -414,3 +414,16 @@ def select(condition: torch.Tensor, when_true: torch.Tensor, when_false: torch.T
         _stream(), code, condition.data_ptr(), when_true.data_ptr(), when_false.data_ptr(), out.data_ptr(),
         condition.numel(), max(when_true.numel(), 1), max(when_false.numel(), 1)))
     return out
+
+
+def masked_softmax_f16(x: torch.Tensor, mask: torch.Tensor, scale: float = 1.0) -> torch.Tensor:
+    """Softmax{scale, Boolean mask} over the last axis of an f16 tensor; the mask (one byte per element) has
+    x's shape or its trailing axes including the last one."""
+    _device_tensor(x, "x"), _device_tensor(mask, "mask")
+    if x.dtype != torch.float16 or mask.element_size() != 1:
+        raise ValueError("masked_softmax_f16 takes f16 values and a one-byte mask")
+    cols = x.shape[-1]
+    out = torch.empty_like(x)
+    abi.check("hyle_b200_masked_softmax_f16", abi.load().hyle_b200_masked_softmax_f16(
+        _stream(), x.data_ptr(), mask.data_ptr(), mask.numel(), scale, out.data_ptr(), x.numel() // cols if cols else 0, cols))
+    return out

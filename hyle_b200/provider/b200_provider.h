@@ -36,7 +36,7 @@ inline constexpr ProviderRuntimeProperties kRuntime{.replay_class = ProviderRepl
                                                     .capture_compatible = true};
 
 enum class Entry : std::uint8_t {
-  kUnary, kBinary, kSelect, kReduceRows, kRmsNorm, kLayerNorm, kSwiglu, kSoftmax, kCast, kArgmax, kQ8Encode, kFp8Encode, kRandomBits, kCategorical,
+  kUnary, kBinary, kSelect, kReduceRows, kRmsNorm, kLayerNorm, kSwiglu, kSoftmax, kMaskedSoftmax, kCast, kArgmax, kQ8Encode, kFp8Encode, kRandomBits, kCategorical,
   kAddRmsNorm, kBiasRowSumMax, kLogitsReduce, kQ8Roundtrip
 };
 
@@ -51,7 +51,7 @@ struct Plan final {
   std::uint64_t cols = 0;
   std::uint64_t rhs_period = 0;
   std::uint64_t gate_stride = 0, up_stride = 0, up_offset = 0;  // SwiGLU layouts, in elements
-  float epsilon = 0.0F;    // norm epsilon, or the scale of CacheStorage::float8
+  float epsilon = 0.0F;    // norm epsilon, the scale of CacheStorage::float8, or the Softmax scale
   bool has_weight = false;
   std::size_t workspace_bytes = 0;
 };
@@ -224,6 +224,20 @@ inline std::optional<Plan> match(const Operation &op, std::span<const TensorDesc
     }
     return p;
   }
+  if (const auto *masked = op.get_if<Softmax>(); masked != nullptr && masked->mask == MaskKind::kBoolean) {
+    // the attention-score form: f16 values, Bool mask of the same shape or of its trailing axes
+    // (last axis included), any scale, f32 accumulation
+    if (in.size() != 2 || out.size() != 1 || in[0].data_type() != DataType::kFloat16 || out[0] != in[0] ||
+        in[1].data_type() != DataType::kBool || masked->kind != SoftmaxKind::kSoftmax || in[0].rank() == 0 ||
+        in[1].rank() == 0 || !trailing_axes(in[0], in[1]) ||
+        (masked->axis != -1 && masked->axis != static_cast<std::int32_t>(in[0].rank()) - 1) ||
+        (masked->accumulation_type != DataType::kUnknown && masked->accumulation_type != DataType::kFloat32))
+      return std::nullopt;
+    p.entry = Entry::kMaskedSoftmax;
+    p.epsilon = masked->scale;
+    p.rhs_period = elements(in[1]);
+    return p;
+  }
   if (const auto *softmax = op.get_if<Softmax>()) {
     if (in.size() != 1 || out.size() != 1 || in[0].data_type() != DataType::kFloat32 || out[0] != in[0] ||
         softmax->scale != 1.0F || softmax->mask != MaskKind::kNone || in[0].rank() == 0 ||
@@ -351,6 +365,9 @@ inline int launch(const Plan &p, hyle_b200_stream_t stream, const void *const *i
     case Entry::kSoftmax:
       return hyle_b200_softmax_f32(stream, p.kind, static_cast<const float *>(in[0]), static_cast<float *>(out[0]),
                                    p.rows, p.cols, workspace, p.workspace_bytes);
+    case Entry::kMaskedSoftmax:
+      return hyle_b200_masked_softmax_f16(stream, in[0], static_cast<const unsigned char *>(in[1]), p.rhs_period, p.epsilon,
+                                          out[0], p.rows, p.cols);
     case Entry::kCast:
       return hyle_b200_cast(stream, p.dtype, p.to_dtype, in[0], out[0], p.count);
     case Entry::kArgmax:

@@ -155,7 +155,13 @@ int main() {
     const std::array out{logits};
     check(taken(*context, Operation(Softmax{}), in, out), "Softmax{axis=-1} f32");
     check(taken(*context, Operation(Softmax{.kind = SoftmaxKind::kLogSoftmax}), in, out), "Softmax{kLogSoftmax} f32");
-    check(!taken(*context, Operation(Softmax{.scale = 0.5F}), in, out), "scaled Softmax not taken");
+    check(!taken(*context, Operation(Softmax{.scale = 0.5F}), in, out), "scaled f32 Softmax without a mask not taken");
+    const auto scores = dense(DataType::kFloat16, {8, 128, 1024});
+    const auto keep = dense(DataType::kBool, {128, 1024});
+    const std::array masked_in{scores, keep};
+    const std::array masked_out{scores};
+    check(taken(*context, Operation(Softmax{.scale = 0.125F, .mask = MaskKind::kBoolean}), masked_in, masked_out),
+          "Softmax{scale, Boolean mask} f16 [8,128,1024] with mask [128,1024]");
     const std::array cast_out{probs16};
     check(taken(*context, Operation(Cast{DataType::kBFloat16}), in, cast_out), "Cast{f32 -> bf16}");
     const std::array fp8_out{dense(DataType::kFloat8E4M3FN, {16, 151936})};

@@ -43,7 +43,7 @@ extern "C" {
 /* Same object as cudaStream_t; spelled out so C callers need no CUDA header. */
 typedef struct CUstream_st *hyle_b200_stream_t;
 
-#define HYLE_B200_ABI_VERSION 9
+#define HYLE_B200_ABI_VERSION 10
 
 enum hyle_b200_result {
   HYLE_B200_OK = 0,
@@ -272,6 +272,17 @@ HYLE_B200_API int hyle_b200_cast(hyle_b200_stream_t stream, int source_dtype, in
 HYLE_B200_API int hyle_b200_select(hyle_b200_stream_t stream, int dtype, const void *condition,
                                    const void *when_true, const void *when_false, void *out,
                                    uint64_t count, uint64_t true_period, uint64_t false_period);
+
+/* Softmax{axis=-1, kSoftmax, scale, mask=kBoolean} on f16 rows, f32 accumulation: the masked, scaled
+ * form of the CPU route (src/compute_provider_native/transformer.cc:44-57,228-275):
+ *   v = f32(in) * scale;  v = -inf where the mask byte is 0;  out = f16_rne(softmax(v)).
+ * mask: one byte per element, mask_count elements repeating over the leading axes (mask_count is a
+ * multiple of cols and divides rows * cols; rows * cols = the tensor's own shape).  A row with NaN
+ * or +inf, or with every element masked, is all NaN.  Results within one f16 step of the CPU route. */
+HYLE_B200_API int hyle_b200_masked_softmax_f16(hyle_b200_stream_t stream, const void *in,
+                                               const unsigned char *mask, uint64_t mask_count,
+                                               float scale, void *out, uint64_t rows,
+                                               uint64_t cols);
 
 /* Cast{f32 -> bf16}, round to nearest even (include/hyle/simd/dtype.h:114-121). */
 HYLE_B200_API int hyle_b200_cast_f32_to_bf16(hyle_b200_stream_t stream, const float *in,

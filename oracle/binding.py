@@ -161,6 +161,17 @@ class Oracle:
         invalid = self.lib.hyle_oracle_categorical(dtype, _ptr(logits), _ptr(identities), rows, cols, _ptr(index), _ptr(logp), _ptr(uniform))
         return index, logp, uniform, int(invalid)
 
+    def masked_softmax_f16(self, x16, mask, scale):
+        """Softmax{scale, Boolean mask} on f16 rows (src/compute_provider_native/transformer.cc:44-57): f32 value times
+        scale, -inf where the mask byte is 0, the pinned f32 softmax, one rounding to f16.  Returns (f16 words, f32)."""
+        x16 = _c(x16, np.uint16)
+        values = x16.view(np.float16).astype(np.float32) * np.float32(scale)
+        values = np.where(np.broadcast_to(np.asarray(mask) != 0, values.shape), values, np.float32(-np.inf)).astype(np.float32)
+        shape = values.shape
+        y = self.softmax(values.reshape(-1, shape[-1])).reshape(shape)
+        with np.errstate(all="ignore"):
+            return y.astype(np.float16).view(np.uint16), y
+
     def reduce_rows(self, kind, x):
         x = _c(x, np.float32)
         rows, cols = x.shape

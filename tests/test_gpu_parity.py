@@ -663,6 +663,33 @@ def test_select_moves_bits(dtype):
     assert torch.equal(ops.select(flat_c, flat_a, flat_b).view(raw), want.reshape(-1)[3:2000])
 
 
+@pytest.mark.parametrize("cols", [1, 7, 128, 1000, 4096, 5000])
+def test_masked_scaled_softmax_f16(oracle, cols):
+    rng = np.random.default_rng(cols)
+    heads, queries = 3, 17
+    x = (4.0 * rng.standard_normal((heads, queries, cols))).astype(np.float16)
+    mask = (rng.random((queries, cols)) < 0.7).astype(np.uint8)          # shared by the heads
+    mask[:, 0] = 1
+    if cols > 1:
+        mask[3, :] = 0                                                    # a fully masked row: all NaN
+        x[1, 5, cols // 2] = np.nan; mask[5, cols // 2] = 1
+        mask[6, :] = 0; mask[6, cols - 1] = 7                             # any non-zero byte is true
+    for scale in (1.0, 0.125):
+        want16, want32 = oracle.masked_softmax_f16(x.view(np.uint16), mask[None], scale)
+        got = ops.masked_softmax_f16(to_dev(x), to_dev(mask), scale).cpu().numpy().view(np.uint16)
+        nan = (want16 & 0x7FFF) > 0x7C00
+        assert np.array_equal((got & 0x7FFF) > 0x7C00, nan)
+        distance = np.abs(ordered16(got[~nan]) - ordered16(want16[~nan]))
+        assert distance.max(initial=0) <= 1 and (distance != 0).mean() < 2e-2
+    # a mask of the tensor's own shape
+    full = (rng.random(x.shape) < 0.5).astype(np.uint8); full[..., 0] = 1
+    want16, _ = oracle.masked_softmax_f16(x.view(np.uint16), full, 0.5)
+    got = ops.masked_softmax_f16(to_dev(x), to_dev(full), 0.5).cpu().numpy().view(np.uint16)
+    nan = (want16 & 0x7FFF) > 0x7C00
+    assert np.array_equal((got & 0x7FFF) > 0x7C00, nan)
+    assert np.abs(ordered16(got[~nan]) - ordered16(want16[~nan])).max(initial=0) <= 1
+
+
 def test_cast_rejects_other_pairs():
     x = torch.zeros(16, device=DEV)
     with pytest.raises(abi.KernelError):

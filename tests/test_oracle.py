@@ -235,6 +235,19 @@ def test_fp8_cache_encode_rules(oracle, ref_floor):
     assert status == 4 and codes[5] == 0 and codes[9] == 0
 
 
+def test_masked_scaled_softmax_rules(oracle):
+    rng = np.random.default_rng(12)
+    x = (3.0 * rng.standard_normal((2, 5, 64))).astype(np.float16)
+    mask = np.ones((5, 64), np.uint8); mask[1, 10:] = 0; mask[2, :] = 0; mask[3, 7] = 0
+    words, values = oracle.masked_softmax_f16(x.view(np.uint16), mask[None], 0.25)
+    assert np.all(values[:, 1, 10:] == 0) and np.allclose(values[:, 1].sum(axis=-1), 1.0, atol=1e-6)
+    assert np.all(np.isnan(values[:, 2]))                       # every element masked: the row is invalid
+    assert np.all(values[:, 3, 7] == 0)
+    ref = np.exp(0.25 * x[0, 0].astype(np.float64)); ref /= ref.sum()
+    assert np.allclose(values[0, 0], ref, rtol=1e-5)
+    assert np.array_equal(words, values.astype(np.float16).view(np.uint16)) or np.isnan(values).any()
+
+
 # ---- sampling ----------------------------------------------------------------------------------------------------------------
 def test_random_bits_match_reference_generator(oracle, golden):
     identities = golden["random_identities"]
