@@ -323,6 +323,20 @@ def other_ops(torch, peak_gbs, only=None, iterations=40):
         report("categorical_f32", "256x151936", rows * cols, rows * cols * 4, ms, 2)
         del logits
 
+    # Paged append: 4096 new Q8_0 rows of 8192 values (8704 bytes) into 256 pages of 16 rows
+    if wanted("paged_append"):
+        sets, page_rows, pages, new_count, row_bytes = 4, 16, 1024, 4096, 8704
+        arenas = [torch.zeros(pages * page_rows, row_bytes, dtype=torch.uint8, device=dev) for _ in range(sets)]
+        fresh = [torch.randint(0, 256, (new_count, row_bytes), dtype=torch.uint8, device=dev) for _ in range(sets)]
+        order = torch.randperm(pages)[: new_count // page_rows].tolist()
+        episode = ops.paged_append_metadata([(0, 0, i * page_rows, page, 0, page_rows) for i, page in enumerate(order)],
+                                            new_count // page_rows, dev)
+        ms = time_op(torch, lambda i: lib.hyle_b200_paged_append(
+            stream, arenas[i].data_ptr(), fresh[i].data_ptr(), episode.data_ptr(), page_rows, pages, new_count,
+            new_count // page_rows, row_bytes), sets, iterations)
+        report("paged_append", "4096 rows x 8704 B into 16-row pages", new_count, 2 * new_count * row_bytes, ms, sets)
+        del arenas, fresh
+
     # 4: f32 logits -> lse, softmax bf16, argmax, B = 256, vocabulary 151936
     if wanted("logits_reduce_f32"):
         sets = 4

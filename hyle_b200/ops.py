@@ -10,6 +10,7 @@ from __future__ import annotations
 
 from typing import Optional, Tuple
 
+import numpy as np
 import torch
 
 from . import abi
@@ -273,6 +274,52 @@ def fp8_e4m3_encode(x: torch.Tensor, scale: float, status: Optional[torch.Tensor
     abi.check("hyle_b200_fp8_e4m3_encode", abi.load().hyle_b200_fp8_e4m3_encode(
         _stream(), _DTYPE[x.dtype], x.data_ptr(), x.numel(), scale, out.data_ptr(), _ptr(status)))
     return out
+
+
+def paged_append_metadata(instructions, capacity: int, device=None) -> torch.Tensor:
+    """Pack an episode for :func:`paged_append`: int32 words {active_count, 0, 0, 0} followed by
+    ``capacity`` instructions of {source_kind, source_page, source_row, destination_page,
+    destination_row, rows, 0, 0} (include/hyle/compute/detail/paged_append_wire.h:11-25).
+    ``instructions`` is a sequence of 6-tuples in that order; unused slots are zero."""
+    if len(instructions) > capacity:
+        raise ValueError("more instructions than the episode's capacity")
+    words = np.zeros(4 + 8 * capacity, dtype=np.uint32)
+    words[0] = len(instructions)
+    for slot, fields in enumerate(instructions):
+        if len(fields) != 6:
+            raise ValueError("an instruction has six fields")
+        words[4 + 8 * slot: 4 + 8 * slot + 6] = [int(f) & 0xFFFFFFFF for f in fields]
+    packed = torch.from_numpy(words.view(np.int32))
+    return packed.to(device) if device is not None else packed
+
+
+def paged_append(arena: torch.Tensor, new_rows: Optional[torch.Tensor], metadata: torch.Tensor, page_rows: int,
+                 capacity: Optional[int] = None) -> torch.Tensor:
+    """Move rows into the pages of ``arena`` [physical_pages * page_rows, row...] in place, as the device
+    resident episode ``metadata`` says (see :func:`paged_append_metadata`); ``new_rows`` [input_rows, row...]
+    holds the packed rows of source kind 0 and may be None.  Malformed instructions are skipped, a
+    malformed episode does nothing (src/compute_backend_cuda/cuda_paged_append.cu:16-45)."""
+    _device_tensor(arena, "arena")
+    _device_tensor(metadata, "metadata")
+    if not arena.is_contiguous() or arena.dim() < 2 or arena.shape[0] % page_rows:
+        raise ValueError("arena must be contiguous [physical_pages * page_rows, row...]")
+    if metadata.dtype != torch.int32 or metadata.dim() != 1 or (metadata.numel() - 4) % 8 or metadata.numel() < 4:
+        raise ValueError("metadata must be int32 words: 4 of header + 8 per instruction")
+    row_bytes = arena[0].numel() * arena.element_size()
+    input_rows = 0
+    if new_rows is not None:
+        _device_tensor(new_rows, "new_rows")
+        if not new_rows.is_contiguous() or new_rows.numel() == 0 or new_rows[0].numel() * new_rows.element_size() != row_bytes:
+            raise ValueError("new_rows must be contiguous rows of the arena's row size")
+        input_rows = new_rows.shape[0]
+    if capacity is None:
+        capacity = (metadata.numel() - 4) // 8
+    elif capacity > (metadata.numel() - 4) // 8:
+        raise ValueError("capacity exceeds the metadata buffer")
+    abi.check("hyle_b200_paged_append", abi.load().hyle_b200_paged_append(
+        _stream(), arena.data_ptr(), _ptr(new_rows), metadata.data_ptr(), page_rows, arena.shape[0] // page_rows,
+        input_rows, capacity, row_bytes))
+    return arena
 
 
 def cast_f32_to_bf16(x: torch.Tensor) -> torch.Tensor:

@@ -18,6 +18,7 @@
 
 #include <hyle/compute/sampling_ops.h>
 
+#include "b200_paged_append.h"
 #include "b200_provider.h"
 
 using namespace hyle::compute;
@@ -227,6 +228,20 @@ int main() {
     check(draw.infer_output_descriptions(draw_in, draw_out).ok() &&
               taken(*context, Operation::custom(draw), draw_in, draw_out),
           "sampling_ops::Categorical{log probability} f32");
+  }
+  {  // paged append: the launcher shaped like the CUDA backend's own, host-side argument rules only
+    detail::PagedAppendNativeSpec spec{16, 64, 32, 0, 8704};
+    check(b200::launch_paged_append(nullptr, nullptr, nullptr, spec, nullptr) == HYLE_B200_OK,
+          "paged append: an episode of capacity 0 is nothing to launch");
+    spec.instruction_capacity = 8;
+    alignas(16) static unsigned char arena[16], rows[16], words[16 + 8 * 32];
+    spec.row_bytes = 8703;
+    check(b200::launch_paged_append(arena, rows, words, spec, nullptr) == HYLE_B200_INVALID_VALUE,
+          "paged append: rows are whole 16-bit elements, as prepare_append demands");
+    spec.row_bytes = 8704;
+    spec.page_rows = 0;
+    check(b200::launch_paged_append(arena, rows, words, spec, nullptr) == HYLE_B200_INVALID_VALUE,
+          "paged append: empty pages are refused");
   }
   std::printf("%d failure(s)\n", failures);
   return failures == 0 ? 0 : 1;

@@ -43,7 +43,7 @@ extern "C" {
 /* Same object as cudaStream_t; spelled out so C callers need no CUDA header. */
 typedef struct CUstream_st *hyle_b200_stream_t;
 
-#define HYLE_B200_ABI_VERSION 10
+#define HYLE_B200_ABI_VERSION 11
 
 enum hyle_b200_result {
   HYLE_B200_OK = 0,
@@ -317,6 +317,26 @@ HYLE_B200_API int hyle_b200_q8_0_decode_bf16(hyle_b200_stream_t stream, const vo
 HYLE_B200_API int hyle_b200_fp8_e4m3_encode(hyle_b200_stream_t stream, int dtype, const void *in,
                                             uint64_t count, float scale, void *out,
                                             uint32_t *status_word);
+
+/* Paged append: the row mover behind the paged KV cache's append / copy step, the consumer of the
+ * rows CacheEncode wrote (launch_paged_append, src/compute_backend_cuda/cuda_paged_append.cu:66-81;
+ * wire structs include/hyle/compute/detail/paged_append_wire.h:11-34).  All in device memory:
+ *   metadata = {u32 active_count, 0, 0, 0} followed by instruction_capacity instructions of
+ *              {u32 source_kind, source_page, source_row, destination_page, destination_row, rows, 0, 0};
+ *   source_kind 0 copies `rows` rows from row source_row of input_rows_data (input_rows packed rows),
+ *   source_kind 1 from (source_page, source_row) of the arena itself; the destination is row
+ *   destination_page * page_rows + destination_row of the arena (physical_pages * page_rows rows).
+ * Rows are row_bytes bytes (even), moved bit for bit.  As in the reference kernel
+ * (cuda_paged_append.cu:16-45) an episode with active_count > instruction_capacity or non-zero
+ * reserved words does nothing, and an instruction with non-zero reserved words, rows == 0, another
+ * source kind, or a coordinate outside the arena or the input is skipped.  Instructions of one episode
+ * must not write a range another of them reads or writes.  The launch shape depends on the capacities
+ * only, so the call can be captured in a CUDA graph and replayed with new metadata contents. */
+HYLE_B200_API int hyle_b200_paged_append(hyle_b200_stream_t stream, void *arena,
+                                         const void *input_rows_data, const void *metadata,
+                                         uint32_t page_rows, uint32_t physical_pages,
+                                         uint32_t input_rows, uint32_t instruction_capacity,
+                                         uint64_t row_bytes);
 
 /* Scratch for the two kernels below, for a tensor of `count` values: a header (ticket and tile
  * counters), per-CTA partial sums, and for the fused round trip one f64 per tile of 8192 values

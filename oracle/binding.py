@@ -16,6 +16,7 @@ import numpy as np
 ORACLE_DIR = os.path.dirname(os.path.abspath(__file__))
 ORACLE_LIB = os.path.join(ORACLE_DIR, "libhyle_oracle.so")
 REF_LIB = os.path.join(ORACLE_DIR, "_ref", "libhyle_ref_floor.so")
+REF_PAGED_LIB = os.path.join(ORACLE_DIR, "_ref", "libhyle_ref_paged.so")
 
 F32, BF16, F16 = 0, 1, 2
 ADD, MULTIPLY, SUBTRACT, DIVIDE, NUMBER_MINIMUM, NUMBER_MAXIMUM = 0, 1, 2, 3, 4, 5  # Binary kinds
@@ -69,6 +70,9 @@ class Oracle:
         L.hyle_oracle_categorical.restype = _u64
         L.hyle_oracle_fp8_e4m3_encode.argtypes = [_i, _vp, _u64, _f, _vp]
         L.hyle_oracle_fp8_e4m3_encode.restype = ctypes.c_uint32
+        _u32 = ctypes.c_uint32
+        L.hyle_oracle_paged_append.argtypes = [_vp, _vp, _vp, _u32, _u32, _u32, _u32, _u64]
+        L.hyle_oracle_paged_append.restype = None
         for name in ("e4m3", "e5m2"):
             getattr(L, f"hyle_oracle_f32_to_{name}").argtypes = [_f]
             getattr(L, f"hyle_oracle_f32_to_{name}").restype = ctypes.c_uint8
@@ -144,6 +148,15 @@ class Oracle:
         out = np.empty(x.shape, np.uint8)
         status = self.lib.hyle_oracle_fp8_e4m3_encode(dtype, _ptr(x), x.size, scale, _ptr(out))
         return out, int(status)
+
+    def paged_append(self, arena, new_rows, words, page_rows):
+        """Returns the arena [pages * page_rows, row bytes] (uint8) after the episode ``words`` (uint32)."""
+        arena = np.array(arena, dtype=np.uint8, order="C", copy=True)
+        new_rows = _c(new_rows, np.uint8) if new_rows is not None else np.zeros((0, arena.shape[1]), np.uint8)
+        words = _c(words, np.uint32)
+        self.lib.hyle_oracle_paged_append(_ptr(arena), _ptr(new_rows), _ptr(words), page_rows, arena.shape[0] // page_rows,
+                                          new_rows.shape[0], (words.size - 4) // 8, arena.shape[1])
+        return arena
 
     def random_bits(self, identities, words):
         identities = _c(identities, np.uint32)
@@ -366,3 +379,23 @@ class RefFloor:
         index, value = np.empty(rows, np.int32), np.empty(rows, np.float32)
         self.lib.hyle_ref_argmax_f32(_ptr(x), _ptr(index), _ptr(value), rows, cols)
         return index, value
+
+
+class RefPaged:
+    """The reference's own paged-append CUDA kernel (oracle/_ref/libhyle_ref_paged.so, built from the
+    reference tree behind ref_paged_shim.cu).  Takes DEVICE pointers; only GPU parity tests use it."""
+
+    @staticmethod
+    def available() -> bool:
+        return os.path.exists(REF_PAGED_LIB)
+
+    def __init__(self):
+        self.lib = ctypes.CDLL(REF_PAGED_LIB)
+        _u32 = ctypes.c_uint32
+        self.lib.hyle_ref_paged_append.argtypes = [_vp, _vp, _vp, _vp, _u32, _u32, _u32, _u32, _u64]
+        self.lib.hyle_ref_paged_append.restype = _i
+
+    def paged_append(self, stream, arena_ptr, rows_ptr, metadata_ptr, page_rows, physical_pages, input_rows, capacity,
+                     row_bytes) -> int:
+        return self.lib.hyle_ref_paged_append(stream, arena_ptr, rows_ptr, metadata_ptr, page_rows, physical_pages,
+                                              input_rows, capacity, row_bytes)

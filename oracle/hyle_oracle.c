@@ -413,6 +413,33 @@ ORACLE_API uint32_t hyle_oracle_fp8_e4m3_encode(int dtype, const void *in, uint6
   return status;
 }
 
+/* ---- paged append (KV cache row mover) ---------------------------------------------------------
+ * src/compute_backend_cuda/cuda_paged_append.cu:11-62 on the wire structs of
+ * include/hyle/compute/detail/paged_append_wire.h:11-34.  words = {active_count, 0, 0, 0} then
+ * capacity x {source_kind, source_page, source_row, destination_page, destination_row, rows, 0, 0}.
+ * Instructions run in order here; an episode's ranges are disjoint, so the order cannot matter. */
+ORACLE_API void hyle_oracle_paged_append(uint8_t *arena, const uint8_t *input, const uint32_t *words, uint32_t page_rows,
+                                         uint32_t physical_pages, uint32_t input_rows, uint32_t capacity,
+                                         uint64_t row_bytes) {
+  const uint32_t active = words[0];
+  if (active > capacity || words[1] != 0 || words[2] != 0 || words[3] != 0) return;
+  for (uint32_t i = 0; i < active; ++i) {
+    const uint32_t *in = words + 4 + 8 * (uint64_t)i;
+    const uint32_t kind = in[0], source_page = in[1], source_row = in[2], page = in[3], row = in[4], rows = in[5];
+    if (in[6] != 0 || in[7] != 0 || rows == 0 || kind > 1) continue;
+    if (page >= physical_pages || row > page_rows || rows > page_rows - row) continue;
+    const uint8_t *source;
+    if (kind == 0) {
+      if (source_row > input_rows || rows > input_rows - source_row) continue;
+      source = input + (uint64_t)source_row * row_bytes;
+    } else {
+      if (source_page >= physical_pages || source_row > page_rows || rows > page_rows - source_row) continue;
+      source = arena + ((uint64_t)source_page * page_rows + source_row) * row_bytes;
+    }
+    memmove(arena + ((uint64_t)page * page_rows + row) * row_bytes, source, (uint64_t)rows * row_bytes);
+  }
+}
+
 /* ---- sampling_ops::RandomBits / Categorical ---------------------------------------------------
  * Philox-4x32-10 (Salmon, Moraes, Dror, Shaw 2011) keyed as the CPU route keys it
  * (src/compute_provider_native/sampling.cc:76-88): key = identity[0..1], counter = (index low,
