@@ -335,6 +335,30 @@ def other_ops(torch, peak_gbs, only=None, iterations=40):
             stream, arenas[i].data_ptr(), fresh[i].data_ptr(), episode.data_ptr(), page_rows, pages, new_count,
             new_count // page_rows, row_bytes), sets, iterations)
         report("paged_append", "4096 rows x 8704 B into 16-row pages", new_count, 2 * new_count * row_bytes, ms, sets)
+        # the same rows through the device-lengths variant: 32 requests of 128 new rows after 24 old ones
+        requests, per_request, history = 32, new_count // 32, 24
+        words = np.zeros(4 + 8 * (1 + requests + 320), dtype=np.uint32)
+        spare = torch.randperm(pages // 2).tolist()
+        records = []
+        for r in range(requests):
+            words[12 + 8 * r: 16 + 8 * r] = (per_request, history, history, history + per_request)
+            for logical in range(history // page_rows, (history + per_request - 1) // page_rows + 1):
+                inherited = max(0, min(page_rows, history - logical * page_rows))
+                records.append((r, logical, spare.pop(), page_rows, pages // 2 + r if inherited else 0xFFFFFFFF, inherited))
+        words[0], words[4], words[5] = 1 + requests + len(records), requests, len(records)
+        for i, record in enumerate(records):
+            words[12 + 8 * (requests + i): 18 + 8 * (requests + i)] = record
+        episode = torch.from_numpy(words.view(np.int32)).to(dev)
+        q = torch.full((requests,), per_request, dtype=torch.int32, device=dev)
+        kv = torch.full((requests,), history + per_request, dtype=torch.int32, device=dev)
+        status = torch.zeros(1, dtype=torch.int32, device=dev)
+        ms = time_op(torch, lambda i: lib.hyle_b200_paged_append_device_lengths(
+            stream, arenas[i].data_ptr(), fresh[i].data_ptr(), episode.data_ptr(), q.data_ptr(), kv.data_ptr(), page_rows,
+            pages, new_count, (words.size - 4) // 8, row_bytes, requests, status.data_ptr()), sets, iterations)
+        assert int(status.item()) == 0
+        moved = sum(record[3] for record in records) * row_bytes  # every initialised row is written once
+        read = (new_count + sum(record[5] for record in records)) * row_bytes
+        report("paged_append_device_lengths", "32 requests x 128 new rows x 8704 B, 16-row pages", new_count, moved + read, ms, sets)
         del arenas, fresh
 
     # 4: f32 logits -> lse, softmax bf16, argmax, B = 256, vocabulary 151936

@@ -322,6 +322,35 @@ def paged_append(arena: torch.Tensor, new_rows: Optional[torch.Tensor], metadata
     return arena
 
 
+def paged_append_device_lengths(arena: torch.Tensor, new_rows: torch.Tensor, metadata: torch.Tensor,
+                                query_lengths: torch.Tensor, kv_lengths: torch.Tensor, page_rows: int,
+                                status: torch.Tensor) -> torch.Tensor:
+    """Paged append whose row ranges are derived on the device from ``query_lengths`` / ``kv_lengths``
+    (int32 [requests]); ``metadata`` is int32 words: 4 of header, then 8 per record (directory, request
+    bounds, dirty pages: include/hyle/compute/detail/device_lengths_paged_append_wire.h:8-24).
+    ``status`` (one int32 word) follows the reference's device status protocol: 0 = ok, 1 = a page
+    record out of range, 4 = inconsistent episode or lengths; nothing is done when it is not 0 on entry."""
+    for name, t in (("arena", arena), ("new_rows", new_rows), ("metadata", metadata), ("query_lengths", query_lengths),
+                    ("kv_lengths", kv_lengths), ("status", status)):
+        _device_tensor(t, name)
+    if not arena.is_contiguous() or arena.dim() < 2 or arena.shape[0] % page_rows:
+        raise ValueError("arena must be contiguous [physical_pages * page_rows, row...]")
+    row_bytes = arena[0].numel() * arena.element_size()
+    if not new_rows.is_contiguous() or new_rows.numel() == 0 or new_rows[0].numel() * new_rows.element_size() != row_bytes:
+        raise ValueError("new_rows must be contiguous rows of the arena's row size")
+    if metadata.dtype != torch.int32 or metadata.dim() != 1 or (metadata.numel() - 4) % 8 or metadata.numel() < 4:
+        raise ValueError("metadata must be int32 words: 4 of header + 8 per record")
+    if query_lengths.dtype != torch.int32 or kv_lengths.dtype != torch.int32 or query_lengths.shape != kv_lengths.shape:
+        raise ValueError("lengths must be int32 tensors of one shape")
+    if status.dtype != torch.int32 or status.numel() != 1:
+        raise ValueError("status is one int32 word")
+    abi.check("hyle_b200_paged_append_device_lengths", abi.load().hyle_b200_paged_append_device_lengths(
+        _stream(), arena.data_ptr(), new_rows.data_ptr(), metadata.data_ptr(), query_lengths.data_ptr(),
+        kv_lengths.data_ptr(), page_rows, arena.shape[0] // page_rows, new_rows.shape[0], (metadata.numel() - 4) // 8,
+        row_bytes, query_lengths.numel(), status.data_ptr()))
+    return arena
+
+
 def cast_f32_to_bf16(x: torch.Tensor) -> torch.Tensor:
     _device_tensor(x, "x")
     if x.dtype != torch.float32:

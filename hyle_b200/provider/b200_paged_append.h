@@ -13,6 +13,7 @@
 
 #include <cstdint>
 
+#include <hyle/compute/detail/device_lengths_paged_append_wire.h>
 #include <hyle/compute/detail/paged_append_wire.h>
 
 #include "hyle_b200.h"
@@ -26,6 +27,20 @@ inline int launch_paged_append(void *arena, const void *rows, const void *metada
                                compute::detail::PagedAppendNativeSpec spec, hyle_b200_stream_t stream) noexcept {
   return hyle_b200_paged_append(stream, arena, rows, metadata, spec.page_rows, spec.physical_pages, spec.input_rows,
                                 spec.instruction_capacity, static_cast<std::uint64_t>(spec.row_bytes));
+}
+
+// The device-lengths variant (launch_device_lengths_paged_append, cuda_paged_append.cu:148-154;
+// called from enqueue_lengths, src/compute_backend_cuda/cuda_paged_append.cc:125-147).  `status` is the
+// queue's device status word with the reference's codes.  HYLE_B200_NOT_SUPPORTED for a domain
+// prepare_lengths declines (cuda_paged_append.cc:112-115).
+inline int launch_device_lengths_paged_append(void *arena, const void *rows, const void *metadata, const void *query_lengths,
+                                              const void *kv_lengths, compute::detail::DeviceLengthsPagedAppendSpec spec,
+                                              unsigned *status, hyle_b200_stream_t stream) noexcept {
+  return hyle_b200_paged_append_device_lengths(
+      stream, arena, rows, metadata, static_cast<const std::int32_t *>(query_lengths),
+      static_cast<const std::int32_t *>(kv_lengths), spec.storage.page_rows, spec.storage.physical_pages,
+      spec.storage.input_rows, spec.storage.instruction_capacity, static_cast<std::uint64_t>(spec.storage.row_bytes),
+      spec.requests, status);
 }
 
 }  // namespace hyle::compute::b200

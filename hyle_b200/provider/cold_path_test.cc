@@ -242,6 +242,15 @@ int main() {
     spec.page_rows = 0;
     check(b200::launch_paged_append(arena, rows, words, spec, nullptr) == HYLE_B200_INVALID_VALUE,
           "paged append: empty pages are refused");
+    detail::DeviceLengthsPagedAppendSpec lengths{{16, 64, 32, 8, 8704}, 33};
+    unsigned status = 0;
+    check(b200::launch_device_lengths_paged_append(arena, rows, words, words, words, lengths, &status, nullptr) ==
+              HYLE_B200_NOT_SUPPORTED,
+          "device-lengths append: more than 32 requests are outside the qualified domain");
+    lengths.requests = 7;
+    check(b200::launch_device_lengths_paged_append(arena, rows, words, words, words, lengths, &status, nullptr) ==
+              HYLE_B200_NOT_SUPPORTED,
+          "device-lengths append: the capacity must hold the directory, the bounds and one page");
   }
   std::printf("%d failure(s)\n", failures);
   return failures == 0 ? 0 : 1;

@@ -43,7 +43,7 @@ extern "C" {
 /* Same object as cudaStream_t; spelled out so C callers need no CUDA header. */
 typedef struct CUstream_st *hyle_b200_stream_t;
 
-#define HYLE_B200_ABI_VERSION 11
+#define HYLE_B200_ABI_VERSION 12
 
 enum hyle_b200_result {
   HYLE_B200_OK = 0,
@@ -337,6 +337,28 @@ HYLE_B200_API int hyle_b200_paged_append(hyle_b200_stream_t stream, void *arena,
                                          uint32_t page_rows, uint32_t physical_pages,
                                          uint32_t input_rows, uint32_t instruction_capacity,
                                          uint64_t row_bytes);
+
+/* Paged append with device-resident lengths (launch_device_lengths_paged_append,
+ * src/compute_backend_cuda/cuda_paged_append.cu:82-154; records
+ * include/hyle/compute/detail/device_lengths_paged_append_wire.h:8-24).  After the 16-byte header
+ * {active_count, 0, 0, 0} the metadata holds 32-byte records: a directory {requests, pages, 0 x 6},
+ * `requests` bounds {query_rows, minimum_previous_rows, maximum_previous_rows, maximum_kv_rows, 0 x 4}
+ * and `pages` dirty pages {request, logical_page, destination_page, initialized_rows, source_page,
+ * source_rows, 0 x 2}.  With q = query_lengths[r], kv = kv_lengths[r] (i32, device memory), request r
+ * had kv - q rows before and owns the packed new rows [sum of earlier q, + q).  Of a page's
+ * initialized rows, those below kv - q are copied from the beginning of source_page (copy on write),
+ * those below kv come from the request's new rows, the rest are zeroed.
+ * *status_word follows the reference's device status protocol (written only by compare-and-swap from
+ * 0): when it is not 0 on entry nothing is done; an episode whose header, directory, bounds or
+ * lengths are inconsistent does nothing and reports 4 (invalid sequence offsets); a bad page record
+ * is skipped and reports 1 (index out of range) -- which of the OTHER pages are then written is
+ * unspecified, here as in the reference.  requests 1..32, input_rows <= INT32_MAX and
+ * instruction_capacity >= requests + 2, otherwise NOT_SUPPORTED (cuda_paged_append.cc:110-115). */
+HYLE_B200_API int hyle_b200_paged_append_device_lengths(
+    hyle_b200_stream_t stream, void *arena, const void *input_rows_data, const void *metadata,
+    const int32_t *query_lengths, const int32_t *kv_lengths, uint32_t page_rows,
+    uint32_t physical_pages, uint32_t input_rows, uint32_t instruction_capacity, uint64_t row_bytes,
+    uint32_t requests, uint32_t *status_word);
 
 /* Scratch for the two kernels below, for a tensor of `count` values: a header (ticket and tile
  * counters), per-CTA partial sums, and for the fused round trip one f64 per tile of 8192 values

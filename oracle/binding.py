@@ -73,6 +73,8 @@ class Oracle:
         _u32 = ctypes.c_uint32
         L.hyle_oracle_paged_append.argtypes = [_vp, _vp, _vp, _u32, _u32, _u32, _u32, _u64]
         L.hyle_oracle_paged_append.restype = None
+        L.hyle_oracle_paged_append_device_lengths.argtypes = [_vp, _vp, _vp, _vp, _vp, _u32, _u32, _u32, _u32, _u64, _u32, _u32]
+        L.hyle_oracle_paged_append_device_lengths.restype = _u32
         for name in ("e4m3", "e5m2"):
             getattr(L, f"hyle_oracle_f32_to_{name}").argtypes = [_f]
             getattr(L, f"hyle_oracle_f32_to_{name}").restype = ctypes.c_uint8
@@ -157,6 +159,16 @@ class Oracle:
         self.lib.hyle_oracle_paged_append(_ptr(arena), _ptr(new_rows), _ptr(words), page_rows, arena.shape[0] // page_rows,
                                           new_rows.shape[0], (words.size - 4) // 8, arena.shape[1])
         return arena
+
+    def paged_append_device_lengths(self, arena, new_rows, words, query_lengths, kv_lengths, page_rows, status=0):
+        """(arena after the episode, status word after it) for the device-lengths records ``words``."""
+        arena = np.array(arena, dtype=np.uint8, order="C", copy=True)
+        new_rows, words = _c(new_rows, np.uint8), _c(words, np.uint32)
+        q, kv = _c(query_lengths, np.int32), _c(kv_lengths, np.int32)
+        status = self.lib.hyle_oracle_paged_append_device_lengths(
+            _ptr(arena), _ptr(new_rows), _ptr(words), _ptr(q), _ptr(kv), page_rows, arena.shape[0] // page_rows,
+            new_rows.shape[0], (words.size - 4) // 8, arena.shape[1], q.size, status)
+        return arena, int(status)
 
     def random_bits(self, identities, words):
         identities = _c(identities, np.uint32)
@@ -394,8 +406,17 @@ class RefPaged:
         _u32 = ctypes.c_uint32
         self.lib.hyle_ref_paged_append.argtypes = [_vp, _vp, _vp, _vp, _u32, _u32, _u32, _u32, _u64]
         self.lib.hyle_ref_paged_append.restype = _i
+        self.lib.hyle_ref_paged_append_device_lengths.argtypes = [_vp, _vp, _vp, _vp, _vp, _vp, _u32, _u32, _u32, _u32, _u64,
+                                                                  _u32, _vp]
+        self.lib.hyle_ref_paged_append_device_lengths.restype = _i
 
     def paged_append(self, stream, arena_ptr, rows_ptr, metadata_ptr, page_rows, physical_pages, input_rows, capacity,
                      row_bytes) -> int:
         return self.lib.hyle_ref_paged_append(stream, arena_ptr, rows_ptr, metadata_ptr, page_rows, physical_pages,
                                               input_rows, capacity, row_bytes)
+
+    def paged_append_device_lengths(self, stream, arena_ptr, rows_ptr, metadata_ptr, query_ptr, kv_ptr, page_rows,
+                                    physical_pages, input_rows, capacity, row_bytes, requests, status_ptr) -> int:
+        return self.lib.hyle_ref_paged_append_device_lengths(stream, arena_ptr, rows_ptr, metadata_ptr, query_ptr, kv_ptr,
+                                                             page_rows, physical_pages, input_rows, capacity, row_bytes,
+                                                             requests, status_ptr)

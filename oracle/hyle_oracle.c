@@ -440,6 +440,71 @@ ORACLE_API void hyle_oracle_paged_append(uint8_t *arena, const uint8_t *input, c
   }
 }
 
+/* Device-lengths variant: src/compute_backend_cuda/cuda_paged_append.cu:82-146 on the records of
+ * include/hyle/compute/detail/device_lengths_paged_append_wire.h:8-24.  words = header, directory,
+ * `requests` bounds, `pages` page records, 8 words each after the 4-word header.  Returns the status
+ * word after the episode (0 ok, 1 a bad page record, 4 an inconsistent episode); a bad page record is
+ * skipped and the remaining pages are still written (the reference leaves that subset unspecified). */
+ORACLE_API uint32_t hyle_oracle_paged_append_device_lengths(uint8_t *arena, const uint8_t *input, const uint32_t *words,
+                                                            const int32_t *query_lengths, const int32_t *kv_lengths,
+                                                            uint32_t page_rows, uint32_t physical_pages, uint32_t input_rows,
+                                                            uint32_t capacity, uint64_t row_bytes, uint32_t requests,
+                                                            uint32_t status) {
+  if (status != 0) return status;
+  const uint32_t active = words[0];
+  const uint32_t *directory = words + 4;
+  const uint32_t listed = directory[0], pages = directory[1];
+  int valid = !(active == 0 || active > capacity || words[1] || words[2] || words[3] || listed != requests || listed > 32 ||
+                pages > active - 1 || listed > active - 1 - pages);
+  for (int i = 2; i < 8; ++i)
+    if (directory[i]) valid = 0;
+  int32_t offsets[33], previous[32], last[32];
+  offsets[0] = 0;
+  if (valid) {
+    for (uint32_t r = 0; r < requests; ++r) {
+      const uint32_t *b = words + 4 + 8 * (uint64_t)(1 + r);
+      const int32_t q = query_lengths[r], kv = kv_lengths[r];
+      const int64_t old = (int64_t)kv - q, next = (int64_t)offsets[r] + q;
+      if (b[4] || b[5] || b[6] || b[7]) valid = 0;
+      if (q < 0 || (uint32_t)q > b[0] || kv < 0 || (uint32_t)kv > b[3] || old < (int64_t)b[1] || old > (int64_t)b[2] || next < 0 ||
+          next > (int64_t)input_rows) {
+        valid = 0;
+        offsets[r + 1] = previous[r] = last[r] = 0;
+      } else {
+        offsets[r + 1] = (int32_t)next;
+        previous[r] = (int32_t)old;
+        last[r] = kv;
+      }
+    }
+  }
+  if (!valid) return 4;
+  for (uint32_t index = 0; index < pages; ++index) {
+    const uint32_t *p = words + 4 + 8 * (uint64_t)(1 + requests + index);
+    const uint32_t request = p[0], logical_page = p[1], destination_page = p[2], initialized = p[3], source_page = p[4],
+                   source_rows = p[5];
+    if (request >= requests || destination_page >= physical_pages || !initialized || initialized > page_rows ||
+        source_rows > page_rows || p[6] || p[7]) {
+      status = 1;
+      continue;
+    }
+    const uint64_t begin = (uint64_t)logical_page * page_rows, prior = (uint64_t)previous[request], next = (uint64_t)last[request];
+    const uint32_t inherited = begin < prior ? (uint32_t)(initialized < prior - begin ? initialized : prior - begin) : 0u;
+    const uint32_t live = begin < next ? (uint32_t)(initialized < next - begin ? initialized : next - begin) : 0u;
+    const uint32_t added = live - inherited;
+    const uint64_t source_row = added ? (uint64_t)offsets[request] + (begin > prior ? begin : prior) - prior : 0;
+    if (inherited > live || (inherited && (source_page >= physical_pages || inherited > source_rows)) ||
+        (added && (source_row > input_rows || added > input_rows - source_row))) {
+      status = 1;
+      continue;
+    }
+    uint8_t *destination = arena + (uint64_t)destination_page * page_rows * row_bytes;
+    if (inherited) memmove(destination, arena + (uint64_t)source_page * page_rows * row_bytes, (uint64_t)inherited * row_bytes);
+    if (added) memcpy(destination + (uint64_t)inherited * row_bytes, input + source_row * row_bytes, (uint64_t)added * row_bytes);
+    if (initialized > live) memset(destination + (uint64_t)live * row_bytes, 0, (uint64_t)(initialized - live) * row_bytes);
+  }
+  return status;
+}
+
 /* ---- sampling_ops::RandomBits / Categorical ---------------------------------------------------
  * Philox-4x32-10 (Salmon, Moraes, Dror, Shaw 2011) keyed as the CPU route keys it
  * (src/compute_provider_native/sampling.cc:76-88): key = identity[0..1], counter = (index low,

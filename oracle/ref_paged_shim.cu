@@ -20,3 +20,21 @@ extern "C" __attribute__((visibility("default"))) int hyle_ref_paged_append(
   return static_cast<int>(ref::launch_paged_append(ref::paged_append_kernel(), arena, rows, metadata, spec,
                                                    static_cast<cudaStream_t>(stream)));
 }
+
+// The device-lengths variant of the same file (launcher at cuda_paged_append.cu:148-154).
+extern "C" __attribute__((visibility("default"))) int hyle_ref_paged_append_device_lengths(
+    void *stream, void *arena, const void *rows, const void *metadata, const void *query_lengths, const void *kv_lengths,
+    uint32_t page_rows, uint32_t physical_pages, uint32_t input_rows, uint32_t instruction_capacity, uint64_t row_bytes,
+    uint32_t requests, unsigned *status) {
+  hyle::compute::detail::DeviceLengthsPagedAppendSpec spec{};
+  spec.storage.page_rows = page_rows;
+  spec.storage.physical_pages = physical_pages;
+  spec.storage.input_rows = input_rows;
+  spec.storage.instruction_capacity = instruction_capacity;
+  spec.storage.row_bytes = static_cast<std::size_t>(row_bytes);
+  spec.requests = requests;
+  namespace ref = hyle::compute::cuda::detail;
+  return static_cast<int>(ref::launch_device_lengths_paged_append(ref::device_lengths_paged_append_kernel(), arena, rows,
+                                                                  metadata, query_lengths, kv_lengths, spec, status,
+                                                                  static_cast<cudaStream_t>(stream)));
+}
