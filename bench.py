@@ -323,6 +323,24 @@ def other_ops(torch, peak_gbs, only=None, iterations=40):
         report("categorical_f32", "256x151936", rows * cols, rows * cols * 4, ms, 2)
         del logits
 
+    # Scan{axis=-1}: f32 over vocabulary rows and over 4096 x 4096; i32 (two passes: check, then write)
+    if wanted("scan"):
+        for rows, cols, sets in ((256, 151936, 2), (4096, 4096, 4)):
+            x = [torch.randn(rows, cols, device=dev) for _ in range(sets)]
+            y = [torch.empty_like(x[0]) for _ in range(sets)]
+            ms = time_op(torch, lambda i: lib.hyle_b200_scan(
+                stream, abi.F32, x[i].data_ptr(), y[i].data_ptr(), rows, cols, 0, None), sets, iterations)
+            report("scan_f32", f"{rows}x{cols}", rows * cols, rows * cols * 8, ms, sets)
+            del x, y
+        sets = 4
+        n = [torch.randint(-1000, 1000, (4096, 4096), dtype=torch.int32, device=dev) for _ in range(sets)]
+        m = [torch.empty_like(n[0]) for _ in range(sets)]
+        status = torch.zeros(1, dtype=torch.int32, device=dev)
+        ms = time_op(torch, lambda i: lib.hyle_b200_scan(
+            stream, abi.I32, n[i].data_ptr(), m[i].data_ptr(), 4096, 4096, 0, status.data_ptr()), sets, iterations)
+        report("scan_i32_checked", "4096x4096", 4096 * 4096, 4096 * 4096 * 8, ms, sets)
+        del n, m
+
     # Paged append: 4096 new Q8_0 rows of 8192 values (8704 bytes) into 256 pages of 16 rows
     if wanted("paged_append"):
         sets, page_rows, pages, new_count, row_bytes = 4, 16, 1024, 4096, 8704

@@ -1,0 +1,183 @@
+// Scan{axis = -1, exclusive}: prefix sums along the rows of a dense [rows, cols] tensor
+// (include/hyle/compute/operation.h:314-321; CPU route src/compute_provider_ggml/standard_index.cc:113-157).
+//   f32: float accumulation; the operator permits reassociation, so the blocked order below is allowed.
+//   i32: int64 accumulation; when any inclusive prefix (the final total included, also for an exclusive
+//        scan) leaves the int32 range the call reports it and writes NO output, as the reference does.
+//
+// HBM-bound: 8 bytes per value.  One CTA walks a row in chunks of 4 values per thread with the row's
+// running total carried in a register; the (row, chunk) steps of a CTA form one sequence and the loads
+// of the next step are issued before the current one is combined, so a chunk's shuffles and its single
+// barrier hide behind the next chunk's memory latency.  Many short rows take 256-thread CTAs (eight
+// per SM), few long rows 1024-thread CTAs (two per SM).
+#include "common.cuh"
+
+namespace hb {
+namespace {
+
+constexpr unsigned kScanOverflow = HYLE_B200_STATUS_SCAN_OVERFLOW;
+
+template <class T> struct Quad { T v[4]; };
+
+// kStream: the values are not needed again (evict-first); the checking pass of the integer scan
+// loads normally so that the writing pass finds rows of moderate size in L2.
+template <class T, bool kVector, bool kStream>
+__device__ __forceinline__ Quad<T> load_quad(const T *row, uint64_t first, uint64_t cols) {
+  Quad<T> q;
+  if constexpr (kVector) {
+    if (first < cols) {
+      const uint4 *address = reinterpret_cast<const uint4 *>(row + first);
+      const uint4 w = kStream ? ld_stream(address) : __ldg(address);
+      const uint32_t words[4] = {w.x, w.y, w.z, w.w};
+#pragma unroll
+      for (int k = 0; k < 4; ++k) memcpy(&q.v[k], &words[k], 4);
+    } else {
+#pragma unroll
+      for (int k = 0; k < 4; ++k) q.v[k] = T(0);
+    }
+  } else {
+#pragma unroll
+    for (int k = 0; k < 4; ++k) q.v[k] = first + k < cols ? row[first + k] : T(0);
+  }
+  return q;
+}
+
+template <class T, bool kVector>
+__device__ __forceinline__ void store_quad(T *row, uint64_t first, uint64_t cols, const T (&v)[4]) {
+  if constexpr (kVector) {
+    if (first < cols) {
+      uint32_t words[4];
+#pragma unroll
+      for (int k = 0; k < 4; ++k) memcpy(&words[k], &v[k], 4);
+      st_stream(reinterpret_cast<uint4 *>(row + first), make_uint4(words[0], words[1], words[2], words[3]));
+    }
+  } else {
+#pragma unroll
+    for (int k = 0; k < 4; ++k)
+      if (first + k < cols) row[first + k] = v[k];
+  }
+}
+
+template <class Acc>
+__device__ __forceinline__ Acc warp_inclusive(Acc value, unsigned lane) {
+#pragma unroll
+  for (int step = 1; step < kWarpSize; step <<= 1) {
+    const Acc below = __shfl_up_sync(kFullMask, value, step);
+    if (lane >= static_cast<unsigned>(step)) value += below;
+  }
+  return value;
+}
+
+// kWrite = false is the checking pass of the i32 scan: the same walk, nothing stored.
+template <class T, class Acc, int kThreads, bool kVector, bool kWrite>
+__global__ void __launch_bounds__(kThreads)
+scan_rows_kernel(const T *__restrict__ in, T *__restrict__ out, uint64_t rows, uint64_t cols, int exclusive, unsigned *status) {
+  grid_dependency_sync();
+  constexpr int kWarps = kThreads / kWarpSize;
+  constexpr uint64_t kChunk = static_cast<uint64_t>(kThreads) * 4;
+  constexpr bool kChecked = sizeof(Acc) == 8;  // the integer scan
+  __shared__ Acc s_total[2][kWarps];
+  if constexpr (kChecked && kWrite) {
+    if ((*reinterpret_cast<volatile unsigned *>(status) & kScanOverflow) != 0) return;  // the check failed: no output
+  }
+  const unsigned lane = threadIdx.x % kWarpSize, warp = threadIdx.x / kWarpSize;
+  const uint64_t chunks = (cols + kChunk - 1) / kChunk;
+  const uint64_t mine = blockIdx.x < rows ? (rows - blockIdx.x + gridDim.x - 1) / gridDim.x : 0;
+  const uint64_t steps = mine * chunks;
+  bool bad = false;
+  Acc carry = 0;
+  uint64_t row = blockIdx.x, chunk = 0;
+  Quad<T> next = steps ? load_quad<T, kVector, kWrite>(in + row * cols, threadIdx.x * 4ull, cols) : Quad<T>{};
+  for (uint64_t step = 0; step < steps; ++step) {
+    const Quad<T> q = next;
+    const uint64_t at_row = row, at = chunk * kChunk + threadIdx.x * 4ull;
+    if (++chunk == chunks) chunk = 0, row += gridDim.x;
+    if (step + 1 < steps) next = load_quad<T, kVector, kWrite>(in + row * cols, chunk * kChunk + threadIdx.x * 4ull, cols);
+    if (at < kChunk) carry = 0;  // first chunk of a row
+    Acc p[4];
+    p[0] = static_cast<Acc>(q.v[0]);
+#pragma unroll
+    for (int k = 1; k < 4; ++k) p[k] = p[k - 1] + static_cast<Acc>(q.v[k]);
+    const Acc through = warp_inclusive(p[3], lane);  // this warp's total up to and including this lane
+    Acc (&totals)[kWarps] = s_total[step & 1];
+    if (lane == kWarpSize - 1) totals[warp] = through;
+    __syncthreads();
+    // every warp scans the warp totals for itself: no second barrier, and the buffers alternate
+    const Acc listed = lane < kWarps ? totals[lane] : Acc(0);
+    const Acc upto = warp_inclusive(listed, lane);
+    // exclusive prefixes are fetched from the neighbour, never formed as "inclusive - own": with an
+    // infinity in the chunk that difference would be NaN for values in front of it
+    const Acc upto_previous_warp = __shfl_sync(kFullMask, upto, (warp + kWarpSize - 1) % kWarpSize);
+    const Acc before_warp = warp == 0 ? Acc(0) : upto_previous_warp;
+    const Acc chunk_total = __shfl_sync(kFullMask, upto, kWarps - 1);
+    const Acc through_previous_lane = __shfl_up_sync(kFullMask, through, 1);
+    const Acc before_lane = lane == 0 ? Acc(0) : through_previous_lane;
+    const Acc base = carry + (before_warp + before_lane);
+    carry += chunk_total;
+    if constexpr (kChecked) {
+#pragma unroll
+      for (int k = 0; k < 4; ++k) {
+        const Acc value = base + p[k];
+        bad |= value < Acc(INT32_MIN) || value > Acc(INT32_MAX);
+      }
+    }
+    if constexpr (kWrite) {
+      T result[4];
+      if (exclusive) {
+        result[0] = static_cast<T>(base);
+#pragma unroll
+        for (int k = 1; k < 4; ++k) result[k] = static_cast<T>(base + p[k - 1]);
+      } else {
+#pragma unroll
+        for (int k = 0; k < 4; ++k) result[k] = static_cast<T>(base + p[k]);
+      }
+      store_quad<T, kVector>(out + at_row * cols, at, cols, result);
+    }
+  }
+  if constexpr (kChecked && !kWrite) {
+    if (__any_sync(kFullMask, bad) && lane == 0) atomicOr(status, kScanOverflow);
+  }
+}
+
+template <class T, class Acc, int kThreads, bool kVector, bool kWrite>
+int launch_scan(cudaStream_t stream, const T *in, T *out, uint64_t rows, uint64_t cols, int exclusive, unsigned *status,
+                unsigned ctas_per_sm) {
+  const unsigned grid = clamp_grid(rows, static_cast<uint64_t>(sm_count()) * ctas_per_sm);
+  return launch(scan_rows_kernel<T, Acc, kThreads, kVector, kWrite>, dim3(grid), dim3(kThreads), 0, stream, in, out, rows, cols,
+                exclusive, status);
+}
+
+template <class T, class Acc, bool kWrite>
+int dispatch_scan(cudaStream_t stream, const T *in, T *out, uint64_t rows, uint64_t cols, int exclusive, unsigned *status) {
+  const bool vector = cols % 4 == 0 && aligned_to(in, 16) && aligned_to(out, 16);
+  // Wide CTAs when there are too few rows to fill the machine with narrow ones, or rows long
+  // enough that a narrow CTA would spend its time on barriers.
+  const bool wide = rows < static_cast<uint64_t>(sm_count()) * 8 || cols >= 32768;
+  if (wide)
+    return vector ? launch_scan<T, Acc, 1024, true, kWrite>(stream, in, out, rows, cols, exclusive, status, 2)
+                  : launch_scan<T, Acc, 1024, false, kWrite>(stream, in, out, rows, cols, exclusive, status, 2);
+  return vector ? launch_scan<T, Acc, 256, true, kWrite>(stream, in, out, rows, cols, exclusive, status, 8)
+                : launch_scan<T, Acc, 256, false, kWrite>(stream, in, out, rows, cols, exclusive, status, 8);
+}
+
+}  // namespace
+}  // namespace hb
+
+using namespace hb;
+
+extern "C" int hyle_b200_scan(hyle_b200_stream_t stream, int dtype, const void *in, void *out, uint64_t rows, uint64_t cols,
+                              int exclusive, uint32_t *status_word) {
+  if (dtype != HYLE_B200_F32 && dtype != HYLE_B200_I32) return HYLE_B200_NOT_SUPPORTED;
+  if (rows == 0 || cols == 0) return HYLE_B200_OK;
+  if (in == nullptr || out == nullptr || !aligned_to(in, 4) || !aligned_to(out, 4) || in == out ||
+      (dtype == HYLE_B200_I32 && (status_word == nullptr || !aligned_to(status_word, 4))))
+    return HYLE_B200_INVALID_VALUE;
+  auto s = reinterpret_cast<cudaStream_t>(stream);
+  if (dtype == HYLE_B200_F32)
+    return dispatch_scan<float, float, true>(s, static_cast<const float *>(in), static_cast<float *>(out), rows, cols, exclusive,
+                                             status_word);
+  const int checked = dispatch_scan<int32_t, long long, false>(s, static_cast<const int32_t *>(in), static_cast<int32_t *>(out),
+                                                               rows, cols, exclusive, status_word);
+  if (checked != HYLE_B200_OK) return checked;
+  return dispatch_scan<int32_t, long long, true>(s, static_cast<const int32_t *>(in), static_cast<int32_t *>(out), rows, cols,
+                                                 exclusive, status_word);
+}

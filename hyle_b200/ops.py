@@ -276,6 +276,23 @@ def fp8_e4m3_encode(x: torch.Tensor, scale: float, status: Optional[torch.Tensor
     return out
 
 
+def scan(x: torch.Tensor, exclusive: bool = False, status: Optional[torch.Tensor] = None) -> torch.Tensor:
+    """Scan{axis=-1, exclusive}: prefix sums along the last axis of a dense f32 / i32 tensor.  For i32 a
+    ``status`` word is required: abi.STATUS_SCAN_OVERFLOW is set there, and the result left unwritten, when
+    a prefix does not fit int32."""
+    _device_tensor(x, "x")
+    if x.dtype not in (torch.float32, torch.int32) or not x.is_contiguous() or x.dim() < 1:
+        raise ValueError("scan takes a dense f32 / i32 tensor")
+    if x.dtype == torch.int32 and status is None:
+        raise ValueError("the i32 scan reports overflow through a status word")
+    out = torch.empty_like(x)
+    cols = x.shape[-1]
+    abi.check("hyle_b200_scan", abi.load().hyle_b200_scan(
+        _stream(), abi.F32 if x.dtype == torch.float32 else abi.I32, x.data_ptr(), out.data_ptr(),
+        x.numel() // cols if cols else 0, cols, int(exclusive), _ptr(status)))
+    return out
+
+
 def paged_append_metadata(instructions, capacity: int, device=None) -> torch.Tensor:
     """Pack an episode for :func:`paged_append`: int32 words {active_count, 0, 0, 0} followed by
     ``capacity`` instructions of {source_kind, source_page, source_row, destination_page,

@@ -36,7 +36,7 @@ inline constexpr ProviderRuntimeProperties kRuntime{.replay_class = ProviderRepl
                                                     .capture_compatible = true};
 
 enum class Entry : std::uint8_t {
-  kUnary, kBinary, kSelect, kReduceRows, kRmsNorm, kLayerNorm, kSwiglu, kSoftmax, kMaskedSoftmax, kCast, kArgmax, kQ8Encode, kFp8Encode, kRandomBits, kCategorical,
+  kUnary, kBinary, kSelect, kReduceRows, kScan, kRmsNorm, kLayerNorm, kSwiglu, kSoftmax, kMaskedSoftmax, kCast, kArgmax, kQ8Encode, kFp8Encode, kRandomBits, kCategorical,
   kAddRmsNorm, kBiasRowSumMax, kLogitsReduce, kQ8Roundtrip
 };
 
@@ -179,6 +179,17 @@ inline std::optional<Plan> match(const Operation &op, std::span<const TensorDesc
       default: return std::nullopt;
     }
     p.entry = Entry::kReduceRows;
+    return p;
+  }
+  if (const auto *scan = op.get_if<Scan>()) {
+    // last axis, f32, same dense description.  The i32 scan reports overflow through a device status
+    // word the custom-kernel interface does not hand to a provider, so it stays with the next one.
+    const auto last = static_cast<int>(in.empty() ? 0 : in[0].rank()) - 1;
+    if (in.size() != 1 || out.size() != 1 || in[0].data_type() != DataType::kFloat32 || in[0].rank() == 0 || out[0] != in[0] ||
+        (scan->axis != -1 && scan->axis != last))
+      return std::nullopt;
+    p.entry = Entry::kScan;
+    p.kind = scan->exclusive ? 1 : 0;
     return p;
   }
   if (const auto *norm = op.get_if<RmsNorm>()) {
@@ -348,6 +359,8 @@ inline int launch(const Plan &p, hyle_b200_stream_t stream, const void *const *i
       return hyle_b200_select(stream, p.dtype, in[0], in[1], in[2], out[0], p.count, p.rhs_period, p.gate_stride);
     case Entry::kBinary:
       return hyle_b200_binary(stream, p.kind, p.dtype, in[0], in[1], out[0], p.count, p.rhs_period);
+    case Entry::kScan:
+      return hyle_b200_scan(stream, HYLE_B200_F32, in[0], out[0], p.rows, p.cols, p.kind, nullptr);
     case Entry::kReduceRows:
       return hyle_b200_reduce_rows_f32(stream, p.kind, static_cast<const float *>(in[0]),
                                        static_cast<float *>(out[0]), p.rows, p.cols);

@@ -118,6 +118,17 @@ int main() {
     const std::array out0{f32_row};
     check(declined(*context, Operation(reduce), in, out0), "Reduce over axis 0 declined");
   }
+  {  // Scan along the last axis, f32; the checked i32 scan and other axes are left to the next provider
+    const std::array in{f32_mat};
+    const std::array out{f32_mat};
+    check(taken(*context, Operation(Scan{.axis = -1, .exclusive = false}), in, out), "Scan{axis=-1} f32");
+    check(taken(*context, Operation(Scan{.axis = 1, .exclusive = true}), in, out), "Scan{axis=1 of 2, exclusive} f32");
+    check(declined(*context, Operation(Scan{.axis = 0}), in, out), "Scan over axis 0 declined");
+    const auto i32_mat = dense(DataType::kInt32, {4096, 4096});
+    const std::array in_i{i32_mat};
+    const std::array out_i{i32_mat};
+    check(declined(*context, Operation(Scan{}), in_i, out_i), "Scan i32 (checked overflow) declined");
+  }
   {  // RmsNorm bf16 with bf16 / f32 weight; f16 weight and non-f32 accumulation are declined
     const std::array out{bf16_mat};
     const std::array in16{bf16_mat, bf16_w};

@@ -43,7 +43,7 @@ extern "C" {
 /* Same object as cudaStream_t; spelled out so C callers need no CUDA header. */
 typedef struct CUstream_st *hyle_b200_stream_t;
 
-#define HYLE_B200_ABI_VERSION 12
+#define HYLE_B200_ABI_VERSION 13
 
 enum hyle_b200_result {
   HYLE_B200_OK = 0,
@@ -121,7 +121,10 @@ enum hyle_b200_status_bits {
    * (src/compute_provider_ggml/ggml_cpu_provider.cc:591-594). */
   HYLE_B200_STATUS_INVALID_FP8_INPUT = 4u,
   /* hyle_b200_categorical met a row with NaN, +inf or no finite value; its index is -1. */
-  HYLE_B200_STATUS_INVALID_CATEGORICAL_ROW = 8u
+  HYLE_B200_STATUS_INVALID_CATEGORICAL_ROW = 8u,
+  /* hyle_b200_scan on i32: a prefix left the int32 range; no output was written
+   * (src/compute_provider_ggml/standard_index.cc:127-134). */
+  HYLE_B200_STATUS_SCAN_OVERFLOW = 16u
 };
 
 HYLE_B200_API int hyle_b200_abi_version(void);
@@ -272,6 +275,17 @@ HYLE_B200_API int hyle_b200_cast(hyle_b200_stream_t stream, int source_dtype, in
 HYLE_B200_API int hyle_b200_select(hyle_b200_stream_t stream, int dtype, const void *condition,
                                    const void *when_true, const void *when_false, void *out,
                                    uint64_t count, uint64_t true_period, uint64_t false_period);
+
+/* Scan{axis=-1, exclusive} (include/hyle/compute/operation.h:314-321; CPU route
+ * src/compute_provider_ggml/standard_index.cc:113-157): prefix sums along the rows of a dense
+ * [rows, cols] tensor, inclusive, or exclusive from zero.  dtype F32: float accumulation in a blocked
+ * order (the operator permits reassociation).  dtype I32: exact, int64 accumulation; if any inclusive
+ * prefix of any row (the row total included, also for an exclusive scan) does not fit int32,
+ * HYLE_B200_STATUS_SCAN_OVERFLOW is set in *status_word and NOTHING is written to out, which takes a
+ * checking pass before the writing pass; status_word is required for I32 and must not already carry
+ * that bit.  out must not alias in. */
+HYLE_B200_API int hyle_b200_scan(hyle_b200_stream_t stream, int dtype, const void *in, void *out,
+                                 uint64_t rows, uint64_t cols, int exclusive, uint32_t *status_word);
 
 /* Softmax{axis=-1, kSoftmax, scale, mask=kBoolean} on f16 rows, f32 accumulation: the masked, scaled
  * form of the CPU route (src/compute_provider_native/transformer.cc:44-57,228-275):

@@ -73,6 +73,10 @@ class Oracle:
         _u32 = ctypes.c_uint32
         L.hyle_oracle_paged_append.argtypes = [_vp, _vp, _vp, _u32, _u32, _u32, _u32, _u64]
         L.hyle_oracle_paged_append.restype = None
+        L.hyle_oracle_scan_f32.argtypes = [_vp, _vp, _u64, _u64, _i]
+        L.hyle_oracle_scan_f32.restype = None
+        L.hyle_oracle_scan_i32.argtypes = [_vp, _vp, _u64, _u64, _i]
+        L.hyle_oracle_scan_i32.restype = _u32
         L.hyle_oracle_paged_append_device_lengths.argtypes = [_vp, _vp, _vp, _vp, _vp, _u32, _u32, _u32, _u32, _u64, _u32, _u32]
         L.hyle_oracle_paged_append_device_lengths.restype = _u32
         for name in ("e4m3", "e5m2"):
@@ -150,6 +154,19 @@ class Oracle:
         out = np.empty(x.shape, np.uint8)
         status = self.lib.hyle_oracle_fp8_e4m3_encode(dtype, _ptr(x), x.size, scale, _ptr(out))
         return out, int(status)
+
+    def scan(self, x, exclusive=False):
+        """(prefix sums along the last axis, status): f32 summed left to right in float; i32 exact, with
+        status 16 and an untouched (zero) result when a prefix leaves the int32 range."""
+        x = np.ascontiguousarray(x)
+        cols = x.shape[-1]
+        rows = x.size // cols if cols else 0
+        out = np.zeros_like(x)
+        if x.dtype == np.float32:
+            self.lib.hyle_oracle_scan_f32(_ptr(x), _ptr(out), rows, cols, int(exclusive))
+            return out, 0
+        assert x.dtype == np.int32
+        return out, int(self.lib.hyle_oracle_scan_i32(_ptr(x), _ptr(out), rows, cols, int(exclusive)))
 
     def paged_append(self, arena, new_rows, words, page_rows):
         """Returns the arena [pages * page_rows, row bytes] (uint8) after the episode ``words`` (uint32)."""

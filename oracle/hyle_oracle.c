@@ -413,6 +413,41 @@ ORACLE_API uint32_t hyle_oracle_fp8_e4m3_encode(int dtype, const void *in, uint6
   return status;
 }
 
+/* ---- Scan{axis = -1, exclusive} ------------------------------------------------------------------
+ * src/compute_provider_ggml/standard_index.cc:113-157: f32 rows are summed left to right in float;
+ * i32 rows in int64, and if any inclusive prefix leaves the int32 range nothing is written and 16 is
+ * returned (the status bit of the GPU library). */
+ORACLE_API void hyle_oracle_scan_f32(const float *in, float *out, uint64_t rows, uint64_t cols, int exclusive) {
+#pragma omp parallel for schedule(static)
+  for (uint64_t r = 0; r < rows; ++r) {
+    float sum = 0.0f;
+    for (uint64_t c = 0; c < cols; ++c) {
+      const float before = sum;
+      sum = c == 0 ? in[r * cols] : sum + in[r * cols + c];
+      out[r * cols + c] = exclusive ? (c == 0 ? 0.0f : before) : sum;
+    }
+  }
+}
+
+ORACLE_API uint32_t hyle_oracle_scan_i32(const int32_t *in, int32_t *out, uint64_t rows, uint64_t cols, int exclusive) {
+  for (uint64_t r = 0; r < rows; ++r) {
+    int64_t sum = 0;
+    for (uint64_t c = 0; c < cols; ++c) {
+      sum += in[r * cols + c];
+      if (sum < INT32_MIN || sum > INT32_MAX) return 16u;
+    }
+  }
+  for (uint64_t r = 0; r < rows; ++r) {
+    int64_t sum = 0;
+    for (uint64_t c = 0; c < cols; ++c) {
+      const int64_t before = sum;
+      sum += in[r * cols + c];
+      out[r * cols + c] = (int32_t)(exclusive ? before : sum);
+    }
+  }
+  return 0;
+}
+
 /* ---- paged append (KV cache row mover) ---------------------------------------------------------
  * src/compute_backend_cuda/cuda_paged_append.cu:11-62 on the wire structs of
  * include/hyle/compute/detail/paged_append_wire.h:11-34.  words = {active_count, 0, 0, 0} then

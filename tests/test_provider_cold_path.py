@@ -29,4 +29,4 @@ def test_adapter_is_selected_by_the_reference_runtime():
     run = subprocess.run([BINARY], capture_output=True, text=True, timeout=120)
     assert run.returncode == 0, run.stdout + run.stderr
     assert "0 failure(s)" in run.stdout
-    assert run.stdout.count("ok  ") >= 45 and "FAIL" not in run.stdout
+    assert run.stdout.count("ok  ") >= 49 and "FAIL" not in run.stdout
