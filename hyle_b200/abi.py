@@ -33,7 +33,7 @@ STATUS_INVALID_CATEGORICAL_ROW = 8
 STATUS_SCAN_OVERFLOW = 16
 EXCHANGE_MAX_RANKS, EXCHANGE_MAILBOX_BYTES, EXCHANGE_HANDLE_BYTES = 8, 256, 64
 
-ABI_VERSION = 13
+ABI_VERSION = 14
 
 _p = ctypes.c_void_p
 _u64 = ctypes.c_uint64
@@ -62,6 +62,7 @@ SIGNATURES = {
     "hyle_b200_cast_f32_to_bf16": (_i, [_p, _p, _p, _u64]),
     "hyle_b200_q8_0_encode": (_i, [_p, _i, _p, _u64, _p, _p]),
     "hyle_b200_fp8_e4m3_encode": (_i, [_p, _i, _p, _u64, _f, _p, _p]),
+    "hyle_b200_strided_cast": (_i, [_p, _i, _i, _p, _p, _u32, _p, _p]),
     "hyle_b200_scan": (_i, [_p, _i, _p, _p, _u64, _u64, _i, _p]),
     "hyle_b200_paged_append": (_i, [_p, _p, _p, _p, _u32, _u32, _u32, _u32, _u64]),
     "hyle_b200_paged_append_device_lengths": (_i, [_p, _p, _p, _p, _p, _p, _u32, _u32, _u32, _u32, _u64, _u32, _p]),

@@ -369,6 +369,61 @@ int launch_cache_encode(cudaStream_t stream, const void *in, void *out, uint64_t
                 static_cast<const In *>(in) + done, static_cast<unsigned char *>(out) + done, count - done, scale, status_word);
 }
 
+// ---- strided views --------------------------------------------------------------------------------
+// Cast (or plain copy) from a view of rank <= 8 with arbitrary byte strides into a dense tensor: the
+// form in which the reference hands non-dense operands to its tensor kernels
+// (src/compute_provider_cuda/tensor_kernel.cu:70-108 reads every operand through byte strides).  The
+// host merges axes that are contiguous with each other, so typical views (slices, permutations of
+// two or three axes, broadcasts) arrive with rank 1-3; a view that collapses to a dense run takes the
+// dense kernels above.
+struct View {
+  uint32_t rank;
+  uint64_t dims[8];     // outermost first
+  int64_t strides[8];   // bytes
+};
+
+template <class Word, int kSrc, int kDst, bool kCopy, class Index>
+__global__ void __launch_bounds__(kThreads)
+strided_kernel(const unsigned char *__restrict__ in, typename Element<kDst>::Word *__restrict__ out, uint64_t count, const View view) {
+  grid_dependency_sync();
+  const uint64_t stride = static_cast<uint64_t>(gridDim.x) * kThreads;
+  for (uint64_t i = static_cast<uint64_t>(blockIdx.x) * kThreads + threadIdx.x; i < count; i += stride) {
+    Index rest = static_cast<Index>(i);
+    int64_t offset = 0;
+#pragma unroll
+    for (int d = 7; d >= 0; --d) {
+      if (d < static_cast<int>(view.rank)) {
+        const Index extent = static_cast<Index>(view.dims[d]);
+        const Index outer = rest / extent;
+        offset += static_cast<int64_t>(rest - outer * extent) * view.strides[d];
+        rest = outer;
+      }
+    }
+    const Word word = *reinterpret_cast<const Word *>(in + offset);
+    if constexpr (kCopy) out[i] = word;
+    else out[i] = static_cast<typename Element<kDst>::Word>(convert<kSrc, kDst>(word));
+  }
+}
+
+template <int kSrc, int kDst, bool kCopy>
+int launch_strided(cudaStream_t stream, const void *in, void *out, uint64_t count, const View &view) {
+  using Word = typename Element<kSrc>::Word;
+  using Out = typename Element<kDst>::Word;
+  const unsigned grid = clamp_grid((count + kThreads - 1) / kThreads, static_cast<uint64_t>(sm_count()) * kCtasPerSm);
+  auto kernel = count <= 0xffffffffull ? strided_kernel<Word, kSrc, kDst, kCopy, uint32_t> : strided_kernel<Word, kSrc, kDst, kCopy, uint64_t>;
+  return launch(kernel, dim3(grid), dim3(kThreads), 0, stream, static_cast<const unsigned char *>(in), static_cast<Out *>(out), count,
+                view);
+}
+
+inline int element_bytes(int dtype) {
+  switch (dtype) {
+    case HYLE_B200_F32: case HYLE_B200_I32: return 4;
+    case HYLE_B200_BF16: case HYLE_B200_F16: return 2;
+    case HYLE_B200_E4M3: case HYLE_B200_E5M2: case HYLE_B200_BOOL: return 1;
+    default: return 0;
+  }
+}
+
 }  // namespace
 }  // namespace hb
 
@@ -431,4 +486,66 @@ extern "C" int hyle_b200_select(hyle_b200_stream_t stream, int dtype, const void
   if (dtype == HYLE_B200_BF16 || dtype == HYLE_B200_F16)
     return launch_select<2>(s, condition, when_true, when_false, out, count, true_period, false_period);
   return HYLE_B200_INVALID_VALUE;
+}
+
+extern "C" int hyle_b200_strided_cast(hyle_b200_stream_t stream, int source_dtype, int destination_dtype, const void *in,
+                                      void *out, uint32_t rank, const int64_t *dims, const int64_t *byte_strides) {
+  const int width = element_bytes(source_dtype), out_width = element_bytes(destination_dtype);
+  if (width == 0 || out_width == 0) return HYLE_B200_NOT_SUPPORTED;
+  if (rank > 8 || (rank != 0 && (dims == nullptr || byte_strides == nullptr))) return HYLE_B200_INVALID_VALUE;
+  uint64_t count = 1;
+  for (uint32_t d = 0; d < rank; ++d) {
+    if (dims[d] < 0 || byte_strides[d] % width != 0) return HYLE_B200_INVALID_VALUE;
+    if (dims[d] != 0 && count > 0xffffffffffffffffull / static_cast<uint64_t>(dims[d])) return HYLE_B200_INVALID_VALUE;
+    count *= static_cast<uint64_t>(dims[d]);
+  }
+  if (count == 0) return HYLE_B200_OK;
+  if (in == nullptr || out == nullptr || !aligned_to(in, width) || !aligned_to(out, out_width)) return HYLE_B200_INVALID_VALUE;
+  // Drop axes of extent 1 and merge neighbours that are contiguous with each other.
+  View view{};
+  for (uint32_t d = 0; d < rank; ++d) {
+    if (dims[d] == 1) continue;
+    if (view.rank != 0 && view.strides[view.rank - 1] == byte_strides[d] * dims[d]) {
+      view.dims[view.rank - 1] *= static_cast<uint64_t>(dims[d]);
+      view.strides[view.rank - 1] = byte_strides[d];
+    } else {
+      view.dims[view.rank] = static_cast<uint64_t>(dims[d]);
+      view.strides[view.rank] = byte_strides[d];
+      ++view.rank;
+    }
+  }
+  auto s = reinterpret_cast<cudaStream_t>(stream);
+  const bool dense = view.rank == 0 || (view.rank == 1 && view.strides[0] == width);
+  if (source_dtype == destination_dtype) {
+    if (dense) return static_cast<int>(cudaMemcpyAsync(out, in, count * width, cudaMemcpyDeviceToDevice, s));
+    if (width == 4) return launch_strided<HYLE_B200_F32, HYLE_B200_F32, true>(s, in, out, count, view);
+    if (width == 2) return launch_strided<HYLE_B200_BF16, HYLE_B200_BF16, true>(s, in, out, count, view);
+    return launch_strided<HYLE_B200_BOOL, HYLE_B200_BOOL, true>(s, in, out, count, view);
+  }
+  if (dense) return hyle_b200_cast(stream, source_dtype, destination_dtype, in, out, count);
+#define HB_STRIDED(S, D) \
+  if (source_dtype == S && destination_dtype == D) return launch_strided<S, D, false>(s, in, out, count, view)
+  HB_STRIDED(HYLE_B200_F32, HYLE_B200_BF16);
+  HB_STRIDED(HYLE_B200_F32, HYLE_B200_F16);
+  HB_STRIDED(HYLE_B200_BF16, HYLE_B200_F32);
+  HB_STRIDED(HYLE_B200_F16, HYLE_B200_F32);
+  HB_STRIDED(HYLE_B200_BF16, HYLE_B200_F16);
+  HB_STRIDED(HYLE_B200_F16, HYLE_B200_BF16);
+  HB_STRIDED(HYLE_B200_I32, HYLE_B200_F32);
+  HB_STRIDED(HYLE_B200_F32, HYLE_B200_BOOL);
+  HB_STRIDED(HYLE_B200_BF16, HYLE_B200_BOOL);
+  HB_STRIDED(HYLE_B200_F16, HYLE_B200_BOOL);
+  HB_STRIDED(HYLE_B200_BOOL, HYLE_B200_F32);
+  HB_STRIDED(HYLE_B200_BOOL, HYLE_B200_BF16);
+  HB_STRIDED(HYLE_B200_BOOL, HYLE_B200_F16);
+  HB_STRIDED(HYLE_B200_F32, HYLE_B200_E4M3);
+  HB_STRIDED(HYLE_B200_BF16, HYLE_B200_E4M3);
+  HB_STRIDED(HYLE_B200_F16, HYLE_B200_E4M3);
+  HB_STRIDED(HYLE_B200_E4M3, HYLE_B200_F32);
+  HB_STRIDED(HYLE_B200_E4M3, HYLE_B200_BF16);
+  HB_STRIDED(HYLE_B200_E4M3, HYLE_B200_F16);
+  HB_STRIDED(HYLE_B200_E5M2, HYLE_B200_BF16);
+  HB_STRIDED(HYLE_B200_E5M2, HYLE_B200_E4M3);
+#undef HB_STRIDED
+  return HYLE_B200_NOT_SUPPORTED;
 }

@@ -8,6 +8,7 @@ CPU tensor raises.
 """
 from __future__ import annotations
 
+import ctypes
 from typing import Optional, Tuple
 
 import numpy as np
@@ -251,6 +252,8 @@ def softmax(x: torch.Tensor, log: bool = False, out: Optional[torch.Tensor] = No
 
 _CAST_TORCH = {abi.F32: torch.float32, abi.BF16: torch.bfloat16, abi.F16: torch.float16, abi.E4M3: torch.uint8,
                abi.E5M2: torch.uint8, abi.BOOL: torch.uint8, abi.I32: torch.int32}
+_CAST_DTYPE = {torch.float32: abi.F32, torch.bfloat16: abi.BF16, torch.float16: abi.F16, torch.int32: abi.I32,
+               torch.uint8: abi.BOOL, torch.bool: abi.BOOL}
 
 
 def cast(x: torch.Tensor, source: int, destination: int) -> torch.Tensor:
@@ -273,6 +276,28 @@ def fp8_e4m3_encode(x: torch.Tensor, scale: float, status: Optional[torch.Tensor
     out = torch.empty(x.shape, dtype=torch.uint8, device=x.device)
     abi.check("hyle_b200_fp8_e4m3_encode", abi.load().hyle_b200_fp8_e4m3_encode(
         _stream(), _DTYPE[x.dtype], x.data_ptr(), x.numel(), scale, out.data_ptr(), _ptr(status)))
+    return out
+
+
+def strided_cast(x: torch.Tensor, dtype: Optional[int] = None) -> torch.Tensor:
+    """Dense copy of ANY view ``x`` (slices, permutations, broadcasts), cast to the library dtype ``dtype``
+    (abi.F32 ...) or kept as it is.  8-bit float codes travel as uint8 with ``source`` / ``dtype`` given as
+    library dtypes through :func:`strided_cast_raw`."""
+    source = _CAST_DTYPE[x.dtype]
+    return strided_cast_raw(x, source, source if dtype is None else dtype)
+
+
+def strided_cast_raw(x: torch.Tensor, source: int, destination: int) -> torch.Tensor:
+    _device_tensor(x, "x")
+    if x.dim() > 8:
+        raise ValueError("views of rank <= 8")
+    if x.element_size() != torch.empty(0, dtype=_CAST_TORCH[source]).element_size():
+        raise ValueError("the view's element size does not match the source type")
+    out = torch.empty(x.shape, dtype=_CAST_TORCH[destination], device=x.device)
+    dims = (ctypes.c_int64 * max(1, x.dim()))(*x.shape)
+    strides = (ctypes.c_int64 * max(1, x.dim()))(*[s * x.element_size() for s in x.stride()])
+    abi.check("hyle_b200_strided_cast", abi.load().hyle_b200_strided_cast(
+        _stream(), source, destination, x.data_ptr(), out.data_ptr(), x.dim(), dims, strides))
     return out
 
 

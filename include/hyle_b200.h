@@ -43,7 +43,7 @@ extern "C" {
 /* Same object as cudaStream_t; spelled out so C callers need no CUDA header. */
 typedef struct CUstream_st *hyle_b200_stream_t;
 
-#define HYLE_B200_ABI_VERSION 13
+#define HYLE_B200_ABI_VERSION 14
 
 enum hyle_b200_result {
   HYLE_B200_OK = 0,
@@ -266,6 +266,18 @@ HYLE_B200_API int hyle_b200_softmax_f32(hyle_b200_stream_t stream, int kind, con
  * Other pairs return NOT_SUPPORTED. */
 HYLE_B200_API int hyle_b200_cast(hyle_b200_stream_t stream, int source_dtype, int destination_dtype,
                                  const void *in, void *out, uint64_t count);
+
+/* Cast -- or a plain copy when the two types are equal -- FROM A STRIDED VIEW into a dense row-major
+ * tensor: `in` addresses element (0, ..., 0); element (i0, ..., ik) lies byte_strides[0]*i0 + ... bytes
+ * from it (rank <= 8; strides are multiples of the element size and may be zero (broadcast) or
+ * negative).  This is how the reference's tensor kernels read every operand
+ * (src/compute_provider_cuda/tensor_kernel.cu:70-108); here a non-dense operand is made dense (and
+ * cast) in one pass and then feeds any other entry point.  Pairs: those of hyle_b200_cast plus every
+ * type onto itself (bits are moved).  A view that is in fact dense takes the dense kernels. */
+HYLE_B200_API int hyle_b200_strided_cast(hyle_b200_stream_t stream, int source_dtype,
+                                         int destination_dtype, const void *in, void *out,
+                                         uint32_t rank, const int64_t *dims,
+                                         const int64_t *byte_strides);
 
 /* Select (include/hyle/compute/operation.h:305, inference src/compute_ops/operation.cc:1309-1328):
  * out[i] = condition[i] != 0 ? when_true[i % true_period] : when_false[i % false_period]; elements

@@ -1,0 +1,96 @@
+"""Cast / copy from strided views: the dense result must equal the oracle's cast of the same view
+made dense on the host.  Bit-exact (NaN payloads as for the dense cast)."""
+import ctypes
+
+import numpy as np
+import pytest
+import torch
+
+from hyle_b200 import abi, ops
+from oracle import binding as ob
+
+
+@pytest.fixture(scope="module")
+def oracle():
+    return ob.Oracle()
+
+
+def views(base):
+    """Named views of a 4-D base tensor [6, 10, 12, 16]."""
+    return {
+        "dense": base,
+        "slice_inner": base[..., 3:11],
+        "slice_outer_step": base[1::2, :, ::3],
+        "transpose_last_two": base.transpose(-1, -2),
+        "permute_all": base.permute(3, 1, 0, 2),
+        "broadcast": base[:, :1, :, :].expand(6, 7, 12, 16),
+        "scalar_broadcast": base[2, 3, 4, 5].expand(5, 9),
+        "rank8": base.reshape(2, 3, 2, 5, 3, 4, 4, 4).permute(7, 0, 5, 2, 3, 1, 6, 4),
+        "single": base[1, 2, 3, 4],
+    }
+
+
+@pytest.mark.gpu
+@pytest.mark.parametrize("pair", [(abi.F32, abi.F32), (abi.F32, abi.BF16), (abi.BF16, abi.F32), (abi.F16, abi.BF16),
+                                  (abi.F32, abi.E4M3), (abi.E4M3, abi.F16), (abi.E5M2, abi.E4M3), (abi.I32, abi.F32),
+                                  (abi.F16, abi.BOOL), (abi.BOOL, abi.F32), (abi.BF16, abi.BF16), (abi.E4M3, abi.E4M3)])
+def test_strided_cast_matches_dense_cast_of_the_same_view(oracle, pair):
+    abi.load()
+    source, destination = pair
+    rng = np.random.default_rng(source * 10 + destination)
+    shape = (6, 10, 12, 16)
+    if source == abi.F32:
+        host = (rng.standard_normal(shape) * 50).astype(np.float32)
+    elif source == abi.I32:
+        host = rng.integers(-2 ** 31, 2 ** 31 - 1, shape, dtype=np.int64).astype(np.int32)
+    elif source in (abi.BF16, abi.F16):
+        host = rng.integers(0, 1 << 16, shape, dtype=np.uint16)
+    elif source == abi.BOOL:
+        host = rng.integers(0, 3, shape).astype(np.uint8)
+    else:
+        host = rng.integers(0, 256, shape, dtype=np.uint8)
+    carrier = {abi.F32: torch.float32, abi.I32: torch.int32, abi.BF16: torch.bfloat16, abi.F16: torch.float16}.get(source, torch.uint8)
+    device = torch.from_numpy(host).cuda()
+    device = device.view(carrier) if device.dtype != carrier else device
+    for (name, d_view), h_view in zip(views(device).items(), views(torch.from_numpy(host)).values()):
+        dense_host = np.ascontiguousarray(h_view.numpy())
+        if source == destination:
+            want = dense_host
+        else:
+            want = oracle.cast(source, destination, dense_host.view(ob.CAST_WORD[source]))
+        got = ops.strided_cast_raw(d_view, source, destination)
+        assert tuple(got.shape) == tuple(d_view.shape), name
+        got_bits = got.cpu().contiguous().view(torch.uint8).numpy().reshape(-1)
+        want_bits = np.ascontiguousarray(want).view(np.uint8).reshape(-1)
+        if destination in (abi.F32, abi.BF16, abi.F16) and source != destination:
+            # NaN payloads are not part of the contract: compare NaN-ness, and bits elsewhere
+            kind, top, frac = {abi.F32: (np.uint32, 0x7f800000, 0x007fffff), abi.BF16: (np.uint16, 0x7f80, 0x007f),
+                               abi.F16: (np.uint16, 0x7c00, 0x03ff)}[destination]
+            g, w = got_bits.view(kind), want_bits.view(kind)
+            nan_g = ((g & top) == top) & ((g & frac) != 0)
+            nan_w = ((w & top) == top) & ((w & frac) != 0)
+            assert np.array_equal(nan_g, nan_w), name
+            assert np.array_equal(g[~nan_w], w[~nan_w]), name
+        else:
+            assert np.array_equal(got_bits, want_bits), name
+
+
+@pytest.mark.gpu
+def test_strided_cast_negative_strides_and_arguments():
+    library = abi.load()
+    stream = torch.cuda.current_stream().cuda_stream
+    x = torch.arange(24, dtype=torch.float32, device="cuda").reshape(4, 6)
+    out = torch.empty(4, 6, dtype=torch.float32, device="cuda")
+    dims = (ctypes.c_int64 * 2)(4, 6)
+    strides = (ctypes.c_int64 * 2)(-24, -4)  # both axes reversed, starting from the last element
+    last = x.data_ptr() + 23 * 4
+    assert library.hyle_b200_strided_cast(stream, abi.F32, abi.F32, last, out.data_ptr(), 2, dims, strides) == abi.OK
+    torch.cuda.synchronize()
+    assert torch.equal(out, x.flip(0, 1))
+    odd = (ctypes.c_int64 * 2)(24, 2)
+    assert library.hyle_b200_strided_cast(stream, abi.F32, abi.F32, x.data_ptr(), out.data_ptr(), 2, dims, odd) == abi.INVALID_VALUE
+    assert library.hyle_b200_strided_cast(stream, abi.F32, abi.F32, x.data_ptr(), out.data_ptr(), 9, dims, strides) == abi.INVALID_VALUE
+    assert library.hyle_b200_strided_cast(stream, abi.F32, abi.I32, x.data_ptr(), out.data_ptr(), 2, dims, strides) == abi.NOT_SUPPORTED
+    empty = (ctypes.c_int64 * 2)(0, 6)
+    assert library.hyle_b200_strided_cast(stream, abi.F32, abi.F32, None, None, 2, empty, strides) == abi.OK
+    assert library.hyle_b200_strided_cast(stream, abi.F32, abi.BF16, x.data_ptr(), out.data_ptr(), 0, None, None) == abi.OK  # a scalar
