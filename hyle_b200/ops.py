@@ -288,7 +288,8 @@ def strided_cast(x: torch.Tensor, dtype: Optional[int] = None) -> torch.Tensor:
 
 
 def strided_cast_raw(x: torch.Tensor, source: int, destination: int) -> torch.Tensor:
-    _device_tensor(x, "x")
+    if not x.is_cuda:
+        raise ValueError("x must be a CUDA tensor (this provider has no CPU route)")
     if x.dim() > 8:
         raise ValueError("views of rank <= 8")
     if x.element_size() != torch.empty(0, dtype=_CAST_TORCH[source]).element_size():
