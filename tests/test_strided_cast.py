@@ -60,7 +60,7 @@ def test_strided_cast_matches_dense_cast_of_the_same_view(oracle, pair):
             want = oracle.cast(source, destination, dense_host.view(ob.CAST_WORD[source]))
         got = ops.strided_cast_raw(d_view, source, destination)
         assert tuple(got.shape) == tuple(d_view.shape), name
-        got_bits = got.cpu().contiguous().view(torch.uint8).numpy().reshape(-1)
+        got_bits = got.cpu().contiguous().reshape(-1).view(torch.uint8).numpy()
         want_bits = np.ascontiguousarray(want).view(np.uint8).reshape(-1)
         if destination in (abi.F32, abi.BF16, abi.F16) and source != destination:
             # NaN payloads are not part of the contract: compare NaN-ness, and bits elsewhere
