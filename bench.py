@@ -190,7 +190,9 @@ def event_pairs_ms(pairs):
 def time_op(torch, launch, sets: int, iterations: int = 40, warmup: int = 5):
     """Average device time of `launch(i)` over rotating buffer sets (footprint >> L2), CUDA events."""
     for i in range(warmup):
-        launch(i % sets)
+        code = launch(i % sets)
+        if code not in (None, 0):
+            raise RuntimeError(f"a timed entry point returned {code}")
     torch.cuda.synchronize()
     start, stop = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
     start.record()
@@ -322,6 +324,44 @@ def other_ops(torch, peak_gbs, only=None, iterations=40):
             2, max(1, iterations // 2))
         report("categorical_f32", "256x151936", rows * cols, rows * cols * 4, ms, 2)
         del logits
+
+    # Select, the masked f16 Softmax, and the gather-and-cast of strided views
+    if wanted("select_softmax_strided"):
+        import ctypes
+
+        sets = 4
+        n = 4096 * 4096
+        cond = [(torch.rand(n, device=dev) < 0.5).to(torch.uint8) for _ in range(sets)]
+        a = [torch.randn(n, device=dev) for _ in range(sets)]
+        b = [torch.randn(n, device=dev) for _ in range(sets)]
+        y = [torch.empty(n, device=dev) for _ in range(sets)]
+        ms = time_op(torch, lambda i: lib.hyle_b200_select(
+            stream, abi.F32, cond[i].data_ptr(), a[i].data_ptr(), b[i].data_ptr(), y[i].data_ptr(), n, n, n), sets, iterations)
+        report("select_f32", "4096x4096, both branches full", n, n * 13, ms, sets)
+        del cond, a, b, y
+        rows, cols = 32768, 2048  # 16 heads x 2048 queries x 2048 keys, one causal mask for all heads
+        scores = [torch.randn(rows, cols, device=dev).to(torch.float16) for _ in range(sets)]
+        probs = [torch.empty_like(scores[0]) for _ in range(sets)]
+        mask = torch.tril(torch.ones(cols, cols, dtype=torch.uint8, device=dev)).contiguous()
+        ms = time_op(torch, lambda i: lib.hyle_b200_masked_softmax_f16(
+            stream, scores[i].data_ptr(), mask.data_ptr(), mask.numel(), 0.125, probs[i].data_ptr(), rows, cols), sets, iterations)
+        report("masked_softmax_f16", "32768x2048, causal mask 2048x2048", rows * cols, rows * cols * 4 + mask.numel(), ms, sets)
+        del scores, probs, mask
+        side = 4096
+        x = [torch.randn(side, side, device=dev) for _ in range(sets)]
+        y = [torch.empty(side, side, device=dev) for _ in range(sets)]
+        dims = (ctypes.c_int64 * 2)(side, side)
+        transposed = (ctypes.c_int64 * 2)(4, 4 * side)
+        ms = time_op(torch, lambda i: lib.hyle_b200_strided_cast(
+            stream, abi.F32, abi.F32, x[i].data_ptr(), y[i].data_ptr(), 2, dims, transposed), sets, iterations)
+        report("strided_copy_f32_transpose", "4096x4096 read through a transposed view", side * side, side * side * 8, ms, sets)
+        half = (ctypes.c_int64 * 2)(side, side // 2)
+        sliced = (ctypes.c_int64 * 2)(4 * side, 4)
+        y16 = [torch.empty(side, side // 2, dtype=torch.bfloat16, device=dev) for _ in range(sets)]
+        ms = time_op(torch, lambda i: lib.hyle_b200_strided_cast(
+            stream, abi.F32, abi.BF16, x[i].data_ptr(), y16[i].data_ptr(), 2, half, sliced), sets, iterations)
+        report("strided_cast_f32_to_bf16_slice", "4096x2048 slice of 4096x4096 rows", side * side // 2, side * side // 2 * 6, ms, sets)
+        del x, y, y16
 
     # Scan{axis=-1}: f32 over vocabulary rows and over 4096 x 4096; i32 (two passes: check, then write)
     if wanted("scan"):

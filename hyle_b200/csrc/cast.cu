@@ -220,6 +220,52 @@ cast_kernel(const void *in, void *out, uint64_t packs) {
   }
 }
 
+// 4-byte destinations: four values per thread-step, so that a warp's store instruction writes 512
+// contiguous bytes.  With eight values per thread the two 16-byte stores of a thread fall into the
+// same 32-byte sector as halves, every sector is written by two instructions, and the store path --
+// these casts write four times (1-byte source) or twice (2-byte source) what they read -- is the limit.
+template <int kSrc, int kDst>
+__global__ void __launch_bounds__(kThreads)
+cast_quads_kernel(const void *in, void *out, uint64_t quads) {
+  grid_dependency_sync();
+  constexpr int kIn = sizeof(typename Element<kSrc>::Word);
+  static_assert(sizeof(typename Element<kDst>::Word) == 4, "4-byte destinations");
+  constexpr int kUnroll = kIn == 4 ? 4 : 8;
+  const uint64_t stride = static_cast<uint64_t>(gridDim.x) * kThreads;
+  auto load = [&](uint64_t q, uint32_t (&w)[4]) {
+    if constexpr (kIn == 1) {
+      const uint32_t v = __ldcs(static_cast<const uint32_t *>(in) + q);
+#pragma unroll
+      for (int e = 0; e < 4; ++e) w[e] = (v >> (8 * e)) & 0xffu;
+    } else if constexpr (kIn == 2) {
+      const uint2 v = ld_stream(static_cast<const uint2 *>(in) + q);
+      w[0] = v.x & 0xffffu, w[1] = v.x >> 16, w[2] = v.y & 0xffffu, w[3] = v.y >> 16;
+    } else {
+      const uint4 v = ld_stream(static_cast<const uint4 *>(in) + q);
+      w[0] = v.x, w[1] = v.y, w[2] = v.z, w[3] = v.w;
+    }
+  };
+  uint64_t i = static_cast<uint64_t>(blockIdx.x) * kThreads + threadIdx.x;
+  for (; i + (kUnroll - 1) * stride < quads; i += kUnroll * stride) {
+    uint32_t w[kUnroll][4];
+#pragma unroll
+    for (int k = 0; k < kUnroll; ++k) load(i + k * stride, w[k]);
+#pragma unroll
+    for (int k = 0; k < kUnroll; ++k) {
+#pragma unroll
+      for (int e = 0; e < 4; ++e) w[k][e] = convert<kSrc, kDst>(w[k][e]);
+      st_stream(static_cast<uint4 *>(out) + i + k * stride, make_uint4(w[k][0], w[k][1], w[k][2], w[k][3]));
+    }
+  }
+  for (; i < quads; i += stride) {
+    uint32_t w[4];
+    load(i, w);
+#pragma unroll
+    for (int e = 0; e < 4; ++e) w[e] = convert<kSrc, kDst>(w[e]);
+    st_stream(static_cast<uint4 *>(out) + i, make_uint4(w[0], w[1], w[2], w[3]));
+  }
+}
+
 // Unaligned tensors and the tail behind the last whole pack.
 template <int kSrc, int kDst>
 __global__ void __launch_bounds__(kThreads)
@@ -238,8 +284,15 @@ int launch_cast(cudaStream_t stream, const void *in, void *out, uint64_t count) 
   const uint64_t resident = static_cast<uint64_t>(sm_count()) * kCtasPerSm;
   const bool vector_ok = aligned_to(in, 8 * sizeof(In) > 16 ? 16 : 8 * sizeof(In)) &&
                          aligned_to(out, 8 * sizeof(Out) > 16 ? 16 : 8 * sizeof(Out));
-  const uint64_t packs = vector_ok ? count / 8 : 0;
-  if (packs != 0) {
+  uint64_t packs = vector_ok ? count / 8 : 0;
+  if constexpr (sizeof(Out) == 4) {
+    if (packs != 0) {
+      const uint64_t quads = packs * 2;
+      const unsigned grid = clamp_grid((quads + kThreads * 8 - 1) / (kThreads * 8), resident);
+      const int status = launch(cast_quads_kernel<kSrc, kDst>, dim3(grid), dim3(kThreads), 0, stream, in, out, quads);
+      if (status != HYLE_B200_OK) return status;
+    }
+  } else if (packs != 0) {
     const unsigned grid = clamp_grid((packs + kThreads * 4 - 1) / (kThreads * 4), resident);
     const int status = launch(cast_kernel<kSrc, kDst>, dim3(grid), dim3(kThreads), 0, stream, in, out, packs);
     if (status != HYLE_B200_OK) return status;
