@@ -440,11 +440,11 @@ __global__ void __launch_bounds__(kThreads)
 strided_kernel(const unsigned char *__restrict__ in, typename Element<kDst>::Word *__restrict__ out, uint64_t count, const View view) {
   grid_dependency_sync();
   const uint64_t stride = static_cast<uint64_t>(gridDim.x) * kThreads;
-  for (uint64_t i = static_cast<uint64_t>(blockIdx.x) * kThreads + threadIdx.x; i < count; i += stride) {
+  auto fetch = [&](uint64_t i) {
     Index rest = static_cast<Index>(i);
     int64_t offset = 0;
 #pragma unroll
-    for (int d = 7; d >= 0; --d) {
+    for (int d = 7; d >= 1; --d) {
       if (d < static_cast<int>(view.rank)) {
         const Index extent = static_cast<Index>(view.dims[d]);
         const Index outer = rest / extent;
@@ -452,17 +452,30 @@ strided_kernel(const unsigned char *__restrict__ in, typename Element<kDst>::Wor
         rest = outer;
       }
     }
-    const Word word = *reinterpret_cast<const Word *>(in + offset);
+    if (view.rank != 0) offset += static_cast<int64_t>(rest) * view.strides[0];  // what is left is the outermost coordinate
+    return *reinterpret_cast<const Word *>(in + offset);
+  };
+  auto put = [&](uint64_t i, Word word) {
     if constexpr (kCopy) out[i] = word;
     else out[i] = static_cast<typename Element<kDst>::Word>(convert<kSrc, kDst>(word));
+  };
+  constexpr int kGather = 8;  // independent loads in flight per thread: one element each is latency-bound
+  uint64_t i = static_cast<uint64_t>(blockIdx.x) * kThreads + threadIdx.x;
+  for (; i + (kGather - 1) * stride < count; i += kGather * stride) {
+    Word words[kGather];
+#pragma unroll
+    for (int k = 0; k < kGather; ++k) words[k] = fetch(i + k * stride);
+#pragma unroll
+    for (int k = 0; k < kGather; ++k) put(i + k * stride, words[k]);
   }
+  for (; i < count; i += stride) put(i, fetch(i));
 }
 
 template <int kSrc, int kDst, bool kCopy>
 int launch_strided(cudaStream_t stream, const void *in, void *out, uint64_t count, const View &view) {
   using Word = typename Element<kSrc>::Word;
   using Out = typename Element<kDst>::Word;
-  const unsigned grid = clamp_grid((count + kThreads - 1) / kThreads, static_cast<uint64_t>(sm_count()) * kCtasPerSm);
+  const unsigned grid = clamp_grid((count + kThreads * 8 - 1) / (kThreads * 8), static_cast<uint64_t>(sm_count()) * kCtasPerSm);
   auto kernel = count <= 0xffffffffull ? strided_kernel<Word, kSrc, kDst, kCopy, uint32_t> : strided_kernel<Word, kSrc, kDst, kCopy, uint64_t>;
   return launch(kernel, dim3(grid), dim3(kThreads), 0, stream, static_cast<const unsigned char *>(in), static_cast<Out *>(out), count,
                 view);

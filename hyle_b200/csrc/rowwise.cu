@@ -577,6 +577,157 @@ masked_softmax_f16_kernel(const unsigned short *x, const unsigned char *__restri
   }
 }
 
+// Rows of 1024-4096 values whose length is a multiple of 8, 16-byte aligned: eight values per
+// thread-step (one 16-byte load of scores, one 8-byte load of mask bytes, one 16-byte store), the row
+// resident in registers, exp as ex2.approx of the scaled difference (relative error about 1e-6, far
+// inside the f16 step the result is rounded to).
+constexpr int kVectorSlots = 2;
+
+__global__ void __launch_bounds__(kThreads)
+masked_softmax_f16_vector_kernel(const uint4 *__restrict__ x, const uint2 *__restrict__ mask, uint4 *__restrict__ y, uint64_t rows,
+                                 uint32_t vectors, uint64_t mask_rows, float scale) {
+  grid_dependency_sync();
+  __shared__ float s_part[2][kWarps];
+  const int t = threadIdx.x, lane = t & 31, warp = t >> 5;
+  auto cta_reduce = [&](float v, int slot, bool maximum) {
+    v = maximum ? warp_max_nan(v) : warp_sum(v);
+    if (lane == 0) s_part[slot][warp] = v;
+    __syncthreads();
+    float total = s_part[slot][0];
+#pragma unroll
+    for (int w = 1; w < kWarps; ++w) total = maximum ? max_nan(total, s_part[slot][w]) : __fadd_rn(total, s_part[slot][w]);
+    return total;
+  };
+  for (uint64_t row = blockIdx.x; row < rows; row += gridDim.x) {
+    const uint4 *in = x + row * vectors;
+    const uint2 *row_mask = mask + (row % mask_rows) * vectors;
+    float v[kVectorSlots][8];
+    float peak = -CUDART_INF_F;
+#pragma unroll
+    for (int k = 0; k < kVectorSlots; ++k) {
+      const uint32_t i = k * kThreads + t;
+      if (i < vectors) {
+        const uint4 w = ld_stream(in + i);
+        const uint2 m = __ldg(row_mask + i);
+        const uint32_t words[4] = {w.x, w.y, w.z, w.w};
+#pragma unroll
+        for (int e = 0; e < 8; ++e) {
+          const unsigned short half = static_cast<unsigned short>(e & 1 ? words[e / 2] >> 16 : words[e / 2] & 0xffffu);
+          const uint32_t keep = ((e < 4 ? m.x : m.y) >> (8 * (e & 3))) & 0xffu;
+          v[k][e] = keep == 0 ? -CUDART_INF_F : __fmul_rn(f16_to_f32(half), scale);
+          peak = max_nan(peak, v[k][e]);
+        }
+      } else {
+#pragma unroll
+        for (int e = 0; e < 8; ++e) v[k][e] = -CUDART_INF_F;
+      }
+    }
+    peak = cta_reduce(peak, 0, true);
+    const bool valid = peak > -CUDART_INF_F && peak < CUDART_INF_F;  // false for NaN too
+    float sum = 0.0f;
+#pragma unroll
+    for (int k = 0; k < kVectorSlots; ++k) {
+#pragma unroll
+      for (int e = 0; e < 8; ++e) {
+        float weight;  // exp(v - peak); masked and padding slots give ex2(-inf) = 0
+        asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(weight) : "f"(__fmul_rn(__fsub_rn(v[k][e], peak), 1.4426950408889634f)));
+        v[k][e] = weight;
+        sum += weight;
+      }
+    }
+    sum = cta_reduce(sum, 1, false);
+    const float inverse = valid ? __fdiv_rn(1.0f, sum) : CUDART_NAN_F;
+#pragma unroll
+    for (int k = 0; k < kVectorSlots; ++k) {
+      const uint32_t i = k * kThreads + t;
+      if (i < vectors) {
+        uint32_t words[4];
+#pragma unroll
+        for (int e = 0; e < 4; ++e) {
+          const uint32_t low = f32_to_f16(valid ? __fmul_rn(v[k][2 * e], inverse) : CUDART_NAN_F);
+          const uint32_t high = f32_to_f16(valid ? __fmul_rn(v[k][2 * e + 1], inverse) : CUDART_NAN_F);
+          words[e] = low | (high << 16);
+        }
+        st_stream(y + row * vectors + i, make_uint4(words[0], words[1], words[2], words[3]));
+      }
+    }
+    __syncthreads();  // the partial slots are rewritten by the next row
+  }
+}
+
+// Rows of up to 2048 values (a multiple of 8): one WARP per row, the row in registers (up to eight
+// 16-byte loads in flight per lane), shuffles only -- no barrier between the three phases of a row.
+template <int kSlots>
+__global__ void __launch_bounds__(128)
+masked_softmax_f16_warp_kernel(const uint4 *__restrict__ x, const uint2 *__restrict__ mask, uint4 *__restrict__ y, uint64_t rows,
+                               uint32_t vectors, uint64_t mask_rows, float scale) {
+  grid_dependency_sync();
+  const int lane = threadIdx.x & 31;
+  const uint64_t warps = static_cast<uint64_t>(gridDim.x) * (blockDim.x / 32);
+  for (uint64_t row = static_cast<uint64_t>(blockIdx.x) * (blockDim.x / 32) + threadIdx.x / 32; row < rows; row += warps) {
+    const uint4 *in = x + row * vectors;
+    const uint2 *row_mask = mask + (row % mask_rows) * vectors;
+    uint4 w[kSlots];
+    uint2 m[kSlots];
+#pragma unroll
+    for (int k = 0; k < kSlots; ++k) {
+      const uint32_t i = k * 32 + lane;
+      w[k] = i < vectors ? ld_stream(in + i) : make_uint4(0, 0, 0, 0);
+      m[k] = i < vectors ? __ldg(row_mask + i) : make_uint2(0, 0);  // padding counts as masked
+    }
+    float v[kSlots][8];
+    float peak = -CUDART_INF_F;
+#pragma unroll
+    for (int k = 0; k < kSlots; ++k) {
+      const uint32_t words[4] = {w[k].x, w[k].y, w[k].z, w[k].w};
+#pragma unroll
+      for (int e = 0; e < 8; ++e) {
+        const unsigned short half = static_cast<unsigned short>(e & 1 ? words[e / 2] >> 16 : words[e / 2] & 0xffffu);
+        const uint32_t keep = ((e < 4 ? m[k].x : m[k].y) >> (8 * (e & 3))) & 0xffu;
+        v[k][e] = keep == 0 ? -CUDART_INF_F : __fmul_rn(f16_to_f32(half), scale);
+        peak = max_nan(peak, v[k][e]);
+      }
+    }
+    peak = warp_max_nan(peak);
+    const bool valid = peak > -CUDART_INF_F && peak < CUDART_INF_F;  // false for NaN too
+    float sum = 0.0f;
+#pragma unroll
+    for (int k = 0; k < kSlots; ++k) {
+#pragma unroll
+      for (int e = 0; e < 8; ++e) {
+        float weight;
+        asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(weight) : "f"(__fmul_rn(__fsub_rn(v[k][e], peak), 1.4426950408889634f)));
+        v[k][e] = weight;
+        sum += weight;
+      }
+    }
+    sum = warp_sum(sum);
+    const float inverse = valid ? __fdiv_rn(1.0f, sum) : CUDART_NAN_F;
+#pragma unroll
+    for (int k = 0; k < kSlots; ++k) {
+      const uint32_t i = k * 32 + lane;
+      if (i < vectors) {
+        uint32_t words[4];
+#pragma unroll
+        for (int e = 0; e < 4; ++e) {
+          const uint32_t low = f32_to_f16(valid ? __fmul_rn(v[k][2 * e], inverse) : CUDART_NAN_F);
+          const uint32_t high = f32_to_f16(valid ? __fmul_rn(v[k][2 * e + 1], inverse) : CUDART_NAN_F);
+          words[e] = low | (high << 16);
+        }
+        st_stream(y + row * vectors + i, make_uint4(words[0], words[1], words[2], words[3]));
+      }
+    }
+  }
+}
+
+template <int kSlots>
+int launch_masked_softmax_warp(cudaStream_t stream, const void *in, const unsigned char *mask, void *out, uint64_t rows,
+                               uint32_t vectors, uint64_t mask_rows, float scale) {
+  const unsigned grid = clamp_grid((rows + 3) / 4, static_cast<uint64_t>(sm_count()) * 16);
+  return launch(masked_softmax_f16_warp_kernel<kSlots>, dim3(grid), dim3(128), 0, stream, static_cast<const uint4 *>(in),
+                reinterpret_cast<const uint2 *>(mask), static_cast<uint4 *>(out), rows, vectors, mask_rows, scale);
+}
+
 }  // namespace
 }  // namespace hb
 
@@ -648,6 +799,20 @@ extern "C" int hyle_b200_masked_softmax_f16(hyle_b200_stream_t stream, const voi
       mask_count % cols != 0 || (rows * cols) % mask_count != 0 || !aligned_to(in, 2) || !aligned_to(out, 2))
     return HYLE_B200_INVALID_VALUE;
   const unsigned grid = clamp_grid(rows, static_cast<uint64_t>(sm_count()) * 8);
+  const bool vector_ok = cols % 8 == 0 && aligned_to(in, 16) && aligned_to(out, 16) && aligned_to(mask, 8);
+  if (vector_ok && cols <= 2048) {
+    auto s = reinterpret_cast<cudaStream_t>(stream);
+    const uint32_t vectors = static_cast<uint32_t>(cols / 8);
+    const uint64_t mask_rows = mask_count / cols;
+    if (vectors <= 32) return launch_masked_softmax_warp<1>(s, in, mask, out, rows, vectors, mask_rows, scale);
+    if (vectors <= 64) return launch_masked_softmax_warp<2>(s, in, mask, out, rows, vectors, mask_rows, scale);
+    if (vectors <= 128) return launch_masked_softmax_warp<4>(s, in, mask, out, rows, vectors, mask_rows, scale);
+    return launch_masked_softmax_warp<8>(s, in, mask, out, rows, vectors, mask_rows, scale);
+  }
+  if (vector_ok && cols <= static_cast<uint64_t>(kThreads) * 8 * kVectorSlots)
+    return launch(masked_softmax_f16_vector_kernel, dim3(grid), dim3(kThreads), 0, reinterpret_cast<cudaStream_t>(stream),
+                  static_cast<const uint4 *>(in), reinterpret_cast<const uint2 *>(mask), static_cast<uint4 *>(out), rows,
+                  static_cast<uint32_t>(cols / 8), mask_count / cols, scale);
   return launch(masked_softmax_f16_kernel, dim3(grid), dim3(kThreads), 0, reinterpret_cast<cudaStream_t>(stream),
                 static_cast<const unsigned short *>(in), mask, static_cast<unsigned short *>(out), rows,
                 static_cast<uint32_t>(cols), mask_count / cols, scale);

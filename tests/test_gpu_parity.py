@@ -663,7 +663,7 @@ def test_select_moves_bits(dtype):
     assert torch.equal(ops.select(flat_c, flat_a, flat_b).view(raw), want.reshape(-1)[3:2000])
 
 
-@pytest.mark.parametrize("cols", [1, 7, 128, 1000, 4096, 5000])
+@pytest.mark.parametrize("cols", [1, 7, 128, 1000, 1024, 2056, 4096, 5000])
 def test_masked_scaled_softmax_f16(oracle, cols):
     rng = np.random.default_rng(cols)
     heads, queries = 3, 17
