@@ -471,10 +471,60 @@ strided_kernel(const unsigned char *__restrict__ in, typename Element<kDst>::Wor
   for (; i < count; i += stride) put(i, fetch(i));
 }
 
+// Views whose innermost (merged) axis is long: a CTA-step takes a segment of one innermost run, so the
+// offset of the run is computed once per step by the whole CTA and no thread divides per element.
+template <class Word, int kSrc, int kDst, bool kCopy>
+__global__ void __launch_bounds__(kThreads)
+strided_runs_kernel(const unsigned char *__restrict__ in, typename Element<kDst>::Word *__restrict__ out, uint64_t runs,
+                    const View view) {
+  grid_dependency_sync();
+  constexpr int kGather = 8;
+  constexpr uint64_t kSegment = static_cast<uint64_t>(kThreads) * kGather;
+  const uint64_t inner = view.dims[view.rank - 1];
+  const int64_t inner_stride = view.strides[view.rank - 1];
+  const uint64_t segments = (inner + kSegment - 1) / kSegment;
+  for (uint64_t unit = blockIdx.x; unit < runs * segments; unit += gridDim.x) {
+    const uint64_t run = unit / segments, segment = unit - run * segments;
+    uint64_t rest = run;
+    int64_t offset = 0;
+#pragma unroll
+    for (int d = 6; d >= 1; --d) {
+      if (d + 1 < static_cast<int>(view.rank)) {
+        const uint64_t outer = rest / view.dims[d];
+        offset += static_cast<int64_t>(rest - outer * view.dims[d]) * view.strides[d];
+        rest = outer;
+      }
+    }
+    if (view.rank > 1) offset += static_cast<int64_t>(rest) * view.strides[0];
+    const uint64_t first = segment * kSegment + threadIdx.x;
+    Word words[kGather];
+#pragma unroll
+    for (int k = 0; k < kGather; ++k) {
+      const uint64_t j = first + static_cast<uint64_t>(k) * kThreads;
+      if (j < inner) words[k] = *reinterpret_cast<const Word *>(in + offset + static_cast<int64_t>(j) * inner_stride);
+    }
+#pragma unroll
+    for (int k = 0; k < kGather; ++k) {
+      const uint64_t j = first + static_cast<uint64_t>(k) * kThreads;
+      if (j < inner) {
+        if constexpr (kCopy) out[run * inner + j] = words[k];
+        else out[run * inner + j] = static_cast<typename Element<kDst>::Word>(convert<kSrc, kDst>(words[k]));
+      }
+    }
+  }
+}
+
 template <int kSrc, int kDst, bool kCopy>
 int launch_strided(cudaStream_t stream, const void *in, void *out, uint64_t count, const View &view) {
   using Word = typename Element<kSrc>::Word;
   using Out = typename Element<kDst>::Word;
+  if (view.rank != 0 && view.dims[view.rank - 1] >= 256) {
+    const uint64_t inner = view.dims[view.rank - 1], runs = count / inner;
+    const uint64_t units = runs * ((inner + kThreads * 8 - 1) / (kThreads * 8));
+    const unsigned run_grid = clamp_grid(units, static_cast<uint64_t>(sm_count()) * kCtasPerSm);
+    return launch(strided_runs_kernel<Word, kSrc, kDst, kCopy>, dim3(run_grid), dim3(kThreads), 0, stream,
+                  static_cast<const unsigned char *>(in), static_cast<Out *>(out), runs, view);
+  }
   const unsigned grid = clamp_grid((count + kThreads * 8 - 1) / (kThreads * 8), static_cast<uint64_t>(sm_count()) * kCtasPerSm);
   auto kernel = count <= 0xffffffffull ? strided_kernel<Word, kSrc, kDst, kCopy, uint32_t> : strided_kernel<Word, kSrc, kDst, kCopy, uint64_t>;
   return launch(kernel, dim3(grid), dim3(kThreads), 0, stream, static_cast<const unsigned char *>(in), static_cast<Out *>(out), count,

@@ -76,6 +76,45 @@ def test_strided_cast_matches_dense_cast_of_the_same_view(oracle, pair):
 
 
 @pytest.mark.gpu
+@pytest.mark.parametrize("pair", [(abi.F32, abi.F32), (abi.F32, abi.BF16), (abi.F16, abi.F32), (abi.E4M3, abi.E4M3)])
+def test_strided_cast_long_inner_runs(oracle, pair):
+    """Views whose merged innermost axis has 256 elements or more take the run-based kernel."""
+    source, destination = pair
+    rng = np.random.default_rng(7 + source)
+    shape = (4, 300, 9, 700)
+    host = {abi.F32: lambda: rng.standard_normal(shape).astype(np.float32),
+            abi.F16: lambda: rng.integers(0, 1 << 16, shape, dtype=np.uint16),
+            abi.E4M3: lambda: rng.integers(0, 256, shape, dtype=np.uint8)}[source]()
+    carrier = {abi.F32: torch.float32, abi.F16: torch.float16}.get(source, torch.uint8)
+    device = torch.from_numpy(host).cuda()
+    device = device.view(carrier) if device.dtype != carrier else device
+
+    def long_views(t):
+        return {
+            "inner_slice": t[..., 10:590],
+            "inner_step": t[1, :, 2, ::2],
+            "inner_is_a_permuted_axis": t[:, :, :, 5].permute(0, 2, 1),
+            "inner_broadcast": t[:, :1, :, :1].expand(4, 3, 9, 1000),
+            "one_axis": t[2, 7, 3, 40:],
+            "ragged_segments": t[0, :2, :, : 2048 // 3 + 1],
+        }
+
+    for (name, d_view), h_view in zip(long_views(device).items(), long_views(torch.from_numpy(host)).values()):
+        dense_host = np.ascontiguousarray(h_view.numpy())
+        want = dense_host if source == destination else oracle.cast(source, destination, dense_host.view(ob.CAST_WORD[source]))
+        got = ops.strided_cast_raw(d_view, source, destination)
+        got_bits = got.cpu().contiguous().reshape(-1).view(torch.uint8).numpy()
+        want_bits = np.ascontiguousarray(want).view(np.uint8).reshape(-1)
+        if source == abi.F16 and destination == abi.F32:  # NaN payloads are not part of the contract
+            g, w = got_bits.view(np.uint32), want_bits.view(np.uint32)
+            nan = (w & 0x7fffffff) > 0x7f800000
+            assert np.array_equal((g & 0x7fffffff) > 0x7f800000, nan), name
+            assert np.array_equal(g[~nan], w[~nan]), name
+        else:
+            assert np.array_equal(got_bits, want_bits), name
+
+
+@pytest.mark.gpu
 def test_strided_cast_negative_strides_and_arguments():
     library = abi.load()
     stream = torch.cuda.current_stream().cuda_stream
