@@ -514,10 +514,92 @@ strided_runs_kernel(const unsigned char *__restrict__ in, typename Element<kDst>
   }
 }
 
+// Transposing views: the innermost axis of the view is strided in the source while another axis
+// (`axis`) is contiguous there.  A 32 x 32 tile goes through shared memory so that the source is read
+// along its contiguous axis and the dense destination is written along its innermost one.
+struct Transposition {
+  uint32_t axis;          // the view axis whose byte stride equals the element size
+  uint64_t dense[8];      // row-major element strides of the dense destination, per view axis
+};
+
+template <class Word, int kSrc, int kDst, bool kCopy, class Index>
+__global__ void __launch_bounds__(256)
+strided_tiles_kernel(const unsigned char *__restrict__ in, typename Element<kDst>::Word *__restrict__ out, uint64_t batches,
+                     const View view, const Transposition plan) {
+  grid_dependency_sync();
+  __shared__ Word tile[32][33];
+  const uint32_t inner_axis = view.rank - 1;
+  const uint64_t inner = view.dims[inner_axis], across = view.dims[plan.axis];
+  const uint64_t tiles_inner = (inner + 31) / 32, tiles_across = (across + 31) / 32;
+  const uint32_t tx = threadIdx.x & 31, ty = threadIdx.x >> 5;  // 32 x 8
+  const uint64_t units = batches * tiles_inner * tiles_across;
+  for (uint64_t unit = blockIdx.x; unit < units; unit += gridDim.x) {
+    // index arithmetic in 32 bits whenever the number of tiles allows: a tile is only 1024 elements
+    Index rest = static_cast<Index>(unit);
+    const Index after_inner = rest / static_cast<Index>(tiles_inner);
+    const uint64_t tile_inner = rest - after_inner * static_cast<Index>(tiles_inner);
+    rest = after_inner / static_cast<Index>(tiles_across);
+    const uint64_t tile_across = after_inner - rest * static_cast<Index>(tiles_across);
+    int64_t source = 0;
+    uint64_t destination = 0;
+#pragma unroll
+    for (int d = 6; d >= 0; --d) {  // the batch index runs over every axis but the two of the tile
+      if (d < static_cast<int>(inner_axis) && d != static_cast<int>(plan.axis)) {
+        const Index outer = rest / static_cast<Index>(view.dims[d]);
+        const uint64_t coordinate = rest - outer * static_cast<Index>(view.dims[d]);
+        source += static_cast<int64_t>(coordinate) * view.strides[d];
+        destination += coordinate * plan.dense[d];
+        rest = outer;
+      }
+    }
+#pragma unroll
+    for (int step = 0; step < 4; ++step) {
+      const uint64_t j = tile_inner * 32 + ty + step * 8, c = tile_across * 32 + tx;
+      if (j < inner && c < across)
+        tile[ty + step * 8][tx] = *reinterpret_cast<const Word *>(in + source + static_cast<int64_t>(j) * view.strides[inner_axis] +
+                                                                  static_cast<int64_t>(c) * view.strides[plan.axis]);
+    }
+    __syncthreads();
+#pragma unroll
+    for (int step = 0; step < 4; ++step) {
+      const uint64_t c = tile_across * 32 + ty + step * 8, j = tile_inner * 32 + tx;
+      if (j < inner && c < across) {
+        const Word word = tile[tx][ty + step * 8];
+        const uint64_t at = destination + c * plan.dense[plan.axis] + j;
+        if constexpr (kCopy) out[at] = word;
+        else out[at] = static_cast<typename Element<kDst>::Word>(convert<kSrc, kDst>(word));
+      }
+    }
+    __syncthreads();
+  }
+}
+
 template <int kSrc, int kDst, bool kCopy>
 int launch_strided(cudaStream_t stream, const void *in, void *out, uint64_t count, const View &view) {
   using Word = typename Element<kSrc>::Word;
   using Out = typename Element<kDst>::Word;
+  if (view.rank >= 2 && view.dims[view.rank - 1] >= 32 && view.strides[view.rank - 1] != static_cast<int64_t>(sizeof(Word))) {
+    Transposition plan{};
+    uint64_t dense = 1;
+    for (int d = static_cast<int>(view.rank) - 1; d >= 0; --d) {
+      plan.dense[d] = dense;
+      dense *= view.dims[d];
+    }
+    int axis = -1;
+    for (uint32_t d = 0; d + 1 < view.rank; ++d)
+      if (view.strides[d] == static_cast<int64_t>(sizeof(Word)) && view.dims[d] >= 32) axis = static_cast<int>(d);
+    if (axis >= 0) {
+      plan.axis = static_cast<uint32_t>(axis);
+      const uint64_t inner = view.dims[view.rank - 1], across = view.dims[axis];
+      const uint64_t batches = count / (inner * across);
+      const uint64_t units = batches * ((inner + 31) / 32) * ((across + 31) / 32);
+      const unsigned tile_grid = clamp_grid(units, static_cast<uint64_t>(sm_count()) * kCtasPerSm);
+      auto tiles = units <= 0xffffffffull ? strided_tiles_kernel<Word, kSrc, kDst, kCopy, uint32_t>
+                                          : strided_tiles_kernel<Word, kSrc, kDst, kCopy, uint64_t>;
+      return launch(tiles, dim3(tile_grid), dim3(256), 0, stream, static_cast<const unsigned char *>(in),
+                    static_cast<Out *>(out), batches, view, plan);
+    }
+  }
   if (view.rank != 0 && view.dims[view.rank - 1] >= 256) {
     const uint64_t inner = view.dims[view.rank - 1], runs = count / inner;
     const uint64_t units = runs * ((inner + kThreads * 8 - 1) / (kThreads * 8));

@@ -97,6 +97,11 @@ def test_strided_cast_long_inner_runs(oracle, pair):
             "inner_broadcast": t[:, :1, :, :1].expand(4, 3, 9, 1000),
             "one_axis": t[2, 7, 3, 40:],
             "ragged_segments": t[0, :2, :, : 2048 // 3 + 1],
+            # transposing views: the innermost axis is strided and another one is contiguous (tiled path)
+            "transpose_with_batches": t.transpose(-1, -3),
+            "transpose_2d": t[0, :, 3, :].t(),
+            "transpose_ragged_tiles": t[1, :37, :, :45].permute(2, 1, 0),
+            "transpose_of_a_slice": t[2, 5:200, 1, 3:500:2].t(),
         }
 
     for (name, d_view), h_view in zip(long_views(device).items(), long_views(torch.from_numpy(host)).values()):
