@@ -431,12 +431,12 @@ def other_ops(torch, peak_gbs, only=None, iterations=40):
         scratch = ops.make_logits_workspace(dev, rows, cols)
         ms = time_op(torch, lambda i: lib.hyle_b200_logits_reduce_f32(
             stream, logits[i].data_ptr(), rows, cols, lse.data_ptr(), probs[i].data_ptr(), idx.data_ptr(),
-            val.data_ptr(), scratch.data_ptr(), scratch.numel()), sets, max(1, iterations // 2))
+            val.data_ptr(), scratch.data_ptr(), scratch.numel(), None), sets, max(1, iterations // 2))
         report("logits_reduce_f32", "256x151936", rows * cols, rows * cols * 6 + rows * 12, ms, sets)
         if os.environ.get("HYLE_B200_LOGITS_CLUSTER_KERNEL"):  # the other kernel, for comparison
             ms = time_op(torch, lambda i: lib.hyle_b200_logits_reduce_f32(
                 stream, logits[i].data_ptr(), rows, cols, lse.data_ptr(), probs[i].data_ptr(), idx.data_ptr(),
-                val.data_ptr(), None, 0), sets, max(1, iterations // 2))
+                val.data_ptr(), None, 0, None), sets, max(1, iterations // 2))
             report("logits_reduce_f32_cluster_kernel", "256x151936", rows * cols, rows * cols * 6 + rows * 12, ms, sets)
         del logits, probs, scratch
     torch.cuda.empty_cache()

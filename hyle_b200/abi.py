@@ -31,9 +31,10 @@ STATUS_EXCHANGE_TIMEOUT = 2
 STATUS_INVALID_FP8_INPUT = 4
 STATUS_INVALID_CATEGORICAL_ROW = 8
 STATUS_SCAN_OVERFLOW = 16
+STATUS_STREAM_WAIT_TIMEOUT = 32
 EXCHANGE_MAX_RANKS, EXCHANGE_MAILBOX_BYTES, EXCHANGE_HANDLE_BYTES = 8, 256, 64
 
-ABI_VERSION = 14
+ABI_VERSION = 15
 
 _p = ctypes.c_void_p
 _u64 = ctypes.c_uint64
@@ -54,8 +55,12 @@ SIGNATURES = {
     "hyle_b200_layer_norm_bf16": (_i, [_p, _p, _p, _p, _p, _u64, _u64, _f]),
     "hyle_b200_swiglu_bf16": (_i, [_p, _p, _p, _p, _u64, _u64, _u64, _u64]),
     "hyle_b200_logits_workspace_bytes": (_u64, [_u64, _u64]),
-    "hyle_b200_logits_reduce_f32": (_i, [_p, _p, _u64, _u64, _p, _p, _p, _p, _p, _u64]),
-    "hyle_b200_softmax_f32": (_i, [_p, _i, _p, _p, _u64, _u64, _p, _u64]),
+    "hyle_b200_logits_reduce_f32": (_i, [_p, _p, _u64, _u64, _p, _p, _p, _p, _p, _u64, _p]),
+    "hyle_b200_logits_reduce_f32_tuned": (_i, [_p, _p, _u64, _u64, _p, _p, _p, _p, _p, _u64, _p, _p]),
+    "hyle_b200_logits_stream_plan": (_i, [_u64, _u64, _p, _p]),
+    "hyle_b200_logits_stream_task": (_i, [_u64, _u32, _u32, _u64, _p, _p, _p]),
+    "hyle_b200_softmax_f32": (_i, [_p, _i, _p, _p, _u64, _u64, _p, _u64, _p]),
+    "hyle_b200_workspace_clear": (_i, [_p, _p, _u64]),
     "hyle_b200_select": (_i, [_p, _i, _p, _p, _p, _p, _u64, _u64, _u64]),
     "hyle_b200_cast": (_i, [_p, _i, _i, _p, _p, _u64]),
     "hyle_b200_masked_softmax_f16": (_i, [_p, _p, _p, _u64, _f, _p, _u64, _u64]),
@@ -80,6 +85,21 @@ SIGNATURES = {
     "hyle_b200_random_bits": (_i, [_p, _p, _u64, _u32, _p]),
     "hyle_b200_categorical": (_i, [_p, _i, _p, _p, _u64, _u64, _p, _p, _p]),
 }
+
+
+
+class StreamTuning(ctypes.Structure):
+    """hyle_b200_stream_tuning: zero fields mean "choose"."""
+    _fields_ = [("chunk_vectors", ctypes.c_int32), ("window_rows", _u32), ("help_after_polls", _u32),
+                ("ctas_per_sm", ctypes.c_int32)]
+
+
+class StreamPlan(ctypes.Structure):
+    """hyle_b200_stream_plan."""
+    _fields_ = [("chunk_vectors", ctypes.c_int32), ("chunks_per_row", _u32), ("chunk_values", _u32),
+                ("window_rows", _u32), ("fixed_tasks_per_cta", _u32), ("ctas_per_sm", ctypes.c_int32),
+                ("grid", _u32), ("help_after_polls", _u32)]
+
 
 _library = None
 

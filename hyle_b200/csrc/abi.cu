@@ -31,3 +31,9 @@ extern "C" const char *hyle_b200_result_string(int result) {
     default: return cudaGetErrorString(static_cast<cudaError_t>(result));
   }
 }
+
+extern "C" int hyle_b200_workspace_clear(hyle_b200_stream_t stream, void *workspace, uint64_t bytes) {
+  if (bytes == 0) return HYLE_B200_OK;
+  if (workspace == nullptr) return HYLE_B200_INVALID_VALUE;
+  return static_cast<int>(cudaMemsetAsync(workspace, 0, bytes, reinterpret_cast<cudaStream_t>(stream)));
+}

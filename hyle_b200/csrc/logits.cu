@@ -45,7 +45,16 @@ struct LogitsParams {
   void *out;       // probabilities / log-probabilities, or nullptr
   int32_t *index;
   float *value;
+  uint32_t *status;  // device status word (may be null): HYLE_B200_STATUS_STREAM_WAIT_TIMEOUT
 };
+
+// TopK's value output is the ELEMENT at the winning index (src/simd/sort/top_k.cc returns
+// scores[index]).  The folded maximum equals it except in sign: the fold orders -0 below +0, so a row
+// whose first maximal element is -0 with a +0 later folds to +0 while the winner is the -0 element.
+// One load that hits L2 (the row was just read).
+__device__ __forceinline__ float element_at(const LogitsParams &p, uint64_t row, uint32_t index, float folded) {
+  return index < p.cols ? p.in[row * p.cols + index] : folded;
+}
 
 struct Best {
   float value;
@@ -332,7 +341,7 @@ logits_kernel(const LogitsParams p) {
       if (!has_nan) {
         if (t == 0) {
           if (p.index != nullptr) p.index[row] = static_cast<int32_t>(s_row_sum.index);
-          if (p.value != nullptr) p.value[row] = maximum;
+          if (p.value != nullptr) p.value[row] = element_at(p, row, s_row_sum.index, maximum);
         }
       } else {
         rescan_argmax(p.in + row * p.cols, p.cols, p.index != nullptr ? p.index + row : nullptr,
@@ -563,7 +572,7 @@ logits_regs_kernel(const LogitsParams p) {
       if (p.lse != nullptr) p.lse[row] = shift;
       if (want_index && !has_nan) {
         if (p.index != nullptr) p.index[row] = static_cast<int32_t>(best_index);
-        if (p.value != nullptr) p.value[row] = maximum;
+        if (p.value != nullptr) p.value[row] = element_at(p, row, best_index, maximum);
       }
     }
 
@@ -626,14 +635,28 @@ logits_regs_kernel(const LogitsParams p) {
 // ================================================================================================
 constexpr int kStreamThreads = 256;
 constexpr int kStreamWarps = kStreamThreads / 32;
-constexpr int kStreamVectors = 10;
-constexpr uint32_t kStreamChunk = kStreamThreads * kStreamVectors * 4;  // values per chunk, at most
-constexpr uint32_t kStreamMaxChunks = 32;                               // one partial per lane
-// Rows between a row's two passes.  Measured at 256 / 1024 rows of 151 936: 32 -> 0.71 / 0.88 of the
-// copy peak (second-pass tasks wait for partials), 40..64 -> 0.77-0.79 / 0.94-0.95, 96 -> 0.72 / 0.83
-// (the window no longer stays in L2).
-constexpr uint32_t kStreamWindow = 64;
+// A task's chunk is kVectors float4 per thread, held in registers for the length of the task.  Two
+// sizes are built: 10 (10 240 values, 40 KB of staging, 4 CTAs per SM) for large batches, where the
+// per-task overhead counts, and 5 (5120 values, 20 KB, 4 CTAs per SM) for small ones, where the
+// launch's ramp and its write-only tail count: half-size tasks halve both.
+constexpr int kStreamVectorsLarge = 10;
+constexpr int kStreamVectorsSmall = 5;
+__host__ __device__ constexpr uint32_t stream_chunk_values(int vectors) { return kStreamThreads * vectors * 4; }
+constexpr size_t stream_stage_bytes(int vectors) { return static_cast<size_t>(kStreamThreads) * vectors * sizeof(float4); }
+constexpr int stream_ctas_per_sm(int) { return 4; }
+constexpr uint32_t kStreamMaxChunks = 32;  // one partial per lane
+constexpr uint64_t kStreamSmallBatchRows = 512;  // up to here the small chunk is taken (when the row fits 32 of them)
+// Rows between a row's two passes must cover the tasks in flight (two per resident CTA), or
+// second-pass tasks find their partials missing; and must stay inside L2 (126 MB).  Measured at
+// 256 / 1024 rows of 151 936 with 10 240-value chunks: 32 rows -> 0.71 / 0.88 of the copy peak,
+// 40..64 -> 0.77-0.79 / 0.94-0.95, 96 -> 0.72 / 0.83 (the window no longer stays in L2).
+constexpr uint32_t kStreamWindowMax = 64;
+constexpr uint64_t kStreamWindowBytes = 40ull << 20;  // of f32 logits between the passes
 constexpr uint64_t kStreamMinRows = 64;  // below this the cluster kernel is as fast or faster
+// A second-pass warp polls this often for a partial before it computes the missing one itself, and
+// this often again before it gives up (which needs a lost store: it cannot be waiting for a CTA that
+// is not running, see the kernel).
+constexpr uint32_t kStreamHelpAfter = 1u << 12;
 constexpr uint32_t kStreamPollLimit = 1u << 22;
 constexpr uint64_t kStreamHeaderBytes = 64;
 
@@ -656,14 +679,44 @@ struct StreamParams {
   uint32_t chunks;  // per row
   uint32_t chunk;   // values per chunk, a multiple of 16
   uint32_t window;  // rows between the passes, at most p.rows
+  uint32_t fixed;   // tasks per CTA taken by position (0..2) instead of from the counter
+  uint32_t help_after;  // polls before a second-pass warp reduces a missing chunk itself
   unsigned long long *next_task;
   uint32_t *ticket;
   uint32_t *epoch;          // launches so far on this workspace; tag = epoch + 1, never 0
   StreamPartial *partials;  // [rows][chunks]
 };
 
-__host__ __device__ inline uint32_t stream_chunks(uint64_t cols) {
-  return static_cast<uint32_t>((cols + kStreamChunk - 1) / kStreamChunk);
+// Position `task` of the ordered list -> (pass, row, chunk):
+//   P1(0) ... P1(w-1), P2(0), P1(w), P2(1), P1(w+1), ..., P2(rows-w) ... P2(rows-1)      (each entry = all its chunks)
+__host__ __device__ inline StreamTask stream_decode(uint64_t task, uint64_t rows, uint32_t chunks, uint32_t window) {
+  const uint64_t paired = rows - window;  // rows whose first pass is interleaved with a second pass
+  StreamTask r;
+  if (task >= 2 * rows * chunks) {
+    r.row = 0;
+    r.chunk_id = 0;
+    r.pass = kStreamEnd;
+    return r;
+  }
+  const uint64_t entry = task / chunks;
+  r.chunk_id = static_cast<uint32_t>(task - entry * chunks);
+  if (entry < window) {
+    r.pass = kStreamFirst;
+    r.row = entry;
+  } else if (entry < window + 2 * paired) {
+    const bool second = ((entry - window) & 1) == 0;
+    r.pass = second ? kStreamSecond : kStreamFirst;
+    r.row = (entry - window) / 2 + (second ? 0 : window);
+  } else {
+    r.pass = kStreamSecond;
+    r.row = paired + (entry - window - 2 * paired);
+  }
+  return r;
+}
+
+__host__ __device__ inline uint32_t stream_chunks(uint64_t cols, int vectors) {
+  const uint64_t chunk = stream_chunk_values(vectors);
+  return static_cast<uint32_t>((cols + chunk - 1) / chunk);
 }
 
 // L2 policies for the two passes: a first-pass line should survive until the second pass reads it
@@ -728,10 +781,51 @@ __device__ __forceinline__ unsigned long long load_relaxed(const unsigned long l
   return v;
 }
 constexpr uint32_t kStreamLoadPollLimit = 1u << 20;  // x up to 20 us each
-constexpr size_t kStreamStageBytes = static_cast<size_t>(kStreamThreads) * kStreamVectors * sizeof(float4);  // 40 KB
 
-template <int kMode, int kFull>
-__global__ void __launch_bounds__(kStreamThreads, 4)
+// One warp reduces chunk `chunk_id` of `row` by itself, from global memory, and publishes the partial.
+// The slow path of a second-pass task whose partial is missing: whoever holds the first-pass task
+// may not be running (a grid larger than what is resident), so the waiter must not depend on it.
+// Two writers of one partial store the same maximum and index and sums that agree to rounding, and
+// each word is stored whole, so a reader may combine words of either.
+// (Scalars by value: a reference to the kernel's parameter struct would make the caller copy it to
+// its stack.)
+__device__ __noinline__ void stream_help_chunk(const float *row_in, uint32_t cols, uint32_t chunk_values, uint32_t chunk_id,
+                                               StreamPartial *out, unsigned long long tag, bool want_index) {
+  const int lane = threadIdx.x & 31;
+  const uint32_t begin = chunk_id * chunk_values;
+  const uint32_t vectors = (min(begin + chunk_values, cols) - begin) / 4;
+  const float4 *src = reinterpret_cast<const float4 *>(row_in + begin);
+  const uint64_t policy = policy_evict_last();
+  float maximum = -CUDART_INF_F;
+  for (uint32_t v = lane; v < vectors; v += 32) {
+    const float4 x = load_hinted(src + v, policy);
+    maximum = max_nan(maximum, max_nan(max_nan(x.x, x.y), max_nan(x.z, x.w)));
+  }
+  maximum = warp_max_nan(maximum);
+  const float reference = maximum == -CUDART_INF_F ? 0.0f : maximum;
+  const float neg_c = -__fmul_rn(reference, kLog2e);
+  float sum = 0.0f;
+  uint32_t index = kNoIndex;
+  for (uint32_t v = lane; v < vectors; v += 32) {
+    const float4 x = load_hinted(src + v, policy);
+    sum += (exp2_approx(fmaf(x.x, kLog2e, neg_c)) + exp2_approx(fmaf(x.y, kLog2e, neg_c))) +
+           (exp2_approx(fmaf(x.z, kLog2e, neg_c)) + exp2_approx(fmaf(x.w, kLog2e, neg_c)));
+    if (want_index && index == kNoIndex) {
+      const uint32_t base = begin + v * 4;
+      index = x.x == maximum ? base : x.y == maximum ? base + 1 : x.z == maximum ? base + 2 : x.w == maximum ? base + 3 : kNoIndex;
+    }
+  }
+  sum = warp_sum(sum);
+  index = __reduce_min_sync(kFullMask, index);
+  if (lane == 0) {
+    store_relaxed(&out->maximum, tag | __float_as_uint(maximum));
+    store_relaxed(&out->sum, tag | __float_as_uint(sum));
+    store_relaxed(&out->index, tag | index);
+  }
+}
+
+template <int kMode, int kVectors, int kFull>
+__global__ void __launch_bounds__(kStreamThreads, stream_ctas_per_sm(kVectors))
 logits_stream_kernel(const StreamParams s) {
   // What needs no global memory (task decoding, barrier set-up) runs before the wait for the
   // previous grid: it overlaps that grid's tail.
@@ -747,34 +841,12 @@ logits_stream_kernel(const StreamParams s) {
   const float neg_inf = -CUDART_INF_F;
   const WarpEntry nothing{neg_inf, 0.0f, kNoIndex, 0u};
 
-  // Position `task` of the ordered list -> (pass, row, chunk).  Thread 0 does this (a 64-bit
-  // division) two tasks ahead, while the CTA works.
-  auto decode = [&](uint64_t task) {
-    const uint64_t paired = p.rows - s.window;  // rows whose first pass is interleaved with a second pass
-    StreamTask r;
-    if (task >= 2 * p.rows * s.chunks) {
-      r.row = 0;
-      r.chunk_id = 0;
-      r.pass = kStreamEnd;
-      return r;
-    }
-    const uint64_t entry = task / s.chunks;
-    r.chunk_id = static_cast<uint32_t>(task - entry * s.chunks);
-    if (entry < s.window) {
-      r.pass = kStreamFirst;
-      r.row = entry;
-    } else if (entry < s.window + 2 * paired) {
-      const bool second = ((entry - s.window) & 1) == 0;
-      r.pass = second ? kStreamSecond : kStreamFirst;
-      r.row = (entry - s.window) / 2 + (second ? 0 : s.window);
-    } else {
-      r.pass = kStreamSecond;
-      r.row = paired + (entry - s.window - 2 * paired);
-    }
-    return r;
-  };
-  // Every CTA's first two tasks are fixed (no atomic before the first load); the rest are claimed.
-  auto claim = [&]() { return 2ull * gridDim.x + atomicAdd(s.next_task, 1ull); };
+  // One thread decodes a list position (a 64-bit division) two tasks ahead, while the CTA works.
+  auto decode = [&](uint64_t task) { return stream_decode(task, p.rows, s.chunks, s.window); };
+  // A CTA's first `fixed` tasks are given by its position (no atomic before the first load), the
+  // rest are claimed.  The host keeps fixed tasks inside the first-pass head of the list: a fixed
+  // second-pass task would start beside the first pass it depends on.
+  auto claim = [&]() { return static_cast<unsigned long long>(s.fixed) * gridDim.x + atomicAdd(s.next_task, 1ull); };
   // The chunk of `task` -> shared memory, one bulk copy issued by one thread.
   auto issue_load = [&](const StreamTask &task) {
     if (task.pass == kStreamEnd) return;
@@ -788,11 +860,15 @@ logits_stream_kernel(const StreamParams s) {
   if (t == 0) {
     mbarrier_init(&s_full, 1);
     asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
-    s_tasks[0] = decode(blockIdx.x);
+    if (s.fixed >= 1u) s_tasks[0] = decode(blockIdx.x);
   }
-  if (t == 64) s_tasks[1] = decode(static_cast<uint64_t>(gridDim.x) + blockIdx.x);
+  if (t == 64 && s.fixed >= 2u) s_tasks[1] = decode(static_cast<uint64_t>(gridDim.x) + blockIdx.x);
   asm volatile("griddepcontrol.wait;" ::: "memory");  // the previous grid has completed and flushed
-  if (t == 0) issue_load(s_tasks[0]);
+  if (t == 0) {
+    if (s.fixed == 0u) s_tasks[0] = decode(claim());
+    issue_load(s_tasks[0]);
+  }
+  if (t == 64 && s.fixed < 2u) s_tasks[1] = decode(claim());
   const unsigned long long tag = static_cast<unsigned long long>(*s.epoch + 1u) << 32;
   __syncthreads();
 
@@ -808,13 +884,53 @@ logits_stream_kernel(const StreamParams s) {
     const uint32_t begin = chunk_id * s.chunk;
     const uint32_t vectors = (min(begin + s.chunk, p.cols) - begin) / 4;
 
+    // Second pass: the row's partials, fetched BEFORE the chunk is taken into registers, so that the
+    // rare slow path below runs with few live registers (and the chunk's copy stays in flight).
+    WarpEntry mine = nothing;
+    bool complete = true;
+    if (second) {
+      // Every warp fetches the row's partials itself, one per lane, and polls until all carry this
+      // launch's tag.  They were written `window` rows ago: the first look almost always succeeds.
+      // A partial still missing after kStreamHelpAfter looks may belong to a CTA that is not running
+      // (the grid is sized to be co-resident, but nothing guarantees it: another kernel may hold SMs),
+      // so the warp then reduces its share of the missing chunks ITSELF, from global memory, and
+      // polls on for the chunks its sibling warps are reducing.  Nothing here waits for a CTA other
+      // than its own, so the kernel completes, with right results, whatever is resident.
+      const StreamPartial *in = s.partials + row * s.chunks + (lane < s.chunks ? lane : 0);
+      unsigned long long m = 0, q = 0, i = 0;
+      auto look = [&]() {
+        if (lane >= s.chunks) return true;
+        m = load_relaxed(&in->maximum);
+        q = load_relaxed(&in->sum);
+        i = load_relaxed(&in->index);
+        return (m ^ tag) >> 32 == 0 && (q ^ tag) >> 32 == 0 && (i ^ tag) >> 32 == 0;
+      };
+      bool have = look();
+      for (uint32_t polls = 0; !__all_sync(kFullMask, have) && polls < s.help_after; ++polls)
+        if (!have) have = look();
+      uint32_t missing = __ballot_sync(kFullMask, !have);
+      if (missing != 0u) {  // warp-uniform, rare
+        for (uint32_t rest = missing; rest != 0u; rest &= rest - 1u) {
+          const uint32_t chunk = __ffs(rest) - 1;
+          if (chunk % kStreamWarps == static_cast<uint32_t>(warp))
+            stream_help_chunk(p.in + row * p.cols, p.cols, s.chunk, chunk, s.partials + row * s.chunks + chunk, tag, want_index);
+        }
+        for (uint32_t polls = 0; !__all_sync(kFullMask, have) && polls < kStreamPollLimit; ++polls)
+          if (!have) have = look();
+      }
+      complete = __all_sync(kFullMask, have);
+      if (lane < s.chunks)
+        mine = WarpEntry{__uint_as_float(static_cast<uint32_t>(m)), __uint_as_float(static_cast<uint32_t>(q)),
+                         static_cast<uint32_t>(i), 0u};
+    }
+
     // The chunk has been on its way since the previous task; take it into registers.
     bool landed = mbarrier_try_wait(&s_full, phase);
     for (uint32_t polls = 0; !landed && polls < kStreamLoadPollLimit; ++polls) landed = mbarrier_try_wait(&s_full, phase);
     phase ^= 1u;
-    float4 x[kStreamVectors];
+    float4 x[kVectors];
 #pragma unroll
-    for (int j = 0; j < kStreamVectors; ++j)
+    for (int j = 0; j < kVectors; ++j)
       x[j] = (j < kFull || j * kStreamThreads + t < vectors) ? stream_stage[j * kStreamThreads + t]
                                                              : make_float4(neg_inf, neg_inf, neg_inf, neg_inf);
     if (!landed) x[0].x = CUDART_NAN_F;  // the load never completed: the row is reported as NaN
@@ -829,7 +945,7 @@ logits_stream_kernel(const StreamParams s) {
       float thread_max = neg_inf;
       int best_slot = 0;
 #pragma unroll
-      for (int j = 0; j < kStreamVectors; ++j) {
+      for (int j = 0; j < kVectors; ++j) {
         const float slot_max = max_nan(max_nan(x[j].x, x[j].y), max_nan(x[j].z, x[j].w));
         if (slot_max > thread_max) best_slot = j;
         thread_max = max_nan(thread_max, slot_max);
@@ -849,7 +965,7 @@ logits_stream_kernel(const StreamParams s) {
       const float neg_c = -__fmul_rn(reference, kLog2e);
       float thread_sum = 0.0f;
 #pragma unroll
-      for (int j = 0; j < kStreamVectors; ++j)
+      for (int j = 0; j < kVectors; ++j)
         thread_sum += (exp2_approx(fmaf(x[j].x, kLog2e, neg_c)) + exp2_approx(fmaf(x[j].y, kLog2e, neg_c))) +
                       (exp2_approx(fmaf(x[j].z, kLog2e, neg_c)) + exp2_approx(fmaf(x[j].w, kLog2e, neg_c)));
       const float warp_total = warp_sum(thread_sum);
@@ -865,24 +981,7 @@ logits_stream_kernel(const StreamParams s) {
         }
       }
     } else {
-      // Every warp fetches the row's partials itself, one per lane, and waits (bounded) until all
-      // carry this launch's tag.  They were written `window` rows ago: the first look succeeds.
-      WarpEntry mine = nothing;
-      bool complete = true;
-      if (lane < s.chunks) {
-        const StreamPartial *in = s.partials + row * s.chunks + lane;
-        unsigned long long m = load_relaxed(&in->maximum), q = load_relaxed(&in->sum), i = load_relaxed(&in->index);
-        for (uint32_t polls = 0; ((m ^ tag) >> 32 != 0 || (q ^ tag) >> 32 != 0 || (i ^ tag) >> 32 != 0) && polls < kStreamPollLimit;
-             ++polls) {
-          m = load_relaxed(&in->maximum);
-          q = load_relaxed(&in->sum);
-          i = load_relaxed(&in->index);
-        }
-        complete = (m ^ tag) >> 32 == 0 && (q ^ tag) >> 32 == 0 && (i ^ tag) >> 32 == 0;
-        mine = WarpEntry{__uint_as_float(static_cast<uint32_t>(m)), __uint_as_float(static_cast<uint32_t>(q)),
-                         static_cast<uint32_t>(i), 0u};
-      }
-      complete = __all_sync(kFullMask, complete);
+      if ((!complete || !landed) && t == 0 && p.status != nullptr) atomicOr(p.status, HYLE_B200_STATUS_STREAM_WAIT_TIMEOUT);
       const Combined all = combine(mine);
       const float maximum = all.maximum, total_sum = all.total, row_c = __fmul_rn(all.maximum, kLog2e);
       const bool valid = complete && landed && maximum > neg_inf && maximum < CUDART_INF_F;  // false for NaN too
@@ -894,7 +993,7 @@ logits_stream_kernel(const StreamParams s) {
         if (p.lse != nullptr) p.lse[row] = shift;
         if (want_index && !has_nan && complete) {
           if (p.index != nullptr) p.index[row] = static_cast<int32_t>(all.index);
-          if (p.value != nullptr) p.value[row] = maximum;
+          if (p.value != nullptr) p.value[row] = element_at(p, row, all.index, maximum);
         }
       }
       const float inverse = valid ? __fdiv_rn(1.0f, total_sum) : nan;
@@ -902,7 +1001,7 @@ logits_stream_kernel(const StreamParams s) {
       if constexpr (kMode == kProbsBf16) {
         uint2 *dst = reinterpret_cast<uint2 *>(static_cast<unsigned short *>(p.out) + row * p.cols + begin) + t;
 #pragma unroll
-        for (int j = 0; j < kStreamVectors; ++j) {
+        for (int j = 0; j < kVectors; ++j) {
           if (j < kFull || j * kStreamThreads + t < vectors)
             st_stream(dst + j * kStreamThreads,
                       make_uint2(pack_bf16x2(exp2_approx(fmaf(x[j].x, kLog2e, neg_row_c)) * inverse,
@@ -913,7 +1012,7 @@ logits_stream_kernel(const StreamParams s) {
       } else {
         float4 *dst = reinterpret_cast<float4 *>(static_cast<float *>(p.out) + row * p.cols + begin) + t;
 #pragma unroll
-        for (int j = 0; j < kStreamVectors; ++j) {
+        for (int j = 0; j < kVectors; ++j) {
           if (j < kFull || j * kStreamThreads + t < vectors) {
             float4 o;
             if constexpr (kMode == kProbsF32)
@@ -1018,40 +1117,132 @@ int resident_clusters(int cluster) {
   return cached[slot][device];
 }
 
-uint64_t stream_workspace_bytes(uint64_t rows, uint64_t cols) {
-  return kStreamHeaderBytes + rows * stream_chunks(cols) * sizeof(StreamPartial);
+// What the streaming kernel will do for a shape: chunk size, window, grid.  Host arithmetic only.
+struct StreamPlan {
+  int vectors = 0;        // float4 per thread and task (0 = the shape is not eligible)
+  uint32_t chunks = 0;    // per row
+  uint32_t chunk = 0;     // values per chunk, a multiple of 16
+  uint32_t window = 0;    // rows between the passes
+  uint32_t fixed = 0;     // tasks per CTA taken by position
+  uint32_t help_after = kStreamHelpAfter;
+  int ctas_per_sm = 0;
+  unsigned grid = 0;
+};
+
+inline bool stream_eligible(uint64_t rows, uint64_t cols, int vectors) {
+  return rows >= kStreamMinRows && cols % 16 == 0 && cols >= kStreamThreads * 4 && cols <= 0x7fffffffull &&
+         stream_chunks(cols, vectors) <= kStreamMaxChunks;
 }
 
-template <int kMode>
-int launch_stream(cudaStream_t stream, const LogitsParams &p, void *workspace) {
+// Partials for the finest chunking the shape may be given.
+uint64_t stream_workspace_bytes(uint64_t rows, uint64_t cols) {
+  const int vectors = stream_chunks(cols, kStreamVectorsSmall) <= kStreamMaxChunks ? kStreamVectorsSmall : kStreamVectorsLarge;
+  return kStreamHeaderBytes + rows * stream_chunks(cols, vectors) * sizeof(StreamPartial);
+}
+
+// CTAs of one instantiation that fit an SM, by the occupancy calculator, cached per device.
+template <class Kernel>
+int stream_resident_ctas(Kernel kernel, size_t shared_bytes, int slot) {
+  static int cached[8][64] = {};
+  int device = 0;
+  cudaGetDevice(&device);
+  if (device < 0 || device >= 64) device = 0;
+  if (cached[slot][device] == 0) {
+    int count = 0;
+    if (cudaOccupancyMaxActiveBlocksPerMultiprocessor(&count, kernel, kStreamThreads, shared_bytes) != cudaSuccess || count <= 0)
+      count = 1;
+    cached[slot][device] = count;
+  }
+  return cached[slot][device];
+}
+
+// `resident` = CTAs per SM the chosen instantiation can hold.  `tuning` may be null.
+StreamPlan make_stream_plan(uint64_t rows, uint64_t cols, const hyle_b200_stream_tuning *tuning, int sms, int resident_small,
+                            int resident_large) {
+  StreamPlan plan{};
+  int vectors = tuning != nullptr ? tuning->chunk_vectors : 0;
+  if (vectors != 0 && vectors != kStreamVectorsSmall && vectors != kStreamVectorsLarge) return plan;
+  if (vectors == 0)
+    vectors = rows <= kStreamSmallBatchRows && stream_eligible(rows, cols, kStreamVectorsSmall) ? kStreamVectorsSmall
+                                                                                                  : kStreamVectorsLarge;
+  if (!stream_eligible(rows, cols, vectors)) return plan;
+  plan.vectors = vectors;
+  plan.chunks = stream_chunks(cols, vectors);
+  plan.chunk = static_cast<uint32_t>((cols / plan.chunks + 15) / 16 * 16);
+  if (static_cast<uint64_t>(plan.chunk) * plan.chunks < cols) plan.chunk += 16;
+  const int resident = vectors == kStreamVectorsSmall ? resident_small : resident_large;
+  int per_sm = stream_ctas_per_sm(vectors);
+  if (tuning != nullptr && tuning->ctas_per_sm > 0 && tuning->ctas_per_sm < per_sm) per_sm = tuning->ctas_per_sm;
+  if (per_sm > resident) per_sm = resident;
+  plan.ctas_per_sm = per_sm;
+  const uint64_t tasks = 2 * rows * plan.chunks;
+  plan.grid = clamp_grid(tasks, static_cast<uint64_t>(sms) * per_sm);
+  // window: cover the tasks in flight (one computing, one loading per CTA), stay inside L2
+  uint64_t window = (2ull * plan.grid + plan.chunks - 1) / plan.chunks;
+  const uint64_t by_bytes = kStreamWindowBytes / (cols * sizeof(float));
+  if (window > by_bytes) window = by_bytes;
+  if (window > kStreamWindowMax) window = kStreamWindowMax;
+  if (window < 8) window = 8;
+  if (tuning != nullptr && tuning->window_rows != 0) window = tuning->window_rows;
+  if (window > rows) window = rows;
+  plan.window = static_cast<uint32_t>(window);
+  const uint64_t head = window * plan.chunks;  // first-pass tasks before the first second-pass task
+  plan.fixed = 2ull * plan.grid <= head ? 2u : plan.grid <= head ? 1u : 0u;
+  if (tuning != nullptr && tuning->help_after_polls != 0) plan.help_after = tuning->help_after_polls;
+  return plan;
+}
+
+template <int kMode, int kVectors>
+int launch_stream_sized(cudaStream_t stream, const LogitsParams &p, void *workspace, const hyle_b200_stream_tuning *tuning) {
+  constexpr int kAlmost = kVectors - 1;
+  constexpr size_t kStage = stream_stage_bytes(kVectors);
+  const int slot = kMode * 2 + (kVectors == kStreamVectorsSmall ? 0 : 1);
+  const int resident = stream_resident_ctas(logits_stream_kernel<kMode, kVectors, 0>, kStage, slot);
+  hyle_b200_stream_tuning chosen{};
+  if (tuning != nullptr) chosen = *tuning;
+  chosen.chunk_vectors = kVectors;
+  const StreamPlan plan = make_stream_plan(p.rows, p.cols, &chosen, sm_count(), resident, resident);
+  if (plan.vectors == 0) return HYLE_B200_INVALID_VALUE;
   StreamParams s{};
   s.p = p;
-  s.chunks = stream_chunks(p.cols);
-  s.chunk = (p.cols / s.chunks + 15) / 16 * 16;
-  if (static_cast<uint64_t>(s.chunk) * s.chunks < p.cols) s.chunk += 16;
-  s.window = static_cast<uint32_t>(p.rows < kStreamWindow ? p.rows : kStreamWindow);
+  s.chunks = plan.chunks;
+  s.chunk = plan.chunk;
+  s.window = plan.window;
+  s.fixed = plan.fixed;
+  s.help_after = plan.help_after;
   unsigned char *base = static_cast<unsigned char *>(workspace);
   s.next_task = reinterpret_cast<unsigned long long *>(base);
   s.ticket = reinterpret_cast<uint32_t *>(base + 8);
   s.epoch = reinterpret_cast<uint32_t *>(base + 12);
   s.partials = reinterpret_cast<StreamPartial *>(base + kStreamHeaderBytes);
-  const uint64_t tasks = 2 * p.rows * s.chunks;
-  const unsigned grid = clamp_grid(tasks, static_cast<uint64_t>(sm_count()) * 4);
   const uint32_t last = p.cols - (s.chunks - 1) * s.chunk;  // the shortest chunk
-  const bool nine_full = s.chunk / 4 >= 9u * kStreamThreads && last / 4 >= 9u * kStreamThreads;
-  return launch(nine_full ? logits_stream_kernel<kMode, 9> : logits_stream_kernel<kMode, 0>, dim3(grid),
-                dim3(kStreamThreads), kStreamStageBytes, stream, s);
+  const bool almost_full = s.chunk / 4 >= static_cast<uint32_t>(kAlmost) * kStreamThreads &&
+                           last / 4 >= static_cast<uint32_t>(kAlmost) * kStreamThreads;
+  return launch(almost_full ? logits_stream_kernel<kMode, kVectors, kAlmost> : logits_stream_kernel<kMode, kVectors, 0>,
+                dim3(plan.grid), dim3(kStreamThreads), kStage, stream, s);
 }
 
 template <int kMode>
-int launch_logits(cudaStream_t stream, LogitsParams p, bool vec, void *workspace, uint64_t workspace_bytes) {
+int launch_stream(cudaStream_t stream, const LogitsParams &p, void *workspace, const hyle_b200_stream_tuning *tuning) {
+  int vectors = tuning != nullptr ? tuning->chunk_vectors : 0;
+  if (vectors == 0)
+    vectors = p.rows <= kStreamSmallBatchRows && stream_eligible(p.rows, p.cols, kStreamVectorsSmall) ? kStreamVectorsSmall
+                                                                                                        : kStreamVectorsLarge;
+  if (vectors == kStreamVectorsSmall) return launch_stream_sized<kMode, kStreamVectorsSmall>(stream, p, workspace, tuning);
+  if (vectors == kStreamVectorsLarge) return launch_stream_sized<kMode, kStreamVectorsLarge>(stream, p, workspace, tuning);
+  return HYLE_B200_INVALID_VALUE;
+}
+
+template <int kMode>
+int launch_logits(cudaStream_t stream, LogitsParams p, bool vec, void *workspace, uint64_t workspace_bytes,
+                  const hyle_b200_stream_tuning *tuning) {
   if (p.cols == 0) return HYLE_B200_NOT_SUPPORTED;
   if constexpr (kMode != kArgmaxOnly) {
     // Many rows with an output tensor: the two-pass streaming kernel (needs the caller's workspace).
-    if (vec && p.out != nullptr && p.out != static_cast<const void *>(p.in) && workspace != nullptr && p.rows >= kStreamMinRows && p.cols % 16 == 0 &&
-        stream_chunks(p.cols) <= kStreamMaxChunks && p.cols >= kStreamThreads * 4 &&
-        workspace_bytes >= stream_workspace_bytes(p.rows, p.cols))
-      return launch_stream<kMode>(stream, p, workspace);
+    if (vec && p.out != nullptr && p.out != static_cast<const void *>(p.in) && workspace != nullptr &&
+        stream_eligible(p.rows, p.cols, kStreamVectorsLarge) && workspace_bytes >= stream_workspace_bytes(p.rows, p.cols))
+      return launch_stream<kMode>(stream, p, workspace, tuning);
+    if (tuning != nullptr) return HYLE_B200_INVALID_VALUE;  // tuning is for the streaming kernel only
   }
   if constexpr (kMode != kArgmaxOnly) {
     // Register-resident fast path: aligned rows of at most 8 x 20480 values.
@@ -1089,31 +1280,66 @@ extern "C" uint64_t hyle_b200_logits_workspace_bytes(uint64_t rows, uint64_t col
   return stream_workspace_bytes(rows, cols);
 }
 
+extern "C" int hyle_b200_logits_reduce_f32_tuned(hyle_b200_stream_t stream, const float *logits, uint64_t rows, uint64_t cols,
+                                                 float *lse, void *probs_bf16, int32_t *argmax_index, float *argmax_value,
+                                                 void *workspace, uint64_t workspace_bytes, uint32_t *status_word,
+                                                 const hyle_b200_stream_tuning *tuning) {
+  if (rows == 0) return HYLE_B200_OK;
+  if (logits == nullptr || cols == 0 || cols > 0x7fffffffull) return HYLE_B200_INVALID_VALUE;
+  if (workspace != nullptr && !aligned_to(workspace, 16)) return HYLE_B200_INVALID_VALUE;
+  LogitsParams p{logits, rows, static_cast<uint32_t>(cols), 0, lse, probs_bf16, argmax_index, argmax_value, status_word};
+  const bool vec = aligned_to(logits, 16) && cols % 8 == 0 && (probs_bf16 == nullptr || aligned_to(probs_bf16, 16));
+  auto s = reinterpret_cast<cudaStream_t>(stream);
+  if (lse == nullptr && probs_bf16 == nullptr)
+    return tuning != nullptr ? HYLE_B200_INVALID_VALUE : launch_logits<kArgmaxOnly>(s, p, vec, nullptr, 0, nullptr);
+  return launch_logits<kProbsBf16>(s, p, vec, workspace, workspace_bytes, tuning);
+}
+
 extern "C" int hyle_b200_logits_reduce_f32(hyle_b200_stream_t stream, const float *logits,
                                            uint64_t rows, uint64_t cols, float *lse,
                                            void *probs_bf16, int32_t *argmax_index,
                                            float *argmax_value, void *workspace,
-                                           uint64_t workspace_bytes) {
-  if (rows == 0) return HYLE_B200_OK;
-  if (logits == nullptr || cols == 0 || cols > 0x7fffffffull) return HYLE_B200_INVALID_VALUE;
-  if (workspace != nullptr && !aligned_to(workspace, 16)) return HYLE_B200_INVALID_VALUE;
-  LogitsParams p{logits, rows, static_cast<uint32_t>(cols), 0, lse, probs_bf16, argmax_index, argmax_value};
-  const bool vec = aligned_to(logits, 16) && cols % 8 == 0 && (probs_bf16 == nullptr || aligned_to(probs_bf16, 16));
-  auto s = reinterpret_cast<cudaStream_t>(stream);
-  if (lse == nullptr && probs_bf16 == nullptr) return launch_logits<kArgmaxOnly>(s, p, vec, nullptr, 0);
-  return launch_logits<kProbsBf16>(s, p, vec, workspace, workspace_bytes);
+                                           uint64_t workspace_bytes, uint32_t *status_word) {
+  return hyle_b200_logits_reduce_f32_tuned(stream, logits, rows, cols, lse, probs_bf16, argmax_index, argmax_value, workspace,
+                                           workspace_bytes, status_word, nullptr);
 }
 
 extern "C" int hyle_b200_softmax_f32(hyle_b200_stream_t stream, int kind, const float *in,
                                      float *out, uint64_t rows, uint64_t cols, void *workspace,
-                                     uint64_t workspace_bytes) {
+                                     uint64_t workspace_bytes, uint32_t *status_word) {
   if (rows == 0 || cols == 0) return HYLE_B200_OK;
   if (in == nullptr || out == nullptr || cols > 0x7fffffffull) return HYLE_B200_INVALID_VALUE;
   if (workspace != nullptr && !aligned_to(workspace, 16)) return HYLE_B200_INVALID_VALUE;
-  LogitsParams p{in, rows, static_cast<uint32_t>(cols), 0, nullptr, out, nullptr, nullptr};
+  LogitsParams p{in, rows, static_cast<uint32_t>(cols), 0, nullptr, out, nullptr, nullptr, status_word};
   const bool vec = aligned_to(in, 16) && aligned_to(out, 16) && cols % 8 == 0;
   auto s = reinterpret_cast<cudaStream_t>(stream);
-  if (kind == HYLE_B200_SOFTMAX) return launch_logits<kProbsF32>(s, p, vec, workspace, workspace_bytes);
-  if (kind == HYLE_B200_LOG_SOFTMAX) return launch_logits<kLogF32>(s, p, vec, workspace, workspace_bytes);
+  if (kind == HYLE_B200_SOFTMAX) return launch_logits<kProbsF32>(s, p, vec, workspace, workspace_bytes, nullptr);
+  if (kind == HYLE_B200_LOG_SOFTMAX) return launch_logits<kLogF32>(s, p, vec, workspace, workspace_bytes, nullptr);
   return HYLE_B200_INVALID_VALUE;
+}
+
+// Host-side introspection of the streaming kernel's schedule (no launch, no device access beyond the
+// cached SM count and occupancy query): what tests and tuning sweeps read.
+extern "C" int hyle_b200_logits_stream_plan(uint64_t rows, uint64_t cols, const hyle_b200_stream_tuning *tuning,
+                                            hyle_b200_stream_plan *plan_out) {
+  if (plan_out == nullptr) return HYLE_B200_INVALID_VALUE;
+  const int small = stream_resident_ctas(logits_stream_kernel<kProbsBf16, kStreamVectorsSmall, 0>,
+                                         stream_stage_bytes(kStreamVectorsSmall), kProbsBf16 * 2);
+  const int large = stream_resident_ctas(logits_stream_kernel<kProbsBf16, kStreamVectorsLarge, 0>,
+                                         stream_stage_bytes(kStreamVectorsLarge), kProbsBf16 * 2 + 1);
+  const StreamPlan plan = make_stream_plan(rows, cols, tuning, sm_count(), small, large);
+  *plan_out = hyle_b200_stream_plan{plan.vectors, plan.chunks, plan.chunk, plan.window, plan.fixed, plan.ctas_per_sm,
+                                    plan.grid, plan.help_after};
+  return plan.vectors == 0 ? HYLE_B200_NOT_SUPPORTED : HYLE_B200_OK;
+}
+
+extern "C" int hyle_b200_logits_stream_task(uint64_t rows, uint32_t chunks, uint32_t window, uint64_t task,
+                                            uint32_t *pass_out, uint64_t *row_out, uint32_t *chunk_out) {
+  if (rows == 0 || chunks == 0 || window == 0 || window > rows || pass_out == nullptr || row_out == nullptr || chunk_out == nullptr)
+    return HYLE_B200_INVALID_VALUE;
+  const StreamTask decoded = stream_decode(task, rows, chunks, window);
+  *pass_out = decoded.pass;
+  *row_out = decoded.row;
+  *chunk_out = decoded.chunk_id;
+  return HYLE_B200_OK;
 }

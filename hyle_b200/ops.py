@@ -35,6 +35,40 @@ def _ptr(t: Optional[torch.Tensor]) -> Optional[int]:
     return None if t is None else t.data_ptr()
 
 
+def _torch_empty(shape, dtype, device) -> torch.Tensor:
+    return torch.empty(shape, dtype=dtype, device=device)
+
+
+_allocate_output = _torch_empty
+
+
+def set_output_allocator(allocate=None):
+    """Route every output tensor the operators create through ``allocate(shape, dtype, device)``.
+
+    For callers that own the device pool (and for tests that place each output between guard bytes).
+    ``None`` restores ``torch.empty``.  Returns the previous allocator."""
+    global _allocate_output
+    previous = _allocate_output
+    _allocate_output = _torch_empty if allocate is None else allocate
+    return previous
+
+
+def _new(shape, dtype, device) -> torch.Tensor:
+    if isinstance(shape, int):
+        shape = (shape,)
+    return _allocate_output(tuple(shape), dtype, device)
+
+
+def new_output(shape, dtype, device="cuda") -> torch.Tensor:
+    """An uninitialised tensor from the output allocator (see :func:`set_output_allocator`), for entry
+    points called with explicit outputs."""
+    return _new(shape, dtype, device)
+
+
+def _new_like(t: torch.Tensor) -> torch.Tensor:
+    return _allocate_output(tuple(t.shape), t.dtype, t.device)
+
+
 def binary(kind: int, lhs: torch.Tensor, rhs: torch.Tensor, out: Optional[torch.Tensor] = None) -> torch.Tensor:
     """Binary{kind}; ``rhs`` has lhs's shape or lhs's trailing axes (NumPy broadcast)."""
     _device_tensor(lhs, "lhs"), _device_tensor(rhs, "rhs")
@@ -43,7 +77,7 @@ def binary(kind: int, lhs: torch.Tensor, rhs: torch.Tensor, out: Optional[torch.
     if tuple(lhs.shape[lhs.dim() - rhs.dim():]) != tuple(rhs.shape):
         raise ValueError("rhs must equal lhs's shape or its trailing axes")
     if out is None:
-        out = torch.empty_like(lhs)
+        out = _new_like(lhs)
     abi.check("hyle_b200_binary", abi.load().hyle_b200_binary(
         _stream(), kind, _DTYPE[lhs.dtype], lhs.data_ptr(), rhs.data_ptr(), out.data_ptr(),
         lhs.numel(), max(rhs.numel(), 1) if lhs.numel() else 1))
@@ -82,7 +116,7 @@ def unary(kind: int, x: torch.Tensor, out: Optional[torch.Tensor] = None) -> tor
     if x.dtype not in _DTYPE:
         raise ValueError("x must be f32 / bf16 / f16")
     if out is None:
-        out = torch.empty_like(x)
+        out = _new_like(x)
     abi.check("hyle_b200_unary", abi.load().hyle_b200_unary(
         _stream(), kind, _DTYPE[x.dtype], x.data_ptr(), out.data_ptr(), x.numel()))
     return out
@@ -95,7 +129,7 @@ def reduce_rows(kind: int, x: torch.Tensor) -> torch.Tensor:
         raise ValueError("reduce_rows takes an f32 tensor of rank >= 1")
     cols = x.shape[-1]
     rows = x.numel() // cols if cols else int(torch.Size(x.shape[:-1]).numel())
-    out = torch.empty(x.shape[:-1], dtype=torch.float32, device=x.device)
+    out = _new(x.shape[:-1], torch.float32, x.device)
     abi.check("hyle_b200_reduce_rows_f32", abi.load().hyle_b200_reduce_rows_f32(
         _stream(), kind, x.data_ptr(), out.data_ptr(), rows, cols))
     return out
@@ -107,9 +141,9 @@ def add_bias_row_sum_max(a: torch.Tensor, bias: torch.Tensor) -> Tuple[torch.Ten
     if a.dtype != torch.float32 or bias.dtype != torch.float32 or a.dim() != 2 or bias.shape != a.shape[1:]:
         raise ValueError("a must be f32 [rows, cols] and bias f32 [cols]")
     rows, cols = a.shape
-    c = torch.empty_like(a)
-    row_sum = torch.empty(rows, dtype=torch.float32, device=a.device)
-    row_max = torch.empty(rows, dtype=torch.float32, device=a.device)
+    c = _new_like(a)
+    row_sum = _new(rows, torch.float32, a.device)
+    row_max = _new(rows, torch.float32, a.device)
     abi.check("hyle_b200_add_bias_row_sum_max_f32", abi.load().hyle_b200_add_bias_row_sum_max_f32(
         _stream(), a.data_ptr(), bias.data_ptr(), c.data_ptr(), row_sum.data_ptr(), row_max.data_ptr(),
         rows, cols))
@@ -135,7 +169,7 @@ def rms_norm(x: torch.Tensor, weight: Optional[torch.Tensor], epsilon: float,
     rows = x.numel() // hidden if hidden else 0
     w_ptr, w_dtype = _weight_args(weight, hidden)
     if out is None:
-        out = torch.empty_like(x)
+        out = _new_like(x)
     abi.check("hyle_b200_rms_norm_bf16", abi.load().hyle_b200_rms_norm_bf16(
         _stream(), x.data_ptr(), w_ptr, w_dtype, out.data_ptr(), rows, hidden, epsilon))
     return out
@@ -150,7 +184,7 @@ def add_rms_norm(x: torch.Tensor, residual: torch.Tensor, weight: Optional[torch
     hidden = x.shape[-1]
     rows = x.numel() // hidden if hidden else 0
     w_ptr, w_dtype = _weight_args(weight, hidden)
-    y, h = torch.empty_like(x), torch.empty_like(x)
+    y, h = _new_like(x), _new_like(x)
     abi.check("hyle_b200_add_rms_norm_bf16", abi.load().hyle_b200_add_rms_norm_bf16(
         _stream(), x.data_ptr(), residual.data_ptr(), w_ptr, w_dtype, y.data_ptr(), h.data_ptr(),
         rows, hidden, epsilon))
@@ -166,7 +200,7 @@ def layer_norm(x: torch.Tensor, scale: Optional[torch.Tensor], bias: Optional[to
     hidden = x.shape[-1]
     rows = x.numel() // hidden if hidden else 0
     if out is None:
-        out = torch.empty_like(x)
+        out = _new_like(x)
     abi.check("hyle_b200_layer_norm_bf16", abi.load().hyle_b200_layer_norm_bf16(
         _stream(), x.data_ptr(), _ptr(scale), _ptr(bias), out.data_ptr(), rows, hidden, eps))
     return out
@@ -179,7 +213,7 @@ def swiglu(gate: torch.Tensor, up: torch.Tensor) -> torch.Tensor:
         raise ValueError("gate and up must be bf16 tensors of one shape")
     cols = gate.shape[-1]
     rows = gate.numel() // cols if cols else 0
-    out = torch.empty_like(gate)
+    out = _new_like(gate)
     abi.check("hyle_b200_swiglu_bf16", abi.load().hyle_b200_swiglu_bf16(
         _stream(), gate.data_ptr(), up.data_ptr(), out.data_ptr(), rows, cols, cols, cols))
     return out
@@ -192,7 +226,7 @@ def swiglu_packed(packed: torch.Tensor) -> torch.Tensor:
         raise ValueError("packed must be bf16 with an even last axis")
     cols = packed.shape[-1] // 2
     rows = packed.numel() // (2 * cols) if cols else 0
-    out = torch.empty(packed.shape[:-1] + (cols,), dtype=torch.bfloat16, device=packed.device)
+    out = _new(packed.shape[:-1] + (cols,), torch.bfloat16, packed.device)
     abi.check("hyle_b200_swiglu_bf16", abi.load().hyle_b200_swiglu_bf16(
         _stream(), packed.data_ptr(), packed.data_ptr() + 2 * cols, out.data_ptr(), rows, cols,
         2 * cols, 2 * cols))
@@ -206,26 +240,44 @@ def make_logits_workspace(device, rows: int, cols: int) -> torch.Tensor:
 
 
 def logits_reduce(logits: torch.Tensor, want_probs: bool = True, want_lse: bool = True,
-                  want_argmax: bool = True, workspace: Optional[torch.Tensor] = None):
+                  want_argmax: bool = True, workspace: Optional[torch.Tensor] = None,
+                  status: Optional[torch.Tensor] = None, tuning: Optional[abi.StreamTuning] = None):
     """Fused log-sum-exp, softmax->bf16 and argmax of f32 [rows, cols] logits.
 
     Returns (lse f32[rows], probs bf16[rows, cols], index i32[rows], value f32[rows]); entries not
     asked for are None.  With a `workspace` (`make_logits_workspace`) large batches take the
-    streaming kernel; without one every batch takes the cluster kernel.
+    streaming kernel; without one every batch takes the cluster kernel.  ``status`` (one int32 word)
+    receives abi.STATUS_STREAM_WAIT_TIMEOUT if the streaming kernel could not complete a row;
+    ``tuning`` overrides its schedule (sweeps, tests of the rare paths).
     """
     _device_tensor(logits, "logits")
     if logits.dtype != torch.float32 or logits.dim() != 2:
         raise ValueError("logits must be f32 [rows, cols]")
     rows, cols = logits.shape
     dev = logits.device
-    lse = torch.empty(rows, dtype=torch.float32, device=dev) if want_lse else None
-    probs = torch.empty(rows, cols, dtype=torch.bfloat16, device=dev) if want_probs else None
-    index = torch.empty(rows, dtype=torch.int32, device=dev) if want_argmax else None
-    value = torch.empty(rows, dtype=torch.float32, device=dev) if want_argmax else None
-    abi.check("hyle_b200_logits_reduce_f32", abi.load().hyle_b200_logits_reduce_f32(
-        _stream(), logits.data_ptr(), rows, cols, _ptr(lse), _ptr(probs), _ptr(index), _ptr(value),
-        _ptr(workspace), 0 if workspace is None else workspace.numel()))
+    lse = _new(rows, torch.float32, dev) if want_lse else None
+    probs = _new((rows, cols), torch.bfloat16, dev) if want_probs else None
+    index = _new(rows, torch.int32, dev) if want_argmax else None
+    value = _new(rows, torch.float32, dev) if want_argmax else None
+    arguments = (_stream(), logits.data_ptr(), rows, cols, _ptr(lse), _ptr(probs), _ptr(index), _ptr(value),
+                 _ptr(workspace), 0 if workspace is None else workspace.numel(), _ptr(status))
+    if tuning is None:
+        abi.check("hyle_b200_logits_reduce_f32", abi.load().hyle_b200_logits_reduce_f32(*arguments))
+    else:
+        abi.check("hyle_b200_logits_reduce_f32_tuned",
+                  abi.load().hyle_b200_logits_reduce_f32_tuned(*arguments, ctypes.addressof(tuning)))
     return lse, probs, index, value
+
+
+def logits_stream_plan(rows: int, cols: int, tuning: Optional[abi.StreamTuning] = None) -> Optional[abi.StreamPlan]:
+    """The streaming kernel's schedule for a shape (host arithmetic), or None when the shape takes the cluster kernel."""
+    plan = abi.StreamPlan()
+    code = abi.load().hyle_b200_logits_stream_plan(rows, cols, None if tuning is None else ctypes.addressof(tuning),
+                                                   ctypes.addressof(plan))
+    if code == abi.NOT_SUPPORTED:
+        return None
+    abi.check("hyle_b200_logits_stream_plan", code)
+    return plan
 
 
 def argmax(logits: torch.Tensor) -> Tuple[torch.Tensor, torch.Tensor]:
@@ -235,7 +287,7 @@ def argmax(logits: torch.Tensor) -> Tuple[torch.Tensor, torch.Tensor]:
 
 
 def softmax(x: torch.Tensor, log: bool = False, out: Optional[torch.Tensor] = None,
-            workspace: Optional[torch.Tensor] = None) -> torch.Tensor:
+            workspace: Optional[torch.Tensor] = None, status: Optional[torch.Tensor] = None) -> torch.Tensor:
     """Softmax{axis=-1, kSoftmax|kLogSoftmax} on f32 rows, f32 output."""
     _device_tensor(x, "x")
     if x.dtype != torch.float32:
@@ -243,10 +295,10 @@ def softmax(x: torch.Tensor, log: bool = False, out: Optional[torch.Tensor] = No
     cols = x.shape[-1]
     rows = x.numel() // cols if cols else 0
     if out is None:
-        out = torch.empty_like(x)
+        out = _new_like(x)
     abi.check("hyle_b200_softmax_f32", abi.load().hyle_b200_softmax_f32(
         _stream(), abi.LOG_SOFTMAX if log else abi.SOFTMAX, x.data_ptr(), out.data_ptr(), rows, cols,
-        _ptr(workspace), 0 if workspace is None else workspace.numel()))
+        _ptr(workspace), 0 if workspace is None else workspace.numel(), _ptr(status)))
     return out
 
 
@@ -262,7 +314,7 @@ def cast(x: torch.Tensor, source: int, destination: int) -> torch.Tensor:
     _device_tensor(x, "x")
     if x.dtype != _CAST_TORCH[source]:
         raise ValueError(f"source type {source} is carried by {_CAST_TORCH[source]}, got {x.dtype}")
-    out = torch.empty(x.shape, dtype=_CAST_TORCH[destination], device=x.device)
+    out = _new(x.shape, _CAST_TORCH[destination], x.device)
     abi.check("hyle_b200_cast", abi.load().hyle_b200_cast(
         _stream(), source, destination, x.data_ptr(), out.data_ptr(), x.numel()))
     return out
@@ -273,7 +325,7 @@ def fp8_e4m3_encode(x: torch.Tensor, scale: float, status: Optional[torch.Tensor
     _device_tensor(x, "x")
     if x.dtype not in _DTYPE:
         raise ValueError("x must be f32 / bf16 / f16")
-    out = torch.empty(x.shape, dtype=torch.uint8, device=x.device)
+    out = _new(x.shape, torch.uint8, x.device)
     abi.check("hyle_b200_fp8_e4m3_encode", abi.load().hyle_b200_fp8_e4m3_encode(
         _stream(), _DTYPE[x.dtype], x.data_ptr(), x.numel(), scale, out.data_ptr(), _ptr(status)))
     return out
@@ -294,7 +346,7 @@ def strided_cast_raw(x: torch.Tensor, source: int, destination: int) -> torch.Te
         raise ValueError("views of rank <= 8")
     if x.element_size() != torch.empty(0, dtype=_CAST_TORCH[source]).element_size():
         raise ValueError("the view's element size does not match the source type")
-    out = torch.empty(x.shape, dtype=_CAST_TORCH[destination], device=x.device)
+    out = _new(x.shape, _CAST_TORCH[destination], x.device)
     dims = (ctypes.c_int64 * max(1, x.dim()))(*x.shape)
     strides = (ctypes.c_int64 * max(1, x.dim()))(*[s * x.element_size() for s in x.stride()])
     abi.check("hyle_b200_strided_cast", abi.load().hyle_b200_strided_cast(
@@ -311,7 +363,7 @@ def scan(x: torch.Tensor, exclusive: bool = False, status: Optional[torch.Tensor
         raise ValueError("scan takes a dense f32 / i32 tensor")
     if x.dtype == torch.int32 and status is None:
         raise ValueError("the i32 scan reports overflow through a status word")
-    out = torch.empty_like(x)
+    out = _new_like(x)
     cols = x.shape[-1]
     abi.check("hyle_b200_scan", abi.load().hyle_b200_scan(
         _stream(), abi.F32 if x.dtype == torch.float32 else abi.I32, x.data_ptr(), out.data_ptr(),
@@ -398,7 +450,7 @@ def cast_f32_to_bf16(x: torch.Tensor) -> torch.Tensor:
     _device_tensor(x, "x")
     if x.dtype != torch.float32:
         raise ValueError("cast_f32_to_bf16 takes f32 input")
-    out = torch.empty(x.shape, dtype=torch.bfloat16, device=x.device)
+    out = _new(x.shape, torch.bfloat16, x.device)
     abi.check("hyle_b200_cast_f32_to_bf16", abi.load().hyle_b200_cast_f32_to_bf16(
         _stream(), x.data_ptr(), out.data_ptr(), x.numel()))
     return out
@@ -416,7 +468,7 @@ def q8_0_encode(x: torch.Tensor, status: Optional[torch.Tensor] = None) -> torch
     _device_tensor(x, "x")
     if x.dtype not in _DTYPE or x.shape[-1] % 32:
         raise ValueError("q8_0_encode takes f32/bf16/f16 with a last axis that is a multiple of 32")
-    out = torch.empty(x.shape[:-1] + (x.shape[-1] // 32 * 34,), dtype=torch.uint8, device=x.device)
+    out = _new(x.shape[:-1] + (x.shape[-1] // 32 * 34,), torch.uint8, x.device)
     abi.check("hyle_b200_q8_0_encode", abi.load().hyle_b200_q8_0_encode(
         _stream(), _DTYPE[x.dtype], x.data_ptr(), x.numel(), out.data_ptr(), _ptr(status)))
     return out
@@ -426,7 +478,7 @@ def q8_0_decode(blocks: torch.Tensor, count: int) -> torch.Tensor:
     _device_tensor(blocks, "blocks")
     if blocks.dtype != torch.uint8 or blocks.numel() != q8_0_bytes(count):
         raise ValueError("blocks must be the U8 carrier of `count` values")
-    out = torch.empty(count, dtype=torch.bfloat16, device=blocks.device)
+    out = _new(count, torch.bfloat16, blocks.device)
     abi.check("hyle_b200_q8_0_decode_bf16", abi.load().hyle_b200_q8_0_decode_bf16(
         _stream(), blocks.data_ptr(), count, out.data_ptr()))
     return out
@@ -444,7 +496,7 @@ def sum_squares(x: torch.Tensor, workspace: torch.Tensor, out: Optional[torch.Te
     if x.dtype != torch.bfloat16:
         raise ValueError("sum_squares takes bf16 input")
     if out is None:
-        out = torch.empty(1, dtype=torch.float64, device=x.device)
+        out = _new(1, torch.float64, x.device)
     abi.check("hyle_b200_sum_squares_bf16", abi.load().hyle_b200_sum_squares_bf16(
         _stream(), x.data_ptr(), x.numel(), out.data_ptr(), workspace.data_ptr(), workspace.numel()))
     return out
@@ -458,11 +510,11 @@ def q8_0_roundtrip(x: torch.Tensor, workspace: torch.Tensor, blocks: Optional[to
     if x.dtype != torch.bfloat16 or x.numel() % 32:
         raise ValueError("q8_0_roundtrip takes bf16 input with a multiple of 32 values")
     if blocks is None:
-        blocks = torch.empty(q8_0_bytes(x.numel()), dtype=torch.uint8, device=x.device)
+        blocks = _new(q8_0_bytes(x.numel()), torch.uint8, x.device)
     if decoded is None:
-        decoded = torch.empty_like(x)
+        decoded = _new_like(x)
     if sum_out is None:
-        sum_out = torch.empty(1, dtype=torch.float64, device=x.device)
+        sum_out = _new(1, torch.float64, x.device)
     abi.check("hyle_b200_q8_0_roundtrip_bf16", abi.load().hyle_b200_q8_0_roundtrip_bf16(
         _stream(), x.data_ptr(), x.numel(), blocks.data_ptr(), decoded.data_ptr(), sum_out.data_ptr(),
         _ptr(status), workspace.data_ptr(), workspace.numel()))
@@ -482,11 +534,11 @@ def q8_0_roundtrip_static(x: torch.Tensor, blocks: Optional[torch.Tensor] = None
     if x.dtype != torch.bfloat16 or x.numel() % 32:
         raise ValueError("q8_0_roundtrip_static takes bf16 input with a multiple of 32 values")
     if blocks is None:
-        blocks = torch.empty(q8_0_bytes(x.numel()), dtype=torch.uint8, device=x.device)
+        blocks = _new(q8_0_bytes(x.numel()), torch.uint8, x.device)
     if decoded is None:
-        decoded = torch.empty_like(x)
+        decoded = _new_like(x)
     if sum_out is None:
-        sum_out = torch.empty(1, dtype=torch.float64, device=x.device)
+        sum_out = _new(1, torch.float64, x.device)
     abi.check("hyle_b200_q8_0_roundtrip_bf16_static", abi.load().hyle_b200_q8_0_roundtrip_bf16_static(
         _stream(), x.data_ptr(), x.numel(), blocks.data_ptr(), decoded.data_ptr(), sum_out.data_ptr(),
         _ptr(status)))
@@ -498,7 +550,7 @@ def random_bits(identities: torch.Tensor, word_count: int) -> torch.Tensor:
     _device_tensor(identities, "identities")
     if identities.dtype != torch.int32 or identities.dim() != 2 or identities.shape[1] != 4:
         raise ValueError("identities must be int32 [rows, 4] holding the u32 words")
-    out = torch.empty(identities.shape[0], word_count, dtype=torch.int32, device=identities.device)
+    out = _new((identities.shape[0], word_count), torch.int32, identities.device)
     abi.check("hyle_b200_random_bits", abi.load().hyle_b200_random_bits(
         _stream(), identities.data_ptr(), identities.shape[0], word_count, out.data_ptr()))
     return out
@@ -513,8 +565,8 @@ def categorical(log_weights: torch.Tensor, identities: torch.Tensor, want_log_pr
     rows, cols = log_weights.shape
     if identities.dtype != torch.int32 or tuple(identities.shape) != (rows, 4):
         raise ValueError("identities must be int32 [rows, 4] holding the u32 words")
-    index = torch.empty(rows, dtype=torch.int32, device=log_weights.device)
-    logp = torch.empty(rows, dtype=torch.float32, device=log_weights.device) if want_log_probability else None
+    index = _new(rows, torch.int32, log_weights.device)
+    logp = _new(rows, torch.float32, log_weights.device) if want_log_probability else None
     abi.check("hyle_b200_categorical", abi.load().hyle_b200_categorical(
         _stream(), _DTYPE[log_weights.dtype], log_weights.data_ptr(), identities.data_ptr(), rows, cols,
         index.data_ptr(), _ptr(logp), _ptr(status)))
@@ -528,7 +580,7 @@ def select(condition: torch.Tensor, when_true: torch.Tensor, when_false: torch.T
     if when_true.dtype != when_false.dtype or condition.element_size() != 1:
         raise ValueError("branches must share a type and the condition must be one byte per element")
     code = {torch.float32: abi.F32, torch.int32: abi.I32, torch.bfloat16: abi.BF16, torch.float16: abi.F16}[when_true.dtype]
-    out = torch.empty(condition.shape, dtype=when_true.dtype, device=condition.device)
+    out = _new(condition.shape, when_true.dtype, condition.device)
     abi.check("hyle_b200_select", abi.load().hyle_b200_select(
         _stream(), code, condition.data_ptr(), when_true.data_ptr(), when_false.data_ptr(), out.data_ptr(),
         condition.numel(), max(when_true.numel(), 1), max(when_false.numel(), 1)))
@@ -542,7 +594,7 @@ def masked_softmax_f16(x: torch.Tensor, mask: torch.Tensor, scale: float = 1.0) 
     if x.dtype != torch.float16 or mask.element_size() != 1:
         raise ValueError("masked_softmax_f16 takes f16 values and a one-byte mask")
     cols = x.shape[-1]
-    out = torch.empty_like(x)
+    out = _new_like(x)
     abi.check("hyle_b200_masked_softmax_f16", abi.load().hyle_b200_masked_softmax_f16(
         _stream(), x.data_ptr(), mask.data_ptr(), mask.numel(), scale, out.data_ptr(), x.numel() // cols if cols else 0, cols))
     return out

@@ -7,11 +7,13 @@
 // tensors' device pointers and makes ONE call through the C ABI (include/hyle_b200.h).  Nothing here
 // allocates, synchronises or falls back to another implementation.
 //
-// The backend is a template parameter because the two things the adapter needs from it -- the
-// cudaStream_t of a QueueSequence and the device pointer of a BufferView -- come from
-// include/hyle/compute/backends/cuda.h, which needs CUDA >= 13.3.  `CudaBackend` (below, compiled
-// only when that header is usable) is the production binding; tests may supply another Backend to
-// drive the cold path on the reference's CPU backend.
+// The backend is a template parameter because the three things the adapter needs from it -- the
+// cudaStream_t of a QueueSequence, the device pointer of a BufferView and the sequence's device
+// status word -- come from the CUDA backend the Context was created on.  Two bindings exist:
+// `backend::Cuda12Backend` (b200_backend.h, a thin backend built with the CUDA 12.x runtime) and
+// `CudaBackend` (below, the reference's own backend, include/hyle/compute/backends/cuda.h, which needs
+// CUDA >= 13.3 and is compiled only when that header is usable).  Tests may supply another Backend
+// to drive the cold path on the reference's CPU backend.
 #pragma once
 
 #include <array>
@@ -182,14 +184,17 @@ inline std::optional<Plan> match(const Operation &op, std::span<const TensorDesc
     return p;
   }
   if (const auto *scan = op.get_if<Scan>()) {
-    // last axis, f32, same dense description.  The i32 scan reports overflow through a device status
-    // word the custom-kernel interface does not hand to a provider, so it stays with the next one.
+    // last axis, f32 or i32, same dense description.  The i32 scan reports overflow through the
+    // sequence's device status word (OutOfRange at the Completion, nothing written), as
+    // src/compute_provider_ggml/standard_index.cc:127-134 does on the host.
     const auto last = static_cast<int>(in.empty() ? 0 : in[0].rank()) - 1;
-    if (in.size() != 1 || out.size() != 1 || in[0].data_type() != DataType::kFloat32 || in[0].rank() == 0 || out[0] != in[0] ||
+    const bool f32 = in[0].data_type() == DataType::kFloat32, i32 = in[0].data_type() == DataType::kInt32;
+    if (in.size() != 1 || out.size() != 1 || (!f32 && !i32) || in[0].rank() == 0 || out[0] != in[0] ||
         (scan->axis != -1 && scan->axis != last))
       return std::nullopt;
     p.entry = Entry::kScan;
     p.kind = scan->exclusive ? 1 : 0;
+    p.dtype = f32 ? HYLE_B200_F32 : HYLE_B200_I32;
     return p;
   }
   if (const auto *norm = op.get_if<RmsNorm>()) {
@@ -349,9 +354,20 @@ inline std::optional<Plan> match(const Operation &op, std::span<const TensorDesc
   return std::nullopt;
 }
 
-// One call through the C ABI.  Returns its cudaError_t-compatible result.
+// Entries whose kernels report through the sequence's device status word.
+inline bool uses_status_word(const Plan &p) noexcept {
+  switch (p.entry) {
+    case Entry::kQ8Encode: case Entry::kFp8Encode: case Entry::kCategorical: case Entry::kQ8Roundtrip: return true;
+    case Entry::kScan: return p.dtype == HYLE_B200_I32;
+    case Entry::kSoftmax: case Entry::kLogitsReduce: return p.workspace_bytes != 0;  // the streaming kernel
+    default: return false;
+  }
+}
+
+// One call through the C ABI.  Returns its cudaError_t-compatible result.  `status_word` is the
+// sequence's device status word, or null for entries that report nothing.
 inline int launch(const Plan &p, hyle_b200_stream_t stream, const void *const *in, void *const *out,
-                  void *workspace) noexcept {
+                  void *workspace, std::uint32_t *status_word) noexcept {
   switch (p.entry) {
     case Entry::kUnary:
       return hyle_b200_unary(stream, p.kind, p.dtype, in[0], out[0], p.count);
@@ -360,7 +376,7 @@ inline int launch(const Plan &p, hyle_b200_stream_t stream, const void *const *i
     case Entry::kBinary:
       return hyle_b200_binary(stream, p.kind, p.dtype, in[0], in[1], out[0], p.count, p.rhs_period);
     case Entry::kScan:
-      return hyle_b200_scan(stream, HYLE_B200_F32, in[0], out[0], p.rows, p.cols, p.kind, nullptr);
+      return hyle_b200_scan(stream, p.dtype, in[0], out[0], p.rows, p.cols, p.kind, status_word);
     case Entry::kReduceRows:
       return hyle_b200_reduce_rows_f32(stream, p.kind, static_cast<const float *>(in[0]),
                                        static_cast<float *>(out[0]), p.rows, p.cols);
@@ -377,7 +393,7 @@ inline int launch(const Plan &p, hyle_b200_stream_t stream, const void *const *i
     }
     case Entry::kSoftmax:
       return hyle_b200_softmax_f32(stream, p.kind, static_cast<const float *>(in[0]), static_cast<float *>(out[0]),
-                                   p.rows, p.cols, workspace, p.workspace_bytes);
+                                   p.rows, p.cols, workspace, p.workspace_bytes, status_word);
     case Entry::kMaskedSoftmax:
       return hyle_b200_masked_softmax_f16(stream, in[0], static_cast<const unsigned char *>(in[1]), p.rhs_period, p.epsilon,
                                           out[0], p.rows, p.cols);
@@ -385,18 +401,19 @@ inline int launch(const Plan &p, hyle_b200_stream_t stream, const void *const *i
       return hyle_b200_cast(stream, p.dtype, p.to_dtype, in[0], out[0], p.count);
     case Entry::kArgmax:
       return hyle_b200_logits_reduce_f32(stream, static_cast<const float *>(in[0]), p.rows, p.cols, nullptr, nullptr,
-                                         static_cast<std::int32_t *>(out[1]), static_cast<float *>(out[0]), nullptr, 0);
+                                         static_cast<std::int32_t *>(out[1]), static_cast<float *>(out[0]), nullptr, 0,
+                                         nullptr);
     case Entry::kQ8Encode:
-      return hyle_b200_q8_0_encode(stream, p.dtype, in[0], p.count, out[0], nullptr);
+      return hyle_b200_q8_0_encode(stream, p.dtype, in[0], p.count, out[0], status_word);
     case Entry::kFp8Encode:
-      return hyle_b200_fp8_e4m3_encode(stream, p.dtype, in[0], p.count, p.epsilon, out[0], nullptr);
+      return hyle_b200_fp8_e4m3_encode(stream, p.dtype, in[0], p.count, p.epsilon, out[0], status_word);
     case Entry::kRandomBits:
       return hyle_b200_random_bits(stream, static_cast<const std::uint32_t *>(in[0]), p.rows,
                                    static_cast<std::uint32_t>(p.cols), static_cast<std::uint32_t *>(out[0]));
     case Entry::kCategorical:
       return hyle_b200_categorical(stream, p.dtype, in[0], static_cast<const std::uint32_t *>(in[1]), p.rows, p.cols,
                                    static_cast<std::int32_t *>(out[0]),
-                                   p.has_weight ? static_cast<float *>(out[1]) : nullptr, nullptr);
+                                   p.has_weight ? static_cast<float *>(out[1]) : nullptr, status_word);
     case Entry::kAddRmsNorm:
       return hyle_b200_add_rms_norm_bf16(stream, in[0], in[1], in[2], p.dtype, out[0], out[1], p.rows, p.cols,
                                          p.epsilon);
@@ -408,10 +425,10 @@ inline int launch(const Plan &p, hyle_b200_stream_t stream, const void *const *i
     case Entry::kLogitsReduce:
       return hyle_b200_logits_reduce_f32(stream, static_cast<const float *>(in[0]), p.rows, p.cols,
                                          static_cast<float *>(out[0]), out[1], static_cast<std::int32_t *>(out[2]),
-                                         static_cast<float *>(out[3]), workspace, p.workspace_bytes);
+                                         static_cast<float *>(out[3]), workspace, p.workspace_bytes, status_word);
     case Entry::kQ8Roundtrip:
       return hyle_b200_q8_0_roundtrip_bf16(stream, in[0], p.count, out[0], out[1], static_cast<double *>(out[2]),
-                                           nullptr, workspace, p.workspace_bytes);
+                                           status_word, workspace, p.workspace_bytes);
   }
   return HYLE_B200_INVALID_VALUE;
 }
@@ -430,11 +447,18 @@ inline AliasSupport alias_support(const Plan &p, std::size_t output, std::size_t
 //   static Result<const void *> pointer(mem::ConstBufferView);
 //   static Result<void *> mutable_pointer(mem::BufferView);
 //   static Status status(int abi_result);                    C ABI result -> Status
+//   static detail::EnqueueResult status_word(detail::QueueSequence &, unsigned **word);
+//       the sequence's device status word (cleared on first use in the sequence; the sequence's
+//       Completion reports what the kernels OR into it)
 template <class Backend>
 struct Kernel final {
   Plan plan;
   struct Invocation final {
     void *workspace = nullptr;
+    // The caller's workspace arrives with arbitrary contents, and the kernels that use one need
+    // counters that start at zero (each launch then leaves them zeroed again).  The first enqueue of
+    // an invocation therefore records one clear of the workspace on the queue's stream.
+    bool workspace_cleared = false;
   };
 
   Result<Invocation> create_invocation(mem::BufferView workspace, mem::AllocatorRef) const noexcept {
@@ -470,9 +494,27 @@ struct Kernel final {
     }
     if (plan.count == 0 && plan.entry != Entry::kReduceRows) return KernelCommandResult::no_op();
     // Recorded on the Queue's stream: no synchronisation, no allocation, no second Completion
-    // (docs/user/compute.md:1560-1565).  A failed launch is the Completion's terminal status.
+    // (docs/user/compute.md:1560-1565).  Once anything is recorded, a later failure is the
+    // Completion's terminal status, never a rejection.
+    bool recorded = false;
+    unsigned *status_word = nullptr;
+    if (uses_status_word(plan)) {
+      auto acquired = Backend::status_word(sequence, &status_word);
+      recorded = acquired.accepted;
+      if (!acquired.status.ok())
+        return recorded ? KernelCommandResult::accepted_command(std::move(acquired.status))
+                        : KernelCommandResult::rejected(std::move(acquired.status));
+    }
+    if (invocation.workspace != nullptr && !invocation.workspace_cleared) {
+      const int cleared = hyle_b200_workspace_clear(*stream, invocation.workspace, plan.workspace_bytes);
+      if (cleared != HYLE_B200_OK)
+        return recorded ? KernelCommandResult::accepted_command(Backend::status(cleared))
+                        : KernelCommandResult::rejected(Backend::status(cleared));
+      invocation.workspace_cleared = true;
+      recorded = true;
+    }
     return KernelCommandResult::accepted_command(
-        Backend::status(launch(plan, *stream, in.data(), out.data(), invocation.workspace)));
+        Backend::status(launch(plan, *stream, in.data(), out.data(), invocation.workspace, status_word)));
   }
 };
 
@@ -539,6 +581,12 @@ struct CudaBackend final {
     return static_cast<void *>(*p);
   }
   static Status status(int result) noexcept { return cuda::status(static_cast<cudaError_t>(result)); }
+  // The reference's same-build seam (src/compute_backend_cuda/native_context.h:72-73).  Its Completion
+  // decodes DeviceStatusCode values, not this library's bits: a build inside the reference tree maps
+  // the bits to codes with a one-thread kernel after the launch, or adopts the codes in the kernels.
+  static detail::EnqueueResult status_word(detail::QueueSequence &sequence, unsigned **word) noexcept {
+    return cuda::detail::acquire_device_status(sequence, word);
+  }
 };
 inline Result<Provider> provider() noexcept { return make_provider<CudaBackend>(); }
 }  // namespace hyle::compute::b200

@@ -43,7 +43,7 @@ extern "C" {
 /* Same object as cudaStream_t; spelled out so C callers need no CUDA header. */
 typedef struct CUstream_st *hyle_b200_stream_t;
 
-#define HYLE_B200_ABI_VERSION 14
+#define HYLE_B200_ABI_VERSION 15
 
 enum hyle_b200_result {
   HYLE_B200_OK = 0,
@@ -124,7 +124,11 @@ enum hyle_b200_status_bits {
   HYLE_B200_STATUS_INVALID_CATEGORICAL_ROW = 8u,
   /* hyle_b200_scan on i32: a prefix left the int32 range; no output was written
    * (src/compute_provider_ggml/standard_index.cc:127-134). */
-  HYLE_B200_STATUS_SCAN_OVERFLOW = 16u
+  HYLE_B200_STATUS_SCAN_OVERFLOW = 16u,
+  /* hyle_b200_logits_reduce_f32 / hyle_b200_softmax_f32, streaming kernel: a second-pass task gave up
+   * waiting for a row's first-pass partials (the launch did not get the co-resident CTAs it was sized
+   * for) or a bulk copy never landed; the affected rows are NaN. */
+  HYLE_B200_STATUS_STREAM_WAIT_TIMEOUT = 32u
 };
 
 HYLE_B200_API int hyle_b200_abi_version(void);
@@ -240,23 +244,70 @@ HYLE_B200_API int hyle_b200_swiglu_bf16(hyle_b200_stream_t stream, const void *g
  * Two kernels.  Without a workspace, or for fewer than 64 rows, a thread-block cluster keeps each
  * row in registers / shared memory (rows too wide for that return NOT_SUPPORTED).  With a
  * workspace of hyle_b200_logits_workspace_bytes(rows, cols) bytes (16-byte aligned, zero-filled
- * once after allocation; each launch leaves it zeroed again; stream-ordered launches only) and an
+ * once after allocation; each launch leaves it re-armed; stream-ordered launches only) and an
  * output tensor, batches of 64 rows or more take a two-pass streaming kernel whose second pass
  * reads the row back from L2: HBM traffic is the same, throughput is higher.
+ *
+ * status_word (device memory, may be NULL): the streaming kernel ORs
+ * HYLE_B200_STATUS_STREAM_WAIT_TIMEOUT into it when a row could not be completed (its outputs are NaN).
+ * That needs a lost store or a bulk copy that never lands: a second-pass task whose first-pass
+ * partials are missing reduces the missing chunks itself instead of waiting for another CTA, so the
+ * kernel completes with right results however many of its CTAs are resident at once.
  */
 HYLE_B200_API uint64_t hyle_b200_logits_workspace_bytes(uint64_t rows, uint64_t cols);
 HYLE_B200_API int hyle_b200_logits_reduce_f32(hyle_b200_stream_t stream, const float *logits,
                                               uint64_t rows, uint64_t cols, float *lse,
                                               void *probs_bf16, int32_t *argmax_index,
                                               float *argmax_value, void *workspace,
-                                              uint64_t workspace_bytes);
+                                              uint64_t workspace_bytes, uint32_t *status_word);
+
+/* Schedule of the streaming kernel.  Zero fields of a tuning mean "choose"; the defaults are the
+ * measured best for the shape.  For tuning sweeps and for tests that force the rare paths (a window
+ * of one row with help_after_polls = 1 makes second-pass tasks reduce their own partials). */
+typedef struct hyle_b200_stream_tuning {
+  int32_t chunk_vectors;      /* float4 per thread and task: 5 (5120-value chunks) or 10 (10240) */
+  uint32_t window_rows;       /* rows between a row's first and second pass */
+  uint32_t help_after_polls;  /* polls before a waiting warp reduces a missing chunk itself */
+  int32_t ctas_per_sm;        /* at most what the kernel was built for (4) and what fits */
+} hyle_b200_stream_tuning;
+typedef struct hyle_b200_stream_plan {
+  int32_t chunk_vectors;
+  uint32_t chunks_per_row;
+  uint32_t chunk_values;
+  uint32_t window_rows;
+  uint32_t fixed_tasks_per_cta;  /* tasks taken by CTA position; always inside the first-pass head */
+  int32_t ctas_per_sm;
+  uint32_t grid;
+  uint32_t help_after_polls;
+} hyle_b200_stream_plan;
+/* hyle_b200_logits_reduce_f32 with an explicit schedule; INVALID_VALUE when the shape does not take
+ * the streaming kernel (no workspace, fewer than 64 rows, unaligned) or the tuning is inconsistent. */
+HYLE_B200_API int hyle_b200_logits_reduce_f32_tuned(hyle_b200_stream_t stream, const float *logits,
+                                                    uint64_t rows, uint64_t cols, float *lse,
+                                                    void *probs_bf16, int32_t *argmax_index,
+                                                    float *argmax_value, void *workspace,
+                                                    uint64_t workspace_bytes, uint32_t *status_word,
+                                                    const hyle_b200_stream_tuning *tuning);
+/* Host-side only: the schedule the streaming kernel would use (NOT_SUPPORTED when the shape is not
+ * eligible), and the (pass, row, chunk) at a position of its ordered task list (pass 0 = first,
+ * 1 = second, 2 = past the end). */
+HYLE_B200_API int hyle_b200_logits_stream_plan(uint64_t rows, uint64_t cols,
+                                               const hyle_b200_stream_tuning *tuning,
+                                               hyle_b200_stream_plan *plan_out);
+HYLE_B200_API int hyle_b200_logits_stream_task(uint64_t rows, uint32_t chunks, uint32_t window,
+                                               uint64_t task, uint32_t *pass_out, uint64_t *row_out,
+                                               uint32_t *chunk_out);
 
 /* Softmax{axis=-1, kind} with f32 output (output dtype = input dtype,
  * src/compute_ops/operation.cc:1619). out may alias in (the cluster kernel is used then).
- * workspace: as for hyle_b200_logits_reduce_f32, may be NULL. */
+ * workspace and status_word: as for hyle_b200_logits_reduce_f32, may be NULL. */
 HYLE_B200_API int hyle_b200_softmax_f32(hyle_b200_stream_t stream, int kind, const float *in,
                                         float *out, uint64_t rows, uint64_t cols, void *workspace,
-                                        uint64_t workspace_bytes);
+                                        uint64_t workspace_bytes, uint32_t *status_word);
+
+/* Stream-ordered clear of a workspace (cudaMemsetAsync): what a caller that receives workspace
+ * memory with arbitrary contents records once before the first launch that uses it. */
+HYLE_B200_API int hyle_b200_workspace_clear(hyle_b200_stream_t stream, void *workspace, uint64_t bytes);
 
 /* Cast{destination type} (include/hyle/compute/operation.h:289-295) for the pairs of the CPU route
  * (src/compute_provider_native/cast.cc:128-176): f32/bf16/f16 among themselves, i32 -> f32,
@@ -429,7 +480,14 @@ HYLE_B200_API int hyle_b200_q8_0_roundtrip_bf16(hyle_b200_stream_t stream, const
  *  - all calls on a device share the array: calls that can overlap on the GPU (different
  *    streams without ordering) race on it; stream-ordered calls are safe, each one clears the
  *    counter on its stream before launching.
- * Inputs, outputs, results and error codes are otherwise those of hyle_b200_q8_0_roundtrip_bf16.
+ *  - the address is cached per device ordinal for the device's PRIMARY context (the one the CUDA
+ *    runtime uses); a second driver context on the same device has its own copy of the array and
+ *    must not share this cache;
+ *  - blocks and decoded values are bit-identical to hyle_b200_q8_0_roundtrip_bf16's.  The sum of
+ *    squares is deterministic for one device and launch grid (two calls on the same data return
+ *    the same bits) but is added in a different order (per-CTA partials, grid = min(1024,
+ *    6 x SMs)), so it agrees with the workspace entry to about 1e-12 relative, not bit for bit.
+ * Inputs, outputs and error codes are otherwise those of hyle_b200_q8_0_roundtrip_bf16.
  */
 #define HYLE_B200_STATIC_MAX_VALUES (UINT64_C(1) << 31)
 HYLE_B200_API int hyle_b200_q8_0_roundtrip_bf16_static(hyle_b200_stream_t stream, const void *in,

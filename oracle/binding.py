@@ -28,10 +28,22 @@ SUM, MEAN, MINIMUM, MAXIMUM = 0, 1, 2, 3
 _vp, _u64, _i, _f = ctypes.c_void_p, ctypes.c_uint64, ctypes.c_int, ctypes.c_float
 
 
+def reference_root() -> str:
+    """Where the reference project's source tree is mounted: ``$HYLE_REF``, else the build machine's
+    mount point.  The one place that default is written; every Makefile takes HYLE_REF from here."""
+    return os.environ.get("HYLE_REF", "/root/reference")
+
+
+def make_environment() -> dict:
+    """The environment for the Makefiles that compile reference sources in place."""
+    return dict(os.environ, HYLE_REF=reference_root())
+
+
 def build(reference: bool = True) -> None:
     """Compile the checker (and the reference floor when the reference tree is mounted)."""
     target = "all" if reference else "libhyle_oracle.so"
-    result = subprocess.run(["make", "-C", ORACLE_DIR, target], capture_output=True, text=True)
+    result = subprocess.run(["make", "-C", ORACLE_DIR, target], capture_output=True, text=True,
+                            env=make_environment())
     if result.returncode != 0:
         raise RuntimeError("building the oracle failed:\n" + result.stdout + result.stderr)
 

@@ -1,6 +1,6 @@
 """Generate tests/golden/ref_floor.npz by RUNNING the reference's own scalar floor.
 
-Needs oracle/_ref/libhyle_ref_floor.so, i.e. the reference tree mounted at /root/reference when
+Needs oracle/_ref/libhyle_ref_floor.so, i.e. the reference tree mounted (at $HYLE_REF) when
 `make -C oracle` ran.  The fixture travels with the repository, so the oracle stays pinned to the
 reference's outputs where the reference tree is absent.  Inputs are seeded; special values follow
 the edge cases of the reference's tests (tests/simd/math_test.cc:1317-1331 invalid softmax rows,

@@ -4,7 +4,7 @@
 // id and host memory, and refuses to hand out a stream, so nothing is ever launched -- this program
 // checks WHICH requests the provider takes and how it declines, not arithmetic.
 //
-// Built by hyle_b200/provider/Makefile against the reference tree in place; prints one line per
+// Built by tests/provider/Makefile against the reference tree in place; prints one line per
 // check and exits non-zero on the first failure.
 #include <array>
 #include <cstdio>
@@ -38,6 +38,9 @@ struct ProbeBackend final {
     return std::unexpected(Status::Unimplemented("probe backend"));
   }
   static Status status(int) noexcept { return Status::Internal("probe backend never launches"); }
+  static detail::EnqueueResult status_word(detail::QueueSequence &, unsigned **) noexcept {
+    return detail::EnqueueResult::rejected(Status::Unimplemented("probe backend"));
+  }
 };
 
 static int failures = 0;
@@ -118,7 +121,7 @@ int main() {
     const std::array out0{f32_row};
     check(declined(*context, Operation(reduce), in, out0), "Reduce over axis 0 declined");
   }
-  {  // Scan along the last axis, f32; the checked i32 scan and other axes are left to the next provider
+  {  // Scan along the last axis, f32 and checked i32; other axes are left to the next provider
     const std::array in{f32_mat};
     const std::array out{f32_mat};
     check(taken(*context, Operation(Scan{.axis = -1, .exclusive = false}), in, out), "Scan{axis=-1} f32");
@@ -127,7 +130,7 @@ int main() {
     const auto i32_mat = dense(DataType::kInt32, {4096, 4096});
     const std::array in_i{i32_mat};
     const std::array out_i{i32_mat};
-    check(declined(*context, Operation(Scan{}), in_i, out_i), "Scan i32 (checked overflow) declined");
+    check(taken(*context, Operation(Scan{}), in_i, out_i), "Scan i32 (overflow reported through the status word)");
   }
   {  // RmsNorm bf16 with bf16 / f32 weight; f16 weight and non-f32 accumulation are declined
     const std::array out{bf16_mat};

@@ -56,7 +56,9 @@ def test_argument_errors_are_reported_before_any_launch(library):
     assert L.hyle_b200_reduce_rows_f32(None, 7, 1 << 20, 1 << 20, 4, 4) == abi.INVALID_VALUE
     assert L.hyle_b200_q8_0_encode(None, abi.BF16, 1 << 20, 33, 1 << 20, None) == abi.INVALID_VALUE  # not /32
     assert L.hyle_b200_q8_0_roundtrip_bf16(None, 1 << 20, 64, 1 << 20, 1 << 20, 1 << 20, None, 1 << 20, 8) == abi.INVALID_VALUE
-    assert L.hyle_b200_logits_reduce_f32(None, None, 4, 4, None, None, None, None, None, 0) == abi.INVALID_VALUE
+    assert L.hyle_b200_logits_reduce_f32(None, None, 4, 4, None, None, None, None, None, 0, None) == abi.INVALID_VALUE
+    assert L.hyle_b200_workspace_clear(None, None, 64) == abi.INVALID_VALUE
+    assert L.hyle_b200_workspace_clear(None, None, 0) == abi.OK
     # empty work is a successful no-op
     assert L.hyle_b200_binary(None, 0, 0, None, None, None, 0, 1) == abi.OK
     assert L.hyle_b200_swiglu_bf16(None, None, None, None, 0, 0, 0, 0) == abi.OK

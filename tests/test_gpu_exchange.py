@@ -30,9 +30,9 @@ def _mailbox(abi, lib):
 def _call(abi, lib, ops, x, pointers, world, rank, epoch, poll_limit):
     count = x.numel()
     workspace = ops.make_workspace("cuda", count)
-    blocks = torch.empty(ops.q8_0_bytes(count), dtype=torch.uint8, device="cuda")
-    decoded = torch.empty_like(x)
-    total = torch.zeros(1, dtype=torch.float64, device="cuda")
+    blocks = ops.new_output(ops.q8_0_bytes(count), torch.uint8)
+    decoded = ops.new_output(x.shape, x.dtype)
+    total = ops.new_output(1, torch.float64).zero_()
     status = torch.zeros(1, dtype=torch.int32, device="cuda")
     abi.check("exchange", lib.hyle_b200_q8_0_roundtrip_bf16_exchange(
         torch.cuda.current_stream().cuda_stream, x.data_ptr(), count, blocks.data_ptr(), decoded.data_ptr(),

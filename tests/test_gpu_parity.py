@@ -119,7 +119,7 @@ def test_binary_variants_and_broadcast_periods(oracle):
         lhs = rng.standard_normal(count).astype(np.float32)
         rhs = rng.standard_normal(period).astype(np.float32)
         for kind, okind in [(abi.BINARY_ADD, ob.ADD), (abi.BINARY_MULTIPLY, ob.MULTIPLY)]:
-            out = torch.empty(count, dtype=torch.float32, device=DEV)
+            out = ops.new_output(count, torch.float32, DEV)
             lhs_dev, rhs_dev = to_dev(lhs), to_dev(rhs)
             abi.check("binary", abi.load().hyle_b200_binary(
                 torch.cuda.current_stream().cuda_stream, kind, abi.F32, lhs_dev.data_ptr(),
@@ -293,32 +293,33 @@ def test_logits_config(oracle, batch):
         assert int(index[row]) == int(np.flatnonzero(logits[row] == peak)[0])
 
 
-def test_logits_config_256_rows_against_size_independent_properties(oracle):
-    """Full workload size: argmax and lse are compared with the checker on every row (cheap), the
-    155 MB of probabilities through row sums and a sampled set of rows."""
+def test_logits_config_256_rows_every_row_against_the_checker(oracle):
+    """The benchmarked shape itself: all 256 rows of lse, probabilities, argmax index and value are
+    compared with the checker, for the cluster kernel and (twice) for the streaming kernel."""
     logits, tied = wl.logits_inputs(256)
-    dev = to_dev(logits)
-    lse, probs, index, value = ops.logits_reduce(dev)
-    want_i, want_v = oracle.argmax(logits)
-    assert np.array_equal(index.cpu().numpy(), want_i)
     assert len(tied) >= 2
-    sums = probs.float().sum(dim=1).cpu().numpy()
-    assert np.all(np.abs(sums - 1.0) < 2e-3)
-    rows = sorted(set(tied + [0, 100, 255]))
-    want_lse, want_p, want_p32, _, _ = oracle.logits_reduce(logits[rows])
-    assert np.all(np.abs(lse.cpu().numpy()[rows] - want_lse) <= F32_REL * np.abs(want_lse))
-    assert_bf16_close(bf16_words(probs[rows]), want_p, want_p32, BF16_REL)
-    # standalone argmax and f32 softmax agree with the fused launch
+    dev = to_dev(logits)
+    want_lse, want_p, want_p32, want_i, want_v = oracle.logits_reduce(logits)
+
+    def compare(lse, probs, index, value):
+        assert np.array_equal(index.cpu().numpy(), want_i)
+        assert_f32_bits(value.cpu().numpy(), want_v)
+        assert np.all(np.abs(lse.cpu().numpy() - want_lse) <= F32_REL * np.abs(want_lse))
+        assert assert_bf16_close(bf16_words(probs), want_p, want_p32, BF16_REL) < 1e-2
+        assert np.all(np.abs(probs.float().sum(dim=1).cpu().numpy() - 1.0) < 2e-3)
+
+    lse, probs, index, value = ops.logits_reduce(dev)
+    compare(lse, probs, index, value)
+    for row in tied:  # the duplicated maximum: the lower copy wins
+        assert int(index[row]) == int(np.flatnonzero(logits[row] == logits[row].max())[0])
+    # standalone argmax agrees with the fused launch
     idx2, val2 = ops.argmax(dev)
     assert torch.equal(idx2, index) and torch.equal(val2, value)
-    # the streaming kernel (taken when a workspace is given) against the same checks
+    del lse, probs
+    # the streaming kernel (taken when a workspace is given): twice, every launch re-arms the workspace
     scratch = ops.make_logits_workspace("cuda", 256, logits.shape[1])
-    for _ in range(2):  # twice: every launch leaves the workspace re-armed
-        lse_s, probs_s, index_s, value_s = ops.logits_reduce(dev, workspace=scratch)
-        assert torch.equal(index_s, index) and torch.equal(value_s, value)
-        assert np.all(np.abs(lse_s.cpu().numpy()[rows] - want_lse) <= F32_REL * np.abs(want_lse))
-        assert_bf16_close(bf16_words(probs_s[rows]), want_p, want_p32, BF16_REL)
-        assert np.all(np.abs(probs_s.float().sum(dim=1).cpu().numpy() - 1.0) < 2e-3)
+    for _ in range(2):
+        compare(*ops.logits_reduce(dev, workspace=scratch))
 
 
 @pytest.mark.parametrize("cols", [1024, 4112, 19456, 40000, 151936, 327680])
@@ -349,6 +350,56 @@ def test_logits_streaming_kernel_shapes_and_invalid_rows(oracle, cols):
         assert np.all(np.abs(got[ok] - want[ok]) <= tol)
     # a smaller batch reuses the same workspace
     check_logits(oracle, x[:64], workspace=scratch)
+
+
+@pytest.mark.parametrize("vectors", [5, 10])
+def test_logits_streaming_kernel_reduces_missing_partials_itself(oracle, vectors):
+    """The rare path, forced: with a window of one row a second-pass task is claimed right behind the
+    first-pass tasks it depends on, and with one poll of patience its warps reduce the missing chunks
+    themselves from global memory instead of waiting for another CTA.  Results and status must be those
+    of the ordinary schedule; the same holds for every schedule a tuning can ask for."""
+    rng = np.random.default_rng(vectors)
+    rows, cols = 96, 40000
+    x = (4.0 * rng.standard_normal((rows, cols))).astype(np.float32)
+    x[2, cols // 2] = np.nan
+    x[4, :] = -np.inf
+    x[7, 5] = x[7, cols - 3] = x[7].max() + 1.0
+    want_lse, want_p, want_p32, want_i, want_v = oracle.logits_reduce(x)
+    dev = to_dev(x)
+    scratch = ops.make_logits_workspace("cuda", rows, cols)
+    status = torch.zeros(1, dtype=torch.int32, device=DEV)
+    for window, patience, per_sm in [(1, 1, 4), (1, 1, 1), (2, 3, 2), (8, 0, 0), (0, 0, 3), (96, 0, 0)]:
+        tuning = abi.StreamTuning(vectors, window, patience, per_sm)
+        plan = ops.logits_stream_plan(rows, cols, tuning)
+        assert plan is not None and plan.chunk_vectors == vectors
+        assert plan.fixed_tasks_per_cta * plan.grid <= plan.window_rows * plan.chunks_per_row  # fixed tasks are first-pass tasks
+        lse, probs, index, value = ops.logits_reduce(dev, workspace=scratch, status=status, tuning=tuning)
+        assert np.array_equal(index.cpu().numpy(), want_i)
+        assert_f32_bits(value.cpu().numpy(), want_v)
+        got_lse = lse.cpu().numpy()
+        ok = ~np.isnan(want_lse)
+        assert np.array_equal(np.isnan(got_lse), ~ok)
+        assert np.all(np.abs(got_lse[ok] - want_lse[ok]) <= F32_REL * np.abs(want_lse[ok]))
+        assert_bf16_close(bf16_words(probs), want_p, want_p32, BF16_REL)
+        assert status.item() == 0
+    with pytest.raises(abi.KernelError):  # a tuning names the streaming kernel: shapes that cannot take it are refused
+        ops.logits_reduce(dev[:8], workspace=scratch, tuning=abi.StreamTuning(vectors, 0, 0, 0))
+    with pytest.raises(abi.KernelError):
+        ops.logits_reduce(dev, workspace=scratch, tuning=abi.StreamTuning(7, 0, 0, 0))
+
+
+def test_logits_stream_plan_of_the_benchmarked_shapes():
+    for rows in (64, 256, 1024, 4096):
+        plan = ops.logits_stream_plan(rows, wl.VOCAB)
+        assert plan is not None
+        assert plan.chunk_vectors == (5 if rows <= 512 else 10)
+        assert plan.chunks_per_row * plan.chunk_values >= wl.VOCAB > (plan.chunks_per_row - 1) * plan.chunk_values
+        assert plan.chunk_values % 16 == 0 and plan.chunks_per_row <= 32
+        assert 8 <= plan.window_rows <= min(rows, 64)
+        assert plan.grid % plan.ctas_per_sm == 0 and 1 <= plan.ctas_per_sm <= 4
+        assert plan.fixed_tasks_per_cta * plan.grid <= plan.window_rows * plan.chunks_per_row
+    assert ops.logits_stream_plan(16, wl.VOCAB) is None          # small batches take the cluster kernel
+    assert ops.logits_stream_plan(256, 151937) is None           # rows must be 64-byte multiples
 
 
 @pytest.mark.parametrize("cols", [1, 7, 8, 1000, 1024, 19000, 19456, 40000, 151936, 262144])
@@ -384,6 +435,24 @@ def test_argmax_golden_cases(oracle, golden):
     assert_f32_bits(val.cpu().numpy(), golden["argmax_value"])
     _, _, idx2, _ = ops.logits_reduce(to_dev(x))
     assert np.array_equal(idx2.cpu().numpy(), golden["argmax_index"])
+
+
+def test_argmax_value_is_the_winning_element_on_signed_zero_ties(oracle):
+    """A row whose maximum is zero, first as -0 and later as +0: the index is the first one's and the
+    value is THAT element (-0), as the reference's top_k_f32 returns scores[index]."""
+    rng = np.random.default_rng(77)
+    for rows, cols in [(3, 1000), (70, 40000)]:
+        x = -np.abs(rng.standard_normal((rows, cols))).astype(np.float32) - 1.0
+        x[0, 3], x[0, cols - 5] = -0.0, 0.0
+        x[1, 7], x[1, 2] = -0.0, 0.0            # +0 first: it wins
+        x[rows - 1, cols // 2], x[rows - 1, cols - 1] = -0.0, 0.0
+        want_i, want_v = oracle.argmax(x)
+        assert want_i[0] == 3 and np.signbit(want_v[0]) and want_i[1] == 2 and not np.signbit(want_v[1])
+        dev = to_dev(x)
+        scratch = ops.make_logits_workspace("cuda", rows, cols)
+        for index, value in (ops.argmax(dev), ops.logits_reduce(dev)[2:], ops.logits_reduce(dev, workspace=scratch)[2:]):
+            assert np.array_equal(index.cpu().numpy(), want_i)
+            assert np.array_equal(value.cpu().numpy().view(np.uint32), want_v.view(np.uint32))
 
 
 # ---- LayerNorm ------------------------------------------------------------------------------------------------------------
@@ -809,6 +878,7 @@ def test_q8_0_rounding_ties_and_ragged_tiles(oracle):
         view = carrier[2:2 + blocks * 34]
         ops.q8_0_roundtrip(dev, ws, blocks=view)
         assert np.array_equal(view.cpu().numpy(), want_b)
+        assert int(carrier[:2].sum()) == 0 and int(carrier[2 + blocks * 34:].sum()) == 0  # margins untouched
         assert torch.equal(ops.q8_0_decode(view, w.size).view(torch.int16), got_d.view(torch.int16))
 
 
@@ -835,3 +905,35 @@ def test_q8_0_full_size_properties():
     assert abs(sum(halves) - total.item()) <= 1e-9 * total.item()
     reference = (w.double() ** 2).sum().item()
     assert abs(total.item() - reference) <= F32_REL * reference
+
+
+def test_q8_0_benchmark_size_chunks_against_checker(oracle):
+    """R = 262144 x 8192, the size the throughput is quoted on: 2^31 values, byte offsets up to 4 GiB in
+    both bf16 tensors, i.e. past the signed 32-bit range from the middle on.  The input is generated on
+    the device; three 1024-row chunks (the first rows, the rows straddling the 2 GiB byte offset, the
+    last rows) are copied back and their blocks and decoded values must equal, byte for byte, the
+    checker's on the very same input words (the formula of tests/compute_provider_ggml/native_paged_test.cc:255-326)."""
+    rows, cols, chunk = 262144, wl.SWEEP_COLS, 1024
+    free, _ = torch.cuda.mem_get_info()
+    if free < 20 * 2 ** 30:
+        pytest.skip("needs about 13 GiB of free device memory")
+    w = wl.q8_sweep_device_shard(wl.shard_rows(rows, 1, 0))
+    ws = ops.make_workspace(DEV, w.numel())
+    status = torch.zeros(1, dtype=torch.int32, device=DEV)
+    blocks, decoded, total = ops.q8_0_roundtrip(w, ws, status=status)
+    assert status.item() == 0
+    blocks2d = blocks.view(rows, cols // 32 * 34)
+    for first in (0, rows // 2 - chunk // 2, rows - chunk):
+        words = bf16_words(w[first:first + chunk]).copy()
+        want_blocks, want_decoded, _, invalid = oracle.q8_0_roundtrip(words)
+        assert not invalid
+        assert np.array_equal(blocks2d[first:first + chunk].cpu().numpy().ravel(), want_blocks), first
+        assert np.array_equal(bf16_words(decoded[first:first + chunk]).ravel(), want_decoded), first
+    # sum of squares against a chunked f64 sum on the device
+    reference = 0.0
+    for first in range(0, rows, 16384):
+        reference += (w[first:first + 16384].double() ** 2).sum().item()
+    assert abs(total.item() - reference) <= F32_REL * reference
+    # the separate decode of the kernel's own blocks reproduces the fused output across the whole 4 GiB
+    again = ops.q8_0_decode(blocks, w.numel())
+    assert torch.equal(again.view(torch.int16), decoded.view(torch.int16).ravel())

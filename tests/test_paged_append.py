@@ -119,7 +119,12 @@ def test_metadata_packing_matches_wire_format():
 
 # ---- GPU ---------------------------------------------------------------------------------------
 def device_bytes(a):
-    return torch.from_numpy(np.ascontiguousarray(a)).cuda()
+    """A device copy placed by the operators' output allocator: inside guard bands during a GPU test,
+    because the arenas made here are written in place by the kernels under test."""
+    a = np.ascontiguousarray(a)
+    out = ops.new_output(a.shape, torch.from_numpy(a).dtype)
+    out.copy_(torch.from_numpy(a))
+    return out
 
 
 def run_product(arena, new_rows, words, page_rows):
@@ -184,6 +189,7 @@ def test_paged_append_malformed_episode_unaligned_bases_and_arguments(oracle):
     d_words = torch.from_numpy(words.view(np.int32).copy()).cuda()
     ops.paged_append(shifted, device_bytes(new_rows), d_words, page_rows)
     assert np.array_equal(shifted.cpu().numpy(), oracle.paged_append(arena, new_rows, words, page_rows))
+    assert int(backing[:2].sum()) == 0 and int(backing[2 + arena.size:].sum()) == 0  # margins untouched
     # Arena-only episode without new rows.
     only_arena = words.copy()
     for slot in range(int(only_arena[0])):

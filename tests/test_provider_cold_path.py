@@ -1,32 +1,56 @@
 """The C++23 provider adapter (hyle_b200/provider) against the REFERENCE's own runtime.
 
-`cold_path_test.cc` registers the adapter with `make_custom_provider`, creates a reference
-`Context` and calls the reference's `compute::prepare` for every operator of the path: the provider
-must be selected for its domain and decline (Status::Unimplemented) outside it.  The program links
-the reference's compute core compiled in place from the reference tree, so it is built only where
-that tree is mounted; elsewhere the prebuilt binary (baseline/_ref, which travels) is run.
+`tests/provider/cold_path_test.cc` registers the adapter with `make_custom_provider`, creates a
+reference `Context` and calls the reference's `compute::prepare` for every operator of the path: the
+provider must be selected for its domain and decline (Status::Unimplemented) outside it.  The program
+links the reference's compute core compiled in place from the reference tree, so it is built only
+where that tree is mounted; elsewhere the prebuilt binary (oracle/_ref/provider, which travels) is run.
 """
 import os
 import subprocess
 
 import pytest
 
+from oracle.binding import make_environment, reference_root
+
 ROOT = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
-BINARY = os.path.join(ROOT, "baseline", "_ref", "b200_cold_path_test")
-REFERENCE = "/root/reference"
+PROVIDER_TESTS = os.path.join(ROOT, "tests", "provider")
+BINARIES = os.path.join(ROOT, "oracle", "_ref", "provider")
+
+
+def build_provider_tests():
+    """Compile both test programs where the reference tree is mounted; returns False elsewhere."""
+    from hyle_b200.build import build
+
+    build()  # the programs link libhyle_b200.so
+    if not os.path.isdir(os.path.join(reference_root(), "include", "hyle")):
+        return False
+    made = subprocess.run(["make", "-C", PROVIDER_TESTS, "-j", "8"], capture_output=True, text=True, timeout=1800,
+                          env=make_environment())
+    assert made.returncode == 0, made.stdout[-3000:] + made.stderr[-3000:]
+    return True
 
 
 def test_adapter_is_selected_by_the_reference_runtime():
-    from hyle_b200.build import build
-
-    build()  # the test binary links libhyle_b200.so for the host-side workspace query
-    if os.path.isdir(os.path.join(REFERENCE, "include", "hyle")):
-        made = subprocess.run(["make", "-C", os.path.join(ROOT, "hyle_b200", "provider"), "-j", "8"],
-                              capture_output=True, text=True, timeout=1200)
-        assert made.returncode == 0, made.stdout[-3000:] + made.stderr[-3000:]
-    if not os.path.exists(BINARY):
-        pytest.skip("reference tree absent and no prebuilt baseline/_ref/b200_cold_path_test")
-    run = subprocess.run([BINARY], capture_output=True, text=True, timeout=120)
+    build_provider_tests()
+    binary = os.path.join(BINARIES, "b200_cold_path_test")
+    if not os.path.exists(binary):
+        pytest.skip("reference tree absent and no prebuilt oracle/_ref/provider/b200_cold_path_test")
+    run = subprocess.run([binary], capture_output=True, text=True, timeout=120)
     assert run.returncode == 0, run.stdout + run.stderr
     assert "0 failure(s)" in run.stdout
     assert run.stdout.count("ok  ") >= 49 and "FAIL" not in run.stdout
+
+
+def test_hot_path_program_is_built_with_the_cold_one():
+    """The GPU half (tests/test_provider_hot_path.py) runs a prebuilt program: make sure it exists
+    wherever the cold one could be built, and that without a GPU it says so instead of failing."""
+    if not build_provider_tests():
+        pytest.skip("reference tree absent: nothing to build here")
+    binary = os.path.join(BINARIES, "b200_hot_path_test")
+    assert os.path.exists(binary)
+    import torch
+
+    if not torch.cuda.is_available():
+        run = subprocess.run([binary], capture_output=True, text=True, timeout=120)
+        assert run.returncode == 77 and "needs a GPU" in run.stdout

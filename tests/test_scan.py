@@ -109,7 +109,7 @@ def test_scan_i32_overflow_reports_and_writes_nothing(oracle):
         _, want_status = oracle.scan(n)
         assert want_status == 16
         d_in = torch.from_numpy(n).cuda()
-        d_out = torch.full_like(d_in, -7)
+        d_out = ops.new_output(d_in.shape, d_in.dtype).fill_(-7)
         status = torch.zeros(1, dtype=torch.int32, device="cuda")
         assert library.hyle_b200_scan(stream, abi.I32, d_in.data_ptr(), d_out.data_ptr(), rows, cols, 0, status.data_ptr()) == abi.OK
         torch.cuda.synchronize()

@@ -124,7 +124,7 @@ def test_strided_cast_negative_strides_and_arguments():
     library = abi.load()
     stream = torch.cuda.current_stream().cuda_stream
     x = torch.arange(24, dtype=torch.float32, device="cuda").reshape(4, 6)
-    out = torch.empty(4, 6, dtype=torch.float32, device="cuda")
+    out = ops.new_output((4, 6), torch.float32)
     dims = (ctypes.c_int64 * 2)(4, 6)
     strides = (ctypes.c_int64 * 2)(-24, -4)  # both axes reversed, starting from the last element
     last = x.data_ptr() + 23 * 4
