@@ -635,17 +635,15 @@ logits_regs_kernel(const LogitsParams p) {
 // ================================================================================================
 constexpr int kStreamThreads = 256;
 constexpr int kStreamWarps = kStreamThreads / 32;
-// A task's chunk is kVectors float4 per thread, held in registers for the length of the task.  Two
-// sizes are built: 10 (10 240 values, 40 KB of staging, 4 CTAs per SM) for large batches, where the
-// per-task overhead counts, and 5 (5120 values, 20 KB, 4 CTAs per SM) for small ones, where the
-// launch's ramp and its write-only tail count: half-size tasks halve both.
-constexpr int kStreamVectorsLarge = 10;
-constexpr int kStreamVectorsSmall = 5;
+// A task's chunk is kStreamVectors float4 per thread (10 240 values, 40 KB of staging, 4 CTAs per
+// SM), held in registers for the length of the task.  Half-size chunks (5 float4, measured on
+// 64 / 256 / 1024 rows of 151 936) lose a quarter of the throughput to the per-task overhead: 0.56
+// against 0.76 of the copy peak at 256 rows.
+constexpr int kStreamVectors = 10;
 __host__ __device__ constexpr uint32_t stream_chunk_values(int vectors) { return kStreamThreads * vectors * 4; }
 constexpr size_t stream_stage_bytes(int vectors) { return static_cast<size_t>(kStreamThreads) * vectors * sizeof(float4); }
-constexpr int stream_ctas_per_sm(int) { return 4; }
+constexpr int kStreamCtasPerSm = 4;
 constexpr uint32_t kStreamMaxChunks = 32;  // one partial per lane
-constexpr uint64_t kStreamSmallBatchRows = 512;  // up to here the small chunk is taken (when the row fits 32 of them)
 // Rows between a row's two passes must cover the tasks in flight (two per resident CTA), or
 // second-pass tasks find their partials missing; and must stay inside L2 (126 MB).  Measured at
 // 256 / 1024 rows of 151 936 with 10 240-value chunks: 32 rows -> 0.71 / 0.88 of the copy peak,
@@ -787,9 +785,7 @@ constexpr uint32_t kStreamLoadPollLimit = 1u << 20;  // x up to 20 us each
 // may not be running (a grid larger than what is resident), so the waiter must not depend on it.
 // Two writers of one partial store the same maximum and index and sums that agree to rounding, and
 // each word is stored whole, so a reader may combine words of either.
-// (Scalars by value: a reference to the kernel's parameter struct would make the caller copy it to
-// its stack.)
-__device__ __noinline__ void stream_help_chunk(const float *row_in, uint32_t cols, uint32_t chunk_values, uint32_t chunk_id,
+__device__ __forceinline__ void stream_help_chunk(const float *row_in, uint32_t cols, uint32_t chunk_values, uint32_t chunk_id,
                                                StreamPartial *out, unsigned long long tag, bool want_index) {
   const int lane = threadIdx.x & 31;
   const uint32_t begin = chunk_id * chunk_values;
@@ -825,7 +821,7 @@ __device__ __noinline__ void stream_help_chunk(const float *row_in, uint32_t col
 }
 
 template <int kMode, int kVectors, int kFull>
-__global__ void __launch_bounds__(kStreamThreads, stream_ctas_per_sm(kVectors))
+__global__ void __launch_bounds__(kStreamThreads, kStreamCtasPerSm)
 logits_stream_kernel(const StreamParams s) {
   // What needs no global memory (task decoding, barrier set-up) runs before the wait for the
   // previous grid: it overlaps that grid's tail.
@@ -864,11 +860,18 @@ logits_stream_kernel(const StreamParams s) {
   }
   if (t == 64 && s.fixed >= 2u) s_tasks[1] = decode(static_cast<uint64_t>(gridDim.x) + blockIdx.x);
   asm volatile("griddepcontrol.wait;" ::: "memory");  // the previous grid has completed and flushed
+  // A CTA's tasks must come in list order (the loop stops at the first position past the end), so
+  // the claims that fill the ring at the start are made by ONE thread: a pair of positions at once
+  // when nothing is fixed.
   if (t == 0) {
-    if (s.fixed == 0u) s_tasks[0] = decode(claim());
+    if (s.fixed == 0u) {
+      const unsigned long long pair = atomicAdd(s.next_task, 2ull);
+      s_tasks[0] = decode(pair);
+      s_tasks[1] = decode(pair + 1);
+    }
     issue_load(s_tasks[0]);
+    if (s.fixed == 1u) s_tasks[1] = decode(claim());
   }
-  if (t == 64 && s.fixed < 2u) s_tasks[1] = decode(claim());
   const unsigned long long tag = static_cast<unsigned long long>(*s.epoch + 1u) << 32;
   __syncthreads();
 
@@ -883,46 +886,6 @@ logits_stream_kernel(const StreamParams s) {
     const uint32_t chunk_id = now.chunk_id;
     const uint32_t begin = chunk_id * s.chunk;
     const uint32_t vectors = (min(begin + s.chunk, p.cols) - begin) / 4;
-
-    // Second pass: the row's partials, fetched BEFORE the chunk is taken into registers, so that the
-    // rare slow path below runs with few live registers (and the chunk's copy stays in flight).
-    WarpEntry mine = nothing;
-    bool complete = true;
-    if (second) {
-      // Every warp fetches the row's partials itself, one per lane, and polls until all carry this
-      // launch's tag.  They were written `window` rows ago: the first look almost always succeeds.
-      // A partial still missing after kStreamHelpAfter looks may belong to a CTA that is not running
-      // (the grid is sized to be co-resident, but nothing guarantees it: another kernel may hold SMs),
-      // so the warp then reduces its share of the missing chunks ITSELF, from global memory, and
-      // polls on for the chunks its sibling warps are reducing.  Nothing here waits for a CTA other
-      // than its own, so the kernel completes, with right results, whatever is resident.
-      const StreamPartial *in = s.partials + row * s.chunks + (lane < s.chunks ? lane : 0);
-      unsigned long long m = 0, q = 0, i = 0;
-      auto look = [&]() {
-        if (lane >= s.chunks) return true;
-        m = load_relaxed(&in->maximum);
-        q = load_relaxed(&in->sum);
-        i = load_relaxed(&in->index);
-        return (m ^ tag) >> 32 == 0 && (q ^ tag) >> 32 == 0 && (i ^ tag) >> 32 == 0;
-      };
-      bool have = look();
-      for (uint32_t polls = 0; !__all_sync(kFullMask, have) && polls < s.help_after; ++polls)
-        if (!have) have = look();
-      uint32_t missing = __ballot_sync(kFullMask, !have);
-      if (missing != 0u) {  // warp-uniform, rare
-        for (uint32_t rest = missing; rest != 0u; rest &= rest - 1u) {
-          const uint32_t chunk = __ffs(rest) - 1;
-          if (chunk % kStreamWarps == static_cast<uint32_t>(warp))
-            stream_help_chunk(p.in + row * p.cols, p.cols, s.chunk, chunk, s.partials + row * s.chunks + chunk, tag, want_index);
-        }
-        for (uint32_t polls = 0; !__all_sync(kFullMask, have) && polls < kStreamPollLimit; ++polls)
-          if (!have) have = look();
-      }
-      complete = __all_sync(kFullMask, have);
-      if (lane < s.chunks)
-        mine = WarpEntry{__uint_as_float(static_cast<uint32_t>(m)), __uint_as_float(static_cast<uint32_t>(q)),
-                         static_cast<uint32_t>(i), 0u};
-    }
 
     // The chunk has been on its way since the previous task; take it into registers.
     bool landed = mbarrier_try_wait(&s_full, phase);
@@ -981,6 +944,51 @@ logits_stream_kernel(const StreamParams s) {
         }
       }
     } else {
+      WarpEntry mine = nothing;
+      bool complete = true;
+      // Every warp fetches the row's partials itself, one per lane, and polls until all carry this
+      // launch's tag.  They were written `window` rows ago: the first look almost always succeeds.
+      // A partial still missing after kStreamHelpAfter looks may belong to a CTA that is not running
+      // (the grid is sized to be co-resident, but nothing guarantees it: another kernel may hold SMs),
+      // so the warp then reduces its share of the missing chunks ITSELF, from global memory, and
+      // polls on for the chunks its sibling warps are reducing.  Nothing here waits for a CTA other
+      // than its own, so the kernel completes, with right results, whatever is resident.
+      const StreamPartial *in = s.partials + row * s.chunks + (lane < s.chunks ? lane : 0);
+      unsigned long long m = 0, q = 0, i = 0;
+      auto look = [&]() {
+        if (lane >= s.chunks) return true;
+        m = load_relaxed(&in->maximum);
+        q = load_relaxed(&in->sum);
+        i = load_relaxed(&in->index);
+        return (m ^ tag) >> 32 == 0 && (q ^ tag) >> 32 == 0 && (i ^ tag) >> 32 == 0;
+      };
+      bool have = look();
+      for (uint32_t polls = 0; !__all_sync(kFullMask, have) && polls < s.help_after; ++polls)
+        if (!have) have = look();
+      uint32_t missing = __ballot_sync(kFullMask, !have);
+      if (missing != 0u) {  // warp-uniform, rare
+        for (uint32_t rest = missing; rest != 0u; rest &= rest - 1u) {
+          const uint32_t chunk = __ffs(rest) - 1;
+          if (chunk % kStreamWarps == static_cast<uint32_t>(warp))
+            stream_help_chunk(p.in + row * p.cols, p.cols, s.chunk, chunk, s.partials + row * s.chunks + chunk, tag, want_index);
+        }
+        for (uint32_t polls = 0; !__all_sync(kFullMask, have) && polls < kStreamPollLimit; ++polls)
+          if (!have) have = look();
+        // The chunk's values are read again (from L2) rather than kept alive across the slow path above:
+        // kept, their forty registers would have to coexist with its working set, and the common path
+        // would pay for the rare one in spills (measured: 45 -> 67 us at 256 x 151 936).
+        const float4 *again = reinterpret_cast<const float4 *>(p.in + row * p.cols + begin) + t;
+        const uint64_t once = policy_evict_first();
+#pragma unroll
+        for (int j = 0; j < kVectors; ++j)
+          x[j] = (j < kFull || j * kStreamThreads + t < vectors) ? load_hinted(again + j * kStreamThreads, once)
+                                                                 : make_float4(neg_inf, neg_inf, neg_inf, neg_inf);
+        if (!landed) x[0].x = CUDART_NAN_F;
+      }
+      complete = __all_sync(kFullMask, have);
+      if (lane < s.chunks)
+        mine = WarpEntry{__uint_as_float(static_cast<uint32_t>(m)), __uint_as_float(static_cast<uint32_t>(q)),
+                         static_cast<uint32_t>(i), 0u};
       if ((!complete || !landed) && t == 0 && p.status != nullptr) atomicOr(p.status, HYLE_B200_STATUS_STREAM_WAIT_TIMEOUT);
       const Combined all = combine(mine);
       const float maximum = all.maximum, total_sum = all.total, row_c = __fmul_rn(all.maximum, kLog2e);
@@ -1035,7 +1043,10 @@ logits_stream_kernel(const StreamParams s) {
     slot = slot_next;
   }
 
-  // The CTA that leaves last re-arms the workspace for the next stream-ordered launch.
+  // The CTA that leaves last re-arms the workspace for the next stream-ordered launch.  The barrier
+  // orders the claiming thread's last atomic (consumed before it left the loop) before the ticket,
+  // so no claim can land on the counter after it has been reset.
+  __syncthreads();
   if (t == 0) {
     __threadfence();
     s_flag = atomicAdd(s.ticket, 1u) == gridDim.x - 1;
@@ -1134,16 +1145,14 @@ inline bool stream_eligible(uint64_t rows, uint64_t cols, int vectors) {
          stream_chunks(cols, vectors) <= kStreamMaxChunks;
 }
 
-// Partials for the finest chunking the shape may be given.
 uint64_t stream_workspace_bytes(uint64_t rows, uint64_t cols) {
-  const int vectors = stream_chunks(cols, kStreamVectorsSmall) <= kStreamMaxChunks ? kStreamVectorsSmall : kStreamVectorsLarge;
-  return kStreamHeaderBytes + rows * stream_chunks(cols, vectors) * sizeof(StreamPartial);
+  return kStreamHeaderBytes + rows * stream_chunks(cols, kStreamVectors) * sizeof(StreamPartial);
 }
 
 // CTAs of one instantiation that fit an SM, by the occupancy calculator, cached per device.
 template <class Kernel>
 int stream_resident_ctas(Kernel kernel, size_t shared_bytes, int slot) {
-  static int cached[8][64] = {};
+  static int cached[4][64] = {};
   int device = 0;
   cudaGetDevice(&device);
   if (device < 0 || device >= 64) device = 0;
@@ -1156,22 +1165,17 @@ int stream_resident_ctas(Kernel kernel, size_t shared_bytes, int slot) {
   return cached[slot][device];
 }
 
-// `resident` = CTAs per SM the chosen instantiation can hold.  `tuning` may be null.
-StreamPlan make_stream_plan(uint64_t rows, uint64_t cols, const hyle_b200_stream_tuning *tuning, int sms, int resident_small,
-                            int resident_large) {
+// `resident` = CTAs per SM the kernel can hold (occupancy calculator).  `tuning` may be null.
+StreamPlan make_stream_plan(uint64_t rows, uint64_t cols, const hyle_b200_stream_tuning *tuning, int sms, int resident) {
   StreamPlan plan{};
-  int vectors = tuning != nullptr ? tuning->chunk_vectors : 0;
-  if (vectors != 0 && vectors != kStreamVectorsSmall && vectors != kStreamVectorsLarge) return plan;
-  if (vectors == 0)
-    vectors = rows <= kStreamSmallBatchRows && stream_eligible(rows, cols, kStreamVectorsSmall) ? kStreamVectorsSmall
-                                                                                                  : kStreamVectorsLarge;
+  if (tuning != nullptr && tuning->chunk_vectors != 0 && tuning->chunk_vectors != kStreamVectors) return plan;
+  const int vectors = kStreamVectors;
   if (!stream_eligible(rows, cols, vectors)) return plan;
   plan.vectors = vectors;
   plan.chunks = stream_chunks(cols, vectors);
   plan.chunk = static_cast<uint32_t>((cols / plan.chunks + 15) / 16 * 16);
   if (static_cast<uint64_t>(plan.chunk) * plan.chunks < cols) plan.chunk += 16;
-  const int resident = vectors == kStreamVectorsSmall ? resident_small : resident_large;
-  int per_sm = stream_ctas_per_sm(vectors);
+  int per_sm = kStreamCtasPerSm;
   if (tuning != nullptr && tuning->ctas_per_sm > 0 && tuning->ctas_per_sm < per_sm) per_sm = tuning->ctas_per_sm;
   if (per_sm > resident) per_sm = resident;
   plan.ctas_per_sm = per_sm;
@@ -1192,16 +1196,12 @@ StreamPlan make_stream_plan(uint64_t rows, uint64_t cols, const hyle_b200_stream
   return plan;
 }
 
-template <int kMode, int kVectors>
-int launch_stream_sized(cudaStream_t stream, const LogitsParams &p, void *workspace, const hyle_b200_stream_tuning *tuning) {
-  constexpr int kAlmost = kVectors - 1;
-  constexpr size_t kStage = stream_stage_bytes(kVectors);
-  const int slot = kMode * 2 + (kVectors == kStreamVectorsSmall ? 0 : 1);
-  const int resident = stream_resident_ctas(logits_stream_kernel<kMode, kVectors, 0>, kStage, slot);
-  hyle_b200_stream_tuning chosen{};
-  if (tuning != nullptr) chosen = *tuning;
-  chosen.chunk_vectors = kVectors;
-  const StreamPlan plan = make_stream_plan(p.rows, p.cols, &chosen, sm_count(), resident, resident);
+template <int kMode>
+int launch_stream(cudaStream_t stream, const LogitsParams &p, void *workspace, const hyle_b200_stream_tuning *tuning) {
+  constexpr int kAlmost = kStreamVectors - 1;
+  constexpr size_t kStage = stream_stage_bytes(kStreamVectors);
+  const int resident = stream_resident_ctas(logits_stream_kernel<kMode, kStreamVectors, 0>, kStage, kMode);
+  const StreamPlan plan = make_stream_plan(p.rows, p.cols, tuning, sm_count(), resident);
   if (plan.vectors == 0) return HYLE_B200_INVALID_VALUE;
   StreamParams s{};
   s.p = p;
@@ -1218,19 +1218,8 @@ int launch_stream_sized(cudaStream_t stream, const LogitsParams &p, void *worksp
   const uint32_t last = p.cols - (s.chunks - 1) * s.chunk;  // the shortest chunk
   const bool almost_full = s.chunk / 4 >= static_cast<uint32_t>(kAlmost) * kStreamThreads &&
                            last / 4 >= static_cast<uint32_t>(kAlmost) * kStreamThreads;
-  return launch(almost_full ? logits_stream_kernel<kMode, kVectors, kAlmost> : logits_stream_kernel<kMode, kVectors, 0>,
+  return launch(almost_full ? logits_stream_kernel<kMode, kStreamVectors, kAlmost> : logits_stream_kernel<kMode, kStreamVectors, 0>,
                 dim3(plan.grid), dim3(kStreamThreads), kStage, stream, s);
-}
-
-template <int kMode>
-int launch_stream(cudaStream_t stream, const LogitsParams &p, void *workspace, const hyle_b200_stream_tuning *tuning) {
-  int vectors = tuning != nullptr ? tuning->chunk_vectors : 0;
-  if (vectors == 0)
-    vectors = p.rows <= kStreamSmallBatchRows && stream_eligible(p.rows, p.cols, kStreamVectorsSmall) ? kStreamVectorsSmall
-                                                                                                        : kStreamVectorsLarge;
-  if (vectors == kStreamVectorsSmall) return launch_stream_sized<kMode, kStreamVectorsSmall>(stream, p, workspace, tuning);
-  if (vectors == kStreamVectorsLarge) return launch_stream_sized<kMode, kStreamVectorsLarge>(stream, p, workspace, tuning);
-  return HYLE_B200_INVALID_VALUE;
 }
 
 template <int kMode>
@@ -1240,7 +1229,7 @@ int launch_logits(cudaStream_t stream, LogitsParams p, bool vec, void *workspace
   if constexpr (kMode != kArgmaxOnly) {
     // Many rows with an output tensor: the two-pass streaming kernel (needs the caller's workspace).
     if (vec && p.out != nullptr && p.out != static_cast<const void *>(p.in) && workspace != nullptr &&
-        stream_eligible(p.rows, p.cols, kStreamVectorsLarge) && workspace_bytes >= stream_workspace_bytes(p.rows, p.cols))
+        stream_eligible(p.rows, p.cols, kStreamVectors) && workspace_bytes >= stream_workspace_bytes(p.rows, p.cols))
       return launch_stream<kMode>(stream, p, workspace, tuning);
     if (tuning != nullptr) return HYLE_B200_INVALID_VALUE;  // tuning is for the streaming kernel only
   }
@@ -1323,11 +1312,9 @@ extern "C" int hyle_b200_softmax_f32(hyle_b200_stream_t stream, int kind, const 
 extern "C" int hyle_b200_logits_stream_plan(uint64_t rows, uint64_t cols, const hyle_b200_stream_tuning *tuning,
                                             hyle_b200_stream_plan *plan_out) {
   if (plan_out == nullptr) return HYLE_B200_INVALID_VALUE;
-  const int small = stream_resident_ctas(logits_stream_kernel<kProbsBf16, kStreamVectorsSmall, 0>,
-                                         stream_stage_bytes(kStreamVectorsSmall), kProbsBf16 * 2);
-  const int large = stream_resident_ctas(logits_stream_kernel<kProbsBf16, kStreamVectorsLarge, 0>,
-                                         stream_stage_bytes(kStreamVectorsLarge), kProbsBf16 * 2 + 1);
-  const StreamPlan plan = make_stream_plan(rows, cols, tuning, sm_count(), small, large);
+  const int resident = stream_resident_ctas(logits_stream_kernel<kProbsBf16, kStreamVectors, 0>, stream_stage_bytes(kStreamVectors),
+                                            kProbsBf16);
+  const StreamPlan plan = make_stream_plan(rows, cols, tuning, sm_count(), resident);
   *plan_out = hyle_b200_stream_plan{plan.vectors, plan.chunks, plan.chunk, plan.window, plan.fixed, plan.ctas_per_sm,
                                     plan.grid, plan.help_after};
   return plan.vectors == 0 ? HYLE_B200_NOT_SUPPORTED : HYLE_B200_OK;

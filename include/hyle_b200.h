@@ -265,7 +265,7 @@ HYLE_B200_API int hyle_b200_logits_reduce_f32(hyle_b200_stream_t stream, const f
  * measured best for the shape.  For tuning sweeps and for tests that force the rare paths (a window
  * of one row with help_after_polls = 1 makes second-pass tasks reduce their own partials). */
 typedef struct hyle_b200_stream_tuning {
-  int32_t chunk_vectors;      /* float4 per thread and task: 5 (5120-value chunks) or 10 (10240) */
+  int32_t chunk_vectors;      /* float4 per thread and task: 10 (10240-value chunks), the one size built */
   uint32_t window_rows;       /* rows between a row's first and second pass */
   uint32_t help_after_polls;  /* polls before a waiting warp reduces a missing chunk itself */
   int32_t ctas_per_sm;        /* at most what the kernel was built for (4) and what fits */

@@ -352,8 +352,7 @@ def test_logits_streaming_kernel_shapes_and_invalid_rows(oracle, cols):
     check_logits(oracle, x[:64], workspace=scratch)
 
 
-@pytest.mark.parametrize("vectors", [5, 10])
-def test_logits_streaming_kernel_reduces_missing_partials_itself(oracle, vectors):
+def test_logits_streaming_kernel_reduces_missing_partials_itself(oracle, vectors=10):
     """The rare path, forced: with a window of one row a second-pass task is claimed right behind the
     first-pass tasks it depends on, and with one poll of patience its warps reduce the missing chunks
     themselves from global memory instead of waiting for another CTA.  Results and status must be those
@@ -392,7 +391,7 @@ def test_logits_stream_plan_of_the_benchmarked_shapes():
     for rows in (64, 256, 1024, 4096):
         plan = ops.logits_stream_plan(rows, wl.VOCAB)
         assert plan is not None
-        assert plan.chunk_vectors == (5 if rows <= 512 else 10)
+        assert plan.chunk_vectors == 10
         assert plan.chunks_per_row * plan.chunk_values >= wl.VOCAB > (plan.chunks_per_row - 1) * plan.chunk_values
         assert plan.chunk_values % 16 == 0 and plan.chunks_per_row <= 32
         assert 8 <= plan.window_rows <= min(rows, 64)
