@@ -2,10 +2,15 @@
 """Benchmark of the B200 provider's hot path.
 
 Headline workload (the only one that shards): the Q8_0 sweep point R x 8192 bf16 -> Q8_0 blocks +
-decoded bf16 + sum of squares, row-sharded over the ranks, per-rank sums combined by one NCCL
-all-reduce.  A step is one pass over the whole tensor.  `value` is Gelem/s with the input resident
-in HBM; `e2e` is the same pass from pinned HOST buffers through the C ABI (host->device and
-device->host copies inside the timed region); `ops` lists the other operators' largest shapes.
+decoded bf16 + sum of squares, row-sharded over the ranks, per-rank sums combined by one exchange of
+8 bytes per rank.  A step is one pass over the whole tensor.  `value` is Gelem/s with the input
+resident in HBM; `e2e` is the same pass from pinned HOST buffers through the C ABI (host->device and
+device->host copies inside the timed region) beside the pinned-copy bandwidth measured in the same
+run; `sweep` holds every point R = 1024 ... 262144; `ops` lists the other operators; `workloads`
+(printed last) is the compact record of the five benchmark workloads: largest shape against the HBM
+roofline, the small shapes in microseconds, and the reference CPU code timed on the host cores.
+Before anything is timed the round trip's output is compared with the CPU checker on three 1024-row
+chunks of the very tensor that is timed (`parity`).
 
     python bench.py [--gpus N] [--steps K] [--warmup W]            # this library
     python bench.py --impl reference [...]                          # the CPU provider restated, host cores
@@ -14,6 +19,7 @@ device->host copies inside the timed region); `ops` lists the other operators' l
 from __future__ import annotations
 
 import argparse
+import ctypes
 import json
 import os
 import statistics
@@ -29,12 +35,23 @@ import numpy as np  # noqa: E402
 SWEEP_COLS = 8192
 DEFAULT_ROWS = 262144                       # 4 GiB of bf16: the largest sweep point
 BYTES_PER_ELEMENT = 2 + 34 / 32 + 2         # read bf16, write Q8_0 block share, write decoded bf16
-# dram__bytes_read.sum + dram__bytes_write.sum per element of the roundtrip kernel, from the ncu
-# capture summarised in profiles/ (the rest of the 3.06 B/value of output is written back from L2 after the kernel).
-NCU_TRAFFIC_BYTES_PER_ELEMENT = 4.66  # profiles/q8_0_roundtrip_R16384.md: 2.00 read + 2.66 written by kernel end
+# dram__bytes_read.sum + dram__bytes_write.sum per element of the round-trip kernel in an ncu capture of a
+# 16384-row launch: 2.00 read + 2.66 written by the end of the kernel (the rest of the 3.06 B/value of
+# output is still in L2 then and is written back afterwards).  Traffic grows in proportion to the tensor.
+NCU_TRAFFIC_BYTES_PER_ELEMENT = 4.66
 FALLBACK_HBM_GBS = 6650.0
 METRIC = "Q8_0 quantise+dequantise+sum-of-squares sweep throughput"
 UNIT = "Gelem/s"
+DTYPE = "bf16->q8_0(int8+f16)"
+PARITY_CHUNK_ROWS = 1024
+
+
+def job_config(rows: int, world: int) -> dict:
+    """What is measured, in the same words for this library and for the reference arm."""
+    return {"workload": f"Q8_0 sweep R={rows} x {SWEEP_COLS} bf16 -> Q8_0 + decoded bf16 + sum of squares",
+            "rows": rows, "cols": SWEEP_COLS, "parallelism": f"row-sharded x{world}, one exchange of 8 bytes per rank",
+            "l2": "inputs larger than L2 (no flush needed)" if rows * SWEEP_COLS * 2 // world > 4 * 126e6
+            else "input fits L2: launches rotate over distinct buffers"}
 
 
 def hbm_peak():
@@ -170,10 +187,11 @@ def run_reference(args):
     line = {
         "impl": "reference", "metric": METRIC, "value": value, "unit": UNIT, "n_gpus": args.gpus,
         "steps": args.steps, "warmup": args.warmup, "ms_per_step": seconds * 1e3, "higher_is_better": True,
-        "scaling": "strong", "vs_baseline": None, "dtype": "bf16->q8_0(int8+f16)", "data": "synthetic",
-        "config": {"workload": f"Q8_0 sweep R={args.rows} x {SWEEP_COLS} bf16 (CPU sample: {sample})",
-                   "l2": "working set larger than the host caches"},
-        "cpu_baseline": {"value": value, "unit": UNIT, "cores": cores, "kind": "port", "sample": sample},
+        "scaling": "strong", "vs_baseline": None, "dtype": DTYPE, "data": "synthetic",
+        "config": job_config(args.rows, args.gpus),
+        "cpu_baseline": {"value": value, "unit": UNIT, "cores": cores, "kind": "port", "sample": sample,
+                         "what": "the CPU provider's Q8_0 path restated in C (the reference delegates it to ggml, "
+                                 "which is not part of its tree), OpenMP over blocks on all host cores"},
         "e2e": {"value": value, "unit": UNIT, "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
         "gpu_launches": 0,
     }
@@ -393,6 +411,17 @@ def other_ops(torch, peak_gbs, only=None, iterations=40):
             stream, arenas[i].data_ptr(), fresh[i].data_ptr(), episode.data_ptr(), page_rows, pages, new_count,
             new_count // page_rows, row_bytes), sets, iterations)
         report("paged_append", "4096 rows x 8704 B into 16-row pages", new_count, 2 * new_count * row_bytes, ms, sets)
+        # The same episode through the REFERENCE's own CUDA kernel (compiled in place into oracle/_ref, used
+        # by the tests as the checker): reported beside the product's number, never part of a product timing.
+        from oracle.binding import RefPaged
+
+        if RefPaged.available():
+            reference = RefPaged()
+            ms = time_op(torch, lambda i: reference.paged_append(
+                stream, arenas[i].data_ptr(), fresh[i].data_ptr(), episode.data_ptr(), page_rows, pages, new_count,
+                new_count // page_rows, row_bytes), sets, iterations)
+            report("paged_append_REFERENCE_KERNEL", "the reference's cuda_paged_append.cu on the same episode (not this library)",
+                   new_count, 2 * new_count * row_bytes, ms, sets)
         # the same rows through the device-lengths variant: 32 requests of 128 new rows after 24 old ones
         requests, per_request, history = 32, new_count // 32, 24
         words = np.zeros(4 + 8 * (1 + requests + 320), dtype=np.uint32)
@@ -443,33 +472,34 @@ def other_ops(torch, peak_gbs, only=None, iterations=40):
     return results
 
 
-def sweep(torch, dist, ops, abi, wl, world: int, rank: int, peak_gbs: float, reducer, peers, iterations: int = 20):
+def sweep(torch, dist, abi, wl, world: int, rank: int, peak_gbs: float, reducer, peers, resident, iterations: int = 20):
     """The whole sweep R = 1024 ... 262144 (16 MiB ... 4 GiB of bf16), row-sharded over the ranks:
-    per point the step time (kernel + all-reduce, max over ranks), Gelem/s and GB/s per GPU."""
+    per point the step time (kernel + exchange, max over ranks), Gelem/s and GB/s per GPU.
+
+    The points run on row ranges of the tensors that are already resident (`resident` = input,
+    blocks, decoded, workspace, partial of the headline point); a small point rotates over distinct
+    ranges, so that no launch finds its input in L2."""
+    w, blocks, decoded, workspace, partial = resident
     points = []
     lib = abi.load()
     stream = torch.cuda.current_stream().cuda_stream
-    workspace = ops.make_workspace("cuda", (wl.SWEEP_ROWS[-1] + world - 1) // world * SWEEP_COLS)
-    partial = torch.zeros(1, dtype=torch.float64, device="cuda")
+    block_row_bytes = SWEEP_COLS // 32 * 34
     for total_rows in wl.SWEEP_ROWS:
-        shard = wl.shard_rows(total_rows, world, rank)
-        # small points rotate over several buffers so that no launch finds its input in L2
-        sets = max(1, min(8, int(600e6 // max(1, shard.rows * SWEEP_COLS * 2))))
-        w = [wl.q8_sweep_device_shard(shard) for _ in range(sets)]
-        count = w[0].numel()
-        blocks = [torch.empty(ops.q8_0_bytes(count), dtype=torch.uint8, device="cuda") for _ in range(sets)]
-        decoded = [torch.empty_like(w[0]) for _ in range(sets)]
+        rows = wl.shard_rows(total_rows, world, rank).rows
+        if rows == 0 or rows > w.shape[0]:
+            continue
+        sets = max(1, min(8, w.shape[0] // rows, int(600e6 // max(1, rows * SWEEP_COLS * 2))))
+        count = rows * SWEEP_COLS
 
         def one(i):
+            first = (i % sets) * rows
+            arguments = (stream, w[first:].data_ptr(), count, blocks[first * block_row_bytes:].data_ptr(),
+                         decoded[first:].data_ptr(), partial.data_ptr(), None, workspace.data_ptr(), workspace.numel())
             if peers is not None:
                 abi.check("roundtrip_exchange", lib.hyle_b200_q8_0_roundtrip_bf16_exchange(
-                    stream, w[i % sets].data_ptr(), count, blocks[i % sets].data_ptr(), decoded[i % sets].data_ptr(),
-                    partial.data_ptr(), None, workspace.data_ptr(), workspace.numel(), peers.pointers, world, rank,
-                    peers.next_epoch(), 0))
+                    *arguments, peers.pointers, world, rank, peers.next_epoch(), 0))
                 return
-            abi.check("roundtrip", lib.hyle_b200_q8_0_roundtrip_bf16(
-                stream, w[i % sets].data_ptr(), count, blocks[i % sets].data_ptr(), decoded[i % sets].data_ptr(),
-                partial.data_ptr(), None, workspace.data_ptr(), workspace.numel()))
+            abi.check("roundtrip", lib.hyle_b200_q8_0_roundtrip_bf16(*arguments))
             if reducer is not None:
                 reducer.sum_f64(partial, stream)
 
@@ -490,12 +520,212 @@ def sweep(torch, dist, ops, abi, wl, world: int, rank: int, peak_gbs: float, red
         seconds = float(ms.item()) * 1e-3
         elements = total_rows * SWEEP_COLS
         gbs_per_gpu = BYTES_PER_ELEMENT * count / seconds / 1e9
-        points.append({"rows": total_rows, "MiB_in": elements * 2 // 2**20, "us_per_step": seconds * 1e6,
-                       "Gelem/s": elements / seconds / 1e9, "GB/s_per_gpu": gbs_per_gpu,
-                       "roofline_frac": gbs_per_gpu / peak_gbs, "buffer_sets": sets})
-        del w, blocks, decoded
-        torch.cuda.empty_cache()
+        points.append({"rows": total_rows, "MiB_in": elements * 2 // 2**20, "us_per_step": round(seconds * 1e6, 2),
+                       "Gelem/s": round(elements / seconds / 1e9, 2), "GB/s_per_gpu": round(gbs_per_gpu, 1),
+                       "roofline_frac": round(gbs_per_gpu / peak_gbs, 4), "buffer_sets": sets})
     return points
+
+
+def parity_check(torch, ops, w, blocks, decoded, first_row: int):
+    """The round trip's output on the tensor that is about to be timed against the CPU checker: the
+    first 1024 rows, the 1024 rows around the middle (at the full size they straddle the 2 GiB byte
+    offset of both bf16 tensors) and the last 1024 rows; bytes of blocks and decoded values must be equal."""
+    from oracle.binding import Oracle
+
+    oracle = Oracle()
+    rows = w.shape[0]
+    chunk = min(PARITY_CHUNK_ROWS, rows)
+    starts = sorted({0, max(0, rows // 2 - chunk // 2), rows - chunk})
+    block_row_bytes = SWEEP_COLS // 32 * 34
+    for first in starts:
+        words = w[first:first + chunk].view(torch.int16).cpu().numpy().view(np.uint16).copy()
+        want_blocks, want_decoded, _, invalid = oracle.q8_0_roundtrip(words)
+        got_blocks = blocks[first * block_row_bytes:(first + chunk) * block_row_bytes].cpu().numpy()
+        got_decoded = decoded[first:first + chunk].view(torch.int16).cpu().numpy().view(np.uint16).ravel()
+        if invalid or not np.array_equal(got_blocks, want_blocks) or not np.array_equal(got_decoded, want_decoded):
+            return f"MISMATCH in rows {first_row + first}..{first_row + first + chunk}"
+    return "checked"
+
+
+def numa_affinity(local_rank: int):
+    """Pin the calling thread to the CPUs next to this rank's GPU (NVML's ideal affinity), so that the pinned
+    staging buffers allocated afterwards are on that NUMA node.  A host-side setting of this process only.
+    Returns (previous affinity, description) or (None, reason)."""
+    try:
+        import pynvml
+
+        pynvml.nvmlInit()
+        index = local_rank
+        visible = os.environ.get("CUDA_VISIBLE_DEVICES")
+        if visible:
+            entries = [e.strip() for e in visible.split(",") if e.strip()]
+            if local_rank < len(entries) and entries[local_rank].isdigit():
+                index = int(entries[local_rank])
+        handle = pynvml.nvmlDeviceGetHandleByIndex(index)
+        previous = os.sched_getaffinity(0)
+        words = pynvml.nvmlDeviceGetCpuAffinity(handle, (os.cpu_count() + 63) // 64)
+        cpus = {64 * w + b for w, word in enumerate(words) for b in range(64) if word >> b & 1} & previous
+        if not cpus:
+            return None, "NVML reports no CPU near the GPU inside this process's CPU set"
+        os.sched_setaffinity(0, cpus)
+        return previous, f"{len(cpus)} CPUs near the GPU"
+    except Exception as problem:  # no NVML, no permission: run unpinned and say so
+        return None, f"not pinned ({type(problem).__name__})"
+
+
+def pinned_copy_bandwidth(torch, chunk_bytes: int = 64 << 20, chunks: int = 8):
+    """GB/s of pinned-memory copies, one cudaMemcpyAsync per 64 MiB chunk: host->device alone,
+    device->host alone, and both directions at once on two streams (what the end-to-end pass does)."""
+    host_a = torch.empty(chunk_bytes * chunks, dtype=torch.uint8, pin_memory=True)
+    host_b = torch.empty(chunk_bytes * chunks, dtype=torch.uint8, pin_memory=True)
+    host_a.zero_(), host_b.zero_()
+    dev_a = torch.empty(chunk_bytes * chunks, dtype=torch.uint8, device="cuda")
+    dev_b = torch.empty(chunk_bytes * chunks, dtype=torch.uint8, device="cuda")
+    up, down = torch.cuda.Stream(), torch.cuda.Stream()
+
+    def run(h2d: bool, d2h: bool):
+        torch.cuda.synchronize()
+        t0 = time.perf_counter()
+        for c in range(chunks):
+            piece = slice(c * chunk_bytes, (c + 1) * chunk_bytes)
+            if h2d:
+                with torch.cuda.stream(up):
+                    dev_a[piece].copy_(host_a[piece], non_blocking=True)
+            if d2h:
+                with torch.cuda.stream(down):
+                    host_b[piece].copy_(dev_b[piece], non_blocking=True)
+        torch.cuda.synchronize()
+        return (int(h2d) + int(d2h)) * chunk_bytes * chunks / (time.perf_counter() - t0) / 1e9
+
+    run(True, True)
+    return {"h2d_GB/s": round(run(True, False), 2), "d2h_GB/s": round(run(False, True), 2),
+            "both_GB/s": round(run(True, True), 2), "how": "pinned host memory, one cudaMemcpyAsync per 64 MiB chunk, 512 MiB per direction"}
+
+
+def time_host(call, repeats: int = 2) -> float:
+    """Seconds of one host-side call: one warm-up, then the mean of `repeats`."""
+    call()
+    t0 = time.perf_counter()
+    for _ in range(repeats):
+        call()
+    return (time.perf_counter() - t0) / repeats
+
+
+def cpu_baselines():
+    """The reference's CPU code for workloads 1-4, timed on the host cores: all cores and one thread.
+
+    Workloads 2-4 run the reference's own Highway-free scalar floor compiled in place from its tree
+    (oracle/_ref/libhyle_ref_floor.so: rms_norm_bf16, swiglu_bf16, softmax_f32, top_k_f32), with the
+    residual add and the f32 -> bf16 cast of the fused forms from the C restatement; workload 1 and
+    the floor's absence fall back to the restatement alone (kind "port").  Rows are split over
+    threads like the reference's parallel_for_ranges.  Returns {workload: record}."""
+    from hyle_b200 import workloads as wl
+    from oracle import binding as ob
+
+    oracle = ob.Oracle()
+    floor = ob.RefFloor() if ob.RefFloor.available() else None
+    cores = os.cpu_count() or 1
+    ptr = lambda a: a.ctypes.data_as(ctypes.c_void_p)
+    records = {}
+
+    def measure(name, kind, full_rows, single_rows, elements_per_row, run):
+        record = {"kind": kind, "unit": "Gelem/s", "cores": cores}
+        for label, threads, rows in (("all_cores", cores, full_rows), ("one_thread", 1, single_rows)):
+            oracle.set_threads(threads)
+            if floor is not None:
+                floor.set_threads(threads)
+            seconds = time_host(lambda: run(rows))
+            record[label] = {"value": round(rows * elements_per_row / seconds / 1e9, 4), "threads": threads,
+                             "sample": f"{rows} of {full_rows} rows", "ms": round(seconds * 1e3, 2)}
+        oracle.set_threads(cores)
+        if floor is not None:
+            floor.set_threads(cores)
+        records[name] = record
+
+    # 1: C = A + bias, row sums and row maxima of C (three operators on the CPU route)
+    a, bias = wl.broadcast_add_inputs(4096, 4096)
+    c, row_sum, row_max = np.empty_like(a), np.empty(4096, np.float32), np.empty(4096, np.float32)
+
+    def add_reduce(rows):
+        oracle.lib.hyle_oracle_binary(ob.ADD, ob.F32, ptr(a), ptr(bias), ptr(c), rows * 4096, 4096)
+        oracle.lib.hyle_oracle_reduce_rows_f32(ob.SUM, ptr(c), ptr(row_sum), rows, 4096)
+        oracle.lib.hyle_oracle_reduce_rows_f32(ob.MAXIMUM, ptr(c), ptr(row_max), rows, 4096)
+    measure("add_bias_row_sum_max_f32", "port", 4096, 512, 4096, add_reduce)
+
+    # 2: h = x + residual, y = RmsNorm(h) * w
+    x, residual, weight, _ = wl.rms_norm_inputs(4096)
+    h, y, y32 = np.empty_like(x), np.empty_like(x), np.empty(x.shape, np.float32)
+
+    def add_norm(rows):
+        oracle.lib.hyle_oracle_binary(ob.ADD, ob.BF16, ptr(x), ptr(residual), ptr(h), rows * 2048, rows * 2048)
+        if floor is not None:
+            floor.lib.hyle_ref_rms_norm_bf16(ptr(h), ptr(weight), ptr(y), rows, 2048, 1e-6)
+        else:
+            oracle.lib.hyle_oracle_rms_norm_bf16(ptr(h), ptr(weight), ob.BF16, ptr(y), ptr(y32), rows, 2048, 1e-6)
+    measure("add_rms_norm_bf16", "reference-floor" if floor else "port", 4096, 512, 2048, add_norm)
+    del y32
+
+    # 3: out = silu(gate) * up
+    gate, up = wl.swiglu_inputs(4096)
+    out, out32 = np.empty_like(gate), None
+
+    def gated(rows):
+        if floor is not None:
+            floor.lib.hyle_ref_swiglu_bf16(ptr(gate), ptr(up), ptr(out), rows, 6144, 6144, 6144)
+        else:
+            nonlocal out32
+            out32 = np.empty(gate.shape, np.float32) if out32 is None else out32
+            oracle.lib.hyle_oracle_swiglu_bf16(ptr(gate), ptr(up), ptr(out), ptr(out32), rows, 6144, 6144, 6144)
+    measure("swiglu_bf16", "reference-floor" if floor else "port", 4096, 256, 6144, gated)
+
+    # 4: softmax (f32) -> bf16, log-sum-exp (the log-softmax shift) and argmax of 151936-wide rows
+    logits, _ = wl.logits_inputs(256)
+    probs32, probs16 = np.empty_like(logits), np.empty(logits.shape, np.uint16)
+    index, value = np.empty(256, np.int32), np.empty(256, np.float32)
+
+    def reduce_logits(rows):
+        if floor is not None:
+            floor.lib.hyle_ref_softmax_f32(0, ptr(logits), ptr(probs32), rows, wl.VOCAB)
+            floor.lib.hyle_ref_argmax_f32(ptr(logits), ptr(index), ptr(value), rows, wl.VOCAB)
+        else:
+            oracle.lib.hyle_oracle_softmax_f32(0, ptr(logits), ptr(probs32), rows, wl.VOCAB)
+            oracle.lib.hyle_oracle_argmax_f32(ptr(logits), ptr(index), ptr(value), rows, wl.VOCAB)
+        oracle.lib.hyle_oracle_cast_f32_to_bf16(ptr(probs32), ptr(probs16), rows * wl.VOCAB)
+    measure("logits_reduce_f32", "reference-floor" if floor else "port", 256, 16, wl.VOCAB, reduce_logits)
+    return records
+
+
+def small_shapes(torch, iterations: int = 200):
+    """The decode-sized shapes of workloads 2-4 in microseconds per launch (launch-bound: no roofline
+    fraction is meaningful at 4 KiB ... 10 MB), back to back on one stream with their inputs in L2."""
+    from hyle_b200 import abi
+
+    lib, stream, dev = abi.load(), torch.cuda.current_stream().cuda_stream, "cuda"
+    shapes = {}
+    weight = (torch.rand(2048, device=dev) + 0.5).bfloat16()
+    for tokens in (1, 64):
+        x, r = torch.randn(tokens, 2048, device=dev).bfloat16(), torch.randn(tokens, 2048, device=dev).bfloat16()
+        y, h = torch.empty_like(x), torch.empty_like(x)
+        ms = time_op(torch, lambda i: lib.hyle_b200_add_rms_norm_bf16(
+            stream, x.data_ptr(), r.data_ptr(), weight.data_ptr(), abi.BF16, y.data_ptr(), h.data_ptr(), tokens, 2048, 1e-6),
+            1, iterations)
+        shapes[f"add_rms_norm_bf16 T={tokens}"] = round(ms * 1e3, 2)
+    for tokens in (1, 8, 32):
+        g, u = torch.randn(tokens, 6144, device=dev).bfloat16(), torch.randn(tokens, 6144, device=dev).bfloat16()
+        o = torch.empty_like(g)
+        ms = time_op(torch, lambda i: lib.hyle_b200_swiglu_bf16(
+            stream, g.data_ptr(), u.data_ptr(), o.data_ptr(), tokens, 6144, 6144, 6144), 1, iterations)
+        shapes[f"swiglu_bf16 T={tokens}"] = round(ms * 1e3, 2)
+    for batch in (1, 16):
+        logits = 4.0 * torch.randn(batch, 151936, device=dev)
+        probs = torch.empty(batch, 151936, dtype=torch.bfloat16, device=dev)
+        lse, val = torch.empty(batch, device=dev), torch.empty(batch, device=dev)
+        idx = torch.empty(batch, dtype=torch.int32, device=dev)
+        ms = time_op(torch, lambda i: lib.hyle_b200_logits_reduce_f32(
+            stream, logits.data_ptr(), batch, 151936, lse.data_ptr(), probs.data_ptr(), idx.data_ptr(), val.data_ptr(),
+            None, 0, None), 1, iterations)
+        shapes[f"logits_reduce_f32 B={batch}"] = round(ms * 1e3, 2)
+    return shapes
 
 
 def run_e2e(torch, ops, abi, shard_rows: int, steps: int, warmup: int):
@@ -628,6 +858,21 @@ def run_gpu(args):
         if reducer is not None:
             reducer.sum_f64(partial, stream)
 
+    # Parity first: one launch, three 1024-row chunks of its output against the CPU checker.
+    parity = "skipped"
+    if not args.skip_parity:
+        step()
+        combine()
+        torch.cuda.synchronize()
+        parity = parity_check(torch, ops, w, blocks, decoded, shard.first_row)
+        if world > 1:
+            verdicts = [None] * world
+            dist.all_gather_object(verdicts, parity)
+            bad = [v for v in verdicts if v != "checked"]
+            parity = bad[0] if bad else "checked"
+        if parity != "checked":
+            raise SystemExit(f"parity check failed before timing: {parity}")
+
     for _ in range(args.warmup):
         step()
         combine()
@@ -661,6 +906,32 @@ def run_gpu(args):
     if int(status.item()) != 0:
         raise SystemExit("the Q8_0 kernel flagged invalid input on synthetic data")
 
+    # Where a multi-GPU step goes: every rank times the bare kernel on its shard (no exchange), and the
+    # step as it ran above.  step - slowest bare kernel = waiting for the slowest rank + the exchange.
+    rank_split = None
+    if world > 1:
+        pairs = [(torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)) for _ in range(10)]
+        for _ in range(3):
+            lib.hyle_b200_q8_0_roundtrip_bf16(stream, w.data_ptr(), count, blocks.data_ptr(), decoded.data_ptr(),
+                                              partial.data_ptr(), None, workspace.data_ptr(), workspace.numel())
+        torch.cuda.synchronize()
+        for a, b in pairs:
+            a.record()
+            lib.hyle_b200_q8_0_roundtrip_bf16(stream, w.data_ptr(), count, blocks.data_ptr(), decoded.data_ptr(),
+                                              partial.data_ptr(), None, workspace.data_ptr(), workspace.numel())
+            b.record()
+        torch.cuda.synchronize()
+        mine = {"rank": rank, "kernel_alone_us": round(statistics.mean(event_pairs_ms(pairs)) * 1e3, 2),
+                "step_us": round(statistics.mean(event_pairs_ms(kernel_events)) * 1e3, 2)}
+        gathered = [None] * world
+        dist.all_gather_object(gathered, mine)
+        slowest = max(g["kernel_alone_us"] for g in gathered)
+        rank_split = {"per_rank": gathered, "slowest_kernel_alone_us": slowest,
+                      "step_us_max": max(g["step_us"] for g in gathered),
+                      "wait_and_exchange_us": round(max(g["step_us"] for g in gathered) - slowest, 2),
+                      "note": "kernel_alone = the round trip without the exchange, timed per rank by CUDA events; "
+                              "step = the fused launch including the wait for the slowest rank's sum"}
+
     # end-to-end from host buffers (every rank moves its own shard).  The pinned staging is
     # 6.06 bytes per element; if that is more than a quarter of the free host memory per rank,
     # time a leading part of the shard instead and say so.
@@ -673,21 +944,36 @@ def run_gpu(args):
             e2e_rows //= 2
     except ImportError:
         pass
+    copy_peak, pinned_to = None, None
     if args.skip_e2e:
         e2e_seconds, h2d, d2h = float("nan"), 0, 0
     else:
-        e2e_seconds, h2d, d2h, _ = run_e2e(torch, ops, abi, e2e_rows, e2e_steps, 1)
+        previous_affinity, pinned_to = numa_affinity(local_rank)  # pinned staging next to the GPU
+        try:
+            if world > 1:
+                dist.barrier()  # all ranks copy at once: the bandwidth a rank sees is its share of the host's
+            copy_peak = pinned_copy_bandwidth(torch)
+            if world > 1:
+                dist.barrier()
+            e2e_seconds, h2d, d2h, _ = run_e2e(torch, ops, abi, e2e_rows, e2e_steps, 1)
+        finally:
+            if previous_affinity is not None:
+                os.sched_setaffinity(0, previous_affinity)
     e2e_seconds *= shard.rows / e2e_rows
     h2d, d2h = h2d * shard.rows // e2e_rows, d2h * shard.rows // e2e_rows
     e2e_t = torch.tensor([e2e_seconds], dtype=torch.float64, device="cuda")
     if world > 1:
         dist.all_reduce(e2e_t, op=dist.ReduceOp.MAX)
 
+    copy_peaks = None
+    if copy_peak is not None and world > 1:
+        copy_peaks = [None] * world
+        dist.all_gather_object(copy_peaks, copy_peak)
+
     sweep_points = None
-    if args.sweep:
-        del w, blocks, decoded
-        torch.cuda.empty_cache()
-        sweep_points = sweep(torch, dist, ops, abi, wl, world, rank, peak_gbs, reducer, peers)
+    if not args.skip_sweep:
+        sweep_points = sweep(torch, dist, abi, wl, world, rank, peak_gbs, reducer, peers,
+                             (w, blocks, decoded, workspace, partial))
 
     if peers is not None:
         peers.close()  # collective (it ends with a barrier), so before rank 0 goes on alone
@@ -714,27 +1000,40 @@ def run_gpu(args):
                 "launch_us": kernel_s * 1e6,
                 "traffic": None if NCU_TRAFFIC_BYTES_PER_ELEMENT is None else NCU_TRAFFIC_BYTES_PER_ELEMENT * count}
 
+    e2e_seconds_max = float(e2e_t.item())
+    e2e = {"value": total_elements / e2e_seconds_max / 1e9, "unit": UNIT,
+           "h2d_bytes_per_step": h2d * world, "d2h_bytes_per_step": d2h * world, "steps": e2e_steps,
+           "rows_timed_per_gpu": e2e_rows, "rows_per_gpu": shard.rows, "host_threads_pinned": pinned_to}
+    if copy_peak is not None:
+        # the end-to-end pass moves h2d + d2h bytes per GPU over its PCIe link while the kernels run beside
+        # the copies: its roofline is the pinned-copy bandwidth with both directions busy, measured just before
+        per_gpu = (h2d + d2h) / e2e_seconds_max / 1e9
+        peaks = copy_peaks if copy_peaks is not None else [copy_peak]
+        slowest_link = min(p["both_GB/s"] for p in peaks)
+        e2e["roofline"] = {"bound": "pcie (pinned host memory <-> device, both directions at once)",
+                           "achieved": round(per_gpu, 2), "peak": slowest_link, "unit": "GB/s per GPU",
+                           "frac": round(per_gpu / slowest_link, 3), "copy_bandwidth": copy_peak,
+                           "copy_bandwidth_all_ranks_at_once": None if copy_peaks is None else
+                           {"both_GB/s_per_rank": [p["both_GB/s"] for p in copy_peaks],
+                            "sum_GB/s": round(sum(p["both_GB/s"] for p in copy_peaks), 1)}}
+
     line = {
         "metric": METRIC, "value": value, "unit": UNIT, "n_gpus": world, "steps": args.steps,
         "warmup": args.warmup, "ms_per_step": ms_per_step, "higher_is_better": True, "scaling": "strong",
-        "vs_baseline": None, "dtype": "bf16->q8_0(int8+f16)", "data": "synthetic",
-        "config": {"workload": f"Q8_0 sweep R={args.rows} x {SWEEP_COLS} bf16 -> Q8_0 + decoded bf16 + sum of squares",
-                   "rows_per_gpu": shard.rows, "parallelism": f"row-sharded x{world}, one exchange of 8 bytes per rank", "exchange": exchange,
-                   "l2": "inputs larger than L2 (no flush needed)" if count * 2 > 4 * 126e6 else "input fits L2: cold-cache not guaranteed"},
+        "vs_baseline": None, "dtype": DTYPE, "data": "synthetic",
+        "config": job_config(args.rows, world),
+        "details": {"rows_per_gpu": shard.rows, "exchange": exchange},
+        "parity": parity,
         "roofline": roofline,
-        "e2e": {"value": total_elements / float(e2e_t.item()) / 1e9, "unit": UNIT,
-                "h2d_bytes_per_step": h2d * world, "d2h_bytes_per_step": d2h * world, "steps": e2e_steps,
-                "rows_timed_per_gpu": e2e_rows, "rows_per_gpu": shard.rows},
+        "e2e": e2e,
         "gpu_launches": args.steps,
         "clocks": clocks,
         "sum_squares": sum_squares,
     }
+    if rank_split is not None:
+        line["multi_gpu_step"] = rank_split
 
-    if args.sweep:
-        line["sweep"] = sweep_points
     if world == 1:
-        if not args.skip_ops:
-            line["ops"] = other_ops(torch, peak_gbs)
         if not args.skip_cpu:
             from oracle.binding import Oracle
 
@@ -743,8 +1042,38 @@ def run_gpu(args):
             oracle.set_threads(cores)
             rows = cpu_sample_rows(oracle, target_seconds=4.0, max_rows=args.rows)
             cpu_value, _ = time_cpu(oracle, rows, steps=3, warmup=1)
+            oracle.set_threads(1)
+            single_rows = max(256, rows // 16)
+            single_value, _ = time_cpu(oracle, single_rows, steps=2, warmup=1)
+            oracle.set_threads(cores)
             line["cpu_baseline"] = {"value": cpu_value, "unit": UNIT, "cores": cores, "kind": "port",
-                                    "sample": f"{rows} of {args.rows} rows x {SWEEP_COLS} per step, 3 timed steps"}
+                                    "sample": f"{rows} of {args.rows} rows x {SWEEP_COLS} per step, 3 timed steps",
+                                    "one_thread": {"value": single_value, "sample": f"{single_rows} rows x {SWEEP_COLS}"}}
+        if not args.skip_ops:
+            line["ops"] = other_ops(torch, peak_gbs)
+    if sweep_points is not None:
+        line["sweep"] = sweep_points
+    if world == 1 and not args.skip_ops:
+        # Printed last, so that a reader of the line's tail still has it: the five benchmark workloads.
+        by_name = {entry["op"]: entry for entry in line["ops"]}
+        baselines = {} if args.skip_cpu else cpu_baselines()
+        workloads = {}
+        for number, name in ((1, "add_bias_row_sum_max_f32"), (2, "add_rms_norm_bf16"), (3, "swiglu_bf16"),
+                             (4, "logits_reduce_f32")):
+            entry = by_name.get(name)
+            if entry is None:
+                continue
+            workloads[f"{number}:{name}"] = {
+                "shape": entry["shape"], "us": round(entry["us"], 2), "GB/s": round(entry["GB/s"], 1),
+                "Gelem/s": round(entry["Gelem/s"], 2), "frac_of_measured_hbm": round(entry["roofline_frac"], 4),
+                "frac_of_nominal_8TB/s": round(entry["GB/s"] / 8000.0, 4), "cpu_baseline": baselines.get(name)}
+        workloads["5:q8_0_roundtrip_bf16"] = {
+            "shape": f"{args.rows}x{SWEEP_COLS}", "us": round(kernel_s * 1e6, 1), "GB/s": round(achieved, 1),
+            "Gelem/s": round(value, 2), "frac_of_measured_hbm": round(achieved / peak_gbs, 4),
+            "frac_of_nominal_8TB/s": round(achieved / 8000.0, 4), "cpu_baseline": line.get("cpu_baseline")}
+        workloads["small_shapes_us_per_launch"] = small_shapes(torch)
+        workloads["host"] = {"nproc": os.cpu_count(), "peak_GB/s": peak_gbs, "peak_kind": peak_kind}
+        line["workloads"] = workloads
     print(json.dumps(line), flush=True)
     shut_down()
 
@@ -758,7 +1087,8 @@ def main():
     parser.add_argument("--rows", type=int, default=DEFAULT_ROWS, help="total rows of the sweep point")
     parser.add_argument("--skip-ops", action="store_true", help="do not time workloads 1-4")
     parser.add_argument("--skip-cpu", action="store_true", help="do not time the CPU baseline")
-    parser.add_argument("--sweep", action="store_true", help="also time every sweep point R = 1024 ... 262144")
+    parser.add_argument("--skip-sweep", action="store_true", help="do not time the other sweep points R = 1024 ... 131072")
+    parser.add_argument("--skip-parity", action="store_true", help="do not compare with the CPU checker before timing")
     parser.add_argument("--skip-e2e", action="store_true", help="do not time the host-buffer pass (profiling runs)")
     parser.add_argument("--exchange", default="fused", choices=["fused", "nccl"],
                         help="how the per-GPU sums of squares are combined when --gpus > 1")

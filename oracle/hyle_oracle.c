@@ -145,6 +145,14 @@ ORACLE_API void hyle_oracle_binary(int kind, int dtype, const void *lhs, const v
                                    uint64_t count, uint64_t rhs_period) {
   if (count == 0) return;
   const uint64_t chunks = count / rhs_period;
+  /* Threads split the rows of a broadcast, or the elements when the operands have one shape: either
+   * way contiguous ranges, as the reference's parallel_for_ranges hands them out. */
+  if (chunks == 1) {
+#pragma omp parallel for schedule(static)
+    for (uint64_t i = 0; i < count; ++i)
+      store_from_f32(out, i, dtype, binary_value(kind, load_as_f32(lhs, i, dtype), load_as_f32(rhs, i, dtype)));
+    return;
+  }
 #pragma omp parallel for schedule(static)
   for (uint64_t c = 0; c < chunks; ++c) {
     for (uint64_t j = 0; j < rhs_period; ++j) {
