@@ -16,6 +16,7 @@ F32, BF16, F16, E4M3, E5M2, BOOL, I32 = 0, 1, 2, 3, 4, 5, 6
 # enum hyle_b200_binary_kind
 BINARY_ADD, BINARY_MULTIPLY, BINARY_SUBTRACT, BINARY_DIVIDE, BINARY_MINIMUM, BINARY_MAXIMUM = 0, 1, 2, 3, 4, 5
 # enum hyle_b200_unary_kind
+GATE_SILU, GATE_GELU, GATE_GELU_TANH = 0, 1, 2  # hyle_b200_gate_kind
 (UNARY_ABS, UNARY_NEG, UNARY_EXP, UNARY_LOG, UNARY_SQRT, UNARY_RSQRT, UNARY_TANH, UNARY_SIGMOID, UNARY_RELU,
  UNARY_GELU, UNARY_GELU_TANH, UNARY_SILU, UNARY_SOFTPLUS) = range(13)
 # enum hyle_b200_reduce_kind
@@ -54,6 +55,7 @@ SIGNATURES = {
     "hyle_b200_add_rms_norm_bf16": (_i, [_p, _p, _p, _p, _i, _p, _p, _u64, _u64, _f]),
     "hyle_b200_layer_norm_bf16": (_i, [_p, _p, _p, _p, _p, _u64, _u64, _f]),
     "hyle_b200_swiglu_bf16": (_i, [_p, _p, _p, _p, _u64, _u64, _u64, _u64]),
+    "hyle_b200_gated_activation": (_i, [_p, _i, _i, _i, _p, _p, _p, _u64, _u64, _u64, _u64]),
     "hyle_b200_logits_workspace_bytes": (_u64, [_u64, _u64]),
     "hyle_b200_logits_reduce_f32": (_i, [_p, _p, _u64, _u64, _p, _p, _p, _p, _p, _u64, _p]),
     "hyle_b200_logits_reduce_f32_tuned": (_i, [_p, _p, _u64, _u64, _p, _p, _p, _p, _p, _u64, _p, _p]),

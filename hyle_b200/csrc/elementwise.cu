@@ -341,15 +341,36 @@ __device__ __forceinline__ float silu(float x) {
   return x == -INFINITY ? 0.0f : product;               // -inf * 0 would be NaN
 }
 
-__device__ __forceinline__ uint32_t swiglu_pair(uint32_t g, uint32_t u) {
-  return pack_bf16x2(__fmul_rn(silu(bf16_lo(g)), bf16_lo(u)), __fmul_rn(silu(bf16_hi(g)), bf16_hi(u)));
+// GatedActivation{activation}: out = storage(act(f32 gate) * f32 up), one rounding
+// (src/compute_provider_native/aten_cpu_provider.cc:414-445,654-665).  With kRoundGate the activated
+// gate is first rounded to the storage type, which makes the result that of Unary{activation}
+// followed by Binary{kMultiply} on 16-bit tensors (two roundings): the form a graph region takes when
+// it fuses those two nodes without changing what they compute.
+template <int kAct>
+__device__ __forceinline__ float gate_activation(float x) {
+  if constexpr (kAct == HYLE_B200_GATE_SILU) return silu(x);
+  if constexpr (kAct == HYLE_B200_GATE_GELU) return unary_op<HYLE_B200_UNARY_GELU, true>(x);
+  return unary_op<HYLE_B200_UNARY_GELU_TANH, true>(x);
 }
+template <int kAct, int kDtype, bool kRoundGate>
+__device__ __forceinline__ float gated_value(float g, float u) {
+  float a = gate_activation<kAct>(g);
+  if constexpr (kRoundGate) a = narrow_scalar<kDtype>(narrow_store<kDtype>(a));
+  return __fmul_rn(a, u);
+}
+template <int kAct, int kDtype, bool kRoundGate>
+__device__ __forceinline__ uint32_t swiglu_pair(uint32_t g, uint32_t u) {
+  return narrow_pack<kDtype>(gated_value<kAct, kDtype, kRoundGate>(narrow_lo<kDtype>(g), narrow_lo<kDtype>(u)),
+                             gated_value<kAct, kDtype, kRoundGate>(narrow_hi<kDtype>(g), narrow_hi<kDtype>(u)));
+}
+template <int kAct, int kDtype, bool kRoundGate>
 __device__ __forceinline__ uint4 swiglu_vec(uint4 g, uint4 u) {
-  return make_uint4(swiglu_pair(g.x, u.x), swiglu_pair(g.y, u.y), swiglu_pair(g.z, u.z),
-                    swiglu_pair(g.w, u.w));
+  return make_uint4(swiglu_pair<kAct, kDtype, kRoundGate>(g.x, u.x), swiglu_pair<kAct, kDtype, kRoundGate>(g.y, u.y),
+                    swiglu_pair<kAct, kDtype, kRoundGate>(g.z, u.z), swiglu_pair<kAct, kDtype, kRoundGate>(g.w, u.w));
 }
 
 // Dense separate gate/up: one flat stream.
+template <int kAct, int kDtype, bool kRoundGate>
 __global__ void __launch_bounds__(kThreads)
 swiglu_flat_kernel(const uint4 *__restrict__ gate, const uint4 *__restrict__ up,
                    uint4 *__restrict__ out, uint64_t vectors) {
@@ -364,12 +385,14 @@ swiglu_flat_kernel(const uint4 *__restrict__ gate, const uint4 *__restrict__ up,
       u[k] = ld_stream(up + i + k * stride);
     }
 #pragma unroll
-    for (int k = 0; k < kUnroll; ++k) st_stream(out + i + k * stride, swiglu_vec(g[k], u[k]));
+    for (int k = 0; k < kUnroll; ++k) st_stream(out + i + k * stride, swiglu_vec<kAct, kDtype, kRoundGate>(g[k], u[k]));
   }
-  for (; i < vectors; i += stride) st_stream(out + i, swiglu_vec(ld_stream(gate + i), ld_stream(up + i)));
+  for (; i < vectors; i += stride)
+    st_stream(out + i, swiglu_vec<kAct, kDtype, kRoundGate>(ld_stream(gate + i), ld_stream(up + i)));
 }
 
 // Row-strided operands (the packed-halves layout): grid = (column tiles, row groups).
+template <int kAct, int kDtype, bool kRoundGate>
 __global__ void __launch_bounds__(kThreads)
 swiglu_rows_kernel(const uint4 *__restrict__ gate, const uint4 *__restrict__ up,
                    uint4 *__restrict__ out, uint64_t rows, uint32_t row_vectors,
@@ -388,15 +411,16 @@ swiglu_rows_kernel(const uint4 *__restrict__ gate, const uint4 *__restrict__ up,
     }
 #pragma unroll
     for (int k = 0; k < kUnroll; ++k)
-      st_stream(out + (row + k * step) * row_vectors + column, swiglu_vec(g[k], u[k]));
+      st_stream(out + (row + k * step) * row_vectors + column, swiglu_vec<kAct, kDtype, kRoundGate>(g[k], u[k]));
   }
   for (; row < rows; row += step)
     st_stream(out + row * row_vectors + column,
-              swiglu_vec(ld_stream(gate + row * gate_stride_vectors + column),
-                         ld_stream(up + row * up_stride_vectors + column)));
+              swiglu_vec<kAct, kDtype, kRoundGate>(ld_stream(gate + row * gate_stride_vectors + column),
+                                                   ld_stream(up + row * up_stride_vectors + column)));
 }
 
 // Any width / alignment.
+template <int kAct, int kDtype, bool kRoundGate>
 __global__ void __launch_bounds__(kThreads)
 swiglu_scalar_kernel(const unsigned short *__restrict__ gate, const unsigned short *__restrict__ up,
                      unsigned short *__restrict__ out, uint64_t rows, uint64_t cols,
@@ -407,9 +431,9 @@ swiglu_scalar_kernel(const unsigned short *__restrict__ gate, const unsigned sho
   for (uint64_t i = static_cast<uint64_t>(blockIdx.x) * kThreads + threadIdx.x; i < count;
        i += stride) {
     const uint64_t row = i / cols, column = i - row * cols;
-    const float g = bf16_to_f32(gate[row * gate_stride + column]);
-    const float u = bf16_to_f32(up[row * up_stride + column]);
-    out[i] = f32_to_bf16(__fmul_rn(silu(g), u));
+    const float g = narrow_scalar<kDtype>(gate[row * gate_stride + column]);
+    const float u = narrow_scalar<kDtype>(up[row * up_stride + column]);
+    out[i] = narrow_store<kDtype>(gated_value<kAct, kDtype, kRoundGate>(g, u));
   }
 }
 
@@ -477,23 +501,19 @@ extern "C" int hyle_b200_binary(hyle_b200_stream_t stream, int kind, int dtype, 
   return HYLE_B200_INVALID_VALUE;
 }
 
-extern "C" int hyle_b200_swiglu_bf16(hyle_b200_stream_t stream, const void *gate, const void *up,
-                                     void *out, uint64_t rows, uint64_t cols,
-                                     uint64_t gate_row_stride, uint64_t up_row_stride) {
-  if (rows == 0 || cols == 0) return HYLE_B200_OK;
-  if (gate == nullptr || up == nullptr || out == nullptr || gate_row_stride < cols ||
-      up_row_stride < cols)
-    return HYLE_B200_INVALID_VALUE;
-  auto s = reinterpret_cast<cudaStream_t>(stream);
+namespace hb {
+namespace {
+template <int kAct, int kDtype, bool kRoundGate>
+int launch_gated(cudaStream_t s, const void *gate, const void *up, void *out, uint64_t rows, uint64_t cols,
+                 uint64_t gate_row_stride, uint64_t up_row_stride) {
   const uint64_t resident = static_cast<uint64_t>(sm_count()) * kCtasPerSm;
   const bool vector_ok = aligned_to(gate, 16) && aligned_to(up, 16) && aligned_to(out, 16) &&
                          cols % 8 == 0 && gate_row_stride % 8 == 0 && up_row_stride % 8 == 0;
   if (vector_ok && gate_row_stride == cols && up_row_stride == cols) {
     const uint64_t vectors = rows * cols / 8;
     const unsigned grid = clamp_grid((vectors + kThreads * kUnroll - 1) / (kThreads * kUnroll), resident);
-    return launch(swiglu_flat_kernel, dim3(grid), dim3(kThreads), 0, s, static_cast<const uint4 *>(gate),
-                                                 static_cast<const uint4 *>(up),
-                                                 static_cast<uint4 *>(out), vectors);
+    return launch(swiglu_flat_kernel<kAct, kDtype, kRoundGate>, dim3(grid), dim3(kThreads), 0, s,
+                  static_cast<const uint4 *>(gate), static_cast<const uint4 *>(up), static_cast<uint4 *>(out), vectors);
   }
   if (vector_ok && cols / 8 <= 0x7fffffffull) {
     const uint64_t row_vectors = cols / 8;
@@ -503,15 +523,57 @@ extern "C" int hyle_b200_swiglu_bf16(hyle_b200_stream_t stream, const void *gate
     if (groups > useful) groups = useful;
     if (groups > 65535) groups = 65535;
     if (groups < 1) groups = 1;
-    return launch(swiglu_rows_kernel, dim3(dim3(tiles, static_cast<unsigned>(groups))), dim3(kThreads), 0, s, 
-        static_cast<const uint4 *>(gate), static_cast<const uint4 *>(up), static_cast<uint4 *>(out),
-        rows, static_cast<uint32_t>(row_vectors), gate_row_stride / 8, up_row_stride / 8);
+    return launch(swiglu_rows_kernel<kAct, kDtype, kRoundGate>, dim3(dim3(tiles, static_cast<unsigned>(groups))), dim3(kThreads), 0, s,
+                  static_cast<const uint4 *>(gate), static_cast<const uint4 *>(up), static_cast<uint4 *>(out), rows,
+                  static_cast<uint32_t>(row_vectors), gate_row_stride / 8, up_row_stride / 8);
   }
   const unsigned grid = clamp_grid((rows * cols + kThreads - 1) / kThreads, resident);
-  return launch(swiglu_scalar_kernel, dim3(grid), dim3(kThreads), 0, s, static_cast<const unsigned short *>(gate),
-                                                 static_cast<const unsigned short *>(up),
-                                                 static_cast<unsigned short *>(out), rows, cols,
-                                                 gate_row_stride, up_row_stride);
+  return launch(swiglu_scalar_kernel<kAct, kDtype, kRoundGate>, dim3(grid), dim3(kThreads), 0, s,
+                static_cast<const unsigned short *>(gate), static_cast<const unsigned short *>(up),
+                static_cast<unsigned short *>(out), rows, cols, gate_row_stride, up_row_stride);
+}
+
+template <int kAct, int kDtype>
+int launch_gated_rounding(cudaStream_t s, int round_gate, const void *gate, const void *up, void *out, uint64_t rows,
+                          uint64_t cols, uint64_t gate_row_stride, uint64_t up_row_stride) {
+  return round_gate ? launch_gated<kAct, kDtype, true>(s, gate, up, out, rows, cols, gate_row_stride, up_row_stride)
+                    : launch_gated<kAct, kDtype, false>(s, gate, up, out, rows, cols, gate_row_stride, up_row_stride);
+}
+template <int kDtype>
+int launch_gated_kind(cudaStream_t s, int activation, int round_gate, const void *gate, const void *up, void *out,
+                      uint64_t rows, uint64_t cols, uint64_t gate_row_stride, uint64_t up_row_stride) {
+  switch (activation) {
+    case HYLE_B200_GATE_SILU:
+      return launch_gated_rounding<HYLE_B200_GATE_SILU, kDtype>(s, round_gate, gate, up, out, rows, cols, gate_row_stride, up_row_stride);
+    case HYLE_B200_GATE_GELU:
+      return launch_gated_rounding<HYLE_B200_GATE_GELU, kDtype>(s, round_gate, gate, up, out, rows, cols, gate_row_stride, up_row_stride);
+    case HYLE_B200_GATE_GELU_TANH:
+      return launch_gated_rounding<HYLE_B200_GATE_GELU_TANH, kDtype>(s, round_gate, gate, up, out, rows, cols, gate_row_stride, up_row_stride);
+    default: return HYLE_B200_INVALID_VALUE;
+  }
+}
+}  // namespace
+}  // namespace hb
+
+extern "C" int hyle_b200_gated_activation(hyle_b200_stream_t stream, int activation, int dtype, int round_gate,
+                                          const void *gate, const void *up, void *out, uint64_t rows, uint64_t cols,
+                                          uint64_t gate_row_stride, uint64_t up_row_stride) {
+  if (activation < HYLE_B200_GATE_SILU || activation > HYLE_B200_GATE_GELU_TANH) return HYLE_B200_INVALID_VALUE;
+  if (dtype != HYLE_B200_BF16 && dtype != HYLE_B200_F16) return HYLE_B200_NOT_SUPPORTED;
+  if (rows == 0 || cols == 0) return HYLE_B200_OK;
+  if (gate == nullptr || up == nullptr || out == nullptr || gate_row_stride < cols || up_row_stride < cols)
+    return HYLE_B200_INVALID_VALUE;
+  auto s = reinterpret_cast<cudaStream_t>(stream);
+  if (dtype == HYLE_B200_BF16)
+    return hb::launch_gated_kind<HYLE_B200_BF16>(s, activation, round_gate, gate, up, out, rows, cols, gate_row_stride, up_row_stride);
+  return hb::launch_gated_kind<HYLE_B200_F16>(s, activation, round_gate, gate, up, out, rows, cols, gate_row_stride, up_row_stride);
+}
+
+extern "C" int hyle_b200_swiglu_bf16(hyle_b200_stream_t stream, const void *gate, const void *up,
+                                     void *out, uint64_t rows, uint64_t cols,
+                                     uint64_t gate_row_stride, uint64_t up_row_stride) {
+  return hyle_b200_gated_activation(stream, HYLE_B200_GATE_SILU, HYLE_B200_BF16, 0, gate, up, out, rows, cols,
+                                    gate_row_stride, up_row_stride);
 }
 
 extern "C" int hyle_b200_unary(hyle_b200_stream_t stream, int kind, int dtype, const void *in, void *out,

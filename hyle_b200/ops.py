@@ -219,6 +219,22 @@ def swiglu(gate: torch.Tensor, up: torch.Tensor) -> torch.Tensor:
     return out
 
 
+def gated_activation(gate: torch.Tensor, up: torch.Tensor, activation: int = abi.GATE_SILU,
+                     round_gate: bool = False) -> torch.Tensor:
+    """GatedActivation{activation, kSeparate} on bf16 / f16 tensors of one shape; with ``round_gate`` the
+    result of Unary{activation} followed by Binary{kMultiply} (the activated gate rounded to storage first)."""
+    _device_tensor(gate, "gate"), _device_tensor(up, "up")
+    if gate.dtype not in (torch.bfloat16, torch.float16) or up.dtype != gate.dtype or gate.shape != up.shape:
+        raise ValueError("gate and up must be bf16 or f16 tensors of one shape")
+    cols = gate.shape[-1]
+    rows = gate.numel() // cols if cols else 0
+    out = _new_like(gate)
+    abi.check("hyle_b200_gated_activation", abi.load().hyle_b200_gated_activation(
+        _stream(), activation, _DTYPE[gate.dtype], int(round_gate), gate.data_ptr(), up.data_ptr(), out.data_ptr(),
+        rows, cols, cols, cols))
+    return out
+
+
 def swiglu_packed(packed: torch.Tensor) -> torch.Tensor:
     """GatedActivation{kSilu, kPackedHalves}: the last axis holds [gate | up]."""
     _device_tensor(packed, "packed")

@@ -4,6 +4,7 @@
 // The IDs name the complete schema including the numerical contract; a change gets a new ID.
 #pragma once
 
+#include <algorithm>
 #include <array>
 #include <cstdint>
 #include <span>
@@ -81,6 +82,53 @@ struct Q8_0Roundtrip final {
     HYLE_ASSIGN_OR_RETURN(outputs[0], TensorDesc::dense(DataType::kUInt8, carrier));
     outputs[1] = inputs[0];
     HYLE_ASSIGN_OR_RETURN(outputs[2], TensorDesc::dense(DataType::kFloat64, std::array<std::int64_t, 1>{1}));
+    return Status::Ok();
+  }
+};
+
+// (gate, up) -> out on bf16 / f16 tensors of one shape:  out = storage(storage(activation(gate)) * up), i.e.
+// Unary{activation} followed by Binary{kMultiply} with BOTH roundings kept, in one pass.  What a graph
+// region presents for that pair of nodes (engine/models/qwen35/block_graph.h:27-40 emits it for 16-bit
+// activations).  activation: kSilu, kGelu or kGeluTanh.
+struct ActivationMultiply final {
+  static constexpr OperationId operation_id{kNamespace, 5};
+  static constexpr std::string_view operation_name = "b200-activation-multiply";
+  UnaryKind activation = UnaryKind::kSilu;
+
+  OperationTraits operation_traits() const noexcept { return {.inputs = {2, 2}, .outputs = 1}; }
+  Status infer_output_descriptions(std::span<const TensorDesc> inputs, std::span<TensorDesc> outputs) const noexcept {
+    if (inputs.size() != 2 || outputs.size() != 1 || inputs[0] != inputs[1])
+      return Status::InvalidArgument("activation-multiply expects gate and up of one description");
+    outputs[0] = inputs[0];
+    return Status::Ok();
+  }
+};
+
+// logits f32[..., V] -> (probabilities bf16[..., V], [values f32[..., 1],] indices i32[..., 1]):
+// Softmax{axis=-1} then Cast{bf16}, and TopK{count=1} of the same logits, in one pass over them.
+// What a graph region presents for a greedy sampling head that also publishes its distribution
+// (engine/inference/sampling_graph.h:339-345 keeps only the index of TopK: `values` = false then).
+struct GreedyHead final {
+  static constexpr OperationId operation_id{kNamespace, 6};
+  static constexpr std::string_view operation_name = "b200-greedy-head";
+  bool values = true;
+
+  OperationTraits operation_traits() const noexcept { return {.inputs = {1, 1}, .outputs = values ? 3u : 2u}; }
+  Status infer_output_descriptions(std::span<const TensorDesc> inputs, std::span<TensorDesc> outputs) const noexcept {
+    if (inputs.size() != 1 || outputs.size() != (values ? 3u : 2u) || inputs[0].rank() == 0 ||
+        inputs[0].data_type() != DataType::kFloat32)
+      return Status::InvalidArgument("greedy-head expects f32 logits[..., vocabulary]");
+    HYLE_ASSIGN_OR_RETURN(outputs[0], TensorDesc::dense(DataType::kBFloat16, inputs[0].dimensions()));
+    std::array<std::int64_t, 8> one{};
+    const auto dimensions = inputs[0].dimensions();
+    if (dimensions.size() > one.size()) return Status::InvalidArgument("greedy-head: rank above 8");
+    std::copy(dimensions.begin(), dimensions.end(), one.begin());
+    one[dimensions.size() - 1] = 1;
+    const std::span<const std::int64_t> selected(one.data(), dimensions.size());
+    if (values) {
+      HYLE_ASSIGN_OR_RETURN(outputs[1], TensorDesc::dense(DataType::kFloat32, selected));
+    }
+    HYLE_ASSIGN_OR_RETURN(outputs[values ? 2 : 1], TensorDesc::dense(DataType::kInt32, selected));
     return Status::Ok();
   }
 };

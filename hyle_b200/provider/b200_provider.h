@@ -39,8 +39,9 @@ inline constexpr ProviderRuntimeProperties kRuntime{.replay_class = ProviderRepl
 
 enum class Entry : std::uint8_t {
   kUnary, kBinary, kSelect, kReduceRows, kScan, kRmsNorm, kLayerNorm, kSwiglu, kSoftmax, kMaskedSoftmax, kCast, kArgmax, kQ8Encode, kFp8Encode, kRandomBits, kCategorical,
-  kAddRmsNorm, kBiasRowSumMax, kLogitsReduce, kQ8Roundtrip
+  kAddRmsNorm, kBiasRowSumMax, kLogitsReduce, kQ8Roundtrip, kActivationMultiply, kGreedyHead
 };
+inline constexpr std::size_t kEntryCount = 22;
 
 // Everything enqueue() needs, frozen at prepare time.  Trivially copyable.
 struct Plan final {
@@ -225,10 +226,13 @@ inline std::optional<Plan> match(const Operation &op, std::span<const TensorDesc
     return p;
   }
   if (const auto *gated = op.get_if<GatedActivation>()) {
-    if (gated->activation != GatedActivationKind::kSilu || in[0].data_type() != DataType::kBFloat16 ||
-        out.size() != 1 || out[0].data_type() != DataType::kBFloat16)
+    // kSilu, kGelu, kGeluTanh on bf16 or f16 (hyle_b200_gate_kind follows GatedActivationKind's order)
+    if (static_cast<int>(gated->activation) > HYLE_B200_GATE_GELU_TANH || !type || *type == HYLE_B200_F32 ||
+        out.size() != 1 || out[0].data_type() != in[0].data_type())
       return std::nullopt;
     p.entry = Entry::kSwiglu;
+    p.kind = static_cast<int>(gated->activation);
+    p.dtype = *type;
     if (gated->inputs == GatedInputKind::kPackedHalves) {
       if (in.size() != 1 || p.cols % 2 != 0 || last_extent(out[0]) * 2 != p.cols) return std::nullopt;
       p.cols /= 2;
@@ -345,6 +349,34 @@ inline std::optional<Plan> match(const Operation &op, std::span<const TensorDesc
     p.workspace_bytes = static_cast<std::size_t>(hyle_b200_logits_workspace_bytes(p.rows, p.cols));
     return p;
   }
+  if (const auto fused = op.custom_as<ActivationMultiply>()) {
+    int kind = -1;
+    switch (fused->activation) {
+      case UnaryKind::kSilu: kind = HYLE_B200_GATE_SILU; break;
+      case UnaryKind::kGelu: kind = HYLE_B200_GATE_GELU; break;
+      case UnaryKind::kGeluTanh: kind = HYLE_B200_GATE_GELU_TANH; break;
+      default: break;
+    }
+    if (kind < 0 || in.size() != 2 || out.size() != 1 || !type || *type == HYLE_B200_F32 || in[1] != in[0] || out[0] != in[0])
+      return std::nullopt;
+    p.entry = Entry::kActivationMultiply;
+    p.kind = kind;
+    p.dtype = *type;
+    p.gate_stride = p.up_stride = p.cols;
+    return p;
+  }
+  if (const auto head = op.custom_as<GreedyHead>()) {
+    const std::size_t index = head->values ? 2 : 1;
+    if (in.size() != 1 || out.size() != index + 1 || in[0].data_type() != DataType::kFloat32 || in[0].rank() == 0 ||
+        out[0].data_type() != DataType::kBFloat16 || elements(out[0]) != p.count ||
+        (head->values && (out[1].data_type() != DataType::kFloat32 || elements(out[1]) != p.rows)) ||
+        out[index].data_type() != DataType::kInt32 || elements(out[index]) != p.rows)
+      return std::nullopt;
+    p.entry = Entry::kGreedyHead;
+    p.has_weight = head->values;
+    p.workspace_bytes = static_cast<std::size_t>(hyle_b200_logits_workspace_bytes(p.rows, p.cols));
+    return p;
+  }
   if (op.custom_as<Q8_0Roundtrip>()) {
     if (in.size() != 1 || out.size() != 3 || in[0].data_type() != DataType::kBFloat16) return std::nullopt;
     p.entry = Entry::kQ8Roundtrip;
@@ -359,7 +391,8 @@ inline bool uses_status_word(const Plan &p) noexcept {
   switch (p.entry) {
     case Entry::kQ8Encode: case Entry::kFp8Encode: case Entry::kCategorical: case Entry::kQ8Roundtrip: return true;
     case Entry::kScan: return p.dtype == HYLE_B200_I32;
-    case Entry::kSoftmax: case Entry::kLogitsReduce: return p.workspace_bytes != 0;  // the streaming kernel
+    case Entry::kSoftmax: case Entry::kLogitsReduce: case Entry::kGreedyHead:
+      return p.workspace_bytes != 0;  // the streaming kernel
     default: return false;
   }
 }
@@ -386,11 +419,18 @@ inline int launch(const Plan &p, hyle_b200_stream_t stream, const void *const *i
     case Entry::kLayerNorm:
       return hyle_b200_layer_norm_bf16(stream, in[0], p.has_weight ? in[1] : nullptr, p.has_weight ? in[2] : nullptr,
                                        out[0], p.rows, p.cols, p.epsilon);
-    case Entry::kSwiglu: {
+    case Entry::kSwiglu:
+    case Entry::kActivationMultiply: {
       const auto *gate = static_cast<const std::uint16_t *>(in[0]);
       const void *up = p.up_offset ? static_cast<const void *>(gate + p.up_offset) : in[1];
-      return hyle_b200_swiglu_bf16(stream, gate, up, out[0], p.rows, p.cols, p.gate_stride, p.up_stride);
+      return hyle_b200_gated_activation(stream, p.kind, p.dtype, p.entry == Entry::kActivationMultiply ? 1 : 0, gate, up,
+                                        out[0], p.rows, p.cols, p.gate_stride, p.up_stride);
     }
+    case Entry::kGreedyHead:
+      return hyle_b200_logits_reduce_f32(stream, static_cast<const float *>(in[0]), p.rows, p.cols, nullptr, out[0],
+                                         static_cast<std::int32_t *>(out[p.has_weight ? 2 : 1]),
+                                         p.has_weight ? static_cast<float *>(out[1]) : nullptr, workspace, p.workspace_bytes,
+                                         status_word);
     case Entry::kSoftmax:
       return hyle_b200_softmax_f32(stream, p.kind, static_cast<const float *>(in[0]), static_cast<float *>(out[0]),
                                    p.rows, p.cols, workspace, p.workspace_bytes, status_word);

@@ -229,6 +229,24 @@ HYLE_B200_API int hyle_b200_swiglu_bf16(hyle_b200_stream_t stream, const void *g
                                         const void *up, void *out, uint64_t rows, uint64_t cols,
                                         uint64_t gate_row_stride, uint64_t up_row_stride);
 
+/* hyle::compute::GatedActivationKind (include/hyle/compute/operation.h:91-95). */
+enum hyle_b200_gate_kind {
+  HYLE_B200_GATE_SILU = 0,
+  HYLE_B200_GATE_GELU = 1,       /* 0.5 x (1 + erf(x / sqrt 2)) */
+  HYLE_B200_GATE_GELU_TANH = 2   /* 0.5 x (1 + tanh(sqrt(2/pi) (x + 0.044715 x^3))) */
+};
+/* GatedActivation{activation} on bf16 or f16 tensors (f16 separate is the form the native CPU route
+ * keeps, src/compute_provider_native/elementwise.cc:660-704):
+ *   out = storage_rne(activation(f32 gate) * f32 up), activation(-inf) = 0.
+ * round_gate != 0 rounds activation(gate) to the storage type before the product: exactly
+ * Unary{activation} followed by Binary{kMultiply} on 16-bit tensors, in one pass.  That is how a graph
+ * region fuses those two nodes (engine/models/qwen35/block_graph.h:27-40 emits them for 16-bit
+ * activations) without changing their result.  Strides as for hyle_b200_swiglu_bf16. */
+HYLE_B200_API int hyle_b200_gated_activation(hyle_b200_stream_t stream, int activation, int dtype,
+                                             int round_gate, const void *gate, const void *up,
+                                             void *out, uint64_t rows, uint64_t cols,
+                                             uint64_t gate_row_stride, uint64_t up_row_stride);
+
 /* ---------------------------------------------------------------------------------------------
  * Logits reduction: per row of f32 logits, in one pass over HBM,
  *   lse[row]          = max + float(log(double sum exp(x - max)))      (the LogSoftmax shift)

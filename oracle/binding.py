@@ -102,6 +102,7 @@ class Oracle:
         L.hyle_oracle_rms_norm_bf16.argtypes = [_vp, _vp, _i, _vp, _vp, _u64, _u64, _f]
         L.hyle_oracle_add_rms_norm_bf16.argtypes = [_vp, _vp, _vp, _i, _vp, _vp, _vp, _u64, _u64, _f]
         L.hyle_oracle_swiglu_bf16.argtypes = [_vp, _vp, _vp, _vp, _u64, _u64, _u64, _u64]
+        L.hyle_oracle_gated_activation.argtypes = [_i, _i, _i, _vp, _vp, _vp, _vp, _u64, _u64, _u64, _u64]
         L.hyle_oracle_softmax_f32.argtypes = [_i, _vp, _vp, _u64, _u64]
         L.hyle_oracle_argmax_f32.argtypes = [_vp, _vp, _vp, _u64, _u64]
         L.hyle_oracle_logits_reduce_f32.argtypes = [_vp, _u64, _u64, _vp, _vp, _vp, _vp, _vp]
@@ -283,6 +284,15 @@ class Oracle:
         out, out32 = np.empty((rows, cols), np.uint16), np.empty((rows, cols), np.float32)
         self.lib.hyle_oracle_swiglu_bf16(_ptr(gate), _ptr(up), _ptr(out), _ptr(out32), rows, cols,
                                          gate_stride, up_stride)
+        return out, out32
+
+    def gated_activation(self, activation, dtype, gate, up, round_gate=False):
+        """(storage words, unrounded f32) of GatedActivation{activation} on bf16 / f16 words [rows, cols]."""
+        gate, up = _c(gate, np.uint16), _c(up, np.uint16)
+        rows, cols = gate.shape
+        out, out32 = np.empty((rows, cols), np.uint16), np.empty((rows, cols), np.float32)
+        self.lib.hyle_oracle_gated_activation(activation, dtype, int(round_gate), _ptr(gate), _ptr(up), _ptr(out),
+                                              _ptr(out32), rows, cols, cols, cols)
         return out, out32
 
     def softmax(self, x, log=False):

@@ -676,6 +676,33 @@ ORACLE_API void hyle_oracle_swiglu_bf16(const uint16_t *gate, const uint16_t *up
   }
 }
 
+/* GatedActivation{kSilu | kGelu | kGeluTanh} on bf16 / f16 storage: the activation in f32 (the
+ * definitions of src/simd/math/activations.cc:21-47 used by unary_value above), times up in f32, one
+ * rounding (src/compute_provider_native/aten_cpu_provider.cc:414-445,654-665).  round_gate: the
+ * activated gate is rounded to storage first, i.e. Unary{activation} then Binary{kMultiply}.
+ * activation: 0 silu, 1 gelu, 2 gelu_tanh. */
+ORACLE_API void hyle_oracle_gated_activation(int activation, int dtype, int round_gate, const uint16_t *gate,
+                                             const uint16_t *up, uint16_t *out, float *out_f32, uint64_t rows,
+                                             uint64_t cols, uint64_t gate_stride, uint64_t up_stride) {
+  const int kind = activation == 0 ? UN_SILU : activation == 1 ? UN_GELU : UN_GELU_TANH;
+#pragma omp parallel for schedule(static)
+  for (uint64_t r = 0; r < rows; ++r) {
+    for (uint64_t c = 0; c < cols; ++c) {
+      const float g = load_as_f32(gate, r * gate_stride + c, dtype);
+      const float u = load_as_f32(up, r * up_stride + c, dtype);
+      float a = unary_value(kind, g);
+      if (round_gate) {
+        uint32_t word = 0;  /* wide enough for any storage type the helpers know */
+        store_from_f32(&word, 0, dtype, a);
+        a = load_as_f32(&word, 0, dtype);
+      }
+      const float v = a * u;
+      if (out_f32) out_f32[r * cols + c] = v;
+      store_from_f32(out, r * cols + c, dtype, v);
+    }
+  }
+}
+
 /* ---- Softmax / LogSoftmax / log-sum-exp -------------------------------------------------------
  * src/simd/math/activations.cc:274-334: finite_row_max rejects NaN and +inf and rows without a
  * finite maximum (all outputs NaN); exp in f32, sum in f64, multiply by float(1/sum);

@@ -158,8 +158,24 @@ int main() {
           "GatedActivation{kSilu, kSeparate} bf16");
     check(taken(*context, Operation(GatedActivation{GatedActivationKind::kSilu, GatedInputKind::kPackedHalves}), one, out),
           "GatedActivation{kSilu, kPackedHalves} bf16");
-    check(!taken(*context, Operation(GatedActivation{GatedActivationKind::kGelu, GatedInputKind::kSeparate}), separate, out),
-          "GatedActivation{kGelu} not taken");
+    check(taken(*context, Operation(GatedActivation{GatedActivationKind::kGelu, GatedInputKind::kSeparate}), separate, out),
+          "GatedActivation{kGelu, kSeparate} bf16");
+    const auto half = dense(DataType::kFloat16, {32, 6144});
+    const std::array separate16{half, half};
+    const std::array out16{half};
+    check(taken(*context, Operation(GatedActivation{GatedActivationKind::kSilu, GatedInputKind::kSeparate}), separate16, out16),
+          "GatedActivation{kSilu, kSeparate} f16 (the form the native CPU route keeps)");
+    const auto wide = dense(DataType::kFloat32, {32, 6144});
+    const std::array separate32{wide, wide};
+    const std::array out32{wide};
+    check(!taken(*context, Operation(GatedActivation{GatedActivationKind::kSilu, GatedInputKind::kSeparate}), separate32, out32),
+          "GatedActivation f32 not taken");
+    std::array<TensorDesc, 1> fused_out{};
+    check(b200::ActivationMultiply{}.infer_output_descriptions(separate, fused_out).ok() &&
+              taken(*context, Operation::custom(b200::ActivationMultiply{.activation = UnaryKind::kGelu}), separate, fused_out),
+          "custom b200-activation-multiply{kGelu}");
+    check(!taken(*context, Operation::custom(b200::ActivationMultiply{.activation = UnaryKind::kTanh}), separate, fused_out),
+          "b200-activation-multiply{kTanh} not taken");
   }
   {  // Softmax / LogSoftmax / Cast / TopK{1}
     const auto logits = dense(DataType::kFloat32, {16, 151936});
@@ -188,6 +204,14 @@ int main() {
     check(!taken(*context, Operation(Cast{DataType::kFloat8E5M2}), in, e5m2_out), "Cast{f32 -> E5M2} not taken (no such CPU pair)");
     const std::array top_out{values, indices};
     check(taken(*context, Operation(TopK{.count = 1}), in, top_out), "TopK{count=1} -> values f32, indices i32");
+    std::array<TensorDesc, 3> head3{};
+    std::array<TensorDesc, 2> head2{};
+    check(b200::GreedyHead{}.infer_output_descriptions(in, head3).ok() && head3[1] == values && head3[2] == indices &&
+              taken(*context, Operation::custom(b200::GreedyHead{}), in, head3),
+          "custom b200-greedy-head -> probabilities bf16, values, indices");
+    check(b200::GreedyHead{.values = false}.infer_output_descriptions(in, head2).ok() && head2[1] == indices &&
+              taken(*context, Operation::custom(b200::GreedyHead{.values = false}), in, head2),
+          "custom b200-greedy-head{values = false} -> probabilities bf16, indices");
   }
   {  // the fused operators and CacheEncode{q8_0}, with inferred outputs
     const std::array in3{bf16_mat, bf16_mat, bf16_w};

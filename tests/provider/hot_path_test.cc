@@ -4,7 +4,7 @@
 // on a Context of the thin CUDA-12 backend (hyle_b200/provider/b200_backend.cc), and compares every
 // output byte with the same entry point called directly through the C ABI on the same device inputs.
 //
-// Every one of the adapter's 20 entries runs twice through one invocation (the second submit reuses
+// Every one of the adapter's 22 entries runs twice through one invocation (the second submit reuses
 // the workspace the first one left behind), with the caller's workspace POISONED (0xFF) before the
 // invocation is created.  Then the error protocol: a NaN in a Q8_0 / FP8 cache-encode input and an
 // invalid Categorical row must complete with Status::InvalidArgument, an overflowing i32 Scan with
@@ -438,12 +438,36 @@ int main() {
                                                             ws_bytes);
                      }, b200::Entry::kQ8Roundtrip});
   }
+  {  // what the graph regions lower to, and the wider gating domain
+    const auto g = dense(DataType::kBFloat16, {32, 6144});
+    cases.push_back({"custom b200-activation-multiply{kSilu} bf16 [32,6144]",
+                     Operation::custom(b200::ActivationMultiply{.activation = UnaryKind::kSilu}), {g, g}, {g},
+                     {bf16_normal(32 * 6144, 40, 1.5f), bf16_normal(32 * 6144, 41, 1.5f)}, 0,
+                     [](auto s, auto in, auto out, void *, std::uint64_t, std::uint32_t *) {
+                       return hyle_b200_gated_activation(s, HYLE_B200_GATE_SILU, HYLE_B200_BF16, 1, in[0], in[1], out[0], 32, 6144, 6144, 6144);
+                     }, b200::Entry::kActivationMultiply});
+    const auto h = dense(DataType::kFloat16, {32, 6144});
+    cases.push_back({"GatedActivation{kGeluTanh, kSeparate} f16 [32,6144]",
+                     Operation(GatedActivation{GatedActivationKind::kGeluTanh, GatedInputKind::kSeparate}), {h, h}, {h},
+                     {f16_normal(32 * 6144, 42, 1.5f), f16_normal(32 * 6144, 43, 1.5f)}, 0,
+                     [](auto s, auto in, auto out, void *, std::uint64_t, std::uint32_t *) {
+                       return hyle_b200_gated_activation(s, HYLE_B200_GATE_GELU_TANH, HYLE_B200_F16, 0, in[0], in[1], out[0], 32, 6144, 6144, 6144);
+                     }, b200::Entry::kSwiglu});
+    const auto logits = dense(DataType::kFloat32, {72, 19456});
+    cases.push_back({"custom b200-greedy-head{values} [72,19456] (streaming kernel, workspace)", Operation::custom(b200::GreedyHead{}), {logits},
+                     {dense(DataType::kBFloat16, {72, 19456}), dense(DataType::kFloat32, {72, 1}), dense(DataType::kInt32, {72, 1})},
+                     {f32_normal(72 * 19456, 44, 4.0f)}, hyle_b200_logits_workspace_bytes(72, 19456),
+                     [](auto s, auto in, auto out, void *ws, std::uint64_t ws_bytes, std::uint32_t *status) {
+                       return hyle_b200_logits_reduce_f32(s, static_cast<const float *>(in[0]), 72, 19456, nullptr, out[0],
+                                                          static_cast<std::int32_t *>(out[2]), static_cast<float *>(out[1]), ws, ws_bytes, status);
+                     }, b200::Entry::kGreedyHead});
+  }
   for (const auto &c : cases) run_case(fixture, c);
-  std::array<bool, 20> covered{};
+  std::array<bool, b200::kEntryCount> covered{};
   for (const auto &c : cases) covered[static_cast<std::size_t>(c.entry)] = true;
   bool all = true;
   for (bool one : covered) all = all && one;
-  check(all, "every Entry of the adapter (20) ran through submit()");
+  check(all, "every Entry of the adapter (" + std::to_string(b200::kEntryCount) + ") ran through submit()");
 
   // ---- the error protocol: device status word -> the Completion's terminal status ------------------------------------------
   const auto resource = fixture.memory.ref();

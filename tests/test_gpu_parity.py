@@ -269,6 +269,43 @@ def test_swiglu_specials_packed_and_odd_shapes(oracle, ):
 
 
 # ---- workload 4: logits -> lse, softmax bf16, argmax ----------------------------------------------------------------------
+@pytest.mark.parametrize("dtype", ["bf16", "f16"])
+@pytest.mark.parametrize("activation", [abi.GATE_SILU, abi.GATE_GELU, abi.GATE_GELU_TANH])
+def test_gated_activation_kinds_and_storage_types(oracle, activation, dtype):
+    """GatedActivation{kSilu|kGelu|kGeluTanh} on bf16 and f16: one storage step from the checker; with the
+    activated gate rounded first, bit-identical to this library's Unary kernel followed by its Multiply."""
+    rng = np.random.default_rng(activation * 2 + (dtype == "f16"))
+    torch_dtype = torch.bfloat16 if dtype == "bf16" else torch.float16
+    code = ob.BF16 if dtype == "bf16" else ob.F16
+    for rows, cols in [(33, 6144), (5, 1000), (3, 7)]:
+        g32 = (1.5 * rng.standard_normal((rows, cols))).astype(np.float32)
+        u32 = (1.5 * rng.standard_normal((rows, cols))).astype(np.float32)
+        g32[0, :4] = [-np.inf, np.inf, np.nan, -0.0]
+        gate = torch.from_numpy(g32).to(DEV).to(torch_dtype)
+        up = torch.from_numpy(u32).to(DEV).to(torch_dtype)
+        gate_words = gate.view(torch.int16).cpu().numpy().view(np.uint16)
+        up_words = up.view(torch.int16).cpu().numpy().view(np.uint16)
+        for round_gate in (False, True):
+            got = ops.gated_activation(gate, up, activation, round_gate).view(torch.int16).cpu().numpy().view(np.uint16)
+            want, _ = oracle.gated_activation(activation, code, gate_words, up_words, round_gate)
+            if dtype == "bf16":
+                assert bf16_ulp_distance(got, want).max(initial=0) <= (2 if round_gate else 1)
+            else:
+                a, b = got.view(np.float16).astype(np.float64), want.view(np.float16).astype(np.float64)
+                assert np.array_equal(np.isnan(a), np.isnan(b))
+                ok = ~np.isnan(b)
+                step = np.maximum(np.abs(b[ok]) * 2.0 ** -10, 2.0 ** -24)
+                assert np.all(np.abs(a[ok] - b[ok]) <= (2 if round_gate else 1) * step)
+        unary_kind = {abi.GATE_SILU: abi.UNARY_SILU, abi.GATE_GELU: abi.UNARY_GELU, abi.GATE_GELU_TANH: abi.UNARY_GELU_TANH}[activation]
+        two_steps = ops.multiply(ops.unary(unary_kind, gate), up)
+        fused = ops.gated_activation(gate, up, activation, True)
+        a, b = two_steps.view(torch.int16), fused.view(torch.int16)
+        nan = torch.isnan(two_steps.float())
+        assert torch.equal(nan, torch.isnan(fused.float())) and torch.equal(a[~nan], b[~nan])
+    with pytest.raises(abi.KernelError):
+        abi.check("gate", abi.load().hyle_b200_gated_activation(0, 3, abi.BF16, 0, 1 << 20, 1 << 20, 1 << 20, 1, 8, 8, 8))
+
+
 def check_logits(oracle, logits, workspace=None):
     lse, probs, index, value = ops.logits_reduce(to_dev(logits), workspace=workspace)
     want_lse, want_p, want_p32, want_i, want_v = oracle.logits_reduce(logits)

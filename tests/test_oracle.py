@@ -34,6 +34,29 @@ def test_swiglu_matches_reference_golden(oracle, golden):
     assert np.array_equal(out[~nan], want[~nan])
 
 
+def test_gated_activation_is_pinned_on_the_reference_floor(oracle, golden):
+    """The general gating entry of the checker: its SiLU / bf16 form is the reference's swiglu_bf16 bit for
+    bit; the GELU forms are the floor-pinned unary activations times up with one rounding; the rounded-gate
+    form is Unary then Multiply."""
+    from oracle import binding as ob
+
+    gate, up = golden["swiglu_gate"], golden["swiglu_up"]
+    want = golden["swiglu_out"]
+    out, _ = oracle.gated_activation(0, ob.BF16, gate, up)
+    nan = (want & 0x7FFF) > 0x7F80
+    assert np.array_equal(out[~nan], want[~nan]) and np.array_equal(nan, (out & 0x7FFF) > 0x7F80)
+    for activation, unary in ((0, ob.SILU), (1, ob.GELU), (2, ob.GELU_TANH)):
+        for dtype in (ob.BF16, ob.F16):
+            words = gate if dtype == ob.BF16 else (oracle.bf16_to_f32(gate).astype(np.float16).view(np.uint16))
+            other = up if dtype == ob.BF16 else (oracle.bf16_to_f32(up).astype(np.float16).view(np.uint16))
+            activated = oracle.unary(unary, dtype, words)
+            two_steps = oracle.binary(ob.MULTIPLY, dtype, activated, other)
+            fused, _ = oracle.gated_activation(activation, dtype, words, other, round_gate=True)
+            both_nan = lambda w: (w & 0x7FFF) > (0x7F80 if dtype == ob.BF16 else 0x7C00)
+            keep = ~both_nan(two_steps)
+            assert np.array_equal(fused[keep], two_steps[keep]) and np.array_equal(both_nan(fused), ~keep)
+
+
 @pytest.mark.parametrize("hidden", [1, 127, 128, 129, 257, 2048, 4096])
 def test_rms_norm_matches_reference_golden(oracle, golden, hidden):
     x, w = golden[f"rms_x_{hidden}"], golden[f"rms_w_{hidden}"]

@@ -54,3 +54,19 @@ def test_hot_path_program_is_built_with_the_cold_one():
     if not torch.cuda.is_available():
         run = subprocess.run([binary], capture_output=True, text=True, timeout=120)
         assert run.returncode == 77 and "needs a GPU" in run.stdout
+
+
+def test_region_provider_claims_the_fused_recipes_under_graph_compile():
+    """`tests/provider/region_test.cc`, CPU half: graph::compile of the reference with the region provider
+    claims Binary{kAdd} -> RmsNorm, Unary{kSilu} -> Binary{kMultiply} and Softmax -> Cast + TopK{1} as three
+    regions lowered to the provider's custom operators, and declines five near misses."""
+    build_provider_tests()
+    binary = os.path.join(BINARIES, "b200_region_test")
+    if not os.path.exists(binary):
+        pytest.skip("reference tree absent and no prebuilt oracle/_ref/provider/b200_region_test")
+    run = subprocess.run([binary], capture_output=True, text=True, timeout=300)
+    assert run.returncode == 0, run.stdout + run.stderr
+    assert "0 failure(s)" in run.stdout and "FAIL" not in run.stdout
+    for line in ("three regions are claimed", "runs as b200-add-rms-norm", "runs as b200-activation-multiply",
+                 "runs as b200-greedy-head", "TopK{count=2}: not claimed", "residual sum nobody else reads"):
+        assert line in run.stdout
