@@ -24,7 +24,7 @@ REDUCE_SUM, REDUCE_MEAN, REDUCE_MINIMUM, REDUCE_MAXIMUM = 0, 1, 2, 3
 # enum hyle_b200_softmax_kind
 SOFTMAX, LOG_SOFTMAX = 0, 1
 # enum hyle_b200_result
-OK, INVALID_VALUE, NOT_SUPPORTED, STATIC_SCRATCH_EXCEEDED = 0, 1, 801, 100001
+OK, INVALID_VALUE, NOT_SUPPORTED, STATIC_SCRATCH_EXCEEDED, IO_ERROR = 0, 1, 801, 100001, 100002
 STATIC_MAX_VALUES = 1 << 31
 # enum hyle_b200_status_bits
 STATUS_INVALID_Q8_INPUT = 1
@@ -35,7 +35,7 @@ STATUS_SCAN_OVERFLOW = 16
 STATUS_STREAM_WAIT_TIMEOUT = 32
 EXCHANGE_MAX_RANKS, EXCHANGE_MAILBOX_BYTES, EXCHANGE_HANDLE_BYTES = 8, 256, 64
 
-ABI_VERSION = 15
+ABI_VERSION = 16
 
 _p = ctypes.c_void_p
 _u64 = ctypes.c_uint64
@@ -84,6 +84,11 @@ SIGNATURES = {
     "hyle_b200_exchange_open": (_i, [ctypes.c_char_p, ctypes.POINTER(_p)]),
     "hyle_b200_exchange_close": (_i, [_p]),
     "hyle_b200_exchange_destroy": (_i, [_p]),
+    "hyle_b200_file_stream_open": (_i, [ctypes.c_char_p, _u64, _u64, _p, ctypes.POINTER(_p)]),
+    "hyle_b200_file_stream_next": (_i, [_p, _p, ctypes.POINTER(_p), ctypes.POINTER(_u64), ctypes.POINTER(_u64)]),
+    "hyle_b200_file_stream_get_report": (_i, [_p, _p]),
+    "hyle_b200_file_stream_close": (_i, [_p]),
+    "hyle_b200_q8_0_decode_file_bf16": (_i, [_p, ctypes.c_char_p, _u64, _u64, _p, _p, _p]),
     "hyle_b200_random_bits": (_i, [_p, _p, _u64, _u32, _p]),
     "hyle_b200_categorical": (_i, [_p, _i, _p, _p, _u64, _u64, _p, _p, _p]),
 }
@@ -94,6 +99,17 @@ class StreamTuning(ctypes.Structure):
     """hyle_b200_stream_tuning: zero fields mean "choose"."""
     _fields_ = [("chunk_vectors", ctypes.c_int32), ("window_rows", _u32), ("help_after_polls", _u32),
                 ("ctas_per_sm", ctypes.c_int32)]
+
+
+class FileStreamOptions(ctypes.Structure):
+    """hyle_b200_file_stream_options: zero fields take the defaults (8 MiB chunks, 4 slots)."""
+    _fields_ = [("chunk_bytes", _u64), ("slots", _u32), ("reserved", _u32), ("chunk_granule", _u64)]
+
+
+class FileStreamReport(ctypes.Structure):
+    """hyle_b200_file_stream_report."""
+    _fields_ = [(name, _u64) for name in ("bytes_read", "bytes_copied", "io_calls", "copies", "staging_bytes", "device_bytes",
+                                           "chunk_bytes", "chunks")]
 
 
 class StreamPlan(ctypes.Structure):

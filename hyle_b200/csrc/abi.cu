@@ -26,6 +26,7 @@ extern "C" const char *hyle_b200_result_string(int result) {
     case HYLE_B200_OK: return "ok";
     case HYLE_B200_INVALID_VALUE: return "invalid argument";
     case HYLE_B200_NOT_SUPPORTED: return "shape or alignment not supported by this library";
+    case HYLE_B200_IO_ERROR: return "file stream: cannot open the file, the range is not inside it, or a read failed";
     case HYLE_B200_STATIC_SCRATCH_EXCEEDED:
       return "count exceeds HYLE_B200_STATIC_MAX_VALUES, the capacity of the library's static scratch";
     default: return cudaGetErrorString(static_cast<cudaError_t>(result));

@@ -1,0 +1,255 @@
+// File -> pinned host memory -> device, as a stream of chunks in file order.
+//
+// The reference feeds on-disk weight banks to the GPU through a pipeline of in-flight staging slots
+// (include/hyle/compute/file_stream.h:23-31: `in_flight_slots`, `staging_bytes_per_slot`;
+// include/hyle/compute/cuda_file_stream.h:10-14 binds it to a CUDA Queue with pinned staging;
+// scheduling in src/compute_stream/file_stream.cc).  This is that pipeline for the one consumer this
+// library has, a kernel that decodes Q8_0 blocks (the GGUF Q8_0 weight layout is this library's
+// carrier: rows of k/32 blocks of 34 bytes, src/compute_ops/low_precision.cc:269-297):
+//
+//   reader thread:   pread(chunk) into pinned slot s  ->  cudaMemcpyAsync(device slot s) on the copy
+//                    stream  ->  event copied[s]
+//   next(consumer):  the consumer's stream waits for copied[s] (device-side), gets the device pointer;
+//                    the call also records done[previous slot] on the consumer's stream, which the copy
+//                    stream waits for before it overwrites that slot
+//
+// so disk reads, host->device copies and the consumer's kernels overlap, the host never waits for the
+// GPU except to reuse a pinned slot whose copy is still in flight, and NOTHING allocates after open():
+// `slots` pinned buffers, `slots` device buffers, 2 x `slots` events, one stream, one thread.
+#include <atomic>
+#include <cerrno>
+#include <condition_variable>
+#include <cstring>
+#include <mutex>
+#include <new>
+#include <thread>
+
+#include <fcntl.h>
+#include <sys/stat.h>
+#include <unistd.h>
+
+#include "common.cuh"
+
+namespace {
+
+constexpr uint32_t kMaxSlots = 16;
+constexpr uint64_t kDefaultChunkBytes = 8ull << 20;
+
+}  // namespace
+
+struct hyle_b200_file_stream {
+  int fd = -1;
+  int device = 0;
+  uint64_t file_offset = 0, bytes = 0, chunk_bytes = 0, chunks = 0;
+  uint32_t slots = 0;
+  unsigned char *pinned[kMaxSlots] = {};
+  unsigned char *resident[kMaxSlots] = {};
+  cudaEvent_t copied[kMaxSlots] = {};  // the H2D copy into slot s has completed
+  cudaEvent_t done[kMaxSlots] = {};    // the consumer has finished with slot s
+  cudaStream_t copy_stream = nullptr;
+  std::thread reader;
+  std::mutex mutex;
+  std::condition_variable changed;
+  uint64_t issued = 0;      // chunks whose copy has been issued (reader -> consumer)
+  uint64_t handed = 0;      // chunks handed to the consumer by next()
+  uint64_t released = 0;    // chunks whose done[] event has been recorded (consumer -> reader)
+  int error = HYLE_B200_OK; // first reader failure
+  bool closing = false;
+  hyle_b200_file_stream_report report{};
+
+  uint64_t chunk_size(uint64_t index) const {
+    const uint64_t start = index * chunk_bytes;
+    return bytes - start < chunk_bytes ? bytes - start : chunk_bytes;
+  }
+
+  void fail(int code) {
+    std::lock_guard lock(mutex);
+    if (error == HYLE_B200_OK) error = code;
+    changed.notify_all();
+  }
+
+  void read_loop() {
+    if (cudaSetDevice(device) != cudaSuccess) return fail(HYLE_B200_INVALID_VALUE);
+    for (uint64_t index = 0; index < chunks; ++index) {
+      const uint32_t slot = static_cast<uint32_t>(index % slots);
+      if (index >= slots) {
+        // slot reuse: its previous chunk must have been released by the consumer (the event exists
+        // then), and its previous copy must have left the pinned buffer
+        std::unique_lock lock(mutex);
+        changed.wait(lock, [&] { return closing || released > index - slots; });
+        if (closing) return;
+        lock.unlock();
+        if (cudaEventSynchronize(copied[slot]) != cudaSuccess) return fail(HYLE_B200_IO_ERROR);
+        if (cudaStreamWaitEvent(copy_stream, done[slot], 0) != cudaSuccess) return fail(HYLE_B200_IO_ERROR);
+      }
+      const uint64_t size = chunk_size(index);
+      uint64_t have = 0;
+      while (have < size) {
+        const ssize_t got = pread(fd, pinned[slot] + have, size - have, static_cast<off_t>(file_offset + index * chunk_bytes + have));
+        ++report.io_calls;
+        if (got < 0 && errno == EINTR) continue;
+        if (got <= 0) return fail(HYLE_B200_IO_ERROR);  // error, or the file ends inside the range
+        have += static_cast<uint64_t>(got);
+      }
+      report.bytes_read += size;
+      if (cudaMemcpyAsync(resident[slot], pinned[slot], size, cudaMemcpyHostToDevice, copy_stream) != cudaSuccess ||
+          cudaEventRecord(copied[slot], copy_stream) != cudaSuccess)
+        return fail(HYLE_B200_IO_ERROR);
+      ++report.copies;
+      report.bytes_copied += size;
+      {
+        std::lock_guard lock(mutex);
+        issued = index + 1;
+        if (closing) return;
+      }
+      changed.notify_all();
+    }
+  }
+};
+
+extern "C" int hyle_b200_file_stream_open(const char *path, uint64_t file_offset, uint64_t bytes,
+                                          const hyle_b200_file_stream_options *options, hyle_b200_file_stream **out) {
+  if (out == nullptr) return HYLE_B200_INVALID_VALUE;
+  *out = nullptr;
+  if (path == nullptr) return HYLE_B200_INVALID_VALUE;
+  uint64_t chunk = options != nullptr && options->chunk_bytes != 0 ? options->chunk_bytes : kDefaultChunkBytes;
+  uint32_t slots = options != nullptr && options->slots != 0 ? options->slots : 4;
+  const uint64_t granule = options != nullptr && options->chunk_granule != 0 ? options->chunk_granule : 1;
+  if (slots < 2 || slots > kMaxSlots || chunk < granule) return HYLE_B200_INVALID_VALUE;
+  chunk -= chunk % granule;  // whole records per chunk (34-byte Q8_0 blocks, rows ...)
+  const int fd = ::open(path, O_RDONLY | O_CLOEXEC);
+  if (fd < 0) return HYLE_B200_IO_ERROR;
+  struct stat info {};
+  if (fstat(fd, &info) != 0 || static_cast<uint64_t>(info.st_size) < file_offset ||
+      static_cast<uint64_t>(info.st_size) - file_offset < bytes) {
+    ::close(fd);
+    return HYLE_B200_IO_ERROR;  // the range is not inside the file
+  }
+  auto *stream = new (std::nothrow) hyle_b200_file_stream();
+  if (stream == nullptr) {
+    ::close(fd);
+    return static_cast<int>(cudaErrorMemoryAllocation);
+  }
+  stream->fd = fd;
+  stream->file_offset = file_offset;
+  stream->bytes = bytes;
+  stream->chunk_bytes = chunk;
+  stream->chunks = (bytes + chunk - 1) / chunk;
+  stream->slots = slots;
+  cudaError_t error = cudaGetDevice(&stream->device);
+  if (error == cudaSuccess) error = cudaStreamCreateWithFlags(&stream->copy_stream, cudaStreamNonBlocking);
+  for (uint32_t s = 0; s < slots && error == cudaSuccess; ++s) {
+    error = cudaHostAlloc(reinterpret_cast<void **>(&stream->pinned[s]), chunk, cudaHostAllocDefault);
+    if (error == cudaSuccess) error = cudaMalloc(reinterpret_cast<void **>(&stream->resident[s]), chunk);
+    if (error == cudaSuccess) error = cudaEventCreateWithFlags(&stream->copied[s], cudaEventDisableTiming);
+    if (error == cudaSuccess) error = cudaEventCreateWithFlags(&stream->done[s], cudaEventDisableTiming);
+  }
+  if (error != cudaSuccess) {
+    hyle_b200_file_stream_close(stream);
+    return static_cast<int>(error);
+  }
+  stream->report.staging_bytes = chunk * slots;
+  stream->report.device_bytes = chunk * slots;
+  stream->report.chunk_bytes = chunk;
+  stream->report.chunks = stream->chunks;
+  if (stream->chunks != 0) stream->reader = std::thread([stream] { stream->read_loop(); });
+  *out = stream;
+  return HYLE_B200_OK;
+}
+
+extern "C" int hyle_b200_file_stream_next(hyle_b200_file_stream *stream, hyle_b200_stream_t consumer, const void **device_chunk,
+                                          uint64_t *chunk_bytes, uint64_t *chunk_offset) {
+  if (stream == nullptr || device_chunk == nullptr || chunk_bytes == nullptr) return HYLE_B200_INVALID_VALUE;
+  *device_chunk = nullptr;
+  *chunk_bytes = 0;
+  auto consumer_stream = reinterpret_cast<cudaStream_t>(consumer);
+  // whatever the consumer enqueued on the previous chunk is what must finish before its slot is reused
+  if (stream->handed != 0 && stream->released < stream->handed) {
+    const uint32_t previous = static_cast<uint32_t>((stream->handed - 1) % stream->slots);
+    const cudaError_t recorded = cudaEventRecord(stream->done[previous], consumer_stream);
+    if (recorded != cudaSuccess) return static_cast<int>(recorded);
+    {
+      std::lock_guard lock(stream->mutex);
+      stream->released = stream->handed;
+    }
+    stream->changed.notify_all();
+  }
+  if (stream->handed == stream->chunks) return HYLE_B200_OK;  // end of the range: *chunk_bytes == 0
+  const uint64_t index = stream->handed;
+  {
+    std::unique_lock lock(stream->mutex);
+    stream->changed.wait(lock, [&] { return stream->issued > index || stream->error != HYLE_B200_OK; });
+    if (stream->issued <= index) return stream->error;
+  }
+  const uint32_t slot = static_cast<uint32_t>(index % stream->slots);
+  const cudaError_t waited = cudaStreamWaitEvent(consumer_stream, stream->copied[slot], 0);
+  if (waited != cudaSuccess) return static_cast<int>(waited);
+  *device_chunk = stream->resident[slot];
+  *chunk_bytes = stream->chunk_size(index);
+  if (chunk_offset != nullptr) *chunk_offset = index * stream->chunk_bytes;
+  stream->handed = index + 1;
+  return HYLE_B200_OK;
+}
+
+extern "C" int hyle_b200_file_stream_get_report(hyle_b200_file_stream *stream, hyle_b200_file_stream_report *report) {
+  if (stream == nullptr || report == nullptr) return HYLE_B200_INVALID_VALUE;
+  std::lock_guard lock(stream->mutex);
+  *report = stream->report;
+  return HYLE_B200_OK;
+}
+
+extern "C" int hyle_b200_file_stream_close(hyle_b200_file_stream *stream) {
+  if (stream == nullptr) return HYLE_B200_OK;
+  {
+    std::lock_guard lock(stream->mutex);
+    stream->closing = true;
+  }
+  stream->changed.notify_all();
+  if (stream->reader.joinable()) stream->reader.join();
+  int device = 0;
+  const bool switched = cudaGetDevice(&device) == cudaSuccess && device != stream->device && cudaSetDevice(stream->device) == cudaSuccess;
+  if (stream->copy_stream != nullptr) cudaStreamSynchronize(stream->copy_stream);
+  for (uint32_t s = 0; s < kMaxSlots; ++s) {
+    // a consumer kernel may still be reading a device slot: the slot is freed after its last event
+    if (stream->done[s] != nullptr) {
+      cudaEventSynchronize(stream->done[s]);
+      cudaEventDestroy(stream->done[s]);
+    }
+    if (stream->copied[s] != nullptr) cudaEventDestroy(stream->copied[s]);
+    if (stream->resident[s] != nullptr) cudaFree(stream->resident[s]);
+    if (stream->pinned[s] != nullptr) cudaFreeHost(stream->pinned[s]);
+  }
+  if (stream->copy_stream != nullptr) cudaStreamDestroy(stream->copy_stream);
+  if (switched) cudaSetDevice(device);
+  if (stream->fd >= 0) ::close(stream->fd);
+  delete stream;
+  return HYLE_B200_OK;
+}
+
+// The Q8_0 bank of `count` values at `file_offset` of `path`, decoded to bf16 at `out` (device), chunk by
+// chunk on `consumer`: disk, PCIe and the decode kernel overlap.  Returns after the last launch is
+// enqueued and the pipeline is torn down (which waits for the last decode).
+extern "C" int hyle_b200_q8_0_decode_file_bf16(hyle_b200_stream_t consumer, const char *path, uint64_t file_offset, uint64_t count,
+                                               void *out_bf16, const hyle_b200_file_stream_options *options,
+                                               hyle_b200_file_stream_report *report) {
+  if (count % 32 != 0 || (count != 0 && out_bf16 == nullptr)) return HYLE_B200_INVALID_VALUE;
+  hyle_b200_file_stream_options chosen{};
+  if (options != nullptr) chosen = *options;
+  chosen.chunk_granule = 34 * 8;  // whole blocks, and chunk offsets that keep the decoded output 16-byte aligned (8 blocks = 512 B of bf16)
+  hyle_b200_file_stream *stream = nullptr;
+  int code = hyle_b200_file_stream_open(path, file_offset, count / 32 * 34, &chosen, &stream);
+  if (code != HYLE_B200_OK) return code;
+  auto *out = static_cast<unsigned char *>(out_bf16);
+  for (;;) {
+    const void *chunk = nullptr;
+    uint64_t bytes = 0, offset = 0;
+    code = hyle_b200_file_stream_next(stream, consumer, &chunk, &bytes, &offset);
+    if (code != HYLE_B200_OK || bytes == 0) break;
+    const uint64_t values = bytes / 34 * 32;
+    code = hyle_b200_q8_0_decode_bf16(consumer, chunk, values, out + offset / 34 * 32 * 2);
+    if (code != HYLE_B200_OK) break;
+  }
+  if (report != nullptr) hyle_b200_file_stream_get_report(stream, report);
+  hyle_b200_file_stream_close(stream);
+  return code;
+}

@@ -9,6 +9,7 @@ CPU tensor raises.
 from __future__ import annotations
 
 import ctypes
+import os
 from typing import Optional, Tuple
 
 import numpy as np
@@ -498,6 +499,59 @@ def q8_0_decode(blocks: torch.Tensor, count: int) -> torch.Tensor:
     abi.check("hyle_b200_q8_0_decode_bf16", abi.load().hyle_b200_q8_0_decode_bf16(
         _stream(), blocks.data_ptr(), count, out.data_ptr()))
     return out
+
+
+def q8_0_decode_file(path: str, count: int, file_offset: int = 0, out: Optional[torch.Tensor] = None,
+                     chunk_bytes: int = 0, slots: int = 0, device="cuda"):
+    """Decode the Q8_0 bank of ``count`` values stored at ``file_offset`` of ``path`` into a bf16 device tensor,
+    streaming the file through pinned staging chunks while the decode kernel runs.  Returns (tensor, report)."""
+    if count % 32:
+        raise ValueError("Q8_0 needs a multiple of 32 values")
+    if out is None:
+        out = _new(count, torch.bfloat16, device)
+    options = abi.FileStreamOptions(chunk_bytes, slots, 0, 0)
+    report = abi.FileStreamReport()
+    abi.check("hyle_b200_q8_0_decode_file_bf16", abi.load().hyle_b200_q8_0_decode_file_bf16(
+        _stream(), os.fsencode(path), file_offset, count, out.data_ptr(), ctypes.addressof(options), ctypes.addressof(report)))
+    return out, report
+
+
+class FileStream:
+    """Chunks of a file range, resident on the device in file order (`hyle_b200_file_stream_*`).
+
+    Iterating yields (device pointer, bytes, offset in the range); a chunk is valid until the next one is asked for."""
+
+    def __init__(self, path: str, nbytes: int, file_offset: int = 0, chunk_bytes: int = 0, slots: int = 0, granule: int = 0):
+        self._handle = ctypes.c_void_p()
+        options = abi.FileStreamOptions(chunk_bytes, slots, 0, granule)
+        abi.check("hyle_b200_file_stream_open", abi.load().hyle_b200_file_stream_open(
+            os.fsencode(path), file_offset, nbytes, ctypes.addressof(options), ctypes.byref(self._handle)))
+
+    def __iter__(self):
+        lib = abi.load()
+        while True:
+            pointer, size, offset = ctypes.c_void_p(), ctypes.c_uint64(), ctypes.c_uint64()
+            abi.check("hyle_b200_file_stream_next", lib.hyle_b200_file_stream_next(
+                self._handle, _stream(), ctypes.byref(pointer), ctypes.byref(size), ctypes.byref(offset)))
+            if size.value == 0:
+                return
+            yield pointer.value, size.value, offset.value
+
+    def report(self) -> abi.FileStreamReport:
+        report = abi.FileStreamReport()
+        abi.check("hyle_b200_file_stream_get_report", abi.load().hyle_b200_file_stream_get_report(self._handle, ctypes.addressof(report)))
+        return report
+
+    def close(self) -> None:
+        if self._handle:
+            abi.load().hyle_b200_file_stream_close(self._handle)
+            self._handle = ctypes.c_void_p()
+
+    def __enter__(self):
+        return self
+
+    def __exit__(self, *exc):
+        self.close()
 
 
 def make_workspace(device, count: int = 0) -> torch.Tensor:

@@ -43,14 +43,16 @@ extern "C" {
 /* Same object as cudaStream_t; spelled out so C callers need no CUDA header. */
 typedef struct CUstream_st *hyle_b200_stream_t;
 
-#define HYLE_B200_ABI_VERSION 15
+#define HYLE_B200_ABI_VERSION 16
 
 enum hyle_b200_result {
   HYLE_B200_OK = 0,
   HYLE_B200_INVALID_VALUE = 1,   /* cudaErrorInvalidValue */
   HYLE_B200_NOT_SUPPORTED = 801, /* cudaErrorNotSupported */
   /* hyle_b200_q8_0_roundtrip_bf16_static: count is above HYLE_B200_STATIC_MAX_VALUES. */
-  HYLE_B200_STATIC_SCRATCH_EXCEEDED = 100001
+  HYLE_B200_STATIC_SCRATCH_EXCEEDED = 100001,
+  /* hyle_b200_file_stream_*: the file cannot be opened, the range is not inside it, or a read failed. */
+  HYLE_B200_IO_ERROR = 100002
 };
 
 /* Storage types, numbered independently of hyle::compute::DataType. */
@@ -512,6 +514,53 @@ HYLE_B200_API int hyle_b200_q8_0_roundtrip_bf16_static(hyle_b200_stream_t stream
                                                        uint64_t count, void *blocks_out,
                                                        void *decoded_bf16, double *sum_squares_out,
                                                        uint32_t *status_word);
+
+/* ---------------------------------------------------------------------------------------------
+ * File -> pinned host memory -> device, in chunks, for weight banks that live on disk.
+ * Replaces, for this library's one consumer (the Q8_0 decode kernel): the reference's file resource
+ * pipeline, include/hyle/compute/cuda_file_stream.h:10-14 over include/hyle/compute/file_stream.h:23-31
+ * (`in_flight_slots` staging slots of `staging_bytes_per_slot`; scheduling in
+ * src/compute_stream/file_stream.cc).  On-disk GGUF Q8_0 weights are this library's carrier layout: rows
+ * of k/32 blocks of 34 bytes (src/compute_ops/low_precision.cc:269-297).
+ *
+ * open() allocates everything: `slots` pinned staging buffers and `slots` device buffers of
+ * chunk_bytes, 2 x slots events, one copy stream, one reader thread; nothing allocates afterwards.
+ * The reader thread preads chunk i into pinned slot i % slots and issues ONE cudaMemcpyAsync for it on
+ * the copy stream.  next() makes the consumer's stream wait (on the device) for that copy and returns
+ * the chunk's device address; the address stays valid until the NEXT call of next(), which records on
+ * the consumer's stream that the chunk is finished with, so that the copy stream may overwrite its
+ * slot.  Chunks arrive in file order; at the end next() returns OK with *chunk_bytes == 0.  A read
+ * error or a file shorter than the range makes next() return HYLE_B200_IO_ERROR.  One consumer thread
+ * per stream object.  close() waits for the consumer's last recorded use, then frees.
+ */
+typedef struct hyle_b200_file_stream hyle_b200_file_stream;
+typedef struct hyle_b200_file_stream_options {
+  uint64_t chunk_bytes;    /* 0: 8 MiB */
+  uint32_t slots;          /* in-flight chunks, 2..16; 0: 4 */
+  uint32_t reserved;
+  uint64_t chunk_granule;  /* chunk_bytes is rounded down to a multiple of this (a record size); 0: 1 */
+} hyle_b200_file_stream_options;
+typedef struct hyle_b200_file_stream_report {
+  uint64_t bytes_read, bytes_copied;  /* so far */
+  uint64_t io_calls, copies;          /* pread calls; cudaMemcpyAsync calls (one per chunk) */
+  uint64_t staging_bytes, device_bytes, chunk_bytes, chunks;
+} hyle_b200_file_stream_report;
+HYLE_B200_API int hyle_b200_file_stream_open(const char *path, uint64_t file_offset, uint64_t bytes,
+                                             const hyle_b200_file_stream_options *options,
+                                             hyle_b200_file_stream **stream_out);
+HYLE_B200_API int hyle_b200_file_stream_next(hyle_b200_file_stream *stream, hyle_b200_stream_t consumer,
+                                             const void **device_chunk, uint64_t *chunk_bytes,
+                                             uint64_t *chunk_offset);
+HYLE_B200_API int hyle_b200_file_stream_get_report(hyle_b200_file_stream *stream,
+                                                   hyle_b200_file_stream_report *report);
+HYLE_B200_API int hyle_b200_file_stream_close(hyle_b200_file_stream *stream);
+/* The Q8_0 bank of `count` values stored at `file_offset` of `path`, decoded into the device tensor
+ * out_bf16 by hyle_b200_q8_0_decode_bf16, one launch per chunk on `consumer`, while later chunks are
+ * read and copied.  Returns when every launch is enqueued and the pipeline has been torn down. */
+HYLE_B200_API int hyle_b200_q8_0_decode_file_bf16(hyle_b200_stream_t consumer, const char *path,
+                                                  uint64_t file_offset, uint64_t count, void *out_bf16,
+                                                  const hyle_b200_file_stream_options *options,
+                                                  hyle_b200_file_stream_report *report);
 
 /* ---------------------------------------------------------------------------------------------
  * The round trip on a row-sharded tensor, with the cross-GPU sum fused into the kernel.
