@@ -61,7 +61,7 @@ def test_q8_0_bank_streams_from_disk_and_decodes_bit_exactly(tmp_path, chunk_byt
 
 @pytest.mark.gpu
 def test_chunks_arrive_in_file_order_and_slots_are_recycled(tmp_path):
-    path, count, header, _, blocks = _bank(tmp_path, 8)
+    path, count, header, _, blocks = _bank(tmp_path, 64)
     nbytes = blocks.size
     pieces = []
     runtime = ctypes.CDLL("libcudart.so.12")  # the runtime torch and the kernel library already share
@@ -81,7 +81,7 @@ def test_chunks_arrive_in_file_order_and_slots_are_recycled(tmp_path):
 
 @pytest.mark.gpu
 def test_a_file_that_ends_inside_the_range_is_an_error_not_a_hang(tmp_path):
-    path, count, header, _, blocks = _bank(tmp_path, 4)
+    path, count, header, _, blocks = _bank(tmp_path, 64)   # 557 056 bytes: nine chunks of 64 KiB
     lib = abi.load()
     handle = ctypes.c_void_p()
     options = abi.FileStreamOptions(65536, 2, 0, 0)

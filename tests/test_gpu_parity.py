@@ -285,19 +285,26 @@ def test_gated_activation_kinds_and_storage_types(oracle, activation, dtype):
         up = torch.from_numpy(u32).to(DEV).to(torch_dtype)
         gate_words = gate.view(torch.int16).cpu().numpy().view(np.uint16)
         up_words = up.view(torch.int16).cpu().numpy().view(np.uint16)
+        to_f64 = (lambda w: wl.bf16_to_f32(w).astype(np.float64)) if dtype == "bf16" else (lambda w: w.view(np.float16).astype(np.float64))
+        relative_step = 2.0 ** -8 if dtype == "bf16" else 2.0 ** -11       # half a storage step, relative
+        gate64, up64 = to_f64(gate_words), to_f64(up_words)
         for round_gate in (False, True):
             got = ops.gated_activation(gate, up, activation, round_gate).view(torch.int16).cpu().numpy().view(np.uint16)
             want, _ = oracle.gated_activation(activation, code, gate_words, up_words, round_gate)
-            if dtype == "bf16":
-                assert bf16_ulp_distance(got, want).max(initial=0) <= (2 if round_gate else 1)
-            else:
-                a, b = got.view(np.float16).astype(np.float64), want.view(np.float16).astype(np.float64)
-                assert np.array_equal(np.isnan(a), np.isnan(b))
-                infinite = np.isinf(b)
-                assert np.array_equal(a[infinite], b[infinite])
-                ok = ~np.isnan(b) & ~infinite
-                step = np.maximum(np.abs(b[ok]) * 2.0 ** -10, 2.0 ** -24)
-                assert np.all(np.abs(a[ok] - b[ok]) <= (2 if round_gate else 1) * step)
+            a, b = to_f64(got), to_f64(want)
+            assert np.array_equal(np.isnan(a), np.isnan(b))
+            infinite = np.isinf(b)
+            assert np.array_equal(a[infinite], b[infinite])
+            ok = ~np.isnan(b) & ~infinite
+            # one storage step (two with the extra rounding of the gate), plus what the erf / tanh forms lose to
+            # cancellation for negative gates: 2.5e-7 |gate| absolute in the activation, times |up|
+            steps = 2 if round_gate else 1
+            with np.errstate(invalid="ignore"):
+                product = np.nan_to_num(np.abs(gate64[ok] * up64[ok]), nan=0.0, posinf=1e30)
+            slack = steps * 2 * relative_step * np.abs(b[ok]) + 2.5e-7 * product * (1 + steps) + 1e-30
+            if dtype == "f16":
+                slack = slack + steps * 2.0 ** -24                                # subnormal f16 results
+            assert np.all(np.abs(a[ok] - b[ok]) <= slack)
         unary_kind = {abi.GATE_SILU: abi.UNARY_SILU, abi.GATE_GELU: abi.UNARY_GELU, abi.GATE_GELU_TANH: abi.UNARY_GELU_TANH}[activation]
         two_steps = ops.multiply(ops.unary(unary_kind, gate), up)
         fused = ops.gated_activation(gate, up, activation, True)
