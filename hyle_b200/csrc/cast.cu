@@ -11,6 +11,8 @@
 //   * i32 -> f32 rounds to nearest even (cast.cc:21-41).
 // HBM-bound: a thread moves eight consecutive elements per step with the widest loads and stores the
 // two element sizes allow (8 to 32 bytes), four steps in flight.
+#include <cmath>
+
 #include "common.cuh"
 
 #include <type_traits>
@@ -361,7 +363,13 @@ int launch_select(cudaStream_t stream, const void *condition, const void *when_t
 }
 
 // ---- CacheEncode{float8(scale)}: value / scale -> E4M3, a non-finite value -> byte 0 and a status bit -------
-// (src/compute_provider_ggml/ggml_cpu_provider.cc:589-596).  One IEEE division per element.
+// (src/compute_provider_ggml/ggml_cpu_provider.cc:589-596).  The byte is that of the IEEE quotient, but
+// the division itself is rarely executed: value * (1 / scale) lies within 2^-22 (relative) of the
+// quotient, the conversion is monotone, so when the two values 2^-21 below and above that product
+// convert to the same byte (one paired conversion instruction) the quotient converts to it too.
+// Otherwise -- the product sits at a rounding boundary of E4M3, about one element in 2^17 -- the division
+// decides.  `inverse` = 0 selects the division for every element (scales whose reciprocal is not a
+// normal number).
 template <int kSrc>
 __device__ __forceinline__ uint32_t cache_code(uint32_t word, float scale, bool &invalid) {
   const float value = decode<kSrc>(word);
@@ -371,19 +379,58 @@ __device__ __forceinline__ uint32_t cache_code(uint32_t word, float scale, bool 
   }
   return f32_to_e4m3(__fdiv_rn(value, scale));
 }
+// The shortcut for one element: the byte when it is certain, and `unsure` set when the product sits at
+// a rounding boundary or the value is not finite (the caller then redoes its pack with cache_code).
+template <int kSrc>
+__device__ __forceinline__ uint32_t cache_code_fast(uint32_t word, float inverse, bool &unsure) {
+  const float value = decode<kSrc>(word);
+  const float product = __fmul_rn(value, inverse);
+  const float margin = __fmul_rn(product, 4.76837158203125e-7f);  // 2^-21
+  unsigned short pair;
+  asm("cvt.rn.satfinite.e4m3x2.f32 %0, %1, %2;" : "=h"(pair) : "f"(__fadd_rn(product, margin)), "f"(__fsub_rn(product, margin)));
+  unsure |= (pair & 0xffu) != (pair >> 8) || !isfinite(value);
+  return pair & 0xffu;
+}
+// Eight elements: branch-free shortcut, and the exact route for the whole pack in the rare unsure case.
+template <int kSrc>
+__device__ __forceinline__ void cache_codes(uint32_t (&w)[8], float scale, float inverse, bool &invalid) {
+  if (inverse != 0.0f) {
+    uint32_t fast[8];
+    bool unsure = false;
+#pragma unroll
+    for (int e = 0; e < 8; ++e) fast[e] = cache_code_fast<kSrc>(w[e], inverse, unsure);
+    if (!unsure) {
+#pragma unroll
+      for (int e = 0; e < 8; ++e) w[e] = fast[e];
+      return;
+    }
+  }
+#pragma unroll
+  for (int e = 0; e < 8; ++e) w[e] = cache_code<kSrc>(w[e], scale, invalid);
+}
 
 template <int kSrc>
 __global__ void __launch_bounds__(kThreads)
-cache_encode_e4m3_kernel(const void *in, void *out, uint64_t packs, float scale, uint32_t *status_word) {
+cache_encode_e4m3_kernel(const void *in, void *out, uint64_t packs, float scale, float inverse, uint32_t *status_word) {
   grid_dependency_sync();
   constexpr int kIn = sizeof(typename Element<kSrc>::Word);
   const uint64_t stride = static_cast<uint64_t>(gridDim.x) * kThreads;
   bool invalid = false;
-  for (uint64_t i = static_cast<uint64_t>(blockIdx.x) * kThreads + threadIdx.x; i < packs; i += stride) {
+  uint64_t i = static_cast<uint64_t>(blockIdx.x) * kThreads + threadIdx.x;
+  for (; i + stride < packs; i += 2 * stride) {  // two packs in flight per thread
+    uint32_t a[8], b[8];
+    const auto first = load_pack<kIn>(in, i), second = load_pack<kIn>(in, i + stride);
+    unpack<kIn>(first, a);
+    unpack<kIn>(second, b);
+    cache_codes<kSrc>(a, scale, inverse, invalid);
+    cache_codes<kSrc>(b, scale, inverse, invalid);
+    store_pack<1>(out, i, pack<1>(a));
+    store_pack<1>(out, i + stride, pack<1>(b));
+  }
+  for (; i < packs; i += stride) {
     uint32_t w[8];
     unpack<kIn>(load_pack<kIn>(in, i), w);
-#pragma unroll
-    for (int e = 0; e < 8; ++e) w[e] = cache_code<kSrc>(w[e], scale, invalid);
+    cache_codes<kSrc>(w, scale, inverse, invalid);
     store_pack<1>(out, i, pack<1>(w));
   }
   if (status_word != nullptr && __any_sync(kFullMask, invalid) && (threadIdx.x & 31) == 0)
@@ -411,8 +458,11 @@ int launch_cache_encode(cudaStream_t stream, const void *in, void *out, uint64_t
   const uint64_t packs = vector_ok ? count / 8 : 0;
   if (packs != 0) {
     const unsigned grid = clamp_grid((packs + kThreads * 4 - 1) / (kThreads * 4), resident);
+    // the reciprocal shortcut needs scale and 1 / scale to be normal numbers (relative error bounds hold)
+    const float reciprocal = 1.0f / scale;
+    const bool normal = std::isnormal(scale) && std::isnormal(reciprocal);
     const int status = launch(cache_encode_e4m3_kernel<kSrc>, dim3(grid), dim3(kThreads), 0, stream, in, out, packs, scale,
-                              status_word);
+                              normal ? reciprocal : 0.0f, status_word);
     if (status != HYLE_B200_OK) return status;
   }
   const uint64_t done = packs * 8;
@@ -574,6 +624,77 @@ strided_tiles_kernel(const unsigned char *__restrict__ in, typename Element<kDst
   }
 }
 
+// The same transposition for 4-byte source words when everything is 16-byte aligned: 64 x 64 tiles, each
+// thread brings in four 16-byte vectors along the source's contiguous axis (all four in flight before the
+// first shared-memory store) and writes four vectors of four results along the destination's innermost
+// axis.  Shared-memory pitch 65 words: the column reads and the scattered scalar stores are at most
+// two-way conflicted, which HBM-bound traffic does not notice.
+template <int kSrc, int kDst, bool kCopy, class Index>
+__global__ void __launch_bounds__(256)
+strided_tiles64_kernel(const unsigned char *__restrict__ in, typename Element<kDst>::Word *__restrict__ out, uint64_t batches,
+                       const View view, const Transposition plan) {
+  grid_dependency_sync();
+  using Out = typename Element<kDst>::Word;
+  __shared__ uint32_t tile[64][65];
+  const uint32_t inner_axis = view.rank - 1;
+  const uint64_t inner = view.dims[inner_axis], across = view.dims[plan.axis];
+  const uint64_t tiles_inner = (inner + 63) / 64, tiles_across = (across + 63) / 64;
+  const uint64_t units = batches * tiles_inner * tiles_across;
+  const int64_t inner_stride = view.strides[inner_axis];
+  for (uint64_t unit = blockIdx.x; unit < units; unit += gridDim.x) {
+    Index rest = static_cast<Index>(unit);
+    const Index after_inner = rest / static_cast<Index>(tiles_inner);
+    const uint64_t tile_inner = rest - after_inner * static_cast<Index>(tiles_inner);
+    rest = after_inner / static_cast<Index>(tiles_across);
+    const uint64_t tile_across = after_inner - rest * static_cast<Index>(tiles_across);
+    int64_t source = 0;
+    uint64_t destination = 0;
+#pragma unroll
+    for (int d = 6; d >= 0; --d) {
+      if (d < static_cast<int>(inner_axis) && d != static_cast<int>(plan.axis)) {
+        const Index outer = rest / static_cast<Index>(view.dims[d]);
+        const uint64_t coordinate = rest - outer * static_cast<Index>(view.dims[d]);
+        source += static_cast<int64_t>(coordinate) * view.strides[d];
+        destination += coordinate * plan.dense[d];
+        rest = outer;
+      }
+    }
+    uint4 q[4];
+#pragma unroll
+    for (int step = 0; step < 4; ++step) {
+      const uint32_t slot = threadIdx.x + step * 256;
+      const uint64_t j = tile_inner * 64 + slot / 16, c = tile_across * 64 + 4 * (slot % 16);
+      q[step] = (j < inner && c < across)
+                    ? ld_stream(reinterpret_cast<const uint4 *>(in + source + static_cast<int64_t>(j) * inner_stride + static_cast<int64_t>(c) * 4))
+                    : make_uint4(0, 0, 0, 0);
+    }
+#pragma unroll
+    for (int step = 0; step < 4; ++step) {
+      const uint32_t slot = threadIdx.x + step * 256;
+      uint32_t *row = &tile[slot / 16][4 * (slot % 16)];
+      row[0] = q[step].x, row[1] = q[step].y, row[2] = q[step].z, row[3] = q[step].w;
+    }
+    __syncthreads();
+#pragma unroll
+    for (int step = 0; step < 4; ++step) {
+      const uint32_t slot = threadIdx.x + step * 256;
+      const uint32_t c_local = slot / 16, j_local = 4 * (slot % 16);
+      const uint64_t c = tile_across * 64 + c_local, j = tile_inner * 64 + j_local;
+      if (c < across && j < inner) {
+        struct alignas(4 * sizeof(Out)) Results { Out v[4]; } results;
+#pragma unroll
+        for (int k = 0; k < 4; ++k) {
+          const uint32_t word = tile[j_local + k][c_local];
+          if constexpr (kCopy) results.v[k] = static_cast<Out>(word);
+          else results.v[k] = static_cast<Out>(convert<kSrc, kDst>(word));
+        }
+        *reinterpret_cast<Results *>(out + destination + c * plan.dense[plan.axis] + j) = results;
+      }
+    }
+    __syncthreads();
+  }
+}
+
 template <int kSrc, int kDst, bool kCopy>
 int launch_strided(cudaStream_t stream, const void *in, void *out, uint64_t count, const View &view) {
   using Word = typename Element<kSrc>::Word;
@@ -592,6 +713,21 @@ int launch_strided(cudaStream_t stream, const void *in, void *out, uint64_t coun
       plan.axis = static_cast<uint32_t>(axis);
       const uint64_t inner = view.dims[view.rank - 1], across = view.dims[axis];
       const uint64_t batches = count / (inner * across);
+      if constexpr (sizeof(Word) == 4) {
+        // the vector form: whole 16-byte vectors on both sides
+        bool aligned = aligned_to(in, 16) && aligned_to(out, 4 * sizeof(Out)) && inner % 4 == 0 && across % 4 == 0 && inner >= 64 &&
+                       across >= 64;
+        for (uint32_t d = 0; d < view.rank; ++d)
+          if (static_cast<int>(d) != axis) aligned = aligned && view.strides[d] % 16 == 0;
+        if (aligned) {
+          const uint64_t units64 = batches * ((inner + 63) / 64) * ((across + 63) / 64);
+          const unsigned grid64 = clamp_grid(units64, static_cast<uint64_t>(sm_count()) * kCtasPerSm);
+          auto tiles64 = units64 <= 0xffffffffull ? strided_tiles64_kernel<kSrc, kDst, kCopy, uint32_t>
+                                                  : strided_tiles64_kernel<kSrc, kDst, kCopy, uint64_t>;
+          return launch(tiles64, dim3(grid64), dim3(256), 0, stream, static_cast<const unsigned char *>(in), static_cast<Out *>(out),
+                        batches, view, plan);
+        }
+      }
       const uint64_t units = batches * ((inner + 31) / 32) * ((across + 31) / 32);
       const unsigned tile_grid = clamp_grid(units, static_cast<uint64_t>(sm_count()) * kCtasPerSm);
       auto tiles = units <= 0xffffffffull ? strided_tiles_kernel<Word, kSrc, kDst, kCopy, uint32_t>

@@ -12,9 +12,10 @@
 // The operator's contract leaves the draw algorithm and the floating math to each backend ("selected
 // IDs need not match across backends"); what is fixed is the uniform above, that -inf has zero mass,
 // that a row with NaN, +inf or no finite value is rejected, and the optional output
-// log p = x[selected] - max - log(total).  Here: one CTA per row, three passes over the row (the
-// second and third hit L2: a 151 936-wide f32 row is 608 KB), f32 weights 2^((x - max) log2e) added
-// in f64, fixed reduction orders: a row's result does not depend on the other rows, the grid or the run.
+// log p = x[selected] - max - log(total).  Here: one CTA per row, the row read from HBM once (maximum,
+// validity and weight sums together), then 1/16 of it again from L2 to locate the draw; f32 weights
+// 2^(x log2e - shift) added in f64, fixed reduction orders: a row's result does not depend on the other
+// rows, the grid or the run.
 #include "common.cuh"
 
 #include <math_constants.h>
@@ -23,6 +24,14 @@ namespace hb {
 namespace {
 
 // ---- Philox-4x32-10 ------------------------------------------------------------------------------
+// The counter-based generator of Salmon, Moraes, Dror and Shaw, "Parallel random numbers: as easy as
+// 1, 2, 3" (SC'11).  The round function, its multipliers (0xD2511F53, 0xCD9E8D57) and its key increments
+// (0x9E3779B9, 0xBB67AE85) are those of the Random123 library, v1.14.0, Copyright 2010-2012
+// D. E. Shaw Research, distributed under the BSD 3-Clause license (redistributions must retain that
+// copyright notice, the list of conditions and the disclaimer of the Random123 LICENSE file).  The
+// operator demands bit equality with the reference's generator
+// (third_party/random123_counter/philox.h), so the arithmetic below is necessarily the published one;
+// ten rounds, the counter in words 0-1, the identity's words 2-3 beside it and words 0-1 as the key.
 struct Words {
   uint32_t x0, x1, x2, x3;
 };
@@ -67,12 +76,14 @@ random_bits_kernel(const uint32_t *__restrict__ identities, uint32_t *out, uint6
 }
 
 // ---- Categorical ---------------------------------------------------------------------------------
-// One CTA of 1024 threads per SM: 148 rows (90 MB of f32 logits at 151 936 columns) in flight, which
-// stays inside the 126 MB of L2 between the passes; twice as many rows in flight do not (measured:
-// DRAM traffic of two passes instead of one).
-constexpr int kDrawThreads = 1024;
+// Two CTAs of 512 threads per SM, a row each: while one CTA waits for its loads the other computes, and
+// 296 rows are in flight at once (a batch of 256 rows is one wave).  The row is read from HBM once; the
+// second pass re-reads 1/16 of it (one warp's run), which is in L2.
+constexpr int kDrawThreads = 512;
+constexpr int kDrawCtasPerSm = 2;
 constexpr int kDrawWarps = kDrawThreads / 32;
 constexpr uint32_t kDrawMaxChunks = 1024;  // chunk totals of one run kept in shared memory (rows up to 524 288 wide)
+static_assert(kDrawThreads / 32 * kDrawMaxChunks * 32 == 524288, "the shared table covers the documented row width");
 
 template <int kDtype>
 __device__ __forceinline__ float load_logit(const void *row, uint32_t i) {
@@ -97,19 +108,19 @@ __device__ __forceinline__ float weight_of(float x, float neg_scaled_max) {
   return r;
 }
 
-// One CTA per row, a warp owns a contiguous run of the row (coalesced loads, 32 elements per step).
-//   pass 1  maximum and validity
-//   pass 2  warp totals of the weights: per-lane f64 sums, one fixed tree per warp; thread 0 chains
-//           the 32 totals -> the threshold total * u falls into one warp's span
-//   pass 3  all warps form the chunk totals of that run (32 elements each, fixed tree); warp 0 chains
-//           them in f64 to the chunk where the cumulative weight first exceeds the threshold and
-//           scans the 32 elements of that chunk.
-// Pass 2 and pass 3 add the same weights in different orders, so when the threshold lies within
+// One CTA per row, a warp owns a contiguous run of the row (coalesced loads).
+//   pass 1  maximum, validity and the weight sums in ONE read of the row ("online": running maximum
+//           per lane, sums rescaled when it grows; lanes -> warp -> row in f64 with fixed trees);
+//           thread 0 chains the 32 warp totals -> the threshold total * u falls into one warp's span
+//   pass 2  (1/32 of the row, from L2) all warps form the chunk totals of that run (32 elements each,
+//           fixed tree); warp 0 chains them in f64 to the chunk where the cumulative weight first
+//           exceeds the threshold and scans the 32 elements of that chunk.
+// Pass 1 and pass 2 add the same weights in different orders, so when the threshold lies within
 // rounding of a boundary the walk can end without a crossing; the draw then is the next element
 // of positive mass (what exact arithmetic would give), or, at the very end of the row, the last
 // index holding the maximum (src/compute_provider_native/sampling.cc:171-176).
 template <int kDtype>
-__global__ void __launch_bounds__(kDrawThreads, 1)
+__global__ void __launch_bounds__(kDrawThreads, kDrawCtasPerSm)
 categorical_kernel(const void *logits, const uint32_t *__restrict__ identities, int32_t *index_out, float *log_probability,
                    uint64_t rows, uint32_t cols, uint32_t *status_word) {
   grid_dependency_sync();
@@ -129,32 +140,75 @@ categorical_kernel(const void *logits, const uint32_t *__restrict__ identities, 
 
   for (uint64_t row = blockIdx.x; row < rows; row += gridDim.x) {
     const void *x = static_cast<const unsigned char *>(logits) + row * cols * kWidth;
-    // pass 1: maximum; NaN or +inf anywhere makes the row invalid
-    float maximum = -CUDART_INF_F;
+    // pass 1 (the only read of the row from HBM): maximum, validity AND the weight sums, "online".  A lane
+    // sums 2^(x log2 e - s) against its own shift s = ceil(log2 e x running maximum) and rescales when the
+    // maximum grows.  The shifts are INTEGERS, so every rescaling (lane, lane -> warp, warp -> row) is an
+    // exact power of two: no lane's weights carry a rounding of their own shift, which would move the
+    // threshold by parts in 10^7 and the draw with it.  Four 16-byte loads are in flight per lane.
+    constexpr float kLog2e = 1.4426950408889634f;
+    float lane_max = -CUDART_INF_F, lane_shift = 0.0f;
+    double lane_sum = 0.0;
     uint32_t bad = 0;
-    // f32 rows whose start is 16-byte aligned are read as float4 in passes 1 and 2 (neither depends
-    // on the order of the elements inside a warp's run); runs start at multiples of 32 elements
+    auto rescale = [](double value, float from_shift, float to_shift) {  // value * 2^(from - to), to >= from
+      return scalbn(value, static_cast<int>(fmaxf(from_shift - to_shift, -4000.0f)));
+    };
+    auto absorb = [&](const float (&v)[4]) {
+      const float high = fmaxf(fmaxf(v[0], v[1]), fmaxf(v[2], v[3]));
+      // NaN: fminf / fmaxf drop it, so test the sum (inf - inf cannot occur: +inf is rejected anyway)
+      const float probe = (v[0] + v[1]) + (v[2] + v[3]);
+      bad |= (probe != probe || high == CUDART_INF_F) ? 1u : 0u;
+      if (high > lane_max && high < CUDART_INF_F) {
+        const float shift = ceilf(__fmul_rn(high, kLog2e));
+        lane_sum = lane_max > -CUDART_INF_F ? rescale(lane_sum, lane_shift, shift) : 0.0;
+        lane_max = high;
+        lane_shift = shift;
+      }
+      if (lane_max > -CUDART_INF_F) {
+        const float minus = -lane_shift;
+        // four weights are added in f32 (a rounding of 6e-8 of their sum, unbiased), the running sum is f64
+        lane_sum += static_cast<double>((weight_of(v[0], minus) + weight_of(v[1], minus)) + (weight_of(v[2], minus) + weight_of(v[3], minus)));
+      }
+    };
+    // f32 rows whose start is 16-byte aligned are read as float4 (the sums do not depend on the order of
+    // the elements inside a warp's run); runs start at multiples of 32 elements
     const bool vectors = kDtype == HYLE_B200_F32 && (reinterpret_cast<uintptr_t>(x) & 15) == 0;
     const uint32_t vector_end = vectors ? begin + (end - begin) / 4 * 4 : begin;
-    for (uint32_t i = begin + 4 * lane; i < vector_end; i += 128) {
-      const float4 v = *reinterpret_cast<const float4 *>(static_cast<const float *>(x) + i);
-      const float high = fmaxf(fmaxf(v.x, v.y), fmaxf(v.z, v.w));
-      // NaN: fminf / fmaxf drop it, so test the sum (inf - inf cannot occur: +inf is rejected anyway)
-      const float probe = (v.x + v.y) + (v.z + v.w);
-      bad |= (probe != probe || high == CUDART_INF_F) ? 1u : 0u;
-      maximum = fmaxf(maximum, high);
+    {
+      const float *row_values = static_cast<const float *>(x);
+      uint32_t i = begin + 4 * lane;
+      for (; i + 3 * 128 < vector_end; i += 4 * 128) {
+        float4 q[4];
+#pragma unroll
+        for (int k = 0; k < 4; ++k) q[k] = *reinterpret_cast<const float4 *>(row_values + i + k * 128);
+#pragma unroll
+        for (int k = 0; k < 4; ++k) {
+          const float v[4] = {q[k].x, q[k].y, q[k].z, q[k].w};
+          absorb(v);
+        }
+      }
+      for (; i < vector_end; i += 128) {
+        const float4 q = *reinterpret_cast<const float4 *>(row_values + i);
+        const float v[4] = {q.x, q.y, q.z, q.w};
+        absorb(v);
+      }
     }
     for (uint32_t i = vector_end + lane; i < end; i += 32) {
-      const float v = load_logit<kDtype>(x, i);
-      bad |= (v != v || v == CUDART_INF_F) ? 1u : 0u;
-      maximum = fmaxf(maximum, v);
+      const float one = load_logit<kDtype>(x, i);
+      const float v[4] = {one, -CUDART_INF_F, -CUDART_INF_F, -CUDART_INF_F};  // -inf: weight 0, no effect on max or probe
+      absorb(v);
     }
+    float maximum = lane_max;
 #pragma unroll
     for (int o = 16; o > 0; o >>= 1) maximum = fmaxf(maximum, __shfl_xor_sync(kFullMask, maximum, o));
     bad = __any_sync(kFullMask, bad != 0) ? 1u : 0u;
+    // lanes -> warp: against the warp's shift, one fixed tree per warp
+    const float warp_shift = ceilf(__fmul_rn(maximum, kLog2e));
+    double sum = lane_max > -CUDART_INF_F && maximum < CUDART_INF_F ? rescale(lane_sum, lane_shift, warp_shift) : 0.0;
+    sum = warp_sum(sum);
     if (lane == 0) {
       s_max[warp] = maximum;
       s_bad[warp] = bad;
+      s_sum[warp] = sum;
     }
     __syncthreads();
     maximum = s_max[0];
@@ -173,23 +227,16 @@ categorical_kernel(const void *logits, const uint32_t *__restrict__ identities, 
       __syncthreads();
       continue;
     }
-    const float neg_scaled_max = -__fmul_rn(maximum, 1.4426950408889634f);
-    // pass 2
-    double sum = 0.0;
-    for (uint32_t i = begin + 4 * lane; i < vector_end; i += 128) {
-      const float4 v = *reinterpret_cast<const float4 *>(static_cast<const float *>(x) + i);
-      sum += (static_cast<double>(weight_of(v.x, neg_scaled_max)) + static_cast<double>(weight_of(v.y, neg_scaled_max))) +
-             (static_cast<double>(weight_of(v.z, neg_scaled_max)) + static_cast<double>(weight_of(v.w, neg_scaled_max)));
-    }
-    for (uint32_t i = vector_end + lane; i < end; i += 32) sum += static_cast<double>(weight_of(load_logit<kDtype>(x, i), neg_scaled_max));
-    sum = warp_sum(sum);
-    if (lane == 0) s_sum[warp] = sum;
-    __syncthreads();
+    // every weight from here on is 2^(x log2 e - row_shift); the common factor cancels in the draw and
+    // is put back into the log-probability below
+    const float row_shift = ceilf(__fmul_rn(maximum, kLog2e));
+    const float neg_scaled_max = -row_shift;
     if (t == 0) {
+      // thread 0 chains the warp totals, each brought (exactly) to the row's shift
       double running = 0.0;
       for (int w = 0; w < kDrawWarps; ++w) {
         s_before[w] = running;
-        running += s_sum[w];
+        if (s_max[w] > -CUDART_INF_F) running += rescale(s_sum[w], ceilf(__fmul_rn(s_max[w], kLog2e)), row_shift);
       }
       s_before[kDrawWarps] = running;
       s_selected = -1;
@@ -203,7 +250,7 @@ categorical_kernel(const void *logits, const uint32_t *__restrict__ identities, 
     const double uniform =
         (static_cast<double>(random.x0) * 1048576.0 + static_cast<double>(random.x1 >> 12) + 0.5) * 2.220446049250313e-16;
     const double threshold = total * uniform;
-    // pass 3: the run whose span of the cumulative sum holds the threshold.  Every thread finds the
+    // pass 2: the run whose span of the cumulative sum holds the threshold.  Every thread finds the
     // owner from the same shared values, so the choice is CTA-uniform.
     int owner = kDrawWarps - 1;
 #pragma unroll
@@ -300,8 +347,9 @@ categorical_kernel(const void *logits, const uint32_t *__restrict__ identities, 
       const int32_t selected = s_selected;
       index_out[row] = selected;
       if (log_probability != nullptr)
+        // log p = x - log(sum e^x), and sum e^x = total * 2^row_shift
         log_probability[row] = static_cast<float>(static_cast<double>(load_logit<kDtype>(x, static_cast<uint32_t>(selected))) -
-                                                  static_cast<double>(maximum) - log(total));
+                                                  (log(total) + static_cast<double>(row_shift) * 0.6931471805599453));
     }
     __syncthreads();  // shared scratch is reused by the next row
   }
@@ -331,7 +379,7 @@ extern "C" int hyle_b200_categorical(hyle_b200_stream_t stream, int dtype, const
   if (log_weights == nullptr || identities == nullptr || index_out == nullptr || cols == 0 || cols > 0x7fffffffull)
     return HYLE_B200_INVALID_VALUE;
   auto s = reinterpret_cast<cudaStream_t>(stream);
-  const unsigned grid = clamp_grid(rows, static_cast<uint64_t>(sm_count()));  // one CTA per SM
+  const unsigned grid = clamp_grid(rows, static_cast<uint64_t>(sm_count()) * kDrawCtasPerSm);
   const uint32_t width = static_cast<uint32_t>(cols);
   if (dtype == HYLE_B200_F32)
     return launch(categorical_kernel<HYLE_B200_F32>, dim3(grid), dim3(kDrawThreads), 0, s, log_weights, identities, index_out,

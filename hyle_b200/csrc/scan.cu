@@ -1,14 +1,22 @@
 // Scan{axis = -1, exclusive}: prefix sums along the rows of a dense [rows, cols] tensor
 // (include/hyle/compute/operation.h:314-321; CPU route src/compute_provider_ggml/standard_index.cc:113-157).
 //   f32: float accumulation; the operator permits reassociation, so the blocked order below is allowed.
-//   i32: int64 accumulation; when any inclusive prefix (the final total included, also for an exclusive
-//        scan) leaves the int32 range the call reports it and writes NO output, as the reference does.
+//   i32: when any inclusive prefix (the final total included, also for an exclusive scan) leaves the
+//        int32 range the call reports it and writes NO output, as the reference does.  That takes a
+//        decision about the whole tensor before the first store, i.e. two kernels.  The first one only
+//        decides: per row the sum of magnitudes (a plain reduction, loads marked evict-last so that the
+//        row stays in L2); a row whose magnitudes sum to at most INT32_MAX cannot overflow, any other
+//        row (rare) is checked exactly by its CTA.  The second one is the f32 scan's walk on 32-bit
+//        integers with wrap-around arithmetic: every prefix is known to fit, so sums modulo 2^32 are
+//        the true values, and its loads hit L2.
 //
 // HBM-bound: 8 bytes per value.  One CTA walks a row in chunks of 4 values per thread with the row's
 // running total carried in a register; the (row, chunk) steps of a CTA form one sequence and the loads
 // of the next step are issued before the current one is combined, so a chunk's shuffles and its single
 // barrier hide behind the next chunk's memory latency.  Many short rows take 256-thread CTAs (eight
 // per SM), few long rows 1024-thread CTAs (two per SM).
+#include <type_traits>
+
 #include "common.cuh"
 
 namespace hb {
@@ -67,14 +75,157 @@ __device__ __forceinline__ Acc warp_inclusive(Acc value, unsigned lane) {
   return value;
 }
 
-// kWrite = false is the checking pass of the i32 scan: the same walk, nothing stored.
+__device__ __forceinline__ uint64_t scan_policy_evict_last() {
+  uint64_t policy;
+  asm volatile("createpolicy.fractional.L2::evict_last.b64 %0, 1.0;" : "=l"(policy));
+  return policy;
+}
+__device__ __forceinline__ int4 load_keep(const int4 *p, uint64_t policy) {
+  int4 v;
+  asm volatile("ld.global.nc.L1::no_allocate.L2::cache_hint.v4.s32 {%0, %1, %2, %3}, [%4], %5;"
+               : "=r"(v.x), "=r"(v.y), "=r"(v.z), "=r"(v.w)
+               : "l"(p), "l"(policy));
+  return v;
+}
+__device__ __forceinline__ unsigned long long magnitude(int32_t v) {
+  return static_cast<unsigned long long>(v < 0 ? 0u - static_cast<uint32_t>(v) : static_cast<uint32_t>(v));
+}
+
+// The deciding pass of the checked i32 scan.  CTA per row (grid-stride): sum of magnitudes; above
+// INT32_MAX the CTA checks the row's prefixes exactly (each thread a contiguous segment: its sum and
+// the extremes of its running sum, then the segments in order).
+constexpr int kCheckThreads = 256;
+template <bool kVector>
+__global__ void __launch_bounds__(kCheckThreads)
+scan_i32_check_kernel(const int32_t *__restrict__ in, uint64_t rows, uint64_t cols, unsigned *status) {
+  grid_dependency_sync();
+  constexpr int kWarps = kCheckThreads / kWarpSize;
+  __shared__ unsigned long long s_warp[kWarps];
+  __shared__ long long s_sum[kCheckThreads], s_low[kCheckThreads], s_high[kCheckThreads];
+  __shared__ int s_exact;
+  const unsigned lane = threadIdx.x % kWarpSize, warp = threadIdx.x / kWarpSize;
+  const uint64_t policy = scan_policy_evict_last();
+  bool bad = false;
+  for (uint64_t row = blockIdx.x; row < rows; row += gridDim.x) {
+    const int32_t *values = in + row * cols;
+    unsigned long long total = 0;
+    if constexpr (kVector) {
+      const int4 *vectors = reinterpret_cast<const int4 *>(values);
+      const uint64_t count = cols / 4;
+      uint64_t v = threadIdx.x;
+      for (; v + 3 * kCheckThreads < count; v += 4 * kCheckThreads) {
+        int4 q[4];
+#pragma unroll
+        for (int k = 0; k < 4; ++k) q[k] = load_keep(vectors + v + k * kCheckThreads, policy);
+#pragma unroll
+        for (int k = 0; k < 4; ++k) total += magnitude(q[k].x) + magnitude(q[k].y) + magnitude(q[k].z) + magnitude(q[k].w);
+      }
+      for (; v < count; v += kCheckThreads) {
+        const int4 q = load_keep(vectors + v, policy);
+        total += magnitude(q.x) + magnitude(q.y) + magnitude(q.z) + magnitude(q.w);
+      }
+    } else {
+      for (uint64_t i = threadIdx.x; i < cols; i += kCheckThreads) total += magnitude(values[i]);
+    }
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) total += __shfl_xor_sync(kFullMask, total, o);
+    if (lane == 0) s_warp[warp] = total;
+    __syncthreads();
+    if (threadIdx.x == 0) {
+      unsigned long long all = 0;
+      for (int w = 0; w < kWarps; ++w) all += s_warp[w];
+      s_exact = all > static_cast<unsigned long long>(INT32_MAX);
+    }
+    __syncthreads();
+    if (s_exact) {  // rare: the magnitudes alone do not rule an overflow out
+      const uint64_t segment = (cols + kCheckThreads - 1) / kCheckThreads;
+      const uint64_t begin = min(threadIdx.x * segment, cols), end = min(begin + segment, cols);
+      long long sum = 0, low = 0, high = 0;  // extremes of the running sum inside the segment (0 = before it)
+      for (uint64_t i = begin; i < end; ++i) {
+        sum += values[i];
+        low = sum < low ? sum : low;
+        high = sum > high ? sum : high;
+      }
+      s_sum[threadIdx.x] = sum, s_low[threadIdx.x] = low, s_high[threadIdx.x] = high;
+      __syncthreads();
+      if (threadIdx.x == 0) {
+        long long base = 0;
+        for (int t = 0; t < kCheckThreads; ++t) {
+          if (base + s_low[t] < static_cast<long long>(INT32_MIN) || base + s_high[t] > static_cast<long long>(INT32_MAX)) bad = true;
+          base += s_sum[t];
+        }
+      }
+    }
+    __syncthreads();  // the shared arrays are reused by the next row
+  }
+  if (bad) atomicOr(status, kScanOverflow);
+}
+
+// The same decision with a WARP per row, for rows of at most 16384 values: no barrier at all, eight
+// 16-byte loads in flight per lane.  The exact check of a suspicious row is done by its warp: each lane
+// a contiguous segment, the segments chained by shuffles.
+template <bool kVector>
+__global__ void __launch_bounds__(kCheckThreads)
+scan_i32_check_warp_kernel(const int32_t *__restrict__ in, uint64_t rows, uint32_t cols, unsigned *status) {
+  grid_dependency_sync();
+  const unsigned lane = threadIdx.x % kWarpSize;
+  const uint64_t warps = static_cast<uint64_t>(gridDim.x) * (kCheckThreads / kWarpSize);
+  const uint64_t policy = scan_policy_evict_last();
+  bool bad = false;
+  for (uint64_t row = static_cast<uint64_t>(blockIdx.x) * (kCheckThreads / kWarpSize) + threadIdx.x / kWarpSize; row < rows;
+       row += warps) {
+    const int32_t *values = in + row * cols;
+    unsigned long long total = 0;
+    if constexpr (kVector) {
+      const int4 *vectors = reinterpret_cast<const int4 *>(values);
+      const uint32_t count = cols / 4;
+      uint32_t v = lane;
+      for (; v + 7 * kWarpSize < count; v += 8 * kWarpSize) {
+        int4 q[8];
+#pragma unroll
+        for (int k = 0; k < 8; ++k) q[k] = load_keep(vectors + v + k * kWarpSize, policy);
+#pragma unroll
+        for (int k = 0; k < 8; ++k) total += magnitude(q[k].x) + magnitude(q[k].y) + magnitude(q[k].z) + magnitude(q[k].w);
+      }
+      for (; v < count; v += kWarpSize) {
+        const int4 q = load_keep(vectors + v, policy);
+        total += magnitude(q.x) + magnitude(q.y) + magnitude(q.z) + magnitude(q.w);
+      }
+    } else {
+      for (uint32_t i = lane; i < cols; i += kWarpSize) total += magnitude(values[i]);
+    }
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) total += __shfl_xor_sync(kFullMask, total, o);
+    if (total > static_cast<unsigned long long>(INT32_MAX)) {  // warp-uniform, rare
+      const uint32_t segment = (cols + kWarpSize - 1) / kWarpSize;
+      const uint32_t begin = min(lane * segment, cols), end = min(begin + segment, cols);
+      long long sum = 0, low = 0, high = 0;
+      for (uint32_t i = begin; i < end; ++i) {
+        sum += values[i];
+        low = sum < low ? sum : low;
+        high = sum > high ? sum : high;
+      }
+      long long base = sum;  // exclusive prefix of the segment sums, lane by lane
+#pragma unroll
+      for (int step = 1; step < kWarpSize; step <<= 1) {
+        const long long below = __shfl_up_sync(kFullMask, base, step);
+        if (lane >= static_cast<unsigned>(step)) base += below;
+      }
+      base -= sum;
+      bad |= base + low < static_cast<long long>(INT32_MIN) || base + high > static_cast<long long>(INT32_MAX);
+    }
+  }
+  if (__any_sync(kFullMask, bad) && lane == 0) atomicOr(status, kScanOverflow);
+}
+
+// kWrite = false walks without storing (kept for the checking instantiation of wide accumulators).
 template <class T, class Acc, int kThreads, bool kVector, bool kWrite>
 __global__ void __launch_bounds__(kThreads)
 scan_rows_kernel(const T *__restrict__ in, T *__restrict__ out, uint64_t rows, uint64_t cols, int exclusive, unsigned *status) {
   grid_dependency_sync();
   constexpr int kWarps = kThreads / kWarpSize;
   constexpr uint64_t kChunk = static_cast<uint64_t>(kThreads) * 4;
-  constexpr bool kChecked = sizeof(Acc) == 8;  // the integer scan
+  constexpr bool kChecked = !std::is_same<T, float>::value;  // the integer scan: decided by the pass before
   __shared__ Acc s_total[2][kWarps];
   if constexpr (kChecked && kWrite) {
     if ((*reinterpret_cast<volatile unsigned *>(status) & kScanOverflow) != 0) return;  // the check failed: no output
@@ -113,11 +264,11 @@ scan_rows_kernel(const T *__restrict__ in, T *__restrict__ out, uint64_t rows, u
     const Acc before_lane = lane == 0 ? Acc(0) : through_previous_lane;
     const Acc base = carry + (before_warp + before_lane);
     carry += chunk_total;
-    if constexpr (kChecked) {
+    if constexpr (kChecked && !kWrite) {
 #pragma unroll
       for (int k = 0; k < 4; ++k) {
-        const Acc value = base + p[k];
-        bad |= value < Acc(INT32_MIN) || value > Acc(INT32_MAX);
+        const long long value = static_cast<long long>(base + p[k]);
+        bad |= value < static_cast<long long>(INT32_MIN) || value > static_cast<long long>(INT32_MAX);
       }
     }
     if constexpr (kWrite) {
@@ -175,9 +326,24 @@ extern "C" int hyle_b200_scan(hyle_b200_stream_t stream, int dtype, const void *
   if (dtype == HYLE_B200_F32)
     return dispatch_scan<float, float, true>(s, static_cast<const float *>(in), static_cast<float *>(out), rows, cols, exclusive,
                                              status_word);
-  const int checked = dispatch_scan<int32_t, long long, false>(s, static_cast<const int32_t *>(in), static_cast<int32_t *>(out),
-                                                               rows, cols, exclusive, status_word);
+  // pass 1 decides (and leaves the rows in L2), pass 2 scans modulo 2^32 and writes unless pass 1 objected
+  const bool vector = cols % 4 == 0 && aligned_to(in, 16);
+  const unsigned grid = clamp_grid(rows, static_cast<uint64_t>(sm_count()) * 8);
+  int checked;
+  if (cols <= 16384 && rows >= static_cast<uint64_t>(sm_count()) * 8) {  // many short rows: a warp each
+    const unsigned warp_grid = clamp_grid((rows + kCheckThreads / kWarpSize - 1) / (kCheckThreads / kWarpSize),
+                                          static_cast<uint64_t>(sm_count()) * 8);
+    checked = vector ? launch(scan_i32_check_warp_kernel<true>, dim3(warp_grid), dim3(kCheckThreads), 0, s,
+                              static_cast<const int32_t *>(in), rows, static_cast<uint32_t>(cols), status_word)
+                     : launch(scan_i32_check_warp_kernel<false>, dim3(warp_grid), dim3(kCheckThreads), 0, s,
+                              static_cast<const int32_t *>(in), rows, static_cast<uint32_t>(cols), status_word);
+  } else {
+    checked = vector ? launch(scan_i32_check_kernel<true>, dim3(grid), dim3(kCheckThreads), 0, s,
+                              static_cast<const int32_t *>(in), rows, cols, status_word)
+                     : launch(scan_i32_check_kernel<false>, dim3(grid), dim3(kCheckThreads), 0, s,
+                              static_cast<const int32_t *>(in), rows, cols, status_word);
+  }
   if (checked != HYLE_B200_OK) return checked;
-  return dispatch_scan<int32_t, long long, true>(s, static_cast<const int32_t *>(in), static_cast<int32_t *>(out), rows, cols,
+  return dispatch_scan<uint32_t, uint32_t, true>(s, static_cast<const uint32_t *>(in), static_cast<uint32_t *>(out), rows, cols,
                                                  exclusive, status_word);
 }

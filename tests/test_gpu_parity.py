@@ -680,6 +680,33 @@ def test_fp8_cache_encode(oracle, dtype):
         assert int(status.item()) == abi.STATUS_INVALID_FP8_INPUT == want_status
 
 
+def test_fp8_cache_encode_at_every_rounding_boundary(oracle):
+    """The kernel multiplies by the reciprocal of the scale and divides only when the product is within
+    2^-21 of a rounding boundary of E4M3.  Inputs placed on and next to every boundary (midpoints of
+    neighbouring E4M3 values, times the scale, and their f32 neighbours) must give the bytes of the division;
+    so must scales whose reciprocal is not a normal number (every element then takes the division)."""
+    codes = np.arange(0, 127, dtype=np.uint8)                       # the non-negative finite codes, ascending
+    values = oracle.cast(ob.E4M3, ob.F32, codes).astype(np.float64)
+    midpoints = (values[:-1] + values[1:]) / 2
+    for scale in (1.0, 0.37, 3.0, 1.0 / 3.0, 1e-3, 417.25, 1e-39, 3e38):
+        with np.errstate(over="ignore", under="ignore"):
+            centre = (np.concatenate([midpoints, values]) * np.float64(np.float32(scale))).astype(np.float32)
+        cases = [centre]
+        for direction in (np.float32(np.inf), np.float32(-np.inf)):
+            step = centre
+            for _ in range(3):
+                step = np.nextafter(step, direction)
+                cases.append(step)
+        x = np.concatenate(cases + [-c for c in cases])
+        x = x[np.isfinite(x)]
+        x = np.concatenate([x, np.zeros((-x.size) % 8, np.float32)])
+        want, want_status = oracle.fp8_e4m3_encode(ob.F32, x, scale)
+        status = torch.zeros(1, dtype=torch.int32, device=DEV)
+        got = ops.fp8_e4m3_encode(to_dev(x), scale, status).cpu().numpy()
+        assert np.array_equal(got, want), scale
+        assert int(status.item()) == want_status == 0
+
+
 # ---- sampling --------------------------------------------------------------------------------------------------------------
 def _identities(rng, rows):
     return rng.integers(0, 2 ** 32, (rows, 4), dtype=np.uint64).astype(np.uint32)

@@ -98,6 +98,37 @@ def test_scan_i32(oracle, rows, cols, exclusive):
 
 
 @pytest.mark.gpu
+@pytest.mark.parametrize("rows,cols", [(37, 4100), (1300, 1024), (1250, 130)])
+def test_scan_i32_rows_whose_magnitudes_exceed_int32_but_whose_prefixes_fit(oracle, rows, cols):
+    """The deciding pass first sums magnitudes; rows that fail that cheap test are checked exactly.  Swinging
+    rows (prefixes between INT32_MIN and INT32_MAX although the magnitudes sum far above) must be scanned, and
+    the scan's wrap-around arithmetic must give the true values, including both extremes."""
+    rng = np.random.default_rng(9)
+    n = rng.integers(-3, 4, (rows, cols)).astype(np.int64)
+    n[:, 10::50] = 2 ** 30
+    n[:, 35::50] = -(2 ** 30)
+    n[5, :] = 0
+    n[5, 0], n[5, 1], n[5, 2], n[5, 3] = 2 ** 31 - 1, -(2 ** 31 - 1), -(2 ** 31), 2 ** 31 - 1   # touches both ends of the range
+    n = n.astype(np.int32)
+    for exclusive in (False, True):
+        want, want_status = oracle.scan(n, exclusive)
+        assert want_status == 0
+        status = torch.zeros(1, dtype=torch.int32, device="cuda")
+        got = ops.scan(torch.from_numpy(n).cuda(), exclusive, status).cpu().numpy()
+        assert int(status.item()) == 0 and np.array_equal(got, want)
+    # one step further and the same row overflows: caught by the exact check, nothing written
+    n[5, 1] = 1   # 2^31 - 1, then + 1
+    _, want_status = oracle.scan(n)
+    assert want_status == 16
+    status = torch.zeros(1, dtype=torch.int32, device="cuda")
+    out = ops.new_output(n.shape, torch.int32).fill_(-7)
+    assert abi.load().hyle_b200_scan(torch.cuda.current_stream().cuda_stream, abi.I32, torch.from_numpy(n).cuda().data_ptr(),
+                                     out.data_ptr(), rows, cols, 0, status.data_ptr()) == abi.OK
+    torch.cuda.synchronize()
+    assert int(status.item()) == abi.STATUS_SCAN_OVERFLOW and bool((out == -7).all())
+
+
+@pytest.mark.gpu
 def test_scan_i32_overflow_reports_and_writes_nothing(oracle):
     library = abi.load()
     stream = torch.cuda.current_stream().cuda_stream
