@@ -345,6 +345,274 @@ int launch_rms(cudaStream_t stream, const void *x, const void *residual, const v
   return launch_status;
 }
 
+// ------------------------------------------------------------------------------------------------
+// RmsNorm on f16 and f32 rows (the other two storages of the CPU route,
+// src/compute_provider_native/normalization.cc:41-80,219-234): the same formula with the storage's own
+// load and a single rounding at the store; the weight has the row's type or is f32.
+// Rows of at most 8 KB: one warp per row, second read from L1.  Longer rows: one CTA per row, the row
+// staged in shared memory in its own storage.
+// ------------------------------------------------------------------------------------------------
+template <int kDtype>
+struct Stored {
+  static constexpr int kBytes = kDtype == HYLE_B200_F32 ? 4 : 2;
+  static __device__ __forceinline__ float load1(const void *base, uint64_t i) {
+    if constexpr (kDtype == HYLE_B200_F32) return static_cast<const float *>(base)[i];
+    else if constexpr (kDtype == HYLE_B200_BF16) return bf16_to_f32(static_cast<const unsigned short *>(base)[i]);
+    else return f16_to_f32(static_cast<const unsigned short *>(base)[i]);
+  }
+  static __device__ __forceinline__ void store1(void *base, uint64_t i, float v) {
+    if constexpr (kDtype == HYLE_B200_F32) static_cast<float *>(base)[i] = v;
+    else if constexpr (kDtype == HYLE_B200_BF16) static_cast<unsigned short *>(base)[i] = f32_to_bf16(v);
+    else static_cast<unsigned short *>(base)[i] = f32_to_f16(v);
+  }
+  // eight consecutive elements starting at element 8 * vec (16-byte aligned storage)
+  static __device__ __forceinline__ void load8(const void *base, uint64_t vec, float (&v)[8]) {
+    if constexpr (kDtype == HYLE_B200_F32) {
+      const float4 a = static_cast<const float4 *>(base)[2 * vec], b = static_cast<const float4 *>(base)[2 * vec + 1];
+      v[0] = a.x, v[1] = a.y, v[2] = a.z, v[3] = a.w, v[4] = b.x, v[5] = b.y, v[6] = b.z, v[7] = b.w;
+    } else {
+      const uint4 w = static_cast<const uint4 *>(base)[vec];
+      const uint32_t words[4] = {w.x, w.y, w.z, w.w};
+#pragma unroll
+      for (int e = 0; e < 8; ++e) {
+        const unsigned short narrow = static_cast<unsigned short>(e & 1 ? words[e / 2] >> 16 : words[e / 2] & 0xffffu);
+        v[e] = kDtype == HYLE_B200_BF16 ? bf16_to_f32(narrow) : f16_to_f32(narrow);
+      }
+    }
+  }
+  static __device__ __forceinline__ void store8(void *base, uint64_t vec, const float (&v)[8]) {
+    if constexpr (kDtype == HYLE_B200_F32) {
+      static_cast<float4 *>(base)[2 * vec] = make_float4(v[0], v[1], v[2], v[3]);
+      static_cast<float4 *>(base)[2 * vec + 1] = make_float4(v[4], v[5], v[6], v[7]);
+    } else {
+      uint32_t words[4];
+#pragma unroll
+      for (int e = 0; e < 4; ++e)
+        words[e] = kDtype == HYLE_B200_BF16
+                       ? pack_bf16x2(v[2 * e], v[2 * e + 1])
+                       : static_cast<uint32_t>(f32_to_f16(v[2 * e])) | static_cast<uint32_t>(f32_to_f16(v[2 * e + 1])) << 16;
+      static_cast<uint4 *>(base)[vec] = make_uint4(words[0], words[1], words[2], words[3]);
+    }
+  }
+};
+
+// y[8] = (x[8] * inverse) * w[8]; kWeight: -1 none, else the weight's dtype
+template <int kWeight>
+__device__ __forceinline__ void scale8(float (&v)[8], float inverse, const void *weight, uint64_t vec) {
+#pragma unroll
+  for (int e = 0; e < 8; ++e) v[e] = __fmul_rn(v[e], inverse);
+  if constexpr (kWeight >= 0) {
+    float w[8];
+    Stored<kWeight>::load8(weight, vec, w);
+#pragma unroll
+    for (int e = 0; e < 8; ++e) v[e] = __fmul_rn(v[e], w[e]);
+  }
+}
+
+template <int kDtype, int kWeight, bool kVec>
+__global__ void __launch_bounds__(kThreads)
+rms_stored_warp_kernel(const void *x, const void *weight, void *y, uint64_t rows, uint32_t hidden, float eps) {
+  grid_dependency_sync();
+  const int lane = threadIdx.x & 31;
+  const uint64_t warps = static_cast<uint64_t>(gridDim.x) * (blockDim.x >> 5);
+  for (uint64_t row = static_cast<uint64_t>(blockIdx.x) * (blockDim.x >> 5) + (threadIdx.x >> 5); row < rows; row += warps) {
+    const char *in = static_cast<const char *>(x) + row * hidden * Stored<kDtype>::kBytes;
+    char *out = static_cast<char *>(y) + row * hidden * Stored<kDtype>::kBytes;
+    float ss = 0.0f;
+    if constexpr (kVec) {
+      for (uint32_t v = lane; v < hidden / 8; v += 32) {
+        float f[8];
+        Stored<kDtype>::load8(in, v, f);
+#pragma unroll
+        for (int e = 0; e < 8; ++e) ss = fmaf(f[e], f[e], ss);
+      }
+    } else {
+      for (uint32_t i = lane; i < hidden; i += 32) {
+        const float f = Stored<kDtype>::load1(in, i);
+        ss = fmaf(f, f, ss);
+      }
+    }
+    // every lane has read its part of the row before the sum is known: y may be x
+    const float inverse = inverse_rms(warp_sum(ss), hidden, eps);
+    if constexpr (kVec) {
+      for (uint32_t v = lane; v < hidden / 8; v += 32) {
+        float f[8];
+        Stored<kDtype>::load8(in, v, f);
+        scale8<kWeight>(f, inverse, weight, v);
+        Stored<kDtype>::store8(out, v, f);
+      }
+    } else {
+      for (uint32_t i = lane; i < hidden; i += 32) {
+        float f = __fmul_rn(Stored<kDtype>::load1(in, i), inverse);
+        if constexpr (kWeight >= 0) f = __fmul_rn(f, Stored<kWeight < 0 ? kDtype : kWeight>::load1(weight, i));
+        Stored<kDtype>::store1(out, i, f);
+      }
+    }
+  }
+}
+
+constexpr uint32_t kMaxStoredRowBytes = 64 * 1024;
+
+template <int kDtype, int kWeight, bool kVec>
+__global__ void __launch_bounds__(kThreads)
+rms_stored_cta_kernel(const void *x, const void *weight, void *y, uint64_t rows, uint32_t hidden, float eps) {
+  grid_dependency_sync();
+  extern __shared__ __align__(16) unsigned char staged_bytes[];
+  __shared__ float s_partial[2][kWarps];
+  const int t = threadIdx.x, lane = t & 31, warp = t >> 5;
+  int parity = 0;
+  for (uint64_t row = blockIdx.x; row < rows; row += gridDim.x, parity ^= 1) {
+    const char *in = static_cast<const char *>(x) + row * hidden * Stored<kDtype>::kBytes;
+    char *out = static_cast<char *>(y) + row * hidden * Stored<kDtype>::kBytes;
+    float ss = 0.0f;
+    if constexpr (kVec) {
+      for (uint32_t v = t; v < hidden / 8; v += kThreads) {
+        float f[8];
+        Stored<kDtype>::load8(in, v, f);
+        Stored<kDtype>::store8(staged_bytes, v, f);  // decode and encode are exact inverses: the stored bits
+#pragma unroll
+        for (int e = 0; e < 8; ++e) ss = fmaf(f[e], f[e], ss);
+      }
+    } else {
+      for (uint32_t i = t; i < hidden; i += kThreads) {
+        const float f = Stored<kDtype>::load1(in, i);
+        Stored<kDtype>::store1(staged_bytes, i, f);
+        ss = fmaf(f, f, ss);
+      }
+    }
+    ss = warp_sum(ss);
+    if (lane == 0) s_partial[parity][warp] = ss;
+    __syncthreads();  // also publishes the staged row
+    float total = s_partial[parity][0];
+#pragma unroll
+    for (int w = 1; w < kWarps; ++w) total = __fadd_rn(total, s_partial[parity][w]);
+    const float inverse = inverse_rms(total, hidden, eps);
+    if constexpr (kVec) {
+      for (uint32_t v = t; v < hidden / 8; v += kThreads) {
+        float f[8];
+        Stored<kDtype>::load8(staged_bytes, v, f);
+        scale8<kWeight>(f, inverse, weight, v);
+        Stored<kDtype>::store8(out, v, f);
+      }
+    } else {
+      for (uint32_t i = t; i < hidden; i += kThreads) {
+        float f = __fmul_rn(Stored<kDtype>::load1(staged_bytes, i), inverse);
+        if constexpr (kWeight >= 0) f = __fmul_rn(f, Stored<kWeight < 0 ? kDtype : kWeight>::load1(weight, i));
+        Stored<kDtype>::store1(out, i, f);
+      }
+    }
+    __syncthreads();  // the staged row is rewritten by the next iteration
+  }
+}
+
+template <int kDtype, int kWeight, bool kVec>
+int launch_rms_stored(cudaStream_t stream, const void *x, const void *weight, void *y, uint64_t rows, uint64_t hidden, float eps) {
+  const uint64_t row_bytes = hidden * Stored<kDtype>::kBytes;
+  const int sms = sm_count();
+  if (row_bytes <= 8 * 1024) {
+    const unsigned grid = clamp_grid((rows + kWarps - 1) / kWarps, static_cast<uint64_t>(sms) * 8);
+    return launch(rms_stored_warp_kernel<kDtype, kWeight, kVec>, dim3(grid), dim3(kThreads), 0, stream, x, weight, y, rows,
+                  static_cast<uint32_t>(hidden), eps);
+  }
+  if (row_bytes > kMaxStoredRowBytes) return HYLE_B200_NOT_SUPPORTED;
+  const size_t staged = (static_cast<size_t>(row_bytes) + 15) & ~static_cast<size_t>(15);
+  auto kernel = rms_stored_cta_kernel<kDtype, kWeight, kVec>;
+  if (staged > 48 * 1024) cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, static_cast<int>(kMaxStoredRowBytes));
+  return launch(kernel, dim3(clamp_grid(rows, static_cast<uint64_t>(sms) * 4)), dim3(kThreads), staged, stream, x, weight, y, rows,
+                static_cast<uint32_t>(hidden), eps);
+}
+
+template <int kDtype>
+int dispatch_rms_stored(cudaStream_t stream, const void *x, const void *weight, int weight_dtype, void *y, uint64_t rows,
+                        uint64_t hidden, float eps) {
+  if (rows == 0 || hidden == 0) return HYLE_B200_OK;
+  const int element = Stored<kDtype>::kBytes;
+  if (x == nullptr || y == nullptr || !aligned_to(x, element) || !aligned_to(y, element) ||
+      (weight != nullptr && weight_dtype != kDtype && weight_dtype != HYLE_B200_F32))
+    return HYLE_B200_INVALID_VALUE;
+  const bool vec = hidden % 8 == 0 && aligned_to(x, 16) && aligned_to(y, 16) && (weight == nullptr || aligned_to(weight, 16));
+  if (weight != nullptr && !aligned_to(weight, weight_dtype == HYLE_B200_F32 ? 4 : 2)) return HYLE_B200_INVALID_VALUE;
+  auto go = [&](auto weight_tag) {
+    constexpr int kWeight = decltype(weight_tag)::value;
+    return vec ? launch_rms_stored<kDtype, kWeight, true>(stream, x, weight, y, rows, hidden, eps)
+               : launch_rms_stored<kDtype, kWeight, false>(stream, x, weight, y, rows, hidden, eps);
+  };
+  if (weight == nullptr) return go(std::integral_constant<int, -1>{});
+  if (weight_dtype == HYLE_B200_F32) return go(std::integral_constant<int, HYLE_B200_F32>{});
+  return go(std::integral_constant<int, kDtype>{});
+}
+
+// ------------------------------------------------------------------------------------------------
+// Reduce{kMinimum | kMaximum} over the last axis of bf16 / f16 rows, the result in the rows' own type
+// (the narrow Min/Max the CPU route keeps, src/compute_provider_native/reduction.cc:203-223).  The
+// comparison runs on the exactly converted f32 values under the f32 kernel's rules (NaN wins, -0 < +0,
+// an empty row gives the identity), and an extremum converts back without rounding.
+// kCta: one CTA per row (long rows); else one warp per row.
+// ------------------------------------------------------------------------------------------------
+template <int kDtype, bool kMaximum, bool kVec, bool kCta>
+__global__ void __launch_bounds__(kThreads)
+narrow_extremum_kernel(const void *in, void *out, uint64_t rows, uint64_t cols) {
+  grid_dependency_sync();
+  __shared__ float s_partial[2][kWarps];
+  const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+  const uint32_t width = kCta ? kThreads : 32, position = kCta ? threadIdx.x : lane;
+  const uint64_t stride = kCta ? gridDim.x : static_cast<uint64_t>(gridDim.x) * kWarps;
+  auto combine = [](float a, float b) { return kMaximum ? max_nan(a, b) : min_nan(a, b); };
+  int parity = 0;
+  for (uint64_t row = kCta ? blockIdx.x : static_cast<uint64_t>(blockIdx.x) * kWarps + warp; row < rows; row += stride, parity ^= 1) {
+    const char *base = static_cast<const char *>(in) + row * cols * Stored<kDtype>::kBytes;
+    float best = kMaximum ? -CUDART_INF_F : CUDART_INF_F;
+    if constexpr (kVec) {
+      const uint64_t vectors = cols / 8;
+      uint64_t v = position;
+      for (; v + width < vectors; v += 2 * width) {  // two 16-byte loads in flight per thread
+        float a[8], b[8];
+        Stored<kDtype>::load8(base, v, a);
+        Stored<kDtype>::load8(base, v + width, b);
+#pragma unroll
+        for (int e = 0; e < 8; ++e) best = combine(best, combine(a[e], b[e]));
+      }
+      if (v < vectors) {
+        float a[8];
+        Stored<kDtype>::load8(base, v, a);
+#pragma unroll
+        for (int e = 0; e < 8; ++e) best = combine(best, a[e]);
+      }
+    } else {
+      for (uint64_t i = position; i < cols; i += width) best = combine(best, Stored<kDtype>::load1(base, i));
+    }
+    best = kMaximum ? warp_max_nan(best) : warp_min_nan(best);
+    if constexpr (kCta) {
+      if (lane == 0) s_partial[parity][warp] = best;
+      __syncthreads();  // double-buffered partials: one barrier per row
+      if (threadIdx.x == 0) {
+        float total = s_partial[parity][0];
+#pragma unroll
+        for (int w = 1; w < kWarps; ++w) total = combine(total, s_partial[parity][w]);
+        Stored<kDtype>::store1(out, row, total);
+      }
+    } else {
+      if (lane == 0) Stored<kDtype>::store1(out, row, best);
+    }
+  }
+}
+
+template <int kDtype, bool kMaximum>
+int launch_narrow_extremum(cudaStream_t stream, const void *in, void *out, uint64_t rows, uint64_t cols) {
+  const bool vec = cols % 8 == 0 && aligned_to(in, 16);
+  const int sms = sm_count();
+  // a warp covers a row of up to 16 KB well; beyond that, or when there are too few rows to give every SM
+  // eight warps, a CTA per row
+  const bool cta = cols > 8192 || rows < static_cast<uint64_t>(sms) * kWarps;
+  const unsigned grid = clamp_grid(cta ? rows : (rows + kWarps - 1) / kWarps, static_cast<uint64_t>(sms) * 8);
+  auto go = [&](auto vec_tag, auto cta_tag) {
+    return launch(narrow_extremum_kernel<kDtype, kMaximum, decltype(vec_tag)::value, decltype(cta_tag)::value>, dim3(grid),
+                  dim3(kThreads), 0, stream, in, out, rows, cols);
+  };
+  if (vec) return cta ? go(std::true_type{}, std::true_type{}) : go(std::true_type{}, std::false_type{});
+  return cta ? go(std::false_type{}, std::true_type{}) : go(std::false_type{}, std::false_type{});
+}
+
 template <bool kResidual>
 int dispatch_rms(cudaStream_t stream, const void *x, const void *residual, const void *weight,
                  int weight_dtype, void *y, void *h, uint64_t rows, uint64_t hidden, float eps) {
@@ -510,19 +778,49 @@ int launch_layer_norm(cudaStream_t stream, const void *x, const void *scale, con
 // One CTA per row; the row stays in registers (16 values per thread) up to 4096 columns and is
 // re-read from L1/L2 beyond that.  The mask has the tensor's shape or repeats over the leading
 // axes with a period that is a multiple of the row length.
+// kAdditive: Softmax{mask = kAdditive} (include/hyle/compute/operation.h:122-126), the mask an f16
+// tensor added after the scaling, v = f32(x) * scale + f32(mask), as the reference's CUDA kernel forms
+// it (src/compute_provider_cuda/reduction_kernel.cu:131-146); -inf entries mask, a row left without a
+// finite maximum (or holding NaN / +inf) is all NaN as above.
 // ================================================================================================
+// One masked value: the Boolean form selects, the additive form adds.
+template <bool kAdditive>
+__device__ __forceinline__ float masked_score(float scaled, uint32_t mask_word) {
+  if constexpr (kAdditive) return __fadd_rn(scaled, f16_to_f32(static_cast<unsigned short>(mask_word)));
+  else return mask_word == 0 ? -CUDART_INF_F : scaled;
+}
+// Mask element e (0..7) of one 8-element step: a byte of a uint2, or a half of a uint4.
+template <bool kAdditive> struct MaskVector { using Type = uint2; };
+template <> struct MaskVector<true> { using Type = uint4; };
+template <bool kAdditive>
+__device__ __forceinline__ uint32_t mask_element(const typename MaskVector<kAdditive>::Type &m, int e) {
+  if constexpr (kAdditive) {
+    const uint32_t words[4] = {m.x, m.y, m.z, m.w};
+    return e & 1 ? words[e / 2] >> 16 : words[e / 2] & 0xffffu;
+  } else {
+    return ((e < 4 ? m.x : m.y) >> (8 * (e & 3))) & 0xffu;
+  }
+}
+template <bool kAdditive>
+__device__ __forceinline__ typename MaskVector<kAdditive>::Type masked_padding() {
+  // padding slots must not count: Boolean 0 = masked; additive -inf (0xfc00 in both halves)
+  if constexpr (kAdditive) return make_uint4(0xfc00fc00u, 0xfc00fc00u, 0xfc00fc00u, 0xfc00fc00u);
+  else return make_uint2(0, 0);
+}
 constexpr int kScoreSlots = 16;
 
+template <bool kAdditive>
 __global__ void __launch_bounds__(kThreads)
-masked_softmax_f16_kernel(const unsigned short *x, const unsigned char *__restrict__ mask, unsigned short *y, uint64_t rows,
+masked_softmax_f16_kernel(const unsigned short *x, const void *__restrict__ mask_storage, unsigned short *y, uint64_t rows,
                           uint32_t cols, uint64_t mask_rows, float scale) {
+  using MaskWord = typename std::conditional<kAdditive, unsigned short, unsigned char>::type;
+  const MaskWord *mask = static_cast<const MaskWord *>(mask_storage);
   grid_dependency_sync();
   __shared__ float s_part[2][kWarps];
   const int t = threadIdx.x, lane = t & 31, warp = t >> 5;
   const bool resident = cols <= kThreads * kScoreSlots;
-  auto value_at = [&](const unsigned short *row, const unsigned char *row_mask, uint32_t i) {
-    const float v = __fmul_rn(f16_to_f32(row[i]), scale);
-    return row_mask[i] == 0 ? -CUDART_INF_F : v;
+  auto value_at = [&](const unsigned short *row, const MaskWord *row_mask, uint32_t i) {
+    return masked_score<kAdditive>(__fmul_rn(f16_to_f32(row[i]), scale), row_mask[i]);
   };
   auto cta_reduce = [&](float v, int slot, bool maximum) {
     v = maximum ? warp_max_nan(v) : warp_sum(v);
@@ -535,7 +833,7 @@ masked_softmax_f16_kernel(const unsigned short *x, const unsigned char *__restri
   };
   for (uint64_t row = blockIdx.x; row < rows; row += gridDim.x) {
     const unsigned short *in = x + row * cols;
-    const unsigned char *row_mask = mask + (row % mask_rows) * cols;
+    const MaskWord *row_mask = mask + (row % mask_rows) * cols;
     unsigned short *out = y + row * cols;
     float v[kScoreSlots];
     float peak = -CUDART_INF_F;
@@ -583,9 +881,10 @@ masked_softmax_f16_kernel(const unsigned short *x, const unsigned char *__restri
 // inside the f16 step the result is rounded to).
 constexpr int kVectorSlots = 2;
 
+template <bool kAdditive>
 __global__ void __launch_bounds__(kThreads)
-masked_softmax_f16_vector_kernel(const uint4 *__restrict__ x, const uint2 *__restrict__ mask, uint4 *__restrict__ y, uint64_t rows,
-                                 uint32_t vectors, uint64_t mask_rows, float scale) {
+masked_softmax_f16_vector_kernel(const uint4 *__restrict__ x, const typename MaskVector<kAdditive>::Type *__restrict__ mask,
+                                 uint4 *__restrict__ y, uint64_t rows, uint32_t vectors, uint64_t mask_rows, float scale) {
   grid_dependency_sync();
   __shared__ float s_part[2][kWarps];
   const int t = threadIdx.x, lane = t & 31, warp = t >> 5;
@@ -600,7 +899,7 @@ masked_softmax_f16_vector_kernel(const uint4 *__restrict__ x, const uint2 *__res
   };
   for (uint64_t row = blockIdx.x; row < rows; row += gridDim.x) {
     const uint4 *in = x + row * vectors;
-    const uint2 *row_mask = mask + (row % mask_rows) * vectors;
+    const typename MaskVector<kAdditive>::Type *row_mask = mask + (row % mask_rows) * vectors;
     float v[kVectorSlots][8];
     float peak = -CUDART_INF_F;
 #pragma unroll
@@ -608,13 +907,12 @@ masked_softmax_f16_vector_kernel(const uint4 *__restrict__ x, const uint2 *__res
       const uint32_t i = k * kThreads + t;
       if (i < vectors) {
         const uint4 w = ld_stream(in + i);
-        const uint2 m = __ldg(row_mask + i);
+        const auto m = __ldg(row_mask + i);
         const uint32_t words[4] = {w.x, w.y, w.z, w.w};
 #pragma unroll
         for (int e = 0; e < 8; ++e) {
           const unsigned short half = static_cast<unsigned short>(e & 1 ? words[e / 2] >> 16 : words[e / 2] & 0xffffu);
-          const uint32_t keep = ((e < 4 ? m.x : m.y) >> (8 * (e & 3))) & 0xffu;
-          v[k][e] = keep == 0 ? -CUDART_INF_F : __fmul_rn(f16_to_f32(half), scale);
+          v[k][e] = masked_score<kAdditive>(__fmul_rn(f16_to_f32(half), scale), mask_element<kAdditive>(m, e));
           peak = max_nan(peak, v[k][e]);
         }
       } else {
@@ -657,23 +955,23 @@ masked_softmax_f16_vector_kernel(const uint4 *__restrict__ x, const uint2 *__res
 
 // Rows of up to 2048 values (a multiple of 8): one WARP per row, the row in registers (up to eight
 // 16-byte loads in flight per lane), shuffles only -- no barrier between the three phases of a row.
-template <int kSlots>
+template <int kSlots, bool kAdditive>
 __global__ void __launch_bounds__(128)
-masked_softmax_f16_warp_kernel(const uint4 *__restrict__ x, const uint2 *__restrict__ mask, uint4 *__restrict__ y, uint64_t rows,
-                               uint32_t vectors, uint64_t mask_rows, float scale) {
+masked_softmax_f16_warp_kernel(const uint4 *__restrict__ x, const typename MaskVector<kAdditive>::Type *__restrict__ mask,
+                               uint4 *__restrict__ y, uint64_t rows, uint32_t vectors, uint64_t mask_rows, float scale) {
   grid_dependency_sync();
   const int lane = threadIdx.x & 31;
   const uint64_t warps = static_cast<uint64_t>(gridDim.x) * (blockDim.x / 32);
   for (uint64_t row = static_cast<uint64_t>(blockIdx.x) * (blockDim.x / 32) + threadIdx.x / 32; row < rows; row += warps) {
     const uint4 *in = x + row * vectors;
-    const uint2 *row_mask = mask + (row % mask_rows) * vectors;
+    const typename MaskVector<kAdditive>::Type *row_mask = mask + (row % mask_rows) * vectors;
     uint4 w[kSlots];
-    uint2 m[kSlots];
+    typename MaskVector<kAdditive>::Type m[kSlots];
 #pragma unroll
     for (int k = 0; k < kSlots; ++k) {
       const uint32_t i = k * 32 + lane;
       w[k] = i < vectors ? ld_stream(in + i) : make_uint4(0, 0, 0, 0);
-      m[k] = i < vectors ? __ldg(row_mask + i) : make_uint2(0, 0);  // padding counts as masked
+      m[k] = i < vectors ? __ldg(row_mask + i) : masked_padding<kAdditive>();  // padding counts as masked
     }
     float v[kSlots][8];
     float peak = -CUDART_INF_F;
@@ -683,8 +981,7 @@ masked_softmax_f16_warp_kernel(const uint4 *__restrict__ x, const uint2 *__restr
 #pragma unroll
       for (int e = 0; e < 8; ++e) {
         const unsigned short half = static_cast<unsigned short>(e & 1 ? words[e / 2] >> 16 : words[e / 2] & 0xffffu);
-        const uint32_t keep = ((e < 4 ? m[k].x : m[k].y) >> (8 * (e & 3))) & 0xffu;
-        v[k][e] = keep == 0 ? -CUDART_INF_F : __fmul_rn(f16_to_f32(half), scale);
+        v[k][e] = masked_score<kAdditive>(__fmul_rn(f16_to_f32(half), scale), mask_element<kAdditive>(m[k], e));
         peak = max_nan(peak, v[k][e]);
       }
     }
@@ -720,12 +1017,34 @@ masked_softmax_f16_warp_kernel(const uint4 *__restrict__ x, const uint2 *__restr
   }
 }
 
-template <int kSlots>
-int launch_masked_softmax_warp(cudaStream_t stream, const void *in, const unsigned char *mask, void *out, uint64_t rows,
+template <int kSlots, bool kAdditive>
+int launch_masked_softmax_warp(cudaStream_t stream, const void *in, const void *mask, void *out, uint64_t rows,
                                uint32_t vectors, uint64_t mask_rows, float scale) {
   const unsigned grid = clamp_grid((rows + 3) / 4, static_cast<uint64_t>(sm_count()) * 16);
-  return launch(masked_softmax_f16_warp_kernel<kSlots>, dim3(grid), dim3(128), 0, stream, static_cast<const uint4 *>(in),
-                reinterpret_cast<const uint2 *>(mask), static_cast<uint4 *>(out), rows, vectors, mask_rows, scale);
+  return launch(masked_softmax_f16_warp_kernel<kSlots, kAdditive>, dim3(grid), dim3(128), 0, stream, static_cast<const uint4 *>(in),
+                static_cast<const typename MaskVector<kAdditive>::Type *>(mask), static_cast<uint4 *>(out), rows, vectors, mask_rows,
+                scale);
+}
+
+template <bool kAdditive>
+int launch_masked_softmax(cudaStream_t s, const void *in, const void *mask, uint64_t mask_count, float scale, void *out, uint64_t rows,
+                          uint64_t cols) {
+  const unsigned grid = clamp_grid(rows, static_cast<uint64_t>(sm_count()) * 8);
+  const bool vector_ok = cols % 8 == 0 && aligned_to(in, 16) && aligned_to(out, 16) && aligned_to(mask, kAdditive ? 16 : 8);
+  const uint64_t mask_rows = mask_count / cols;
+  if (vector_ok && cols <= 2048) {
+    const uint32_t vectors = static_cast<uint32_t>(cols / 8);
+    if (vectors <= 32) return launch_masked_softmax_warp<1, kAdditive>(s, in, mask, out, rows, vectors, mask_rows, scale);
+    if (vectors <= 64) return launch_masked_softmax_warp<2, kAdditive>(s, in, mask, out, rows, vectors, mask_rows, scale);
+    if (vectors <= 128) return launch_masked_softmax_warp<4, kAdditive>(s, in, mask, out, rows, vectors, mask_rows, scale);
+    return launch_masked_softmax_warp<8, kAdditive>(s, in, mask, out, rows, vectors, mask_rows, scale);
+  }
+  if (vector_ok && cols <= static_cast<uint64_t>(kThreads) * 8 * kVectorSlots)
+    return launch(masked_softmax_f16_vector_kernel<kAdditive>, dim3(grid), dim3(kThreads), 0, s, static_cast<const uint4 *>(in),
+                  static_cast<const typename MaskVector<kAdditive>::Type *>(mask), static_cast<uint4 *>(out), rows,
+                  static_cast<uint32_t>(cols / 8), mask_rows, scale);
+  return launch(masked_softmax_f16_kernel<kAdditive>, dim3(grid), dim3(kThreads), 0, s, static_cast<const unsigned short *>(in), mask,
+                static_cast<unsigned short *>(out), rows, static_cast<uint32_t>(cols), mask_rows, scale);
 }
 
 }  // namespace
@@ -750,6 +1069,21 @@ extern "C" int hyle_b200_reduce_rows_f32(hyle_b200_stream_t stream, int kind, co
   return launch_row_f32<kOpNone>(reinterpret_cast<cudaStream_t>(stream), p);
 }
 
+extern "C" int hyle_b200_reduce_rows_extremum(hyle_b200_stream_t stream, int kind, int dtype, const void *in, void *out,
+                                              uint64_t rows, uint64_t cols) {
+  if (rows == 0) return HYLE_B200_OK;
+  if (out == nullptr || (in == nullptr && cols != 0) || (kind != HYLE_B200_REDUCE_MINIMUM && kind != HYLE_B200_REDUCE_MAXIMUM) ||
+      (dtype != HYLE_B200_BF16 && dtype != HYLE_B200_F16) || !aligned_to(in, 2) || !aligned_to(out, 2))
+    return HYLE_B200_INVALID_VALUE;
+  auto s = reinterpret_cast<cudaStream_t>(stream);
+  const bool maximum = kind == HYLE_B200_REDUCE_MAXIMUM;
+  if (dtype == HYLE_B200_BF16)
+    return maximum ? launch_narrow_extremum<HYLE_B200_BF16, true>(s, in, out, rows, cols)
+                   : launch_narrow_extremum<HYLE_B200_BF16, false>(s, in, out, rows, cols);
+  return maximum ? launch_narrow_extremum<HYLE_B200_F16, true>(s, in, out, rows, cols)
+                 : launch_narrow_extremum<HYLE_B200_F16, false>(s, in, out, rows, cols);
+}
+
 extern "C" int hyle_b200_add_bias_row_sum_max_f32(hyle_b200_stream_t stream, const float *a,
                                                   const float *bias, float *c, float *row_sum,
                                                   float *row_max, uint64_t rows, uint64_t cols) {
@@ -771,6 +1105,17 @@ extern "C" int hyle_b200_rms_norm_bf16(hyle_b200_stream_t stream, const void *x,
                                        float epsilon) {
   return dispatch_rms<false>(reinterpret_cast<cudaStream_t>(stream), x, nullptr, weight, weight_dtype,
                              y, nullptr, rows, hidden, epsilon);
+}
+
+extern "C" int hyle_b200_rms_norm(hyle_b200_stream_t stream, int dtype, const void *x, const void *weight, int weight_dtype,
+                                  void *y, uint64_t rows, uint64_t hidden, float epsilon) {
+  auto s = reinterpret_cast<cudaStream_t>(stream);
+  switch (dtype) {
+    case HYLE_B200_BF16: return dispatch_rms<false>(s, x, nullptr, weight, weight_dtype, y, nullptr, rows, hidden, epsilon);
+    case HYLE_B200_F16: return dispatch_rms_stored<HYLE_B200_F16>(s, x, weight, weight_dtype, y, rows, hidden, epsilon);
+    case HYLE_B200_F32: return dispatch_rms_stored<HYLE_B200_F32>(s, x, weight, weight_dtype, y, rows, hidden, epsilon);
+    default: return HYLE_B200_INVALID_VALUE;
+  }
 }
 
 extern "C" int hyle_b200_add_rms_norm_bf16(hyle_b200_stream_t stream, const void *x,
@@ -798,22 +1143,16 @@ extern "C" int hyle_b200_masked_softmax_f16(hyle_b200_stream_t stream, const voi
   if (in == nullptr || mask == nullptr || out == nullptr || cols > 0x7fffffffull || mask_count == 0 ||
       mask_count % cols != 0 || (rows * cols) % mask_count != 0 || !aligned_to(in, 2) || !aligned_to(out, 2))
     return HYLE_B200_INVALID_VALUE;
-  const unsigned grid = clamp_grid(rows, static_cast<uint64_t>(sm_count()) * 8);
-  const bool vector_ok = cols % 8 == 0 && aligned_to(in, 16) && aligned_to(out, 16) && aligned_to(mask, 8);
-  if (vector_ok && cols <= 2048) {
-    auto s = reinterpret_cast<cudaStream_t>(stream);
-    const uint32_t vectors = static_cast<uint32_t>(cols / 8);
-    const uint64_t mask_rows = mask_count / cols;
-    if (vectors <= 32) return launch_masked_softmax_warp<1>(s, in, mask, out, rows, vectors, mask_rows, scale);
-    if (vectors <= 64) return launch_masked_softmax_warp<2>(s, in, mask, out, rows, vectors, mask_rows, scale);
-    if (vectors <= 128) return launch_masked_softmax_warp<4>(s, in, mask, out, rows, vectors, mask_rows, scale);
-    return launch_masked_softmax_warp<8>(s, in, mask, out, rows, vectors, mask_rows, scale);
-  }
-  if (vector_ok && cols <= static_cast<uint64_t>(kThreads) * 8 * kVectorSlots)
-    return launch(masked_softmax_f16_vector_kernel, dim3(grid), dim3(kThreads), 0, reinterpret_cast<cudaStream_t>(stream),
-                  static_cast<const uint4 *>(in), reinterpret_cast<const uint2 *>(mask), static_cast<uint4 *>(out), rows,
-                  static_cast<uint32_t>(cols / 8), mask_count / cols, scale);
-  return launch(masked_softmax_f16_kernel, dim3(grid), dim3(kThreads), 0, reinterpret_cast<cudaStream_t>(stream),
-                static_cast<const unsigned short *>(in), mask, static_cast<unsigned short *>(out), rows,
-                static_cast<uint32_t>(cols), mask_count / cols, scale);
+  return launch_masked_softmax<false>(reinterpret_cast<cudaStream_t>(stream), in, mask, mask_count, scale, out, rows, cols);
+}
+
+extern "C" int hyle_b200_additive_masked_softmax_f16(hyle_b200_stream_t stream, const void *in, const void *mask_f16,
+                                                     uint64_t mask_count, float scale, void *out, uint64_t rows,
+                                                     uint64_t cols) {
+  if (rows == 0 || cols == 0) return HYLE_B200_OK;
+  if (in == nullptr || mask_f16 == nullptr || out == nullptr || cols > 0x7fffffffull || mask_count == 0 ||
+      mask_count % cols != 0 || (rows * cols) % mask_count != 0 || !aligned_to(in, 2) || !aligned_to(out, 2) ||
+      !aligned_to(mask_f16, 2))
+    return HYLE_B200_INVALID_VALUE;
+  return launch_masked_softmax<true>(reinterpret_cast<cudaStream_t>(stream), in, mask_f16, mask_count, scale, out, rows, cols);
 }

@@ -124,13 +124,19 @@ def unary(kind: int, x: torch.Tensor, out: Optional[torch.Tensor] = None) -> tor
 
 
 def reduce_rows(kind: int, x: torch.Tensor) -> torch.Tensor:
-    """Reduce{kind, axes={-1}} of an f32 tensor; output drops the last axis."""
+    """Reduce{kind, axes={-1}} of an f32 tensor, or its Minimum / Maximum for a bf16 or f16 tensor (result in
+    the tensor's type); output drops the last axis."""
     _device_tensor(x, "x")
-    if x.dtype != torch.float32 or x.dim() < 1:
-        raise ValueError("reduce_rows takes an f32 tensor of rank >= 1")
+    narrow = x.dtype in (torch.bfloat16, torch.float16) and kind in (abi.REDUCE_MINIMUM, abi.REDUCE_MAXIMUM)
+    if not (x.dtype == torch.float32 or narrow) or x.dim() < 1 or not x.is_contiguous():
+        raise ValueError("reduce_rows takes a dense f32 tensor of rank >= 1 (bf16 / f16 for Minimum and Maximum)")
     cols = x.shape[-1]
     rows = x.numel() // cols if cols else int(torch.Size(x.shape[:-1]).numel())
-    out = _new(x.shape[:-1], torch.float32, x.device)
+    out = _new(x.shape[:-1], x.dtype, x.device)
+    if narrow:
+        abi.check("hyle_b200_reduce_rows_extremum", abi.load().hyle_b200_reduce_rows_extremum(
+            _stream(), kind, _DTYPE[x.dtype], x.data_ptr(), out.data_ptr(), rows, cols))
+        return out
     abi.check("hyle_b200_reduce_rows_f32", abi.load().hyle_b200_reduce_rows_f32(
         _stream(), kind, x.data_ptr(), out.data_ptr(), rows, cols))
     return out
@@ -162,17 +168,26 @@ def _weight_args(weight: Optional[torch.Tensor], hidden: int):
 
 def rms_norm(x: torch.Tensor, weight: Optional[torch.Tensor], epsilon: float,
              out: Optional[torch.Tensor] = None) -> torch.Tensor:
-    """RmsNorm{epsilon, accumulation=f32} over the last axis of a bf16 tensor."""
+    """RmsNorm{epsilon, accumulation=f32} over the last axis of a bf16, f16 or f32 tensor; the weight has x's
+    type or is f32."""
     _device_tensor(x, "x")
-    if x.dtype != torch.bfloat16:
-        raise ValueError("rms_norm takes bf16 input")
+    if x.dtype not in _DTYPE or not x.is_contiguous():
+        raise ValueError("rms_norm takes a dense bf16, f16 or f32 tensor")
     hidden = x.shape[-1]
     rows = x.numel() // hidden if hidden else 0
-    w_ptr, w_dtype = _weight_args(weight, hidden)
+    if x.dtype == torch.bfloat16:
+        w_ptr, w_dtype = _weight_args(weight, hidden)
+    elif weight is None:
+        w_ptr, w_dtype = None, _DTYPE[x.dtype]
+    else:
+        _device_tensor(weight, "weight")
+        if weight.numel() != hidden or weight.dtype not in (x.dtype, torch.float32) or not weight.is_contiguous():
+            raise ValueError("weight must have x's type or be f32, with `hidden` elements")
+        w_ptr, w_dtype = weight.data_ptr(), _DTYPE[weight.dtype]
     if out is None:
         out = _new_like(x)
-    abi.check("hyle_b200_rms_norm_bf16", abi.load().hyle_b200_rms_norm_bf16(
-        _stream(), x.data_ptr(), w_ptr, w_dtype, out.data_ptr(), rows, hidden, epsilon))
+    abi.check("hyle_b200_rms_norm", abi.load().hyle_b200_rms_norm(
+        _stream(), _DTYPE[x.dtype], x.data_ptr(), w_ptr, w_dtype, out.data_ptr(), rows, hidden, epsilon))
     return out
 
 
@@ -658,13 +673,18 @@ def select(condition: torch.Tensor, when_true: torch.Tensor, when_false: torch.T
 
 
 def masked_softmax_f16(x: torch.Tensor, mask: torch.Tensor, scale: float = 1.0) -> torch.Tensor:
-    """Softmax{scale, Boolean mask} over the last axis of an f16 tensor; the mask (one byte per element) has
-    x's shape or its trailing axes including the last one."""
+    """Softmax{scale, mask} over the last axis of an f16 tensor; the mask has x's shape or its trailing axes
+    including the last one.  A one-byte mask is Boolean (0 masks); an f16 mask is additive (added after the
+    scaling, -inf masks)."""
     _device_tensor(x, "x"), _device_tensor(mask, "mask")
-    if x.dtype != torch.float16 or mask.element_size() != 1:
-        raise ValueError("masked_softmax_f16 takes f16 values and a one-byte mask")
+    additive = mask.dtype == torch.float16
+    if x.dtype != torch.float16 or not (additive or mask.element_size() == 1):
+        raise ValueError("masked_softmax_f16 takes f16 values and a one-byte (Boolean) or f16 (additive) mask")
+    if not x.is_contiguous() or not mask.is_contiguous():
+        raise ValueError("masked_softmax_f16 takes dense tensors")
     cols = x.shape[-1]
     out = _new_like(x)
-    abi.check("hyle_b200_masked_softmax_f16", abi.load().hyle_b200_masked_softmax_f16(
+    name = "hyle_b200_additive_masked_softmax_f16" if additive else "hyle_b200_masked_softmax_f16"
+    abi.check(name, getattr(abi.load(), name)(
         _stream(), x.data_ptr(), mask.data_ptr(), mask.numel(), scale, out.data_ptr(), x.numel() // cols if cols else 0, cols))
     return out

@@ -48,7 +48,7 @@ struct Plan final {
   Entry entry{};
   int kind = 0;            // unary / binary / reduce / softmax kind in the C ABI's numbering
   int dtype = 0;           // hyle_b200_dtype of the data (or of the norm weight for the norms)
-  int to_dtype = 0;        // Cast: hyle_b200_dtype of the output
+  int to_dtype = 0;        // Cast: hyle_b200_dtype of the output; RmsNorm: of the rows
   std::uint64_t count = 0; // total elements of input 0
   std::uint64_t rows = 0;
   std::uint64_t cols = 0;
@@ -56,7 +56,18 @@ struct Plan final {
   std::uint64_t gate_stride = 0, up_stride = 0, up_offset = 0;  // SwiGLU layouts, in elements
   float epsilon = 0.0F;    // norm epsilon, the scale of CacheStorage::float8, or the Softmax scale
   bool has_weight = false;
-  std::size_t workspace_bytes = 0;
+  std::size_t workspace_bytes = 0;  // what the kernel itself needs, at the start of the workspace
+  // Strided inputs: each is first made dense in the workspace (behind the kernel's part) by
+  // hyle_b200_strided_cast, type onto itself, and the kernel reads the dense temporary.
+  struct Gather final {
+    std::uint8_t input = 0, rank = 0;
+    int dtype = 0;
+    std::array<std::int64_t, kMaxTensorRank> dimensions{}, byte_strides{};
+    std::size_t offset = 0;  // of the temporary, from the start of the workspace
+  };
+  std::array<Gather, 4> gathers{};
+  std::uint8_t gather_count = 0;
+  std::size_t total_workspace_bytes = 0;  // the kernel's part and the temporaries
 };
 
 // Storage types hyle_b200_cast knows.
@@ -112,8 +123,8 @@ inline bool trailing_axes(const TensorDesc &lhs, const TensorDesc &rhs) noexcept
 }
 
 // The provider's domain.  nullopt = decline (another provider may take the request).
-inline std::optional<Plan> match(const Operation &op, std::span<const TensorDesc> in,
-                                 std::span<const TensorDesc> out) noexcept {
+inline std::optional<Plan> match_dense(const Operation &op, std::span<const TensorDesc> in,
+                                       std::span<const TensorDesc> out) noexcept {
   if (in.empty() || out.empty() || !all_dense(in, out)) return std::nullopt;
   Plan p{};
   p.count = elements(in[0]);
@@ -166,10 +177,16 @@ inline std::optional<Plan> match(const Operation &op, std::span<const TensorDesc
     return p;
   }
   if (const auto *reduce = op.get_if<Reduce>()) {
-    // last axis only, f32, dense output without the reduced axis
-    if (in.size() != 1 || out.size() != 1 || in[0].data_type() != DataType::kFloat32 || in[0].rank() == 0 ||
-        reduce->keep_dimensions || elements(out[0]) != p.rows || out[0].data_type() != DataType::kFloat32)
+    // last axis only, dense output without the reduced axis; f32 every kind, bf16 and f16 the extrema
+    // (exact in the rows' own type, f32 comparison)
+    const bool narrow = type && *type != HYLE_B200_F32;
+    if (in.size() != 1 || out.size() != 1 || !type || in[0].rank() == 0 || reduce->keep_dimensions ||
+        elements(out[0]) != p.rows || out[0].data_type() != in[0].data_type())
       return std::nullopt;
+    if (narrow && ((reduce->kind != ReductionKind::kMinimum && reduce->kind != ReductionKind::kMaximum) ||
+                   (reduce->accumulation_type != DataType::kUnknown && reduce->accumulation_type != DataType::kFloat32)))
+      return std::nullopt;
+    p.dtype = *type;
     const auto axes = reduce->axes.values();
     const auto last = static_cast<int>(in[0].rank()) - 1;
     if (reduce->axes.is_all() ? in[0].rank() != 1 : (axes.size() != 1 || (axes[0] != -1 && axes[0] != last)))
@@ -199,13 +216,18 @@ inline std::optional<Plan> match(const Operation &op, std::span<const TensorDesc
     return p;
   }
   if (const auto *norm = op.get_if<RmsNorm>()) {
-    if (in.empty() || in.size() > 2 || out.size() != 1 || in[0].data_type() != DataType::kBFloat16 ||
-        out[0] != in[0] || norm->accumulation_type != DataType::kFloat32)
+    // bf16, f16 or f32 rows; the weight of the row's type or f32 (rows beyond 64 KB only as bf16, up to 32768)
+    if (in.empty() || in.size() > 2 || out.size() != 1 || !type || out[0] != in[0] ||
+        norm->accumulation_type != DataType::kFloat32)
+      return std::nullopt;
+    if (*type == HYLE_B200_BF16 ? p.cols > 32768 : p.cols * (*type == HYLE_B200_F32 ? 4 : 2) > 65536)
       return std::nullopt;
     p.has_weight = in.size() == 2;
+    p.to_dtype = *type;
+    p.dtype = *type;
     if (p.has_weight) {
       const auto weight = abi_dtype(in[1].data_type());
-      if (!weight || *weight == HYLE_B200_F16 || elements(in[1]) != p.cols) return std::nullopt;
+      if (!weight || (*weight != *type && *weight != HYLE_B200_F32) || elements(in[1]) != p.cols) return std::nullopt;
       p.dtype = *weight;
     }
     p.entry = Entry::kRmsNorm;
@@ -244,16 +266,19 @@ inline std::optional<Plan> match(const Operation &op, std::span<const TensorDesc
     }
     return p;
   }
-  if (const auto *masked = op.get_if<Softmax>(); masked != nullptr && masked->mask == MaskKind::kBoolean) {
-    // the attention-score form: f16 values, Bool mask of the same shape or of its trailing axes
-    // (last axis included), any scale, f32 accumulation
+  if (const auto *masked = op.get_if<Softmax>(); masked != nullptr && masked->mask != MaskKind::kNone) {
+    // the attention-score form: f16 values, a Bool mask or f16 addends of the same shape or of its
+    // trailing axes (last axis included), any scale, f32 accumulation
+    const bool additive = masked->mask == MaskKind::kAdditive;
     if (in.size() != 2 || out.size() != 1 || in[0].data_type() != DataType::kFloat16 || out[0] != in[0] ||
-        in[1].data_type() != DataType::kBool || masked->kind != SoftmaxKind::kSoftmax || in[0].rank() == 0 ||
+        in[1].data_type() != (additive ? DataType::kFloat16 : DataType::kBool) ||
+        masked->kind != SoftmaxKind::kSoftmax || in[0].rank() == 0 ||
         in[1].rank() == 0 || !trailing_axes(in[0], in[1]) ||
         (masked->axis != -1 && masked->axis != static_cast<std::int32_t>(in[0].rank()) - 1) ||
         (masked->accumulation_type != DataType::kUnknown && masked->accumulation_type != DataType::kFloat32))
       return std::nullopt;
     p.entry = Entry::kMaskedSoftmax;
+    p.kind = additive ? 1 : 0;
     p.epsilon = masked->scale;
     p.rhs_period = elements(in[1]);
     return p;
@@ -386,6 +411,58 @@ inline std::optional<Plan> match(const Operation &op, std::span<const TensorDesc
   return std::nullopt;
 }
 
+inline std::size_t aligned_256(std::size_t bytes) noexcept { return (bytes + 255) & ~static_cast<std::size_t>(255); }
+inline std::size_t storage_width(int cast_type) noexcept {
+  return cast_type == HYLE_B200_F32 || cast_type == HYLE_B200_I32 ? 4 : (cast_type == HYLE_B200_BF16 || cast_type == HYLE_B200_F16 ? 2 : 1);
+}
+
+// The provider's domain including strided INPUTS (plain storage, non-negative strides that are
+// multiples of the element size, as the reference reads every operand of its tensor kernels,
+// src/compute_provider_cuda/tensor_kernel.cu:70-108): the request is matched with those inputs
+// described dense, and the plan gathers each into a dense temporary before the kernel.  Outputs must
+// be dense.
+inline std::optional<Plan> match(const Operation &op, std::span<const TensorDesc> in,
+                                 std::span<const TensorDesc> out) noexcept {
+  bool strided = false;
+  for (const auto &d : in) strided = strided || !d.is_dense();
+  if (!strided) {
+    auto plan = match_dense(op, in, out);
+    if (plan) plan->total_workspace_bytes = plan->workspace_bytes;
+    return plan;
+  }
+  std::array<TensorDesc, 4> dense_in{};
+  if (in.size() > dense_in.size()) return std::nullopt;
+  for (std::size_t i = 0; i < in.size(); ++i) {
+    dense_in[i] = in[i];
+    if (in[i].is_dense()) continue;
+    const auto type = cast_dtype(in[i].data_type());
+    if (!in[i].is_plain() || !type || in[i].rank() == 0) return std::nullopt;
+    for (const auto stride : in[i].byte_strides())
+      if (stride < 0 || stride % static_cast<std::int64_t>(storage_width(*type)) != 0) return std::nullopt;
+    auto made = TensorDesc::dense(in[i].data_type(), in[i].dimensions());
+    if (!made) return std::nullopt;
+    dense_in[i] = *made;
+  }
+  auto plan = match_dense(op, std::span<const TensorDesc>(dense_in.data(), in.size()), out);
+  if (!plan) return std::nullopt;
+  std::size_t end = aligned_256(plan->workspace_bytes);
+  for (std::size_t i = 0; i < in.size(); ++i) {
+    if (in[i].is_dense()) continue;
+    auto &gather = plan->gathers[plan->gather_count++];
+    gather.input = static_cast<std::uint8_t>(i);
+    gather.rank = static_cast<std::uint8_t>(in[i].rank());
+    gather.dtype = *cast_dtype(in[i].data_type());
+    for (std::size_t axis = 0; axis < in[i].rank(); ++axis) {
+      gather.dimensions[axis] = in[i].dimensions()[axis];
+      gather.byte_strides[axis] = in[i].byte_strides()[axis];
+    }
+    gather.offset = end;
+    end = aligned_256(end + elements(in[i]) * storage_width(gather.dtype));
+  }
+  plan->total_workspace_bytes = end;
+  return plan;
+}
+
 // Entries whose kernels report through the sequence's device status word.
 inline bool uses_status_word(const Plan &p) noexcept {
   switch (p.entry) {
@@ -411,11 +488,12 @@ inline int launch(const Plan &p, hyle_b200_stream_t stream, const void *const *i
     case Entry::kScan:
       return hyle_b200_scan(stream, p.dtype, in[0], out[0], p.rows, p.cols, p.kind, status_word);
     case Entry::kReduceRows:
+      if (p.dtype != HYLE_B200_F32) return hyle_b200_reduce_rows_extremum(stream, p.kind, p.dtype, in[0], out[0], p.rows, p.cols);
       return hyle_b200_reduce_rows_f32(stream, p.kind, static_cast<const float *>(in[0]),
                                        static_cast<float *>(out[0]), p.rows, p.cols);
     case Entry::kRmsNorm:
-      return hyle_b200_rms_norm_bf16(stream, in[0], p.has_weight ? in[1] : nullptr, p.dtype, out[0], p.rows, p.cols,
-                                     p.epsilon);
+      return hyle_b200_rms_norm(stream, p.to_dtype, in[0], p.has_weight ? in[1] : nullptr, p.dtype, out[0], p.rows, p.cols,
+                                p.epsilon);
     case Entry::kLayerNorm:
       return hyle_b200_layer_norm_bf16(stream, in[0], p.has_weight ? in[1] : nullptr, p.has_weight ? in[2] : nullptr,
                                        out[0], p.rows, p.cols, p.epsilon);
@@ -435,6 +513,8 @@ inline int launch(const Plan &p, hyle_b200_stream_t stream, const void *const *i
       return hyle_b200_softmax_f32(stream, p.kind, static_cast<const float *>(in[0]), static_cast<float *>(out[0]),
                                    p.rows, p.cols, workspace, p.workspace_bytes, status_word);
     case Entry::kMaskedSoftmax:
+      if (p.kind == 1)
+        return hyle_b200_additive_masked_softmax_f16(stream, in[0], in[1], p.rhs_period, p.epsilon, out[0], p.rows, p.cols);
       return hyle_b200_masked_softmax_f16(stream, in[0], static_cast<const unsigned char *>(in[1]), p.rhs_period, p.epsilon,
                                           out[0], p.rows, p.cols);
     case Entry::kCast:
@@ -503,7 +583,7 @@ struct Kernel final {
 
   Result<Invocation> create_invocation(mem::BufferView workspace, mem::AllocatorRef) const noexcept {
     Invocation invocation{};
-    if (plan.workspace_bytes != 0) {
+    if (plan.total_workspace_bytes != 0) {
       auto pointer = Backend::mutable_pointer(workspace);
       if (!pointer) return std::unexpected(std::move(pointer).error());
       invocation.workspace = *pointer;
@@ -545,7 +625,18 @@ struct Kernel final {
         return recorded ? KernelCommandResult::accepted_command(std::move(acquired.status))
                         : KernelCommandResult::rejected(std::move(acquired.status));
     }
-    if (invocation.workspace != nullptr && !invocation.workspace_cleared) {
+    for (std::size_t g = 0; g < plan.gather_count; ++g) {
+      const auto &gather = plan.gathers[g];
+      void *dense = static_cast<std::byte *>(invocation.workspace) + gather.offset;
+      const int gathered = hyle_b200_strided_cast(*stream, gather.dtype, gather.dtype, in[gather.input], dense, gather.rank,
+                                                  gather.dimensions.data(), gather.byte_strides.data());
+      if (gathered != HYLE_B200_OK)
+        return recorded ? KernelCommandResult::accepted_command(Backend::status(gathered))
+                        : KernelCommandResult::rejected(Backend::status(gathered));
+      in[gather.input] = dense;
+      recorded = true;
+    }
+    if (plan.workspace_bytes != 0 && !invocation.workspace_cleared) {
       const int cleared = hyle_b200_workspace_clear(*stream, invocation.workspace, plan.workspace_bytes);
       if (cleared != HYLE_B200_OK)
         return recorded ? KernelCommandResult::accepted_command(Backend::status(cleared))
@@ -553,8 +644,8 @@ struct Kernel final {
       invocation.workspace_cleared = true;
       recorded = true;
     }
-    return KernelCommandResult::accepted_command(
-        Backend::status(launch(plan, *stream, in.data(), out.data(), invocation.workspace, status_word)));
+    return KernelCommandResult::accepted_command(Backend::status(
+        launch(plan, *stream, in.data(), out.data(), plan.workspace_bytes != 0 ? invocation.workspace : nullptr, status_word)));
   }
 };
 
@@ -567,16 +658,16 @@ struct Factory final {
     const ResourceRequirement storage{.required_properties = Backend::memory(), .minimum_alignment = 16};
     for (auto &requirement : inputs) requirement = storage;
     for (auto &requirement : outputs) requirement = storage;
-    const WorkspaceRequirement workspace{.size = plan->workspace_bytes, .alignment = 256};
+    const WorkspaceRequirement workspace{.size = plan->total_workspace_bytes, .alignment = 256};
     return KernelProposal{.route = static_cast<std::uint64_t>(plan->entry),
                           .runtime = kRuntime,
                           .workspace_resource = {.required_properties = Backend::memory(), .minimum_alignment = 256},
                           .cost = {.workspace = workspace,
                                    .persistent_bytes = 0,
                                    .copy_bytes = 0,
-                                   .repack_bytes = 0,
+                                   .repack_bytes = plan->gather_count != 0 ? plan->total_workspace_bytes - aligned_256(plan->workspace_bytes) : 0,
                                    .synchronization_count = 0,
-                                   .dispatch_count = 1},
+                                   .dispatch_count = 1u + plan->gather_count},
                           .implementation = ProviderImplementationId{static_cast<std::uint64_t>(plan->entry) + 1}};
   }
   KernelPreparation prepare(const KernelPrepareRequest &request, mem::AllocatorRef allocator) const noexcept {
@@ -584,7 +675,7 @@ struct Factory final {
     if (!plan) return KernelPreparation::unsupported(Status::Unimplemented("hyle-b200: declined at prepare"));
     auto kernel = make_custom_kernel(
         Kernel<Backend>{*plan},
-        {.workspace = {.size = plan->workspace_bytes, .alignment = 256}, .runtime = kRuntime, .persistent_bytes = 0},
+        {.workspace = {.size = plan->total_workspace_bytes, .alignment = 256}, .runtime = kRuntime, .persistent_bytes = 0},
         allocator);
     if (!kernel) return KernelPreparation::error(std::move(kernel).error());
     return KernelPreparation::prepared(std::move(*kernel));

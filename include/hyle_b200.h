@@ -43,7 +43,7 @@ extern "C" {
 /* Same object as cudaStream_t; spelled out so C callers need no CUDA header. */
 typedef struct CUstream_st *hyle_b200_stream_t;
 
-#define HYLE_B200_ABI_VERSION 16
+#define HYLE_B200_ABI_VERSION 17
 
 enum hyle_b200_result {
   HYLE_B200_OK = 0,
@@ -180,6 +180,14 @@ HYLE_B200_API int hyle_b200_reduce_rows_f32(hyle_b200_stream_t stream, int kind,
  * three separate calls above bit for bit (same summation order).  Any of c/row_sum/row_max may be
  * NULL to skip that output.
  */
+/* Reduce{kMinimum | kMaximum, axes={-1}} over dense bf16 or f16 rows, the result in the rows' type:
+ * the narrow Min/Max of the CPU route (src/compute_provider_native/reduction.cc:203-223: f16 both
+ * kinds, bf16 the maximum; bf16 minimum is taken here as well).  Exact: the rules of
+ * hyle_b200_reduce_rows_f32 on the converted values, and an extremum converts back unchanged. */
+HYLE_B200_API int hyle_b200_reduce_rows_extremum(hyle_b200_stream_t stream, int kind, int dtype,
+                                                 const void *in, void *out, uint64_t rows,
+                                                 uint64_t cols);
+
 HYLE_B200_API int hyle_b200_add_bias_row_sum_max_f32(hyle_b200_stream_t stream, const float *a,
                                                      const float *bias, float *c,
                                                      float *row_sum, float *row_max,
@@ -196,6 +204,15 @@ HYLE_B200_API int hyle_b200_add_bias_row_sum_max_f32(hyle_b200_stream_t stream, 
 HYLE_B200_API int hyle_b200_rms_norm_bf16(hyle_b200_stream_t stream, const void *x,
                                           const void *weight, int weight_dtype, void *y,
                                           uint64_t rows, uint64_t hidden, float epsilon);
+
+/* RmsNorm on rows stored as dtype (HYLE_B200_BF16: the entry above; HYLE_B200_F16 and HYLE_B200_F32:
+ * the other two storages the CPU route takes, src/compute_provider_native/normalization.cc:219-234),
+ * same formula, the result rounded once to dtype.  weight: NULL, or [hidden] stored as dtype or as
+ * f32 (weight_dtype).  Rows of more than 64 KB (f16, f32) are HYLE_B200_NOT_SUPPORTED.  y may alias
+ * x exactly. */
+HYLE_B200_API int hyle_b200_rms_norm(hyle_b200_stream_t stream, int dtype, const void *x,
+                                     const void *weight, int weight_dtype, void *y, uint64_t rows,
+                                     uint64_t hidden, float epsilon);
 
 /* Fusion of Binary{kAdd} (bf16: f32 add, one RNE) with the RmsNorm above:
  *   h = bf16_rne(f32(x) + f32(residual));  y = RmsNorm(h)   -- the norm reads the ROUNDED h, so
@@ -380,6 +397,21 @@ HYLE_B200_API int hyle_b200_masked_softmax_f16(hyle_b200_stream_t stream, const 
                                                const unsigned char *mask, uint64_t mask_count,
                                                float scale, void *out, uint64_t rows,
                                                uint64_t cols);
+
+/* Softmax{axis=-1, kSoftmax, scale, mask=kAdditive} on f16 rows (include/hyle/compute/operation.h:122-126;
+ * the reference forms the value in src/compute_provider_cuda/reduction_kernel.cu:131-146):
+ *   v = f32(in) * scale + f32(mask);  out = f16_rne(softmax(v)),  f32 accumulation.
+ * mask_f16: f16 addends (0 keeps, -inf masks, anything finite biases), mask_count of them repeating
+ * over the leading axes under the rules of hyle_b200_masked_softmax_f16, whose treatment of NaN,
+ * +inf and fully masked rows applies.  Product and sum are rounded to f32 separately (the ATen CPU
+ * provider's order, src/compute_provider_native/aten_cpu_provider.cc:500-505, but without its f16
+ * rounding of the product); the native CPU route is NOT followed here: it tests the first byte of
+ * each addend as if it were a Boolean (src/compute_provider_native/transformer.cc:44-57).  Results
+ * within one f16 step of the f32 composition above. */
+HYLE_B200_API int hyle_b200_additive_masked_softmax_f16(hyle_b200_stream_t stream, const void *in,
+                                                        const void *mask_f16, uint64_t mask_count,
+                                                        float scale, void *out, uint64_t rows,
+                                                        uint64_t cols);
 
 /* Cast{f32 -> bf16}, round to nearest even (include/hyle/simd/dtype.h:114-121). */
 HYLE_B200_API int hyle_b200_cast_f32_to_bf16(hyle_b200_stream_t stream, const float *in,

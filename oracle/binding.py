@@ -100,6 +100,7 @@ class Oracle:
         L.hyle_oracle_reduce_rows_f32.argtypes = [_i, _vp, _vp, _u64, _u64]
         L.hyle_oracle_row_sum_f64.argtypes = [_vp, _vp, _vp, _u64, _u64]
         L.hyle_oracle_rms_norm_bf16.argtypes = [_vp, _vp, _i, _vp, _vp, _u64, _u64, _f]
+        L.hyle_oracle_rms_norm.argtypes = [_i, _vp, _vp, _i, _vp, _vp, _u64, _u64, _f]
         L.hyle_oracle_add_rms_norm_bf16.argtypes = [_vp, _vp, _vp, _i, _vp, _vp, _vp, _u64, _u64, _f]
         L.hyle_oracle_swiglu_bf16.argtypes = [_vp, _vp, _vp, _vp, _u64, _u64, _u64, _u64]
         L.hyle_oracle_gated_activation.argtypes = [_i, _i, _i, _vp, _vp, _vp, _vp, _u64, _u64, _u64, _u64]
@@ -221,7 +222,14 @@ class Oracle:
         scale, -inf where the mask byte is 0, the pinned f32 softmax, one rounding to f16.  Returns (f16 words, f32)."""
         x16 = _c(x16, np.uint16)
         values = x16.view(np.float16).astype(np.float32) * np.float32(scale)
-        values = np.where(np.broadcast_to(np.asarray(mask) != 0, values.shape), values, np.float32(-np.inf)).astype(np.float32)
+        mask = np.asarray(mask)
+        if mask.dtype == np.float16:
+            # MaskKind::kAdditive: the addend joins after the scaling, each step rounded to f32
+            # (src/compute_provider_cuda/reduction_kernel.cu:131-146)
+            with np.errstate(all="ignore"):
+                values = (values + np.broadcast_to(mask.astype(np.float32), values.shape)).astype(np.float32)
+        else:
+            values = np.where(np.broadcast_to(mask != 0, values.shape), values, np.float32(-np.inf)).astype(np.float32)
         shape = values.shape
         y = self.softmax(values.reshape(-1, shape[-1])).reshape(shape)
         with np.errstate(all="ignore"):
@@ -233,6 +241,13 @@ class Oracle:
         out = np.empty(rows, np.float32)
         self.lib.hyle_oracle_reduce_rows_f32(kind, _ptr(x), _ptr(out), rows, cols)
         return out
+
+    def reduce_rows_narrow(self, kind, dtype, words):
+        """Minimum / Maximum of bf16 or f16 rows in the rows' type (src/compute_provider_native/reduction.cc:203-223):
+        the f32 reduction on the exactly converted values; an extremum is one of them, so it converts back unchanged
+        (NaN becomes the canonical quiet NaN of the type)."""
+        words = _c(words, np.uint16)
+        return self.cast(F32, dtype, self.reduce_rows(kind, self.cast(dtype, F32, words).view(np.float32)))
 
     def row_sum_f64(self, x):
         x = _c(x, np.float32)
@@ -255,6 +270,16 @@ class Oracle:
         w, wdt = self._weight(weight)
         y, y32 = np.empty_like(x), np.empty(x.shape, np.float32)
         self.lib.hyle_oracle_rms_norm_bf16(_ptr(x), _ptr(w), wdt, _ptr(y), _ptr(y32), rows, hidden, eps)
+        return y, y32
+
+    def rms_norm_stored(self, dtype, x, weight, weight_dtype, eps):
+        """RmsNorm on rows stored as `dtype` (F32 / F16 / BF16; 16-bit words for the narrow ones); the weight,
+        if any, is stored as `weight_dtype`.  Returns (stored result, f32 before the rounding)."""
+        x = _c(x, np.float32 if dtype == F32 else np.uint16)
+        rows, hidden = x.shape
+        w = None if weight is None else _c(weight, np.float32 if weight_dtype == F32 else np.uint16)
+        y, y32 = np.empty_like(x), np.empty(x.shape, np.float32)
+        self.lib.hyle_oracle_rms_norm(dtype, _ptr(x), _ptr(w), weight_dtype, _ptr(y), _ptr(y32), rows, hidden, eps)
         return y, y32
 
     def layer_norm(self, x, scale, bias, eps):

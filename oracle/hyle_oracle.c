@@ -239,6 +239,29 @@ ORACLE_API void hyle_oracle_rms_norm_bf16(const uint16_t *x, const void *weight,
             hidden, eps);
 }
 
+/* RmsNorm on rows of any floating storage (src/compute_provider_native/normalization.cc:41-80 takes f32,
+ * f16 and bf16 rows with a weight of the row's type or of f32): the formula above, the storage's own
+ * load, one rounding at the store.  y_f32 receives the value before that rounding. */
+ORACLE_API void hyle_oracle_rms_norm(int dtype, const void *x, const void *weight, int weight_dtype, void *y,
+                                     float *y_f32, uint64_t rows, uint64_t hidden, float eps) {
+  if (hidden == 0) return;
+#pragma omp parallel for schedule(static)
+  for (uint64_t r = 0; r < rows; ++r) {
+    float ss = 0.0f;
+    for (uint64_t i = 0; i < hidden; ++i) {
+      const float v = load_as_f32(x, r * hidden + i, dtype);
+      ss = fmaf(v, v, ss);
+    }
+    const float inverse = 1.0f / sqrtf(ss / (float)hidden + eps);
+    for (uint64_t i = 0; i < hidden; ++i) {
+      float v = load_as_f32(x, r * hidden + i, dtype) * inverse;
+      if (weight != NULL) v = v * load_as_f32(weight, i, weight_dtype);
+      if (y_f32) y_f32[r * hidden + i] = v;
+      store_from_f32(y, r * hidden + i, dtype, v);
+    }
+  }
+}
+
 /* ---- LayerNorm, bf16 storage, f32 accumulation ------------------------------------------------
  * src/simd/math/activations.cc:148-174: sequential f32 sum -> mean; fma-accumulated centered squares;
  * inverse = 1.0f / sqrt(ss / n + eps); y = round(fma((x - mean) * inverse, scale, bias)) or, without

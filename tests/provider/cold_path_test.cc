@@ -132,6 +132,35 @@ int main() {
     const std::array out_i{i32_mat};
     check(taken(*context, Operation(Scan{}), in_i, out_i), "Scan i32 (overflow reported through the status word)");
   }
+  {  // strided inputs are gathered first (a workspace is declared); strided outputs are declined
+    const auto turned = f32_mat.transposed().value();
+    const auto upright = dense(DataType::kFloat32, {4096, 64});
+    const std::array in{turned};
+    const std::array out{upright};
+    check(taken(*context, Operation(Unary{UnaryKind::kExp}), in, out), "Unary f32 on a transposed input view");
+    const auto plan = b200::match(Operation(Unary{UnaryKind::kExp}), in, out);
+    check(plan && plan->gather_count == 1 && plan->workspace_bytes == 0 && plan->total_workspace_bytes == 64 * 4096 * 4,
+          "the plan gathers that input into a workspace of its dense size");
+    const std::array dense_in{upright};
+    const std::array turned_out{turned};
+    check(!taken(*context, Operation(Unary{UnaryKind::kExp}), dense_in, turned_out), "Unary f32 into a transposed output not taken");
+  }
+  {  // narrow Reduce: the extrema of bf16 / f16 rows in their own type; sums stay with the f32 kernel
+    const auto half_rows = dense(DataType::kFloat16, {64, 2048}), half_col = dense(DataType::kFloat16, {64});
+    const auto bf_col = dense(DataType::kBFloat16, {64});
+    const std::array half_in{half_rows};
+    const std::array half_out{half_col};
+    const std::array bf_in{bf16_mat};
+    const std::array bf_out{bf_col};
+    const std::array<std::int32_t, 1> last{-1};
+    const auto last_axis = [&](ReductionKind kind) {
+      return Operation(Reduce{.kind = kind, .axes = Axes::from(last).value(), .accumulation_type = DataType::kFloat32});
+    };
+    check(taken(*context, last_axis(ReductionKind::kMinimum), half_in, half_out), "Reduce{kMinimum} f16 rows");
+    check(taken(*context, last_axis(ReductionKind::kMaximum), half_in, half_out), "Reduce{kMaximum} f16 rows");
+    check(taken(*context, last_axis(ReductionKind::kMaximum), bf_in, bf_out), "Reduce{kMaximum} bf16 rows");
+    check(!taken(*context, last_axis(ReductionKind::kSum), half_in, half_out), "Reduce{kSum} f16 not taken");
+  }
   {  // RmsNorm bf16 with bf16 / f32 weight; f16 weight and non-f32 accumulation are declined
     const std::array out{bf16_mat};
     const std::array in16{bf16_mat, bf16_w};
@@ -139,7 +168,21 @@ int main() {
     const std::array inh{bf16_mat, f16_w};
     check(taken(*context, Operation(RmsNorm{.epsilon = 1e-6F}), in16, out), "RmsNorm bf16, bf16 weight");
     check(taken(*context, Operation(RmsNorm{.epsilon = 1e-6F}), in32, out), "RmsNorm bf16, f32 weight");
-    check(!taken(*context, Operation(RmsNorm{.epsilon = 1e-6F}), inh, out), "RmsNorm with f16 weight not taken");
+    check(!taken(*context, Operation(RmsNorm{.epsilon = 1e-6F}), inh, out), "RmsNorm bf16 with f16 weight not taken");
+    const auto half_rows = dense(DataType::kFloat16, {64, 2048}), float_rows = dense(DataType::kFloat32, {64, 2048});
+    const auto half_w = dense(DataType::kFloat16, {2048}), float_w = dense(DataType::kFloat32, {2048});
+    const std::array half_in{half_rows, half_w}, half_wide{half_rows, float_w};
+    const std::array float_in{float_rows, float_w}, float_narrow{float_rows, half_w};
+    const std::array half_out{half_rows};
+    const std::array float_out{float_rows};
+    check(taken(*context, Operation(RmsNorm{.epsilon = 1e-6F}), half_in, half_out), "RmsNorm f16, f16 weight");
+    check(taken(*context, Operation(RmsNorm{.epsilon = 1e-6F}), half_wide, half_out), "RmsNorm f16, f32 weight");
+    check(taken(*context, Operation(RmsNorm{.epsilon = 1e-6F}), float_in, float_out), "RmsNorm f32, f32 weight");
+    check(!taken(*context, Operation(RmsNorm{.epsilon = 1e-6F}), float_narrow, float_out), "RmsNorm f32 with f16 weight not taken");
+    const auto long_rows = dense(DataType::kFloat32, {4, 32768});
+    const std::array long_in{long_rows};
+    const std::array long_out{long_rows};
+    check(!taken(*context, Operation(RmsNorm{.epsilon = 1e-6F}), long_in, long_out), "RmsNorm f32 rows beyond 64 KB not taken");
   }
   {  // LayerNorm bf16: alone, or with bf16 scale and bias
     const std::array out{bf16_mat};
@@ -193,6 +236,12 @@ int main() {
     const std::array masked_out{scores};
     check(taken(*context, Operation(Softmax{.scale = 0.125F, .mask = MaskKind::kBoolean}), masked_in, masked_out),
           "Softmax{scale, Boolean mask} f16 [8,128,1024] with mask [128,1024]");
+    const std::array biased_in{scores, dense(DataType::kFloat16, {128, 1024})};
+    check(taken(*context, Operation(Softmax{.scale = 0.125F, .mask = MaskKind::kAdditive}), biased_in, masked_out),
+          "Softmax{scale, additive mask} f16 [8,128,1024] with f16 addends [128,1024]");
+    const std::array wide_in{scores, dense(DataType::kFloat32, {128, 1024})};
+    check(!taken(*context, Operation(Softmax{.scale = 0.125F, .mask = MaskKind::kAdditive}), wide_in, masked_out),
+          "additive mask of another floating type not taken");
     const std::array cast_out{probs16};
     check(taken(*context, Operation(Cast{DataType::kBFloat16}), in, cast_out), "Cast{f32 -> bf16}");
     const std::array fp8_out{dense(DataType::kFloat8E4M3FN, {16, 151936})};

@@ -288,6 +288,27 @@ int main() {
                        return hyle_b200_unary(s, HYLE_B200_UNARY_TANH, HYLE_B200_F32, in[0], out[0], 37000);
                      }, b200::Entry::kUnary});
   }
+  {  // strided inputs: gathered into the workspace by hyle_b200_strided_cast, then the dense kernel
+    const auto turned = dense(DataType::kFloat32, {37, 1000}).transposed().value();  // [1000,37], strides {4, 4000}
+    const auto upright = dense(DataType::kFloat32, {1000, 37});
+    cases.push_back({"Unary{kTanh} f32 on a transposed view [1000,37]", Operation(Unary{UnaryKind::kTanh}), {turned}, {upright},
+                     {f32_normal(37000, 48)}, 37000 * 4,
+                     [](auto s, auto in, auto out, void *ws, std::uint64_t, std::uint32_t *) {
+                       const std::int64_t dims[2] = {1000, 37}, strides[2] = {4, 4000};
+                       const int rc = hyle_b200_strided_cast(s, HYLE_B200_F32, HYLE_B200_F32, in[0], ws, 2, dims, strides);
+                       return rc != HYLE_B200_OK ? rc : hyle_b200_unary(s, HYLE_B200_UNARY_TANH, HYLE_B200_F32, ws, out[0], 37000);
+                     }, b200::Entry::kUnary});
+    const std::int64_t slice_dims[2] = {64, 2048}, slice_strides[2] = {2 * 3072, 2};
+    const auto slice = TensorDesc::strided_bytes(DataType::kBFloat16, slice_dims, slice_strides).value();  // columns 0..2047 of [64,3072]
+    const auto rows = dense(DataType::kBFloat16, {64, 2048}), w = dense(DataType::kBFloat16, {2048});
+    cases.push_back({"RmsNorm bf16 on a column slice [64,2048] of [64,3072]", Operation(RmsNorm{.epsilon = 1e-6F}), {slice, w}, {rows},
+                     {bf16_normal(slice.required_bytes().value() / 2, 49), bf16_normal(2048, 50)}, 64 * 2048 * 2,
+                     [](auto s, auto in, auto out, void *ws, std::uint64_t, std::uint32_t *) {
+                       const std::int64_t dims[2] = {64, 2048}, strides[2] = {2 * 3072, 2};
+                       const int rc = hyle_b200_strided_cast(s, HYLE_B200_BF16, HYLE_B200_BF16, in[0], ws, 2, dims, strides);
+                       return rc != HYLE_B200_OK ? rc : hyle_b200_rms_norm_bf16(s, ws, in[1], HYLE_B200_BF16, out[0], 64, 2048, 1e-6F);
+                     }, b200::Entry::kRmsNorm});
+  }
   {  // Binary with a trailing-axis broadcast
     const auto a = dense(DataType::kFloat32, {64, 4096}), b = dense(DataType::kFloat32, {4096});
     cases.push_back({"Binary{kAdd} f32 [64,4096] + [4096]", Operation(Binary{BinaryKind::kAdd}), {a, b}, {a},
@@ -312,6 +333,13 @@ int main() {
                        return hyle_b200_reduce_rows_f32(s, HYLE_B200_REDUCE_MAXIMUM, static_cast<const float *>(in[0]),
                                                         static_cast<float *>(out[0]), 64, 4096);
                      }, b200::Entry::kReduceRows});
+    const auto h = dense(DataType::kFloat16, {64, 4096}), hr = dense(DataType::kFloat16, {64});
+    cases.push_back({"Reduce{kMinimum, axes={-1}} f16",
+                     Operation(Reduce{.kind = ReductionKind::kMinimum, .axes = Axes::from(last_axis).value(), .accumulation_type = DataType::kFloat32}),
+                     {h}, {hr}, {f16_normal(64 * 4096, 47)}, 0,
+                     [](auto s, auto in, auto out, void *, std::uint64_t, std::uint32_t *) {
+                       return hyle_b200_reduce_rows_extremum(s, HYLE_B200_REDUCE_MINIMUM, HYLE_B200_F16, in[0], out[0], 64, 4096);
+                     }, b200::Entry::kReduceRows});
   }
   {  // Scan f32
     const auto a = dense(DataType::kFloat32, {16, 5000});
@@ -326,6 +354,17 @@ int main() {
                      {bf16_normal(64 * 2048, 9), bf16_normal(2048, 10)}, 0,
                      [](auto s, auto in, auto out, void *, std::uint64_t, std::uint32_t *) {
                        return hyle_b200_rms_norm_bf16(s, in[0], in[1], HYLE_B200_BF16, out[0], 64, 2048, 1e-6F);
+                     }, b200::Entry::kRmsNorm});
+    const auto xh = dense(DataType::kFloat16, {64, 2048}), xf = dense(DataType::kFloat32, {24, 5000});
+    cases.push_back({"RmsNorm f16 [64,2048], f32 weight", Operation(RmsNorm{.epsilon = 1e-6F}), {xh, dense(DataType::kFloat32, {2048})}, {xh},
+                     {f16_normal(64 * 2048, 43), f32_normal(2048, 44)}, 0,
+                     [](auto s, auto in, auto out, void *, std::uint64_t, std::uint32_t *) {
+                       return hyle_b200_rms_norm(s, HYLE_B200_F16, in[0], in[1], HYLE_B200_F32, out[0], 64, 2048, 1e-6F);
+                     }, b200::Entry::kRmsNorm});
+    cases.push_back({"RmsNorm f32 [24,5000], f32 weight", Operation(RmsNorm{.epsilon = 1e-6F}), {xf, dense(DataType::kFloat32, {5000})}, {xf},
+                     {f32_normal(24 * 5000, 45), f32_normal(5000, 46)}, 0,
+                     [](auto s, auto in, auto out, void *, std::uint64_t, std::uint32_t *) {
+                       return hyle_b200_rms_norm(s, HYLE_B200_F32, in[0], in[1], HYLE_B200_F32, out[0], 24, 5000, 1e-6F);
                      }, b200::Entry::kRmsNorm});
     cases.push_back({"LayerNorm bf16 [64,2048], scale and bias", Operation(LayerNorm{.epsilon = 1e-5F}), {x, w, w}, {x},
                      {bf16_normal(64 * 2048, 11), bf16_normal(2048, 12), bf16_normal(2048, 13)}, 0,
@@ -361,6 +400,14 @@ int main() {
                      [](auto s, auto in, auto out, void *, std::uint64_t, std::uint32_t *) {
                        return hyle_b200_masked_softmax_f16(s, in[0], static_cast<const unsigned char *>(in[1]), 128 * 1024, 0.125F,
                                                            out[0], 4 * 128, 1024);
+                     }, b200::Entry::kMaskedSoftmax});
+    Bytes addends = f16_normal(128 * 1024, 41, 2.0f);
+    for (std::size_t i = 0; i < 128 * 1024; i += 3)  // a third of the positions masked outright, never a row's first
+      if (i % 1024 != 0) addends[2 * i] = std::byte{0x00}, addends[2 * i + 1] = std::byte{0xfc};
+    cases.push_back({"Softmax{scale, additive mask} f16 [4,128,1024]", Operation(Softmax{.scale = 0.125F, .mask = MaskKind::kAdditive}),
+                     {x, dense(DataType::kFloat16, {128, 1024})}, {x}, {f16_normal(4 * 128 * 1024, 42, 3.0f), addends}, 0,
+                     [](auto s, auto in, auto out, void *, std::uint64_t, std::uint32_t *) {
+                       return hyle_b200_additive_masked_softmax_f16(s, in[0], in[1], 128 * 1024, 0.125F, out[0], 4 * 128, 1024);
                      }, b200::Entry::kMaskedSoftmax});
   }
   {  // Cast and TopK{1}

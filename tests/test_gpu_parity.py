@@ -234,6 +234,61 @@ def test_rms_norm_hidden_sizes(oracle, hidden):
     assert ops.rms_norm(torch.empty((0, hidden), dtype=torch.bfloat16, device=DEV), None, 1e-6).numel() == 0
 
 
+@pytest.mark.parametrize("hidden", [1, 8, 127, 1000, 1024, 2048, 2056, 4096, 5000, 16384])
+def test_rms_norm_f16_and_f32_rows(oracle, hidden):
+    """RmsNorm on the other two storages of the CPU route: f16 rows within one f16 step of the checker (the sums
+    differ in order), f32 rows within 4e-6 relative; the weight of the row's type or f32; y may be x."""
+    rng = np.random.default_rng(7 * hidden + 1)
+    rows = 19
+    x32 = rng.standard_normal((rows, hidden)).astype(np.float32)
+    w32 = rng.uniform(0.5, 1.5, hidden).astype(np.float32)
+    x16, w16 = x32.astype(np.float16), w32.astype(np.float16)
+    for weight, code in ((None, abi.F16), (w16, abi.F16), (w32, abi.F32)):
+        want, _ = oracle.rms_norm_stored(abi.F16, x16.view(np.uint16), None if weight is None else
+                                         (weight if code == abi.F32 else weight.view(np.uint16)), code, 1e-6)
+        got = ops.rms_norm(to_dev(x16), None if weight is None else to_dev(weight), 1e-6)
+        distance = np.abs(ordered16(got.cpu().numpy().view(np.uint16)) - ordered16(want))
+        assert distance.max() <= 1 and (distance != 0).mean() < 2e-2
+    for weight in (None, w32):
+        want, _ = oracle.rms_norm_stored(abi.F32, x32, weight, abi.F32, 1e-6)
+        got = ops.rms_norm(to_dev(x32), None if weight is None else to_dev(weight), 1e-6).cpu().numpy()
+        assert np.allclose(got, want, rtol=4e-6, atol=0)
+    t = to_dev(x32)
+    ops.rms_norm(t, to_dev(w32), 1e-6, out=t)
+    assert np.allclose(t.cpu().numpy(), want, rtol=4e-6, atol=0)
+    odd = to_dev(np.concatenate([np.zeros(1, np.float16), x16.reshape(-1)]))[1:].view(rows, hidden)   # 2-byte aligned only
+    want, _ = oracle.rms_norm_stored(abi.F16, x16.view(np.uint16), None, abi.F16, 1e-6)
+    assert np.abs(ordered16(ops.rms_norm(odd, None, 1e-6).cpu().numpy().view(np.uint16)) - ordered16(want)).max() <= 1
+    with pytest.raises(abi.KernelError):
+        ops.rms_norm(torch.zeros((2, 16392), device=DEV), None, 1e-6)      # an f32 row beyond 64 KB
+
+
+@pytest.mark.parametrize("shape", [(1, 1), (7, 13), (300, 1000), (1500, 1024), (5, 16384), (3, 40000), (2000, 136)])
+@pytest.mark.parametrize("dtype", [abi.BF16, abi.F16])
+def test_narrow_rows_minimum_and_maximum(oracle, shape, dtype):
+    """Reduce{kMinimum | kMaximum} of bf16 / f16 rows in their own type: exact, NaN wins, -0 < +0."""
+    rng = np.random.default_rng(shape[0] * 31 + shape[1] + dtype)
+    values = (50.0 * rng.standard_normal(shape)).astype(np.float32)
+    words = oracle.cast(abi.F32, dtype, values)
+    if shape[1] > 4:
+        words[0, :] = 0x8000; words[0, 3] = 0x0000                        # -0 everywhere, one +0
+        if shape[0] > 2:
+            words[1, shape[1] // 2] = 0x7E00 if dtype == abi.F16 else 0x7FC0      # a NaN
+            words[2, 1] = 0xFC00 if dtype == abi.F16 else 0xFF80                  # -inf
+    torch_type = torch.float16 if dtype == abi.F16 else torch.bfloat16
+    x = torch.from_numpy(words.view(np.int16)).to(DEV).view(torch_type)
+    for kind in (abi.REDUCE_MINIMUM, abi.REDUCE_MAXIMUM):
+        want = oracle.reduce_rows_narrow(kind, dtype, words)
+        got = ops.reduce_rows(kind, x).view(torch.int16).cpu().numpy().view(np.uint16)
+        nan = (want & 0x7FFF) > (0x7C00 if dtype == abi.F16 else 0x7F80)
+        assert np.array_equal((got & 0x7FFF) > (0x7C00 if dtype == abi.F16 else 0x7F80), nan)
+        assert np.array_equal(got[~nan], want[~nan])
+    odd = torch.cat([x.reshape(-1)[:1], x.reshape(-1)])[1:].view(shape)        # 2-byte aligned rows
+    assert torch.equal(ops.reduce_rows(abi.REDUCE_MAXIMUM, odd).view(torch.int16), ops.reduce_rows(abi.REDUCE_MAXIMUM, x).view(torch.int16))
+    empty = ops.reduce_rows(abi.REDUCE_MINIMUM, torch.empty((3, 0), dtype=torch_type, device=DEV))
+    assert torch.isinf(empty.float()).all() and (empty.float() > 0).all()
+
+
 # ---- workload 3: SwiGLU (bf16) ----------------------------------------------------------------------------------------
 @pytest.mark.parametrize("tokens", [1, 8, 32, 4096])
 def test_swiglu_config(oracle, tokens):
@@ -829,6 +884,41 @@ def test_masked_scaled_softmax_f16(oracle, cols):
     nan = (want16 & 0x7FFF) > 0x7C00
     assert np.array_equal((got & 0x7FFF) > 0x7C00, nan)
     assert np.abs(ordered16(got[~nan]) - ordered16(want16[~nan])).max(initial=0) <= 1
+
+
+@pytest.mark.parametrize("cols", [1, 7, 128, 1000, 1024, 2056, 4096, 5000])
+def test_additive_masked_softmax_f16(oracle, cols):
+    """Softmax{scale, mask=kAdditive}: f16 addends of the trailing axes or of the tensor's shape; 0 keeps, -inf masks."""
+    rng = np.random.default_rng(100 + cols)
+    heads, queries = 3, 17
+    x = (4.0 * rng.standard_normal((heads, queries, cols))).astype(np.float16)
+    addend = (2.0 * rng.standard_normal((queries, cols))).astype(np.float16)
+    addend[rng.random((queries, cols)) < 0.3] = -np.inf
+    addend[:, 0] = 0
+    if cols > 1:
+        addend[3, :] = -np.inf                                            # a fully masked row: all NaN
+        addend[5, cols // 2] = np.nan                                     # NaN addend: the row is NaN
+        addend[6, :] = -np.inf; addend[6, cols - 1] = 3.5
+        x[2, 7, cols - 1] = np.inf                                        # +inf score: NaN
+        addend[8, 0] = np.inf
+    for scale in (1.0, 0.125):
+        want16, _ = oracle.masked_softmax_f16(x.view(np.uint16), addend[None], scale)
+        got = ops.masked_softmax_f16(to_dev(x), to_dev(addend), scale).cpu().numpy().view(np.uint16)
+        nan = (want16 & 0x7FFF) > 0x7C00
+        assert np.array_equal((got & 0x7FFF) > 0x7C00, nan)
+        distance = np.abs(ordered16(got[~nan]) - ordered16(want16[~nan]))
+        assert distance.max(initial=0) <= 1 and (distance != 0).mean() < 2e-2
+    full = (rng.standard_normal(x.shape)).astype(np.float16); full[rng.random(x.shape) < 0.5] = -np.inf; full[..., 0] = 0
+    want16, _ = oracle.masked_softmax_f16(x.view(np.uint16), full, 0.5)
+    got = ops.masked_softmax_f16(to_dev(x), to_dev(full), 0.5).cpu().numpy().view(np.uint16)
+    nan = (want16 & 0x7FFF) > 0x7C00
+    assert np.array_equal((got & 0x7FFF) > 0x7C00, nan)
+    assert np.abs(ordered16(got[~nan]) - ordered16(want16[~nan])).max(initial=0) <= 1
+    # all-zero addends are the unmasked scaled softmax: bit-equal to the Boolean kernel with an all-true mask
+    zero = np.zeros((queries, cols), np.float16)
+    a = ops.masked_softmax_f16(to_dev(x), to_dev(zero), 0.25)
+    b = ops.masked_softmax_f16(to_dev(x), to_dev(np.ones((queries, cols), np.uint8)), 0.25)
+    assert torch.equal(a.view(torch.int16), b.view(torch.int16))
 
 
 def test_cast_rejects_other_pairs():

@@ -269,6 +269,15 @@ def test_masked_scaled_softmax_rules(oracle):
     ref = np.exp(0.25 * x[0, 0].astype(np.float64)); ref /= ref.sum()
     assert np.allclose(values[0, 0], ref, rtol=1e-5)
     assert np.array_equal(words, values.astype(np.float16).view(np.uint16)) or np.isnan(values).any()
+    # additive form: 0 / -inf addends reproduce the Boolean mask exactly, a finite addend biases the score
+    addend = np.where(mask != 0, np.float16(0), np.float16(-np.inf)).astype(np.float16)
+    words_add, values_add = oracle.masked_softmax_f16(x.view(np.uint16), addend[None], 0.25)
+    assert np.array_equal(words_add, words)
+    addend[0, 3] = 1.5
+    _, biased = oracle.masked_softmax_f16(x.view(np.uint16), addend[None], 0.25)
+    z = 0.25 * x[0, 0].astype(np.float64); z[3] += 1.5
+    ref = np.exp(z - z.max()); ref /= ref.sum()
+    assert np.allclose(biased[0, 0], ref, rtol=1e-5)
 
 
 # ---- sampling ----------------------------------------------------------------------------------------------------------------
