@@ -315,6 +315,15 @@ def other_ops(torch, peak_gbs, only=None, iterations=40):
             stream, x16[i].data_ptr(), scale.data_ptr(), bias.data_ptr(), y16[i].data_ptr(), 4096, 2048, 1e-5), sets, iterations)
         report("layer_norm_bf16", "4096x2048", 4096 * 2048, 2 * 4096 * 2048 * 2, ms, sets)
         del x16, y16
+        # the same kernel on eight times the rows: an 8 us launch is dominated by the launch-to-launch boundary
+        sets = 3
+        x16 = [torch.randn(32768, 2048, device=dev).to(torch.bfloat16) for _ in range(sets)]
+        y16 = [torch.empty_like(x16[0]) for _ in range(sets)]
+        ms = time_op(torch, lambda i: lib.hyle_b200_layer_norm_bf16(
+            stream, x16[i].data_ptr(), scale.data_ptr(), bias.data_ptr(), y16[i].data_ptr(), 32768, 2048, 1e-5), sets, iterations)
+        report("layer_norm_bf16", "32768x2048", 32768 * 2048, 2 * 32768 * 2048 * 2, ms, sets)
+        del x16, y16
+        sets = 8
         x32 = [torch.randn(4096, 4096, device=dev) for _ in range(sets)]
         codes = [torch.empty(4096, 4096, dtype=torch.uint8, device=dev) for _ in range(sets)]
         ms = time_op(torch, lambda i: lib.hyle_b200_cast(
@@ -364,7 +373,18 @@ def other_ops(torch, peak_gbs, only=None, iterations=40):
         ms = time_op(torch, lambda i: lib.hyle_b200_masked_softmax_f16(
             stream, scores[i].data_ptr(), mask.data_ptr(), mask.numel(), 0.125, probs[i].data_ptr(), rows, cols), sets, iterations)
         report("masked_softmax_f16", "32768x2048, causal mask 2048x2048", rows * cols, rows * cols * 4 + mask.numel(), ms, sets)
-        del scores, probs, mask
+        addend = torch.where(mask != 0, 0.0, float("-inf")).to(torch.float16).contiguous()
+        ms = time_op(torch, lambda i: lib.hyle_b200_additive_masked_softmax_f16(
+            stream, scores[i].data_ptr(), addend.data_ptr(), addend.numel(), 0.125, probs[i].data_ptr(), rows, cols), sets, iterations)
+        report("additive_masked_softmax_f16", "32768x2048, causal f16 addends 2048x2048", rows * cols,
+               rows * cols * 4 + addend.numel() * 2, ms, sets)
+        ms = time_op(torch, lambda i: lib.hyle_b200_reduce_rows_extremum(
+            stream, abi.REDUCE_MAXIMUM, abi.F16, scores[i].data_ptr(), probs[i].data_ptr(), rows, cols), sets, iterations)
+        report("reduce_max_f16", "32768x2048", rows * cols, rows * cols * 2 + rows * 2, ms, sets)
+        ms = time_op(torch, lambda i: lib.hyle_b200_rms_norm(
+            stream, abi.F16, scores[i].data_ptr(), None, abi.F16, probs[i].data_ptr(), rows, cols, 1e-6), sets, iterations)
+        report("rms_norm_f16", "32768x2048", rows * cols, rows * cols * 4, ms, sets)
+        del scores, probs, mask, addend
         side = 4096
         x = [torch.randn(side, side, device=dev) for _ in range(sets)]
         y = [torch.empty(side, side, device=dev) for _ in range(sets)]
@@ -397,6 +417,16 @@ def other_ops(torch, peak_gbs, only=None, iterations=40):
         ms = time_op(torch, lambda i: lib.hyle_b200_scan(
             stream, abi.I32, n[i].data_ptr(), m[i].data_ptr(), 4096, 4096, 0, status.data_ptr()), sets, iterations)
         report("scan_i32_checked", "4096x4096", 4096 * 4096, 4096 * 4096 * 8, ms, sets)
+        # "an overflow writes nothing" forces the whole input to be checked before the first store: a tensor that
+        # does not stay in L2 between the two passes is read twice, 12 bytes per value moved
+        report("scan_i32_checked (12 B per value: input read twice)", "4096x4096", 4096 * 4096, 4096 * 4096 * 12, ms, sets)
+        del n, m
+        sets = 8
+        n = [torch.randint(-1000, 1000, (2048, 4096), dtype=torch.int32, device=dev) for _ in range(sets)]
+        m = [torch.empty_like(n[0]) for _ in range(sets)]
+        ms = time_op(torch, lambda i: lib.hyle_b200_scan(
+            stream, abi.I32, n[i].data_ptr(), m[i].data_ptr(), 2048, 4096, 0, status.data_ptr()), sets, iterations)
+        report("scan_i32_checked", "2048x4096 (32 MiB: the writing pass reads it from L2)", 2048 * 4096, 2048 * 4096 * 8, ms, sets)
         del n, m
 
     # Paged append: 4096 new Q8_0 rows of 8192 values (8704 bytes) into 256 pages of 16 rows

@@ -624,23 +624,28 @@ strided_tiles_kernel(const unsigned char *__restrict__ in, typename Element<kDst
   }
 }
 
-// The same transposition for 4-byte source words when everything is 16-byte aligned: 64 x 64 tiles, each
-// thread brings in four 16-byte vectors along the source's contiguous axis (all four in flight before the
-// first shared-memory store) and writes four vectors of four results along the destination's innermost
-// axis.  Shared-memory pitch 65 words: the column reads and the scattered scalar stores are at most
-// two-way conflicted, which HBM-bound traffic does not notice.
+// The same transposition for 4-byte source words when everything is 16-byte aligned: 64 x 64 tiles moved
+// with 16-byte accesses at every step.  A thread loads a 4 x 4 block (four 16-byte vectors from four
+// consecutive source rows, all in flight), transposes it in registers (a renaming), and stores the four
+// transposed vectors to shared memory, which holds the tile TRANSPOSED, [across][inner], as 16 groups of
+// four words per row; it then reads one group per step along the destination's innermost axis and writes
+// 16 bytes (or four converted results) to global memory.  The group index is XORed with (row / 4) % 8, so
+// the eight lanes of a quarter warp hit eight different bank groups both when storing (eight rows four
+// apart, one group) and when loading (one row, eight groups): no padding, no bank conflict, a quarter of
+// the shared-memory instructions of a word-by-word transposition.
 template <int kSrc, int kDst, bool kCopy, class Index>
 __global__ void __launch_bounds__(256)
 strided_tiles64_kernel(const unsigned char *__restrict__ in, typename Element<kDst>::Word *__restrict__ out, uint64_t batches,
                        const View view, const Transposition plan) {
   grid_dependency_sync();
   using Out = typename Element<kDst>::Word;
-  __shared__ uint32_t tile[64][65];
+  __shared__ uint4 tile[64][16];
   const uint32_t inner_axis = view.rank - 1;
   const uint64_t inner = view.dims[inner_axis], across = view.dims[plan.axis];
   const uint64_t tiles_inner = (inner + 63) / 64, tiles_across = (across + 63) / 64;
   const uint64_t units = batches * tiles_inner * tiles_across;
   const int64_t inner_stride = view.strides[inner_axis];
+  const uint32_t group = threadIdx.x / 16, member = threadIdx.x % 16;  // block rows 4*group.., block columns 4*member..
   for (uint64_t unit = blockIdx.x; unit < units; unit += gridDim.x) {
     Index rest = static_cast<Index>(unit);
     const Index after_inner = rest / static_cast<Index>(tiles_inner);
@@ -660,33 +665,33 @@ strided_tiles64_kernel(const unsigned char *__restrict__ in, typename Element<kD
       }
     }
     uint4 q[4];
+    {
+      const uint64_t j = tile_inner * 64 + 4 * group, c = tile_across * 64 + 4 * member;
 #pragma unroll
-    for (int step = 0; step < 4; ++step) {
-      const uint32_t slot = threadIdx.x + step * 256;
-      const uint64_t j = tile_inner * 64 + slot / 16, c = tile_across * 64 + 4 * (slot % 16);
-      q[step] = (j < inner && c < across)
-                    ? ld_stream(reinterpret_cast<const uint4 *>(in + source + static_cast<int64_t>(j) * inner_stride + static_cast<int64_t>(c) * 4))
-                    : make_uint4(0, 0, 0, 0);
+      for (int k = 0; k < 4; ++k)
+        q[k] = (j + k < inner && c < across)
+                   ? ld_stream(reinterpret_cast<const uint4 *>(in + source + static_cast<int64_t>(j + k) * inner_stride + static_cast<int64_t>(c) * 4))
+                   : make_uint4(0, 0, 0, 0);
     }
-#pragma unroll
-    for (int step = 0; step < 4; ++step) {
-      const uint32_t slot = threadIdx.x + step * 256;
-      uint32_t *row = &tile[slot / 16][4 * (slot % 16)];
-      row[0] = q[step].x, row[1] = q[step].y, row[2] = q[step].z, row[3] = q[step].w;
-    }
+    // transposed block: row 4*member + m of the transposed tile, group `group` (inner 4*group .. +3)
+    const uint32_t swizzle = member & 7;  // ((4 * member + m) / 4) % 8
+    tile[4 * member + 0][group ^ swizzle] = make_uint4(q[0].x, q[1].x, q[2].x, q[3].x);
+    tile[4 * member + 1][group ^ swizzle] = make_uint4(q[0].y, q[1].y, q[2].y, q[3].y);
+    tile[4 * member + 2][group ^ swizzle] = make_uint4(q[0].z, q[1].z, q[2].z, q[3].z);
+    tile[4 * member + 3][group ^ swizzle] = make_uint4(q[0].w, q[1].w, q[2].w, q[3].w);
     __syncthreads();
 #pragma unroll
     for (int step = 0; step < 4; ++step) {
-      const uint32_t slot = threadIdx.x + step * 256;
-      const uint32_t c_local = slot / 16, j_local = 4 * (slot % 16);
+      const uint32_t c_local = group + 16 * step, j_local = 4 * member;
       const uint64_t c = tile_across * 64 + c_local, j = tile_inner * 64 + j_local;
       if (c < across && j < inner) {
+        const uint4 words = tile[c_local][member ^ ((c_local / 4) & 7)];
+        const uint32_t word[4] = {words.x, words.y, words.z, words.w};
         struct alignas(4 * sizeof(Out)) Results { Out v[4]; } results;
 #pragma unroll
         for (int k = 0; k < 4; ++k) {
-          const uint32_t word = tile[j_local + k][c_local];
-          if constexpr (kCopy) results.v[k] = static_cast<Out>(word);
-          else results.v[k] = static_cast<Out>(convert<kSrc, kDst>(word));
+          if constexpr (kCopy) results.v[k] = static_cast<Out>(word[k]);
+          else results.v[k] = static_cast<Out>(convert<kSrc, kDst>(word[k]));
         }
         *reinterpret_cast<Results *>(out + destination + c * plan.dense[plan.axis] + j) = results;
       }

@@ -82,6 +82,7 @@ random_bits_kernel(const uint32_t *__restrict__ identities, uint32_t *out, uint6
 constexpr int kDrawThreads = 512;
 constexpr int kDrawCtasPerSm = 2;
 constexpr int kDrawWarps = kDrawThreads / 32;
+constexpr int kDrawBatch = 8;  // chunk loads in flight per warp in the second pass
 constexpr uint32_t kDrawMaxChunks = 1024;  // chunk totals of one run kept in shared memory (rows up to 524 288 wide)
 static_assert(kDrawThreads / 32 * kDrawMaxChunks * 32 == 524288, "the shared table covers the documented row width");
 
@@ -124,7 +125,7 @@ __global__ void __launch_bounds__(kDrawThreads, kDrawCtasPerSm)
 categorical_kernel(const void *logits, const uint32_t *__restrict__ identities, int32_t *index_out, float *log_probability,
                    uint64_t rows, uint32_t cols, uint32_t *status_word) {
   grid_dependency_sync();
-  __shared__ float s_max[kDrawWarps];
+  __shared__ float s_max[kDrawWarps], s_shift[kDrawWarps];
   __shared__ uint32_t s_bad[kDrawWarps];
   __shared__ double s_sum[kDrawWarps];
   __shared__ double s_before[kDrawWarps + 1];
@@ -141,33 +142,38 @@ categorical_kernel(const void *logits, const uint32_t *__restrict__ identities, 
   for (uint64_t row = blockIdx.x; row < rows; row += gridDim.x) {
     const void *x = static_cast<const unsigned char *>(logits) + row * cols * kWidth;
     // pass 1 (the only read of the row from HBM): maximum, validity AND the weight sums, "online".  A lane
-    // sums 2^(x log2 e - s) against its own shift s = ceil(log2 e x running maximum) and rescales when the
-    // maximum grows.  The shifts are INTEGERS, so every rescaling (lane, lane -> warp, warp -> row) is an
-    // exact power of two: no lane's weights carry a rounding of their own shift, which would move the
-    // threshold by parts in 10^7 and the draw with it.  Four 16-byte loads are in flight per lane.
+    // sums 2^(x log2 e - s) against its own shift s and raises s when an element would exceed it.  The
+    // shifts are INTEGERS, so every rescaling (lane, lane -> warp, warp -> row) is an exact power of two: no
+    // lane's weights carry a rounding of their own shift, which would move the threshold by parts in 10^7
+    // and the draw with it.  A raised shift gets kDrawHeadroom binades of room, so a slowly growing maximum
+    // does not rescale at every record (the path diverges the warp): weights then sit at most 2^-headroom
+    // below 1, which only narrows the range above the flush-to-zero floor from 126 to 118 binades.
+    // Four 16-byte loads are in flight per lane.
     constexpr float kLog2e = 1.4426950408889634f;
-    float lane_max = -CUDART_INF_F, lane_shift = 0.0f;
+    constexpr float kDrawHeadroom = 8.0f;
+    constexpr float kNoShift = -3.0e38f;  // below every finite x log2 e: the first finite element raises it
+    float lane_max = -CUDART_INF_F, lane_shift = kNoShift;
     double lane_sum = 0.0;
     uint32_t bad = 0;
-    auto rescale = [](double value, float from_shift, float to_shift) {  // value * 2^(from - to), to >= from
-      return scalbn(value, static_cast<int>(fmaxf(from_shift - to_shift, -4000.0f)));
+    auto rescale = [](double value, float from_shift, float to_shift) {  // value * 2^(from - to), to >= from: exact
+      const int exponent = static_cast<int>(fmaxf(from_shift - to_shift, -1022.0f));  // 2^-1022 of a sum <= 2^20 is nothing
+      return value * __hiloint2double((1023 + exponent) << 20, 0);
     };
     auto absorb = [&](const float (&v)[4]) {
-      const float high = fmaxf(fmaxf(v[0], v[1]), fmaxf(v[2], v[3]));
-      // NaN: fminf / fmaxf drop it, so test the sum (inf - inf cannot occur: +inf is rejected anyway)
-      const float probe = (v[0] + v[1]) + (v[2] + v[3]);
-      bad |= (probe != probe || high == CUDART_INF_F) ? 1u : 0u;
-      if (high > lane_max && high < CUDART_INF_F) {
-        const float shift = ceilf(__fmul_rn(high, kLog2e));
-        lane_sum = lane_max > -CUDART_INF_F ? rescale(lane_sum, lane_shift, shift) : 0.0;
-        lane_max = high;
+      const float high = fmaxf(fmaxf(v[0], v[1]), fmaxf(v[2], v[3]));  // drops NaN: those show in the weights
+      const float scaled = __fmul_rn(high, kLog2e);
+      if (scaled > lane_shift && high < CUDART_INF_F) {  // rare after the first elements
+        const float shift = ceilf(scaled) + kDrawHeadroom;
+        lane_sum = rescale(lane_sum, lane_shift, shift);
         lane_shift = shift;
       }
-      if (lane_max > -CUDART_INF_F) {
-        const float minus = -lane_shift;
-        // four weights are added in f32 (a rounding of 6e-8 of their sum, unbiased), the running sum is f64
-        lane_sum += static_cast<double>((weight_of(v[0], minus) + weight_of(v[1], minus)) + (weight_of(v[2], minus) + weight_of(v[3], minus)));
-      }
+      lane_max = fmaxf(lane_max, high);
+      const float minus = -lane_shift;
+      // four weights are added in f32 (a rounding of 6e-8 of their sum, unbiased), the running sum is f64;
+      // a NaN element makes its weight NaN, -inf gives 0, +inf is rejected through the maximum
+      const float weights = (weight_of(v[0], minus) + weight_of(v[1], minus)) + (weight_of(v[2], minus) + weight_of(v[3], minus));
+      bad |= (weights != weights || high == CUDART_INF_F) ? 1u : 0u;
+      lane_sum += static_cast<double>(weights);
     };
     // f32 rows whose start is 16-byte aligned are read as float4 (the sums do not depend on the order of
     // the elements inside a warp's run); runs start at multiples of 32 elements
@@ -201,21 +207,25 @@ categorical_kernel(const void *logits, const uint32_t *__restrict__ identities, 
 #pragma unroll
     for (int o = 16; o > 0; o >>= 1) maximum = fmaxf(maximum, __shfl_xor_sync(kFullMask, maximum, o));
     bad = __any_sync(kFullMask, bad != 0) ? 1u : 0u;
-    // lanes -> warp: against the warp's shift, one fixed tree per warp
-    const float warp_shift = ceilf(__fmul_rn(maximum, kLog2e));
-    double sum = lane_max > -CUDART_INF_F && maximum < CUDART_INF_F ? rescale(lane_sum, lane_shift, warp_shift) : 0.0;
-    sum = warp_sum(sum);
+    // lanes -> warp: against the largest shift of the warp, one fixed tree per warp
+    float warp_shift = lane_shift;
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) warp_shift = fmaxf(warp_shift, __shfl_xor_sync(kFullMask, warp_shift, o));
+    const double sum = warp_sum(bad ? 0.0 : rescale(lane_sum, lane_shift, warp_shift));
     if (lane == 0) {
       s_max[warp] = maximum;
+      s_shift[warp] = warp_shift;
       s_bad[warp] = bad;
       s_sum[warp] = sum;
     }
     __syncthreads();
     maximum = s_max[0];
     bad = s_bad[0];
+    float row_shift = s_shift[0];
 #pragma unroll
     for (int w = 1; w < kDrawWarps; ++w) {
       maximum = fmaxf(maximum, s_max[w]);
+      row_shift = fmaxf(row_shift, s_shift[w]);
       bad |= s_bad[w];
     }
     if (bad != 0 || !(maximum > -CUDART_INF_F)) {  // CTA-uniform: reject the row
@@ -229,14 +239,13 @@ categorical_kernel(const void *logits, const uint32_t *__restrict__ identities, 
     }
     // every weight from here on is 2^(x log2 e - row_shift); the common factor cancels in the draw and
     // is put back into the log-probability below
-    const float row_shift = ceilf(__fmul_rn(maximum, kLog2e));
     const float neg_scaled_max = -row_shift;
     if (t == 0) {
       // thread 0 chains the warp totals, each brought (exactly) to the row's shift
       double running = 0.0;
       for (int w = 0; w < kDrawWarps; ++w) {
         s_before[w] = running;
-        if (s_max[w] > -CUDART_INF_F) running += rescale(s_sum[w], ceilf(__fmul_rn(s_max[w], kLog2e)), row_shift);
+        running += rescale(s_sum[w], s_shift[w], row_shift);
       }
       s_before[kDrawWarps] = running;
       s_selected = -1;
@@ -260,11 +269,21 @@ categorical_kernel(const void *logits, const uint32_t *__restrict__ identities, 
     const uint32_t chunks = (owner_end - owner_begin + 31) / 32;
     if (chunks <= kDrawMaxChunks) {
       // all warps share the owner's run: chunk totals (fixed tree) into shared memory ...
-      for (uint32_t c = warp; c < chunks; c += kDrawWarps) {
-        const uint32_t i = owner_begin + 32 * c + lane;
-        const double weight = i < owner_end ? static_cast<double>(weight_of(load_logit<kDtype>(x, i), neg_scaled_max)) : 0.0;
-        const double chunk_total = warp_sum(weight);
-        if (lane == 0) s_chunk[c] = chunk_total;
+      // (the loads of kDrawBatch chunks are issued before the first is summed: the run comes from L2 and a
+      // load per chunk in sequence would cost an L2 round trip each)
+      for (uint32_t first = warp; first < chunks; first += kDrawWarps * kDrawBatch) {
+        float value[kDrawBatch];
+#pragma unroll
+        for (int k = 0; k < kDrawBatch; ++k) {
+          const uint32_t c = first + k * kDrawWarps, i = owner_begin + 32 * c + lane;
+          value[k] = c < chunks && i < owner_end ? load_logit<kDtype>(x, i) : -CUDART_INF_F;  // -inf: weight 0
+        }
+#pragma unroll
+        for (int k = 0; k < kDrawBatch; ++k) {
+          const uint32_t c = first + k * kDrawWarps;
+          const double chunk_total = warp_sum(static_cast<double>(weight_of(value[k], neg_scaled_max)));
+          if (lane == 0 && c < chunks) s_chunk[c] = chunk_total;
+        }
       }
       __syncthreads();
       // ... then warp 0 chains them, 32 at a time, to the chunk where the cumulative weight first
