@@ -149,6 +149,10 @@ categorical_kernel(const void *logits, const uint32_t *__restrict__ identities, 
     // does not rescale at every record (the path diverges the warp): weights then sit at most 2^-headroom
     // below 1, which only narrows the range above the flush-to-zero floor from 126 to 118 binades.
     // Four 16-byte loads are in flight per lane.
+    // the row's uniform does not depend on the data: its ten Philox rounds run under the first loads
+    const Words random = philox_block(identities + row * 4, 0);
+    const double uniform =
+        (static_cast<double>(random.x0) * 1048576.0 + static_cast<double>(random.x1 >> 12) + 0.5) * 2.220446049250313e-16;
     constexpr float kLog2e = 1.4426950408889634f;
     constexpr float kDrawHeadroom = 8.0f;
     constexpr float kNoShift = -3.0e38f;  // below every finite x log2 e: the first finite element raises it
@@ -255,9 +259,6 @@ categorical_kernel(const void *logits, const uint32_t *__restrict__ identities, 
     }
     __syncthreads();
     const double total = s_before[kDrawWarps];
-    const Words random = philox_block(identities + row * 4, 0);
-    const double uniform =
-        (static_cast<double>(random.x0) * 1048576.0 + static_cast<double>(random.x1 >> 12) + 0.5) * 2.220446049250313e-16;
     const double threshold = total * uniform;
     // pass 2: the run whose span of the cumulative sum holds the threshold.  Every thread finds the
     // owner from the same shared values, so the choice is CTA-uniform.
@@ -288,27 +289,41 @@ categorical_kernel(const void *logits, const uint32_t *__restrict__ identities, 
       __syncthreads();
       // ... then warp 0 chains them, 32 at a time, to the chunk where the cumulative weight first
       // exceeds the threshold, and scans the 32 elements of that chunk
+      // (two levels: each lane adds a strip of consecutive chunk totals, one scan finds the strip, a second
+      // one the chunk inside it: two warp scans instead of one per 32 chunks)
       if (warp == 0) {
-        double cumulative = s_before[owner];
+        const uint32_t strip = (chunks + 31) / 32;  // <= 32 because chunks <= kDrawMaxChunks
+        double strip_total = 0.0;
+        for (uint32_t k = 0; k < strip; ++k) {
+          const uint32_t c = lane * strip + k;
+          if (c < chunks) strip_total += s_chunk[c];
+        }
+        const double start = s_before[owner];
+        const double inclusive = start + warp_inclusive_scan(strip_total, lane);
+        const unsigned crossed = __ballot_sync(kFullMask, strip_total > 0.0 && inclusive > threshold);
         int32_t found = -1;
-        for (uint32_t group = 0; group < chunks && found < 0; group += 32) {
-          const uint32_t c = group + lane;
-          const double inclusive = cumulative + warp_inclusive_scan(c < chunks ? s_chunk[c] : 0.0, lane);
-          const unsigned crossed = __ballot_sync(kFullMask, c < chunks && inclusive > threshold);
-          if (crossed != 0) {
-            const int first = __ffs(crossed) - 1;
-            const double previous = __shfl_sync(kFullMask, inclusive, first > 0 ? first - 1 : 0);
-            const double before = first > 0 ? previous : cumulative;
-            const uint32_t base = owner_begin + 32 * (group + first);
-            const uint32_t i = base + lane;
-            const double weight = i < owner_end ? static_cast<double>(weight_of(load_logit<kDtype>(x, i), neg_scaled_max)) : 0.0;
-            const double within = before + warp_inclusive_scan(weight, lane);
-            const unsigned hit = __ballot_sync(kFullMask, weight > 0.0 && within > threshold);
-            const unsigned massive = __ballot_sync(kFullMask, weight > 0.0);
-            // the scan and the tree may disagree in the last bit: then the chunk's last element of mass
-            found = static_cast<int32_t>(base + (hit != 0 ? __ffs(hit) - 1 : 31 - __clz(massive)));
-          }
-          cumulative = __shfl_sync(kFullMask, inclusive, 31);
+        if (crossed != 0) {
+          const int first = __ffs(crossed) - 1;
+          const double previous = __shfl_sync(kFullMask, inclusive, first > 0 ? first - 1 : 0);
+          const double strip_before = first > 0 ? previous : start;
+          const uint32_t c = first * strip + lane;
+          const bool mine = lane < strip && c < chunks;
+          const double chunk_total = mine ? s_chunk[c] : 0.0;
+          const double through = strip_before + warp_inclusive_scan(chunk_total, lane);
+          const unsigned reached = __ballot_sync(kFullMask, mine && chunk_total > 0.0 && through > threshold);
+          const unsigned filled = __ballot_sync(kFullMask, mine && chunk_total > 0.0);  // not empty: the strip's total is positive
+          // the strip sums and the scan may disagree in the last bit: then the strip's last chunk of mass
+          const int chosen = reached != 0 ? __ffs(reached) - 1 : 31 - __clz(filled);
+          const double chunk_previous = __shfl_sync(kFullMask, through, chosen > 0 ? chosen - 1 : 0);
+          const double before = chosen > 0 ? chunk_previous : strip_before;
+          const uint32_t base = owner_begin + 32 * (first * strip + chosen);
+          const uint32_t i = base + lane;
+          const double weight = i < owner_end ? static_cast<double>(weight_of(load_logit<kDtype>(x, i), neg_scaled_max)) : 0.0;
+          const double within = before + warp_inclusive_scan(weight, lane);
+          const unsigned hit = __ballot_sync(kFullMask, weight > 0.0 && within > threshold);
+          const unsigned massive = __ballot_sync(kFullMask, weight > 0.0);  // not empty: the chunk's total is positive
+          // the same for the elements: the chunk's last element of mass
+          found = static_cast<int32_t>(base + (hit != 0 ? __ffs(hit) - 1 : 31 - __clz(massive)));
         }
         if (lane == 0) {
           s_selected = found;
