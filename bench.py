@@ -759,52 +759,74 @@ def small_shapes(torch, iterations: int = 200):
 
 
 def run_e2e(torch, ops, abi, shard_rows: int, steps: int, warmup: int):
-    """One pass from pinned host buffers: chunks flow host -> device -> kernel -> host on rotating
-    streams so both copy directions and the kernels overlap."""
-    chunk_rows = min(shard_rows, 4096)                     # 64 MiB of bf16 per chunk
+    """One pass from pinned host buffers through the C ABI and back, as a three-stage pipeline: a stream that
+    only copies host -> device, one that only runs the kernel, one that only copies device -> host, chained
+    per chunk by events over four rotating sets of device buffers.  Both copy directions therefore run all
+    the time (chunks on one stream each would fall into step: all copying in, then all copying out).  Timed
+    with CUDA events from the first copy in to the last copy out."""
+    chunk_rows = min(shard_rows, 4096, max(1024, shard_rows // 16))   # 64 MiB of bf16 per chunk, at least 16 chunks
     chunks = (shard_rows + chunk_rows - 1) // chunk_rows
-    lanes = min(3, chunks)
+    lanes = min(4, chunks)
     host_in = torch.empty((shard_rows, SWEEP_COLS), dtype=torch.bfloat16, pin_memory=True)
     host_in.copy_(torch.randn(1024, SWEEP_COLS).mul_(0.02).bfloat16().repeat((shard_rows + 1023) // 1024, 1)[:shard_rows])
     host_blocks = torch.empty(shard_rows * SWEEP_COLS // 32 * 34, dtype=torch.uint8, pin_memory=True)
     host_decoded = torch.empty((shard_rows, SWEEP_COLS), dtype=torch.bfloat16, pin_memory=True)
     host_sums = torch.empty(chunks, dtype=torch.float64, pin_memory=True)
-    streams = [torch.cuda.Stream() for _ in range(lanes)]
+    copy_in, compute, copy_out = torch.cuda.Stream(), torch.cuda.Stream(), torch.cuda.Stream()
     dev_in = [torch.empty((chunk_rows, SWEEP_COLS), dtype=torch.bfloat16, device="cuda") for _ in range(lanes)]
     dev_blocks = [torch.empty(chunk_rows * SWEEP_COLS // 32 * 34, dtype=torch.uint8, device="cuda") for _ in range(lanes)]
     dev_decoded = [torch.empty((chunk_rows, SWEEP_COLS), dtype=torch.bfloat16, device="cuda") for _ in range(lanes)]
     dev_sums = torch.zeros(chunks, dtype=torch.float64, device="cuda")
     workspaces = [ops.make_workspace("cuda", chunk_rows * SWEEP_COLS) for _ in range(lanes)]
+    arrived = [torch.cuda.Event() for _ in range(lanes)]     # the chunk is on the device
+    consumed = [torch.cuda.Event() for _ in range(lanes)]    # the kernel has read it: the input set is free
+    produced = [torch.cuda.Event() for _ in range(lanes)]    # the kernel's outputs are complete
+    drained = [torch.cuda.Event() for _ in range(lanes)]     # the outputs are on the host: the output set is free
+    first, last = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
     lib = abi.load()
     block_bytes_per_row = SWEEP_COLS // 32 * 34
 
     def one_pass():
+        first.record(copy_in)
         for c in range(chunks):
             lane = c % lanes
-            first = c * chunk_rows
-            rows = min(chunk_rows, shard_rows - first)
-            with torch.cuda.stream(streams[lane]):
-                dev_in[lane][:rows].copy_(host_in[first:first + rows], non_blocking=True)
+            begin = c * chunk_rows
+            rows = min(chunk_rows, shard_rows - begin)
+            with torch.cuda.stream(copy_in):
+                if c >= lanes:
+                    copy_in.wait_event(consumed[lane])
+                dev_in[lane][:rows].copy_(host_in[begin:begin + rows], non_blocking=True)
+                arrived[lane].record(copy_in)
+            with torch.cuda.stream(compute):
+                compute.wait_event(arrived[lane])
+                if c >= lanes:
+                    compute.wait_event(drained[lane])
                 abi.check("roundtrip", lib.hyle_b200_q8_0_roundtrip_bf16(
-                    streams[lane].cuda_stream, dev_in[lane].data_ptr(), rows * SWEEP_COLS, dev_blocks[lane].data_ptr(),
+                    compute.cuda_stream, dev_in[lane].data_ptr(), rows * SWEEP_COLS, dev_blocks[lane].data_ptr(),
                     dev_decoded[lane].data_ptr(), dev_sums[c:].data_ptr(), None, workspaces[lane].data_ptr(),
                     workspaces[lane].numel()))
-                host_blocks[first * block_bytes_per_row:(first + rows) * block_bytes_per_row].copy_(
+                consumed[lane].record(compute)
+                produced[lane].record(compute)
+            with torch.cuda.stream(copy_out):
+                copy_out.wait_event(produced[lane])
+                host_blocks[begin * block_bytes_per_row:(begin + rows) * block_bytes_per_row].copy_(
                     dev_blocks[lane][:rows * block_bytes_per_row], non_blocking=True)
-                host_decoded[first:first + rows].copy_(dev_decoded[lane][:rows], non_blocking=True)
-        for s in streams:
-            s.synchronize()
-        host_sums.copy_(dev_sums)
-        return float(host_sums.sum())
+                host_decoded[begin:begin + rows].copy_(dev_decoded[lane][:rows], non_blocking=True)
+                drained[lane].record(copy_out)
+        with torch.cuda.stream(copy_out):
+            host_sums.copy_(dev_sums, non_blocking=True)   # ordered behind the last kernel through produced[]
+            last.record(copy_out)
+        last.synchronize()
+        return float(host_sums.sum()), first.elapsed_time(last) * 1e-3
 
     for _ in range(warmup):
         one_pass()
     torch.cuda.synchronize()
-    t0 = time.perf_counter()
+    seconds = 0.0
     for _ in range(steps):
-        total = one_pass()
+        total, elapsed = one_pass()
+        seconds += elapsed / steps
     torch.cuda.synchronize()
-    seconds = (time.perf_counter() - t0) / steps
     h2d = shard_rows * SWEEP_COLS * 2
     d2h = shard_rows * block_bytes_per_row + shard_rows * SWEEP_COLS * 2 + chunks * 8
     return seconds, h2d, d2h, total
