@@ -35,7 +35,7 @@ STATUS_SCAN_OVERFLOW = 16
 STATUS_STREAM_WAIT_TIMEOUT = 32
 EXCHANGE_MAX_RANKS, EXCHANGE_MAILBOX_BYTES, EXCHANGE_HANDLE_BYTES = 8, 256, 64
 
-ABI_VERSION = 17
+ABI_VERSION = 18
 
 _p = ctypes.c_void_p
 _u64 = ctypes.c_uint64
@@ -67,6 +67,7 @@ SIGNATURES = {
     "hyle_b200_cast": (_i, [_p, _i, _i, _p, _p, _u64]),
     "hyle_b200_masked_softmax_f16": (_i, [_p, _p, _p, _u64, _f, _p, _u64, _u64]),
     "hyle_b200_reduce_rows_extremum": (_i, [_p, _i, _i, _p, _p, _u64, _u64]),
+    "hyle_b200_selfcheck_q8_0_scale": (_i, [_p, _p]),
     "hyle_b200_rms_norm": (_i, [_p, _i, _p, _p, _i, _p, _u64, _u64, _f]),
     "hyle_b200_additive_masked_softmax_f16": (_i, [_p, _p, _p, _u64, _f, _p, _u64, _u64]),
     "hyle_b200_cast_f32_to_bf16": (_i, [_p, _p, _p, _u64]),

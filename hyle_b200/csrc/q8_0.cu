@@ -13,6 +13,8 @@
 // produces are staged in shared memory and leave as 16-byte coalesced stores.
 #include "common.cuh"
 
+#include <math_constants.h>
+
 #include <cstring>
 
 namespace hb {
@@ -36,19 +38,34 @@ constexpr uint32_t kLimitBitsF32 = 0x4afde040u;  // bits of 8319008.0f = 65504 *
 //   magnitude = f - 2^23         exact
 // The signed integer is then formed as 1.5 * 2^23 + sign * magnitude, whose bit pattern holds the
 // two's-complement code in its low byte; subtracting 1.5 * 2^23 again gives the code as a float.
+// The signed integer is the magnitude with p's sign bit (one logic operation); added to 1.5 * 2^23 it
+// gives a bit pattern whose low byte is the two's-complement code.  Five FP32-pipe operations per value.
 struct Rounded {
-  float value;     // roundf(p) as a float; +0 when the code is 0, like (float)(int8_t)code
+  float value;     // roundf(p) as a float; -0 when p < 0 rounds to 0: the decode adds +0 (see decoded_value)
   uint32_t bits;   // bit pattern whose low byte is the int8 code
 };
 __device__ __forceinline__ Rounded round_half_away(float p) {
   const float f = __fadd_rz(__fadd_rz(fabsf(p), 0.5f), 8388608.0f);
   const float magnitude = __fadd_rn(f, -8388608.0f);
-  const float sign = __uint_as_float((__float_as_uint(p) & 0x80000000u) | 0x3f800000u);  // +-1
-  const float shifted = fmaf(magnitude, sign, 12582912.0f);  // 1.5 * 2^23 + signed integer, exact
   Rounded r;
-  r.bits = __float_as_uint(shifted);
-  r.value = __fadd_rn(shifted, -12582912.0f);
+  r.value = __uint_as_float(__float_as_uint(magnitude) | (__float_as_uint(p) & 0x80000000u));
+  r.bits = __float_as_uint(__fadd_rn(r.value, 12582912.0f));  // 1.5 * 2^23 + signed integer, exact
   return r;
+}
+// scale * (float)code as the CPU forms it: the code 0 is +0 there, so a product of -0 becomes +0
+// (x + +0 is x for every other x, and (-0) + (+0) is +0 in round-to-nearest).
+__device__ __forceinline__ float decoded_value(float scale, float rounded) { return __fmaf_rn(scale, rounded, 0.0f); }
+
+// amax / 127 and 1 / d, correctly rounded like the CPU's two IEEE divisions, without the division
+// sequence: q0 = RN(a * y) with y = RN(1 / 127), r = a - 127 * q0 exactly (one fma), d = RN(q0 + r * y)
+// (Markstein's correction: with a correctly rounded reciprocal and a faithful q0 the result is the correctly
+// rounded quotient); __frcp_rn is the IEEE reciprocal.  hyle_b200_selfcheck_q8_0_scale compares both with
+// __fdiv_rn for EVERY magnitude the kernel accepts (tests/test_gpu_parity.py).
+__device__ __forceinline__ float scale_quotient(float amax) {
+  constexpr float kReciprocal127 = 0.00787401574803149606f;
+  const float q0 = __fmul_rn(amax, kReciprocal127);
+  const float r = __fmaf_rn(-127.0f, q0, amax);
+  return __fmaf_rn(r, kReciprocal127, q0);
 }
 
 // Low bytes of four words -> one word.
@@ -276,11 +293,12 @@ q8_0_kernel(const void *__restrict__ in, uint64_t blocks, unsigned char *__restr
       if (k == sub) mine = m;
     }
     const bool valid = mine <= kLimitBitsF32;
-    const float d = __fdiv_rn(__uint_as_float(mine), 127.0f);
+    const float d = scale_quotient(__uint_as_float(mine));
     const unsigned short scale = f32_to_f16(d);
-    const bool zero_block = !valid || scale == 0;
-    const float my_inverse = zero_block ? 0.0f : __fdiv_rn(1.0f, d);   // 0 marks a zero block
-    const uint32_t my_scale = zero_block ? 0u : static_cast<uint32_t>(scale);
+    // inverse 0: a block whose scale rounds to zero (all its products are +-0, all its codes and decoded
+    // values come out as zeros by themselves); inverse NaN: invalid input, patched below
+    const float my_inverse = !valid ? CUDART_NAN_F : (scale == 0 ? 0.0f : __frcp_rn(d));
+    const uint32_t my_scale = valid ? static_cast<uint32_t>(scale) : 0u;
     invalid_seen |= !valid;
 #pragma unroll
     for (int k = 0; k < kVectorsPerThread; ++k) {
@@ -297,8 +315,15 @@ q8_0_kernel(const void *__restrict__ in, uint64_t blocks, unsigned char *__restr
       for (int i = 0; i < 8; ++i) q[i] = round_half_away(__fmul_rn(v[k][i], inverse));
       uint32_t w0 = pack_low_bytes(q[0].bits, q[1].bits, q[2].bits, q[3].bits);
       uint32_t w1 = pack_low_bytes(q[4].bits, q[5].bits, q[6].bits, q[7].bits);
-      const bool zero = inverse == 0.0f;  // also covers invalid input, where the products are NaN
-      if (zero) w0 = w1 = 0u;
+      // Invalid input (NaN, infinity, a magnitude beyond 65504 * 127) makes the block all zeros.  No valid
+      // block needs a select, so the patch sits behind a warp-uniform branch that is practically never taken.
+      if (__builtin_expect(__any_sync(kFullMask, inverse != inverse), 0)) {
+        if (inverse != inverse) {
+          w0 = w1 = 0u;
+#pragma unroll
+          for (int i = 0; i < 8; ++i) q[i].value = 0.0f;
+        }
+      }
       if constexpr (kEncode) {
         if (full || block < tile_blocks) {
           unsigned short *dst = reinterpret_cast<unsigned short *>(staged[buffer] + block * 34);
@@ -312,11 +337,10 @@ q8_0_kernel(const void *__restrict__ in, uint64_t blocks, unsigned char *__restr
       if constexpr (kDecode) {
         if (full || block < tile_blocks) {
           const float s = f16_to_f32(static_cast<unsigned short>(stored_scale));
-          uint4 out = make_uint4(pack_bf16x2(__fmul_rn(s, q[0].value), __fmul_rn(s, q[1].value)),
-                                 pack_bf16x2(__fmul_rn(s, q[2].value), __fmul_rn(s, q[3].value)),
-                                 pack_bf16x2(__fmul_rn(s, q[4].value), __fmul_rn(s, q[5].value)),
-                                 pack_bf16x2(__fmul_rn(s, q[6].value), __fmul_rn(s, q[7].value)));
-          if (zero) out = make_uint4(0u, 0u, 0u, 0u);
+          uint4 out = make_uint4(pack_bf16x2(decoded_value(s, q[0].value), decoded_value(s, q[1].value)),
+                                 pack_bf16x2(decoded_value(s, q[2].value), decoded_value(s, q[3].value)),
+                                 pack_bf16x2(decoded_value(s, q[4].value), decoded_value(s, q[5].value)),
+                                 pack_bf16x2(decoded_value(s, q[6].value), decoded_value(s, q[7].value)));
           st_stream(reinterpret_cast<uint4 *>(decoded + (first_block + block) * 32 + sub * 8), out);
         }
       }
@@ -480,6 +504,29 @@ unsigned q8_grid(uint64_t blocks) {
 }  // namespace hb
 
 using namespace hb;
+
+// Every magnitude the encoder accepts (bit patterns 0 ... 65504 * 127), and for each the scale it leads to:
+// the two shortcuts against the IEEE divisions they replace.
+__global__ void __launch_bounds__(kThreads) selfcheck_scale_kernel(unsigned long long *mismatches) {
+  unsigned long long bad = 0;
+  for (uint64_t bits = static_cast<uint64_t>(blockIdx.x) * kThreads + threadIdx.x; bits <= kLimitBitsF32;
+       bits += static_cast<uint64_t>(gridDim.x) * kThreads) {
+    const float amax = __uint_as_float(static_cast<uint32_t>(bits));
+    const float d = scale_quotient(amax);
+    bad += __float_as_uint(d) != __float_as_uint(__fdiv_rn(amax, 127.0f));
+    if (f32_to_f16(d) != 0) bad += __float_as_uint(__frcp_rn(d)) != __float_as_uint(__fdiv_rn(1.0f, d));
+  }
+  bad = __reduce_add_sync(kFullMask, static_cast<unsigned>(bad));
+  if ((threadIdx.x & 31) == 0 && bad != 0) atomicAdd(mismatches, bad);
+}
+
+extern "C" int hyle_b200_selfcheck_q8_0_scale(hyle_b200_stream_t stream, unsigned long long *mismatches) {
+  if (mismatches == nullptr || !aligned_to(mismatches, 8)) return HYLE_B200_INVALID_VALUE;
+  auto s = reinterpret_cast<cudaStream_t>(stream);
+  const cudaError_t cleared = cudaMemsetAsync(mismatches, 0, sizeof(unsigned long long), s);
+  if (cleared != cudaSuccess) return static_cast<int>(cleared);
+  return launch(selfcheck_scale_kernel, dim3(static_cast<unsigned>(sm_count()) * 8), dim3(kThreads), 0, s, mismatches);
+}
 
 extern "C" uint64_t hyle_b200_sum_squares_workspace_bytes(uint64_t count) {
   const uint64_t tiles = (count / 32 + kTileBlocks - 1) / kTileBlocks;

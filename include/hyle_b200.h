@@ -43,7 +43,7 @@ extern "C" {
 /* Same object as cudaStream_t; spelled out so C callers need no CUDA header. */
 typedef struct CUstream_st *hyle_b200_stream_t;
 
-#define HYLE_B200_ABI_VERSION 17
+#define HYLE_B200_ABI_VERSION 18
 
 enum hyle_b200_result {
   HYLE_B200_OK = 0,
@@ -416,6 +416,15 @@ HYLE_B200_API int hyle_b200_additive_masked_softmax_f16(hyle_b200_stream_t strea
 /* Cast{f32 -> bf16}, round to nearest even (include/hyle/simd/dtype.h:114-121). */
 HYLE_B200_API int hyle_b200_cast_f32_to_bf16(hyle_b200_stream_t stream, const float *in,
                                              void *out_bf16, uint64_t count);
+
+/* Verification hook, no counterpart in the reference: the encoder forms a block's scale amax / 127
+ * and its reciprocal without the division sequence (a multiplication by RN(1/127) with one fused
+ * correction step; the IEEE reciprocal instruction).  This call compares both, bit for bit, with the
+ * correctly rounded divisions for EVERY magnitude the encoder accepts (2^31-odd bit patterns, a few
+ * milliseconds) and stores the number of disagreements, which must be 0, in *mismatches (device
+ * memory, 8 bytes). */
+HYLE_B200_API int hyle_b200_selfcheck_q8_0_scale(hyle_b200_stream_t stream,
+                                                 unsigned long long *mismatches);
 
 /* ---------------------------------------------------------------------------------------------
  * Q8_0: blocks of 32 values -> 34 bytes {f16 scale (little endian), 32 x int8}

@@ -973,6 +973,30 @@ def _encode_case(oracle, values, dtype):
     return got, invalid
 
 
+def test_q8_0_scale_shortcuts_equal_the_divisions_for_every_magnitude():
+    """amax / 127 by multiplication and one fused correction, and 1 / d by the IEEE reciprocal instruction,
+    against __fdiv_rn for all 2^31-odd magnitudes the encoder accepts: no disagreement."""
+    counter = torch.full((1,), -1, dtype=torch.int64, device=DEV)
+    abi.check("selfcheck", abi.load().hyle_b200_selfcheck_q8_0_scale(torch.cuda.current_stream().cuda_stream, counter.data_ptr()))
+    assert int(counter.item()) == 0
+
+
+def test_q8_0_negative_values_that_round_to_zero_decode_to_plus_zero(oracle):
+    """The code 0 decodes to +0 whatever the sign of the value it came from ((float)(int8_t)0 is +0 on the CPU)."""
+    x = np.zeros((4, 64), np.float32)
+    x[:, 0] = 100.0
+    x[:, 1:9] = -0.3          # |p| < 0.5: code 0
+    x[:, 9:17] = -0.0
+    x[2, :32] = -1e-30        # a block whose scale rounds to zero: all codes 0
+    words = wl.f32_to_bf16(x)
+    want_blocks, want_decoded, _, invalid = oracle.q8_0_roundtrip(words)
+    blocks, decoded, _ = ops.q8_0_roundtrip(to_dev_bf16(words), ops.make_workspace(DEV, words.size))
+    assert not invalid
+    assert np.array_equal(blocks.cpu().numpy().ravel(), want_blocks.ravel())
+    assert np.array_equal(bf16_words(decoded).ravel(), want_decoded.ravel())
+    assert not (bf16_words(decoded) == 0x8000).any()
+
+
 @pytest.mark.parametrize("dtype", ["f32", "bf16", "f16"])
 def test_q8_0_known_answers(oracle, dtype):
     # tests/compute_provider_ggml/native_paged_test.cc:255-276: ties, zero block, three input types
