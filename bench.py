@@ -36,9 +36,9 @@ SWEEP_COLS = 8192
 DEFAULT_ROWS = 262144                       # 4 GiB of bf16: the largest sweep point
 BYTES_PER_ELEMENT = 2 + 34 / 32 + 2         # read bf16, write Q8_0 block share, write decoded bf16
 # dram__bytes_read.sum + dram__bytes_write.sum per element of the round-trip kernel in an ncu capture of a
-# 16384-row launch: 2.00 read + 2.66 written by the end of the kernel (the rest of the 3.06 B/value of
+# 16384-row launch: 2.00 read + 2.73 written by the end of the kernel (the rest of the 3.06 B/value of
 # output is still in L2 then and is written back afterwards).  Traffic grows in proportion to the tensor.
-NCU_TRAFFIC_BYTES_PER_ELEMENT = 4.66
+NCU_TRAFFIC_BYTES_PER_ELEMENT = 4.73
 FALLBACK_HBM_GBS = 6650.0
 METRIC = "Q8_0 quantise+dequantise+sum-of-squares sweep throughput"
 UNIT = "Gelem/s"
