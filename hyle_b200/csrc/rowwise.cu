@@ -409,7 +409,9 @@ __device__ __forceinline__ void scale8(float (&v)[8], float inverse, const void 
   }
 }
 
-template <int kDtype, int kWeight, bool kVec>
+// kKeep > 0: rows of at most kKeep * 256 values (vector path) stay in registers between the two passes,
+// kKeep groups of eight values per lane, all loads in flight at once; the row is read once.
+template <int kDtype, int kWeight, bool kVec, int kKeep = 0>
 __global__ void __launch_bounds__(kThreads)
 rms_stored_warp_kernel(const void *x, const void *weight, void *y, uint64_t rows, uint32_t hidden, float eps) {
   grid_dependency_sync();
@@ -419,6 +421,34 @@ rms_stored_warp_kernel(const void *x, const void *weight, void *y, uint64_t rows
     const char *in = static_cast<const char *>(x) + row * hidden * Stored<kDtype>::kBytes;
     char *out = static_cast<char *>(y) + row * hidden * Stored<kDtype>::kBytes;
     float ss = 0.0f;
+    if constexpr (kVec && kKeep > 0) {
+      float f[kKeep][8];
+      const uint32_t vectors = hidden / 8;
+#pragma unroll
+      for (int k = 0; k < kKeep; ++k) {
+        const uint32_t v = k * 32 + lane;
+        if (v < vectors) {
+          Stored<kDtype>::load8(in, v, f[k]);
+        } else {
+#pragma unroll
+          for (int e = 0; e < 8; ++e) f[k][e] = 0.0f;
+        }
+      }
+#pragma unroll
+      for (int k = 0; k < kKeep; ++k)
+#pragma unroll
+        for (int e = 0; e < 8; ++e) ss = fmaf(f[k][e], f[k][e], ss);
+      const float inverse = inverse_rms(warp_sum(ss), hidden, eps);
+#pragma unroll
+      for (int k = 0; k < kKeep; ++k) {
+        const uint32_t v = k * 32 + lane;
+        if (v < vectors) {
+          scale8<kWeight>(f[k], inverse, weight, v);
+          Stored<kDtype>::store8(out, v, f[k]);
+        }
+      }
+      continue;
+    }
     if constexpr (kVec) {
       for (uint32_t v = lane; v < hidden / 8; v += 32) {
         float f[8];
@@ -511,8 +541,16 @@ int launch_rms_stored(cudaStream_t stream, const void *x, const void *weight, vo
   const int sms = sm_count();
   if (row_bytes <= 8 * 1024) {
     const unsigned grid = clamp_grid((rows + kWarps - 1) / kWarps, static_cast<uint64_t>(sms) * 8);
-    return launch(rms_stored_warp_kernel<kDtype, kWeight, kVec>, dim3(grid), dim3(kThreads), 0, stream, x, weight, y, rows,
-                  static_cast<uint32_t>(hidden), eps);
+    auto go = [&](auto keep_tag) {
+      return launch(rms_stored_warp_kernel<kDtype, kWeight, kVec, decltype(keep_tag)::value>, dim3(grid), dim3(kThreads), 0, stream,
+                    x, weight, y, rows, static_cast<uint32_t>(hidden), eps);
+    };
+    if constexpr (kVec) {
+      if (hidden <= 512) return go(std::integral_constant<int, 2>{});
+      if (hidden <= 1024) return go(std::integral_constant<int, 4>{});
+      if (hidden <= 2048) return go(std::integral_constant<int, 8>{});
+    }
+    return go(std::integral_constant<int, 0>{});
   }
   if (row_bytes > kMaxStoredRowBytes) return HYLE_B200_NOT_SUPPORTED;
   const size_t staged = (static_cast<size_t>(row_bytes) + 15) & ~static_cast<size_t>(15);
