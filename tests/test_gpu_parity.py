@@ -1123,3 +1123,61 @@ def test_q8_0_benchmark_size_chunks_against_checker(oracle):
     # the separate decode of the kernel's own blocks reproduces the fused output across the whole 4 GiB
     again = ops.q8_0_decode(blocks, w.numel())
     assert torch.equal(again.view(torch.int16), decoded.view(torch.int16).ravel())
+
+
+# ---- stream capture ----------------------------------------------------------------------------------------------------------
+def test_a_sequence_of_entry_points_replays_in_a_cuda_graph():
+    """The provider declares its kernels capture-compatible (no synchronisation, no allocation, launch shapes that
+    depend on sizes only).  One graph holds the residual norm, the gating, the streaming logits reduction with
+    its workspace, the Q8_0 round trip with its workspace, the checked scan (two kernels) and the categorical
+    draw; three replays on new inputs must give the bits of the same calls made eagerly, which also shows that
+    every launch leaves its workspace armed for the next."""
+    generator = torch.Generator(device=DEV)
+    x = torch.empty((128, 2048), dtype=torch.bfloat16, device=DEV)
+    r = torch.empty_like(x)
+    w = (torch.rand(2048, device=DEV) + 0.5).bfloat16()
+    gate = torch.empty((64, 6144), dtype=torch.bfloat16, device=DEV)
+    up = torch.empty_like(gate)
+    logits = torch.empty((64, 40000), device=DEV)
+    bank = torch.empty((64, 8192), dtype=torch.bfloat16, device=DEV)
+    counts = torch.empty((32, 4096), dtype=torch.int32, device=DEV)
+    identities = torch.arange(64 * 4, dtype=torch.int32, device=DEV).view(64, 4).contiguous()
+    logits_ws = ops.make_logits_workspace(DEV, 64, 40000)
+    bank_ws = ops.make_workspace(DEV, bank.numel())
+    status = torch.zeros(1, dtype=torch.int32, device=DEV)
+    assert ops.logits_stream_plan(64, 40000) is not None            # this shape does take the streaming kernel
+
+    def refill(seed):
+        generator.manual_seed(seed)
+        for t, scale in ((x, 1.0), (r, 1.0), (gate, 1.5), (up, 1.5), (logits, 4.0), (bank, 0.02)):
+            t.copy_(torch.randn(t.shape, generator=generator, device=DEV) * scale)
+        counts.copy_(torch.randint(-1000, 1000, counts.shape, generator=generator, device=DEV, dtype=torch.int32))
+
+    def sequence():
+        y, h = ops.add_rms_norm(x, r, w, 1e-6)
+        out = ops.swiglu(gate, up)
+        lse, probs, index, value = ops.logits_reduce(logits, workspace=logits_ws, status=status)
+        blocks, decoded, total = ops.q8_0_roundtrip(bank, bank_ws, status=status)
+        prefix = ops.scan(counts, status=status)
+        draw, logp = ops.categorical(logits, identities, status=status)
+        return [y, h, out, lse, probs, index, value, blocks, decoded, total, prefix, draw, logp]
+
+    refill(0)
+    stream = torch.cuda.Stream()
+    graph = torch.cuda.CUDAGraph()
+    with torch.cuda.stream(stream):
+        sequence()                                                   # warm-up outside the capture
+        stream.synchronize()
+        with torch.cuda.graph(graph, stream=stream):
+            captured = sequence()
+    torch.cuda.synchronize()
+    for seed in (1, 2, 3):
+        refill(seed)
+        torch.cuda.synchronize()
+        graph.replay()
+        torch.cuda.synchronize()
+        eager = sequence()
+        torch.cuda.synchronize()
+        for got, want in zip(captured, eager):
+            assert torch.equal(got.view(torch.uint8), want.view(torch.uint8))
+        assert status.item() == 0
