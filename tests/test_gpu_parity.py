@@ -1181,3 +1181,28 @@ def test_a_sequence_of_entry_points_replays_in_a_cuda_graph():
         for got, want in zip(captured, eager):
             assert torch.equal(got.view(torch.uint8), want.view(torch.uint8))
         assert status.item() == 0
+
+
+# ---- more than 2^31 elements, more than 2^32 bytes ---------------------------------------------------------------------------
+def test_elementwise_entries_index_beyond_two_to_the_31_elements():
+    """Unary, Binary (trailing-axis broadcast), Select and Cast on 2^31 + 4104 bf16 / f32 elements: the last elements,
+    and elements on both sides of the 2^31 element and 2^32 byte marks, carry the values of the small case."""
+    count = 2 ** 31 + 4104
+    probes = torch.tensor([0, 1, 2 ** 31 - 8, 2 ** 31 - 1, 2 ** 31, 2 ** 31 + 1, 2 ** 31 + 4096, count - 9, count - 1], device=DEV)
+    x = torch.empty(count, dtype=torch.bfloat16, device=DEV)
+    x.view(torch.int16).copy_(torch.arange(count, device=DEV, dtype=torch.int64).remainder_(24001).sub_(12000).to(torch.int16))
+    x.copy_(x.view(torch.int16).to(torch.bfloat16) * 0.25)            # values -3000 ... 3000, exact in bf16 steps
+    want = x[probes].float()
+    got = ops.unary(abi.UNARY_ABS, x)
+    assert torch.equal(got[probes].float(), want.abs())
+    del got
+    row = torch.arange(8, device=DEV, dtype=torch.float32).bfloat16()       # broadcast of period 8
+    got = ops.binary(abi.BINARY_ADD, x.view(-1, 8), row)
+    assert torch.equal(got.view(-1)[probes].float(), (want + (probes % 8).float()).bfloat16().float())
+    del got
+    got = ops.cast(x, abi.BF16, abi.F32)                                    # 8 GiB written
+    assert torch.equal(got[probes], want)
+    del got
+    condition = (torch.arange(count, device=DEV, dtype=torch.int64).remainder_(3) == 0).to(torch.uint8)
+    got = ops.select(condition, x, ops.unary(abi.UNARY_NEG, x))
+    assert torch.equal(got[probes].float(), torch.where(probes % 3 == 0, want, -want))
