@@ -944,20 +944,27 @@ def run_gpu(args):
     if world > 1:
         dist.barrier()
     torch.cuda.synchronize()
-    kernel_events = [(torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)) for _ in range(args.steps)]
+    # A step is ONE launch unless the sums are combined by a library call behind it; only then is the kernel
+    # bracketed by events of its own (an event between two launches keeps the second from starting under the
+    # first's tail, so the one-launch steps are timed as a whole and divided).
+    bracket = reducer is not None
+    kernel_events = [(torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)) for _ in range(args.steps)] if bracket else []
     start, stop = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
     start.record()
     for k in range(args.steps):
-        kernel_events[k][0].record()
+        if bracket:
+            kernel_events[k][0].record()
         step()
-        kernel_events[k][1].record()
+        if bracket:
+            kernel_events[k][1].record()
         combine()
     stop.record()
     torch.cuda.synchronize()
     if world > 1:
         dist.barrier()
     elapsed_ms = torch.tensor([start.elapsed_time(stop)], dtype=torch.float64, device="cuda")
-    kernel_ms = torch.tensor([statistics.mean(event_pairs_ms(kernel_events))], dtype=torch.float64, device="cuda")
+    launch_ms = statistics.mean(event_pairs_ms(kernel_events)) if bracket else start.elapsed_time(stop) / args.steps
+    kernel_ms = torch.tensor([launch_ms], dtype=torch.float64, device="cuda")
     if world > 1:
         dist.all_reduce(elapsed_ms, op=dist.ReduceOp.MAX)
         dist.all_reduce(kernel_ms, op=dist.ReduceOp.MAX)
@@ -982,7 +989,7 @@ def run_gpu(args):
             b.record()
         torch.cuda.synchronize()
         mine = {"rank": rank, "kernel_alone_us": round(statistics.mean(event_pairs_ms(pairs)) * 1e3, 2),
-                "step_us": round(statistics.mean(event_pairs_ms(kernel_events)) * 1e3, 2)}
+                "step_us": round(launch_ms * 1e3, 2)}
         gathered = [None] * world
         dist.all_gather_object(gathered, mine)
         slowest = max(g["kernel_alone_us"] for g in gathered)
