@@ -14,6 +14,7 @@
 #include "common.cuh"
 
 #include <math_constants.h>
+#include <type_traits>
 
 #include <cstring>
 
@@ -267,84 +268,92 @@ q8_0_kernel(const void *__restrict__ in, uint64_t blocks, unsigned char *__restr
     const uint64_t first_block = tile * kTileBlocks;
     const uint32_t tile_blocks = static_cast<uint32_t>(min(static_cast<uint64_t>(kTileBlocks), blocks - first_block));
     const bool full = tile_blocks == kTileBlocks;
-    float v[kVectorsPerThread][8];
-    uint32_t amax_bits[kVectorsPerThread];
-#pragma unroll
-    for (int k = 0; k < kVectorsPerThread; ++k) {
-      const uint32_t block = k * 64 + (t >> 2);
-      if (full || block < tile_blocks) {
-        load8<kDtype>(in, (first_block + block) * 32 + sub * 8, v[k], amax_bits[k]);
-      } else {
-#pragma unroll
-        for (int i = 0; i < 8; ++i) v[k][i] = 0.0f;
-        amax_bits[k] = 0;
-      }
-    }
+    // The tile's work, compiled twice: a full tile (all but the last) carries no per-block bounds test, so its
+    // loads, staging stores and decoded stores sit in straight-line code (the tests cost three branches with
+    // their convergence barriers per eight values).
     float tile_sum = 0.0f;
-    // Block maxima: after two xor shuffles all four lanes of a group hold the maximum of each of
-    // their four blocks.  The two IEEE divisions per block are then done ONCE: lane `sub` of the
-    // group handles block `sub` and the group shares the results by shuffle.
-    uint32_t mine = 0;
+    auto process = [&](auto full_tag) {
+      constexpr bool kFullTile = decltype(full_tag)::value;
+      float v[kVectorsPerThread][8];
+      uint32_t amax_bits[kVectorsPerThread];
 #pragma unroll
-    for (int k = 0; k < kVectorsPerThread; ++k) {
-      uint32_t m = amax_bits[k];
-      m = max(m, __shfl_xor_sync(kFullMask, m, 1));
-      m = max(m, __shfl_xor_sync(kFullMask, m, 2));
-      if (k == sub) mine = m;
-    }
-    const bool valid = mine <= kLimitBitsF32;
-    const float d = scale_quotient(__uint_as_float(mine));
-    const unsigned short scale = f32_to_f16(d);
-    // inverse 0: a block whose scale rounds to zero (all its products are +-0, all its codes and decoded
-    // values come out as zeros by themselves); inverse NaN: invalid input, patched below
-    const float my_inverse = !valid ? CUDART_NAN_F : (scale == 0 ? 0.0f : __frcp_rn(d));
-    const uint32_t my_scale = valid ? static_cast<uint32_t>(scale) : 0u;
-    invalid_seen |= !valid;
+      for (int k = 0; k < kVectorsPerThread; ++k) {
+        const uint32_t block = k * 64 + (t >> 2);
+        if (kFullTile || block < tile_blocks) {
+          load8<kDtype>(in, (first_block + block) * 32 + sub * 8, v[k], amax_bits[k]);
+        } else {
 #pragma unroll
-    for (int k = 0; k < kVectorsPerThread; ++k) {
-      const uint32_t block = k * 64 + (t >> 2);
-      const int source = (threadIdx.x & 28) + k;  // lane within the warp that divided for block k
-      const float inverse = __shfl_sync(kFullMask, my_inverse, source);
-      const uint32_t stored_scale = __shfl_sync(kFullMask, my_scale, source);
-      if constexpr (kSumSquares) {
-#pragma unroll
-        for (int i = 0; i < 8; ++i) tile_sum = fmaf(v[k][i], v[k][i], tile_sum);
-      }
-      Rounded q[8];
-#pragma unroll
-      for (int i = 0; i < 8; ++i) q[i] = round_half_away(__fmul_rn(v[k][i], inverse));
-      uint32_t w0 = pack_low_bytes(q[0].bits, q[1].bits, q[2].bits, q[3].bits);
-      uint32_t w1 = pack_low_bytes(q[4].bits, q[5].bits, q[6].bits, q[7].bits);
-      // Invalid input (NaN, infinity, a magnitude beyond 65504 * 127) makes the block all zeros.  No valid
-      // block needs a select, so the patch sits behind a warp-uniform branch that is practically never taken.
-      if (__builtin_expect(__any_sync(kFullMask, inverse != inverse), 0)) {
-        if (inverse != inverse) {
-          w0 = w1 = 0u;
-#pragma unroll
-          for (int i = 0; i < 8; ++i) q[i].value = 0.0f;
+          for (int i = 0; i < 8; ++i) v[k][i] = 0.0f;
+          amax_bits[k] = 0;
         }
       }
-      if constexpr (kEncode) {
-        if (full || block < tile_blocks) {
-          unsigned short *dst = reinterpret_cast<unsigned short *>(staged[buffer] + block * 34);
-          if (sub == 0) dst[0] = static_cast<unsigned short>(stored_scale);
-          dst[1 + sub * 4 + 0] = static_cast<unsigned short>(w0 & 0xffffu);
-          dst[1 + sub * 4 + 1] = static_cast<unsigned short>(w0 >> 16);
-          dst[1 + sub * 4 + 2] = static_cast<unsigned short>(w1 & 0xffffu);
-          dst[1 + sub * 4 + 3] = static_cast<unsigned short>(w1 >> 16);
+      // Block maxima: after two xor shuffles all four lanes of a group hold the maximum of each of
+      // their four blocks.  The two IEEE divisions per block are then done ONCE: lane `sub` of the
+      // group handles block `sub` and the group shares the results by shuffle.
+      uint32_t mine = 0;
+#pragma unroll
+      for (int k = 0; k < kVectorsPerThread; ++k) {
+        uint32_t m = amax_bits[k];
+        m = max(m, __shfl_xor_sync(kFullMask, m, 1));
+        m = max(m, __shfl_xor_sync(kFullMask, m, 2));
+        if (k == sub) mine = m;
+      }
+      const bool valid = mine <= kLimitBitsF32;
+      const float d = scale_quotient(__uint_as_float(mine));
+      const unsigned short scale = f32_to_f16(d);
+      // inverse 0: a block whose scale rounds to zero (all its products are +-0, all its codes and decoded
+      // values come out as zeros by themselves); inverse NaN: invalid input, patched below
+      const float my_inverse = !valid ? CUDART_NAN_F : (scale == 0 ? 0.0f : __frcp_rn(d));
+      const uint32_t my_scale = valid ? static_cast<uint32_t>(scale) : 0u;
+      invalid_seen |= !valid;
+#pragma unroll
+      for (int k = 0; k < kVectorsPerThread; ++k) {
+        const uint32_t block = k * 64 + (t >> 2);
+        const int source = (threadIdx.x & 28) + k;  // lane within the warp that divided for block k
+        const float inverse = __shfl_sync(kFullMask, my_inverse, source);
+        const uint32_t stored_scale = __shfl_sync(kFullMask, my_scale, source);
+        if constexpr (kSumSquares) {
+#pragma unroll
+          for (int i = 0; i < 8; ++i) tile_sum = fmaf(v[k][i], v[k][i], tile_sum);
+        }
+        Rounded q[8];
+#pragma unroll
+        for (int i = 0; i < 8; ++i) q[i] = round_half_away(__fmul_rn(v[k][i], inverse));
+        uint32_t w0 = pack_low_bytes(q[0].bits, q[1].bits, q[2].bits, q[3].bits);
+        uint32_t w1 = pack_low_bytes(q[4].bits, q[5].bits, q[6].bits, q[7].bits);
+        // Invalid input (NaN, infinity, a magnitude beyond 65504 * 127) makes the block all zeros.  No valid
+        // block needs a select, so the patch sits behind a warp-uniform branch that is practically never taken.
+        if (__builtin_expect(__any_sync(kFullMask, inverse != inverse), 0)) {
+          if (inverse != inverse) {
+            w0 = w1 = 0u;
+#pragma unroll
+            for (int i = 0; i < 8; ++i) q[i].value = 0.0f;
+          }
+        }
+        if constexpr (kEncode) {
+          if (kFullTile || block < tile_blocks) {
+            unsigned short *dst = reinterpret_cast<unsigned short *>(staged[buffer] + block * 34);
+            if (sub == 0) dst[0] = static_cast<unsigned short>(stored_scale);
+            dst[1 + sub * 4 + 0] = static_cast<unsigned short>(w0 & 0xffffu);
+            dst[1 + sub * 4 + 1] = static_cast<unsigned short>(w0 >> 16);
+            dst[1 + sub * 4 + 2] = static_cast<unsigned short>(w1 & 0xffffu);
+            dst[1 + sub * 4 + 3] = static_cast<unsigned short>(w1 >> 16);
+          }
+        }
+        if constexpr (kDecode) {
+          if (kFullTile || block < tile_blocks) {
+            const float s = f16_to_f32(static_cast<unsigned short>(stored_scale));
+            uint4 out = make_uint4(pack_bf16x2(decoded_value(s, q[0].value), decoded_value(s, q[1].value)),
+                                   pack_bf16x2(decoded_value(s, q[2].value), decoded_value(s, q[3].value)),
+                                   pack_bf16x2(decoded_value(s, q[4].value), decoded_value(s, q[5].value)),
+                                   pack_bf16x2(decoded_value(s, q[6].value), decoded_value(s, q[7].value)));
+            st_stream(reinterpret_cast<uint4 *>(decoded + (first_block + block) * 32 + sub * 8), out);
+          }
         }
       }
-      if constexpr (kDecode) {
-        if (full || block < tile_blocks) {
-          const float s = f16_to_f32(static_cast<unsigned short>(stored_scale));
-          uint4 out = make_uint4(pack_bf16x2(decoded_value(s, q[0].value), decoded_value(s, q[1].value)),
-                                 pack_bf16x2(decoded_value(s, q[2].value), decoded_value(s, q[3].value)),
-                                 pack_bf16x2(decoded_value(s, q[4].value), decoded_value(s, q[5].value)),
-                                 pack_bf16x2(decoded_value(s, q[6].value), decoded_value(s, q[7].value)));
-          st_stream(reinterpret_cast<uint4 *>(decoded + (first_block + block) * 32 + sub * 8), out);
-        }
-      }
-    }
+    };
+    if (full) process(std::true_type{});
+    else process(std::false_type{});
     if constexpr (kSumSquares && !kDynamic) sum += static_cast<double>(tile_sum);
     if constexpr (kDynamic) {
       const float warp_total = warp_sum(tile_sum);
