@@ -69,11 +69,6 @@ __device__ __forceinline__ float scale_quotient(float amax) {
   return __fmaf_rn(r, kReciprocal127, q0);
 }
 
-// Low bytes of four words -> one word.
-__device__ __forceinline__ uint32_t pack_low_bytes(uint32_t a, uint32_t b, uint32_t c, uint32_t d) {
-  return __byte_perm(__byte_perm(a, b, 0x0040), __byte_perm(c, d, 0x0040), 0x5410);
-}
-
 // Eight consecutive values as f32 plus the largest magnitude bit pattern among them.
 template <int kDtype>
 __device__ __forceinline__ void load8(const void *in, uint64_t element, float v[8], uint32_t &amax_bits) {
@@ -243,7 +238,7 @@ __device__ __forceinline__ void finish_sum(double thread_sum, SumSquaresState ws
 // kEncode: write Q8_0 blocks.  kDecode: write decoded bf16.  kSumSquares: accumulate sum x^2.
 // kDynamic (needs kEncode and kSumSquares): tiles come from the workspace's counter.
 template <int kDtype, bool kEncode, bool kDecode, bool kSumSquares, bool kDynamic = false>
-__global__ void __launch_bounds__(kThreads)
+__global__ void __launch_bounds__(kThreads, 4)  // four CTAs per SM: 64 registers
 q8_0_kernel(const void *__restrict__ in, uint64_t blocks, unsigned char *__restrict__ blocks_out,
             unsigned short *__restrict__ decoded, double *sum_out, uint32_t *status_word,
             void *workspace, int out_aligned, const Exchange exchange) {
@@ -306,6 +301,11 @@ q8_0_kernel(const void *__restrict__ in, uint64_t blocks, unsigned char *__restr
       const float my_inverse = !valid ? CUDART_NAN_F : (scale == 0 ? 0.0f : __frcp_rn(d));
       const uint32_t my_scale = valid ? static_cast<uint32_t>(scale) : 0u;
       invalid_seen |= !valid;
+      // Invalid input (NaN, infinity, a magnitude beyond 65504 * 127) makes its block all zeros.  No valid block
+      // needs a select, so the patch is compiled into a second copy of the loop below that a warp enters only
+      // when one of the 32 blocks it handles in this tile is invalid (one vote per tile).
+      auto emit = [&](auto patch_tag) {
+      constexpr bool kPatch = decltype(patch_tag)::value;
 #pragma unroll
       for (int k = 0; k < kVectorsPerThread; ++k) {
         const uint32_t block = k * 64 + (t >> 2);
@@ -319,13 +319,14 @@ q8_0_kernel(const void *__restrict__ in, uint64_t blocks, unsigned char *__restr
         Rounded q[8];
 #pragma unroll
         for (int i = 0; i < 8; ++i) q[i] = round_half_away(__fmul_rn(v[k][i], inverse));
-        uint32_t w0 = pack_low_bytes(q[0].bits, q[1].bits, q[2].bits, q[3].bits);
-        uint32_t w1 = pack_low_bytes(q[4].bits, q[5].bits, q[6].bits, q[7].bits);
-        // Invalid input (NaN, infinity, a magnitude beyond 65504 * 127) makes the block all zeros.  No valid
-        // block needs a select, so the patch sits behind a warp-uniform branch that is practically never taken.
-        if (__builtin_expect(__any_sync(kFullMask, inverse != inverse), 0)) {
+        // two codes per 16-bit store (a block starts on a 2-byte boundary only): the low bytes of two words
+        uint32_t pair[4];
+#pragma unroll
+        for (int i = 0; i < 4; ++i) pair[i] = __byte_perm(q[2 * i].bits, q[2 * i + 1].bits, 0x0040);
+        if constexpr (kPatch) {
           if (inverse != inverse) {
-            w0 = w1 = 0u;
+#pragma unroll
+            for (int i = 0; i < 4; ++i) pair[i] = 0u;
 #pragma unroll
             for (int i = 0; i < 8; ++i) q[i].value = 0.0f;
           }
@@ -334,10 +335,8 @@ q8_0_kernel(const void *__restrict__ in, uint64_t blocks, unsigned char *__restr
           if (kFullTile || block < tile_blocks) {
             unsigned short *dst = reinterpret_cast<unsigned short *>(staged[buffer] + block * 34);
             if (sub == 0) dst[0] = static_cast<unsigned short>(stored_scale);
-            dst[1 + sub * 4 + 0] = static_cast<unsigned short>(w0 & 0xffffu);
-            dst[1 + sub * 4 + 1] = static_cast<unsigned short>(w0 >> 16);
-            dst[1 + sub * 4 + 2] = static_cast<unsigned short>(w1 & 0xffffu);
-            dst[1 + sub * 4 + 3] = static_cast<unsigned short>(w1 >> 16);
+#pragma unroll
+            for (int i = 0; i < 4; ++i) dst[1 + sub * 4 + i] = static_cast<unsigned short>(pair[i]);
           }
         }
         if constexpr (kDecode) {
@@ -351,6 +350,9 @@ q8_0_kernel(const void *__restrict__ in, uint64_t blocks, unsigned char *__restr
           }
         }
       }
+      };
+      if (__builtin_expect(__any_sync(kFullMask, !valid), 0)) emit(std::true_type{});
+      else emit(std::false_type{});
     };
     if (full) process(std::true_type{});
     else process(std::false_type{});
