@@ -205,8 +205,30 @@ def event_pairs_ms(pairs):
     return [a.elapsed_time(b) for a, b in pairs]
 
 
-def time_op(torch, launch, sets: int, iterations: int = 40, warmup: int = 5):
-    """Average device time of `launch(i)` over rotating buffer sets (footprint >> L2), CUDA events."""
+class StreamArgument:
+    """The stream argument of the timed ctypes calls: a handle that `time_op` can redirect, so the same
+    `launch` closure runs on the default stream and, for the graph measurement, on the capturing one.  (A
+    plain attribute: resolving torch's current stream on every launch costs more than a small kernel.)"""
+
+    def __init__(self, torch):
+        self.use(torch.cuda.current_stream())
+
+    def use(self, stream):
+        self._as_parameter_ = ctypes.c_void_p(stream.cuda_stream)
+
+
+STREAM = None  # set by the functions that time operators
+
+
+class Timed(float):
+    """Milliseconds per launch in a stream of eager launches; `.graph` = the same launches replayed from a
+    CUDA graph (no host launch cost between them), or None where that was not measured."""
+    graph = None
+
+
+def time_op(torch, launch, sets: int, iterations: int = 40, warmup: int = 5, graph: bool = True):
+    """Average device time of `launch(i)` over rotating buffer sets (footprint >> L2), CUDA events: issued
+    eagerly back to back, and (`.graph`) the same sequence captured once into a CUDA graph and replayed."""
     for i in range(warmup):
         code = launch(i % sets)
         if code not in (None, 0):
@@ -218,7 +240,27 @@ def time_op(torch, launch, sets: int, iterations: int = 40, warmup: int = 5):
         launch(i % sets)
     stop.record()
     torch.cuda.synchronize()
-    return start.elapsed_time(stop) / iterations
+    result = Timed(start.elapsed_time(stop) / iterations)
+    if graph and STREAM is not None:
+        side = torch.cuda.Stream()
+        captured = torch.cuda.CUDAGraph()
+        with torch.cuda.stream(side):
+            STREAM.use(side)
+            launch(0)
+            side.synchronize()
+            with torch.cuda.graph(captured, stream=side):
+                for i in range(iterations):
+                    launch(i % sets)
+            captured.replay()
+            side.synchronize()
+            start.record(side)
+            captured.replay()
+            stop.record(side)
+            side.synchronize()
+        STREAM.use(torch.cuda.current_stream())  # outside the `with`: the stream the eager launches use
+        result.graph = start.elapsed_time(stop) / iterations
+        del captured
+    return result
 
 
 def other_ops(torch, peak_gbs, only=None, iterations=40):
@@ -229,16 +271,22 @@ def other_ops(torch, peak_gbs, only=None, iterations=40):
 
     results = []
     dev = "cuda"
-    lib, stream = abi.load(), torch.cuda.current_stream().cuda_stream
+    global STREAM
+    lib, stream = abi.load(), StreamArgument(torch)
+    STREAM = stream
 
     def wanted(name):
         return only is None or name in only
 
     def report(name, shape, elements, algorithmic_bytes, ms, sets):
         gbs = algorithmic_bytes / (ms * 1e-3) / 1e9
-        results.append({"op": name, "shape": shape, "us": ms * 1e3, "GB/s": gbs, "Gelem/s": elements / (ms * 1e-3) / 1e9,
-                        "roofline_frac": gbs / peak_gbs, "algorithmic_bytes": algorithmic_bytes,
-                        "buffer_sets": sets})
+        entry = {"op": name, "shape": shape, "us": ms * 1e3, "GB/s": gbs, "Gelem/s": elements / (ms * 1e-3) / 1e9,
+                 "roofline_frac": gbs / peak_gbs, "algorithmic_bytes": algorithmic_bytes, "buffer_sets": sets}
+        replayed = getattr(ms, "graph", None)
+        if replayed:  # the same launches replayed from a CUDA graph
+            entry["us_graph"] = replayed * 1e3
+            entry["roofline_frac_graph"] = algorithmic_bytes / (replayed * 1e-3) / 1e9 / peak_gbs
+        results.append(entry)
 
     # 1: f32 broadcast add + row sum + row max, 4096 x 4096
     if wanted("add_bias_row_sum_max_f32"):
@@ -449,7 +497,7 @@ def other_ops(torch, peak_gbs, only=None, iterations=40):
             reference = RefPaged()
             ms = time_op(torch, lambda i: reference.paged_append(
                 stream, arenas[i].data_ptr(), fresh[i].data_ptr(), episode.data_ptr(), page_rows, pages, new_count,
-                new_count // page_rows, row_bytes), sets, iterations)
+                new_count // page_rows, row_bytes), sets, iterations, graph=False)
             report("paged_append_REFERENCE_KERNEL", "the reference's cuda_paged_append.cu on the same episode (not this library)",
                    new_count, 2 * new_count * row_bytes, ms, sets)
         # the same rows through the device-lengths variant: 32 requests of 128 new rows after 24 old ones
@@ -738,8 +786,15 @@ def small_shapes(torch, iterations: int = 200):
     fraction is meaningful at 4 KiB ... 10 MB), back to back on one stream with their inputs in L2."""
     from hyle_b200 import abi
 
-    lib, stream, dev = abi.load(), torch.cuda.current_stream().cuda_stream, "cuda"
+    global STREAM
+    lib, stream, dev = abi.load(), StreamArgument(torch), "cuda"
+    STREAM = stream
     shapes = {}
+
+    def record(name, ms):
+        shapes[name] = round(ms * 1e3, 2)
+        if ms.graph:
+            shapes[name + " (graph replay)"] = round(ms.graph * 1e3, 2)
     weight = (torch.rand(2048, device=dev) + 0.5).bfloat16()
     for tokens in (1, 64):
         x, r = torch.randn(tokens, 2048, device=dev).bfloat16(), torch.randn(tokens, 2048, device=dev).bfloat16()
@@ -747,13 +802,13 @@ def small_shapes(torch, iterations: int = 200):
         ms = time_op(torch, lambda i: lib.hyle_b200_add_rms_norm_bf16(
             stream, x.data_ptr(), r.data_ptr(), weight.data_ptr(), abi.BF16, y.data_ptr(), h.data_ptr(), tokens, 2048, 1e-6),
             1, iterations)
-        shapes[f"add_rms_norm_bf16 T={tokens}"] = round(ms * 1e3, 2)
+        record(f"add_rms_norm_bf16 T={tokens}", ms)
     for tokens in (1, 8, 32):
         g, u = torch.randn(tokens, 6144, device=dev).bfloat16(), torch.randn(tokens, 6144, device=dev).bfloat16()
         o = torch.empty_like(g)
         ms = time_op(torch, lambda i: lib.hyle_b200_swiglu_bf16(
             stream, g.data_ptr(), u.data_ptr(), o.data_ptr(), tokens, 6144, 6144, 6144), 1, iterations)
-        shapes[f"swiglu_bf16 T={tokens}"] = round(ms * 1e3, 2)
+        record(f"swiglu_bf16 T={tokens}", ms)
     for batch in (1, 16):
         logits = 4.0 * torch.randn(batch, 151936, device=dev)
         probs = torch.empty(batch, 151936, dtype=torch.bfloat16, device=dev)
@@ -762,7 +817,7 @@ def small_shapes(torch, iterations: int = 200):
         ms = time_op(torch, lambda i: lib.hyle_b200_logits_reduce_f32(
             stream, logits.data_ptr(), batch, 151936, lse.data_ptr(), probs.data_ptr(), idx.data_ptr(), val.data_ptr(),
             None, 0, None), 1, iterations)
-        shapes[f"logits_reduce_f32 B={batch}"] = round(ms * 1e3, 2)
+        record(f"logits_reduce_f32 B={batch}", ms)
     return shapes
 
 
@@ -1138,7 +1193,10 @@ def run_gpu(args):
             workloads[f"{number}:{name}"] = {
                 "shape": entry["shape"], "us": round(entry["us"], 2), "GB/s": round(entry["GB/s"], 1),
                 "Gelem/s": round(entry["Gelem/s"], 2), "frac_of_measured_hbm": round(entry["roofline_frac"], 4),
-                "frac_of_nominal_8TB/s": round(entry["GB/s"] / 8000.0, 4), "cpu_baseline": baselines.get(name)}
+                "frac_of_nominal_8TB/s": round(entry["GB/s"] / 8000.0, 4),
+                "us_graph": None if "us_graph" not in entry else round(entry["us_graph"], 2),
+                "frac_of_measured_hbm_graph": None if "us_graph" not in entry else round(entry["roofline_frac_graph"], 4),
+                "cpu_baseline": baselines.get(name)}
         workloads["5:q8_0_roundtrip_bf16"] = {
             "shape": f"{args.rows}x{SWEEP_COLS}", "us": round(kernel_s * 1e6, 1), "GB/s": round(achieved, 1),
             "Gelem/s": round(value, 2), "frac_of_measured_hbm": round(achieved / peak_gbs, 4),
