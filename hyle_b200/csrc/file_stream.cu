@@ -83,22 +83,23 @@ struct hyle_b200_file_stream {
         if (cudaStreamWaitEvent(copy_stream, done[slot], 0) != cudaSuccess) return fail(HYLE_B200_IO_ERROR);
       }
       const uint64_t size = chunk_size(index);
-      uint64_t have = 0;
+      uint64_t have = 0, calls = 0;
       while (have < size) {
         const ssize_t got = pread(fd, pinned[slot] + have, size - have, static_cast<off_t>(file_offset + index * chunk_bytes + have));
-        ++report.io_calls;
+        ++calls;
         if (got < 0 && errno == EINTR) continue;
         if (got <= 0) return fail(HYLE_B200_IO_ERROR);  // error, or the file ends inside the range
         have += static_cast<uint64_t>(got);
       }
-      report.bytes_read += size;
       if (cudaMemcpyAsync(resident[slot], pinned[slot], size, cudaMemcpyHostToDevice, copy_stream) != cudaSuccess ||
           cudaEventRecord(copied[slot], copy_stream) != cudaSuccess)
         return fail(HYLE_B200_IO_ERROR);
-      ++report.copies;
-      report.bytes_copied += size;
       {
-        std::lock_guard lock(mutex);
+        std::lock_guard lock(mutex);  // the report is read under the same lock
+        report.io_calls += calls;
+        report.bytes_read += size;
+        ++report.copies;
+        report.bytes_copied += size;
         issued = index + 1;
         if (closing) return;
       }
