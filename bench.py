@@ -545,7 +545,15 @@ def other_ops(torch, peak_gbs, only=None, iterations=40):
                 stream, logits[i].data_ptr(), rows, cols, lse.data_ptr(), probs[i].data_ptr(), idx.data_ptr(),
                 val.data_ptr(), None, 0, None), sets, max(1, iterations // 2))
             report("logits_reduce_f32_cluster_kernel", "256x151936", rows * cols, rows * cols * 6 + rows * 12, ms, sets)
-        del logits, probs, scratch
+        # Softmax and LogSoftmax alone (f32 in, f32 out: 8 B per value), the same streaming kernel
+        del probs
+        out32 = [torch.empty(rows, cols, device=dev) for _ in range(2)]
+        for name, kind in (("softmax_f32", abi.SOFTMAX), ("log_softmax_f32", abi.LOG_SOFTMAX)):
+            ms = time_op(torch, lambda i: lib.hyle_b200_softmax_f32(
+                stream, kind, logits[i].data_ptr(), out32[i % 2].data_ptr(), rows, cols, scratch.data_ptr(), scratch.numel(),
+                None), sets, max(1, iterations // 2))
+            report(name, "256x151936", rows * cols, rows * cols * 8, ms, sets)
+        del logits, out32, scratch
     torch.cuda.empty_cache()
     return results
 
