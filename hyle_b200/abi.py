@@ -35,7 +35,7 @@ STATUS_SCAN_OVERFLOW = 16
 STATUS_STREAM_WAIT_TIMEOUT = 32
 EXCHANGE_MAX_RANKS, EXCHANGE_MAILBOX_BYTES, EXCHANGE_HANDLE_BYTES = 8, 256, 64
 
-ABI_VERSION = 18
+ABI_VERSION = 19
 
 _p = ctypes.c_void_p
 _u64 = ctypes.c_uint64
@@ -89,6 +89,7 @@ SIGNATURES = {
     "hyle_b200_exchange_close": (_i, [_p]),
     "hyle_b200_exchange_destroy": (_i, [_p]),
     "hyle_b200_file_stream_open": (_i, [ctypes.c_char_p, _u64, _u64, _p, ctypes.POINTER(_p)]),
+    "hyle_b200_file_stream_read_group": (_i, [_p, _p, _p, _u32]),
     "hyle_b200_file_stream_next": (_i, [_p, _p, ctypes.POINTER(_p), ctypes.POINTER(_u64), ctypes.POINTER(_u64)]),
     "hyle_b200_file_stream_get_report": (_i, [_p, _p]),
     "hyle_b200_file_stream_close": (_i, [_p]),
@@ -108,6 +109,11 @@ class StreamTuning(ctypes.Structure):
 class FileStreamOptions(ctypes.Structure):
     """hyle_b200_file_stream_options: zero fields take the defaults (8 MiB chunks, 4 slots)."""
     _fields_ = [("chunk_bytes", _u64), ("slots", _u32), ("reserved", _u32), ("chunk_granule", _u64)]
+
+
+class FileRange(ctypes.Structure):
+    """hyle_b200_file_range."""
+    _fields_ = [("file_offset", _u64), ("bytes", _u64), ("destination", ctypes.c_void_p)]
 
 
 class FileStreamReport(ctypes.Structure):

@@ -55,6 +55,8 @@ struct hyle_b200_file_stream {
   uint64_t released = 0;    // chunks whose done[] event has been recorded (consumer -> reader)
   int error = HYLE_B200_OK; // first reader failure
   bool closing = false;
+  uint64_t file_bytes = 0;  // size of the file at open
+  uint64_t group_chunks = 0;  // chunks copied by read_group so far (slot rotation across groups)
   hyle_b200_file_stream_report report{};
 
   uint64_t chunk_size(uint64_t index) const {
@@ -132,6 +134,7 @@ extern "C" int hyle_b200_file_stream_open(const char *path, uint64_t file_offset
     return static_cast<int>(cudaErrorMemoryAllocation);
   }
   stream->fd = fd;
+  stream->file_bytes = static_cast<uint64_t>(info.st_size);
   stream->file_offset = file_offset;
   stream->bytes = bytes;
   stream->chunk_bytes = chunk;
@@ -141,7 +144,7 @@ extern "C" int hyle_b200_file_stream_open(const char *path, uint64_t file_offset
   if (error == cudaSuccess) error = cudaStreamCreateWithFlags(&stream->copy_stream, cudaStreamNonBlocking);
   for (uint32_t s = 0; s < slots && error == cudaSuccess; ++s) {
     error = cudaHostAlloc(reinterpret_cast<void **>(&stream->pinned[s]), chunk, cudaHostAllocDefault);
-    if (error == cudaSuccess) error = cudaMalloc(reinterpret_cast<void **>(&stream->resident[s]), chunk);
+    if (error == cudaSuccess && bytes != 0) error = cudaMalloc(reinterpret_cast<void **>(&stream->resident[s]), chunk);
     if (error == cudaSuccess) error = cudaEventCreateWithFlags(&stream->copied[s], cudaEventDisableTiming);
     if (error == cudaSuccess) error = cudaEventCreateWithFlags(&stream->done[s], cudaEventDisableTiming);
   }
@@ -150,7 +153,7 @@ extern "C" int hyle_b200_file_stream_open(const char *path, uint64_t file_offset
     return static_cast<int>(error);
   }
   stream->report.staging_bytes = chunk * slots;
-  stream->report.device_bytes = chunk * slots;
+  stream->report.device_bytes = bytes != 0 ? chunk * slots : 0;
   stream->report.chunk_bytes = chunk;
   stream->report.chunks = stream->chunks;
   if (stream->chunks != 0) stream->reader = std::thread([stream] { stream->read_loop(); });
@@ -190,6 +193,55 @@ extern "C" int hyle_b200_file_stream_next(hyle_b200_file_stream *stream, hyle_b2
   if (chunk_offset != nullptr) *chunk_offset = index * stream->chunk_bytes;
   stream->handed = index + 1;
   return HYLE_B200_OK;
+}
+
+// A group of byte ranges -> device destinations of the caller's own, through the pinned slots: the calling
+// thread reads chunk k + 1 while the copy of chunk k is in flight.
+extern "C" int hyle_b200_file_stream_read_group(hyle_b200_file_stream *stream, hyle_b200_stream_t consumer,
+                                                const hyle_b200_file_range *ranges, uint32_t count) {
+  if (stream == nullptr || (ranges == nullptr && count != 0) || stream->chunks != 0) return HYLE_B200_INVALID_VALUE;
+  for (uint32_t r = 0; r < count; ++r) {
+    if (ranges[r].bytes != 0 && ranges[r].destination == nullptr) return HYLE_B200_INVALID_VALUE;
+    if (ranges[r].file_offset > stream->file_bytes || stream->file_bytes - ranges[r].file_offset < ranges[r].bytes)
+      return HYLE_B200_IO_ERROR;  // nothing has been copied
+  }
+  bool copied_any = false;
+  for (uint32_t r = 0; r < count; ++r) {
+    for (uint64_t done_bytes = 0; done_bytes < ranges[r].bytes;) {
+      const uint32_t slot = static_cast<uint32_t>(stream->group_chunks % stream->slots);
+      // the slot's previous copy must have left the pinned buffer (an event never recorded is complete)
+      if (cudaEventSynchronize(stream->copied[slot]) != cudaSuccess) return HYLE_B200_IO_ERROR;
+      const uint64_t size = ranges[r].bytes - done_bytes < stream->chunk_bytes ? ranges[r].bytes - done_bytes : stream->chunk_bytes;
+      uint64_t have = 0, calls = 0;
+      while (have < size) {
+        const ssize_t got = pread(stream->fd, stream->pinned[slot] + have, size - have,
+                                  static_cast<off_t>(ranges[r].file_offset + done_bytes + have));
+        ++calls;
+        if (got < 0 && errno == EINTR) continue;
+        if (got <= 0) return HYLE_B200_IO_ERROR;  // the file shrank after open, or a read error
+        have += static_cast<uint64_t>(got);
+      }
+      cudaError_t error = cudaMemcpyAsync(static_cast<unsigned char *>(ranges[r].destination) + done_bytes, stream->pinned[slot],
+                                          size, cudaMemcpyHostToDevice, stream->copy_stream);
+      if (error == cudaSuccess) error = cudaEventRecord(stream->copied[slot], stream->copy_stream);
+      if (error != cudaSuccess) return static_cast<int>(error);
+      {
+        std::lock_guard lock(stream->mutex);
+        stream->report.io_calls += calls;
+        stream->report.bytes_read += size;
+        stream->report.bytes_copied += size;
+        ++stream->report.copies;
+      }
+      ++stream->group_chunks;
+      done_bytes += size;
+      copied_any = true;
+    }
+  }
+  if (!copied_any) return HYLE_B200_OK;
+  // the consumer's stream continues after the group's last copy
+  const uint32_t last = static_cast<uint32_t>((stream->group_chunks - 1) % stream->slots);
+  const cudaError_t chained = cudaStreamWaitEvent(reinterpret_cast<cudaStream_t>(consumer), stream->copied[last], 0);
+  return chained == cudaSuccess ? HYLE_B200_OK : static_cast<int>(chained);
 }
 
 extern "C" int hyle_b200_file_stream_get_report(hyle_b200_file_stream *stream, hyle_b200_file_stream_report *report) {

@@ -552,6 +552,22 @@ class FileStream:
                 return
             yield pointer.value, size.value, offset.value
 
+    def read_group(self, ranges) -> None:
+        """Copy byte ranges of the file into device tensors: ``ranges`` = [(file offset, tensor or (pointer, bytes))].
+        Only for a stream opened with ``nbytes == 0``.  The current stream waits for the group's last copy."""
+        table = (abi.FileRange * len(ranges))()
+        for entry, (offset, target) in zip(table, ranges):
+            if isinstance(target, torch.Tensor):
+                _device_tensor(target, "destination")
+                if not target.is_contiguous():
+                    raise ValueError("destinations must be dense")
+                pointer, size = target.data_ptr(), target.numel() * target.element_size()
+            else:
+                pointer, size = target
+            entry.file_offset, entry.bytes, entry.destination = offset, size, pointer
+        abi.check("hyle_b200_file_stream_read_group", abi.load().hyle_b200_file_stream_read_group(
+            self._handle, _stream(), ctypes.addressof(table) if len(ranges) else None, len(ranges)))
+
     def report(self) -> abi.FileStreamReport:
         report = abi.FileStreamReport()
         abi.check("hyle_b200_file_stream_get_report", abi.load().hyle_b200_file_stream_get_report(self._handle, ctypes.addressof(report)))

@@ -43,7 +43,7 @@ extern "C" {
 /* Same object as cudaStream_t; spelled out so C callers need no CUDA header. */
 typedef struct CUstream_st *hyle_b200_stream_t;
 
-#define HYLE_B200_ABI_VERSION 18
+#define HYLE_B200_ABI_VERSION 19
 
 enum hyle_b200_result {
   HYLE_B200_OK = 0,
@@ -573,6 +573,16 @@ HYLE_B200_API int hyle_b200_q8_0_roundtrip_bf16_static(hyle_b200_stream_t stream
  * slot.  Chunks arrive in file order; at the end next() returns OK with *chunk_bytes == 0.  A read
  * error or a file shorter than the range makes next() return HYLE_B200_IO_ERROR.  One consumer thread
  * per stream object.  close() waits for the consumer's last recorded use, then frees.
+ *
+ * A stream opened with bytes == 0 has no sequential reader and no device slots; it serves
+ * read_group(): a group of byte ranges of the file, each copied to a device destination of the
+ * caller's own (the reference's StreamReadGroup of StreamReadRange{file_offset, destination, bytes},
+ * include/hyle/compute/file_stream.h:84-93: how tensors of a weight file reach their buffers).
+ * The calling thread reads each range in chunks into the pinned slots, one cudaMemcpyAsync per
+ * chunk on the copy stream, reading the next chunk while the previous copy is in flight; on return
+ * the consumer's stream has been made to wait for the group's last copy.  Ranges are checked
+ * against the file's size before anything is copied (HYLE_B200_IO_ERROR); destinations need no
+ * alignment.
  */
 typedef struct hyle_b200_file_stream hyle_b200_file_stream;
 typedef struct hyle_b200_file_stream_options {
@@ -592,6 +602,14 @@ HYLE_B200_API int hyle_b200_file_stream_open(const char *path, uint64_t file_off
 HYLE_B200_API int hyle_b200_file_stream_next(hyle_b200_file_stream *stream, hyle_b200_stream_t consumer,
                                              const void **device_chunk, uint64_t *chunk_bytes,
                                              uint64_t *chunk_offset);
+typedef struct hyle_b200_file_range {
+  uint64_t file_offset;  /* from the start of the file */
+  uint64_t bytes;
+  void *destination;     /* device memory */
+} hyle_b200_file_range;
+HYLE_B200_API int hyle_b200_file_stream_read_group(hyle_b200_file_stream *stream,
+                                                   hyle_b200_stream_t consumer,
+                                                   const hyle_b200_file_range *ranges, uint32_t count);
 HYLE_B200_API int hyle_b200_file_stream_get_report(hyle_b200_file_stream *stream,
                                                    hyle_b200_file_stream_report *report);
 HYLE_B200_API int hyle_b200_file_stream_close(hyle_b200_file_stream *stream);

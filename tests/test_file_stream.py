@@ -96,3 +96,38 @@ def test_a_file_that_ends_inside_the_range_is_an_error_not_a_hang(tmp_path):
             break
     assert codes[-1] == abi.IO_ERROR and codes.count(abi.OK) >= 1
     assert lib.hyle_b200_file_stream_close(handle) == abi.OK
+
+
+@pytest.mark.gpu
+def test_a_group_of_ranges_lands_in_the_callers_tensors(tmp_path):
+    """read_group: ranges of one file -> device tensors of the caller's own (how the tensors of a weight file reach
+    their buffers): ragged sizes, unaligned offsets and destinations, a range longer than all slots together, an
+    empty range; two groups in a row reuse the slots; a range beyond the end is refused before anything is copied."""
+    rng = np.random.default_rng(5)
+    payload = rng.integers(0, 256, 3_000_001, dtype=np.uint8)
+    path = tmp_path / "weights.bin"
+    payload.tofile(path)
+    with ops.FileStream(str(path), 0, chunk_bytes=64 << 10, slots=3) as stream:
+        assert stream.report().device_bytes == 0 and stream.report().staging_bytes == 3 * (64 << 10)
+        big = torch.zeros(1_000_003, dtype=torch.uint8, device="cuda")
+        odd = torch.zeros(4099, dtype=torch.uint8, device="cuda")[3:]            # an unaligned destination
+        words = torch.zeros(1000, dtype=torch.float32, device="cuda")
+        empty = torch.zeros(0, dtype=torch.uint8, device="cuda")
+        stream.read_group([(17, big), (2_000_000, odd), (1_500_000, words), (5, empty)])
+        tail = torch.zeros(257, dtype=torch.uint8, device="cuda")
+        stream.read_group([(payload.size - 257, tail)])
+        torch.cuda.synchronize()
+        assert np.array_equal(big.cpu().numpy(), payload[17:17 + big.numel()])
+        assert np.array_equal(odd.cpu().numpy(), payload[2_000_000:2_000_000 + odd.numel()])
+        assert np.array_equal(words.cpu().numpy().view(np.uint8), payload[1_500_000:1_500_000 + 4000])
+        assert np.array_equal(tail.cpu().numpy(), payload[-257:])
+        report = stream.report()
+        assert report.bytes_copied == big.numel() + odd.numel() + 4000 + 257 and report.copies >= 16 + 1 + 1 + 1
+        before = big.clone()
+        with pytest.raises(abi.KernelError):
+            stream.read_group([(0, big), (payload.size - 100, tail)])             # the second range ends beyond the file
+        torch.cuda.synchronize()
+        assert torch.equal(big, before)                                           # refused as a whole
+    with ops.FileStream(str(path), 1024) as sequential:                           # a sequential stream has no groups
+        with pytest.raises(abi.KernelError):
+            sequential.read_group([(0, tail)])
