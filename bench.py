@@ -903,6 +903,50 @@ def run_e2e(torch, ops, abi, shard_rows: int, steps: int, warmup: int):
     return seconds, h2d, d2h, total
 
 
+def file_stream_bench(torch, ops, abi, blocks, values: int = 512 * 1024 * 1024 // 34 * 32, passes: int = 3):
+    """The on-disk form of the path: a Q8_0 bank (the blocks the headline launch just produced) is written to a
+    temporary file and streamed back through `hyle_b200_file_stream_*` into the decode kernel (file -> pinned
+    slots -> device -> `hyle_b200_q8_0_decode_bf16` per chunk).  Reads come from the page cache, so this times
+    the pipeline, not a disk.  Wall clock, best of `passes` after a warm-up: the streaming phase (first next()
+    to the last decode's completion) in GB/s of file bytes, and open() / close(), which allocate and free the
+    pinned and device slots, on their own."""
+    import tempfile
+
+    values -= values % 256
+    size = values // 32 * 34
+    if blocks.numel() < size:
+        return None
+    lib = abi.load()
+    out = torch.empty(values, dtype=torch.bfloat16, device="cuda")
+    consumer = torch.cuda.current_stream().cuda_stream
+    best = None
+    with tempfile.NamedTemporaryFile(prefix="hyle_b200_bank_", suffix=".q8_0") as bank:
+        bank.write(memoryview(blocks[:size].cpu().numpy()))
+        bank.flush()
+        for _ in range(passes + 1):
+            torch.cuda.synchronize()
+            t0 = time.perf_counter()
+            stream = ops.FileStream(bank.name, size, granule=34 * 8)
+            t1 = time.perf_counter()
+            for pointer, nbytes, offset in stream:
+                abi.check("decode", lib.hyle_b200_q8_0_decode_bf16(consumer, pointer, nbytes // 34 * 32,
+                                                                   out.data_ptr() + offset // 34 * 64))
+            torch.cuda.synchronize()
+            t2 = time.perf_counter()
+            report = stream.report()
+            stream.close()
+            t3 = time.perf_counter()
+            if best is None or t2 - t1 < best[1]:
+                best = (t1 - t0, t2 - t1, t3 - t2, report)
+    opened, streamed, closed, report = best
+    return {"bank_MiB": round(size / 2 ** 20, 1), "GB/s_of_file_bytes": round(size / streamed / 1e9, 2),
+            "stream_ms": round(streamed * 1e3, 2), "open_ms": round(opened * 1e3, 2), "close_ms": round(closed * 1e3, 2),
+            "chunk_MiB": round(report.chunk_bytes / 2 ** 20, 2), "chunks": int(report.chunks), "copies": int(report.copies),
+            "pread_calls": int(report.io_calls), "pinned_MiB": round(report.staging_bytes / 2 ** 20, 1),
+            "what": "Q8_0 bank from the page cache -> pinned slots (several threads read a chunk together) -> one "
+                    "cudaMemcpyAsync per chunk -> decode kernel -> bf16 tensor"}
+
+
 def run_ops_only(args):
     """Time only the named operators of workloads 1-4 (short command for profiling one kernel)."""
     import torch
@@ -1152,6 +1196,13 @@ def run_gpu(args):
                             "h2d_GB/s_per_rank": [p["h2d_GB/s"] for p in copy_peaks],
                             "sum_pass_mix_GB/s": round(sum(p["pass_mix_GB/s"] for p in copy_peaks), 1)}}
 
+    streamed = None
+    if world == 1 and not args.skip_e2e:
+        streamed = file_stream_bench(torch, ops, abi, blocks)
+        if streamed is not None and copy_peak is not None:
+            streamed["h2d_pinned_copy_GB/s"] = copy_peak["h2d_GB/s"]
+            streamed["frac_of_pinned_copy"] = round(streamed["GB/s_of_file_bytes"] / copy_peak["h2d_GB/s"], 3)
+
     line = {
         "metric": METRIC, "value": value, "unit": UNIT, "n_gpus": world, "steps": args.steps,
         "warmup": args.warmup, "ms_per_step": ms_per_step, "higher_is_better": True, "scaling": "strong",
@@ -1161,6 +1212,7 @@ def run_gpu(args):
         "parity": parity,
         "roofline": roofline,
         "e2e": e2e,
+        "file_stream": streamed,
         "gpu_launches": args.steps,
         "clocks": clocks,
         "sum_squares": sum_squares,

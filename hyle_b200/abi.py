@@ -108,7 +108,7 @@ class StreamTuning(ctypes.Structure):
 
 class FileStreamOptions(ctypes.Structure):
     """hyle_b200_file_stream_options: zero fields take the defaults (8 MiB chunks, 4 slots)."""
-    _fields_ = [("chunk_bytes", _u64), ("slots", _u32), ("reserved", _u32), ("chunk_granule", _u64)]
+    _fields_ = [("chunk_bytes", _u64), ("slots", _u32), ("readers", _u32), ("chunk_granule", _u64)]
 
 
 class FileRange(ctypes.Structure):

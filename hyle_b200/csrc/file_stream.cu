@@ -34,6 +34,14 @@ namespace {
 
 constexpr uint32_t kMaxSlots = 16;
 constexpr uint64_t kDefaultChunkBytes = 8ull << 20;
+constexpr uint32_t kMaxReaders = 16;
+// default: half of the host's hardware threads, at most 8 (one thread moves about 10 GB/s out of the page cache)
+uint32_t default_readers() {
+  const unsigned threads = std::thread::hardware_concurrency();
+  const unsigned half = threads / 2;
+  return half < 1 ? 1u : (half > 8 ? 8u : half);
+}
+constexpr uint64_t kPieceBytes = 1ull << 20;  // what one pread call of one reader covers
 
 }  // namespace
 
@@ -58,6 +66,99 @@ struct hyle_b200_file_stream {
   uint64_t file_bytes = 0;  // size of the file at open
   uint64_t group_chunks = 0;  // chunks copied by read_group so far (slot rotation across groups)
   hyle_b200_file_stream_report report{};
+
+  // A chunk is read by `readers` threads at once, a piece of kPieceBytes each (one thread copies from the page
+  // cache at about 10 GB/s; the host-to-device link takes five times that).  The coordinator (the reader
+  // thread, or the caller of read_group) posts a job and takes pieces itself; helpers take the rest.
+  uint32_t readers = 1;
+  std::thread helpers[kMaxReaders];
+  std::mutex job_mutex;
+  std::condition_variable job_posted, job_finished;
+  uint64_t job_generation = 0;
+  unsigned char *job_target = nullptr;
+  uint64_t job_offset = 0, job_bytes = 0, job_pieces = 0;
+  std::atomic<uint64_t> job_ticket{0};  // generation << 32 | next piece
+  uint64_t job_done = 0, job_calls = 0;
+  bool job_failed = false, helpers_stop = false;
+
+  // Pieces of job `generation` until none is left.  The ticket holds the job's generation beside the next
+  // piece, and a piece is claimed by compare-and-swap on the pair: a helper that wakes up late can never
+  // claim (or skip) a piece of a job it was not woken for.  The job's fields are written before the
+  // ticket is published (release) and read after it is seen (acquire).
+  void take_pieces(uint64_t generation) {
+    uint64_t calls = 0, finished = 0;
+    bool failed = false;
+    for (;;) {
+      uint64_t ticket = job_ticket.load(std::memory_order_acquire);
+      uint64_t piece = 0;
+      bool claimed = false;
+      while ((ticket >> 32) == (generation & 0xffffffffull) && (ticket & 0xffffffffull) < job_pieces) {
+        if (job_ticket.compare_exchange_weak(ticket, ticket + 1, std::memory_order_acq_rel, std::memory_order_acquire)) {
+          piece = ticket & 0xffffffffull;
+          claimed = true;
+          break;
+        }
+      }
+      if (!claimed) break;
+      const uint64_t begin = piece * kPieceBytes, size = job_bytes - begin < kPieceBytes ? job_bytes - begin : kPieceBytes;
+      uint64_t have = 0;
+      while (have < size && !failed) {
+        const ssize_t got = pread(fd, job_target + begin + have, size - have, static_cast<off_t>(job_offset + begin + have));
+        ++calls;
+        if (got < 0 && errno == EINTR) continue;
+        if (got <= 0) failed = true;  // error, or the file ends inside the range
+        else have += static_cast<uint64_t>(got);
+      }
+      ++finished;
+    }
+    if (finished == 0) return;
+    std::lock_guard lock(job_mutex);
+    job_done += finished;
+    job_calls += calls;
+    job_failed = job_failed || failed;
+    if (job_done == job_pieces) job_finished.notify_all();
+  }
+
+  void helper_loop() {
+    uint64_t seen = 0;
+    for (;;) {
+      {
+        std::unique_lock lock(job_mutex);
+        job_posted.wait(lock, [&] { return helpers_stop || job_generation != seen; });
+        if (helpers_stop) return;
+        seen = job_generation;
+      }
+      take_pieces(seen);
+    }
+  }
+
+  // bytes of the file at `offset` -> target, by all readers; the number of pread calls comes back in *calls.
+  // One coordinator at a time (the reader thread, or the caller of read_group).
+  bool read_parallel(unsigned char *target, uint64_t offset, uint64_t size, uint64_t *calls) {
+    uint64_t generation = 0;
+    {
+      std::lock_guard lock(job_mutex);
+      job_target = target;
+      job_offset = offset;
+      job_bytes = size;
+      job_pieces = (size + kPieceBytes - 1) / kPieceBytes;
+      job_done = 0;
+      job_calls = 0;
+      job_failed = false;
+      generation = ++job_generation;
+      job_ticket.store((generation & 0xffffffffull) << 32, std::memory_order_release);
+    }
+    if (job_pieces == 0) {
+      *calls = 0;
+      return true;
+    }
+    if (readers > 1 && job_pieces > 1) job_posted.notify_all();
+    take_pieces(generation);
+    std::unique_lock lock(job_mutex);
+    job_finished.wait(lock, [&] { return job_done == job_pieces; });
+    *calls = job_calls;
+    return !job_failed;
+  }
 
   uint64_t chunk_size(uint64_t index) const {
     const uint64_t start = index * chunk_bytes;
@@ -85,14 +186,8 @@ struct hyle_b200_file_stream {
         if (cudaStreamWaitEvent(copy_stream, done[slot], 0) != cudaSuccess) return fail(HYLE_B200_IO_ERROR);
       }
       const uint64_t size = chunk_size(index);
-      uint64_t have = 0, calls = 0;
-      while (have < size) {
-        const ssize_t got = pread(fd, pinned[slot] + have, size - have, static_cast<off_t>(file_offset + index * chunk_bytes + have));
-        ++calls;
-        if (got < 0 && errno == EINTR) continue;
-        if (got <= 0) return fail(HYLE_B200_IO_ERROR);  // error, or the file ends inside the range
-        have += static_cast<uint64_t>(got);
-      }
+      uint64_t calls = 0;
+      if (!read_parallel(pinned[slot], file_offset + index * chunk_bytes, size, &calls)) return fail(HYLE_B200_IO_ERROR);
       if (cudaMemcpyAsync(resident[slot], pinned[slot], size, cudaMemcpyHostToDevice, copy_stream) != cudaSuccess ||
           cudaEventRecord(copied[slot], copy_stream) != cudaSuccess)
         return fail(HYLE_B200_IO_ERROR);
@@ -140,6 +235,8 @@ extern "C" int hyle_b200_file_stream_open(const char *path, uint64_t file_offset
   stream->chunk_bytes = chunk;
   stream->chunks = (bytes + chunk - 1) / chunk;
   stream->slots = slots;
+  stream->readers = options != nullptr && options->readers != 0 ? options->readers : default_readers();
+  if (stream->readers > kMaxReaders) stream->readers = kMaxReaders;
   cudaError_t error = cudaGetDevice(&stream->device);
   if (error == cudaSuccess) error = cudaStreamCreateWithFlags(&stream->copy_stream, cudaStreamNonBlocking);
   for (uint32_t s = 0; s < slots && error == cudaSuccess; ++s) {
@@ -156,6 +253,7 @@ extern "C" int hyle_b200_file_stream_open(const char *path, uint64_t file_offset
   stream->report.device_bytes = bytes != 0 ? chunk * slots : 0;
   stream->report.chunk_bytes = chunk;
   stream->report.chunks = stream->chunks;
+  for (uint32_t h = 1; h < stream->readers; ++h) stream->helpers[h] = std::thread([stream] { stream->helper_loop(); });
   if (stream->chunks != 0) stream->reader = std::thread([stream] { stream->read_loop(); });
   *out = stream;
   return HYLE_B200_OK;
@@ -212,15 +310,9 @@ extern "C" int hyle_b200_file_stream_read_group(hyle_b200_file_stream *stream, h
       // the slot's previous copy must have left the pinned buffer (an event never recorded is complete)
       if (cudaEventSynchronize(stream->copied[slot]) != cudaSuccess) return HYLE_B200_IO_ERROR;
       const uint64_t size = ranges[r].bytes - done_bytes < stream->chunk_bytes ? ranges[r].bytes - done_bytes : stream->chunk_bytes;
-      uint64_t have = 0, calls = 0;
-      while (have < size) {
-        const ssize_t got = pread(stream->fd, stream->pinned[slot] + have, size - have,
-                                  static_cast<off_t>(ranges[r].file_offset + done_bytes + have));
-        ++calls;
-        if (got < 0 && errno == EINTR) continue;
-        if (got <= 0) return HYLE_B200_IO_ERROR;  // the file shrank after open, or a read error
-        have += static_cast<uint64_t>(got);
-      }
+      uint64_t calls = 0;
+      if (!stream->read_parallel(stream->pinned[slot], ranges[r].file_offset + done_bytes, size, &calls))
+        return HYLE_B200_IO_ERROR;  // the file shrank after open, or a read error
       cudaError_t error = cudaMemcpyAsync(static_cast<unsigned char *>(ranges[r].destination) + done_bytes, stream->pinned[slot],
                                           size, cudaMemcpyHostToDevice, stream->copy_stream);
       if (error == cudaSuccess) error = cudaEventRecord(stream->copied[slot], stream->copy_stream);
@@ -259,6 +351,13 @@ extern "C" int hyle_b200_file_stream_close(hyle_b200_file_stream *stream) {
   }
   stream->changed.notify_all();
   if (stream->reader.joinable()) stream->reader.join();
+  {
+    std::lock_guard lock(stream->job_mutex);
+    stream->helpers_stop = true;
+  }
+  stream->job_posted.notify_all();
+  for (auto &helper : stream->helpers)
+    if (helper.joinable()) helper.join();
   int device = 0;
   const bool switched = cudaGetDevice(&device) == cudaSuccess && device != stream->device && cudaSetDevice(stream->device) == cudaSuccess;
   if (stream->copy_stream != nullptr) cudaStreamSynchronize(stream->copy_stream);

@@ -565,9 +565,10 @@ HYLE_B200_API int hyle_b200_q8_0_roundtrip_bf16_static(hyle_b200_stream_t stream
  * of k/32 blocks of 34 bytes (src/compute_ops/low_precision.cc:269-297).
  *
  * open() allocates everything: `slots` pinned staging buffers and `slots` device buffers of
- * chunk_bytes, 2 x slots events, one copy stream, one reader thread; nothing allocates afterwards.
- * The reader thread preads chunk i into pinned slot i % slots and issues ONE cudaMemcpyAsync for it on
- * the copy stream.  next() makes the consumer's stream wait (on the device) for that copy and returns
+ * chunk_bytes, 2 x slots events, one copy stream, the reader threads; nothing allocates afterwards.
+ * Chunk i is read into pinned slot i % slots by `readers` threads at once (a MiB per pread call: one
+ * thread copies from the page cache at about a fifth of the host-to-device link), then ONE
+ * cudaMemcpyAsync for it is issued on the copy stream.  next() makes the consumer's stream wait (on the device) for that copy and returns
  * the chunk's device address; the address stays valid until the NEXT call of next(), which records on
  * the consumer's stream that the chunk is finished with, so that the copy stream may overwrite its
  * slot.  Chunks arrive in file order; at the end next() returns OK with *chunk_bytes == 0.  A read
@@ -588,7 +589,7 @@ typedef struct hyle_b200_file_stream hyle_b200_file_stream;
 typedef struct hyle_b200_file_stream_options {
   uint64_t chunk_bytes;    /* 0: 8 MiB */
   uint32_t slots;          /* in-flight chunks, 2..16; 0: 4 */
-  uint32_t reserved;
+  uint32_t readers;        /* threads that read one chunk together, 1..16; 0: half the hardware threads, at most 8 */
   uint64_t chunk_granule;  /* chunk_bytes is rounded down to a multiple of this (a record size); 0: 1 */
 } hyle_b200_file_stream_options;
 typedef struct hyle_b200_file_stream_report {
