@@ -421,25 +421,57 @@ inline std::size_t storage_width(int cast_type) noexcept {
 // src/compute_provider_cuda/tensor_kernel.cu:70-108): the request is matched with those inputs
 // described dense, and the plan gathers each into a dense temporary before the kernel.  Outputs must
 // be dense.
+// `input` viewed with the dimensions `target` under the NumPy rule (axes aligned at the end; an extent of 1,
+// or a missing leading axis, repeats): the strides of the input where the extents agree, zero where it
+// repeats -- what the reference's own broadcast view produces (src/compute_ops/operation.cc:440-472).
+inline std::optional<TensorDesc> expanded(const TensorDesc &input, std::span<const std::int64_t> target) noexcept {
+  if (!input.is_plain() || target.size() < input.rank() || target.size() > kMaxTensorRank) return std::nullopt;
+  std::array<std::int64_t, kMaxTensorRank> strides{};
+  const std::size_t prefix = target.size() - input.rank();
+  for (std::size_t axis = prefix; axis < target.size(); ++axis) {
+    const std::int64_t extent = input.dimensions()[axis - prefix];
+    if (extent == target[axis]) strides[axis] = input.byte_strides()[axis - prefix];
+    else if (extent != 1) return std::nullopt;
+  }
+  auto made = TensorDesc::strided_bytes(input.data_type(), target, std::span<const std::int64_t>(strides.data(), target.size()));
+  if (!made) return std::nullopt;
+  return *made;
+}
+
 inline std::optional<Plan> match(const Operation &op, std::span<const TensorDesc> in,
                                  std::span<const TensorDesc> out) noexcept {
+  if (in.size() > 4) return std::nullopt;
+  // What each input is read as.  Binary operands follow the NumPy rule on both sides (infer_binary,
+  // src/compute_ops/operation.cc:476-486): an operand that is neither the output's shape nor (on the right)
+  // its trailing axes is read through its broadcast view, i.e. as a strided input.
+  std::array<TensorDesc, 4> viewed{};
+  for (std::size_t i = 0; i < in.size(); ++i) viewed[i] = in[i];
+  if (op.get_if<Binary>() != nullptr && in.size() == 2 && out.size() == 1 && out[0].is_dense()) {
+    for (std::size_t i = 0; i < 2; ++i) {
+      const bool as_is = in[i].rank() == out[0].rank() && elements(in[i]) == elements(out[0]);
+      const bool trailing = i == 1 && in[1].is_dense() && trailing_axes(out[0], in[1]);
+      if (as_is || trailing) continue;
+      const auto view = expanded(in[i], out[0].dimensions());
+      if (!view) return std::nullopt;
+      viewed[i] = *view;
+    }
+  }
   bool strided = false;
-  for (const auto &d : in) strided = strided || !d.is_dense();
+  for (std::size_t i = 0; i < in.size(); ++i) strided = strided || !viewed[i].is_dense();
   if (!strided) {
     auto plan = match_dense(op, in, out);
     if (plan) plan->total_workspace_bytes = plan->workspace_bytes;
     return plan;
   }
   std::array<TensorDesc, 4> dense_in{};
-  if (in.size() > dense_in.size()) return std::nullopt;
   for (std::size_t i = 0; i < in.size(); ++i) {
-    dense_in[i] = in[i];
-    if (in[i].is_dense()) continue;
-    const auto type = cast_dtype(in[i].data_type());
-    if (!in[i].is_plain() || !type || in[i].rank() == 0) return std::nullopt;
-    for (const auto stride : in[i].byte_strides())
+    dense_in[i] = viewed[i];
+    if (viewed[i].is_dense()) continue;
+    const auto type = cast_dtype(viewed[i].data_type());
+    if (!viewed[i].is_plain() || !type || viewed[i].rank() == 0) return std::nullopt;
+    for (const auto stride : viewed[i].byte_strides())
       if (stride < 0 || stride % static_cast<std::int64_t>(storage_width(*type)) != 0) return std::nullopt;
-    auto made = TensorDesc::dense(in[i].data_type(), in[i].dimensions());
+    auto made = TensorDesc::dense(viewed[i].data_type(), viewed[i].dimensions());
     if (!made) return std::nullopt;
     dense_in[i] = *made;
   }
@@ -447,17 +479,17 @@ inline std::optional<Plan> match(const Operation &op, std::span<const TensorDesc
   if (!plan) return std::nullopt;
   std::size_t end = aligned_256(plan->workspace_bytes);
   for (std::size_t i = 0; i < in.size(); ++i) {
-    if (in[i].is_dense()) continue;
+    if (viewed[i].is_dense()) continue;
     auto &gather = plan->gathers[plan->gather_count++];
     gather.input = static_cast<std::uint8_t>(i);
-    gather.rank = static_cast<std::uint8_t>(in[i].rank());
-    gather.dtype = *cast_dtype(in[i].data_type());
-    for (std::size_t axis = 0; axis < in[i].rank(); ++axis) {
-      gather.dimensions[axis] = in[i].dimensions()[axis];
-      gather.byte_strides[axis] = in[i].byte_strides()[axis];
+    gather.rank = static_cast<std::uint8_t>(viewed[i].rank());
+    gather.dtype = *cast_dtype(viewed[i].data_type());
+    for (std::size_t axis = 0; axis < viewed[i].rank(); ++axis) {
+      gather.dimensions[axis] = viewed[i].dimensions()[axis];
+      gather.byte_strides[axis] = viewed[i].byte_strides()[axis];
     }
     gather.offset = end;
-    end = aligned_256(end + elements(in[i]) * storage_width(gather.dtype));
+    end = aligned_256(end + elements(viewed[i]) * storage_width(gather.dtype));
   }
   plan->total_workspace_bytes = end;
   return plan;

@@ -141,6 +141,21 @@ int main() {
     const auto plan = b200::match(Operation(Unary{UnaryKind::kExp}), in, out);
     check(plan && plan->gather_count == 1 && plan->workspace_bytes == 0 && plan->total_workspace_bytes == 64 * 4096 * 4,
           "the plan gathers that input into a workspace of its dense size");
+    // Binary under the NumPy rule on both sides: a column vector, a scalar-like [1, 1], a row on the left
+    const auto column = dense(DataType::kFloat32, {64, 1}), one = dense(DataType::kFloat32, {1, 1});
+    const std::array mat_out{f32_mat};
+    const std::array with_column{f32_mat, column};
+    const std::array with_one{f32_mat, one};
+    const std::array row_left{f32_row, f32_mat};
+    check(taken(*context, Operation(Binary{BinaryKind::kMultiply}), with_column, mat_out), "Binary f32 [64,4096] * [64,1] (column broadcast)");
+    check(taken(*context, Operation(Binary{BinaryKind::kAdd}), with_one, mat_out), "Binary f32 [64,4096] + [1,1]");
+    check(taken(*context, Operation(Binary{BinaryKind::kSubtract}), row_left, mat_out), "Binary f32 [4096] - [64,4096] (left operand broadcast)");
+    const auto column_plan = b200::match(Operation(Binary{BinaryKind::kMultiply}), with_column, mat_out);
+    check(column_plan && column_plan->gather_count == 1 && column_plan->gathers[0].input == 1 &&
+              column_plan->gathers[0].byte_strides[0] == 4 && column_plan->gathers[0].byte_strides[1] == 0,
+          "the column is gathered through strides {4, 0}");
+    const std::array mismatched{f32_mat, dense(DataType::kFloat32, {32, 1})};
+    check(!taken(*context, Operation(Binary{BinaryKind::kMultiply}), mismatched, mat_out), "Binary with an extent that cannot broadcast not taken");
     const std::array dense_in{upright};
     const std::array turned_out{turned};
     check(!taken(*context, Operation(Unary{UnaryKind::kExp}), dense_in, turned_out), "Unary f32 into a transposed output not taken");

@@ -309,6 +309,17 @@ int main() {
                        return rc != HYLE_B200_OK ? rc : hyle_b200_rms_norm_bf16(s, ws, in[1], HYLE_B200_BF16, out[0], 64, 2048, 1e-6F);
                      }, b200::Entry::kRmsNorm});
   }
+  {  // Binary under the NumPy rule: a column vector on the right, gathered with a zero stride
+    const auto a = dense(DataType::kFloat32, {64, 4096}), column = dense(DataType::kFloat32, {64, 1});
+    cases.push_back({"Binary{kMultiply} f32 [64,4096] * [64,1]", Operation(Binary{BinaryKind::kMultiply}), {a, column}, {a},
+                     {f32_normal(64 * 4096, 51), f32_normal(64, 52)}, 64 * 4096 * 4,
+                     [](auto s, auto in, auto out, void *ws, std::uint64_t, std::uint32_t *) {
+                       const std::int64_t dims[2] = {64, 4096}, strides[2] = {4, 0};
+                       const int rc = hyle_b200_strided_cast(s, HYLE_B200_F32, HYLE_B200_F32, in[1], ws, 2, dims, strides);
+                       return rc != HYLE_B200_OK ? rc
+                                                 : hyle_b200_binary(s, HYLE_B200_BINARY_MULTIPLY, HYLE_B200_F32, in[0], ws, out[0], 64 * 4096, 64 * 4096);
+                     }, b200::Entry::kBinary});
+  }
   {  // Binary with a trailing-axis broadcast
     const auto a = dense(DataType::kFloat32, {64, 4096}), b = dense(DataType::kFloat32, {4096});
     cases.push_back({"Binary{kAdd} f32 [64,4096] + [4096]", Operation(Binary{BinaryKind::kAdd}), {a, b}, {a},
