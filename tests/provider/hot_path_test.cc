@@ -17,6 +17,7 @@
 #include <bit>
 #include <cmath>
 #include <cstdint>
+#include <chrono>
 #include <cstdio>
 #include <cstring>
 #include <functional>
@@ -129,6 +130,8 @@ struct Tensor final {
   }
   const void *device() const { return backend::pointer(storage.view()).value(); }
 };
+
+static void *out_pointer(Tensor &t) { return backend::pointer(t.storage.view()).value(); }
 
 struct Fixture final {
   Context context;
@@ -615,6 +618,63 @@ int main() {
     check(pattern, "fill_async then copy_async on the Queue: ordered on its stream, one wait covers the prefix");
     // a provider made for this backend is refused by a Context of another backend id
     check(fixture.queue.drain().ok() && fixture.context.drain().ok(), "Queue::drain and Context::drain");
+  }
+  {  // what the seam costs on the host: submit() of a prepared invocation against the bare C-ABI call
+    const auto x = dense(DataType::kFloat32, {1, 1024});
+    std::vector<Tensor> in, out;
+    in.emplace_back(x, resource);
+    out.emplace_back(x, resource);
+    in[0].write(f32_normal(1024, 60)).IgnoreError();
+    std::vector<ConstTensorView> in_views{in[0].view.as_const()};
+    std::vector<TensorView> out_views{out[0].view};
+    auto prepared = prepare(fixture.context, Operation(Unary{UnaryKind::kExp}), std::span<const ConstTensorView>(in_views),
+                            std::span<const TensorView>(out_views), resource);
+    // an invocation carries one flight at a time: eight of them take turns
+    std::vector<OperationInvocation> invocations;
+    bool timed = prepared.has_value();
+    for (int k = 0; k < 8 && timed; ++k) {
+      auto made = prepared->create_invocation();
+      timed = made.has_value();
+      if (timed) invocations.push_back(std::move(*made));
+    }
+    constexpr int kSubmits = 2000;
+    double through_seam = 0.0, direct = 0.0;
+    if (timed) {
+      // their Completions are kept in a ring: the one replaced finished seven launches ago, so waiting for it
+      // returns at once and the loop measures the producer side
+      std::vector<Completion> ring(8);
+      std::vector<bool> flown(8, false);
+      auto submit_one = [&](int i) {
+        const std::size_t turn = static_cast<std::size_t>(i) % ring.size();
+        if (flown[turn] && !ring[turn].wait().ok()) return false;
+        flown[turn] = true;
+        auto done = invocations[turn].submit(fixture.queue, in_views, out_views);
+        if (!done) {
+          std::printf("      submit %d: %s\n", i, std::string(done.error().message()).c_str());
+          return false;
+        }
+        ring[turn] = std::move(*done);
+        return true;
+      };
+      for (int i = 0; i < 100 && timed; ++i) timed = submit_one(i);
+      timed = timed && fixture.queue.drain().ok();
+      auto t0 = std::chrono::steady_clock::now();
+      for (int i = 0; i < kSubmits && timed; ++i) timed = submit_one(i);
+      auto t1 = std::chrono::steady_clock::now();
+      timed = timed && fixture.queue.drain().ok();
+      through_seam = std::chrono::duration<double, std::micro>(t1 - t0).count() / kSubmits;
+      auto stream = backend::stream(fixture.queue);
+      if (stream) {
+        t0 = std::chrono::steady_clock::now();
+        for (int i = 0; i < kSubmits; ++i) hyle_b200_unary(*stream, HYLE_B200_UNARY_EXP, HYLE_B200_F32, in[0].device(), out_pointer(out[0]), 1024);
+        t1 = std::chrono::steady_clock::now();
+        cudaDeviceSynchronize();
+        direct = std::chrono::duration<double, std::micro>(t1 - t0).count() / kSubmits;
+      }
+    }
+    check(timed, "2000 submits of a prepared operator (eight invocations in turn) on the Queue, then 2000 direct calls on its stream");
+    std::printf("      host cost per operator: %.2f us through OperationInvocation::submit (sequence, Completion, enqueue), "
+                "%.2f us for the bare hyle_b200_unary call\n", through_seam, direct);
   }
   std::printf("%d check(s), %d failure(s)\n", checks, failures);
   return failures == 0 ? 0 : 1;
