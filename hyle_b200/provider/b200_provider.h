@@ -29,6 +29,7 @@
 #include <hyle/compute/sampling_ops.h>
 
 #include "b200_ops.h"
+#include "b200_trace.h"
 #include "hyle_b200.h"
 
 namespace hyle::compute::b200 {
@@ -42,6 +43,15 @@ enum class Entry : std::uint8_t {
   kAddRmsNorm, kBiasRowSumMax, kLogitsReduce, kQ8Roundtrip, kActivationMultiply, kGreedyHead
 };
 inline constexpr std::size_t kEntryCount = 22;
+// Trace zone names, in the order of Entry.
+inline constexpr std::array<const char *, kEntryCount> kEnqueueZone{
+    "hyle_b200.enqueue.unary", "hyle_b200.enqueue.binary", "hyle_b200.enqueue.select", "hyle_b200.enqueue.reduce_rows",
+    "hyle_b200.enqueue.scan", "hyle_b200.enqueue.rms_norm", "hyle_b200.enqueue.layer_norm", "hyle_b200.enqueue.swiglu",
+    "hyle_b200.enqueue.softmax", "hyle_b200.enqueue.masked_softmax", "hyle_b200.enqueue.cast", "hyle_b200.enqueue.argmax",
+    "hyle_b200.enqueue.q8_0_encode", "hyle_b200.enqueue.fp8_encode", "hyle_b200.enqueue.random_bits",
+    "hyle_b200.enqueue.categorical", "hyle_b200.enqueue.add_rms_norm", "hyle_b200.enqueue.bias_row_sum_max",
+    "hyle_b200.enqueue.logits_reduce", "hyle_b200.enqueue.q8_0_roundtrip", "hyle_b200.enqueue.activation_multiply",
+    "hyle_b200.enqueue.greedy_head"};
 
 // Everything enqueue() needs, frozen at prepare time.  Trivially copyable.
 struct Plan final {
@@ -628,6 +638,7 @@ struct Kernel final {
   KernelCommandResult enqueue(Invocation &invocation, detail::QueueSequence &sequence,
                               std::span<const ConstTensorView> inputs,
                               std::span<const TensorView> outputs) const noexcept {
+    HYLE_B200_TRACE_ZONE(kEnqueueZone[static_cast<std::size_t>(plan.entry)]);
     auto stream = Backend::stream(sequence);
     if (!stream) return KernelCommandResult::rejected(std::move(stream).error());
     std::array<const void *, 4> in{};
@@ -685,6 +696,7 @@ template <class Backend>
 struct Factory final {
   Result<KernelProposal> propose(const KernelRequest &request, std::span<ResourceRequirement> inputs,
                                  std::span<ResourceRequirement> outputs) const noexcept {
+    HYLE_B200_TRACE_ZONE("hyle_b200.propose");
     const auto plan = match(request.operation, request.inputs, request.outputs);
     if (!plan) return std::unexpected(Status::Unimplemented("hyle-b200: operation outside the provider's domain"));
     const ResourceRequirement storage{.required_properties = Backend::memory(), .minimum_alignment = 16};
@@ -703,6 +715,7 @@ struct Factory final {
                           .implementation = ProviderImplementationId{static_cast<std::uint64_t>(plan->entry) + 1}};
   }
   KernelPreparation prepare(const KernelPrepareRequest &request, mem::AllocatorRef allocator) const noexcept {
+    HYLE_B200_TRACE_ZONE("hyle_b200.prepare");
     const auto plan = match(request.operation, request.inputs, request.outputs);
     if (!plan) return KernelPreparation::unsupported(Status::Unimplemented("hyle-b200: declined at prepare"));
     auto kernel = make_custom_kernel(

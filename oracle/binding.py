@@ -14,7 +14,8 @@ import subprocess
 import numpy as np
 
 ORACLE_DIR = os.path.dirname(os.path.abspath(__file__))
-ORACLE_LIB = os.path.join(ORACLE_DIR, "libhyle_oracle.so")
+# HYLE_ORACLE_LIB: another build of the same file (the sanitizer build of tests/test_sanitizers.py).
+ORACLE_LIB = os.environ.get("HYLE_ORACLE_LIB") or os.path.join(ORACLE_DIR, "libhyle_oracle.so")
 REF_LIB = os.path.join(ORACLE_DIR, "_ref", "libhyle_ref_floor.so")
 REF_PAGED_LIB = os.path.join(ORACLE_DIR, "_ref", "libhyle_ref_paged.so")
 
