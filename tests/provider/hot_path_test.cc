@@ -24,6 +24,7 @@
 #include <limits>
 #include <span>
 #include <string>
+#include <thread>
 #include <vector>
 
 #include <cuda_runtime_api.h>
@@ -618,6 +619,88 @@ int main() {
     check(pattern, "fill_async then copy_async on the Queue: ordered on its stream, one wait covers the prefix");
     // a provider made for this backend is refused by a Context of another backend id
     check(fixture.queue.drain().ok() && fixture.context.drain().ok(), "Queue::drain and Context::drain");
+  }
+  {  // Two host threads with a Queue each: prepare on the shared Context and submit concurrently (one producer per
+     // Queue at a time, different Queues concurrently: samples/package/graph/custom_kernel/cuda_main.cc:157-166;
+     // Factory::propose/prepare are const and may run from several threads).  Each lane repeats its operator and
+     // must read back, every time, the bytes a single submit gave before the threads started.
+    struct Lane final {
+      std::string name;
+      Operation operation;
+      std::vector<TensorDesc> in, out;
+      std::vector<Bytes> data;
+      std::string error;
+      int rounds = 0;
+    };
+    const auto weights = dense(DataType::kBFloat16, {256, 8192});
+    const auto rows = dense(DataType::kFloat32, {72, 19456});
+    std::vector<Lane> lanes;
+    lanes.push_back({"b200-q8_0-roundtrip (workspace, status word)", Operation::custom(b200::Q8_0Roundtrip{}), {weights},
+                     {dense(DataType::kUInt8, {256, 8704}), weights, dense(DataType::kFloat64, {1})},
+                     {bf16_normal(256 * 8192, 70, 0.02f)}});
+    lanes.push_back({"b200-logits-reduce (streaming kernel, workspace, status word)", Operation::custom(b200::LogitsReduce{}), {rows},
+                     {dense(DataType::kFloat32, {72}), dense(DataType::kBFloat16, {72, 19456}), dense(DataType::kInt32, {72}),
+                      dense(DataType::kFloat32, {72})},
+                     {f32_normal(72 * 19456, 71, 4.0f)}});
+    lanes.push_back({"CacheEncode{q8_0} (status word)", Operation::custom(model_ops::CacheEncode{CacheStorage::q8_0().value()}),
+                     {dense(DataType::kBFloat16, {64, 8192})}, {dense(DataType::kUInt8, {64, 8704})}, {bf16_normal(64 * 8192, 72)}});
+    constexpr int kRounds = 40;
+    auto run_lane = [&](Lane &lane, int rounds, std::vector<Bytes> *expected, bool compare) {
+      auto own_queue = fixture.context.create_queue();
+      if (!own_queue) return void(lane.error = "create_queue");
+      std::vector<Tensor> inputs, outputs;
+      for (const auto &desc : lane.in) inputs.emplace_back(desc, resource);
+      for (const auto &desc : lane.out) outputs.emplace_back(desc, resource);
+      for (std::size_t i = 0; i < inputs.size(); ++i)
+        if (!inputs[i].write(lane.data[i]).ok()) return void(lane.error = "writing an input");
+      std::vector<ConstTensorView> in_views;
+      std::vector<TensorView> out_views;
+      for (auto &t : inputs) in_views.push_back(t.view.as_const());
+      for (auto &t : outputs) out_views.push_back(t.view);
+      auto prepared = prepare(fixture.context, lane.operation, std::span<const ConstTensorView>(in_views),
+                              std::span<const TensorView>(out_views), resource);
+      if (!prepared) return void(lane.error = "prepare: " + std::string(prepared.error().message()));
+      const auto requirement = prepared->workspace_requirement();
+      mem::Buffer workspace;
+      if (requirement.size != 0) {
+        workspace = mem::Buffer::create(resource, requirement.size, requirement.alignment).value();
+        workspace.view().fill(kPoison).IgnoreError();
+      }
+      auto invocation = prepared->create_invocation(requirement.size != 0 ? workspace.view() : mem::BufferView{});
+      if (!invocation) return void(lane.error = "create_invocation: " + std::string(invocation.error().message()));
+      for (int round = 0; round < rounds; ++round) {
+        for (auto &t : outputs) t.storage.view().fill(kCanary).IgnoreError();
+        auto done = invocation->submit(*own_queue, in_views, out_views);
+        if (!done) return void(lane.error = "submit: " + std::string(done.error().message()));
+        const Status waited = done->wait();
+        if (!waited.ok()) return void(lane.error = "wait: " + std::string(waited.message()));
+        for (std::size_t i = 0; i < outputs.size(); ++i) {
+          Bytes now = outputs[i].read();
+          if (!compare) expected->push_back(std::move(now));
+          else if (now != (*expected)[i]) return void(lane.error = "output " + std::to_string(i) + " differs in round " + std::to_string(round));
+        }
+        ++lane.rounds;
+      }
+      if (!own_queue->drain().ok()) lane.error = "drain";
+    };
+    std::vector<std::vector<Bytes>> expected(lanes.size());
+    for (std::size_t k = 0; k < lanes.size(); ++k) run_lane(lanes[k], 1, &expected[k], false);
+    bool alone = true;
+    for (auto &lane : lanes) {
+      alone = alone && lane.error.empty();
+      lane.rounds = 0;
+    }
+    if (alone) {
+      std::vector<std::thread> threads;
+      for (std::size_t k = 0; k < lanes.size(); ++k)
+        threads.emplace_back([&, k] { run_lane(lanes[k], kRounds, &expected[k], true); });
+      for (auto &thread : threads) thread.join();
+    }
+    for (const auto &lane : lanes) {
+      check(lane.error.empty() && lane.rounds == kRounds,
+            "concurrent Queues: " + lane.name + ", " + std::to_string(kRounds) + " submits beside two other host threads, same bytes every time" +
+                (lane.error.empty() ? "" : " [" + lane.error + "]"));
+    }
   }
   {  // what the seam costs on the host: submit() of a prepared invocation against the bare C-ABI call
     const auto x = dense(DataType::kFloat32, {1, 1024});
