@@ -727,9 +727,11 @@ struct Factory final {
   }
 };
 
+// `allocator`: where the Provider's own cold objects live (default: the system allocator), as in
+// make_custom_provider (include/hyle/compute/custom_kernel.h:327-360).
 template <class Backend>
-Result<Provider> make_provider() noexcept {
-  return make_custom_provider(kIdentity, Backend::id(), Factory<Backend>{});
+Result<Provider> make_provider(mem::AllocatorRef allocator = {}) noexcept {
+  return make_custom_provider(kIdentity, Backend::id(), Factory<Backend>{}, allocator);
 }
 
 }  // namespace hyle::compute::b200

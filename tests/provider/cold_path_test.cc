@@ -43,6 +43,19 @@ struct ProbeBackend final {
   }
 };
 
+// The same stand-in under another backend id: a provider made for it must not enter a CPU Context.
+struct ForeignBackend final {
+  static constexpr BackendId id() noexcept { return BackendId{0x6879'6c65'6232'3030ULL, 0x7e57ULL}; }
+  static constexpr hyle::mem::MemoryProperty memory() noexcept { return ProbeBackend::memory(); }
+  static Result<hyle_b200_stream_t> stream(detail::QueueSequence &s) noexcept { return ProbeBackend::stream(s); }
+  static Result<const void *> pointer(hyle::mem::ConstBufferView v) noexcept { return ProbeBackend::pointer(v); }
+  static Result<void *> mutable_pointer(hyle::mem::BufferView v) noexcept { return ProbeBackend::mutable_pointer(v); }
+  static Status status(int code) noexcept { return ProbeBackend::status(code); }
+  static detail::EnqueueResult status_word(detail::QueueSequence &s, unsigned **word) noexcept {
+    return ProbeBackend::status_word(s, word);
+  }
+};
+
 static int failures = 0;
 static void check(bool ok, const char *what) {
   std::printf("%s  %s\n", ok ? "ok  " : "FAIL", what);
@@ -73,6 +86,16 @@ int main() {
   auto context = Context::create(cpu::device(), std::move(*provider));
   check(context.has_value(), "Context::create with the b200 provider as the only provider");
   if (!context) return 1;
+
+  {  // backend mismatch is Unimplemented at Context creation (src/compute/custom_kernel.cc:64-67)
+    auto foreign = b200::make_provider<ForeignBackend>();
+    bool refused = foreign.has_value();
+    if (refused) {
+      auto wrong = Context::create(cpu::device(), std::move(*foreign));
+      refused = !wrong.has_value() && wrong.error().IsUnimplemented();
+    }
+    check(refused, "a provider made for another backend id is refused by a CPU Context: Unimplemented");
+  }
 
   const auto f32_mat = dense(DataType::kFloat32, {64, 4096});
   const auto f32_row = dense(DataType::kFloat32, {4096});
@@ -353,6 +376,67 @@ int main() {
     check(b200::launch_device_lengths_paged_append(arena, rows, words, words, words, lengths, &status, nullptr) ==
               HYLE_B200_NOT_SUPPORTED,
           "device-lengths append: the capacity must hold the directory, the bounds and one page");
+  }
+  {  // Every cold allocation may fail: provider, Context, prepare and create_invocation then end in
+     // ResourceExhausted with nothing left allocated, and the next attempt with memory succeeds (the
+     // reference checks its own sample the same way: tests/compute/custom_kernel_test.cc:541-581).
+    struct Budget final {
+      hyle::mem::AllocatorRef backing = hyle::mem::system_allocator();
+      std::size_t asked = 0, refuse_at = SIZE_MAX, live = 0;
+      static void *take(void *self, std::size_t size, std::size_t alignment) noexcept {
+        auto &b = *static_cast<Budget *>(self);
+        if (b.asked++ == b.refuse_at) return nullptr;
+        void *p = b.backing.allocate(size, alignment);
+        if (p != nullptr) ++b.live;
+        return p;
+      }
+      static void give(void *self, void *p, std::size_t size, std::size_t alignment) noexcept {
+        auto &b = *static_cast<Budget *>(self);
+        if (p != nullptr) --b.live;
+        b.backing.deallocate(p, size, alignment);
+      }
+      static void *resize(void *self, void *p, std::size_t old_size, std::size_t size, std::size_t alignment) noexcept {
+        auto &b = *static_cast<Budget *>(self);
+        if (size != 0 && b.asked++ == b.refuse_at) return nullptr;
+        void *next = b.backing.reallocate(p, old_size, size, alignment);
+        if (size == 0) {
+          if (p != nullptr) --b.live;
+        } else if (next != nullptr && p == nullptr) {
+          ++b.live;
+        }
+        return next;
+      }
+      hyle::mem::AllocatorRef ref() noexcept { return {&take, &give, &resize, this}; }
+    };
+    const std::array add_in{f32_mat, f32_row};
+    const std::array add_out{f32_mat};
+    auto attempt = [&](Budget &budget) -> Status {
+      auto made = b200::make_provider<ProbeBackend>(budget.ref());
+      if (!made) return std::move(made).error();
+      const std::array bindings{ProviderBinding{std::move(*made), 100}};
+      auto own = Context::create(cpu::device(), {.metadata_allocator = budget.ref(), .providers = bindings});
+      if (!own) return std::move(own).error();
+      auto prepared = prepare(*own, Operation(Binary{BinaryKind::kAdd}), add_in, add_out, hyle::mem::system_resource());
+      if (!prepared) return std::move(prepared).error();
+      if (prepared->provider().id != b200::kIdentity.id) return Status::Internal("another provider was selected");
+      auto invocation = prepared->create_invocation();
+      if (!invocation) return std::move(invocation).error();
+      return Status::Ok();
+    };
+    Budget budget;
+    const bool plain = attempt(budget).ok() && budget.live == 0;
+    const std::size_t allocations = budget.asked;
+    bool every = plain && allocations > 0;
+    for (std::size_t k = 0; every && k < allocations; ++k) {
+      budget.asked = 0;
+      budget.refuse_at = k;
+      every = attempt(budget).IsResourceExhausted() && budget.live == 0;
+      budget.asked = 0;
+      budget.refuse_at = SIZE_MAX;
+      every = every && attempt(budget).ok() && budget.live == 0;
+    }
+    std::printf("      %zu cold allocations between make_provider and create_invocation\n", allocations);
+    check(every, "each cold allocation refused in turn: ResourceExhausted, nothing left allocated, the next attempt succeeds");
   }
   std::printf("%d failure(s)\n", failures);
   return failures == 0 ? 0 : 1;
