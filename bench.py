@@ -1084,18 +1084,21 @@ def run_gpu(args):
     # step as it ran above.  step - slowest bare kernel = waiting for the slowest rank + the exchange.
     rank_split = None
     if world > 1:
-        pairs = [(torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)) for _ in range(10)]
+        # timed like the step itself: one pair of events around a run of launches (an event between two
+        # launches costs more than the exchange this split is looking for)
+        alone_launches = 20
+        first, last = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
         for _ in range(3):
             lib.hyle_b200_q8_0_roundtrip_bf16(stream, w.data_ptr(), count, blocks.data_ptr(), decoded.data_ptr(),
                                               partial.data_ptr(), None, workspace.data_ptr(), workspace.numel())
         torch.cuda.synchronize()
-        for a, b in pairs:
-            a.record()
+        first.record()
+        for _ in range(alone_launches):
             lib.hyle_b200_q8_0_roundtrip_bf16(stream, w.data_ptr(), count, blocks.data_ptr(), decoded.data_ptr(),
                                               partial.data_ptr(), None, workspace.data_ptr(), workspace.numel())
-            b.record()
+        last.record()
         torch.cuda.synchronize()
-        mine = {"rank": rank, "kernel_alone_us": round(statistics.mean(event_pairs_ms(pairs)) * 1e3, 2),
+        mine = {"rank": rank, "kernel_alone_us": round(first.elapsed_time(last) / alone_launches * 1e3, 2),
                 "step_us": round(launch_ms * 1e3, 2)}
         gathered = [None] * world
         dist.all_gather_object(gathered, mine)
@@ -1103,7 +1106,7 @@ def run_gpu(args):
         rank_split = {"per_rank": gathered, "slowest_kernel_alone_us": slowest,
                       "step_us_max": max(g["step_us"] for g in gathered),
                       "wait_and_exchange_us": round(max(g["step_us"] for g in gathered) - slowest, 2),
-                      "note": "kernel_alone = the round trip without the exchange, timed per rank by CUDA events; "
+                      "note": "kernel_alone = the round trip without the exchange, a run of 20 launches timed per rank by one pair of CUDA events; "
                               "step = the fused launch including the wait for the slowest rank's sum"}
 
     # end-to-end from host buffers (every rank moves its own shard).  The pinned staging is

@@ -35,7 +35,7 @@ STATUS_SCAN_OVERFLOW = 16
 STATUS_STREAM_WAIT_TIMEOUT = 32
 EXCHANGE_MAX_RANKS, EXCHANGE_MAILBOX_BYTES, EXCHANGE_HANDLE_BYTES = 8, 256, 64
 
-ABI_VERSION = 19
+ABI_VERSION = 20
 
 _p = ctypes.c_void_p
 _u64 = ctypes.c_uint64
@@ -74,6 +74,7 @@ SIGNATURES = {
     "hyle_b200_q8_0_encode": (_i, [_p, _i, _p, _u64, _p, _p]),
     "hyle_b200_fp8_e4m3_encode": (_i, [_p, _i, _p, _u64, _f, _p, _p]),
     "hyle_b200_strided_cast": (_i, [_p, _i, _i, _p, _p, _u32, _p, _p]),
+    "hyle_b200_strided_scatter": (_i, [_p, _i, _p, _p, _u32, _p, _p]),
     "hyle_b200_scan": (_i, [_p, _i, _p, _p, _u64, _u64, _i, _p]),
     "hyle_b200_paged_append": (_i, [_p, _p, _p, _p, _u32, _u32, _u32, _u32, _u64]),
     "hyle_b200_paged_append_device_lengths": (_i, [_p, _p, _p, _p, _p, _p, _u32, _u32, _u32, _u32, _u64, _u32, _p]),

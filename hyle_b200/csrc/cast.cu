@@ -754,6 +754,97 @@ int launch_strided(cudaStream_t stream, const void *in, void *out, uint64_t coun
                 view);
 }
 
+// ---- dense -> strided view ---------------------------------------------------------------------------
+// The mirror of the kernels above for OUTPUTS: an operator's dense result is placed into a destination
+// that is a view (a slice of a larger tensor, a permuted layout), as the reference's tensor kernels write
+// every output through its byte strides (src/compute_provider_cuda/tensor_kernel.cu:70-108).  Bits are
+// moved; the element type is the same on both sides.  `Word` may be wider than the element: when the
+// innermost axis is contiguous and everything is 16-byte aligned the host widens elements to uint4.
+template <class Word, class Index>
+__global__ void __launch_bounds__(kThreads)
+scatter_kernel(const Word *__restrict__ in, unsigned char *__restrict__ out, uint64_t count, const View view) {
+  grid_dependency_sync();
+  const uint64_t stride = static_cast<uint64_t>(gridDim.x) * kThreads;
+  auto place = [&](uint64_t i, Word word) {
+    Index rest = static_cast<Index>(i);
+    int64_t offset = 0;
+#pragma unroll
+    for (int d = 7; d >= 1; --d) {
+      if (d < static_cast<int>(view.rank)) {
+        const Index extent = static_cast<Index>(view.dims[d]);
+        const Index outer = rest / extent;
+        offset += static_cast<int64_t>(rest - outer * extent) * view.strides[d];
+        rest = outer;
+      }
+    }
+    if (view.rank != 0) offset += static_cast<int64_t>(rest) * view.strides[0];
+    *reinterpret_cast<Word *>(out + offset) = word;
+  };
+  constexpr int kBatch = 8;  // dense loads in flight per thread
+  uint64_t i = static_cast<uint64_t>(blockIdx.x) * kThreads + threadIdx.x;
+  for (; i + (kBatch - 1) * stride < count; i += kBatch * stride) {
+    Word words[kBatch];
+#pragma unroll
+    for (int k = 0; k < kBatch; ++k) words[k] = in[i + k * stride];
+#pragma unroll
+    for (int k = 0; k < kBatch; ++k) place(i + k * stride, words[k]);
+  }
+  for (; i < count; i += stride) place(i, in[i]);
+}
+
+// A long innermost axis: a CTA-step takes a segment of one innermost run, its offset computed once.
+template <class Word>
+__global__ void __launch_bounds__(kThreads)
+scatter_runs_kernel(const Word *__restrict__ in, unsigned char *__restrict__ out, uint64_t runs, const View view) {
+  grid_dependency_sync();
+  constexpr int kBatch = 8;
+  constexpr uint64_t kSegment = static_cast<uint64_t>(kThreads) * kBatch;
+  const uint64_t inner = view.dims[view.rank - 1];
+  const int64_t inner_stride = view.strides[view.rank - 1];
+  const uint64_t segments = (inner + kSegment - 1) / kSegment;
+  for (uint64_t unit = blockIdx.x; unit < runs * segments; unit += gridDim.x) {
+    const uint64_t run = unit / segments, segment = unit - run * segments;
+    uint64_t rest = run;
+    int64_t offset = 0;
+#pragma unroll
+    for (int d = 6; d >= 1; --d) {
+      if (d + 1 < static_cast<int>(view.rank)) {
+        const uint64_t outer = rest / view.dims[d];
+        offset += static_cast<int64_t>(rest - outer * view.dims[d]) * view.strides[d];
+        rest = outer;
+      }
+    }
+    if (view.rank > 1) offset += static_cast<int64_t>(rest) * view.strides[0];
+    const uint64_t first = segment * kSegment + threadIdx.x;
+    Word words[kBatch];
+#pragma unroll
+    for (int k = 0; k < kBatch; ++k) {
+      const uint64_t j = first + static_cast<uint64_t>(k) * kThreads;
+      if (j < inner) words[k] = in[run * inner + j];
+    }
+#pragma unroll
+    for (int k = 0; k < kBatch; ++k) {
+      const uint64_t j = first + static_cast<uint64_t>(k) * kThreads;
+      if (j < inner) *reinterpret_cast<Word *>(out + offset + static_cast<int64_t>(j) * inner_stride) = words[k];
+    }
+  }
+}
+
+template <class Word>
+int launch_scatter(cudaStream_t stream, const void *in, void *out, uint64_t count, const View &view) {
+  if (view.rank != 0 && view.dims[view.rank - 1] >= 256) {
+    const uint64_t inner = view.dims[view.rank - 1], runs = count / inner;
+    const uint64_t units = runs * ((inner + kThreads * 8 - 1) / (kThreads * 8));
+    const unsigned grid = clamp_grid(units, static_cast<uint64_t>(sm_count()) * kCtasPerSm);
+    return launch(scatter_runs_kernel<Word>, dim3(grid), dim3(kThreads), 0, stream, static_cast<const Word *>(in),
+                  static_cast<unsigned char *>(out), runs, view);
+  }
+  const unsigned grid = clamp_grid((count + kThreads * 8 - 1) / (kThreads * 8), static_cast<uint64_t>(sm_count()) * kCtasPerSm);
+  auto kernel = count <= 0xffffffffull ? scatter_kernel<Word, uint32_t> : scatter_kernel<Word, uint64_t>;
+  return launch(kernel, dim3(grid), dim3(kThreads), 0, stream, static_cast<const Word *>(in), static_cast<unsigned char *>(out),
+                count, view);
+}
+
 inline int element_bytes(int dtype) {
   switch (dtype) {
     case HYLE_B200_F32: case HYLE_B200_I32: return 4;
@@ -887,4 +978,47 @@ extern "C" int hyle_b200_strided_cast(hyle_b200_stream_t stream, int source_dtyp
   HB_STRIDED(HYLE_B200_E5M2, HYLE_B200_E4M3);
 #undef HB_STRIDED
   return HYLE_B200_NOT_SUPPORTED;
+}
+
+extern "C" int hyle_b200_strided_scatter(hyle_b200_stream_t stream, int dtype, const void *in, void *out, uint32_t rank,
+                                         const int64_t *dims, const int64_t *byte_strides) {
+  const int width = element_bytes(dtype);
+  if (width == 0) return HYLE_B200_NOT_SUPPORTED;
+  if (rank > 8 || (rank != 0 && (dims == nullptr || byte_strides == nullptr))) return HYLE_B200_INVALID_VALUE;
+  uint64_t count = 1;
+  for (uint32_t d = 0; d < rank; ++d) {
+    if (dims[d] < 0 || byte_strides[d] % width != 0) return HYLE_B200_INVALID_VALUE;
+    if (dims[d] > 1 && byte_strides[d] == 0) return HYLE_B200_INVALID_VALUE;  // two elements at one address
+    if (dims[d] != 0 && count > 0xffffffffffffffffull / static_cast<uint64_t>(dims[d])) return HYLE_B200_INVALID_VALUE;
+    count *= static_cast<uint64_t>(dims[d]);
+  }
+  if (count == 0) return HYLE_B200_OK;
+  if (in == nullptr || out == nullptr || !aligned_to(in, width) || !aligned_to(out, width)) return HYLE_B200_INVALID_VALUE;
+  View view{};
+  for (uint32_t d = 0; d < rank; ++d) {
+    if (dims[d] == 1) continue;
+    if (view.rank != 0 && view.strides[view.rank - 1] == byte_strides[d] * dims[d]) {
+      view.dims[view.rank - 1] *= static_cast<uint64_t>(dims[d]);
+      view.strides[view.rank - 1] = byte_strides[d];
+    } else {
+      view.dims[view.rank] = static_cast<uint64_t>(dims[d]);
+      view.strides[view.rank] = byte_strides[d];
+      ++view.rank;
+    }
+  }
+  auto s = reinterpret_cast<cudaStream_t>(stream);
+  if (view.rank == 0 || (view.rank == 1 && view.strides[0] == width))
+    return static_cast<int>(cudaMemcpyAsync(out, in, count * width, cudaMemcpyDeviceToDevice, s));
+  // Contiguous innermost runs of whole, aligned 16-byte groups move as uint4.
+  const uint32_t last = view.rank - 1;
+  bool wide = view.strides[last] == width && (view.dims[last] * width) % 16 == 0 && aligned_to(in, 16) && aligned_to(out, 16);
+  for (uint32_t d = 0; d < last; ++d) wide = wide && view.strides[d] % 16 == 0;
+  if (wide) {
+    view.dims[last] = view.dims[last] * width / 16;
+    view.strides[last] = 16;
+    return launch_scatter<uint4>(s, in, out, count * width / 16, view);
+  }
+  if (width == 4) return launch_scatter<uint32_t>(s, in, out, count, view);
+  if (width == 2) return launch_scatter<uint16_t>(s, in, out, count, view);
+  return launch_scatter<uint8_t>(s, in, out, count, view);
 }

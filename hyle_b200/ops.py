@@ -386,6 +386,27 @@ def strided_cast_raw(x: torch.Tensor, source: int, destination: int) -> torch.Te
     return out
 
 
+def strided_scatter(dense: torch.Tensor, out: torch.Tensor) -> torch.Tensor:
+    """Place the dense tensor ``dense`` into ``out``, ANY view of the same shape and element size that does not
+    overlap itself (a slice of a larger tensor, a permuted layout); bytes of ``out``'s storage outside the view
+    are left alone.  Returns ``out``."""
+    _device_tensor(dense, "dense")
+    if not out.is_cuda or out.device != dense.device:
+        raise ValueError("out must be a CUDA tensor on dense's device")
+    if not dense.is_contiguous() or tuple(dense.shape) != tuple(out.shape) or dense.element_size() != out.element_size():
+        raise ValueError("dense must be contiguous and have out's shape and element size")
+    if out.dim() > 8:
+        raise ValueError("views of rank <= 8")
+    dtype = {4: abi.F32, 2: abi.BF16, 1: abi.BOOL}.get(out.element_size())
+    if dtype is None:
+        raise ValueError("elements of 1, 2 or 4 bytes")
+    dims = (ctypes.c_int64 * max(1, out.dim()))(*out.shape)
+    strides = (ctypes.c_int64 * max(1, out.dim()))(*[s * out.element_size() for s in out.stride()])
+    abi.check("hyle_b200_strided_scatter", abi.load().hyle_b200_strided_scatter(
+        _stream(), dtype, dense.data_ptr(), out.data_ptr(), out.dim(), dims, strides))
+    return out
+
+
 def scan(x: torch.Tensor, exclusive: bool = False, status: Optional[torch.Tensor] = None) -> torch.Tensor:
     """Scan{axis=-1, exclusive}: prefix sums along the last axis of a dense f32 / i32 tensor.  For i32 a
     ``status`` word is required: abi.STATUS_SCAN_OVERFLOW is set there, and the result left unwritten, when

@@ -43,7 +43,7 @@ extern "C" {
 /* Same object as cudaStream_t; spelled out so C callers need no CUDA header. */
 typedef struct CUstream_st *hyle_b200_stream_t;
 
-#define HYLE_B200_ABI_VERSION 19
+#define HYLE_B200_ABI_VERSION 20
 
 enum hyle_b200_result {
   HYLE_B200_OK = 0,
@@ -366,6 +366,19 @@ HYLE_B200_API int hyle_b200_strided_cast(hyle_b200_stream_t stream, int source_d
                                          int destination_dtype, const void *in, void *out,
                                          uint32_t rank, const int64_t *dims,
                                          const int64_t *byte_strides);
+
+/* The mirror for outputs: a dense row-major tensor `in` is placed INTO A STRIDED VIEW `out` of the same
+ * element type (bits are moved): element (i0, ..., ik) goes byte_strides[0]*i0 + ... bytes from `out`
+ * (rank <= 8; strides are multiples of the element size and may be negative, but not zero on an axis
+ * longer than one: two elements would share an address).  The reference's tensor kernels write every
+ * output through its byte strides (src/compute_provider_cuda/tensor_kernel.cu:70-108); here an operator
+ * writes its dense result and this entry places it, e.g. into a slice of a larger tensor.  Bytes of the
+ * destination outside the view are not touched.  dtype: any storage type of hyle_b200_cast (only its
+ * width matters).  Contiguous innermost runs move 16 bytes per thread when everything is 16-byte
+ * aligned; a destination whose innermost axis is strided is written element by element. */
+HYLE_B200_API int hyle_b200_strided_scatter(hyle_b200_stream_t stream, int dtype, const void *in, void *out,
+                                            uint32_t rank, const int64_t *dimensions,
+                                            const int64_t *byte_strides);
 
 /* Select (include/hyle/compute/operation.h:305, inference src/compute_ops/operation.cc:1309-1328):
  * out[i] = condition[i] != 0 ? when_true[i % true_period] : when_false[i % false_period]; elements

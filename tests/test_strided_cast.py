@@ -138,3 +138,75 @@ def test_strided_cast_negative_strides_and_arguments():
     empty = (ctypes.c_int64 * 2)(0, 6)
     assert library.hyle_b200_strided_cast(stream, abi.F32, abi.F32, None, None, 2, empty, strides) == abi.OK
     assert library.hyle_b200_strided_cast(stream, abi.F32, abi.BF16, x.data_ptr(), out.data_ptr(), 0, None, None) == abi.OK  # a scalar
+
+
+# ---- the mirror: a dense result placed into a strided destination ---------------------------------------------
+
+
+def scatter_destinations(base):
+    """Views of a base tensor [6, 40, 12, 320] that do not overlap themselves."""
+    return {
+        "dense": base,
+        "slice_inner": base[..., 16:272],            # contiguous runs of 256 elements: 16-byte groups when aligned
+        "slice_inner_odd": base[..., 3:300],          # ragged, unaligned runs
+        "slice_outer_step": base[1::2, :, ::3],
+        "short_inner": base[..., 5:12],               # the element-wise kernel
+        "transpose_last_two": base.transpose(-1, -2),
+        "permute_all": base.permute(3, 1, 0, 2),
+        "inner_step": base[2, :, 3, ::2],
+        "one_row": base[1, 2, 3, 8:],
+        "single": base[1, 2, 3, 4],
+        "rank8": base.reshape(2, 3, 5, 8, 3, 4, 16, 20).permute(7, 0, 5, 2, 3, 1, 6, 4),
+    }
+
+
+@pytest.mark.gpu
+@pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16, torch.uint8])
+def test_strided_scatter_places_a_dense_tensor_into_a_view_and_touches_nothing_else(dtype):
+    abi.load()
+    rng = np.random.default_rng(91)
+    shape = (6, 40, 12, 320)
+    word = {torch.float32: np.uint32, torch.bfloat16: np.uint16, torch.uint8: np.uint8}[dtype]
+    before = rng.integers(0, np.iinfo(word).max, shape, dtype=word, endpoint=True)
+    for name in scatter_destinations(torch.from_numpy(before)):
+        host = before.copy()
+        h_view = scatter_destinations(torch.from_numpy(host))[name]
+        payload = rng.integers(0, np.iinfo(word).max, tuple(h_view.shape), dtype=word, endpoint=True)
+        h_view.copy_(torch.from_numpy(payload))  # what the destination's storage must look like afterwards
+        storage = torch.from_numpy(before.copy()).cuda()
+        storage = storage.view(dtype) if dtype != torch.uint8 else storage
+        d_view = scatter_destinations(storage)[name]
+        dense = torch.from_numpy(payload).cuda()
+        dense = dense.view(dtype) if dtype != torch.uint8 else dense
+        returned = ops.strided_scatter(dense.reshape(d_view.shape), d_view)
+        assert returned.data_ptr() == d_view.data_ptr()
+        got = storage.cpu().view(torch.uint8).numpy().reshape(-1)
+        assert np.array_equal(got, host.view(np.uint8).reshape(-1)), name
+
+
+@pytest.mark.gpu
+def test_strided_scatter_then_strided_cast_is_the_identity_and_arguments_are_checked():
+    library = abi.load()
+    stream = torch.cuda.current_stream().cuda_stream
+    x = torch.arange(24, dtype=torch.float32, device="cuda").reshape(4, 6)
+    storage = torch.full((8, 12), -1.0, dtype=torch.float32, device="cuda")
+    view = storage[1:8:2, 1:12:2]
+    ops.strided_scatter(x, view)
+    assert torch.equal(ops.strided_cast(view), x)
+    assert torch.equal(storage[::2], torch.full((4, 12), -1.0, device="cuda"))
+    dims = (ctypes.c_int64 * 2)(4, 6)
+    # both axes reversed, starting from the last element of a dense [4, 6] destination
+    out = torch.zeros(4, 6, dtype=torch.float32, device="cuda")
+    reverse = (ctypes.c_int64 * 2)(-24, -4)
+    assert library.hyle_b200_strided_scatter(stream, abi.F32, x.data_ptr(), out.data_ptr() + 23 * 4, 2, dims, reverse) == abi.OK
+    torch.cuda.synchronize()
+    assert torch.equal(out, x.flip(0, 1))
+    broadcast = (ctypes.c_int64 * 2)(0, 4)  # four rows at one address: not a destination
+    assert library.hyle_b200_strided_scatter(stream, abi.F32, x.data_ptr(), out.data_ptr(), 2, dims, broadcast) == abi.INVALID_VALUE
+    odd = (ctypes.c_int64 * 2)(24, 2)
+    assert library.hyle_b200_strided_scatter(stream, abi.F32, x.data_ptr(), out.data_ptr(), 2, dims, odd) == abi.INVALID_VALUE
+    assert library.hyle_b200_strided_scatter(stream, abi.F32, x.data_ptr(), out.data_ptr(), 9, dims, reverse) == abi.INVALID_VALUE
+    assert library.hyle_b200_strided_scatter(stream, 99, x.data_ptr(), out.data_ptr(), 2, dims, reverse) == abi.NOT_SUPPORTED
+    empty = (ctypes.c_int64 * 2)(0, 6)
+    assert library.hyle_b200_strided_scatter(stream, abi.F32, None, None, 2, empty, reverse) == abi.OK
+    assert library.hyle_b200_strided_scatter(stream, abi.F32, x.data_ptr(), out.data_ptr(), 0, None, None) == abi.OK  # a scalar
