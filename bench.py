@@ -447,7 +447,16 @@ def other_ops(torch, peak_gbs, only=None, iterations=40):
         ms = time_op(torch, lambda i: lib.hyle_b200_strided_cast(
             stream, abi.F32, abi.BF16, x[i].data_ptr(), y16[i].data_ptr(), 2, half, sliced), sets, iterations)
         report("strided_cast_f32_to_bf16_slice", "4096x2048 slice of 4096x4096 rows", side * side // 2, side * side // 2 * 6, ms, sets)
-        del x, y, y16
+        # the mirror: dense rows placed into the left half of wider rows (16-byte groups), and into a transposed layout
+        narrow = [torch.randn(side, side // 2, device=dev) for _ in range(sets)]
+        ms = time_op(torch, lambda i: lib.hyle_b200_strided_scatter(
+            stream, abi.F32, narrow[i].data_ptr(), y[i].data_ptr(), 2, half, sliced), sets, iterations)
+        report("strided_scatter_f32_slice", "4096x2048 placed into a slice of 4096x4096 rows", side * side // 2, side * side // 2 * 8, ms, sets)
+        ms = time_op(torch, lambda i: lib.hyle_b200_strided_scatter(
+            stream, abi.F32, x[i].data_ptr(), y[i].data_ptr(), 2, dims, transposed), sets, iterations)
+        report("strided_scatter_f32_transpose", "4096x4096 written through a transposed view (the tiled transposition, from the destination's side)", side * side,
+               side * side * 8, ms, sets)
+        del x, y, y16, narrow
 
     # Scan{axis=-1}: f32 over vocabulary rows and over 4096 x 4096; i32 (two passes: check, then write)
     if wanted("scan"):

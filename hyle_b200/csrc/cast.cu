@@ -845,6 +845,32 @@ int launch_scatter(cudaStream_t stream, const void *in, void *out, uint64_t coun
                 count, view);
 }
 
+// Drops axes of extent 1 and merges neighbours that are contiguous with each other.
+inline View merged_view(uint32_t rank, const int64_t *dims, const int64_t *byte_strides) {
+  View view{};
+  for (uint32_t d = 0; d < rank; ++d) {
+    if (dims[d] == 1) continue;
+    if (view.rank != 0 && view.strides[view.rank - 1] == byte_strides[d] * dims[d]) {
+      view.dims[view.rank - 1] *= static_cast<uint64_t>(dims[d]);
+      view.strides[view.rank - 1] = byte_strides[d];
+    } else {
+      view.dims[view.rank] = static_cast<uint64_t>(dims[d]);
+      view.strides[view.rank] = byte_strides[d];
+      ++view.rank;
+    }
+  }
+  return view;
+}
+
+// Bits of `width`-byte elements from a (merged) view into a dense tensor.
+inline int copy_from_view(cudaStream_t s, int width, const void *in, void *out, uint64_t count, const View &view) {
+  if (view.rank == 0 || (view.rank == 1 && view.strides[0] == width))
+    return static_cast<int>(cudaMemcpyAsync(out, in, count * width, cudaMemcpyDeviceToDevice, s));
+  if (width == 4) return launch_strided<HYLE_B200_F32, HYLE_B200_F32, true>(s, in, out, count, view);
+  if (width == 2) return launch_strided<HYLE_B200_BF16, HYLE_B200_BF16, true>(s, in, out, count, view);
+  return launch_strided<HYLE_B200_BOOL, HYLE_B200_BOOL, true>(s, in, out, count, view);
+}
+
 inline int element_bytes(int dtype) {
   switch (dtype) {
     case HYLE_B200_F32: case HYLE_B200_I32: return 4;
@@ -931,27 +957,10 @@ extern "C" int hyle_b200_strided_cast(hyle_b200_stream_t stream, int source_dtyp
   }
   if (count == 0) return HYLE_B200_OK;
   if (in == nullptr || out == nullptr || !aligned_to(in, width) || !aligned_to(out, out_width)) return HYLE_B200_INVALID_VALUE;
-  // Drop axes of extent 1 and merge neighbours that are contiguous with each other.
-  View view{};
-  for (uint32_t d = 0; d < rank; ++d) {
-    if (dims[d] == 1) continue;
-    if (view.rank != 0 && view.strides[view.rank - 1] == byte_strides[d] * dims[d]) {
-      view.dims[view.rank - 1] *= static_cast<uint64_t>(dims[d]);
-      view.strides[view.rank - 1] = byte_strides[d];
-    } else {
-      view.dims[view.rank] = static_cast<uint64_t>(dims[d]);
-      view.strides[view.rank] = byte_strides[d];
-      ++view.rank;
-    }
-  }
+  const View view = merged_view(rank, dims, byte_strides);
   auto s = reinterpret_cast<cudaStream_t>(stream);
   const bool dense = view.rank == 0 || (view.rank == 1 && view.strides[0] == width);
-  if (source_dtype == destination_dtype) {
-    if (dense) return static_cast<int>(cudaMemcpyAsync(out, in, count * width, cudaMemcpyDeviceToDevice, s));
-    if (width == 4) return launch_strided<HYLE_B200_F32, HYLE_B200_F32, true>(s, in, out, count, view);
-    if (width == 2) return launch_strided<HYLE_B200_BF16, HYLE_B200_BF16, true>(s, in, out, count, view);
-    return launch_strided<HYLE_B200_BOOL, HYLE_B200_BOOL, true>(s, in, out, count, view);
-  }
+  if (source_dtype == destination_dtype) return copy_from_view(s, width, in, out, count, view);
   if (dense) return hyle_b200_cast(stream, source_dtype, destination_dtype, in, out, count);
 #define HB_STRIDED(S, D) \
   if (source_dtype == S && destination_dtype == D) return launch_strided<S, D, false>(s, in, out, count, view)
@@ -994,21 +1003,40 @@ extern "C" int hyle_b200_strided_scatter(hyle_b200_stream_t stream, int dtype, c
   }
   if (count == 0) return HYLE_B200_OK;
   if (in == nullptr || out == nullptr || !aligned_to(in, width) || !aligned_to(out, width)) return HYLE_B200_INVALID_VALUE;
-  View view{};
-  for (uint32_t d = 0; d < rank; ++d) {
-    if (dims[d] == 1) continue;
-    if (view.rank != 0 && view.strides[view.rank - 1] == byte_strides[d] * dims[d]) {
-      view.dims[view.rank - 1] *= static_cast<uint64_t>(dims[d]);
-      view.strides[view.rank - 1] = byte_strides[d];
-    } else {
-      view.dims[view.rank] = static_cast<uint64_t>(dims[d]);
-      view.strides[view.rank] = byte_strides[d];
-      ++view.rank;
-    }
-  }
+  View view = merged_view(rank, dims, byte_strides);
   auto s = reinterpret_cast<cudaStream_t>(stream);
   if (view.rank == 0 || (view.rank == 1 && view.strides[0] == width))
     return static_cast<int>(cudaMemcpyAsync(out, in, count * width, cudaMemcpyDeviceToDevice, s));
+  // A destination that is dense in a PERMUTED axis order (a transposed layout without gaps) is the same
+  // move seen from the other side: its storage, walked in its own order, reads the dense source through
+  // permuted strides -- the gathering kernels above, with their shared-memory tiles for transpositions.
+  {
+    uint32_t order[8];
+    for (uint32_t d = 0; d < view.rank; ++d) order[d] = d;
+    for (uint32_t a = 1; a < view.rank; ++a)  // insertion sort, largest destination stride first
+      for (uint32_t b = a; b > 0 && view.strides[order[b]] > view.strides[order[b - 1]]; --b) {
+        const uint32_t t = order[b];
+        order[b] = order[b - 1];
+        order[b - 1] = t;
+      }
+    bool permutation = view.strides[order[view.rank - 1]] == width;
+    for (uint32_t a = 0; permutation && a + 1 < view.rank; ++a)
+      permutation = view.strides[order[a]] == view.strides[order[a + 1]] * static_cast<int64_t>(view.dims[order[a + 1]]);
+    if (permutation) {
+      int64_t source_stride[8];  // of the dense source, per axis of the merged view
+      int64_t running = width;
+      for (int d = static_cast<int>(view.rank) - 1; d >= 0; --d) {
+        source_stride[d] = running;
+        running *= static_cast<int64_t>(view.dims[d]);
+      }
+      int64_t turned_dims[8], turned_strides[8];
+      for (uint32_t a = 0; a < view.rank; ++a) {
+        turned_dims[a] = static_cast<int64_t>(view.dims[order[a]]);
+        turned_strides[a] = source_stride[order[a]];
+      }
+      return copy_from_view(s, width, in, out, count, merged_view(view.rank, turned_dims, turned_strides));
+    }
+  }
   // Contiguous innermost runs of whole, aligned 16-byte groups move as uint4.
   const uint32_t last = view.rank - 1;
   bool wide = view.strides[last] == width && (view.dims[last] * width) % 16 == 0 && aligned_to(in, 16) && aligned_to(out, 16);

@@ -77,10 +77,6 @@ struct Plan final {
   };
   std::array<Gather, 4> gathers{};
   std::uint8_t gather_count = 0;
-  // Strided outputs, the mirror: the kernel writes a dense temporary in the workspace (behind the gathers'
-  // temporaries) and hyle_b200_strided_scatter places it into the output's view.  `input` is the output's index.
-  std::array<Gather, 4> scatters{};
-  std::uint8_t scatter_count = 0;
   std::size_t total_workspace_bytes = 0;  // the kernel's part and the temporaries
 };
 
@@ -452,8 +448,8 @@ inline std::optional<TensorDesc> expanded(const TensorDesc &input, std::span<con
   return *made;
 }
 
-inline std::optional<Plan> match_inputs(const Operation &op, std::span<const TensorDesc> in,
-                                        std::span<const TensorDesc> out) noexcept {
+inline std::optional<Plan> match(const Operation &op, std::span<const TensorDesc> in,
+                                 std::span<const TensorDesc> out) noexcept {
   if (in.size() > 4) return std::nullopt;
   // What each input is read as.  Binary operands follow the NumPy rule on both sides (infer_binary,
   // src/compute_ops/operation.cc:476-486): an operand that is neither the output's shape nor (on the right)
@@ -504,51 +500,6 @@ inline std::optional<Plan> match_inputs(const Operation &op, std::span<const Ten
     }
     gather.offset = end;
     end = aligned_256(end + elements(viewed[i]) * storage_width(gather.dtype));
-  }
-  plan->total_workspace_bytes = end;
-  return plan;
-}
-
-// Dense or strided operands on both sides.  A non-dense OUTPUT (a slice of a larger tensor, a permuted
-// layout: the reference's tensor kernels write through byte strides, tensor_kernel.cu:70-108) is matched
-// as its dense counterpart and placed afterwards.  Not for the checked i32 Scan, whose contract is that a
-// failed check writes nothing: a placed temporary would be written regardless.
-inline std::optional<Plan> match(const Operation &op, std::span<const TensorDesc> in,
-                                 std::span<const TensorDesc> out) noexcept {
-  bool placed = false;
-  for (const auto &desc : out) placed = placed || !desc.is_dense();
-  if (!placed) return match_inputs(op, in, out);
-  if (out.size() > 4) return std::nullopt;
-  std::array<TensorDesc, 4> dense_out{};
-  for (std::size_t i = 0; i < out.size(); ++i) {
-    dense_out[i] = out[i];
-    if (out[i].is_dense()) continue;
-    const auto type = cast_dtype(out[i].data_type());
-    if (!out[i].is_plain() || !type || out[i].rank() == 0) return std::nullopt;
-    for (std::size_t axis = 0; axis < out[i].rank(); ++axis) {
-      const auto stride = out[i].byte_strides()[axis];
-      if (stride < 0 || stride % static_cast<std::int64_t>(storage_width(*type)) != 0) return std::nullopt;
-      if (stride == 0 && out[i].dimensions()[axis] > 1) return std::nullopt;  // two elements at one address
-    }
-    auto made = TensorDesc::dense(out[i].data_type(), out[i].dimensions());
-    if (!made) return std::nullopt;
-    dense_out[i] = *made;
-  }
-  auto plan = match_inputs(op, in, std::span<const TensorDesc>(dense_out.data(), out.size()));
-  if (!plan || (plan->entry == Entry::kScan && plan->dtype == HYLE_B200_I32)) return std::nullopt;
-  std::size_t end = aligned_256(plan->total_workspace_bytes);
-  for (std::size_t i = 0; i < out.size(); ++i) {
-    if (out[i].is_dense()) continue;
-    auto &scatter = plan->scatters[plan->scatter_count++];
-    scatter.input = static_cast<std::uint8_t>(i);
-    scatter.rank = static_cast<std::uint8_t>(out[i].rank());
-    scatter.dtype = *cast_dtype(out[i].data_type());
-    for (std::size_t axis = 0; axis < out[i].rank(); ++axis) {
-      scatter.dimensions[axis] = out[i].dimensions()[axis];
-      scatter.byte_strides[axis] = out[i].byte_strides()[axis];
-    }
-    scatter.offset = end;
-    end = aligned_256(end + elements(out[i]) * storage_width(scatter.dtype));
   }
   plan->total_workspace_bytes = end;
   return plan;
@@ -736,22 +687,8 @@ struct Kernel final {
       invocation.workspace_cleared = true;
       recorded = true;
     }
-    std::array<void *, 4> placed{};
-    for (std::size_t k = 0; k < plan.scatter_count; ++k) {
-      const auto &scatter = plan.scatters[k];
-      placed[k] = out[scatter.input];
-      out[scatter.input] = static_cast<std::byte *>(invocation.workspace) + scatter.offset;
-    }
-    const int launched =
-        launch(plan, *stream, in.data(), out.data(), plan.workspace_bytes != 0 ? invocation.workspace : nullptr, status_word);
-    if (launched != HYLE_B200_OK) return KernelCommandResult::accepted_command(Backend::status(launched));
-    for (std::size_t k = 0; k < plan.scatter_count; ++k) {
-      const auto &scatter = plan.scatters[k];
-      const int moved = hyle_b200_strided_scatter(*stream, scatter.dtype, out[scatter.input], placed[k], scatter.rank,
-                                                  scatter.dimensions.data(), scatter.byte_strides.data());
-      if (moved != HYLE_B200_OK) return KernelCommandResult::accepted_command(Backend::status(moved));
-    }
-    return KernelCommandResult::accepted_command(Backend::status(HYLE_B200_OK));
+    return KernelCommandResult::accepted_command(Backend::status(
+        launch(plan, *stream, in.data(), out.data(), plan.workspace_bytes != 0 ? invocation.workspace : nullptr, status_word)));
   }
 };
 
@@ -772,11 +709,9 @@ struct Factory final {
                           .cost = {.workspace = workspace,
                                    .persistent_bytes = 0,
                                    .copy_bytes = 0,
-                                   .repack_bytes = plan->gather_count + plan->scatter_count != 0
-                                                       ? plan->total_workspace_bytes - aligned_256(plan->workspace_bytes)
-                                                       : 0,
+                                   .repack_bytes = plan->gather_count != 0 ? plan->total_workspace_bytes - aligned_256(plan->workspace_bytes) : 0,
                                    .synchronization_count = 0,
-                                   .dispatch_count = 1u + plan->gather_count + plan->scatter_count},
+                                   .dispatch_count = 1u + plan->gather_count},
                           .implementation = ProviderImplementationId{static_cast<std::uint64_t>(plan->entry) + 1}};
   }
   KernelPreparation prepare(const KernelPrepareRequest &request, mem::AllocatorRef allocator) const noexcept {

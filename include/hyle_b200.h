@@ -373,9 +373,14 @@ HYLE_B200_API int hyle_b200_strided_cast(hyle_b200_stream_t stream, int source_d
  * longer than one: two elements would share an address).  The reference's tensor kernels write every
  * output through its byte strides (src/compute_provider_cuda/tensor_kernel.cu:70-108); here an operator
  * writes its dense result and this entry places it, e.g. into a slice of a larger tensor.  Bytes of the
- * destination outside the view are not touched.  dtype: any storage type of hyle_b200_cast (only its
+ * destination outside the view are not touched.  The public custom-kernel seam never needs it: for exact
+ * shapes the reference's prepare admits only the inferred, dense output description
+ * (src/compute/operation.cc:265-296); it serves callers of the C ABI that own a strided destination
+ * (a provider bound through the reference's private seam, whose bounded shape domains skip that check).  dtype: any storage type of hyle_b200_cast (only its
  * width matters).  Contiguous innermost runs move 16 bytes per thread when everything is 16-byte
- * aligned; a destination whose innermost axis is strided is written element by element. */
+ * aligned; a destination that is dense in a permuted axis order (a transposed layout without gaps) takes
+ * the tiled transposition of hyle_b200_strided_cast seen from the destination's side; any other
+ * destination whose innermost axis is strided is written element by element. */
 HYLE_B200_API int hyle_b200_strided_scatter(hyle_b200_stream_t stream, int dtype, const void *in, void *out,
                                             uint32_t rank, const int64_t *dimensions,
                                             const int64_t *byte_strides);

@@ -151,8 +151,9 @@ def scatter_destinations(base):
         "slice_inner_odd": base[..., 3:300],          # ragged, unaligned runs
         "slice_outer_step": base[1::2, :, ::3],
         "short_inner": base[..., 5:12],               # the element-wise kernel
-        "transpose_last_two": base.transpose(-1, -2),
+        "transpose_last_two": base.transpose(-1, -2),     # dense in a permuted order: the tiled transposition
         "permute_all": base.permute(3, 1, 0, 2),
+        "transposed_slice": base[..., 3:300].transpose(-1, -2),  # a transposition with gaps: element by element
         "inner_step": base[2, :, 3, ::2],
         "one_row": base[1, 2, 3, 8:],
         "single": base[1, 2, 3, 4],
