@@ -57,6 +57,12 @@ __device__ __forceinline__ float f16_to_f32(unsigned short h) {
   asm("cvt.f32.f16 %0, %1;" : "=f"(r) : "h"(h));
   return r;
 }
+// Two f32 -> packed f16 pair, round to nearest even, one conversion instruction for both.
+__device__ __forceinline__ uint32_t pack_f16x2(float lo, float hi) {
+  uint32_t r;
+  asm("cvt.rn.f16x2.f32 %0, %1, %2;" : "=r"(r) : "f"(hi), "f"(lo));
+  return r;
+}
 __device__ __forceinline__ unsigned short f32_to_f16(float v) {
   unsigned short r;
   asm("cvt.rn.f16.f32 %0, %1;" : "=h"(r) : "f"(v));

@@ -46,7 +46,7 @@ __device__ __forceinline__ float narrow_hi(uint32_t w) {
 template <int kDtype>
 __device__ __forceinline__ uint32_t narrow_pack(float lo, float hi) {
   if constexpr (kDtype == HYLE_B200_BF16) return pack_bf16x2(lo, hi);
-  return static_cast<uint32_t>(f32_to_f16(lo)) | (static_cast<uint32_t>(f32_to_f16(hi)) << 16);
+  return pack_f16x2(lo, hi);
 }
 template <int kDtype>
 __device__ __forceinline__ float narrow_scalar(unsigned short s) {

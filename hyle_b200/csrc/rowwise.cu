@@ -390,7 +390,7 @@ struct Stored {
       for (int e = 0; e < 4; ++e)
         words[e] = kDtype == HYLE_B200_BF16
                        ? pack_bf16x2(v[2 * e], v[2 * e + 1])
-                       : static_cast<uint32_t>(f32_to_f16(v[2 * e])) | static_cast<uint32_t>(f32_to_f16(v[2 * e + 1])) << 16;
+                       : pack_f16x2(v[2 * e], v[2 * e + 1]);
       static_cast<uint4 *>(base)[vec] = make_uint4(words[0], words[1], words[2], words[3]);
     }
   }
@@ -979,11 +979,8 @@ masked_softmax_f16_vector_kernel(const uint4 *__restrict__ x, const typename Mas
       if (i < vectors) {
         uint32_t words[4];
 #pragma unroll
-        for (int e = 0; e < 4; ++e) {
-          const uint32_t low = f32_to_f16(valid ? __fmul_rn(v[k][2 * e], inverse) : CUDART_NAN_F);
-          const uint32_t high = f32_to_f16(valid ? __fmul_rn(v[k][2 * e + 1], inverse) : CUDART_NAN_F);
-          words[e] = low | (high << 16);
-        }
+        for (int e = 0; e < 4; ++e)  // inverse is NaN for an invalid row, and NaN times any weight is NaN
+          words[e] = pack_f16x2(__fmul_rn(v[k][2 * e], inverse), __fmul_rn(v[k][2 * e + 1], inverse));
         st_stream(y + row * vectors + i, make_uint4(words[0], words[1], words[2], words[3]));
       }
     }
@@ -993,13 +990,30 @@ masked_softmax_f16_vector_kernel(const uint4 *__restrict__ x, const typename Mas
 
 // Rows of up to 2048 values (a multiple of 8): one WARP per row, the row in registers (up to eight
 // 16-byte loads in flight per lane), shuffles only -- no barrier between the three phases of a row.
-template <int kSlots, bool kAdditive>
+// The kernel is bound by instruction issue and by the XU pipe (exponentials and conversions), not by
+// HBM alone, so the per-value work is kept short.  Always: an invalid row multiplies by inverse = NaN,
+// which needs no select, and two results leave in one packed f32 -> f16x2 conversion.  kFast, for
+// |scale| <= 32 (every attention scale):
+//   - the weight is ex2(fma(v, log2e, -c)) with c = RN(peak * log2e) instead of ex2((v - peak) * log2e).
+//     c differs from peak * log2e by at most half an ulp of c, which is 2^-3 for the values an f16 score
+//     times 32 (plus an f16 addend) can reach, and every exponent of the row is off by that same amount:
+//     it cancels in the normalisation.  (For larger scales half an ulp of c could overflow the exponential
+//     of the maximum itself; they keep the exact subtraction.)
+//   - Boolean masks with a positive scale fold it into the same fma, ex2(fma(x, scale * log2e, -c)), the
+//     maximum taken over the unscaled values (a positive scale keeps the order, NaN and the infinities); a
+//     masked value is -inf before and after;
+//   - the additive form makes v = fma(x, scale, addend) (one rounding where the reference's kernel has two:
+//     an f32 ulp, against an f16 result).
+template <int kSlots, bool kAdditive, bool kFast>
 __global__ void __launch_bounds__(128)
 masked_softmax_f16_warp_kernel(const uint4 *__restrict__ x, const typename MaskVector<kAdditive>::Type *__restrict__ mask,
                                uint4 *__restrict__ y, uint64_t rows, uint32_t vectors, uint64_t mask_rows, float scale) {
   grid_dependency_sync();
+  constexpr float kLog2e = 1.4426950408889634f;
+  constexpr bool kFold = kFast && !kAdditive;
   const int lane = threadIdx.x & 31;
   const uint64_t warps = static_cast<uint64_t>(gridDim.x) * (blockDim.x / 32);
+  const float factor = kFold ? __fmul_rn(scale, kLog2e) : kLog2e;  // of the stored value v in the exponent
   for (uint64_t row = static_cast<uint64_t>(blockIdx.x) * (blockDim.x / 32) + threadIdx.x / 32; row < rows; row += warps) {
     const uint4 *in = x + row * vectors;
     const typename MaskVector<kAdditive>::Type *row_mask = mask + (row % mask_rows) * vectors;
@@ -1019,36 +1033,37 @@ masked_softmax_f16_warp_kernel(const uint4 *__restrict__ x, const typename MaskV
 #pragma unroll
       for (int e = 0; e < 8; ++e) {
         const unsigned short half = static_cast<unsigned short>(e & 1 ? words[e / 2] >> 16 : words[e / 2] & 0xffffu);
-        v[k][e] = masked_score<kAdditive>(__fmul_rn(f16_to_f32(half), scale), mask_element<kAdditive>(m[k], e));
+        const uint32_t mask_word = mask_element<kAdditive>(m[k], e);
+        if constexpr (kFold) v[k][e] = mask_word == 0 ? -CUDART_INF_F : f16_to_f32(half);
+        else if constexpr (kFast) v[k][e] = __fmaf_rn(f16_to_f32(half), scale, f16_to_f32(static_cast<unsigned short>(mask_word)));
+        else v[k][e] = masked_score<kAdditive>(__fmul_rn(f16_to_f32(half), scale), mask_word);
         peak = max_nan(peak, v[k][e]);
       }
     }
     peak = warp_max_nan(peak);
     const bool valid = peak > -CUDART_INF_F && peak < CUDART_INF_F;  // false for NaN too
+    const float neg_c = valid ? -__fmul_rn(peak, factor) : 0.0f;
     float sum = 0.0f;
 #pragma unroll
     for (int k = 0; k < kSlots; ++k) {
 #pragma unroll
       for (int e = 0; e < 8; ++e) {
+        const float exponent = kFast ? __fmaf_rn(v[k][e], factor, neg_c) : __fmul_rn(__fsub_rn(v[k][e], peak), kLog2e);
         float weight;
-        asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(weight) : "f"(__fmul_rn(__fsub_rn(v[k][e], peak), 1.4426950408889634f)));
+        asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(weight) : "f"(exponent));
         v[k][e] = weight;
         sum += weight;
       }
     }
     sum = warp_sum(sum);
-    const float inverse = valid ? __fdiv_rn(1.0f, sum) : CUDART_NAN_F;
+    const float inverse = valid ? __fdiv_rn(1.0f, sum) : CUDART_NAN_F;  // NaN times any weight is NaN
 #pragma unroll
     for (int k = 0; k < kSlots; ++k) {
       const uint32_t i = k * 32 + lane;
       if (i < vectors) {
         uint32_t words[4];
 #pragma unroll
-        for (int e = 0; e < 4; ++e) {
-          const uint32_t low = f32_to_f16(valid ? __fmul_rn(v[k][2 * e], inverse) : CUDART_NAN_F);
-          const uint32_t high = f32_to_f16(valid ? __fmul_rn(v[k][2 * e + 1], inverse) : CUDART_NAN_F);
-          words[e] = low | (high << 16);
-        }
+        for (int e = 0; e < 4; ++e) words[e] = pack_f16x2(__fmul_rn(v[k][2 * e], inverse), __fmul_rn(v[k][2 * e + 1], inverse));
         st_stream(y + row * vectors + i, make_uint4(words[0], words[1], words[2], words[3]));
       }
     }
@@ -1059,7 +1074,9 @@ template <int kSlots, bool kAdditive>
 int launch_masked_softmax_warp(cudaStream_t stream, const void *in, const void *mask, void *out, uint64_t rows,
                                uint32_t vectors, uint64_t mask_rows, float scale) {
   const unsigned grid = clamp_grid((rows + 3) / 4, static_cast<uint64_t>(sm_count()) * 16);
-  return launch(masked_softmax_f16_warp_kernel<kSlots, kAdditive>, dim3(grid), dim3(128), 0, stream, static_cast<const uint4 *>(in),
+  const bool fast = kAdditive ? (scale >= -32.0f && scale <= 32.0f) : (scale > 0.0f && scale <= 32.0f);  // false for NaN
+  return launch(fast ? masked_softmax_f16_warp_kernel<kSlots, kAdditive, true> : masked_softmax_f16_warp_kernel<kSlots, kAdditive, false>,
+                dim3(grid), dim3(128), 0, stream, static_cast<const uint4 *>(in),
                 static_cast<const typename MaskVector<kAdditive>::Type *>(mask), static_cast<uint4 *>(out), rows, vectors, mask_rows,
                 scale);
 }

@@ -870,7 +870,9 @@ def test_masked_scaled_softmax_f16(oracle, cols):
         mask[3, :] = 0                                                    # a fully masked row: all NaN
         x[1, 5, cols // 2] = np.nan; mask[5, cols // 2] = 1
         mask[6, :] = 0; mask[6, cols - 1] = 7                             # any non-zero byte is true
-    for scale in (1.0, 0.125):
+    # positive scales take the kernel that folds the scale into the exponent (rows of up to 2048 values); zero, negative
+    # and huge ones the plain form
+    for scale in (1.0, 0.125, 0.3, -0.5, 0.0, 1e10):
         want16, want32 = oracle.masked_softmax_f16(x.view(np.uint16), mask[None], scale)
         got = ops.masked_softmax_f16(to_dev(x), to_dev(mask), scale).cpu().numpy().view(np.uint16)
         nan = (want16 & 0x7FFF) > 0x7C00
