@@ -277,6 +277,11 @@ HYLE_B200_API int hyle_b200_gated_activation(hyle_b200_stream_t stream, int acti
  * src/simd/sort/top_k.cc:17-27,51-69.
  * Rows holding NaN or +inf, or only -inf, get NaN lse and NaN probs (include/hyle/simd/math.h:307-311);
  * argmax is still defined for them.  Any output pointer may be NULL.
+ * Domain: finite logits below 2^27 (1.3e8) in magnitude.  The kernels subtract one constant,
+ * RN(max * log2 e), from every exponent inside the multiplication; its rounding (half an ulp, at most 8
+ * in that domain) cancels between a weight and the sum and is taken back out of the lse.  Larger
+ * magnitudes (the CPU route subtracts the maximum itself and takes any finite value) are outside what
+ * this entry point computes correctly.
  *
  * Two kernels.  Without a workspace, or for fewer than 64 rows, a thread-block cluster keeps each
  * row in registers / shared memory (rows too wide for that return NOT_SUPPORTED).  With a

@@ -453,6 +453,22 @@ def test_logits_streaming_kernel_shapes_and_invalid_rows(oracle, cols):
     check_logits(oracle, x[:64], workspace=scratch)
 
 
+@pytest.mark.parametrize("offset", [0.0, -3.0e4, 1.0e6, 1.0e8, -1.2e8])
+def test_logits_of_large_magnitude(oracle, offset):
+    """The kernels subtract ONE constant c = RN(max * log2 e) from every exponent of a row, fused into the multiplication.
+    c misses max * log2 e by up to half an ulp of c, the same amount for every element: it cancels between a weight
+    and the sum, and the lse takes it back out.  That holds while half an ulp of c is a small number, i.e. for logits
+    below 2^27 in magnitude -- the domain the header states; both kernels, rows far from zero."""
+    rng = np.random.default_rng(17)
+    cols = 19456
+    spread = max(4.0, abs(offset) * 2.0 ** -20)  # keep neighbours distinguishable in f32 around the offset
+    for rows in (8, 72):                          # the cluster kernel, the streaming kernel
+        x = (np.float32(offset) + np.float32(spread) * rng.standard_normal((rows, cols)).astype(np.float32)).astype(np.float32)
+        x[1, 7] = x[1].max() + np.float32(8.0 * spread)
+        scratch = ops.make_logits_workspace("cuda", rows, cols) if rows >= 64 else None
+        check_logits(oracle, x, workspace=scratch)
+
+
 def test_logits_streaming_kernel_reduces_missing_partials_itself(oracle, vectors=10):
     """The rare path, forced: with a window of one row a second-pass task is claimed right behind the
     first-pass tasks it depends on, and with one poll of patience its warps reduce the missing chunks
