@@ -919,7 +919,7 @@ def test_additive_masked_softmax_f16(oracle, cols):
         addend[6, :] = -np.inf; addend[6, cols - 1] = 3.5
         x[2, 7, cols - 1] = np.inf                                        # +inf score: NaN
         addend[8, 0] = np.inf
-    for scale in (1.0, 0.125):
+    for scale in (1.0, 0.125, -0.7, 100.0):  # beyond |scale| = 32 the kernel keeps the exact subtraction of the maximum
         want16, _ = oracle.masked_softmax_f16(x.view(np.uint16), addend[None], scale)
         got = ops.masked_softmax_f16(to_dev(x), to_dev(addend), scale).cpu().numpy().view(np.uint16)
         nan = (want16 & 0x7FFF) > 0x7C00
