@@ -209,34 +209,42 @@ __device__ __forceinline__ float sigmoid_exact(float x) {
   return x < 0.0f ? __fdiv_rn(e, 1.0f + e) : __fdiv_rn(1.0f, 1.0f + e);  // NaN falls through both compares
 }
 
-// sigmoid to about 1e-6 relative in some six instructions, for results that are rounded to 16-bit
-// storage anyway: e = 2^(24 - |x| log2 e) so that ex2.approx (which flushes subnormal results)
-// still resolves exp(-|x|) down to 2^-150; the bias is removed inside the reciprocal.
-__device__ __forceinline__ float sigmoid_fast(float x) {
+// sigmoid to about 1e-6 relative in five instructions, for results that are rounded to 16-bit storage
+// anyway: sigmoid(x) = 1 / (1 + 2^-t), t = x log2 e, evaluated as 2^-16 / (2^-16 + 2^(-t - 16)).  The
+// bias of 2^-16 keeps the exponential finite down to t = -144, so the quotient still resolves the
+// sigmoid where the CPU's expf underflows gradually (a 16-bit result of x * sigmoid(x) is zero below
+// that), and no branch or select separates the two signs of x.  Returns r with sigmoid(x) = r * 2^-16
+// (a sigmoid below 2^-126 is an f32 subnormal with fewer bits, still more than the 16-bit result keeps).
+// NaN propagates; -inf gives r = 0, +inf gives r = 2^16.
+constexpr float kSigmoidUnbias = 1.52587890625e-05f;  // 2^-16
+__device__ __forceinline__ float sigmoid_reciprocal(float x) {
   constexpr float kLog2e = 1.4426950408889634f;
-  constexpr float kBias = 16777216.0f;               // 2^24
-  constexpr float kUnbias = 5.9604644775390625e-8f;  // 2^-24
-  float e24;
-  asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(e24) : "f"(fmaf(-fabsf(x), kLog2e, 24.0f)));
+  float e;
+  asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(e) : "f"(fmaf(x, -kLog2e, -16.0f)));
   float r;
-  asm("rcp.approx.ftz.f32 %0, %1;" : "=f"(r) : "f"(fmaf(e24, kUnbias, 1.0f)));  // 1 / (1 + e), in (0.5, 1]
-  const float numerator = x < 0.0f ? e24 : kBias;    // 2^24 * (e or 1)
-  return __fmul_rn(numerator, __fmul_rn(r, kUnbias));
+  asm("rcp.approx.ftz.f32 %0, %1;" : "=f"(r) : "f"(__fadd_rn(e, kSigmoidUnbias)));
+  return r;
+}
+__device__ __forceinline__ float sigmoid_fast(float x) { return __fmul_rn(sigmoid_reciprocal(x), kSigmoidUnbias); }
+// x * sigmoid(x) with silu(-inf) = 0: the argument is held at -150 from below (max.NaN keeps a NaN), where
+// the sigmoid is zero already, so -inf * 0 never forms and no select is needed.
+__device__ __forceinline__ float silu_fast(float x) {
+  const float held = max_nan(x, -150.0f);
+  return __fmul_rn(held, sigmoid_fast(held));
 }
 
-// kFast (16-bit storage): the sigmoid-shaped kinds go through sigmoid_fast.  tanh(|x|) = 2 s(2|x|) - 1
+// kFast (16-bit storage): the sigmoid-shaped kinds go through sigmoid_reciprocal.  tanh(|x|) = 2 s(2|x|) - 1
 // cancels near zero, where the odd series takes over; gelu_tanh = x s(2 inner) needs no 1 + tanh.
 template <int kKind, bool kFast>
 __device__ __forceinline__ float unary_op(float x) {
   if constexpr (kFast && kKind == HYLE_B200_UNARY_SIGMOID) return sigmoid_fast(x);
-  if constexpr (kFast && kKind == HYLE_B200_UNARY_SILU) {
-    const float product = __fmul_rn(x, sigmoid_fast(x));  // unconditional: a select, not a branch
-    return x == -INFINITY ? 0.0f : product;
-  }
+  if constexpr (kFast && kKind == HYLE_B200_UNARY_SILU) return silu_fast(x);
   if constexpr (kFast && kKind == HYLE_B200_UNARY_GELU_TANH) {
-    const float inner = 0.79788456080286535588f * x * fmaf(0.044715f, x * x, 1.0f);
-    const float product = __fmul_rn(x, sigmoid_fast(2.0f * inner));
-    return x == -INFINITY ? 0.0f : product;
+    // 2 inner = 2 * 0.7978845608 * x * (1 + 0.044715 x^2) = x * (c1 + c2 x^2); the argument is held at -1e4
+    // from below, where the sigmoid is zero already (gelu(-inf) = 0 without a select)
+    const float held = max_nan(x, -1.0e4f);
+    const float twice_inner = __fmul_rn(held, fmaf(0.07135481627f, __fmul_rn(held, held), 1.59576912161f));
+    return __fmul_rn(held, sigmoid_fast(twice_inner));
   }
   if constexpr (kFast && kKind == HYLE_B200_UNARY_TANH) {
     const float a = fabsf(x), a2 = a * a;
@@ -330,16 +338,10 @@ int launch_unary(cudaStream_t stream, const void *in, void *out, uint64_t count)
 // silu(x) = x * sigmoid(x) with the overflow-free sigmoid of src/simd/math/activations.cc:21-25:
 // e = exp(-|x|); sigmoid = x < 0 ? e/(1+e) : 1/(1+e); silu(-inf) = 0 (:44-47).
 //
-// About fourteen instructions per element, two of them on the special-function unit.  The exponential is
-// carried with a 2^24 bias, e24 = 2^(24 - |x| log2 e), so that ex2.approx (which flushes subnormal
-// results) still resolves exp(-|x|) down to 2^-150, the range where the scalar expf of the
-// reference underflows gradually; the bias is removed inside the reciprocal.  Accuracy: about
-// 1e-6 relative, i.e. the result differs from the checker only when the bf16 rounding is within
-// that distance of a tie.
-__device__ __forceinline__ float silu(float x) {
-  const float product = __fmul_rn(x, sigmoid_fast(x));  // computed unconditionally: a select, not a branch
-  return x == -INFINITY ? 0.0f : product;               // -inf * 0 would be NaN
-}
+// About ten instructions per element, two of them on the special-function unit: see sigmoid_reciprocal
+// above.  Accuracy: about 1e-6 relative, i.e. the result differs from the checker only when the bf16
+// rounding is within that distance of a tie.
+__device__ __forceinline__ float silu(float x) { return silu_fast(x); }
 
 // GatedActivation{activation}: out = storage(act(f32 gate) * f32 up), one rounding
 // (src/compute_provider_native/aten_cpu_provider.cc:414-445,654-665).  With kRoundGate the activated
