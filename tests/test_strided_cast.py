@@ -92,6 +92,8 @@ def test_strided_cast_long_inner_runs(oracle, pair):
     def long_views(t):
         return {
             "inner_slice": t[..., 10:590],
+            "inner_slice_on_four_element_boundaries": t[..., 8:592],  # four elements per access
+            "inner_slice_of_every_other_row": t[:, ::2, :, 16:528],
             "inner_step": t[1, :, 2, ::2],
             "inner_is_a_permuted_axis": t[:, :, :, 5].permute(0, 2, 1),
             "inner_broadcast": t[:, :1, :, :1].expand(4, 3, 9, 1000),
