@@ -36,25 +36,47 @@ struct Words {
   uint32_t x0, x1, x2, x3;
 };
 
-__device__ __forceinline__ Words philox_block(const uint32_t *identity, uint64_t index) {
-  Words v{static_cast<uint32_t>(index), static_cast<uint32_t>(index >> 32), identity[2], identity[3]};
-  uint32_t key0 = identity[0], key1 = identity[1];
+// One widening multiply instruction gives both halves of a product.
+__device__ __forceinline__ uint64_t multiply_wide(uint32_t a, uint32_t b) {
+  uint64_t product;
+  asm("mul.wide.u32 %0, %1, %2;" : "=l"(product) : "r"(a), "r"(b));
+  return product;
+}
+
+// The ten round keys of one identity: the same for every block of its row.
+struct RoundKeys {
+  uint32_t k0[10], k1[10];
+};
+__device__ __forceinline__ RoundKeys round_keys(uint32_t key0, uint32_t key1) {
+  RoundKeys keys;
 #pragma unroll
   for (int round = 0; round < 10; ++round) {
-    // one widening multiply gives both halves of each product
-    const uint64_t p0 = static_cast<uint64_t>(0xd2511f53u) * v.x0, p1 = static_cast<uint64_t>(0xcd9e8d57u) * v.x2;
-    v = Words{static_cast<uint32_t>(p1 >> 32) ^ v.x1 ^ key0, static_cast<uint32_t>(p1),
-              static_cast<uint32_t>(p0 >> 32) ^ v.x3 ^ key1, static_cast<uint32_t>(p0)};
-    key0 += 0x9e3779b9u;
-    key1 += 0xbb67ae85u;
+    keys.k0[round] = key0 + static_cast<uint32_t>(round) * 0x9e3779b9u;
+    keys.k1[round] = key1 + static_cast<uint32_t>(round) * 0xbb67ae85u;
+  }
+  return keys;
+}
+__device__ __forceinline__ Words philox_rounds(Words v, const RoundKeys &keys) {
+#pragma unroll
+  for (int round = 0; round < 10; ++round) {
+    const uint64_t p0 = multiply_wide(0xd2511f53u, v.x0), p1 = multiply_wide(0xcd9e8d57u, v.x2);
+    v = Words{static_cast<uint32_t>(p1 >> 32) ^ v.x1 ^ keys.k0[round], static_cast<uint32_t>(p1),
+              static_cast<uint32_t>(p0 >> 32) ^ v.x3 ^ keys.k1[round], static_cast<uint32_t>(p0)};
   }
   return v;
 }
 
-constexpr int kBitsThreads = 256;
+__device__ __forceinline__ Words philox_block(const uint32_t *identity, uint64_t index) {
+  const Words v{static_cast<uint32_t>(index), static_cast<uint32_t>(index >> 32), identity[2], identity[3]};
+  return philox_rounds(v, round_keys(identity[0], identity[1]));
+}
 
+constexpr int kBitsThreads = 256;
+constexpr int kBitsSpan = 4;  // blocks per lane and span
+
+// Rows of few words (RandomBits{8}: two blocks per row): one block per thread, rows and blocks flattened.
 __global__ void __launch_bounds__(kBitsThreads)
-random_bits_kernel(const uint32_t *__restrict__ identities, uint32_t *out, uint64_t rows, uint32_t words) {
+random_bits_block_kernel(const uint32_t *__restrict__ identities, uint32_t *out, uint64_t rows, uint32_t words) {
   grid_dependency_sync();
   const uint64_t blocks_per_row = (static_cast<uint64_t>(words) + 3) / 4;
   const uint64_t total = rows * blocks_per_row;
@@ -71,6 +93,45 @@ random_bits_kernel(const uint32_t *__restrict__ identities, uint32_t *out, uint6
       if (left > 1) dst[1] = w.x1;
       if (left > 2) dst[2] = w.x2;
       if (left > 3) dst[3] = w.x3;
+    }
+  }
+}
+
+// Long rows: a warp takes kBitsSpan x 32 consecutive blocks of one row.  Lane l computes blocks l, l + 32, ...
+// of the span, so every store instruction of the warp writes 512 contiguous bytes, and the row's identity is
+// loaded and its ten round keys are formed once per span instead of once per block.
+__global__ void __launch_bounds__(kBitsThreads)
+random_bits_span_kernel(const uint32_t *__restrict__ identities, uint32_t *out, uint64_t rows, uint32_t words) {
+  grid_dependency_sync();
+  const uint32_t blocks_per_row = (words + 3) / 4;
+  const uint32_t spans_per_row = (blocks_per_row + kBitsSpan * 32 - 1) / (kBitsSpan * 32);
+  const uint64_t total = rows * spans_per_row;
+  const int lane = threadIdx.x & 31;
+  const uint64_t warps = static_cast<uint64_t>(gridDim.x) * (kBitsThreads / 32);
+  for (uint64_t span = static_cast<uint64_t>(blockIdx.x) * (kBitsThreads / 32) + threadIdx.x / 32; span < total; span += warps) {
+    const uint64_t row = span / spans_per_row;
+    const uint32_t first = static_cast<uint32_t>(span - row * spans_per_row) * (kBitsSpan * 32);
+    const uint32_t *identity = identities + row * 4;
+    const uint32_t id0 = identity[0], id1 = identity[1], id2 = identity[2], id3 = identity[3];
+    const RoundKeys keys = round_keys(id0, id1);
+    uint32_t *row_out = out + row * words;
+    const bool aligned = (reinterpret_cast<uintptr_t>(row_out) & 15) == 0;
+#pragma unroll
+    for (int k = 0; k < kBitsSpan; ++k) {
+      const uint32_t block = first + k * 32 + lane;
+      if (block < blocks_per_row) {
+        const Words w = philox_rounds(Words{block, 0u, id2, id3}, keys);
+        uint32_t *dst = row_out + static_cast<uint64_t>(block) * 4;
+        const uint32_t left = words - block * 4;
+        if (left >= 4 && aligned) {
+          *reinterpret_cast<uint4 *>(dst) = make_uint4(w.x0, w.x1, w.x2, w.x3);
+        } else {
+          dst[0] = w.x0;
+          if (left > 1) dst[1] = w.x1;
+          if (left > 2) dst[2] = w.x2;
+          if (left > 3) dst[3] = w.x3;
+        }
+      }
     }
   }
 }
@@ -400,9 +461,16 @@ extern "C" int hyle_b200_random_bits(hyle_b200_stream_t stream, const uint32_t *
   if (identities == nullptr || out == nullptr || word_count > 0x7fffffffu || !aligned_to(identities, 4) ||
       !aligned_to(out, 4))
     return HYLE_B200_INVALID_VALUE;
-  const uint64_t blocks = rows * ((static_cast<uint64_t>(word_count) + 3) / 4);
+  const uint64_t blocks_per_row = (static_cast<uint64_t>(word_count) + 3) / 4;
+  if (blocks_per_row >= kBitsSpan * 32) {  // rows of 512 words and more: warp spans
+    const uint64_t spans = rows * ((blocks_per_row + kBitsSpan * 32 - 1) / (kBitsSpan * 32));
+    const unsigned span_grid = clamp_grid((spans + kBitsThreads / 32 - 1) / (kBitsThreads / 32), static_cast<uint64_t>(sm_count()) * 8);
+    return launch(random_bits_span_kernel, dim3(span_grid), dim3(kBitsThreads), 0, reinterpret_cast<cudaStream_t>(stream),
+                  identities, out, rows, word_count);
+  }
+  const uint64_t blocks = rows * blocks_per_row;
   const unsigned grid = clamp_grid((blocks + kBitsThreads - 1) / kBitsThreads, static_cast<uint64_t>(sm_count()) * 8);
-  return launch(random_bits_kernel, dim3(grid), dim3(kBitsThreads), 0, reinterpret_cast<cudaStream_t>(stream), identities,
+  return launch(random_bits_block_kernel, dim3(grid), dim3(kBitsThreads), 0, reinterpret_cast<cudaStream_t>(stream), identities,
                 out, rows, word_count);
 }
 

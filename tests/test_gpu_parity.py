@@ -783,7 +783,7 @@ def _identities(rng, rows):
     return rng.integers(0, 2 ** 32, (rows, 4), dtype=np.uint64).astype(np.uint32)
 
 
-@pytest.mark.parametrize("words", [1, 3, 4, 7, 64, 1001])
+@pytest.mark.parametrize("words", [1, 3, 4, 7, 64, 508, 512, 1001, 2053, 4096])  # rows of 512 words and more take warp spans
 def test_random_bits_bit_exact(oracle, golden, words):
     rng = np.random.default_rng(words)
     identities = np.concatenate([golden["random_identities"], _identities(rng, 700)])
