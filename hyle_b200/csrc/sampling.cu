@@ -72,7 +72,7 @@ __device__ __forceinline__ Words philox_block(const uint32_t *identity, uint64_t
 }
 
 constexpr int kBitsThreads = 256;
-constexpr int kBitsSpan = 4;  // blocks per lane and span
+constexpr int kBitsSpan = 16;  // blocks per lane and span
 
 // Rows of few words (RandomBits{8}: two blocks per row): one block per thread, rows and blocks flattened.
 __global__ void __launch_bounds__(kBitsThreads)
@@ -462,7 +462,7 @@ extern "C" int hyle_b200_random_bits(hyle_b200_stream_t stream, const uint32_t *
       !aligned_to(out, 4))
     return HYLE_B200_INVALID_VALUE;
   const uint64_t blocks_per_row = (static_cast<uint64_t>(word_count) + 3) / 4;
-  if (blocks_per_row >= kBitsSpan * 32) {  // rows of 512 words and more: warp spans
+  if (blocks_per_row >= 128) {  // rows of 512 words and more: warp spans
     const uint64_t spans = rows * ((blocks_per_row + kBitsSpan * 32 - 1) / (kBitsSpan * 32));
     const unsigned span_grid = clamp_grid((spans + kBitsThreads / 32 - 1) / (kBitsThreads / 32), static_cast<uint64_t>(sm_count()) * 8);
     return launch(random_bits_span_kernel, dim3(span_grid), dim3(kBitsThreads), 0, reinterpret_cast<cudaStream_t>(stream),
