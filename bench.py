@@ -668,7 +668,7 @@ def numa_affinity(local_rank: int):
         return None, f"not pinned ({type(problem).__name__})"
 
 
-def pinned_copy_bandwidth(torch, chunk_bytes: int = 64 << 20, chunks: int = 8, together=None):
+def pinned_copy_bandwidth(torch, chunk_bytes: int = 64 << 20, chunks: int = 24, together=None):
     """GB/s of pinned-memory copies, one cudaMemcpyAsync per chunk: host->device alone, device->host alone,
     both directions at once on two streams, and both at once in the proportion of the end-to-end pass (per
     64 MiB copied in, 98 MiB copied out: the Q8_0 blocks and the decoded tensor), which is the copy-only
@@ -702,7 +702,7 @@ def pinned_copy_bandwidth(torch, chunk_bytes: int = 64 << 20, chunks: int = 8, t
     run(True, True)
     return {"h2d_GB/s": round(run(True, False), 2), "d2h_GB/s": round(run(False, True), 2),
             "both_GB/s": round(run(True, True), 2), "pass_mix_GB/s": round(run(True, True, out_chunk), 2),
-            "how": "pinned host memory, one cudaMemcpyAsync per chunk of 64 MiB (98 MiB out in the mix), eight chunks per direction"}
+            "how": f"pinned host memory, one cudaMemcpyAsync per chunk of 64 MiB (98 MiB out in the mix), {chunks} chunks per direction"}
 
 
 def time_host(call, repeats: int = 2) -> float:
