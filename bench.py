@@ -838,12 +838,14 @@ def small_shapes(torch, iterations: int = 200):
     return shapes
 
 
-def run_e2e(torch, ops, abi, shard_rows: int, steps: int, warmup: int):
+def run_e2e(torch, ops, abi, shard_rows: int, steps: int, warmup: int, copies_only: bool = False):
     """One pass from pinned host buffers through the C ABI and back, as a three-stage pipeline: a stream that
     only copies host -> device, one that only runs the kernel, one that only copies device -> host, chained
     per chunk by events over four rotating sets of device buffers.  Both copy directions therefore run all
     the time (chunks on one stream each would fall into step: all copying in, then all copying out).  Timed
-    with CUDA events from the first copy in to the last copy out."""
+    with CUDA events from the first copy in to the last copy out.  `copies_only` records the same pipeline
+    without the kernel launches: the same copies in the same order behind the same events, which is the
+    ceiling the host link sets for this pass."""
     chunk_rows = min(shard_rows, 4096, max(1024, shard_rows // 16))   # 64 MiB of bf16 per chunk, at least 16 chunks
     chunks = (shard_rows + chunk_rows - 1) // chunk_rows
     lanes = min(4, chunks)
@@ -881,10 +883,11 @@ def run_e2e(torch, ops, abi, shard_rows: int, steps: int, warmup: int):
                 compute.wait_event(arrived[lane])
                 if c >= lanes:
                     compute.wait_event(drained[lane])
-                abi.check("roundtrip", lib.hyle_b200_q8_0_roundtrip_bf16(
-                    compute.cuda_stream, dev_in[lane].data_ptr(), rows * SWEEP_COLS, dev_blocks[lane].data_ptr(),
-                    dev_decoded[lane].data_ptr(), dev_sums[c:].data_ptr(), None, workspaces[lane].data_ptr(),
-                    workspaces[lane].numel()))
+                if not copies_only:
+                    abi.check("roundtrip", lib.hyle_b200_q8_0_roundtrip_bf16(
+                        compute.cuda_stream, dev_in[lane].data_ptr(), rows * SWEEP_COLS, dev_blocks[lane].data_ptr(),
+                        dev_decoded[lane].data_ptr(), dev_sums[c:].data_ptr(), None, workspaces[lane].data_ptr(),
+                        workspaces[lane].numel()))
                 consumed[lane].record(compute)
                 produced[lane].record(compute)
             with torch.cuda.stream(copy_out):
@@ -1093,30 +1096,45 @@ def run_gpu(args):
     # step as it ran above.  step - slowest bare kernel = waiting for the slowest rank + the exchange.
     rank_split = None
     if world > 1:
-        # timed like the step itself: one pair of events around a run of launches (an event between two
-        # launches costs more than the exchange this split is looking for)
-        alone_launches = 20
-        first, last = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
-        for _ in range(3):
+        # Blocks of ten bare launches and ten whole steps take turns, so both see the same clocks (a block measured
+        # after the other would run under the power cap the first one provoked); each block is one pair of events
+        # around its run of launches (an event between two launches costs more than the exchange looked for).
+        def bare():
             lib.hyle_b200_q8_0_roundtrip_bf16(stream, w.data_ptr(), count, blocks.data_ptr(), decoded.data_ptr(),
                                               partial.data_ptr(), None, workspace.data_ptr(), workspace.numel())
-        torch.cuda.synchronize()
-        first.record()
-        for _ in range(alone_launches):
-            lib.hyle_b200_q8_0_roundtrip_bf16(stream, w.data_ptr(), count, blocks.data_ptr(), decoded.data_ptr(),
-                                              partial.data_ptr(), None, workspace.data_ptr(), workspace.numel())
-        last.record()
-        torch.cuda.synchronize()
-        mine = {"rank": rank, "kernel_alone_us": round(first.elapsed_time(last) / alone_launches * 1e3, 2),
-                "step_us": round(launch_ms * 1e3, 2)}
+
+        def whole():
+            step()
+            combine()
+
+        def block_ms(launch, launches=10):
+            first, last = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            first.record()
+            for _ in range(launches):
+                launch()
+            last.record()
+            last.synchronize()
+            return first.elapsed_time(last) / launches
+
+        alone_ms, whole_ms = [], []
+        for _ in range(4):
+            dist.barrier()
+            torch.cuda.synchronize()
+            alone_ms.append(block_ms(bare))
+            dist.barrier()
+            torch.cuda.synchronize()
+            whole_ms.append(block_ms(whole))
+        mine = {"rank": rank, "kernel_alone_us": round(statistics.mean(alone_ms) * 1e3, 2),
+                "step_us": round(statistics.mean(whole_ms) * 1e3, 2)}
         gathered = [None] * world
         dist.all_gather_object(gathered, mine)
         slowest = max(g["kernel_alone_us"] for g in gathered)
         rank_split = {"per_rank": gathered, "slowest_kernel_alone_us": slowest,
                       "step_us_max": max(g["step_us"] for g in gathered),
                       "wait_and_exchange_us": round(max(g["step_us"] for g in gathered) - slowest, 2),
-                      "note": "kernel_alone = the round trip without the exchange, a run of 20 launches timed per rank by one pair of CUDA events; "
-                              "step = the fused launch including the wait for the slowest rank's sum"}
+                      "note": "kernel_alone = the round trip without the exchange, step = the launch including the wait for the "
+                              "slowest rank's sum (and the library all-reduce where that is the exchange); blocks of ten launches "
+                              "of each kind taking turns, each block between one pair of CUDA events, mean of four blocks"}
 
     # end-to-end from host buffers (every rank moves its own shard).  The pinned staging is
     # 6.06 bytes per element; if that is more than a quarter of the free host memory per rank,
@@ -1142,12 +1160,17 @@ def run_gpu(args):
             if world > 1:
                 dist.barrier()
             e2e_seconds, h2d, d2h, _ = run_e2e(torch, ops, abi, e2e_rows, e2e_steps, 1)
+            if world > 1:
+                dist.barrier()
+            # the ceiling of that pass: the same pipeline without its kernels, all ranks at once
+            copies_seconds, _, _, _ = run_e2e(torch, ops, abi, e2e_rows, e2e_steps, 1, copies_only=True)
         finally:
             if previous_affinity is not None:
                 os.sched_setaffinity(0, previous_affinity)
     e2e_seconds *= shard.rows / e2e_rows
     h2d, d2h = h2d * shard.rows // e2e_rows, d2h * shard.rows // e2e_rows
-    e2e_t = torch.tensor([e2e_seconds], dtype=torch.float64, device="cuda")
+    e2e_t = torch.tensor([e2e_seconds, float("nan") if args.skip_e2e else copies_seconds * shard.rows / e2e_rows],
+                         dtype=torch.float64, device="cuda")
     if world > 1:
         dist.all_reduce(e2e_t, op=dist.ReduceOp.MAX)
 
@@ -1186,7 +1209,7 @@ def run_gpu(args):
                 "launch_us": kernel_s * 1e6,
                 "traffic": None if NCU_TRAFFIC_BYTES_PER_ELEMENT is None else NCU_TRAFFIC_BYTES_PER_ELEMENT * count}
 
-    e2e_seconds_max = float(e2e_t.item())
+    e2e_seconds_max, copies_seconds_max = float(e2e_t[0].item()), float(e2e_t[1].item())
     e2e = {"value": total_elements / e2e_seconds_max / 1e9, "unit": UNIT,
            "h2d_bytes_per_step": h2d * world, "d2h_bytes_per_step": d2h * world, "steps": e2e_steps,
            "rows_timed_per_gpu": e2e_rows, "rows_per_gpu": shard.rows, "host_threads_pinned": pinned_to}
@@ -1195,12 +1218,11 @@ def run_gpu(args):
         # the copies: its roofline is the same bytes in the same proportion as bare pinned copies, both
         # directions busy, all ranks at once, measured just before; the slowest rank's link bounds the step
         per_gpu = (h2d + d2h) / e2e_seconds_max / 1e9
-        peaks = copy_peaks if copy_peaks is not None else [copy_peak]
-        slowest_link = min(p["pass_mix_GB/s"] for p in peaks)
-        e2e["roofline"] = {"bound": "pcie (pinned host memory <-> device: the pass's own copies without the kernels, "
-                                    "64 MiB in and 98 MiB out per chunk on two streams)",
-                           "achieved": round(per_gpu, 2), "peak": slowest_link, "unit": "GB/s per GPU",
-                           "frac": round(per_gpu / slowest_link, 3), "copy_bandwidth": copy_peak,
+        ceiling = (h2d + d2h) / copies_seconds_max / 1e9
+        e2e["roofline"] = {"bound": "pcie (pinned host memory <-> device): the same pipeline recorded without its kernels -- "
+                                    "the same copies behind the same events, all ranks at once, max over ranks",
+                           "achieved": round(per_gpu, 2), "peak": round(ceiling, 2), "unit": "GB/s per GPU",
+                           "frac": round(per_gpu / ceiling, 3), "copy_bandwidth": copy_peak,
                            "copy_bandwidth_all_ranks_at_once": None if copy_peaks is None else
                            {"pass_mix_GB/s_per_rank": [p["pass_mix_GB/s"] for p in copy_peaks],
                             "both_GB/s_per_rank": [p["both_GB/s"] for p in copy_peaks],
