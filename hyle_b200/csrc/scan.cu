@@ -289,6 +289,65 @@ scan_rows_kernel(const T *__restrict__ in, T *__restrict__ out, uint64_t rows, u
   }
 }
 
+// Many short rows: a WARP per row.  A lane takes four consecutive values of each 128-value piece, kPieces
+// pieces (16: 8 KB of a row per warp) are loaded before the first is scanned (independent 16-byte loads in
+// flight: with one warp per row there are few warps, so each must keep many loads going), and a piece costs one
+// warp scan of the lanes' totals -- no shared memory and no barrier, which is what the CTA form above spends
+// most of its stalls on when a row is only a few of its chunks long.
+template <class T, class Acc, bool kVector, bool kExclusive>
+__global__ void __launch_bounds__(256)
+scan_rows_warp_kernel(const T *__restrict__ in, T *__restrict__ out, uint64_t rows, uint32_t cols, unsigned *status) {
+  grid_dependency_sync();
+  constexpr int kPieces = 16;
+  constexpr bool kChecked = !std::is_same<T, float>::value;  // the integer scan: decided by the pass before
+  if constexpr (kChecked) {
+    if ((*reinterpret_cast<volatile unsigned *>(status) & kScanOverflow) != 0) return;  // the check failed: no output
+  }
+  const unsigned lane = threadIdx.x % kWarpSize;
+  const uint64_t warps = static_cast<uint64_t>(gridDim.x) * (blockDim.x / kWarpSize);
+  for (uint64_t row = static_cast<uint64_t>(blockIdx.x) * (blockDim.x / kWarpSize) + threadIdx.x / kWarpSize; row < rows; row += warps) {
+    const T *row_in = in + row * cols;
+    T *row_out = out + row * cols;
+    Acc carry = 0;
+    for (uint32_t first = 0; first < cols; first += kPieces * 128) {
+      Quad<T> q[kPieces];
+#pragma unroll
+      for (int j = 0; j < kPieces; ++j) q[j] = load_quad<T, kVector, true>(row_in, first + j * 128 + lane * 4, cols);
+#pragma unroll
+      for (int j = 0; j < kPieces; ++j) {
+        const uint32_t at = first + j * 128 + lane * 4;
+        if (first + j * 128 >= cols) break;  // warp-uniform
+        Acc p[4];
+        p[0] = static_cast<Acc>(q[j].v[0]);
+#pragma unroll
+        for (int k = 1; k < 4; ++k) p[k] = p[k - 1] + static_cast<Acc>(q[j].v[k]);
+        const Acc through = warp_inclusive(p[3], lane);
+        // exclusive prefixes are fetched from the neighbour, never formed as "inclusive - own"
+        const Acc through_previous_lane = __shfl_up_sync(kFullMask, through, 1);
+        const Acc base = carry + (lane == 0 ? Acc(0) : through_previous_lane);
+        carry += __shfl_sync(kFullMask, through, kWarpSize - 1);
+        T result[4];
+        if constexpr (kExclusive) {
+          result[0] = static_cast<T>(base);
+#pragma unroll
+          for (int k = 1; k < 4; ++k) result[k] = static_cast<T>(base + p[k - 1]);
+        } else {
+#pragma unroll
+          for (int k = 0; k < 4; ++k) result[k] = static_cast<T>(base + p[k]);
+        }
+        store_quad<T, kVector>(row_out, at, cols, result);
+      }
+    }
+  }
+}
+
+template <class T, class Acc, bool kVector>
+int launch_scan_warp(cudaStream_t stream, const T *in, T *out, uint64_t rows, uint64_t cols, int exclusive, unsigned *status) {
+  const unsigned grid = clamp_grid((rows + 7) / 8, static_cast<uint64_t>(sm_count()) * 8);
+  return launch(exclusive ? scan_rows_warp_kernel<T, Acc, kVector, true> : scan_rows_warp_kernel<T, Acc, kVector, false>, dim3(grid),
+                dim3(256), 0, stream, in, out, rows, static_cast<uint32_t>(cols), status);
+}
+
 template <class T, class Acc, int kThreads, bool kVector, bool kWrite>
 int launch_scan(cudaStream_t stream, const T *in, T *out, uint64_t rows, uint64_t cols, int exclusive, unsigned *status,
                 unsigned ctas_per_sm) {
@@ -300,6 +359,9 @@ int launch_scan(cudaStream_t stream, const T *in, T *out, uint64_t rows, uint64_
 template <class T, class Acc, bool kWrite>
 int dispatch_scan(cudaStream_t stream, const T *in, T *out, uint64_t rows, uint64_t cols, int exclusive, unsigned *status) {
   const bool vector = cols % 4 == 0 && aligned_to(in, 16) && aligned_to(out, 16);
+  if (cols <= 16384 && rows >= static_cast<uint64_t>(sm_count()) * 8)  // many short rows: a warp each
+    return vector ? launch_scan_warp<T, Acc, true>(stream, in, out, rows, cols, exclusive, status)
+                  : launch_scan_warp<T, Acc, false>(stream, in, out, rows, cols, exclusive, status);
   // Wide CTAs when there are too few rows to fill the machine with narrow ones, or rows long
   // enough that a narrow CTA would spend its time on barriers.
   const bool wide = rows < static_cast<uint64_t>(sm_count()) * 8 || cols >= 32768;
