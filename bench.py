@@ -838,14 +838,16 @@ def small_shapes(torch, iterations: int = 200):
     return shapes
 
 
-def run_e2e(torch, ops, abi, shard_rows: int, steps: int, warmup: int, copies_only: bool = False):
+def run_e2e(torch, ops, abi, shard_rows: int, steps: int, warmup: int, copies_only: bool = False, together=None):
     """One pass from pinned host buffers through the C ABI and back, as a three-stage pipeline: a stream that
     only copies host -> device, one that only runs the kernel, one that only copies device -> host, chained
     per chunk by events over four rotating sets of device buffers.  Both copy directions therefore run all
     the time (chunks on one stream each would fall into step: all copying in, then all copying out).  Timed
     with CUDA events from the first copy in to the last copy out.  `copies_only` records the same pipeline
     without the kernel launches: the same copies in the same order behind the same events, which is the
-    ceiling the host link sets for this pass."""
+    ceiling the host link sets for this pass.  `together` (a barrier among the ranks) is called before every
+    timed pass: the ranks share the host's memory and links, so their passes must run at the same time for
+    the max over ranks to be the time of the job (buffer set-up takes each rank a different time)."""
     chunk_rows = min(shard_rows, 4096, max(1024, shard_rows // 16))   # 64 MiB of bf16 per chunk, at least 16 chunks
     chunks = (shard_rows + chunk_rows - 1) // chunk_rows
     lanes = min(4, chunks)
@@ -907,6 +909,8 @@ def run_e2e(torch, ops, abi, shard_rows: int, steps: int, warmup: int, copies_on
     torch.cuda.synchronize()
     seconds = 0.0
     for _ in range(steps):
+        if together is not None:
+            together()
         total, elapsed = one_pass()
         seconds += elapsed / steps
     torch.cuda.synchronize()
@@ -1159,11 +1163,10 @@ def run_gpu(args):
             copy_peak = pinned_copy_bandwidth(torch, together=dist.barrier if world > 1 else None)
             if world > 1:
                 dist.barrier()
-            e2e_seconds, h2d, d2h, _ = run_e2e(torch, ops, abi, e2e_rows, e2e_steps, 1)
-            if world > 1:
-                dist.barrier()
+            in_step = dist.barrier if world > 1 else None
+            e2e_seconds, h2d, d2h, _ = run_e2e(torch, ops, abi, e2e_rows, e2e_steps, 1, together=in_step)
             # the ceiling of that pass: the same pipeline without its kernels, all ranks at once
-            copies_seconds, _, _, _ = run_e2e(torch, ops, abi, e2e_rows, e2e_steps, 1, copies_only=True)
+            copies_seconds, _, _, _ = run_e2e(torch, ops, abi, e2e_rows, e2e_steps, 1, copies_only=True, together=in_step)
         finally:
             if previous_affinity is not None:
                 os.sched_setaffinity(0, previous_affinity)
